@@ -1,0 +1,112 @@
+"""Seeded golden cases shared by make_golden.py (which records the reference's answers)
+and by the tests (which replay them).  Inputs are never stored: they are regenerated
+from the seed, and the fixture keeps a SHA-256 of them to catch generator drift."""
+import hashlib
+
+import numpy as np
+import torch
+
+# name -> parameters of one reference run.  `lens` is the sequence of append() lengths.
+CASES = {
+    # tiny shapes: exercise ragged appends, decode steps, init-sink fill, LRU eviction
+    "tiny_mixed": dict(H=4, HKV=2, D=32, n_init=16, n_local=64, bs=16, max_cached=6, topk=3, exc=16,
+                       repr_topk=2, base=10000.0, lens=[100, 1, 1, 1, 77, 200, 1, 1, 33, 5] + [1] * 30,
+                       seed=11, strategy="lru", decay=None, qscale=1.0),
+    "tiny_mha": dict(H=4, HKV=4, D=32, n_init=8, n_local=48, bs=16, max_cached=8, topk=4, exc=32,
+                     repr_topk=1, base=10000.0, lens=[17, 150, 3, 90, 1, 1, 1, 240],
+                     seed=12, strategy="lru", decay=None, qscale=1.0),
+    "tiny_lru_s": dict(H=4, HKV=1, D=32, n_init=16, n_local=64, bs=16, max_cached=5, topk=3, exc=16,
+                       repr_topk=3, base=10000.0, lens=[400, 1, 1], seed=13, strategy="lru-s", decay=0.9,
+                       qscale=1.0),
+    # total thrash: max_cached == topk, every exec block evicts (shape of the cache-stress config)
+    "tiny_thrash": dict(H=4, HKV=2, D=32, n_init=16, n_local=64, bs=16, max_cached=3, topk=3, exc=64,
+                        repr_topk=2, base=10000.0, lens=[500, 1, 300], seed=14, strategy="lru", decay=None,
+                        qscale=1.5),
+    # head_dim 128 / block 128: the shapes the CUDA path runs
+    "d128_prefill": dict(H=8, HKV=2, D=128, n_init=128, n_local=512, bs=128, max_cached=6, topk=4, exc=128,
+                         repr_topk=4, base=1000000.0, lens=[1536, 700, 1, 1, 1], seed=21, strategy="lru",
+                         decay=None, qscale=1.0),
+    "d128_ragged": dict(H=4, HKV=4, D=128, n_init=64, n_local=256, bs=128, max_cached=4, topk=2, exc=256,
+                        repr_topk=2, base=500000.0, lens=[333, 1, 1, 900, 77, 1, 1, 1, 1, 640], seed=22,
+                        strategy="lru", decay=None, qscale=1.3),
+    "d128_decode": dict(H=8, HKV=2, D=128, n_init=128, n_local=256, bs=128, max_cached=8, topk=4, exc=128,
+                        repr_topk=4, base=1000000.0, lens=[1400] + [1] * 150, seed=23, strategy="lru",
+                        decay=None, qscale=1.0),
+}
+
+PROJ_SEED = 12345
+N_PROJ = 8
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """Round fp32 values to the nearest bf16-representable fp32 (so bf16 and fp32 runs see equal inputs)."""
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+def make_inputs(case: dict):
+    """List of (q (H,L,D), k (H_kv,L,D), v (H_kv,L,D)) fp32 torch tensors, one per append."""
+    rng = np.random.default_rng(case["seed"])
+    out = []
+    for L in case["lens"]:
+        q = bf16_round(rng.standard_normal((case["H"], L, case["D"]), dtype=np.float32) * case["qscale"])
+        k = bf16_round(rng.standard_normal((case["HKV"], L, case["D"]), dtype=np.float32))
+        v = bf16_round(rng.standard_normal((case["HKV"], L, case["D"]), dtype=np.float32))
+        out.append((torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v)))
+    return out
+
+
+def inputs_digest(inputs) -> str:
+    h = hashlib.sha256()
+    for q, k, v in inputs:
+        for t in (q, k, v):
+            h.update(t.numpy().tobytes())
+    return h.hexdigest()
+
+
+def projection(width: int) -> torch.Tensor:
+    """Fixed random (width, N_PROJ) float64 matrix: a compact high-precision fingerprint of each row."""
+    rng = np.random.default_rng(PROJ_SEED + width)
+    return torch.from_numpy(rng.standard_normal((width, N_PROJ)))
+
+
+def project_rows(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(x.shape[0], -1).to(torch.float64)
+    return x2 @ projection(x2.shape[1])
+
+
+def sample_rows(n: int, limit: int = 96) -> torch.Tensor:
+    """Row indices whose fp16 values are stored in full (all rows when there are few)."""
+    if n <= limit:
+        return torch.arange(n)
+    return torch.unique(torch.linspace(0, n - 1, limit).round().long())
+
+
+# direct cases of the multi-stage attention class: (H, H_kv, D, Lq, [(Lk, sliding_window, complement, get_score)])
+MULTI_STAGE_SPECS = [
+    (4, 2, 32, 5, [(37, 16, False, True), (9, (40, 16), True, False)]),
+    (2, 2, 64, 1, [(20, 8, False, True), (0, None, False, False), (12, None, False, True)]),
+    (4, 2, 128, 70, [(200, 128, False, True), (300, (250, 128), True, True)]),
+    (4, 1, 128, 33, [(33, None, False, True)]),
+    (2, 2, 128, 129, [(257, 64, False, True), (128, (300, 64), True, False), (5, (3, 2), True, True)]),
+    (4, 1, 128, 1, [(300, 256, False, True), (140, None, False, False)]),
+]
+
+
+def multi_stage_inputs(ci: int):
+    """[(q (H,Lq,D), k (H_kv,Lk,D), v)] per stage of case ci, bf16-representable fp32."""
+    H, HKV, D, Lq, stages = MULTI_STAGE_SPECS[ci]
+    rng = np.random.default_rng(7700 + ci)
+    out = []
+    for (Lk, _, _, _) in stages:
+        q = torch.from_numpy(bf16_round(rng.standard_normal((H, Lq, D), dtype=np.float32)))
+        k = torch.from_numpy(bf16_round(rng.standard_normal((HKV, Lk, D), dtype=np.float32)))
+        v = torch.from_numpy(bf16_round(rng.standard_normal((HKV, Lk, D), dtype=np.float32)))
+        out.append((q, k, v))
+    return out
+
+
+def rope_inputs():
+    rng = np.random.default_rng(7799)
+    q = torch.from_numpy(rng.standard_normal((2, 7, 128), dtype=np.float32))
+    k = torch.from_numpy(rng.standard_normal((2, 300, 128), dtype=np.float32))
+    return q, k
