@@ -1,0 +1,228 @@
+/*
+ * infllm_b200 — C ABI of the B200 (sm_100a) context-memory attention library.
+ *
+ * The reference (thunlp/InfLLM) is pure Python and has no FFI.  This header is the native
+ * boundary that the Python drop-in classes (infllm_b200.attention.ContextManager,
+ * CudaMultiStageDotProductionAttention, RotaryEmbeddingESM) bind with ctypes.  Each entry
+ * point names the reference code it replaces, as file:line inside the reference repository.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative INFLLM_E_* code; nothing throws,
+ *     aborts or traps.  infllm_last_error() gives the message of the calling thread's last error.
+ *   - pointers named d_* are device pointers, h_* host pointers.  `stream` is a cudaStream_t
+ *     passed as void*; work is enqueued on it and the call returns without synchronising unless
+ *     stated otherwise.  The caller owns every buffer it passes in.
+ *   - activations are bf16 (INFLLM_BF16) or fp16 (INFLLM_FP16); accumulators are fp32.
+ *   - tensor layouts are given as (dims) with explicit element strides where the caller may
+ *     pass a view; head_dim is always contiguous.
+ */
+#ifndef INFLLM_B200_H
+#define INFLLM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INFLLM_OK 0
+#define INFLLM_E_BADARG (-1)    /* a size, stride or pointer is not acceptable */
+#define INFLLM_E_CAPACITY (-2)  /* e.g. max_cached_block < topk: the reference asserts in CudaCache.alloc
+                                   (inf_llm/attention/context_manager.py:19) */
+#define INFLLM_E_CUDA (-3)      /* a CUDA runtime call failed; message holds cudaGetErrorString */
+#define INFLLM_E_TIMEOUT (-4)   /* a bounded wait ran out */
+#define INFLLM_E_UNSUPPORTED (-5)
+#define INFLLM_E_NOMEM (-6)
+
+#define INFLLM_BF16 0
+#define INFLLM_FP16 1
+
+#define INFLLM_CACHE_LRU 0   /* cache_strategy "lru"   (context_manager.py:504-508) */
+#define INFLLM_CACHE_LRU_S 1 /* cache_strategy "lru-s" (context_manager.py:454-470, 510-513) */
+
+/* mask modes of one attention stage (torch_impl.py:60-78) */
+#define INFLLM_MASK_NONE 0
+#define INFLLM_MASK_WINDOW 1     /* keep 0 <= i - j + offset < size */
+#define INFLLM_MASK_COMPLEMENT 2 /* keep i - j + offset >= size */
+
+const char* infllm_last_error(void);
+/* Library build information: "infllm_b200 <version> sm_100a". */
+const char* infllm_version(void);
+
+/* ------------------------------------------------------------------ RoPE
+ * Replaces RotaryEmbeddingESM (inf_llm/attention/rope.py:4-112).
+ * infllm_rope_table: fp32 cos/sin of angle = (t * scale) * inv_freq[f], t in [0, length), f in
+ *   [0, head_dim/2); d_cos/d_sin are (length, head_dim/2) (rope.py:49-65; the reference stores the
+ *   halves duplicated).  h_inv_freq holds head_dim/2 fp32 values (rope.py:22-24).
+ * infllm_rope_apply: out[h, t, :] = x[h, t, :] rotated to position pos0 + t * pos_step (pos_step 0
+ *   gives the "one angle" form of rope.py:89-104; pos_step 1 the window-relative form of
+ *   rope.py:35-47, 107-112).  Math in fp32, result rounded to `dtype` like the reference.
+ *   x is (n_heads, len, head_dim) with element strides x_hs (head) and x_ts (token); out likewise. */
+int infllm_rope_table(const float* h_inv_freq, float scale, int head_dim, int64_t length,
+                      float* d_cos, float* d_sin, void* stream);
+int infllm_rope_apply(const void* d_x, int64_t x_hs, int64_t x_ts, void* d_out, int64_t o_hs, int64_t o_ts,
+                      int n_heads, int64_t len, int head_dim, const float* d_cos, const float* d_sin,
+                      int64_t table_len, int64_t pos0, int pos_step, int dtype, void* stream);
+
+/* ------------------------------------------------- multi-stage attention
+ * Replaces MultiStageDotProductionAttention.append / get_result
+ * (inf_llm/attention/dot_production_attention/base.py:3-30, torch_impl.py:15-96,
+ * triton_impl.py:403-556): attention that is normalised jointly over several append()ed stages.
+ *
+ * State carried between stages, owned by the caller: d_acc (n_heads, lq, head_dim) fp32 un-normalised
+ * output, d_m (n_heads, lq) fp32 running row maximum in the log2 domain, d_l (n_heads, lq) fp32
+ * running denominator.
+ *
+ * infllm_attn_stage: fold one stage into the state.  first != 0 starts from an empty state (the
+ *   buffers need not be initialised).  q (n_heads, lq, head_dim), k/v (n_kv_heads, lk, head_dim)
+ *   with head/token element strides; lk may be 0.  mask_mode/mask_offset/mask_size as above, with
+ *   i the query row and j the key row of this stage.
+ * infllm_attn_finalize: out = acc / l in `dtype`, d_lse (n_heads, lq) fp32 = log-sum-exp of every row
+ *   in the log2 domain (row with no visible key: out 0, lse -inf).
+ * infllm_attn_colsum: per-key score of one stage = sum over queries of the jointly normalised
+ *   probability (torch_impl.py:27-30; triton_impl.py:231-401), computed from the final d_lse.
+ *   d_score is (n_heads, lk) fp32 with head stride score_hs; accumulate != 0 adds into it. */
+int infllm_attn_stage(const void* d_q, int64_t q_hs, int64_t q_ts,
+                      const void* d_k, int64_t k_hs, int64_t k_ts,
+                      const void* d_v, int64_t v_hs, int64_t v_ts,
+                      int n_heads, int n_kv_heads, int64_t lq, int64_t lk, int head_dim,
+                      int mask_mode, int64_t mask_offset, int64_t mask_size,
+                      float* d_acc, float* d_m, float* d_l, int first, int dtype, void* stream);
+int infllm_attn_finalize(const float* d_acc, const float* d_m, const float* d_l,
+                         void* d_out, int64_t o_hs, int64_t o_ts, float* d_lse,
+                         int n_heads, int64_t lq, int head_dim, int dtype, void* stream);
+int infllm_attn_colsum(const void* d_q, int64_t q_hs, int64_t q_ts,
+                       const void* d_k, int64_t k_hs, int64_t k_ts,
+                       int n_heads, int n_kv_heads, int64_t lq, int64_t lk, int head_dim,
+                       int mask_mode, int64_t mask_offset, int64_t mask_size,
+                       const float* d_lse, float* d_score, int64_t score_hs, int accumulate,
+                       int dtype, void* stream);
+
+/* ------------------------------------------------------ retrieval kernels
+ * infllm_block_topk replaces calc_block_topk / VectorTensor.get_topk
+ *   (context_manager.py:366-383, 159-163): scores[b] = <block_k[b, :], qbar> for b < n_blocks
+ *   (fp32 accumulation), then the k highest in descending order, ties to the lower id.
+ *   d_block_k (n_blocks, width) in `dtype`, row stride `width`; d_qbar (width) fp32.
+ *   d_scores (n_blocks) fp32 scratch/out; d_out_ids (k) int32; d_out_scores (k) fp32 (may be NULL).
+ *   id_base is added to every id written (unit-range sharding).  k <= 1024.
+ * infllm_repr_select replaces get_block_k + mean (context_manager.py:268-277, 664-670): for each of
+ *   n_new consecutive blocks of block_size tokens starting at row tok0 of d_k, and each query
+ *   head h, the repr_topk tokens with the largest d_score[h, tok] (ties to the lower token) are
+ *   gathered from K head h / (n_heads / n_kv_heads) and averaged; rows written to
+ *   d_block_k_out (n_new, n_heads * head_dim) in `dtype`. */
+int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int width, const float* d_qbar,
+                      float* d_scores, int k, int id_base, int32_t* d_out_ids, float* d_out_scores,
+                      int dtype, void* stream);
+int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float* d_score, int64_t score_hs,
+                       int64_t tok0, int n_new, int block_size, int repr_topk,
+                       int n_heads, int n_kv_heads, int head_dim, void* d_block_k_out, int dtype,
+                       void* stream);
+
+/* ---------------------------------------------------------- decode attention
+ * Split-K attention of ONE query token per head over a list of key/value segments, followed by a
+ * log-sum-exp merge; replaces the two attn.append calls of ContextManager._append
+ * (context_manager.py:486-489, 526-531) when the exec block is a single token.
+ * Segment s: keys/values (n_kv_heads, seg_len[s], head_dim), tokens contiguous, at h_seg_k[s] / h_seg_v[s]
+ * (device pointers) with head stride h_seg_hs[s] elements; h_seg_q[s] selects the query variant
+ * (0: d_q0, 1: d_q1) — the local stage uses the window-relative rotation, the global stage the
+ * one-angle rotation.  The h_seg_* arrays are HOST arrays of n_seg <= INFLLM_MAX_SEGMENTS entries.
+ * The keys are cut into chunks of 128; every chunk yields one partial: normalised output
+ * d_part_o (max_parts, n_heads, head_dim) fp32 and log2-domain log-sum-exp d_part_lse (max_parts,
+ * n_heads); *n_parts receives how many were written (infllm_attn_decode_max_parts bounds it).
+ * logit_seg >= 0 also exports that segment's scaled log2-domain logits to d_logits (n_heads, seg_len).
+ * infllm_lse_merge combines n_part partials into out (n_heads, head_dim) in `dtype` (head stride o_hs)
+ * and d_lse (n_heads, may be NULL): the same merge serves the chunks of one GPU and the per-rank
+ * partials gathered from several GPUs (unit-range sharding). */
+#define INFLLM_MAX_SEGMENTS 80
+int64_t infllm_attn_decode_max_parts(int n_seg, int64_t total_keys);
+int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim,
+                       int n_seg, const void* const* h_seg_k, const void* const* h_seg_v,
+                       const int64_t* h_seg_hs, const int32_t* h_seg_len, const int32_t* h_seg_q,
+                       float* d_part_o, float* d_part_lse, int max_parts, int* n_parts,
+                       int logit_seg, float* d_logits, int dtype, void* stream);
+int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads, int head_dim,
+                     void* d_out, int64_t o_hs, float* d_lse, int dtype, void* stream);
+
+/* ------------------------------------------------------------ context memory
+ * One infllm_ctx is the native state of one batch element ("unit") of the reference's
+ * ContextManager (context_manager.py:196-816): token buffers for the local window and the
+ * un-sealed remainder, the init sink, representative keys, the pinned host store of sealed
+ * memory units, the GPU cache of max_cached_block units with LRU replacement, and the
+ * exec-block loop of append() (context_manager.py:682-813, _append :474-545, append_global
+ * :614-679). */
+typedef struct infllm_ctx infllm_ctx;
+
+typedef struct infllm_config {
+  int32_t n_heads, n_kv_heads, head_dim;
+  int32_t n_init, n_local, block_size, max_cached_block, topk, exc_block_size, repr_topk;
+  int32_t cache_strategy; /* INFLLM_CACHE_* */
+  int32_t dtype;          /* INFLLM_BF16 / INFLLM_FP16 */
+  float score_decay;      /* lru-s only */
+  float rope_base, rope_scale;
+  int32_t device;         /* CUDA device ordinal */
+  int32_t shard_rank, shard_world; /* unit-range sharding of the store; 0,1 = not sharded */
+  int32_t reserved[6];
+} infllm_config;
+
+/* Validates the configuration (exc_block_size <= n_local, context_manager.py:219;
+ * max_cached_block >= topk, context_manager.py:19 -> INFLLM_E_CAPACITY) and allocates nothing
+ * large: buffers are created on the first append (context_manager.py:292-363). */
+int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out);
+int infllm_ctx_destroy(infllm_ctx* ctx);
+/* Forget every token but keep the allocations (device buffers, pinned host store). */
+int infllm_ctx_reset(infllm_ctx* ctx);
+
+/* ContextManager.append (context_manager.py:682-813) for one unit: q (n_heads, len, head_dim) and
+ * k, v (n_kv_heads, len, head_dim), un-rotated, element strides given; out (n_heads, len, head_dim).
+ * Runs every exec block of the call; synchronises with the host once per exec block that has more
+ * sealed units than topk (the retrieved ids are needed to plan the cache), otherwise asynchronous. */
+int infllm_ctx_append(infllm_ctx* ctx, const void* d_q, int64_t q_hs, int64_t q_ts,
+                      const void* d_k, int64_t k_hs, int64_t k_ts,
+                      const void* d_v, int64_t v_hs, int64_t v_ts,
+                      void* d_out, int64_t o_hs, int64_t o_ts, int64_t len, void* stream);
+
+/* Introspection (what the reference keeps as Python attributes). */
+typedef struct infllm_ctx_info {
+  int64_t length;        /* ContextManager.length (context_manager.py:211, 793, 815) */
+  int64_t frontier;      /* first token not yet in the init sink or a sealed unit */
+  int64_t num_blocks;    /* num_global_block (:319, 673) */
+  int64_t init_len;      /* init_k.size(-2) (:341, 628-646) */
+  int64_t num_cached;    /* len(cached_blocks[u]) */
+  int64_t load_count;    /* LRU clock (:226, 505) */
+  int64_t exec_blocks;   /* exec blocks run by the last append */
+  int64_t h2d_bytes, d2h_bytes; /* store traffic since create/reset */
+  int64_t cache_hits, cache_misses, evictions;
+} infllm_ctx_info;
+int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
+/* cached_blocks[u] in dict order: ids and stamps (LRU clock, or lru-s score). Returns count in *n. */
+int infllm_ctx_get_cached(infllm_ctx* ctx, int32_t* h_ids, double* h_stamps, int cap, int* n);
+/* Retrieval of exec block `eb` of the last append, in the order the scorer returned it. */
+int infllm_ctx_get_topk(infllm_ctx* ctx, int64_t eb, int32_t* h_ids, int cap, int* n);
+/* Copies representative-key rows [b0, b0+n) (n_heads*head_dim each, `dtype`) to a host buffer; synchronises. */
+int infllm_ctx_get_block_k(infllm_ctx* ctx, int64_t b0, int64_t n, void* h_dst);
+/* Test/bench hook: install a synthetic store without running a prefill (decode-only workloads):
+ * n_units sealed units whose K/V the library reads from h_units (n_units, 2, n_kv_heads, block_size,
+ * head_dim) — copied into the pinned store — representative keys from h_block_k (n_units, n_heads*head_dim),
+ * an init sink (n_kv_heads, n_init, head_dim) x2 and a local window (n_kv_heads, n_local, head_dim) x2,
+ * all in `dtype` on the host.  length becomes n_init + n_units*block_size + n_local. */
+int infllm_ctx_load_synthetic(infllm_ctx* ctx, int64_t n_units, const void* h_units, const void* h_block_k,
+                              const void* h_init_k, const void* h_init_v, const void* h_win_k,
+                              const void* h_win_v, void* stream);
+
+/* ----------------------------------------------------- host logic, GPU-free
+ * The LRU table alone (context_manager.py:246-265, 495-515): dict-ordered ids with stamps.
+ * Exposed so that the eviction order can be tested without a device. */
+typedef struct infllm_lru infllm_lru;
+int infllm_lru_create(int capacity, infllm_lru** out);
+int infllm_lru_destroy(infllm_lru* t);
+/* Evicts for `wanted` (n ids), writes evicted ids (in eviction order) to h_evicted (cap n_cached), count to *n_evicted. */
+int infllm_lru_plan(infllm_lru* t, const int32_t* wanted, int n, int32_t* h_evicted, int* n_evicted);
+int infllm_lru_stamp(infllm_lru* t, const int32_t* wanted, int n, double value);
+int infllm_lru_scale(infllm_lru* t, double factor);             /* lru-s decay */
+int infllm_lru_add(infllm_lru* t, int32_t id, double value);    /* lru-s score add */
+int infllm_lru_items(infllm_lru* t, int32_t* h_ids, double* h_stamps, int cap, int* n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFLLM_B200_H */

@@ -1,0 +1,135 @@
+"""ctypes binding of libinfllm_b200.so (the C ABI declared in include/infllm_b200.h).
+
+The library is the product: there is no Python or CPU fallback.  If it has not been built
+(`python -m infllm_b200.build`) importing this module raises ImportError.
+"""
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libinfllm_b200.so")
+
+OK, E_BADARG, E_CAPACITY, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_NOMEM = 0, -1, -2, -3, -4, -5, -6
+BF16, FP16 = 0, 1
+CACHE_LRU, CACHE_LRU_S = 0, 1
+MASK_NONE, MASK_WINDOW, MASK_COMPLEMENT = 0, 1, 2
+MAX_SEGMENTS = 80
+
+
+class InfLLMError(RuntimeError):
+    """A call into libinfllm_b200 returned an error code."""
+
+    def __init__(self, code, message):
+        super().__init__(f"infllm_b200 error {code}: {message}")
+        self.code = code
+
+
+class InfLLMCapacityError(InfLLMError, AssertionError):
+    """The cache cannot hold a retrieval (the reference asserts in CudaCache.alloc)."""
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
+        ("n_init", c_int32), ("n_local", c_int32), ("block_size", c_int32), ("max_cached_block", c_int32),
+        ("topk", c_int32), ("exc_block_size", c_int32), ("repr_topk", c_int32),
+        ("cache_strategy", c_int32), ("dtype", c_int32),
+        ("score_decay", c_float), ("rope_base", c_float), ("rope_scale", c_float),
+        ("device", c_int32), ("shard_rank", c_int32), ("shard_world", c_int32),
+        ("reserved", c_int32 * 6),
+    ]
+
+
+class CtxInfo(ctypes.Structure):
+    _fields_ = [(n, c_int64) for n in (
+        "length", "frontier", "num_blocks", "init_len", "num_cached", "load_count", "exec_blocks",
+        "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions")]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "infllm_last_error": (c_char_p, []),
+    "infllm_version": (c_char_p, []),
+    "infllm_rope_table": (c_int, [POINTER(c_float), c_float, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "infllm_rope_apply": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,
+                                  c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "infllm_attn_stage": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                  c_int, c_int, c_int64, c_int64, c_int, c_int, c_int64, c_int64,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "infllm_attn_finalize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
+                                     c_int, c_int64, c_int, c_int, c_void_p]),
+    "infllm_attn_colsum": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int64,
+                                   c_int64, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int,
+                                   c_int, c_void_p]),
+    "infllm_block_topk": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                  c_int, c_void_p]),
+    "infllm_repr_select": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "infllm_attn_decode_max_parts": (c_int64, [c_int, c_int64]),
+    "infllm_attn_decode": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p),
+                                   POINTER(c_void_p), POINTER(c_int64), POINTER(c_int32), POINTER(c_int32),
+                                   c_void_p, c_void_p, c_int, POINTER(c_int), c_int, c_void_p, c_int, c_void_p]),
+    "infllm_lse_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int,
+                                 c_void_p]),
+    "infllm_ctx_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),
+    "infllm_ctx_destroy": (c_int, [c_void_p]),
+    "infllm_ctx_reset": (c_int, [c_void_p]),
+    "infllm_ctx_append": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                  c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "infllm_ctx_get_info": (c_int, [c_void_p, POINTER(CtxInfo)]),
+    "infllm_ctx_get_cached": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_double), c_int, POINTER(c_int)]),
+    "infllm_ctx_get_topk": (c_int, [c_void_p, c_int64, POINTER(c_int32), c_int, POINTER(c_int)]),
+    "infllm_ctx_get_block_k": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),
+    "infllm_ctx_load_synthetic": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p]),
+    "infllm_lru_create": (c_int, [c_int, POINTER(c_void_p)]),
+    "infllm_lru_destroy": (c_int, [c_void_p]),
+    "infllm_lru_plan": (c_int, [c_void_p, POINTER(c_int32), c_int, POINTER(c_int32), POINTER(c_int)]),
+    "infllm_lru_stamp": (c_int, [c_void_p, POINTER(c_int32), c_int, c_double]),
+    "infllm_lru_scale": (c_int, [c_void_p, c_double]),
+    "infllm_lru_add": (c_int, [c_void_p, c_int32, c_double]),
+    "infllm_lru_items": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_double), c_int, POINTER(c_int)]),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build the CUDA library first (python -m infllm_b200.build). "
+        "infllm_b200 has no fallback implementation.")
+
+lib = ctypes.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here means the library is stale
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(rc):
+    """Raise for a non-zero return code of the C ABI."""
+    if rc == OK:
+        return
+    msg = lib.infllm_last_error().decode("utf-8", "replace")
+    if rc == E_CAPACITY:
+        raise InfLLMCapacityError(rc, msg)
+    raise InfLLMError(rc, msg)
+
+
+def dtype_code(dtype):
+    import torch
+
+    if dtype == torch.bfloat16:
+        return BF16
+    if dtype == torch.float16:
+        return FP16
+    raise TypeError(f"infllm_b200 kernels take bfloat16 or float16 activations, got {dtype}")
+
+
+def stream_ptr(device=None):
+    import torch
+
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(t, what):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor: infllm_b200 has no CPU path")

@@ -1,0 +1,14 @@
+"""Attention-forward registry with the reference's names (inf_llm/attention/__init__.py:8-13;
+the misspelt ATTN_FORWRAD is the reference's public name)."""
+from .context_manager import ContextManager
+from .dot_production_attention import CudaMultiStageDotProductionAttention, get_multi_stage_dot_production_attention
+from .inf_llm import inf_llm_forward
+from .rope import RotaryEmbeddingESM
+
+ATTN_FORWRAD = {
+    "inf-llm": inf_llm_forward,
+}
+ATTN_FORWARD = ATTN_FORWRAD
+
+__all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward",
+           "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention"]

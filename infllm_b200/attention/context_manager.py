@@ -1,0 +1,173 @@
+"""ContextManager with the interface of the reference (inf_llm/attention/context_manager.py:196-816).
+
+The state and the exec-block loop live in libinfllm_b200 (one native context per batch element,
+see include/infllm_b200.h); this class validates arguments the way the reference does, feeds
+tensors in and exposes the reference's observable attributes."""
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+
+class ContextManager:
+    """Per-layer context memory: sliding local window, init sink, sealed memory units with
+    representative keys, top-k retrieval, a GPU cache of max_cached_block units with LRU
+    replacement over a pinned host store.
+
+    Constructor arguments are those of the reference (context_manager.py:197-209).  `fattn` and
+    `async_global_stream` are accepted and ignored: there is one attention implementation, and the
+    host store always refills on a side stream.  `faiss` and `chunk_topk_calc` are not built."""
+
+    def __init__(self, position_embedding, n_init, n_local, block_size, max_cached_block, topk, exc_block_size,
+                 score_decay: Optional[float] = None, fattn: bool = False, repr_topk: int = 1,
+                 cache_strategy="lru", chunk_topk_calc: Optional[int] = None, async_global_stream: bool = False,
+                 pin_memory: bool = False, faiss: bool = False, perhead: bool = False):
+        self.length = 0
+        self.position_embedding = position_embedding
+        self.n_init = n_init
+        self.n_local = n_local
+        self.block_size = block_size
+        self.max_cached_block = max_cached_block
+        self.exc_block_size = exc_block_size
+        self.score_decay = score_decay
+        assert exc_block_size <= n_local  # context_manager.py:219
+        self.topk = topk
+        self.fattn = fattn
+        self.initialized = False
+        self.repr_topk = repr_topk
+        self.cache_strategy = cache_strategy
+        self.chunk_topk_calc = chunk_topk_calc
+        self.async_global_stream = async_global_stream
+        self.pin_memory = pin_memory
+        self.faiss = faiss
+        self.perhead = perhead
+        assert cache_strategy in ["lru", "lru-s"]  # context_manager.py:238
+        if faiss:
+            raise NotImplementedError("faiss retrieval is not built (the reference needs the faiss package for it)")
+        if chunk_topk_calc is not None:
+            raise NotImplementedError("chunk_topk_calc (batched top-k) is not built")
+        self._ctx = []  # native contexts, one per unit
+
+    # -- native contexts
+    def _init(self, q, k):
+        batch, heads, _, dim = q.shape
+        heads_kv = k.size(1)
+        self.batch_size, self.num_heads, self.num_heads_kv, self.dim_head = batch, heads, heads_kv, dim
+        if self.perhead:  # context_manager.py:690-704: every head is its own unit
+            self.num_units, self.unit_size, self.unit_size_kv = batch * heads, 1, 1
+        else:
+            self.num_units, self.unit_size, self.unit_size_kv = batch, heads, heads_kv
+        self.dtype = q.dtype
+        self.device = q.device
+        pe = self.position_embedding
+        cfg = _lib.Config(
+            n_heads=self.unit_size, n_kv_heads=self.unit_size_kv, head_dim=dim, n_init=self.n_init,
+            n_local=self.n_local, block_size=self.block_size, max_cached_block=self.max_cached_block, topk=self.topk,
+            exc_block_size=self.exc_block_size, repr_topk=self.repr_topk,
+            cache_strategy=_lib.CACHE_LRU if self.cache_strategy == "lru" else _lib.CACHE_LRU_S,
+            dtype=_lib.dtype_code(q.dtype), score_decay=float(self.score_decay or 0.0), rope_base=float(pe.base),
+            rope_scale=float(pe.distance_scale), device=q.device.index if q.device.index is not None else
+            torch.cuda.current_device(), shard_rank=0, shard_world=1)
+        for _ in range(self.num_units):
+            h = ctypes.c_void_p()
+            _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))
+            self._ctx.append(h)
+        self.initialized = True
+
+    def __del__(self):
+        try:
+            for h in self._ctx:
+                _lib.lib.infllm_ctx_destroy(h)
+        except Exception:
+            pass
+        self._ctx = []
+
+    # -- the path
+    def append(self, local_q, local_k, local_v, global_q, global_k, global_v):
+        """context_manager.py:682-813.  q (B, H, L, D); k, v (B, H_kv, L, D); returns (B, H, L, D).
+        The global tensors must be the local ones (inf_llm/attention/inf_llm.py:58-59 passes the same
+        projections twice); the kernels rotate them per stage themselves."""
+        for t in (local_q, local_k, local_v):
+            _lib.require_cuda(t, "ContextManager.append input")
+        if global_q is not local_q and global_q.data_ptr() != local_q.data_ptr():
+            raise NotImplementedError("distinct global_q/k/v tensors are not supported: pass the local ones")
+        assert local_q.dim() == 4
+        batch, heads, length, dim = local_q.shape
+        for t in (local_q, local_k, local_v):  # context_manager.py:301-306
+            assert t.size(0) == batch and t.size(2) == length and t.size(3) == dim
+        if not self.initialized:
+            self._init(local_q, local_k)
+        assert heads == self.num_heads and local_k.size(1) == self.num_heads_kv and batch == self.batch_size
+        q, k, v = local_q, local_k, local_v
+        if q.stride(-1) != 1:
+            q = q.contiguous()
+        if k.stride(-1) != 1 or k.stride() != v.stride():
+            k, v = k.contiguous(), v.contiguous()
+        out = torch.empty((batch, heads, length, dim), dtype=q.dtype, device=q.device)
+        stream = _lib.stream_ptr(q.device)
+        if self.perhead:
+            g = heads // self.num_heads_kv
+            for b in range(batch):
+                for h in range(heads):
+                    qq, kk, vv, oo = q[b, h:h + 1], k[b, h // g:h // g + 1], v[b, h // g:h // g + 1], out[b, h:h + 1]
+                    self._append_unit(self._ctx[b * heads + h], qq, kk, vv, oo, length, stream)
+        else:
+            for b in range(batch):
+                self._append_unit(self._ctx[b], q[b], k[b], v[b], out[b], length, stream)
+        self.length += length
+        return out
+
+    @staticmethod
+    def _append_unit(ctx, q, k, v, o, length, stream):
+        _lib.check(_lib.lib.infllm_ctx_append(
+            ctx, q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(),
+            v.stride(0), v.stride(1), o.data_ptr(), o.stride(0), o.stride(1), length, stream))
+
+    def size(self, *args, **kwargs):
+        return self.length
+
+    # -- what the reference keeps as attributes
+    def info(self, u=0):
+        info = _lib.CtxInfo()
+        _lib.check(_lib.lib.infllm_ctx_get_info(self._ctx[u], ctypes.byref(info)))
+        return {n: getattr(info, n) for n, _ in _lib.CtxInfo._fields_}
+
+    @property
+    def num_global_block(self):
+        return self.info()["num_blocks"] if self._ctx else 0
+
+    @property
+    def cached_blocks(self):
+        """[{block id: stamp}] per unit, in the reference's dict order (context_manager.py:318)."""
+        out = []
+        for h in self._ctx:
+            cap = self.max_cached_block + self.topk
+            ids, st, n = (ctypes.c_int32 * cap)(), (ctypes.c_double * cap)(), ctypes.c_int()
+            _lib.check(_lib.lib.infllm_ctx_get_cached(h, ids, st, cap, ctypes.byref(n)))
+            out.append({int(ids[i]): st[i] for i in range(n.value)})
+        return out
+
+    def last_topk(self, u=0):
+        """Retrieved ids of every exec block of the last append, in scorer order."""
+        n_eb = self.info(u)["exec_blocks"]
+        out = []
+        for eb in range(n_eb):
+            ids, n = (ctypes.c_int32 * max(self.topk, 1))(), ctypes.c_int()
+            _lib.check(_lib.lib.infllm_ctx_get_topk(self._ctx[u], eb, ids, self.topk, ctypes.byref(n)))
+            out.append([int(ids[i]) for i in range(n.value)])
+        return out
+
+    def block_k_rows(self, u=0):
+        """Representative keys (num_blocks, H*D) of unit u as a host tensor."""
+        n = self.info(u)["num_blocks"]
+        t = torch.empty((n, self.unit_size * self.dim_head), dtype=self.dtype)
+        if n:
+            _lib.check(_lib.lib.infllm_ctx_get_block_k(self._ctx[u], 0, n, t.data_ptr()))
+        return t
+
+    def reset(self):
+        for h in self._ctx:
+            _lib.check(_lib.lib.infllm_ctx_reset(h))
+        self.length = 0

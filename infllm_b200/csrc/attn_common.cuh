@@ -1,0 +1,72 @@
+// Parameter blocks shared by the attention kernels and the context-memory runtime.
+#pragma once
+#include "common.cuh"
+
+namespace infllm {
+
+// One contiguous run of keys/values of a stage.  Tokens are `ts` elements apart, heads `hs`.
+struct KvSeg {
+  const void* k;
+  const void* v;
+  int64_t hs;
+  int32_t ts;
+  int32_t len;
+};
+
+constexpr int kMaxSeg = 80;    // segments per launch (retrieved units + init sink + overflow + window)
+constexpr int kMaxStage = 2;   // stages fused in one launch
+
+// One stage = one append() of the reference's multi-stage attention: its own queries, mask and keys.
+struct StageDesc {
+  const void* q;  // (H, lq, D)
+  int64_t q_hs, q_ts;
+  int32_t mask_mode;
+  int32_t seg_begin, seg_end;  // range in AttnParams::seg
+  int64_t mask_offset, mask_size;
+  int64_t lk;  // total keys of the stage
+};
+
+struct AttnParams {
+  StageDesc stage[kMaxStage];
+  KvSeg seg[kMaxSeg];
+  int32_t n_stage;
+  int32_t n_heads, n_kv_heads;
+  int32_t first, last;  // first: start from an empty state; last: write out/lse instead of the state
+  int64_t lq;
+  float* acc;  // (H, lq, D) fp32 state
+  float* m;    // (H, lq)
+  float* l;    // (H, lq)
+  void* out;   // (H, lq, D) in dtype, when last
+  int64_t o_hs, o_ts;
+  float* lse;  // (H, lq) log2-domain LSE, when last (may be null)
+  float scale_log2;  // log2(e) / sqrt(D)
+};
+
+// [lo, hi] inclusive range of key indices of a stage that a block of query rows [i0, i1] can see
+__host__ __device__ inline void visible_key_range(int mode, int64_t off, int64_t size, int64_t i0, int64_t i1,
+                                                  int64_t lk, int64_t* lo, int64_t* hi) {
+  int64_t a = 0, b = lk - 1;
+  if (mode == INFLLM_MASK_WINDOW) {
+    a = i0 + off - size + 1;
+    b = i1 + off;
+  } else if (mode == INFLLM_MASK_COMPLEMENT) {
+    b = i1 + off - size;
+  }
+  *lo = a < 0 ? 0 : a;
+  *hi = b > lk - 1 ? lk - 1 : b;
+}
+
+__device__ __forceinline__ bool mask_keep(int mode, int64_t off, int64_t size, int64_t i, int64_t j) {
+  int64_t dist = i - j + off;
+  if (mode == INFLLM_MASK_WINDOW) return dist >= 0 && dist < size;
+  if (mode == INFLLM_MASK_COMPLEMENT) return dist >= size;
+  return true;
+}
+
+int attn_general_launch(const AttnParams& p, int head_dim, int dtype, cudaStream_t s);
+int attn_colsum_launch(const void* q, int64_t q_hs, int64_t q_ts, const void* k, int64_t k_hs, int64_t k_ts,
+                       int n_heads, int n_kv_heads, int64_t lq, int64_t lk, int head_dim, int mask_mode,
+                       int64_t mask_offset, int64_t mask_size, const float* lse, float* score, int64_t score_hs,
+                       int accumulate, int dtype, cudaStream_t s);
+
+}  // namespace infllm

@@ -1,0 +1,816 @@
+// Native state and exec-block loop of one unit of the context memory.
+//
+// Follows ContextManager of the reference (inf_llm/attention/context_manager.py:196-816) in
+// behaviour, not in structure.  Tokens are addressed by their absolute index in the sequence:
+//   [0, init_len)                          the init sink            (reference: init_k / init_v)
+//   [n_init + b*bs, n_init + (b+1)*bs)     sealed memory unit b     (reference: global_blocks[u][b])
+//   [frontier, length)                     the un-sealed remainder  (reference: global_remainder),
+//                                          whose tail of n_local tokens is the local window (local_k/v)
+// The remainder lives in ONE device buffer per tensor (raw keys, rotated keys, values, accumulated
+// local score); there is no gather buffer: the attention kernels read retrieved units in place
+// from their cache slots, the sink from its own buffer and the overflow from the remainder buffer.
+// Sealed units are copied to a pinned host store on a side stream and come back into one of
+// max_cached_block cache slots with cudaMemcpyAsync when retrieval asks for them.
+#include <algorithm>
+#include <list>
+#include <unordered_map>
+#include <vector>
+
+#include "attn_common.cuh"
+
+namespace infllm {
+
+// kernels of the other translation units
+int rope_apply_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
+                      int n_heads, int64_t len, int head_dim, const float* cos_t, const float* sin_t,
+                      int64_t table_len, int64_t pos0, int pos_step, int dtype, cudaStream_t s);
+int copy_rows_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
+                     int n_heads, int64_t len, int head_dim, cudaStream_t s);
+int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t len, int exc, int head_dim,
+                float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s);
+int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s);
+int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
+                       int64_t tok0, int n_new, int block_size, int repr_topk, int n_heads, int n_kv_heads,
+                       int head_dim, void* out, int dtype, cudaStream_t s);
+int attn_decode_launch(const void* q0, const void* q1, int n_heads, int n_kv_heads, int head_dim, int n_seg,
+                       const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s);
+int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
+                     int64_t o_hs, float* lse, int dtype, cudaStream_t s);
+int decode_score_launch(const float* logits, int64_t len, const float* lse, float* score, int64_t score_hs,
+                        int n_heads, cudaStream_t s);
+
+// ------------------------------------------------------------------------------------- LRU table
+// cached_blocks[u] of the reference: a dict id -> stamp whose iteration (insertion) order breaks
+// ties at eviction (context_manager.py:246-265: stable sort of dict items by stamp).
+struct LruTable {
+  int capacity;
+  std::list<std::pair<int32_t, double>> items;  // dict order
+  std::unordered_map<int32_t, std::list<std::pair<int32_t, double>>::iterator> index;
+
+  explicit LruTable(int cap) : capacity(cap) {}
+  bool has(int32_t id) const { return index.count(id) != 0; }
+  size_t size() const { return items.size(); }
+  void clear() {
+    items.clear();
+    index.clear();
+  }
+  // context_manager.py:496-502 + 246-265
+  void plan(const int32_t* wanted, int n, std::vector<int32_t>* evicted) {
+    evicted->clear();
+    long num_remove = (long)items.size() - capacity;
+    for (int i = 0; i < n; ++i)
+      if (!has(wanted[i])) ++num_remove;
+    if (num_remove <= 0) return;
+    std::vector<std::pair<int32_t, double>> order(items.begin(), items.end());
+    std::stable_sort(order.begin(), order.end(),
+                     [](const std::pair<int32_t, double>& a, const std::pair<int32_t, double>& b) {
+                       return a.second < b.second;
+                     });
+    std::vector<int32_t> keep(wanted, wanted + n);
+    std::sort(keep.begin(), keep.end());
+    long removed = 0;
+    for (auto& kv : order) {
+      if (!std::binary_search(keep.begin(), keep.end(), kv.first)) {
+        auto it = index.find(kv.first);
+        items.erase(it->second);
+        index.erase(it);
+        evicted->push_back(kv.first);
+        ++removed;
+      }
+      if (removed >= num_remove) return;
+    }
+  }
+  // context_manager.py:504-513: assignment keeps an existing key in place, a new key goes last
+  void stamp(const int32_t* wanted, int n, double value) {
+    for (int i = 0; i < n; ++i) set(wanted[i], value);
+  }
+  void set(int32_t id, double value) {
+    auto it = index.find(id);
+    if (it != index.end()) {
+      it->second->second = value;
+    } else {
+      items.emplace_back(id, value);
+      index[id] = std::prev(items.end());
+    }
+  }
+  void scale(double f) {
+    for (auto& kv : items) kv.second *= f;
+  }
+  bool add(int32_t id, double v) {
+    auto it = index.find(id);
+    if (it == index.end()) return false;
+    it->second->second += v;
+    return true;
+  }
+};
+
+// --------------------------------------------------------------------------------------- context
+struct TokenBuffers {
+  void* k_raw = nullptr;  // (H_kv, cap, D) un-rotated keys
+  void* k_rot = nullptr;  // (H_kv, cap, D) keys rotated to position (token - rope_origin)
+  void* v = nullptr;      // (H_kv, cap, D)
+  float* score = nullptr; // (H, cap) accumulated local attention mass
+  int64_t cap = 0;        // tokens
+  int64_t t0 = 0;         // absolute token index of slot 0
+};
+
+}  // namespace infllm
+
+using namespace infllm;
+
+struct infllm_ctx {
+  infllm_config cfg;
+  int esz = 2;                 // bytes per activation element
+  int64_t width = 0;           // n_heads * head_dim
+  int64_t unit_elems = 0;      // n_kv_heads * block_size * head_dim (K or V of one unit)
+  int64_t unit_bytes = 0;      // K and V of one unit
+  bool initialized = false;
+
+  int64_t length = 0, frontier = 0, num_blocks = 0, init_len = 0, load_count = 0;
+  bool init_full = false;
+
+  TokenBuffers tb;
+  void* init_k = nullptr;  // (H_kv, n_init, D)
+  void* init_v = nullptr;
+  void* block_k = nullptr;  // (block_k_cap, width)
+  int64_t block_k_cap = 0;
+
+  // RoPE
+  float *cos_t = nullptr, *sin_t = nullptr;
+  int64_t tab_len = 0;
+  int64_t rope_origin = -1;  // absolute token index that has position 0 in k_rot
+
+  // per-call scratch
+  int64_t sub_max = 0;       // tokens per internal sub-append
+  void *q_loc = nullptr, *q_glb = nullptr;  // (H, sub_max, D)
+  float* qbar = nullptr;     // (sub_max/exc + 1, width)
+  float* lse = nullptr;      // (H, exc)
+  float *st_acc = nullptr, *st_m = nullptr, *st_l = nullptr;  // carried attention state (H, exc, D) / (H, exc)
+  float* scores = nullptr;   // (scores_cap) unit scores
+  int64_t scores_cap = 0;
+  int32_t* d_topk = nullptr; // (topk)
+  int32_t* h_topk = nullptr; // pinned
+  float *part_o = nullptr, *part_lse = nullptr, *dec_logits = nullptr;
+  int max_parts = 0;
+
+  // unit store
+  void* cache = nullptr;  // (max_cached, 2, H_kv, bs, D)
+  std::vector<int> free_slots;
+  std::unordered_map<int32_t, int> slot_of;
+  std::vector<void*> slabs;  // pinned host memory
+  int64_t slab_units = 0;
+  LruTable lru{0};
+
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr;
+  bool attn_recorded = false;
+
+  // trace of the last append
+  std::vector<std::vector<int32_t>> trace_topk;
+  infllm_ctx_info counters{};
+
+  char* host_unit(int64_t b) { return (char*)slabs[b / slab_units] + (b % slab_units) * unit_bytes; }
+};
+
+namespace {
+
+int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+int free_buffers(TokenBuffers& tb, cudaStream_t s) {
+  if (tb.k_raw) INFLLM_CUDA_OK(cudaFreeAsync(tb.k_raw, s));
+  if (tb.k_rot) INFLLM_CUDA_OK(cudaFreeAsync(tb.k_rot, s));
+  if (tb.v) INFLLM_CUDA_OK(cudaFreeAsync(tb.v, s));
+  if (tb.score) INFLLM_CUDA_OK(cudaFreeAsync(tb.score, s));
+  tb = TokenBuffers{};
+  return INFLLM_OK;
+}
+
+int lazy_init(infllm_ctx* c, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  // keep freed device memory in the pool: the token buffers are re-created at every compaction
+  cudaMemPool_t pool;
+  INFLLM_CUDA_OK(cudaDeviceGetDefaultMemPool(&pool, g.device));
+  uint64_t keep = UINT64_MAX;
+  INFLLM_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+
+  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_main, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_copy, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_attn, cudaEventDisableTiming));
+
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
+  c->sub_max = round_up(std::max<int64_t>(16384, 2 * g.exc_block_size), g.exc_block_size);
+  // RoPE table: positions of a call stay below n_local + sub_max; twice that so that the origin
+  // moves (and the window is re-rotated) only every sub_max tokens
+  c->tab_len = g.n_local + 2 * c->sub_max + 1;
+  INFLLM_CUDA_OK(cudaMalloc(&c->cos_t, c->tab_len * (D / 2) * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->sin_t, c->tab_len * (D / 2) * sizeof(float)));
+  {
+    std::vector<float> inv(D / 2);
+    // rope.py:22-24: 1 / base ** (arange(0, D, 2) / D) in fp32
+    for (int i = 0; i < D / 2; ++i) inv[i] = 1.0f / powf(g.rope_base, (float)(2 * i) / (float)D);
+    INFLLM_TRY(infllm_rope_table(inv.data(), g.rope_scale, (int)D, c->tab_len, c->cos_t, c->sin_t, s));
+  }
+  if (g.n_init > 0) {
+    INFLLM_CUDA_OK(cudaMalloc(&c->init_k, HKV * g.n_init * D * c->esz));
+    INFLLM_CUDA_OK(cudaMalloc(&c->init_v, HKV * g.n_init * D * c->esz));
+  }
+  INFLLM_CUDA_OK(cudaMalloc(&c->q_loc, H * c->sub_max * D * c->esz));
+  INFLLM_CUDA_OK(cudaMalloc(&c->q_glb, H * c->sub_max * D * c->esz));
+  INFLLM_CUDA_OK(cudaMalloc(&c->qbar, (c->sub_max / g.exc_block_size + 1) * c->width * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->lse, H * g.exc_block_size * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->st_acc, H * g.exc_block_size * D * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->st_m, H * g.exc_block_size * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
+  // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
+  int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
+  c->max_parts = (int)(dec_keys / 128 + g.topk + 8);
+  INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->cache, (int64_t)g.max_cached_block * c->unit_bytes));
+  c->free_slots.clear();
+  for (int i = g.max_cached_block - 1; i >= 0; --i) c->free_slots.push_back(i);
+  c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
+  c->initialized = true;
+  return INFLLM_OK;
+}
+
+// make room for tokens [frontier, length + add) in the token buffers
+int ensure_tokens(infllm_ctx* c, int64_t add, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  TokenBuffers& tb = c->tb;
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
+  if (tb.cap > 0 && c->length + add - tb.t0 <= tb.cap) return INFLLM_OK;
+  const int64_t live0 = c->frontier, live = c->length - c->frontier;
+  const int64_t need = live + add;
+  TokenBuffers nb;
+  nb.cap = round_up(need + std::max<int64_t>(4096, g.n_local), 256);
+  nb.t0 = live0;
+  INFLLM_CUDA_OK(cudaMallocAsync(&nb.k_raw, HKV * nb.cap * D * c->esz, s));
+  INFLLM_CUDA_OK(cudaMallocAsync(&nb.k_rot, HKV * nb.cap * D * c->esz, s));
+  INFLLM_CUDA_OK(cudaMallocAsync(&nb.v, HKV * nb.cap * D * c->esz, s));
+  INFLLM_CUDA_OK(cudaMallocAsync((void**)&nb.score, H * nb.cap * sizeof(float), s));
+  if (live > 0) {
+    const int64_t off = (live0 - tb.t0) * D * c->esz;
+    const size_t w = live * D * c->esz;
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(nb.k_raw, nb.cap * D * c->esz, (char*)tb.k_raw + off, tb.cap * D * c->esz, w, HKV,
+                                     cudaMemcpyDeviceToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(nb.k_rot, nb.cap * D * c->esz, (char*)tb.k_rot + off, tb.cap * D * c->esz, w, HKV,
+                                     cudaMemcpyDeviceToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(nb.v, nb.cap * D * c->esz, (char*)tb.v + off, tb.cap * D * c->esz, w, HKV,
+                                     cudaMemcpyDeviceToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(nb.score, nb.cap * sizeof(float), tb.score + (live0 - tb.t0),
+                                     tb.cap * sizeof(float), live * sizeof(float), H, cudaMemcpyDeviceToDevice, s));
+  }
+  if (tb.cap > 0) {
+    // offloads still reading the old buffers run on the copy stream
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
+    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
+    INFLLM_TRY(free_buffers(tb, s));
+  }
+  c->tb = nb;
+  return INFLLM_OK;
+}
+
+int ensure_block_k(infllm_ctx* c, int64_t n, cudaStream_t s) {
+  if (n <= c->block_k_cap) return INFLLM_OK;
+  int64_t cap = std::max<int64_t>(16, c->block_k_cap);
+  while (cap < n) cap *= 2;  // VectorTensor.append_cache doubles (context_manager.py:128-138)
+  void* nb = nullptr;
+  INFLLM_CUDA_OK(cudaMallocAsync(&nb, cap * c->width * c->esz, s));
+  if (c->num_blocks > 0)
+    INFLLM_CUDA_OK(cudaMemcpyAsync(nb, c->block_k, c->num_blocks * c->width * c->esz, cudaMemcpyDeviceToDevice, s));
+  if (c->block_k) INFLLM_CUDA_OK(cudaFreeAsync(c->block_k, s));
+  c->block_k = nb;
+  c->block_k_cap = cap;
+  return INFLLM_OK;
+}
+
+int ensure_host_units(infllm_ctx* c, int64_t n) {
+  while ((int64_t)c->slabs.size() * c->slab_units < n) {
+    void* p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, c->slab_units * c->unit_bytes, cudaHostAllocDefault);
+    if (e != cudaSuccess) return fail(INFLLM_E_NOMEM, "pinned host store: cudaHostAlloc of %lld bytes failed: %s",
+                                      (long long)(c->slab_units * c->unit_bytes), cudaGetErrorString(e));
+    c->slabs.push_back(p);
+  }
+  return INFLLM_OK;
+}
+
+int ensure_scores(infllm_ctx* c, int64_t n, cudaStream_t s) {
+  if (n <= c->scores_cap) return INFLLM_OK;
+  int64_t cap = std::max<int64_t>(1024, c->scores_cap);
+  while (cap < n) cap *= 2;
+  if (c->scores) INFLLM_CUDA_OK(cudaFreeAsync(c->scores, s));
+  INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->scores, cap * sizeof(float), s));
+  c->scores_cap = cap;
+  return INFLLM_OK;
+}
+
+// retrieval + cache plan + refill of one exec block; ids in scorer order
+int retrieve_and_refill(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  ids->clear();
+  const int64_t n = c->num_blocks;
+  if (n <= g.topk) {  // context_manager.py:370-371
+    for (int64_t b = 0; b < n; ++b) ids->push_back((int32_t)b);
+  } else {
+    INFLLM_TRY(ensure_scores(c, n, s));
+    INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
+                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s));
+    INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
+    INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
+    ids->assign(c->h_topk, c->h_topk + g.topk);
+  }
+  if (ids->empty()) return INFLLM_OK;
+  std::vector<int32_t> evicted;
+  c->lru.plan(ids->data(), (int)ids->size(), &evicted);
+  for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
+    auto it = c->slot_of.find(b);
+    if (it != c->slot_of.end()) {
+      c->free_slots.push_back(it->second);
+      c->slot_of.erase(it);
+    }
+  }
+  c->counters.evictions += (int64_t)evicted.size();
+  if (g.cache_strategy == INFLLM_CACHE_LRU) {
+    c->load_count += 1;
+    c->lru.stamp(ids->data(), (int)ids->size(), (double)c->load_count);
+  } else {
+    c->lru.stamp(ids->data(), (int)ids->size(), 0.0);
+  }
+  bool any_miss = false;
+  for (int32_t b : *ids) {
+    if (c->slot_of.count(b)) {
+      c->counters.cache_hits += 1;
+      continue;
+    }
+    if (c->free_slots.empty())
+      return fail(INFLLM_E_CAPACITY, "no free cache slot for unit %d (max_cached_block %d)", b, g.max_cached_block);
+    if (!any_miss) {
+      // slots freed above may still be read by the previous exec block's attention
+      if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn, 0));
+      any_miss = true;
+    }
+    int slot = c->free_slots.back();
+    c->free_slots.pop_back();
+    c->slot_of[b] = slot;
+    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
+                                   cudaMemcpyHostToDevice, c->copy_stream));
+    c->counters.cache_misses += 1;
+    c->counters.h2d_bytes += c->unit_bytes;
+  }
+  if (any_miss) {
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
+    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
+  }
+  return INFLLM_OK;
+}
+
+// after an exec block that ended at absolute token `end`: sink fill and sealing (context_manager.py:614-679)
+int seal_after(infllm_ctx* c, int64_t end, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  TokenBuffers& tb = c->tb;
+  const int64_t D = g.head_dim, HKV = g.n_kv_heads, bs = g.block_size;
+  int64_t rem = end - c->frontier;
+  if (!c->init_full && rem > g.n_local) {
+    int64_t take = std::min<int64_t>(g.n_init - c->init_len, rem - g.n_local);
+    if (take > 0) {
+      const size_t w = take * D * c->esz;
+      const int64_t src = (c->frontier - tb.t0) * D * c->esz, dst = c->init_len * D * c->esz;
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_k + dst, g.n_init * D * c->esz, (char*)tb.k_raw + src,
+                                       tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_v + dst, g.n_init * D * c->esz, (char*)tb.v + src,
+                                       tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
+    }
+    c->init_len += take;
+    c->frontier += take;
+    rem -= take;
+    if (c->init_len == g.n_init) c->init_full = true;
+  }
+  int n_new = 0;
+  while (rem - bs >= g.n_local) {
+    rem -= bs;
+    ++n_new;
+  }
+  if (n_new == 0) return INFLLM_OK;
+  INFLLM_TRY(ensure_block_k(c, c->num_blocks + n_new, s));
+  INFLLM_TRY(ensure_host_units(c, c->num_blocks + n_new));
+  INFLLM_TRY(repr_select_launch(tb.k_raw, tb.cap * D, D, tb.score, tb.cap, c->frontier - tb.t0, n_new, (int)bs,
+                                g.repr_topk, g.n_heads, g.n_kv_heads, (int)D,
+                                (char*)c->block_k + c->num_blocks * c->width * c->esz, g.dtype, s));
+  // offload to the host store on the side stream (MemoryUnit.__init__, context_manager.py:39-45)
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
+  INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_main, 0));
+  for (int i = 0; i < n_new; ++i) {
+    const int64_t b = c->num_blocks + i;
+    const int64_t src = (c->frontier + i * bs - tb.t0) * D * c->esz;
+    char* hu = c->host_unit(b);
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(hu, bs * D * c->esz, (char*)tb.k_raw + src, tb.cap * D * c->esz, bs * D * c->esz,
+                                     HKV, cudaMemcpyDeviceToHost, c->copy_stream));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(hu + c->unit_bytes / 2, bs * D * c->esz, (char*)tb.v + src, tb.cap * D * c->esz,
+                                     bs * D * c->esz, HKV, cudaMemcpyDeviceToHost, c->copy_stream));
+    c->counters.d2h_bytes += c->unit_bytes;
+  }
+  c->num_blocks += n_new;
+  c->frontier += n_new * bs;
+  return INFLLM_OK;
+}
+
+// one internal call of at most sub_max tokens whose exec-block boundaries coincide with the caller's
+int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const char* k, int64_t k_hs, int64_t k_ts,
+               const char* v, int64_t v_hs, int64_t v_ts, char* out, int64_t o_hs, int64_t o_ts, int64_t L,
+               cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads, bs = g.block_size;
+  const int esz = c->esz;
+  const int64_t T = c->length;
+  INFLLM_TRY(ensure_tokens(c, L, s));
+  TokenBuffers& tb = c->tb;
+  const int64_t kv_hs = tb.cap * D;  // head stride of the token buffers, elements
+  // ---- ingest the new tokens
+  const int64_t at = T - tb.t0;
+  INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
+  INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
+  INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
+  // ---- RoPE: keys keep the position (token - rope_origin) until the table would run out
+  const int64_t win0 = std::max<int64_t>(T - g.n_local, 0);  // oldest key any query of this call can see locally
+  if (c->rope_origin < 0 || T + L - c->rope_origin > c->tab_len || win0 < c->rope_origin) {
+    c->rope_origin = win0;
+    if (T > win0)
+      INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + (win0 - tb.t0) * D * esz, kv_hs, D,
+                                   (char*)tb.k_rot + (win0 - tb.t0) * D * esz, kv_hs, D, (int)HKV, T - win0, (int)D,
+                                   c->cos_t, c->sin_t, c->tab_len, 0, 1, g.dtype, s));
+  }
+  INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + at * D * esz, kv_hs, D, (char*)tb.k_rot + at * D * esz, kv_hs, D,
+                               (int)HKV, L, (int)D, c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, 1, g.dtype,
+                               s));
+  // queries: window-relative rotation for the local stage, the single position n_local-1 for the
+  // global stage (context_manager.py:480 and :744-747)
+  const int64_t q_hs_s = c->sub_max * D;
+  INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_loc, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
+                               T - c->rope_origin, 1, g.dtype, s));
+  INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_glb, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
+                               g.n_local - 1, 0, g.dtype, s));
+  INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
+
+  std::vector<int32_t> ids;
+  std::vector<KvSeg> gsegs;
+  int eb = 0;
+  for (int64_t st = 0; st < L; st += g.exc_block_size, ++eb) {  // context_manager.py:762
+    const int64_t ed = std::min<int64_t>(st + g.exc_block_size, L);
+    const int64_t S = T + st, E = T + ed, lq = ed - st;
+    const int64_t ks = std::max<int64_t>(S - g.n_local, 0), lk = E - ks;  // local keys [ks, E) (:772-773)
+    INFLLM_TRY(retrieve_and_refill(c, eb, &ids, s));
+    c->trace_topk.push_back(ids);
+    const int64_t ovf = std::max<int64_t>(E - c->frontier - g.n_local, 0);  // :391
+    // global key segments: retrieved units (in place in their cache slots), sink, overflow
+    gsegs.clear();
+    for (int32_t b : ids) {
+      const char* base = (const char*)c->cache + (int64_t)c->slot_of[b] * c->unit_bytes;
+      gsegs.push_back({base, base + c->unit_bytes / 2, bs * D, (int32_t)D, (int32_t)bs});
+    }
+    if (c->init_len > 0) gsegs.push_back({c->init_k, c->init_v, g.n_init * D, (int32_t)D, (int32_t)c->init_len});
+    if (ovf > 0)
+      gsegs.push_back({(char*)tb.k_raw + (c->frontier - tb.t0) * D * esz, (char*)tb.v + (c->frontier - tb.t0) * D * esz,
+                       kv_hs, (int32_t)D, (int32_t)ovf});
+    char* out_eb = out + st * o_ts * esz;
+    const char* qloc_eb = (const char*)c->q_loc + st * D * esz;
+    const char* qglb_eb = (const char*)c->q_glb + st * D * esz;
+    if (lq == 1 && D == 128) {
+      // ---- one-token exec block: split-K decode over [visible window | global segments]
+      const int64_t wlo = std::max<int64_t>(E - g.n_local, ks);  // window mask of the single query
+      std::vector<KvSeg> segs;
+      std::vector<int32_t> qsel;
+      segs.push_back({(char*)tb.k_rot + (wlo - tb.t0) * D * esz, (char*)tb.v + (wlo - tb.t0) * D * esz, kv_hs,
+                      (int32_t)D, (int32_t)(E - wlo)});
+      qsel.push_back(0);
+      for (auto& sgm : gsegs) {
+        segs.push_back(sgm);
+        qsel.push_back(1);
+      }
+      int parts = 0;
+      for (size_t base = 0; base < segs.size();) {
+        // all segments fit one launch in every supported configuration; guard anyway
+        if (segs.size() > (size_t)kMaxSeg)
+          return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
+        INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
+                                      qsel.data(), c->part_o, c->part_lse, c->max_parts, &parts, 0, c->dec_logits,
+                                      g.dtype, s));
+        base = segs.size();
+      }
+      INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s));
+      INFLLM_TRY(decode_score_launch(c->dec_logits, E - wlo, c->lse, tb.score + (wlo - tb.t0), tb.cap, (int)H, s));
+    } else {
+      // ---- local stage + global stage, jointly normalised (context_manager.py:486-489, 526-533)
+      AttnParams P{};
+      P.n_heads = (int)H; P.n_kv_heads = (int)HKV; P.lq = lq; P.first = 1;
+      P.acc = c->st_acc; P.m = c->st_m; P.l = c->st_l;
+      P.out = out_eb; P.o_hs = o_hs; P.o_ts = o_ts; P.lse = c->lse;
+      P.scale_log2 = kLog2e / sqrtf((float)D);
+      P.stage[0].q = qloc_eb; P.stage[0].q_hs = q_hs_s; P.stage[0].q_ts = D;
+      P.stage[0].mask_mode = INFLLM_MASK_WINDOW; P.stage[0].mask_offset = lk - lq; P.stage[0].mask_size = g.n_local;
+      P.stage[0].lk = lk; P.stage[0].seg_begin = 0; P.stage[0].seg_end = 1;
+      P.seg[0] = {(char*)tb.k_rot + (ks - tb.t0) * D * esz, (char*)tb.v + (ks - tb.t0) * D * esz, kv_hs, (int32_t)D,
+                  (int32_t)lk};
+      // The reference passes a complement window for the global stage whose offset makes every
+      // (query, key) pair visible (context_manager.py:437); the stage is therefore unmasked.
+      size_t done = 0;
+      int nseg = 1;
+      int64_t glk = 0;
+      while (done < gsegs.size() && nseg < kMaxSeg) {
+        P.seg[nseg++] = gsegs[done];
+        glk += gsegs[done].len;
+        ++done;
+      }
+      P.n_stage = 2;
+      P.stage[1].q = qglb_eb; P.stage[1].q_hs = q_hs_s; P.stage[1].q_ts = D;
+      P.stage[1].mask_mode = INFLLM_MASK_NONE; P.stage[1].lk = glk; P.stage[1].seg_begin = 1; P.stage[1].seg_end = nseg;
+      P.last = done == gsegs.size();
+      INFLLM_TRY(attn_general_launch(P, (int)D, g.dtype, s));
+      while (done < gsegs.size()) {  // more segments than one launch holds: carry the state
+        AttnParams R{};
+        R.n_heads = (int)H; R.n_kv_heads = (int)HKV; R.lq = lq; R.first = 0;
+        R.acc = c->st_acc; R.m = c->st_m; R.l = c->st_l;
+        R.out = out_eb; R.o_hs = o_hs; R.o_ts = o_ts; R.lse = c->lse; R.scale_log2 = P.scale_log2;
+        R.n_stage = 1;
+        R.stage[0].q = qglb_eb; R.stage[0].q_hs = q_hs_s; R.stage[0].q_ts = D; R.stage[0].mask_mode = INFLLM_MASK_NONE;
+        int ns = 0;
+        int64_t rl = 0;
+        while (done < gsegs.size() && ns < kMaxSeg) {
+          R.seg[ns++] = gsegs[done];
+          rl += gsegs[done].len;
+          ++done;
+        }
+        R.stage[0].lk = rl; R.stage[0].seg_begin = 0; R.stage[0].seg_end = ns;
+        R.last = done == gsegs.size();
+        INFLLM_TRY(attn_general_launch(R, (int)D, g.dtype, s));
+      }
+      // accumulated local score of every window key (context_manager.py:488, 623-625)
+      INFLLM_TRY(attn_colsum_launch(qloc_eb, q_hs_s, D, (char*)tb.k_rot + (ks - tb.t0) * D * esz, kv_hs, D, (int)H,
+                                    (int)HKV, lq, lk, (int)D, INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse,
+                                    tb.score + (ks - tb.t0), tb.cap, 1, g.dtype, s));
+    }
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
+    c->attn_recorded = true;
+    INFLLM_TRY(seal_after(c, E, s));
+  }
+  c->length += L;
+  c->counters.exec_blocks += eb;
+  return INFLLM_OK;
+}
+
+}  // namespace
+
+extern "C" int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out) {
+  if (!cfg || !out) return fail(INFLLM_E_BADARG, "ctx_create: null pointer");
+  const infllm_config& g = *cfg;
+  if (g.n_heads <= 0 || g.n_kv_heads <= 0 || g.n_heads % g.n_kv_heads)
+    return fail(INFLLM_E_BADARG, "ctx_create: %d heads / %d kv heads", g.n_heads, g.n_kv_heads);
+  if (g.head_dim != 128 && g.head_dim != 64)
+    return fail(INFLLM_E_UNSUPPORTED, "ctx_create: head_dim %d (64 and 128 are built)", g.head_dim);
+  if (g.n_init < 0 || g.n_local <= 0 || g.block_size <= 0 || g.topk <= 0 || g.exc_block_size <= 0 || g.repr_topk <= 0)
+    return fail(INFLLM_E_BADARG, "ctx_create: sizes must be positive");
+  if (g.exc_block_size > g.n_local)  // context_manager.py:219
+    return fail(INFLLM_E_BADARG, "ctx_create: exc_block_size %d > n_local %d", g.exc_block_size, g.n_local);
+  if (g.max_cached_block < g.topk)  // CudaCache.alloc would assert (context_manager.py:19)
+    return fail(INFLLM_E_CAPACITY, "ctx_create: max_cached_block %d < topk %d: a retrieval could not be held in the cache",
+                g.max_cached_block, g.topk);
+  if (g.repr_topk > g.block_size) return fail(INFLLM_E_BADARG, "ctx_create: repr_topk %d > block_size %d", g.repr_topk, g.block_size);
+  if (g.block_size % 8) return fail(INFLLM_E_BADARG, "ctx_create: block_size %d must be a multiple of 8", g.block_size);
+  if (g.dtype != INFLLM_BF16 && g.dtype != INFLLM_FP16) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: dtype code %d", g.dtype);
+  if (g.cache_strategy != INFLLM_CACHE_LRU)
+    return fail(INFLLM_E_UNSUPPORTED, "ctx_create: cache strategy code %d (only lru is built)", g.cache_strategy);
+  if (g.topk > 1024) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: topk %d > 1024", g.topk);
+  infllm_ctx* c = new (std::nothrow) infllm_ctx();
+  if (!c) return fail(INFLLM_E_NOMEM, "ctx_create: out of host memory");
+  c->cfg = g;
+  c->esz = 2;
+  c->width = (int64_t)g.n_heads * g.head_dim;
+  c->unit_elems = (int64_t)g.n_kv_heads * g.block_size * g.head_dim;
+  c->unit_bytes = 2 * c->unit_elems * c->esz;
+  c->lru = LruTable(g.max_cached_block);
+  *out = c;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_reset(infllm_ctx* c) {
+  if (!c) return fail(INFLLM_E_BADARG, "ctx_reset: null context");
+  if (c->initialized) {
+    INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+    INFLLM_CUDA_OK(cudaStreamSynchronize(c->copy_stream));
+  }
+  c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
+  c->init_full = false;
+  c->rope_origin = -1;
+  c->tb.t0 = 0;
+  c->lru.clear();
+  c->slot_of.clear();
+  c->free_slots.clear();
+  for (int i = c->cfg.max_cached_block - 1; i >= 0; --i) c->free_slots.push_back(i);
+  c->trace_topk.clear();
+  c->attn_recorded = false;
+  c->counters = infllm_ctx_info{};
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
+  if (!c) return INFLLM_OK;
+  if (c->initialized) {
+    cudaSetDevice(c->cfg.device);
+    cudaDeviceSynchronize();
+    free_buffers(c->tb, nullptr);
+    void* dev[] = {c->init_k, c->init_v, c->cos_t, c->sin_t, c->q_loc, c->q_glb, c->qbar, c->lse, c->st_acc, c->st_m,
+                   c->st_l, c->d_topk, c->part_o, c->part_lse, c->dec_logits, c->cache};
+    for (void* p : dev)
+      if (p) cudaFree(p);
+    if (c->block_k) cudaFreeAsync(c->block_k, nullptr);
+    if (c->scores) cudaFreeAsync(c->scores, nullptr);
+    if (c->h_topk) cudaFreeHost(c->h_topk);
+    for (void* p : c->slabs) cudaFreeHost(p);
+    cudaStreamDestroy(c->copy_stream);
+    cudaEventDestroy(c->ev_main);
+    cudaEventDestroy(c->ev_copy);
+    cudaEventDestroy(c->ev_sync);
+    cudaEventDestroy(c->ev_attn);
+    cudaDeviceSynchronize();
+  }
+  delete c;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, int64_t q_ts, const void* d_k,
+                                 int64_t k_hs, int64_t k_ts, const void* d_v, int64_t v_hs, int64_t v_ts, void* d_out,
+                                 int64_t o_hs, int64_t o_ts, int64_t len, void* stream) {
+  if (!c) return fail(INFLLM_E_BADARG, "ctx_append: null context");
+  if (len < 0 || (len > 0 && (!d_q || !d_k || !d_v || !d_out))) return fail(INFLLM_E_BADARG, "ctx_append: bad argument");
+  if (len == 0) return INFLLM_OK;
+  if ((o_hs % 2) || (o_ts % 2) || ((uintptr_t)d_out % 4))
+    return fail(INFLLM_E_BADARG, "ctx_append: output rows must be 4-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+  if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
+  c->trace_topk.clear();
+  c->counters.exec_blocks = 0;
+  const int esz = c->esz;
+  for (int64_t off = 0; off < len; off += c->sub_max) {
+    const int64_t n = std::min<int64_t>(c->sub_max, len - off);
+    INFLLM_TRY(append_sub(c, (const char*)d_q + off * q_ts * esz, q_hs, q_ts, (const char*)d_k + off * k_ts * esz, k_hs,
+                          k_ts, (const char*)d_v + off * v_ts * esz, v_hs, v_ts, (char*)d_out + off * o_ts * esz, o_hs,
+                          o_ts, n, s));
+  }
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_info(infllm_ctx* c, infllm_ctx_info* info) {
+  if (!c || !info) return fail(INFLLM_E_BADARG, "ctx_get_info: null pointer");
+  *info = c->counters;
+  info->length = c->length;
+  info->frontier = c->frontier;
+  info->num_blocks = c->num_blocks;
+  info->init_len = c->init_len;
+  info->num_cached = (int64_t)c->lru.size();
+  info->load_count = c->load_count;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_cached(infllm_ctx* c, int32_t* h_ids, double* h_stamps, int cap, int* n) {
+  if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_cached: null pointer");
+  int i = 0;
+  for (auto& kv : c->lru.items) {
+    if (i < cap) {
+      if (h_ids) h_ids[i] = kv.first;
+      if (h_stamps) h_stamps[i] = kv.second;
+    }
+    ++i;
+  }
+  *n = i;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_topk(infllm_ctx* c, int64_t eb, int32_t* h_ids, int cap, int* n) {
+  if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_topk: null pointer");
+  if (eb < 0 || eb >= (int64_t)c->trace_topk.size())
+    return fail(INFLLM_E_BADARG, "ctx_get_topk: exec block %lld of %zu", (long long)eb, c->trace_topk.size());
+  const auto& t = c->trace_topk[eb];
+  for (int i = 0; i < (int)t.size() && i < cap; ++i) h_ids[i] = t[i];
+  *n = (int)t.size();
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_block_k(infllm_ctx* c, int64_t b0, int64_t n, void* h_dst) {
+  if (!c || !h_dst) return fail(INFLLM_E_BADARG, "ctx_get_block_k: null pointer");
+  if (b0 < 0 || n < 0 || b0 + n > c->num_blocks) return fail(INFLLM_E_BADARG, "ctx_get_block_k: range outside the %lld sealed units", (long long)c->num_blocks);
+  if (n == 0) return INFLLM_OK;
+  INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+  INFLLM_CUDA_OK(cudaDeviceSynchronize());
+  INFLLM_CUDA_OK(cudaMemcpy(h_dst, (char*)c->block_k + b0 * c->width * c->esz, n * c->width * c->esz, cudaMemcpyDeviceToHost));
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_load_synthetic(infllm_ctx* c, int64_t n_units, const void* h_units, const void* h_block_k,
+                                         const void* h_init_k, const void* h_init_v, const void* h_win_k,
+                                         const void* h_win_v, void* stream) {
+  if (!c || !h_units || !h_block_k || !h_win_k || !h_win_v) return fail(INFLLM_E_BADARG, "ctx_load_synthetic: null pointer");
+  const infllm_config& g = c->cfg;
+  if (g.n_init > 0 && (!h_init_k || !h_init_v)) return fail(INFLLM_E_BADARG, "ctx_load_synthetic: null init sink");
+  cudaStream_t s = (cudaStream_t)stream;
+  INFLLM_CUDA_OK(cudaSetDevice(g.device));
+  if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
+  INFLLM_TRY(infllm_ctx_reset(c));
+  const int64_t D = g.head_dim, HKV = g.n_kv_heads;
+  INFLLM_TRY(ensure_host_units(c, n_units));
+  for (int64_t b = 0; b < n_units; ++b) memcpy(c->host_unit(b), (const char*)h_units + b * c->unit_bytes, c->unit_bytes);
+  INFLLM_TRY(ensure_block_k(c, n_units, s));
+  INFLLM_CUDA_OK(cudaMemcpyAsync(c->block_k, h_block_k, n_units * c->width * c->esz, cudaMemcpyHostToDevice, s));
+  if (g.n_init > 0) {
+    INFLLM_CUDA_OK(cudaMemcpyAsync(c->init_k, h_init_k, HKV * g.n_init * D * c->esz, cudaMemcpyHostToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpyAsync(c->init_v, h_init_v, HKV * g.n_init * D * c->esz, cudaMemcpyHostToDevice, s));
+  }
+  c->init_len = g.n_init;
+  c->init_full = true;
+  c->num_blocks = n_units;
+  c->frontier = g.n_init + n_units * (int64_t)g.block_size;
+  c->length = c->frontier;
+  // the local window enters through the ordinary ingest path, without queries: tokens only
+  INFLLM_TRY(ensure_tokens(c, g.n_local, s));
+  TokenBuffers& tb = c->tb;
+  const int64_t kv_hs = tb.cap * D;
+  void* tmp = nullptr;
+  const size_t wbytes = HKV * (int64_t)g.n_local * D * c->esz;
+  INFLLM_CUDA_OK(cudaMallocAsync(&tmp, 2 * wbytes, s));
+  INFLLM_CUDA_OK(cudaMemcpyAsync(tmp, h_win_k, wbytes, cudaMemcpyHostToDevice, s));
+  INFLLM_CUDA_OK(cudaMemcpyAsync((char*)tmp + wbytes, h_win_v, wbytes, cudaMemcpyHostToDevice, s));
+  const int64_t at = c->length - tb.t0;
+  INFLLM_TRY(copy_rows_launch(tmp, (int64_t)g.n_local * D, D, (char*)tb.k_raw + at * D * c->esz, kv_hs, D, (int)HKV,
+                              g.n_local, (int)D, s));
+  INFLLM_TRY(copy_rows_launch((char*)tmp + wbytes, (int64_t)g.n_local * D, D, (char*)tb.v + at * D * c->esz, kv_hs, D,
+                              (int)HKV, g.n_local, (int)D, s));
+  INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, g.n_local * sizeof(float), g.n_heads, s));
+  c->rope_origin = c->length;
+  INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + at * D * c->esz, kv_hs, D, (char*)tb.k_rot + at * D * c->esz, kv_hs, D,
+                               (int)HKV, g.n_local, (int)D, c->cos_t, c->sin_t, c->tab_len, 0, 1, g.dtype, s));
+  INFLLM_CUDA_OK(cudaFreeAsync(tmp, s));
+  c->length += g.n_local;
+  INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  return INFLLM_OK;
+}
+
+// ------------------------------------------------------------------ LRU table alone (host, GPU-free)
+struct infllm_lru {
+  LruTable t;
+  explicit infllm_lru(int cap) : t(cap) {}
+};
+
+extern "C" int infllm_lru_create(int capacity, infllm_lru** out) {
+  if (!out || capacity <= 0) return fail(INFLLM_E_BADARG, "lru_create: bad argument");
+  *out = new (std::nothrow) infllm_lru(capacity);
+  return *out ? INFLLM_OK : fail(INFLLM_E_NOMEM, "lru_create: out of host memory");
+}
+extern "C" int infllm_lru_destroy(infllm_lru* t) {
+  delete t;
+  return INFLLM_OK;
+}
+extern "C" int infllm_lru_plan(infllm_lru* t, const int32_t* wanted, int n, int32_t* h_evicted, int* n_evicted) {
+  if (!t || (n > 0 && !wanted) || !n_evicted) return fail(INFLLM_E_BADARG, "lru_plan: null pointer");
+  std::vector<int32_t> ev;
+  t->t.plan(wanted, n, &ev);
+  for (size_t i = 0; i < ev.size(); ++i)
+    if (h_evicted) h_evicted[i] = ev[i];
+  *n_evicted = (int)ev.size();
+  return INFLLM_OK;
+}
+extern "C" int infllm_lru_stamp(infllm_lru* t, const int32_t* wanted, int n, double value) {
+  if (!t || (n > 0 && !wanted)) return fail(INFLLM_E_BADARG, "lru_stamp: null pointer");
+  t->t.stamp(wanted, n, value);
+  return INFLLM_OK;
+}
+extern "C" int infllm_lru_scale(infllm_lru* t, double factor) {
+  if (!t) return fail(INFLLM_E_BADARG, "lru_scale: null pointer");
+  t->t.scale(factor);
+  return INFLLM_OK;
+}
+extern "C" int infllm_lru_add(infllm_lru* t, int32_t id, double value) {
+  if (!t) return fail(INFLLM_E_BADARG, "lru_add: null pointer");
+  return t->t.add(id, value) ? INFLLM_OK : fail(INFLLM_E_BADARG, "lru_add: id %d is not in the table", id);
+}
+extern "C" int infllm_lru_items(infllm_lru* t, int32_t* h_ids, double* h_stamps, int cap, int* n) {
+  if (!t || !n) return fail(INFLLM_E_BADARG, "lru_items: null pointer");
+  int i = 0;
+  for (auto& kv : t->t.items) {
+    if (i < cap) {
+      if (h_ids) h_ids[i] = kv.first;
+      if (h_stamps) h_stamps[i] = kv.second;
+    }
+    ++i;
+  }
+  *n = i;
+  return INFLLM_OK;
+}

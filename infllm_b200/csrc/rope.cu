@@ -1,0 +1,157 @@
+// Rotary position embedding kernels.
+// Follows RotaryEmbeddingESM of the reference (inf_llm/attention/rope.py): half-rotation layout,
+// fp32 tables of angle = (t * scale) * inv_freq, fp32 products added and rounded once to the
+// activation type.  HBM-bound elementwise work: 16-byte loads/stores, one thread per 8+8 elements.
+#include "common.cuh"
+
+namespace infllm {
+
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float scale, int half, int64_t length,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= length * half) return;
+  int64_t t = idx / half;
+  int f = (int)(idx - t * half);
+  float ang = __fmul_rn(__fmul_rn((float)t, scale), inv_freq[f]);  // rope.py:53-55
+  cos_t[idx] = cosf(ang);
+  sin_t[idx] = sinf(ang);
+}
+
+// x (H, L, D) strided -> out (H, L, D) strided, row t rotated to position pos0 + t*pos_step.
+template <typename T>
+__global__ void rope_apply_kernel(const T* __restrict__ x, int64_t x_hs, int64_t x_ts, T* __restrict__ out,
+                                  int64_t o_hs, int64_t o_ts, int n_heads, int64_t len, int head_dim,
+                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                  int64_t pos0, int pos_step) {
+  const int half = head_dim / 2;
+  const int chunks = half / 8;  // 16-byte chunks per half row
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_heads * len * chunks;
+  if (idx >= total) return;
+  int c = (int)(idx % chunks);
+  int64_t t = (idx / chunks) % len;
+  int h = (int)(idx / ((int64_t)chunks * len));
+  const T* src = x + h * x_hs + t * x_ts + c * 8;
+  T* dst = out + h * o_hs + t * o_ts + c * 8;
+  int64_t pos = pos0 + t * pos_step;
+  const float* cs = cos_t + pos * half + c * 8;
+  const float* sn = sin_t + pos * half + c * 8;
+  uint4 lo = *reinterpret_cast<const uint4*>(src);
+  uint4 hi = *reinterpret_cast<const uint4*>(src + half);
+  const T* a = reinterpret_cast<const T*>(&lo);
+  const T* b = reinterpret_cast<const T*>(&hi);
+  uint4 olo, ohi;
+  T* oa = reinterpret_cast<T*>(&olo);
+  T* ob = reinterpret_cast<T*>(&ohi);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float x1 = Act<T>::to_f(a[i]), x2 = Act<T>::to_f(b[i]);
+    float cv = cs[i], sv = sn[i];
+    // (x * cos) + (rotate_half(x) * sin), each product rounded to fp32 first (rope.py:47)
+    oa[i] = Act<T>::from_f(__fadd_rn(__fmul_rn(x1, cv), __fmul_rn(-x2, sv)));
+    ob[i] = Act<T>::from_f(__fadd_rn(__fmul_rn(x2, cv), __fmul_rn(x1, sv)));
+  }
+  *reinterpret_cast<uint4*>(dst) = olo;
+  *reinterpret_cast<uint4*>(dst + half) = ohi;
+}
+
+// plain strided row copy (H, L, D) -> (H, L, D), 16 bytes per thread
+template <typename T>
+__global__ void copy_rows_kernel(const T* __restrict__ x, int64_t x_hs, int64_t x_ts, T* __restrict__ out,
+                                 int64_t o_hs, int64_t o_ts, int n_heads, int64_t len, int head_dim) {
+  const int chunks = head_dim / 8;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_heads * len * chunks;
+  if (idx >= total) return;
+  int c = (int)(idx % chunks);
+  int64_t t = (idx / chunks) % len;
+  int h = (int)(idx / ((int64_t)chunks * len));
+  *reinterpret_cast<uint4*>(out + h * o_hs + t * o_ts + c * 8) =
+      *reinterpret_cast<const uint4*>(x + h * x_hs + t * x_ts + c * 8);
+}
+
+// mean over the rows of each exec block of the one-angle-rotated queries:
+// qbar[e, h*D + d] = mean_t q[h, e*exc + t, d]  (context_manager.py:373-375), fp32.
+template <typename T>
+__global__ void qbar_kernel(const T* __restrict__ q, int64_t q_hs, int64_t q_ts, int64_t len, int exc,
+                            int head_dim, float* __restrict__ qbar, int64_t qbar_stride) {
+  int e = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  int64_t st = (int64_t)e * exc;
+  int64_t ed = st + exc < len ? st + exc : len;
+  float acc = 0.f;
+  const T* p = q + h * q_hs + d;
+  for (int64_t t = st; t < ed; ++t) acc += Act<T>::to_f(p[t * q_ts]);
+  qbar[e * qbar_stride + (int64_t)h * head_dim + d] = acc / (float)(ed - st);
+}
+
+int rope_apply_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
+                      int n_heads, int64_t len, int head_dim, const float* cos_t, const float* sin_t,
+                      int64_t table_len, int64_t pos0, int pos_step, int dtype, cudaStream_t s) {
+  if (len == 0) return INFLLM_OK;
+  if (head_dim % 16 != 0) return fail(INFLLM_E_BADARG, "rope: head_dim %d is not a multiple of 16", head_dim);
+  if (pos0 < 0 || pos0 + (len - 1) * pos_step >= table_len)
+    return fail(INFLLM_E_BADARG, "rope: positions [%lld, %lld] outside the table of %lld rows", (long long)pos0,
+                (long long)(pos0 + (len - 1) * pos_step), (long long)table_len);
+  if ((x_hs | x_ts | o_hs | o_ts) % 8 != 0 || ((uintptr_t)x | (uintptr_t)out) % 16 != 0)
+    return fail(INFLLM_E_BADARG, "rope: rows must be 16-byte aligned");
+  int64_t total = (int64_t)n_heads * len * (head_dim / 16);
+  int threads = 256;
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    rope_apply_kernel<T><<<(unsigned)ceil_div(total, threads), threads, 0, s>>>(
+        (const T*)x, x_hs, x_ts, (T*)out, o_hs, o_ts, n_heads, len, head_dim, cos_t, sin_t, pos0, pos_step);
+  });
+  INFLLM_LAUNCH_OK("rope_apply_kernel");
+  return INFLLM_OK;
+}
+
+int copy_rows_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
+                     int n_heads, int64_t len, int head_dim, cudaStream_t s) {
+  if (len == 0) return INFLLM_OK;
+  if ((x_hs | x_ts | o_hs | o_ts) % 8 != 0 || ((uintptr_t)x | (uintptr_t)out) % 16 != 0 || head_dim % 8)
+    return fail(INFLLM_E_BADARG, "copy_rows: rows must be 16-byte aligned");
+  int64_t total = (int64_t)n_heads * len * (head_dim / 8);
+  copy_rows_kernel<__half><<<(unsigned)ceil_div(total, 256), 256, 0, s>>>(
+      (const __half*)x, x_hs, x_ts, (__half*)out, o_hs, o_ts, n_heads, len, head_dim);
+  INFLLM_LAUNCH_OK("copy_rows_kernel");
+  return INFLLM_OK;
+}
+
+int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t len, int exc, int head_dim,
+                float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s) {
+  if (len == 0) return INFLLM_OK;
+  dim3 grid((unsigned)ceil_div(len, exc), n_heads);
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    qbar_kernel<T><<<grid, head_dim, 0, s>>>((const T*)q, q_hs, q_ts, len, exc, head_dim, qbar, qbar_stride);
+  });
+  INFLLM_LAUNCH_OK("qbar_kernel");
+  return INFLLM_OK;
+}
+
+}  // namespace infllm
+
+extern "C" int infllm_rope_table(const float* h_inv_freq, float scale, int head_dim, int64_t length,
+                                 float* d_cos, float* d_sin, void* stream) {
+  using namespace infllm;
+  if (!h_inv_freq || !d_cos || !d_sin || head_dim <= 0 || head_dim % 2 || length <= 0)
+    return fail(INFLLM_E_BADARG, "rope_table: bad argument");
+  cudaStream_t s = (cudaStream_t)stream;
+  int half = head_dim / 2;
+  float* d_inv = nullptr;
+  INFLLM_CUDA_OK(cudaMallocAsync(&d_inv, half * sizeof(float), s));
+  INFLLM_CUDA_OK(cudaMemcpyAsync(d_inv, h_inv_freq, half * sizeof(float), cudaMemcpyHostToDevice, s));
+  int64_t total = length * half;
+  rope_table_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, s>>>(d_inv, scale, half, length, d_cos, d_sin);
+  INFLLM_LAUNCH_OK("rope_table_kernel");
+  INFLLM_CUDA_OK(cudaFreeAsync(d_inv, s));
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_rope_apply(const void* d_x, int64_t x_hs, int64_t x_ts, void* d_out, int64_t o_hs,
+                                 int64_t o_ts, int n_heads, int64_t len, int head_dim, const float* d_cos,
+                                 const float* d_sin, int64_t table_len, int64_t pos0, int pos_step, int dtype,
+                                 void* stream) {
+  using namespace infllm;
+  if (!d_x || !d_out || !d_cos || !d_sin) return fail(INFLLM_E_BADARG, "rope_apply: null pointer");
+  return rope_apply_launch(d_x, x_hs, x_ts, d_out, o_hs, o_ts, n_heads, len, head_dim, d_cos, d_sin, table_len,
+                           pos0, pos_step, dtype, (cudaStream_t)stream);
+}
