@@ -29,7 +29,8 @@ struct DecodeParams {
   uint8_t qsel[kMaxSeg];            // query variant per segment
   int32_t n_seg, n_heads, n_kv_heads;
   int32_t logit_seg;  // segment whose raw logits are exported, or -1
-  const void* q[2];   // (H, D) each
+  const void* q[2];   // (H, D) each, heads q_hs elements apart
+  int64_t q_hs;
   float* part_o;      // (n_part, H, D)
   float* part_lse;    // (n_part, H)
   float* logits;      // (H, seg_len[logit_seg])
@@ -42,7 +43,7 @@ attn_decode_kernel(const __grid_constant__ DecodeParams P) {
   static_assert(HD == 128, "one half-warp covers a 128-element row");
   __shared__ float s_q[kMaxGroup][HD];
   __shared__ float s_p[kMaxGroup][kDecodeChunk];
-  __shared__ float s_o[kDecodeThreads / 16][kMaxGroup][HD / 16][8 + 1];
+  __shared__ float s_o[kDecodeThreads / 16][kMaxGroup][HD / 8][8 + 1];  // [half-warp][head][16-byte chunk][element]
   __shared__ float s_m[kMaxGroup], s_l[kMaxGroup];
 
   const int part = blockIdx.x, hkv = blockIdx.y;
@@ -55,7 +56,7 @@ attn_decode_kernel(const __grid_constant__ DecodeParams P) {
   const T* qsrc = (const T*)P.q[P.qsel[sg]];
   for (int i = threadIdx.x; i < group * HD; i += kDecodeThreads) {
     int gi = i / HD, d = i % HD;
-    s_q[gi][d] = Act<T>::to_f(qsrc[(int64_t)(hkv * group + gi) * HD + d]);
+    s_q[gi][d] = Act<T>::to_f(qsrc[(int64_t)(hkv * group + gi) * P.q_hs + d]);
   }
   __syncthreads();
 
@@ -211,7 +212,7 @@ int decode_score_launch(const float* logits, int64_t len, const float* lse, floa
   return INFLLM_OK;
 }
 
-int attn_decode_launch(const void* q0, const void* q1, int n_heads, int n_kv_heads, int head_dim, int n_seg,
+int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
                        int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s) {
   if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "decode attention: head_dim %d (128 is built)", head_dim);
@@ -238,7 +239,7 @@ int attn_decode_launch(const void* q0, const void* q1, int n_heads, int n_kv_hea
   if (parts == 0) return INFLLM_OK;
   if (parts > max_parts) return fail(INFLLM_E_CAPACITY, "decode attention: %d partials exceed the scratch for %d", parts, max_parts);
   P.n_seg = ns; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.logit_seg = logit_seg_packed;
-  P.q[0] = q0; P.q[1] = q1 ? q1 : q0;
+  P.q[0] = q0; P.q[1] = q1 ? q1 : q0; P.q_hs = q_hs;
   P.part_o = part_o; P.part_lse = part_lse; P.logits = logits;
   P.scale_log2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid(parts, n_kv_heads);
@@ -275,7 +276,7 @@ extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_head
   if (logit_seg >= 0 && !d_logits) return fail(INFLLM_E_BADARG, "attn_decode: logits requested without a buffer");
   KvSeg segs[kMaxSeg];
   for (int i = 0; i < n_seg; ++i) segs[i] = {h_seg_k[i], h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
-  return attn_decode_launch(d_q0, d_q1, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o, d_part_lse,
+  return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o, d_part_lse,
                             max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream);
 }
 

@@ -33,7 +33,7 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
 int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
                        int64_t tok0, int n_new, int block_size, int repr_topk, int n_heads, int n_kv_heads,
                        int head_dim, void* out, int dtype, cudaStream_t s);
-int attn_decode_launch(const void* q0, const void* q1, int n_heads, int n_kv_heads, int head_dim, int n_seg,
+int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
                        int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s);
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
@@ -329,7 +329,6 @@ int retrieve_and_refill(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids
     INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
     ids->assign(c->h_topk, c->h_topk + g.topk);
   }
-  if (ids->empty()) return INFLLM_OK;
   std::vector<int32_t> evicted;
   c->lru.plan(ids->data(), (int)ids->size(), &evicted);
   for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
@@ -501,7 +500,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         // all segments fit one launch in every supported configuration; guard anyway
         if (segs.size() > (size_t)kMaxSeg)
           return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
-        INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
+        INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
                                       qsel.data(), c->part_o, c->part_lse, c->max_parts, &parts, 0, c->dec_logits,
                                       g.dtype, s));
         base = segs.size();
