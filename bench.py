@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the context-memory attention layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T]
+
+Workload (N=1): one Mistral-7B-shaped attention layer in bf16 — hidden 4096, 32 query / 8 KV heads,
+head_dim 128, RoPE base 1e6 — over a 131072-token prompt of seeded N(0,1) hidden states fed through
+the attention-forward API in 8192-token calls and executed in 512-token exec blocks; n_init 128,
+n_local 4096, memory units of 128 tokens, topk 16, repr_topk 4, max_cached_block 32, LRU.  64 units are
+"planted": their hidden states lean (cos 0.6) towards a direction that a later 512-token query span
+leans towards in projection space, so retrieval has real winners.  One step = one whole prompt.
+
+Prints ONE JSON line.  `value` is tokens/s with the hidden states resident in HBM, `e2e` the same
+through the same call with hidden states in pinned host memory (H2D and D2H copies timed),
+`roofline` the exec-block attention kernel against the measured tensor peak, `cpu_baseline` the CPU
+oracle (a restatement of the reference's torch path) on the host cores for a bounded steady-state
+sample.  `--impl reference` times only that CPU path.  With N > 1 (torchrun) every rank runs its own
+prompt through its own layer replica: the path has no cross-sequence exchange, so scaling is weak and
+there is no collective on the data path.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(hidden=4096, H=32, HKV=8, D=128, base=1e6, n_init=128, n_local=4096, bs=128, topk=16, repr_topk=4,
+           max_cached=32, exc=512, chunk=8192, tokens=131072, planted=64)
+
+
+# ------------------------------------------------------------------------------------ workload
+def make_weights(device, dtype):
+    ws = []
+    for seed, shape in zip((1, 2, 3, 4), ((CFG["H"] * CFG["D"], CFG["hidden"]), (CFG["HKV"] * CFG["D"], CFG["hidden"]),
+                                          (CFG["HKV"] * CFG["D"], CFG["hidden"]), (CFG["hidden"], CFG["H"] * CFG["D"]))):
+        g = torch.Generator().manual_seed(seed)
+        ws.append((torch.randn(shape, generator=g) * 0.02).to(device=device, dtype=dtype))
+    return ws
+
+
+def make_hidden(tokens, seed, weights, device):
+    """(1, tokens, hidden) bf16 on `device`: N(0,1) with planted key units and matching query spans."""
+    wq, wk, _, _ = weights
+    g = torch.Generator(device=device).manual_seed(seed)
+    h = torch.empty((1, tokens, CFG["hidden"]), dtype=torch.bfloat16, device=device)
+    step = 16384
+    for s in range(0, tokens, step):
+        n = min(step, tokens - s)
+        h[0, s:s + n] = torch.randn((n, CFG["hidden"]), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    n_units = (tokens - CFG["n_init"] - CFG["n_local"]) // CFG["bs"]
+    n_plant = min(CFG["planted"], max(n_units // 4, 0))
+    if n_plant:
+        gc = torch.Generator().manual_seed(5)
+        units = torch.randperm(n_units, generator=gc)[:n_plant].tolist()
+        u = torch.randn((n_plant, CFG["hidden"]), generator=gc).to(device)
+        u = u / u.norm(dim=1, keepdim=True)
+        # query-side direction whose projection points where the planted keys' projection points
+        grp = CFG["H"] // CFG["HKV"]
+        target = (wk.float() @ u.T).view(CFG["HKV"], 1, CFG["D"], n_plant).expand(-1, grp, -1, -1).reshape(-1, n_plant)
+        w = torch.linalg.lstsq(wq.float(), target).solution.T  # (n_plant, hidden)
+        w = w / w.norm(dim=1, keepdim=True)
+        scale = math.sqrt(CFG["hidden"])
+        n_eb = tokens // CFG["exc"]
+        for i, b in enumerate(units):
+            st = CFG["n_init"] + b * CFG["bs"]
+            blk = h[0, st:st + CFG["bs"]].float()
+            h[0, st:st + CFG["bs"]] = (0.8 * blk + 0.6 * scale * u[i]).to(torch.bfloat16)
+            first_eb = (st + CFG["bs"] + CFG["n_local"]) // CFG["exc"] + 2  # first exec block that can retrieve it
+            if first_eb >= n_eb:
+                continue
+            eb = first_eb + int(torch.randint(0, n_eb - first_eb, (1,), generator=gc))
+            span = h[0, eb * CFG["exc"]:(eb + 1) * CFG["exc"]].float()
+            h[0, eb * CFG["exc"]:(eb + 1) * CFG["exc"]] = (0.8 * span + 0.6 * scale * w[i]).to(torch.bfloat16)
+    return h
+
+
+class Layer:
+    """The attention layer as a caller of the attention-forward API sees it."""
+
+    def __init__(self, device, forward, rope, dtype=torch.bfloat16):
+        self.wq, self.wk, self.wv, self.wo = make_weights(device, dtype)
+        self.forward, self.rope, self.pkv = forward, rope, None
+        lin = torch.nn.functional.linear
+        self.pq, self.pk = (lambda x: lin(x, self.wq)), (lambda x: lin(x, self.wk))
+        self.pv, self.po = (lambda x: lin(x, self.wv)), (lambda x: lin(x, self.wo))
+
+    def __call__(self, x):
+        o, self.pkv = self.forward(None, x, x, self.rope, True, self.pkv, self.pq, self.pk, self.pv, self.po,
+                                   CFG["D"], CFG["H"], CFG["HKV"])
+        return o
+
+    def reset(self):
+        if self.pkv is not None:
+            self.pkv.reset()
+
+
+def prefill_device(layer, hidden):
+    layer.reset()
+    out = None
+    for s in range(0, hidden.size(1), CFG["chunk"]):
+        out = layer(hidden[:, s:s + CFG["chunk"]])
+    return out
+
+
+def prefill_host(layer, h_hidden, h_out, d_in, d_out_unused=None):
+    """Same prompt with the hidden states in pinned host memory: every chunk is copied in, its output copied out."""
+    layer.reset()
+    for s in range(0, h_hidden.size(1), CFG["chunk"]):
+        n = min(CFG["chunk"], h_hidden.size(1) - s)
+        d_in[:, :n].copy_(h_hidden[:, s:s + n], non_blocking=True)
+        o = layer(d_in[:, :n])
+        h_out[:, s:s + n].copy_(o, non_blocking=True)
+
+
+# --------------------------------------------------------------------------------- CPU oracle arm
+def cpu_steady_state_sample(tokens_at=65536, sample_tokens=2048, repeats=1, threads=None):
+    """Times the CPU oracle (the reference's torch path restated) on `sample_tokens` tokens of the same
+    layer in steady state: context memory pre-filled to `tokens_at` tokens (seeded random keys, values,
+    representative keys and scores), projections included.  Returns (tokens/s, seconds, cores)."""
+    from oracle.infllm_oracle import OracleContextMemory
+
+    if threads:
+        torch.set_num_threads(threads)
+    cores = torch.get_num_threads()
+    wq, wk, wv, wo = make_weights("cpu", torch.float32)
+    g = torch.Generator().manual_seed(99)
+    best = None
+    for _ in range(repeats):
+        mem = OracleContextMemory(CFG["n_init"], CFG["n_local"], CFG["bs"], CFG["max_cached"], CFG["topk"], CFG["exc"],
+                                  CFG["repr_topk"], CFG["base"], 1.0)
+        nb = (tokens_at - CFG["n_local"] - CFG["n_init"]) // CFG["bs"]
+        mem.length = tokens_at
+        mem.init_len, mem.init_full = CFG["n_init"], True
+        mem.frontier = CFG["n_init"] + nb * CFG["bs"]
+        mem.k_log = torch.randn((CFG["HKV"], tokens_at, CFG["D"]), generator=g)
+        mem.v_log = torch.randn((CFG["HKV"], tokens_at, CFG["D"]), generator=g)
+        mem.acc = torch.rand((CFG["H"], tokens_at), generator=g)
+        mem.block_k = list(torch.randn((nb, CFG["H"] * CFG["D"]), generator=g))
+        x = torch.randn((sample_tokens, CFG["hidden"]), generator=g)
+        t0 = time.perf_counter()
+        with torch.inference_mode():
+            q = (x @ wq.T).view(sample_tokens, CFG["H"], CFG["D"]).permute(1, 0, 2)
+            k = (x @ wk.T).view(sample_tokens, CFG["HKV"], CFG["D"]).permute(1, 0, 2)
+            v = (x @ wv.T).view(sample_tokens, CFG["HKV"], CFG["D"]).permute(1, 0, 2)
+            o = mem.append(q, k, v)
+            _ = o.permute(1, 0, 2).reshape(sample_tokens, -1) @ wo.T
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_tokens / best, best, cores
+
+
+SAMPLE_DESC = ("{n} tokens ({eb} exec blocks of 512) of the same layer in steady state at 65536 tokens of context "
+               "(479 sealed units, full window), projections included, fp32 torch on the host")
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    n = 2048
+    for _ in range(args.warmup):
+        cpu_steady_state_sample(sample_tokens=n)
+    t0 = time.perf_counter()
+    cores = 0
+    for _ in range(args.steps):
+        _, _, cores = cpu_steady_state_sample(sample_tokens=n)
+    dt = time.perf_counter() - t0
+    val = n * args.steps / dt
+    line = dict(metric="exec-block prefill tokens/s/GPU @128K ctx", value=val, unit="tokens/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps, higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload="mistral-7b attention layer, 131072-token prefill, exec 512, n_local 4096, "
+                                     "topk 16, repr_topk 4, max_cached 32 (CPU arm: steady-state sample)"),
+                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port",
+                                  sample=SAMPLE_DESC.format(n=n, eb=n // 512)),
+                e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------- GPU arm
+def sample_clocks_start(gpu_index):
+    f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+    q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    try:
+        p = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                              "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+    except OSError:
+        return None, f
+    return p, f
+
+
+def sample_clocks_stop(p, f):
+    if p is not None:
+        p.terminate()
+        try:
+            p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            p.kill()
+    f.flush()
+    f.seek(0)
+    sm, mx, reasons = [], 0, set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for ln in f.read().splitlines():
+        parts = [x.strip() for x in ln.split(",")]
+        if len(parts) < 7:
+            continue
+        try:
+            sm.append(float(parts[0]))
+            mx = max(mx, float(parts[1]))
+        except ValueError:
+            continue
+        for nme, val in zip(names, parts[3:7]):
+            if val.lower().startswith("active"):
+                reasons.add(nme)
+    f.close()
+    os.unlink(f.name)
+    sm.sort()
+    med = sm[len(sm) // 2] if sm else None
+    return dict(sm_mhz=med, sm_max_mhz=mx or None, reasons=sorted(reasons), samples=len(sm))
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops_sustained") or d.get("bf16_tflops"), d.get("hbm_gbs"), "measured"
+    return 1400.0, 6650.0, "fallback"
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from infllm_b200 import _lib
+    from infllm_b200.attention import ATTN_FORWRAD, RotaryEmbeddingESM
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    tokens = args.tokens
+    fwd = ATTN_FORWRAD["inf-llm"](n_local=CFG["n_local"], n_init=CFG["n_init"], topk=CFG["topk"], block_size=CFG["bs"],
+                                  max_cached_block=CFG["max_cached"], exc_block_size=CFG["exc"], fattn=True,
+                                  repr_topk=CFG["repr_topk"])
+    layer = Layer(dev, fwd, RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0))
+    hidden = make_hidden(tokens, seed=rank, weights=(layer.wq, layer.wk, layer.wv, layer.wo), device=dev)
+    h_hidden = torch.empty(hidden.shape, dtype=hidden.dtype, pin_memory=True)
+    h_hidden.copy_(hidden)
+    h_out = torch.empty((1, tokens, CFG["hidden"]), dtype=hidden.dtype, pin_memory=True)
+    d_in = torch.empty((1, CFG["chunk"], CFG["hidden"]), dtype=hidden.dtype, device=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    with torch.inference_mode():
+        for _ in range(args.warmup):
+            prefill_device(layer, hidden)
+        layer.pkv.profile(True)
+        layer.pkv.get_profile()
+        clk_p, clk_f = sample_clocks_start(local_rank)
+        l0 = _lib.lib.infllm_launch_count()
+        ms = timed(lambda: prefill_device(layer, hidden), args.steps)
+        launches = _lib.lib.infllm_launch_count() - l0
+        prof = layer.pkv.get_profile()
+        info = layer.pkv.info()
+        layer.pkv.profile(False)
+        clocks = sample_clocks_stop(clk_p, clk_f)
+        for _ in range(min(args.warmup, 1)):
+            prefill_host(layer, h_hidden, h_out, d_in)
+        ms_e2e = timed(lambda: (prefill_host(layer, h_hidden, h_out, d_in), h_out[0, -1, 0].item()), args.steps)
+
+    value = world * tokens * args.steps / (ms / 1e3)
+    e2e = world * tokens * args.steps / (ms_e2e / 1e3)
+    tf_peak, _, which = measured_peaks()
+    attn_ms, attn_flops, attn_n = prof["attn"]
+    achieved = attn_flops / (attn_ms / 1e3) / 1e12 if attn_ms > 0 else None
+    line = dict(
+        metric="exec-block prefill tokens/s/GPU @128K ctx", value=value, unit="tokens/s", n_gpus=world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload=f"mistral-7b attention layer (hidden 4096, 32q/8kv, d128, rope 1e6), {tokens}-token prefill "
+                             "in 8192-token calls, exec 512, n_init 128, n_local 4096, unit 128, topk 16, repr_topk 4, "
+                             "max_cached 32, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
+                    replicas=world),
+        e2e=dict(value=e2e, unit="tokens/s", h2d_bytes_per_step=int(hidden.numel() * 2),
+                 d2h_bytes_per_step=int(h_out.numel() * 2), ms_per_step=ms_e2e / args.steps),
+        gpu_launches=int(launches),
+        roofline=dict(bound="tensor", kernel="exec-block attention (local + global stage)", achieved=achieved,
+                      peak=tf_peak, unit="TFLOP/s", frac=(achieved / tf_peak if achieved else None), traffic=None,
+                      peak_source=f"bf16_tflops_sustained of {which}", launches=int(attn_n),
+                      us_per_launch=1e3 * attn_ms / max(attn_n, 1),
+                      flops_per_launch=attn_flops / max(attn_n, 1)),
+        kernels={k: dict(ms=v[0], launches=v[2]) for k, v in prof.items()},
+        store=dict(h2d_bytes=info["h2d_bytes"], d2h_bytes=info["d2h_bytes"], hits=info["cache_hits"],
+                   misses=info["cache_misses"], evictions=info["evictions"]),
+        clocks=clocks)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
+        line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port", seconds=secs,
+                                    sample=SAMPLE_DESC.format(n=2048, eb=4))
+    if rank == 0:
+        print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=CFG["tokens"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    run_ours(args, rank, world, local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

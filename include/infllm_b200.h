@@ -194,6 +194,20 @@ typedef struct infllm_ctx_info {
   int64_t cache_hits, cache_misses, evictions;
 } infllm_ctx_info;
 int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
+/* Per-kernel timing, off by default.  When enabled, the context records a CUDA event pair around each
+ * launch of its hot kernels on the stream they run on.  infllm_ctx_get_profile synchronises, adds up
+ * and clears the records: for each slot the device milliseconds, the algorithmic work (FLOPs of visible
+ * query-key pairs for the attention slots, bytes for the HBM-bound slots) and the number of launches. */
+#define INFLLM_PROF_ATTN 0   /* exec-block attention: 4*D*H*(visible pairs) FLOPs */
+#define INFLLM_PROF_COLSUM 1 /* local-score pass: 2*D*H*(visible local pairs) FLOPs */
+#define INFLLM_PROF_DECODE 2 /* one-token attention: K and V bytes of every attended key */
+#define INFLLM_PROF_TOPK 3   /* unit scoring + top-k: bytes of the representative keys */
+#define INFLLM_PROF_SLOTS 4
+int infllm_ctx_profile(infllm_ctx* ctx, int enable);
+int infllm_ctx_get_profile(infllm_ctx* ctx, double* ms, double* work, int64_t* launches);
+/* Number of kernels this library has launched in the process so far. */
+long long infllm_launch_count(void);
+
 /* cached_blocks[u] in dict order: ids and stamps (LRU clock, or lru-s score). Returns count in *n. */
 int infllm_ctx_get_cached(infllm_ctx* ctx, int32_t* h_ids, double* h_stamps, int cap, int* n);
 /* Retrieval of exec block `eb` of the last append, in the order the scorer returned it. */

@@ -15,6 +15,7 @@ BF16, FP16 = 0, 1
 CACHE_LRU, CACHE_LRU_S = 0, 1
 MASK_NONE, MASK_WINDOW, MASK_COMPLEMENT = 0, 1, 2
 MAX_SEGMENTS = 80
+PROF_ATTN, PROF_COLSUM, PROF_DECODE, PROF_TOPK, PROF_SLOTS = 0, 1, 2, 3, 4
 
 
 class InfLLMError(RuntimeError):
@@ -78,6 +79,9 @@ SIGNATURES = {
     "infllm_ctx_append": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                   c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "infllm_ctx_get_info": (c_int, [c_void_p, POINTER(CtxInfo)]),
+    "infllm_ctx_profile": (c_int, [c_void_p, c_int]),
+    "infllm_ctx_get_profile": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), POINTER(c_int64)]),
+    "infllm_launch_count": (ctypes.c_longlong, []),
     "infllm_ctx_get_cached": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_double), c_int, POINTER(c_int)]),
     "infllm_ctx_get_topk": (c_int, [c_void_p, c_int64, POINTER(c_int32), c_int, POINTER(c_int)]),
     "infllm_ctx_get_block_k": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),

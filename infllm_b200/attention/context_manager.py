@@ -74,6 +74,8 @@ class ContextManager:
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))
             self._ctx.append(h)
+            if getattr(self, "_profile", False):
+                _lib.check(_lib.lib.infllm_ctx_profile(h, 1))
         self.initialized = True
 
     def __del__(self):
@@ -166,6 +168,26 @@ class ContextManager:
         if n:
             _lib.check(_lib.lib.infllm_ctx_get_block_k(self._ctx[u], 0, n, t.data_ptr()))
         return t
+
+    def profile(self, enable=True):
+        """Time the hot kernels with CUDA events on their stream (off by default)."""
+        self._profile = bool(enable)
+        for h in self._ctx:
+            _lib.check(_lib.lib.infllm_ctx_profile(h, int(enable)))
+
+    def get_profile(self):
+        """{slot: (device ms, algorithmic work, launches)} summed over units since the last call."""
+        names = ("attn", "colsum", "decode", "topk")
+        tot = {n: [0.0, 0.0, 0] for n in names}
+        for h in self._ctx:
+            ms, work = (ctypes.c_double * _lib.PROF_SLOTS)(), (ctypes.c_double * _lib.PROF_SLOTS)()
+            n = (ctypes.c_int64 * _lib.PROF_SLOTS)()
+            _lib.check(_lib.lib.infllm_ctx_get_profile(h, ms, work, n))
+            for i, name in enumerate(names):
+                tot[name][0] += ms[i]
+                tot[name][1] += work[i]
+                tot[name][2] += n[i]
+        return {k: tuple(v) for k, v in tot.items()}
 
     def reset(self):
         for h in self._ctx:

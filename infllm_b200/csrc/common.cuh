@@ -15,6 +15,7 @@ namespace infllm {
 // ---- error plumbing: one message per host thread, codes from the public header
 void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
+void count_launch();  // every kernel launch of the library is counted (infllm_launch_count)
 
 #define INFLLM_CUDA_OK(expr)                                                                  \
   do {                                                                                        \
@@ -29,6 +30,7 @@ int fail(int code, const char* fmt, ...);
     cudaError_t _e = cudaGetLastError();                                                      \
     if (_e != cudaSuccess)                                                                    \
       return ::infllm::fail(INFLLM_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+    ::infllm::count_launch();                                                                 \
   } while (0)
 
 #define INFLLM_TRY(expr)        \

@@ -167,6 +167,15 @@ struct infllm_ctx {
   cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr;
   bool attn_recorded = false;
 
+  // optional per-kernel timing (infllm_ctx_profile): CUDA events around the launches on their stream
+  bool prof = false;
+  std::vector<cudaEvent_t> ev_pool;
+  size_t ev_used = 0;
+  struct Pending { int slot; cudaEvent_t a, b; };
+  std::vector<Pending> pending;
+  double prof_ms[INFLLM_PROF_SLOTS] = {0}, prof_work[INFLLM_PROF_SLOTS] = {0};
+  int64_t prof_launches[INFLLM_PROF_SLOTS] = {0};
+
   // trace of the last append
   std::vector<std::vector<int32_t>> trace_topk;
   infllm_ctx_info counters{};
@@ -177,6 +186,32 @@ struct infllm_ctx {
 namespace {
 
 int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// timing scope: records an event pair around the launches issued while it lives
+struct ProfScope {
+  infllm_ctx* c;
+  cudaStream_t s;
+  int slot;
+  cudaEvent_t a = nullptr, b = nullptr;
+  ProfScope(infllm_ctx* c_, cudaStream_t s_, int slot_, double work) : c(c_), s(s_), slot(slot_) {
+    if (!c->prof) return;
+    while (c->ev_pool.size() < c->ev_used + 2) {
+      cudaEvent_t e;
+      if (cudaEventCreate(&e) != cudaSuccess) return;
+      c->ev_pool.push_back(e);
+    }
+    a = c->ev_pool[c->ev_used++];
+    b = c->ev_pool[c->ev_used++];
+    c->prof_work[slot] += work;
+    c->prof_launches[slot] += 1;
+    cudaEventRecord(a, s);
+  }
+  ~ProfScope() {
+    if (!a) return;
+    cudaEventRecord(b, s);
+    c->pending.push_back({slot, a, b});
+  }
+};
 
 int free_buffers(TokenBuffers& tb, cudaStream_t s) {
   if (tb.k_raw) INFLLM_CUDA_OK(cudaFreeAsync(tb.k_raw, s));
@@ -322,8 +357,11 @@ int retrieve_and_refill(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids
     for (int64_t b = 0; b < n; ++b) ids->push_back((int32_t)b);
   } else {
     INFLLM_TRY(ensure_scores(c, n, s));
-    INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
-                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s));
+    {
+      ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
+      INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
+                                   g.topk, 0, c->d_topk, nullptr, g.dtype, s));
+    }
     INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
     INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
@@ -496,6 +534,9 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         qsel.push_back(1);
       }
       int parts = 0;
+      double dec_keys = 0;
+      for (auto& sgm : segs) dec_keys += sgm.len;
+      ProfScope ps(c, s, INFLLM_PROF_DECODE, dec_keys * HKV * D * 2 * esz);
       for (size_t base = 0; base < segs.size();) {
         // all segments fit one launch in every supported configuration; guard anyway
         if (segs.size() > (size_t)kMaxSeg)
@@ -533,7 +574,13 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       P.stage[1].q = qglb_eb; P.stage[1].q_hs = q_hs_s; P.stage[1].q_ts = D;
       P.stage[1].mask_mode = INFLLM_MASK_NONE; P.stage[1].lk = glk; P.stage[1].seg_begin = 1; P.stage[1].seg_end = nseg;
       P.last = done == gsegs.size();
-      INFLLM_TRY(attn_general_launch(P, (int)D, g.dtype, s));
+      double local_pairs = 0, all_glk = 0;
+      for (int64_t i = 0; i < lq; ++i) local_pairs += (double)std::min<int64_t>(S + i + 1, g.n_local);
+      for (auto& sgm : gsegs) all_glk += sgm.len;
+      {
+        ProfScope ps(c, s, INFLLM_PROF_ATTN, 4.0 * D * H * (local_pairs + (double)lq * all_glk));
+        INFLLM_TRY(attn_general_launch(P, (int)D, g.dtype, s));
+      }
       while (done < gsegs.size()) {  // more segments than one launch holds: carry the state
         AttnParams R{};
         R.n_heads = (int)H; R.n_kv_heads = (int)HKV; R.lq = lq; R.first = 0;
@@ -550,9 +597,11 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         }
         R.stage[0].lk = rl; R.stage[0].seg_begin = 0; R.stage[0].seg_end = ns;
         R.last = done == gsegs.size();
+        ProfScope ps(c, s, INFLLM_PROF_ATTN, 0.0);
         INFLLM_TRY(attn_general_launch(R, (int)D, g.dtype, s));
       }
       // accumulated local score of every window key (context_manager.py:488, 623-625)
+      ProfScope ps(c, s, INFLLM_PROF_COLSUM, 2.0 * D * H * local_pairs);
       INFLLM_TRY(attn_colsum_launch(qloc_eb, q_hs_s, D, (char*)tb.k_rot + (ks - tb.t0) * D * esz, kv_hs, D, (int)H,
                                     (int)HKV, lq, lk, (int)D, INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse,
                                     tb.score + (ks - tb.t0), tb.cap, 1, g.dtype, s));
@@ -639,6 +688,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     cudaEventDestroy(c->ev_copy);
     cudaEventDestroy(c->ev_sync);
     cudaEventDestroy(c->ev_attn);
+    for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     cudaDeviceSynchronize();
   }
   delete c;
@@ -677,6 +727,35 @@ extern "C" int infllm_ctx_get_info(infllm_ctx* c, infllm_ctx_info* info) {
   info->init_len = c->init_len;
   info->num_cached = (int64_t)c->lru.size();
   info->load_count = c->load_count;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_profile(infllm_ctx* c, int enable) {
+  if (!c) return fail(INFLLM_E_BADARG, "ctx_profile: null context");
+  c->prof = enable != 0;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_profile(infllm_ctx* c, double* ms, double* work, int64_t* launches) {
+  if (!c || !ms || !work || !launches) return fail(INFLLM_E_BADARG, "ctx_get_profile: null pointer");
+  if (c->initialized) {
+    INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+    for (auto& p : c->pending) {
+      INFLLM_CUDA_OK(cudaEventSynchronize(p.b));
+      float t = 0.f;
+      INFLLM_CUDA_OK(cudaEventElapsedTime(&t, p.a, p.b));
+      c->prof_ms[p.slot] += t;
+    }
+  }
+  c->pending.clear();
+  c->ev_used = 0;
+  for (int i = 0; i < INFLLM_PROF_SLOTS; ++i) {
+    ms[i] = c->prof_ms[i];
+    work[i] = c->prof_work[i];
+    launches[i] = c->prof_launches[i];
+    c->prof_ms[i] = c->prof_work[i] = 0;
+    c->prof_launches[i] = 0;
+  }
   return INFLLM_OK;
 }
 
