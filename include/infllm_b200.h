@@ -205,6 +205,10 @@ int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
 #define INFLLM_PROF_SLOTS 4
 int infllm_ctx_profile(infllm_ctx* ctx, int enable);
 int infllm_ctx_get_profile(infllm_ctx* ctx, double* ms, double* work, int64_t* launches);
+/* The tensor-core kernels bound every wait on a barrier; a wait that runs out makes the kernel record
+ * an error and return instead of hanging.  infllm_device_error synchronises the device, reads the
+ * record (code 0 = none, 1 = wait ran out; `where` identifies the wait) and clears it. */
+int infllm_device_error(int* code, int* where);
 /* Number of kernels this library has launched in the process so far. */
 long long infllm_launch_count(void);
 

@@ -81,6 +81,7 @@ SIGNATURES = {
     "infllm_ctx_get_info": (c_int, [c_void_p, POINTER(CtxInfo)]),
     "infllm_ctx_profile": (c_int, [c_void_p, c_int]),
     "infllm_ctx_get_profile": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), POINTER(c_int64)]),
+    "infllm_device_error": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "infllm_launch_count": (ctypes.c_longlong, []),
     "infllm_ctx_get_cached": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_double), c_int, POINTER(c_int)]),
     "infllm_ctx_get_topk": (c_int, [c_void_p, c_int64, POINTER(c_int32), c_int, POINTER(c_int)]),
@@ -137,3 +138,10 @@ def stream_ptr(device=None):
 def require_cuda(t, what):
     if not t.is_cuda:
         raise RuntimeError(f"{what} must be a CUDA tensor: infllm_b200 has no CPU path")
+
+
+def device_error():
+    """(code, where) of the tensor-core kernels' error record; clears it.  Synchronises the device."""
+    code, where = c_int(), c_int()
+    check(lib.infllm_device_error(ctypes.byref(code), ctypes.byref(where)))
+    return code.value, where.value

@@ -4,6 +4,7 @@ The state and the exec-block loop live in libinfllm_b200 (one native context per
 see include/infllm_b200.h); this class validates arguments the way the reference does, feeds
 tensors in and exposes the reference's observable attributes."""
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -70,6 +71,8 @@ class ContextManager:
             dtype=_lib.dtype_code(q.dtype), score_decay=float(self.score_decay or 0.0), rope_base=float(pe.base),
             rope_scale=float(pe.distance_scale), device=q.device.index if q.device.index is not None else
             torch.cuda.current_device(), shard_rank=0, shard_world=1)
+        if os.environ.get("INFLLM_B200_NO_TC", "0") == "1":
+            cfg.reserved[0] = 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))

@@ -1,0 +1,627 @@
+// Tensor-core (tcgen05 + TMEM + TMA) attention kernels for head_dim 128.
+//
+// attn_tc_kernel    one 128-query tile of one head per CTA, all stages of an exec block fused:
+//                   local window stage (window-relative rotated q/k, causal window mask) and global
+//                   stage (one-angle q; retrieved units in their cache slots, init sink, overflow),
+//                   jointly normalised.  Warp-specialised: 4 softmax warps (one query row per thread,
+//                   row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
+//                   TMEM (two buffers), P goes through shared memory as a K-major operand, O stays in
+//                   TMEM for the whole tile with lazy rescaling; K/V tiles are double buffered.
+// colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes, each thread sums
+//                   exp2(s - lse) over the queries that see its key.
+// Every mbarrier wait is bounded; a wait that runs out records an error code and the CTA unwinds.
+#include <type_traits>
+
+#include "attn_common.cuh"
+#include "tc_common.cuh"
+#include "attn_tc.cuh"
+
+namespace infllm {
+
+using namespace tc;
+
+__device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] blockIdx.y
+
+__device__ __forceinline__ void record_error(int* err, int code, int where) {
+  if (atomicCAS(&err[0], 0, code) == 0) {
+    err[1] = where;
+    err[2] = blockIdx.x;
+    err[3] = blockIdx.y;
+  }
+}
+
+// wait that also gives up when another role of the CTA has already failed
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err,
+                                              int where) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+  }
+  *abort_flag = 1;
+  record_error(err, kErrWaitTimeout, where);
+  return false;
+}
+
+// tiles [first, last] of a segment that intersect the visible key range [vis_lo, vis_hi] of the stage
+__device__ __forceinline__ bool seg_tiles(int64_t vis_lo, int64_t vis_hi, int64_t seg_j0, int seg_len, int* first,
+                                          int* last) {
+  int64_t a = vis_lo - seg_j0, b = vis_hi - seg_j0;
+  if (a < 0) a = 0;
+  if (b > seg_len - 1) b = seg_len - 1;
+  if (a > b) return false;
+  *first = (int)(a / kTile);
+  *last = (int)(b / kTile);
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+namespace smem_layout {
+constexpr int kQ = 0;
+constexpr int kK = kQ + 2 * kSubTileBytes;      // two stages
+constexpr int kV = kK + 4 * kSubTileBytes;      // two stages
+constexpr int kP = kV + 4 * kSubTileBytes;
+constexpr int kBar = kP + 2 * kSubTileBytes;    // barriers + tmem slot + abort flag
+constexpr int kTotal = kBar + 256;
+}  // namespace smem_layout
+
+enum Bar { Q_FULL = 0, Q_EMPTY, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_FULL0,
+           S_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, P_EMPTY, O_FULL, N_BARS };
+
+template <typename T>
+__global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__ AttnTcParams P) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t sQ = s_base + smem_layout::kQ, sK = s_base + smem_layout::kK, sV = s_base + smem_layout::kV,
+                 sP = s_base + smem_layout::kP;
+  const uint32_t bars = s_base + smem_layout::kBar;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + smem_layout::kBar + N_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + smem_layout::kBar + N_BARS * 8 + 8);
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, hkv = h / (P.n_heads / P.n_kv_heads);
+  const int64_t i0 = (int64_t)blockIdx.x * kTile;
+  const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < N_BARS; ++i) {
+      uint32_t cnt = (i == S_EMPTY0 || i == S_EMPTY1 || i == P_FULL) ? 128u : 1u;
+      mbar_init(bar(i), cnt);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS0 = tmem, tS1 = tmem + 128, tO = tmem + 256;
+  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
+  constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
+
+  if (warp == 4) {
+    // ======================================================================== TMA producer
+    if (lane == 0) {
+      int it = 0, sidx = 0;
+      bool ok = true;
+      for (int st = 0; st < P.n_stage && ok; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        if (sidx >= 1) ok = wait_or_abort(bar(Q_EMPTY), (sidx - 1) & 1, abort_flag, P.err, 100);
+        if (!ok) break;
+        mbar_expect_tx(bar(Q_FULL), 2 * kSubTileBytes);
+        tma_load_3d(sQ, &P.maps[S.map_q], bar(Q_FULL), 0, S.q_row0 + (int)i0, h);
+        tma_load_3d(sQ + kSubTileBytes, &P.maps[S.map_q], bar(Q_FULL), 64, S.q_row0 + (int)i0, h);
+        ++sidx;
+        int64_t seg_j0 = 0;
+        for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+          const TcSeg& G = P.seg[sg];
+          int tf, tl;
+          if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+            for (int t = tf; t <= tl && ok; ++t, ++it) {
+              const int b = it & 1, tok = G.tok0 + t * kTile;
+              if (it >= 2) ok = wait_or_abort(bar(K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 101);
+              if (!ok) break;
+              const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
+              mbar_expect_tx(bar(K_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_k < 0) {
+                tma_load_3d(dk, &P.maps[G.map_k], bar(K_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dk + kSubTileBytes, &P.maps[G.map_k], bar(K_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dk, &P.maps[G.map_k], bar(K_FULL0 + b), 0, tok, hkv, G.c3_k);
+                tma_load_4d(dk + kSubTileBytes, &P.maps[G.map_k], bar(K_FULL0 + b), 64, tok, hkv, G.c3_k);
+              }
+              if (it >= 2) ok = wait_or_abort(bar(V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 102);
+              if (!ok) break;
+              mbar_expect_tx(bar(V_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_v < 0) {
+                tma_load_3d(dv, &P.maps[G.map_v], bar(V_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dv + kSubTileBytes, &P.maps[G.map_v], bar(V_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dv, &P.maps[G.map_v], bar(V_FULL0 + b), 0, tok, hkv, G.c3_v);
+                tma_load_4d(dv + kSubTileBytes, &P.maps[G.map_v], bar(V_FULL0 + b), 64, tok, hkv, G.c3_v);
+              }
+            }
+          }
+          seg_j0 += G.len;
+        }
+      }
+      if (!ok) {
+        // give loads that are still in flight a bounded chance to land before the CTA's memory goes away
+        for (int b = 0; b < 2; ++b) {
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(K_FULL0 + b), 0) && !mbar_try_wait(bar(K_FULL0 + b), 1); ++i) __nanosleep(64);
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(V_FULL0 + b), 0) && !mbar_try_wait(bar(V_FULL0 + b), 1); ++i) __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ========================================================================== MMA issuer
+    if (lane == 0) {
+      int it = 0, sidx = 0;
+      bool ok = true;
+      auto issue_pv = [&](int j) -> bool {
+        const int b = j & 1;
+        if (!wait_or_abort(bar(P_FULL), j & 1, abort_flag, P.err, 200)) return false;
+        if (!wait_or_abort(bar(V_FULL0 + b), (j >> 1) & 1, abort_flag, P.err, 201)) return false;
+        tc_fence_after();
+        const uint32_t vt = sV + b * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A = P [128 queries x 16 keys], K-major; B = V [16 keys x 128 d], d contiguous (MN-major)
+          uint64_t ad = make_sdesc(sP + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          uint64_t bd = make_sdesc(vt + ks * 2048, kSubTileBytes, 1024);
+          mma_ss(tO, ad, bd, idesc_pv, (j > 0) || (ks > 0));
+        }
+        tc_commit(bar(V_EMPTY0 + b));
+        tc_commit(bar(P_EMPTY));
+        return true;
+      };
+      for (int st = 0; st < P.n_stage && ok; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        ok = wait_or_abort(bar(Q_FULL), sidx & 1, abort_flag, P.err, 202);
+        ++sidx;
+        // total tiles of this stage, to know the last QK that reads the stage's Q tile
+        int n_tiles = 0;
+        {
+          int64_t j0s = 0;
+          for (int sg = S.seg_begin; sg < S.seg_end; ++sg) {
+            int tf, tl;
+            if (seg_tiles(vis_lo, vis_hi, j0s, P.seg[sg].len, &tf, &tl)) n_tiles += tl - tf + 1;
+            j0s += P.seg[sg].len;
+          }
+        }
+        for (int t = 0; t < n_tiles && ok; ++t, ++it) {
+          const int b = it & 1;
+          ok = wait_or_abort(bar(K_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 203);
+          if (ok && it >= 2) ok = wait_or_abort(bar(S_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 204);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t kt = sK + b * 2 * kSubTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            uint64_t ad = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            uint64_t bd = make_sdesc(kt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            mma_ss(b ? tS1 : tS0, ad, bd, idesc_qk, ks > 0);
+          }
+          tc_commit(bar(S_FULL0 + b));
+          tc_commit(bar(K_EMPTY0 + b));
+          if (t == n_tiles - 1) tc_commit(bar(Q_EMPTY));
+          if (it >= 1) ok = issue_pv(it - 1);
+        }
+      }
+      if (ok && it >= 1) ok = issue_pv(it - 1);
+      if (ok) tc_commit(bar(O_FULL));
+    }
+  } else {
+    // ===================================================================== softmax / epilogue
+    const int row = warp * 32 + lane;
+    const int64_t qi = i0 + row;
+    const bool row_valid = qi < P.lq;
+    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    int it = 0;
+    bool ok = true;
+    for (int st = 0; st < P.n_stage && ok; ++st) {
+      const TcStage& S = P.stage[st];
+      int64_t vis_lo, vis_hi;
+      visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+      if (vis_lo > vis_hi) continue;
+      // keys [jlo, jhi] of this stage are visible to this thread's query row
+      int64_t jlo = 0, jhi = S.lk - 1;
+      if (S.mask_mode == INFLLM_MASK_WINDOW) {
+        jlo = qi + S.mask_offset - S.mask_size + 1;
+        jhi = qi + S.mask_offset;
+      } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
+        jhi = qi + S.mask_offset - S.mask_size;
+      }
+      if (!row_valid) jhi = -1, jlo = 0;
+      int64_t seg_j0 = 0;
+      for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+        const TcSeg& G = P.seg[sg];
+        int tf, tl;
+        if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+          for (int t = tf; t <= tl && ok; ++t, ++it) {
+            const int b = it & 1;
+            ok = __all_sync(0xffffffffu, wait_or_abort(bar(S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 300));
+            if (!ok) break;
+            tc_fence_after();
+            float s[kTile];
+            const uint32_t ts = (b ? tS1 : tS0) + lane_base;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(S_EMPTY0 + b));
+            // visible columns of this tile for this row: [c_lo, c_hi]
+            const int64_t jt = seg_j0 + (int64_t)t * kTile;
+            int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
+            int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
+            int c_lo = (int)(a - jt), c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt));
+            float mx = -INFINITY;
+            if (c_lo == 0 && c_hi == kTile - 1) {
+#pragma unroll
+              for (int c = 0; c < kTile; ++c) {
+                s[c] *= P.scale_log2;
+                mx = fmaxf(mx, s[c]);
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < kTile; ++c) {
+                s[c] = (c >= c_lo && c <= c_hi) ? s[c] * P.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[c]);
+              }
+            }
+            // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
+            float alpha = 1.f;
+            bool resc = false;
+            if (mx > m_ref) {
+              if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated for this row yet
+              } else if (mx - m_ref > 8.f) {
+                alpha = exp2f(m_ref - mx);
+                l_sum *= alpha;
+                m_ref = mx;
+                resc = true;
+              }
+            }
+            const float ms = m_ref == -INFINITY ? 0.f : m_ref;
+            uint32_t pk[kTile / 2];
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < kTile; c += 2) {
+              float p0 = exp2f(s[c] - ms), p1 = exp2f(s[c + 1] - ms);
+              rs += p0 + p1;
+              typename Act<T>::T2 v2 = Act<T>::from_f2(p0, p1);
+              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            l_sum += rs;
+            // P buffer and O are free once PV of the previous tile has completed
+            if (it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(P_EMPTY), (it - 1) & 1, abort_flag, P.err, 301));
+            if (!ok) break;
+            if (__any_sync(0xffffffffu, resc) && it >= 1) {
+              tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tO + lane_base + c * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+                tmem_st32(tO + lane_base + c * 32, o);
+              }
+              tmem_wait_st();
+              tc_fence_before();
+            }
+            // P row -> shared memory, K-major with the 128-byte swizzle (two 64-key halves)
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              uint4 v = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+              *reinterpret_cast<uint4*>(smem + smem_layout::kP + (c >> 3) * kSubTileBytes + swz_off(row, c & 7)) = v;
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(bar(P_FULL));
+          }
+        }
+        seg_j0 += G.len;
+      }
+    }
+    // ---- epilogue: O / l -> out, log-sum-exp
+    if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(O_FULL), 0, abort_flag, P.err, 302));
+    if (ok) {
+      tc_fence_after();
+      const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
+      T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (it >= 1) {
+          tmem_ld32(tO + lane_base + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] = 0;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int k = 0; k < 32; k += 8) {
+            uint4 v;
+            uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              typename Act<T>::T2 v2 = Act<T>::from_f2(__uint_as_float(o[k + 2 * e]) * inv,
+                                                       __uint_as_float(o[k + 2 * e + 1]) * inv);
+              pv[e] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
+          }
+        }
+      }
+      if (row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
+    }
+  }
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------------------------ column sums
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_tc_kernel(const __grid_constant__ ColsumTcParams P) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sK = smem_u32(smem), sQ = sK + 2 * kSubTileBytes;
+  unsigned char* tail = smem + 4 * kSubTileBytes;
+  const uint32_t bar_k = smem_u32(tail), bar_q = bar_k + 8, bar_mma = bar_k + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 24);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 32);
+  float* s_lse = reinterpret_cast<float*>(tail + 64);  // 128 floats
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, hkv = h / P.group;
+  const int64_t j0 = (int64_t)blockIdx.x * kTile;
+  const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+  if (threadIdx.x == 0) {
+    mbar_init(bar_k, 1);
+    mbar_init(bar_q, 1);
+    mbar_init(bar_mma, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  constexpr uint32_t idesc = make_idesc(kBf16, 128, 128, false);
+
+  // query rows that can see a key of this tile
+  int64_t qi_lo = 0, qi_hi = P.lq - 1;
+  if (P.mask_mode == INFLLM_MASK_WINDOW) {
+    qi_lo = j0 - P.mask_offset;
+    qi_hi = j0 + keys - 1 - P.mask_offset + P.mask_size - 1;
+  } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
+    qi_lo = j0 - P.mask_offset + P.mask_size;
+  }
+  if (qi_lo < 0) qi_lo = 0;
+  if (qi_hi > P.lq - 1) qi_hi = P.lq - 1;
+  // this thread's key and the queries that see it
+  const int krow = warp * 32 + lane;
+  const int64_t kj = j0 + krow;
+  int64_t vi_lo = 0, vi_hi = P.lq - 1;
+  if (P.mask_mode == INFLLM_MASK_WINDOW) {
+    vi_lo = kj - P.mask_offset;
+    vi_hi = kj - P.mask_offset + P.mask_size - 1;
+  } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
+    vi_lo = kj - P.mask_offset + P.mask_size;
+  }
+  if (vi_lo < 0) vi_lo = 0;
+  if (vi_hi > P.lq - 1) vi_hi = P.lq - 1;
+  if (kj >= P.lk) vi_hi = -1;
+
+  float total = 0.f;
+  bool ok = true;
+  if (qi_lo <= qi_hi) {
+    const int t_first = (int)(qi_lo / kTile), t_last = (int)(qi_hi / kTile);
+    if (threadIdx.x == 0) {
+      mbar_expect_tx(bar_k, 2 * kSubTileBytes);
+      tma_load_3d(sK, &P.map_k, bar_k, 0, P.k_tok0 + (int)j0, hkv);
+      tma_load_3d(sK + kSubTileBytes, &P.map_k, bar_k, 64, P.k_tok0 + (int)j0, hkv);
+    }
+    for (int t = t_first; t <= t_last && ok; ++t) {
+      const int n = t - t_first;
+      const int64_t q0 = (int64_t)t * kTile;
+      if (threadIdx.x == 0) {
+        mbar_expect_tx(bar_q, 2 * kSubTileBytes);
+        tma_load_3d(sQ, &P.map_q, bar_q, 0, P.q_row0 + (int)q0, h);
+        tma_load_3d(sQ + kSubTileBytes, &P.map_q, bar_q, 64, P.q_row0 + (int)q0, h);
+      }
+      s_lse[threadIdx.x] = (q0 + threadIdx.x < P.lq) ? P.lse[(int64_t)h * P.lq + q0 + threadIdx.x] : INFINITY;
+      if (threadIdx.x == 0) {
+        if (n == 0) ok = wait_or_abort(bar_k, 0, abort_flag, P.err, 400);
+        if (ok) ok = wait_or_abort(bar_q, n & 1, abort_flag, P.err, 401);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            // S^T = K Q^T: keys are the M rows (TMEM lanes), queries the N columns
+            uint64_t ad = make_sdesc(sK + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            uint64_t bd = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            mma_ss(tmem, ad, bd, idesc, ks > 0);
+          }
+          tc_commit(bar_mma);
+        }
+      }
+      __syncthreads();  // s_lse visible; thread 0 has issued (or given up)
+      ok = __all_sync(0xffffffffu, wait_or_abort(bar_mma, n & 1, abort_flag, P.err, 402));
+      if (ok) {
+        tc_fence_after();
+        const uint32_t ta = tmem + (((uint32_t)(warp * 32)) << 16);
+        int64_t a = vi_lo > q0 ? vi_lo : q0, e = vi_hi < q0 + kTile - 1 ? vi_hi : q0 + kTile - 1;
+        const int c_lo = (int)(a - q0), c_hi = (int)(e - q0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(ta + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            int col = c * 32 + k;
+            float ls = s_lse[col];
+            float pv = exp2f(__uint_as_float(r[k]) * P.scale_log2 - ls);
+            total += (col >= c_lo && col <= c_hi && ls != -INFINITY) ? pv : 0.f;
+          }
+        }
+        tc_fence_before();
+      }
+      __syncthreads();  // TMEM tile and the Q buffer may be overwritten by the next iteration
+      ok = !(*abort_flag);
+    }
+  }
+  if (ok && kj < P.lk) {
+    float* dst = P.score + (int64_t)h * P.score_hs + kj;
+    *dst = P.accumulate ? *dst + total : total;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+// ---------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int encode_tensor_map(CUtensorMap* map, int dtype, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn enc = get_encoder();
+  if (!enc) return fail(INFLLM_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+  }
+  for (int i = 0; i < rank - 1; ++i) gs[i] = strides_bytes[i];
+  CUresult r = enc(map, dtype == INFLLM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(INFLLM_E_BADARG, "cuTensorMapEncodeTiled failed with code %d (rank %d, inner dim %llu)", (int)r, rank,
+                (unsigned long long)dims[0]);
+  return INFLLM_OK;
+}
+
+// rows of `D`=128 elements: (D, rows, heads) view of a (heads, rows, D) tensor with element strides hs / ts
+int encode_rows_map(CUtensorMap* map, int dtype, const void* base, int64_t rows, int64_t heads, int64_t hs, int64_t ts) {
+  uint64_t dims[3] = {128, (uint64_t)rows, (uint64_t)heads};
+  uint64_t strides[2] = {(uint64_t)ts * 2, (uint64_t)hs * 2};
+  uint32_t box[3] = {64, 128, 1};
+  return encode_tensor_map(map, dtype, base, 3, dims, strides, box);
+}
+
+bool tc_rows_ok(const void* base, int64_t hs, int64_t ts) {
+  return ((uintptr_t)base % 16) == 0 && (hs * 2) % 16 == 0 && (ts * 2) % 16 == 0 && hs > 0 && ts > 0;
+}
+
+int tc_get_error_ptr(int** p) {
+  void* d = nullptr;
+  INFLLM_CUDA_OK(cudaGetSymbolAddress(&d, g_tc_error));
+  *p = (int*)d;
+  return INFLLM_OK;
+}
+
+int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
+  if (P.lq <= 0) return INFLLM_OK;
+  dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads);
+  const size_t smem = smem_layout::kTotal + 1024;
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    auto kern = attn_tc_kernel<T>;
+    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, 192, smem, s>>>(P);
+  });
+  INFLLM_LAUNCH_OK("attn_tc_kernel");
+  return INFLLM_OK;
+}
+
+int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, int q_row0, int k_tok0, int n_heads,
+                          int n_kv_heads, int64_t lq, int64_t lk, int mask_mode, int64_t mask_offset,
+                          int64_t mask_size, const float* lse, float* score, int64_t score_hs, int accumulate,
+                          int dtype, cudaStream_t s) {
+  ColsumTcParams P{};
+  P.map_q = map_q; P.map_k = map_k;
+  P.q_row0 = q_row0; P.k_tok0 = k_tok0; P.n_heads = n_heads; P.group = n_heads / n_kv_heads;
+  P.lq = lq; P.lk = lk; P.mask_mode = mask_mode; P.accumulate = accumulate;
+  P.mask_offset = mask_offset; P.mask_size = mask_size; P.lse = lse; P.score = score; P.score_hs = score_hs;
+  P.scale_log2 = kLog2e / sqrtf(128.f);
+  INFLLM_TRY(tc_get_error_ptr(&P.err));
+  dim3 grid((unsigned)ceil_div(lk, kTile), n_heads);
+  const size_t smem = 4 * kSubTileBytes + 64 + 128 * sizeof(float) + 1024;
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    auto kern = colsum_tc_kernel<T>;
+    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, 128, smem, s>>>(P);
+  });
+  INFLLM_LAUNCH_OK("colsum_tc_kernel");
+  return INFLLM_OK;
+}
+
+int colsum_tc_launch(const void* q, int64_t q_hs, int64_t q_ts, const void* k, int64_t k_hs, int64_t k_ts, int n_heads,
+                     int n_kv_heads, int64_t lq, int64_t lk, int mask_mode, int64_t mask_offset, int64_t mask_size,
+                     const float* lse, float* score, int64_t score_hs, int accumulate, int dtype, cudaStream_t s) {
+  CUtensorMap mq, mk;
+  INFLLM_TRY(encode_rows_map(&mq, dtype, q, lq, n_heads, q_hs, q_ts));
+  INFLLM_TRY(encode_rows_map(&mk, dtype, k, lk, n_kv_heads, k_hs, k_ts));
+  return colsum_tc_launch_maps(mq, mk, 0, 0, n_heads, n_kv_heads, lq, lk, mask_mode, mask_offset, mask_size, lse, score,
+                               score_hs, accumulate, dtype, s);
+}
+
+}  // namespace infllm
+
+// Reads and clears the error record of the tensor-core kernels: code 0 = none, 1 = a bounded wait ran out.
+// Synchronises the device.
+extern "C" int infllm_device_error(int* code, int* where) {
+  using namespace infllm;
+  int h[4] = {0, 0, 0, 0};
+  INFLLM_CUDA_OK(cudaDeviceSynchronize());
+  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h, g_tc_error, sizeof(h)));
+  if (h[0] != 0) {
+    int z[4] = {0, 0, 0, 0};
+    INFLLM_CUDA_OK(cudaMemcpyToSymbol(g_tc_error, z, sizeof(z)));
+  }
+  if (code) *code = h[0];
+  if (where) *where = h[1];
+  return INFLLM_OK;
+}

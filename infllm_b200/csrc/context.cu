@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "attn_common.cuh"
+#include "attn_tc.cuh"
 
 namespace infllm {
 
@@ -163,6 +164,12 @@ struct infllm_ctx {
   int64_t slab_units = 0;
   LruTable lru{0};
 
+  // tensor-core path: tensor maps of the buffers the kernels read through TMA
+  bool use_tc = false;
+  int64_t init_cap = 0;  // rows allocated for the sink buffers (at least one 128-row tile)
+  CUtensorMap m_qloc, m_qglb, m_krot, m_kraw, m_v, m_cache, m_initk, m_initv;
+  int* tc_err = nullptr;
+
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr;
   bool attn_recorded = false;
@@ -249,12 +256,17 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
     for (int i = 0; i < D / 2; ++i) inv[i] = 1.0f / powf(g.rope_base, (float)(2 * i) / (float)D);
     INFLLM_TRY(infllm_rope_table(inv.data(), g.rope_scale, (int)D, c->tab_len, c->cos_t, c->sin_t, s));
   }
-  if (g.n_init > 0) {
-    INFLLM_CUDA_OK(cudaMalloc(&c->init_k, HKV * g.n_init * D * c->esz));
-    INFLLM_CUDA_OK(cudaMalloc(&c->init_v, HKV * g.n_init * D * c->esz));
-  }
+  // buffers that TMA tiles may over-read are zero-filled once: a tile row past the valid data must not
+  // hold NaN bit patterns (0 * NaN would poison P V)
+  c->init_cap = std::max<int64_t>(g.n_init, 128);
+  INFLLM_CUDA_OK(cudaMalloc(&c->init_k, HKV * c->init_cap * D * c->esz));
+  INFLLM_CUDA_OK(cudaMalloc(&c->init_v, HKV * c->init_cap * D * c->esz));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->init_k, 0, HKV * c->init_cap * D * c->esz, s));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->init_v, 0, HKV * c->init_cap * D * c->esz, s));
   INFLLM_CUDA_OK(cudaMalloc(&c->q_loc, H * c->sub_max * D * c->esz));
   INFLLM_CUDA_OK(cudaMalloc(&c->q_glb, H * c->sub_max * D * c->esz));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->q_loc, 0, H * c->sub_max * D * c->esz, s));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->q_glb, 0, H * c->sub_max * D * c->esz, s));
   INFLLM_CUDA_OK(cudaMalloc(&c->qbar, (c->sub_max / g.exc_block_size + 1) * c->width * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->lse, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_acc, H * g.exc_block_size * D * sizeof(float)));
@@ -269,6 +281,21 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->cache, (int64_t)g.max_cached_block * c->unit_bytes));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, (int64_t)g.max_cached_block * c->unit_bytes, s));
+  c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.reserved[0] & 1);
+  if (c->use_tc) {
+    INFLLM_TRY(encode_rows_map(&c->m_qloc, g.dtype, c->q_loc, c->sub_max, H, c->sub_max * D, D));
+    INFLLM_TRY(encode_rows_map(&c->m_qglb, g.dtype, c->q_glb, c->sub_max, H, c->sub_max * D, D));
+    INFLLM_TRY(encode_rows_map(&c->m_initk, g.dtype, c->init_k, c->init_cap, HKV, c->init_cap * D, D));
+    INFLLM_TRY(encode_rows_map(&c->m_initv, g.dtype, c->init_v, c->init_cap, HKV, c->init_cap * D, D));
+    // cache slots as (D, block_size, H_kv, 2 * slots): the last index is slot * 2 + (0 keys | 1 values)
+    uint64_t dims[4] = {128, (uint64_t)g.block_size, (uint64_t)HKV, 2ull * g.max_cached_block};
+    uint64_t strides[3] = {(uint64_t)(D * c->esz), (uint64_t)(g.block_size * D * c->esz),
+                           (uint64_t)(c->unit_bytes / 2)};
+    uint32_t box[4] = {64, 128, 1, 1};
+    INFLLM_TRY(encode_tensor_map(&c->m_cache, g.dtype, c->cache, 4, dims, strides, box));
+    INFLLM_TRY(tc_get_error_ptr(&c->tc_err));
+  }
   c->free_slots.clear();
   for (int i = g.max_cached_block - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
@@ -310,6 +337,11 @@ int ensure_tokens(infllm_ctx* c, int64_t add, cudaStream_t s) {
     INFLLM_TRY(free_buffers(tb, s));
   }
   c->tb = nb;
+  if (c->use_tc) {
+    INFLLM_TRY(encode_rows_map(&c->m_krot, g.dtype, nb.k_rot, nb.cap, HKV, nb.cap * D, D));
+    INFLLM_TRY(encode_rows_map(&c->m_kraw, g.dtype, nb.k_raw, nb.cap, HKV, nb.cap * D, D));
+    INFLLM_TRY(encode_rows_map(&c->m_v, g.dtype, nb.v, nb.cap, HKV, nb.cap * D, D));
+  }
   return INFLLM_OK;
 }
 
@@ -422,9 +454,9 @@ int seal_after(infllm_ctx* c, int64_t end, cudaStream_t s) {
     if (take > 0) {
       const size_t w = take * D * c->esz;
       const int64_t src = (c->frontier - tb.t0) * D * c->esz, dst = c->init_len * D * c->esz;
-      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_k + dst, g.n_init * D * c->esz, (char*)tb.k_raw + src,
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_k + dst, c->init_cap * D * c->esz, (char*)tb.k_raw + src,
                                        tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
-      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_v + dst, g.n_init * D * c->esz, (char*)tb.v + src,
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_v + dst, c->init_cap * D * c->esz, (char*)tb.v + src,
                                        tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
     }
     c->init_len += take;
@@ -477,6 +509,15 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
   INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
   INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
   INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
+  if (c->use_tc) {
+    // a 128-row tile that ends the window may reach past the last ingested token: keep those rows finite
+    const int64_t pad = std::min<int64_t>(128, tb.cap - (at + L));
+    if (pad > 0) {
+      INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.v + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
+      INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.k_rot + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
+      INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.k_raw + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
+    }
+  }
   // ---- RoPE: keys keep the position (token - rope_origin) until the table would run out
   const int64_t win0 = std::max<int64_t>(T - g.n_local, 0);  // oldest key any query of this call can see locally
   if (c->rope_origin < 0 || T + L - c->rope_origin > c->tab_len || win0 < c->rope_origin) {
@@ -514,7 +555,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       const char* base = (const char*)c->cache + (int64_t)c->slot_of[b] * c->unit_bytes;
       gsegs.push_back({base, base + c->unit_bytes / 2, bs * D, (int32_t)D, (int32_t)bs});
     }
-    if (c->init_len > 0) gsegs.push_back({c->init_k, c->init_v, g.n_init * D, (int32_t)D, (int32_t)c->init_len});
+    if (c->init_len > 0) gsegs.push_back({c->init_k, c->init_v, c->init_cap * D, (int32_t)D, (int32_t)c->init_len});
     if (ovf > 0)
       gsegs.push_back({(char*)tb.k_raw + (c->frontier - tb.t0) * D * esz, (char*)tb.v + (c->frontier - tb.t0) * D * esz,
                        kv_hs, (int32_t)D, (int32_t)ovf});
@@ -550,6 +591,35 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       INFLLM_TRY(decode_score_launch(c->dec_logits, E - wlo, c->lse, tb.score + (wlo - tb.t0), tb.cap, (int)H, s));
     } else {
       // ---- local stage + global stage, jointly normalised (context_manager.py:486-489, 526-533)
+      double local_pairs = 0, all_glk = 0;
+      for (int64_t i = 0; i < lq; ++i) local_pairs += (double)std::min<int64_t>(S + i + 1, g.n_local);
+      for (auto& sgm : gsegs) all_glk += sgm.len;
+      const bool tc_now = c->use_tc && lq > 64 && gsegs.size() + 1 <= (size_t)kMaxSeg;
+      if (tc_now) {
+        AttnTcParams TP{};
+        TP.maps[0] = c->m_qloc; TP.maps[1] = c->m_qglb; TP.maps[2] = c->m_krot; TP.maps[3] = c->m_kraw;
+        TP.maps[4] = c->m_v; TP.maps[5] = c->m_cache; TP.maps[6] = c->m_initk; TP.maps[7] = c->m_initv;
+        TP.n_stage = 2; TP.n_heads = (int)H; TP.n_kv_heads = (int)HKV; TP.lq = lq;
+        TP.out = out_eb; TP.o_hs = o_hs; TP.o_ts = o_ts; TP.lse = c->lse;
+        TP.scale_log2 = kLog2e / sqrtf((float)D); TP.err = c->tc_err;
+        TP.stage[0].map_q = 0; TP.stage[0].q_row0 = (int)st; TP.stage[0].mask_mode = INFLLM_MASK_WINDOW;
+        TP.stage[0].mask_offset = lk - lq; TP.stage[0].mask_size = g.n_local; TP.stage[0].lk = lk;
+        TP.stage[0].seg_begin = 0; TP.stage[0].seg_end = 1;
+        TP.seg[0] = {2, 4, (int32_t)(ks - tb.t0), -1, -1, (int32_t)lk};
+        int ns = 1;
+        // The reference passes a complement window for the global stage whose offset makes every
+        // (query, key) pair visible (context_manager.py:437); the stage is therefore unmasked.
+        for (int32_t b : ids) {
+          const int slot = c->slot_of[b];
+          TP.seg[ns++] = {5, 5, 0, slot * 2, slot * 2 + 1, (int32_t)bs};
+        }
+        if (c->init_len > 0) TP.seg[ns++] = {6, 7, 0, -1, -1, (int32_t)c->init_len};
+        if (ovf > 0) TP.seg[ns++] = {3, 4, (int32_t)(c->frontier - tb.t0), -1, -1, (int32_t)ovf};
+        TP.stage[1].map_q = 1; TP.stage[1].q_row0 = (int)st; TP.stage[1].mask_mode = INFLLM_MASK_NONE;
+        TP.stage[1].lk = (int64_t)all_glk; TP.stage[1].seg_begin = 1; TP.stage[1].seg_end = ns;
+        ProfScope ps(c, s, INFLLM_PROF_ATTN, 4.0 * D * H * (local_pairs + (double)lq * all_glk));
+        INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
+      } else {
       AttnParams P{};
       P.n_heads = (int)H; P.n_kv_heads = (int)HKV; P.lq = lq; P.first = 1;
       P.acc = c->st_acc; P.m = c->st_m; P.l = c->st_l;
@@ -560,8 +630,6 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       P.stage[0].lk = lk; P.stage[0].seg_begin = 0; P.stage[0].seg_end = 1;
       P.seg[0] = {(char*)tb.k_rot + (ks - tb.t0) * D * esz, (char*)tb.v + (ks - tb.t0) * D * esz, kv_hs, (int32_t)D,
                   (int32_t)lk};
-      // The reference passes a complement window for the global stage whose offset makes every
-      // (query, key) pair visible (context_manager.py:437); the stage is therefore unmasked.
       size_t done = 0;
       int nseg = 1;
       int64_t glk = 0;
@@ -574,9 +642,6 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       P.stage[1].q = qglb_eb; P.stage[1].q_hs = q_hs_s; P.stage[1].q_ts = D;
       P.stage[1].mask_mode = INFLLM_MASK_NONE; P.stage[1].lk = glk; P.stage[1].seg_begin = 1; P.stage[1].seg_end = nseg;
       P.last = done == gsegs.size();
-      double local_pairs = 0, all_glk = 0;
-      for (int64_t i = 0; i < lq; ++i) local_pairs += (double)std::min<int64_t>(S + i + 1, g.n_local);
-      for (auto& sgm : gsegs) all_glk += sgm.len;
       {
         ProfScope ps(c, s, INFLLM_PROF_ATTN, 4.0 * D * H * (local_pairs + (double)lq * all_glk));
         INFLLM_TRY(attn_general_launch(P, (int)D, g.dtype, s));
@@ -600,11 +665,18 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         ProfScope ps(c, s, INFLLM_PROF_ATTN, 0.0);
         INFLLM_TRY(attn_general_launch(R, (int)D, g.dtype, s));
       }
+      }
       // accumulated local score of every window key (context_manager.py:488, 623-625)
       ProfScope ps(c, s, INFLLM_PROF_COLSUM, 2.0 * D * H * local_pairs);
-      INFLLM_TRY(attn_colsum_launch(qloc_eb, q_hs_s, D, (char*)tb.k_rot + (ks - tb.t0) * D * esz, kv_hs, D, (int)H,
-                                    (int)HKV, lq, lk, (int)D, INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse,
-                                    tb.score + (ks - tb.t0), tb.cap, 1, g.dtype, s));
+      if (c->use_tc && lq >= 128 && lk >= 128) {
+        INFLLM_TRY(colsum_tc_launch_maps(c->m_qloc, c->m_krot, (int)st, (int)(ks - tb.t0), (int)H, (int)HKV, lq, lk,
+                                         INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse, tb.score + (ks - tb.t0),
+                                         tb.cap, 1, g.dtype, s));
+      } else {
+        INFLLM_TRY(attn_colsum_launch(qloc_eb, q_hs_s, D, (char*)tb.k_rot + (ks - tb.t0) * D * esz, kv_hs, D, (int)H,
+                                      (int)HKV, lq, lk, (int)D, INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse,
+                                      tb.score + (ks - tb.t0), tb.cap, 1, g.dtype, s));
+      }
     }
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
     c->attn_recorded = true;
@@ -809,8 +881,10 @@ extern "C" int infllm_ctx_load_synthetic(infllm_ctx* c, int64_t n_units, const v
   INFLLM_TRY(ensure_block_k(c, n_units, s));
   INFLLM_CUDA_OK(cudaMemcpyAsync(c->block_k, h_block_k, n_units * c->width * c->esz, cudaMemcpyHostToDevice, s));
   if (g.n_init > 0) {
-    INFLLM_CUDA_OK(cudaMemcpyAsync(c->init_k, h_init_k, HKV * g.n_init * D * c->esz, cudaMemcpyHostToDevice, s));
-    INFLLM_CUDA_OK(cudaMemcpyAsync(c->init_v, h_init_v, HKV * g.n_init * D * c->esz, cudaMemcpyHostToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(c->init_k, c->init_cap * D * c->esz, h_init_k, g.n_init * D * c->esz,
+                                     g.n_init * D * c->esz, HKV, cudaMemcpyHostToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync(c->init_v, c->init_cap * D * c->esz, h_init_v, g.n_init * D * c->esz,
+                                     g.n_init * D * c->esz, HKV, cudaMemcpyHostToDevice, s));
   }
   c->init_len = g.n_init;
   c->init_full = true;

@@ -66,10 +66,17 @@ def _run(case, dtype=torch.bfloat16):
     return cm, ora, stats
 
 
+@pytest.mark.parametrize("kernels", ["tcgen05", "generic"])
 @pytest.mark.parametrize("name", D128)
-def test_context_memory_matches_oracle(name):
+def test_context_memory_matches_oracle(name, kernels, monkeypatch):
+    """Both kernel families behind the exec-block loop: the tcgen05 kernels (default for blocks of more than
+    64 queries) and the shape-generic mma.sync kernels."""
+    monkeypatch.setenv("INFLLM_B200_NO_TC", "1" if kernels == "generic" else "0")
     case = C.CASES[name]
     cm, ora, stats = _run(case)
+    from infllm_b200 import _lib
+
+    assert _lib.device_error() == (0, 0), "a bounded wait of a tensor-core kernel ran out"
     assert cm.size() == sum(case["lens"])
     # retrieval: identical to the reference recording wherever no near-tie intervened
     meta, z = load_golden(name)

@@ -233,3 +233,8 @@ def test_decode_split_k_and_merge_match_oracle(H, HKV, seg_lens):
         L.check(L.lib.infllm_lse_merge(po.data_ptr(), pl.data_ptr(), 2, H, D, out2.data_ptr(), D, None, L.BF16,
                                        L.stream_ptr()))
         _check_out(out2, want[:, 0])
+
+
+def test_tensor_core_kernels_reported_no_timeout():
+    """Collected after the kernel tests of this file: no bounded wait may have run out."""
+    assert _L().device_error() == (0, 0)
