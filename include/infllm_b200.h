@@ -143,6 +143,27 @@ int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_heads, int n_kv
 int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads, int head_dim,
                      void* d_out, int64_t o_hs, float* d_lse, int dtype, void* stream);
 
+/* infllm_attn_decode_noalloc has no counterpart in the reference.  It is infllm_attn_decode followed by
+ * infllm_lse_merge in one call that allocates nothing: the split-K partials go to a scratch array that is
+ * part of the library image (about 5.3 MB of every GPU that loads the library, until the process exits)
+ * instead of a buffer from the caller.  It is meant for callers that hold raw device pointers but cannot
+ * obtain device memory themselves at the point of the call: a serving engine whose own pool has already
+ * claimed the whole GPU, so that cudaMalloc fails or stalls every stream; a plugin running inside such
+ * an engine's step function, where allocation is forbidden by contract; a latency-critical decode loop
+ * that must not touch an allocator at all.  The caller still passes the queries, the key/value segments
+ * and the output: d_out (n_heads, head_dim) in `dtype` with head stride o_hs, d_lse (n_heads) or NULL.
+ * Limits: head_dim 128, n_heads <= 64, and at most 160 chunks of 128 keys summed over the segments (a
+ * segment of L keys takes ceil(L/128) chunks); beyond that the call returns INFLLM_E_CAPACITY and
+ * nothing is launched.  The first call made on a device looks up the scratch address for that device
+ * (a cudaGetSymbolAddress call with that device current); make that first call before any stream
+ * capture begins.  All calls on a device share the one scratch array, which keeps what the last call
+ * wrote: two calls that may overlap on the GPU (different streams, or concurrent host threads) race
+ * and must be serialised by the caller.  Nothing in the array needs clearing between calls. */
+int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim,
+                               int n_seg, const void* const* h_seg_k, const void* const* h_seg_v,
+                               const int64_t* h_seg_hs, const int32_t* h_seg_len, const int32_t* h_seg_q,
+                               void* d_out, int64_t o_hs, float* d_lse, int dtype, void* stream);
+
 /* ------------------------------------------------------------ context memory
  * One infllm_ctx is the native state of one batch element ("unit") of the reference's
  * ContextManager (context_manager.py:196-816): token buffers for the local window and the

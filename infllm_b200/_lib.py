@@ -71,6 +71,9 @@ SIGNATURES = {
     "infllm_attn_decode": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p),
                                    POINTER(c_void_p), POINTER(c_int64), POINTER(c_int32), POINTER(c_int32),
                                    c_void_p, c_void_p, c_int, POINTER(c_int), c_int, c_void_p, c_int, c_void_p]),
+    "infllm_attn_decode_noalloc": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p),
+                                           POINTER(c_void_p), POINTER(c_int64), POINTER(c_int32), POINTER(c_int32),
+                                           c_void_p, c_int64, c_void_p, c_int, c_void_p]),
     "infllm_lse_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int,
                                  c_void_p]),
     "infllm_ctx_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),

@@ -280,6 +280,60 @@ extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_head
                             max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream);
 }
 
+// ------------------------------------------------------------------------ allocation-free variant
+// Scratch for infllm_attn_decode_noalloc: the split-K partials live in this file-scope array instead of
+// a caller-provided buffer.  Every GPU that loads the library holds these bytes until the process exits.
+constexpr int kStaticMaxParts = 160;  // 160 chunks of 128 keys
+constexpr int kStaticMaxHeads = 64;
+constexpr size_t kStaticFloats = (size_t)kStaticMaxParts * kStaticMaxHeads * (128 + 1);  // outputs + log-sum-exps
+static __device__ __align__(256) float g_decode_scratch[kStaticFloats];
+// device addresses of the array, one per device ordinal, looked up on the first call made on that device
+static float* g_decode_scratch_ptr[64] = {nullptr};
+
+extern "C" int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads,
+                                          int head_dim, int n_seg, const void* const* h_seg_k,
+                                          const void* const* h_seg_v, const int64_t* h_seg_hs,
+                                          const int32_t* h_seg_len, const int32_t* h_seg_q, void* d_out, int64_t o_hs,
+                                          float* d_lse, int dtype, void* stream) {
+  using namespace infllm;
+  if (!d_q0 || !h_seg_k || !h_seg_v || !h_seg_hs || !h_seg_len || !h_seg_q || !d_out)
+    return fail(INFLLM_E_BADARG, "attn_decode_noalloc: null pointer");
+  if (n_seg <= 0 || n_seg > kMaxSeg)
+    return fail(INFLLM_E_BADARG, "attn_decode_noalloc: %d segments (1..%d)", n_seg, kMaxSeg);
+  if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "attn_decode_noalloc: head_dim %d (128 is built)", head_dim);
+  if (n_heads <= 0 || n_heads > kStaticMaxHeads)
+    return fail(INFLLM_E_CAPACITY, "attn_decode_noalloc: %d heads exceed the built-in scratch for %d", n_heads,
+                kStaticMaxHeads);
+  long parts = 0;
+  for (int i = 0; i < n_seg; ++i)
+    if (h_seg_len[i] > 0) parts += (h_seg_len[i] + kDecodeChunk - 1) / kDecodeChunk;
+  if (parts > kStaticMaxParts)
+    return fail(INFLLM_E_CAPACITY,
+                "attn_decode_noalloc: %ld chunks of %d keys exceed the built-in scratch for %d chunks; use "
+                "infllm_attn_decode with a caller-provided buffer", parts, kDecodeChunk, kStaticMaxParts);
+  if (parts == 0) return fail(INFLLM_E_BADARG, "attn_decode_noalloc: no keys");
+  int dev = 0;
+  INFLLM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(INFLLM_E_UNSUPPORTED, "attn_decode_noalloc: device ordinal %d", dev);
+  if (!g_decode_scratch_ptr[dev]) {
+    // In host code the array's name is only a handle; the kernels need its address on the current device.
+    float* p = nullptr;
+    INFLLM_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_decode_scratch));
+    g_decode_scratch_ptr[dev] = p;
+  }
+  float* part_o = g_decode_scratch_ptr[dev];
+  float* part_lse = part_o + (size_t)kStaticMaxParts * kStaticMaxHeads * 128;
+  KvSeg segs[kMaxSeg];
+  for (int i = 0; i < n_seg; ++i) segs[i] = {h_seg_k[i], h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
+  int n_parts = 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  // Nothing in the scratch has to start at zero: every partial the merge reads is written by the
+  // split-K kernel of this same call, whatever an earlier call left behind.
+  INFLLM_TRY(attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, part_o,
+                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s));
+  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s);
+}
+
 extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads,
                                 int head_dim, void* d_out, int64_t o_hs, float* d_lse, int dtype, void* stream) {
   using namespace infllm;
