@@ -72,7 +72,9 @@ class ContextManager:
             rope_scale=float(pe.distance_scale), device=q.device.index if q.device.index is not None else
             torch.cuda.current_device(), shard_rank=0, shard_world=1)
         if os.environ.get("INFLLM_B200_NO_TC", "0") == "1":
-            cfg.reserved[0] = 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
+            cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
+        if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":
+            cfg.reserved[0] |= 2  # debugging aid: rank every exec block's units on the device, no look-ahead staging
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))

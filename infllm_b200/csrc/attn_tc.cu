@@ -3,8 +3,8 @@
 // attn_tc_kernel    one 128-query tile of one head per CTA, all stages of an exec block fused:
 //                   local window stage (window-relative rotated q/k, causal window mask) and global
 //                   stage (one-angle q; retrieved units in their cache slots, init sink, overflow),
-//                   jointly normalised.  Warp-specialised: 4 softmax warps (one query row per thread,
-//                   row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
+//                   jointly normalised.  Warp-specialised: 8 softmax warps (two threads per query row, each
+//                   owning half of the tile's key columns; row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
 //                   TMEM (two buffers), P goes through shared memory as a K-major operand, O stays in
 //                   TMEM for the whole tile with lazy rescaling; K/V tiles are double buffered.
 // colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes, each thread sums
@@ -43,6 +43,25 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// The two threads that share a query row publish a progress counter in shared memory; bounded like every wait.
+constexpr int kPairDone = 0x40000000;
+__device__ __forceinline__ bool pair_wait(volatile int* flag, int want, volatile int* abort_flag, int* err, int where) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (*flag >= want) return true;
+    if (*abort_flag) return false;
+    if (i > 256) __nanosleep(32);
+  }
+  *abort_flag = 1;
+  record_error(err, kErrWaitTimeout, where);
+  return false;
+}
+
 // tiles [first, last] of a segment that intersect the visible key range [vis_lo, vis_hi] of the stage
 __device__ __forceinline__ bool seg_tiles(int64_t vis_lo, int64_t vis_hi, int64_t seg_j0, int seg_len, int* first,
                                           int* last) {
@@ -62,14 +81,17 @@ constexpr int kK = kQ + 2 * kSubTileBytes;      // two stages
 constexpr int kV = kK + 4 * kSubTileBytes;      // two stages
 constexpr int kP = kV + 4 * kSubTileBytes;
 constexpr int kBar = kP + 2 * kSubTileBytes;    // barriers + tmem slot + abort flag
-constexpr int kTotal = kBar + 256;
+constexpr int kXmax = kBar + 256;                // row maxima: 2 tile parities x 2 halves x 128 rows of fp32
+constexpr int kXsum = kXmax + 2048;              // row sums: 2 halves x 128 rows
+constexpr int kXflag = kXsum + 1024;             // progress counters: 2 halves x 128 rows
+constexpr int kTotal = kXflag + 1024;
 }  // namespace smem_layout
 
 enum Bar { Q_FULL = 0, Q_EMPTY, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_FULL0,
            S_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, P_EMPTY, O_FULL, N_BARS };
 
 template <typename T>
-__global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__ AttnTcParams P) {
+__global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__ AttnTcParams P) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -79,6 +101,9 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
   const uint32_t bars = s_base + smem_layout::kBar;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + smem_layout::kBar + N_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + smem_layout::kBar + N_BARS * 8 + 8);
+  float* xmax = reinterpret_cast<float*>(smem + smem_layout::kXmax);
+  float* xsum = reinterpret_cast<float*>(smem + smem_layout::kXsum);
+  volatile int* xflag = reinterpret_cast<volatile int*>(smem + smem_layout::kXflag);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,13 +113,14 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) {
-      uint32_t cnt = (i == S_EMPTY0 || i == S_EMPTY1 || i == P_FULL) ? 128u : 1u;
+      uint32_t cnt = (i == S_EMPTY0 || i == S_EMPTY1 || i == P_FULL) ? 256u : 1u;
       mbar_init(bar(i), cnt);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (threadIdx.x < 256) xflag[threadIdx.x] = 0;
+  if (warp == 9) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -107,7 +133,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
   constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
   constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ======================================================================== TMA producer
     if (lane == 0) {
       int it = 0, sidx = 0;
@@ -164,7 +190,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ========================================================================== MMA issuer
     if (lane == 0) {
       int it = 0, sidx = 0;
@@ -227,11 +253,15 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
     }
   } else {
     // ===================================================================== softmax / epilogue
-    const int row = warp * 32 + lane;
+    // Eight warps: warp w and warp w+4 own the same 32 query rows (TMEM lanes) and split the tile's
+    // 128 key columns in halves; they exchange their partial row maxima through shared memory.
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;
     const int64_t qi = i0 + row;
     const bool row_valid = qi < P.lq;
-    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
-    float m_ref = -INFINITY, l_sum = 0.f;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    const int col0 = half * 64;
+    float m_ref = -INFINITY, l_part = 0.f;  // m_ref in the scaled log2 domain; l over this thread's columns
     int it = 0;
     bool ok = true;
     for (int st = 0; st < P.n_stage && ok; ++st) {
@@ -258,32 +288,39 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 300));
             if (!ok) break;
             tc_fence_after();
-            float s[kTile];
-            const uint32_t ts = (b ? tS1 : tS0) + lane_base;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, reinterpret_cast<uint32_t*>(s) + c * 32);
+            float s[64];
+            const uint32_t ts = (b ? tS1 : tS0) + lane_base + col0;
+            tmem_ld32(ts, reinterpret_cast<uint32_t*>(s));
+            tmem_ld32(ts + 32, reinterpret_cast<uint32_t*>(s) + 32);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(bar(S_EMPTY0 + b));
-            // visible columns of this tile for this row: [c_lo, c_hi]
+            // visible columns of this tile for this row: [c_lo, c_hi] in tile coordinates
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
-            int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
-            int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
-            int c_lo = (int)(a - jt), c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt));
-            float mx = -INFINITY;
-            if (c_lo == 0 && c_hi == kTile - 1) {
+            const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
+            const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
+            const int c_lo = (int)(a - jt) - col0;
+            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt)) - col0;
+            if (!(c_lo <= 0 && c_hi >= 63)) {
 #pragma unroll
-              for (int c = 0; c < kTile; ++c) {
-                s[c] *= P.scale_log2;
-                mx = fmaxf(mx, s[c]);
-              }
-            } else {
-#pragma unroll
-              for (int c = 0; c < kTile; ++c) {
-                s[c] = (c >= c_lo && c <= c_hi) ? s[c] * P.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[c]);
-              }
+              for (int c = 0; c < 64; ++c) s[c] = (c >= c_lo && c <= c_hi) ? s[c] : -INFINITY;
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+              mx4[0] = fmaxf(mx4[0], s[c]);
+              mx4[1] = fmaxf(mx4[1], s[c + 1]);
+              mx4[2] = fmaxf(mx4[2], s[c + 2]);
+              mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the other half's maximum of the same row
+            xmax[(it & 1) * 256 + half * 128 + row] = mx;
+            __threadfence_block();
+            xflag[half * 128 + row] = it + 1;
+            ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 303));
+            if (!ok) break;
+            mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
             // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
             float alpha = 1.f;
             bool resc = false;
@@ -291,45 +328,49 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
               if (m_ref == -INFINITY) {
                 m_ref = mx;  // nothing accumulated for this row yet
               } else if (mx - m_ref > 8.f) {
-                alpha = exp2f(m_ref - mx);
-                l_sum *= alpha;
+                alpha = ex2_approx(m_ref - mx);
+                l_part *= alpha;
                 m_ref = mx;
                 resc = true;
               }
             }
-            const float ms = m_ref == -INFINITY ? 0.f : m_ref;
-            uint32_t pk[kTile / 2];
-            float rs = 0.f;
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+            uint32_t pk[32];
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < kTile; c += 2) {
-              float p0 = exp2f(s[c] - ms), p1 = exp2f(s[c + 1] - ms);
-              rs += p0 + p1;
-              typename Act<T>::T2 v2 = Act<T>::from_f2(p0, p1);
-              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v2);
+            for (int c = 0; c < 64; c += 4) {
+              float p0 = ex2_approx(fmaf(s[c], P.scale_log2, neg_m));
+              float p1 = ex2_approx(fmaf(s[c + 1], P.scale_log2, neg_m));
+              float p2 = ex2_approx(fmaf(s[c + 2], P.scale_log2, neg_m));
+              float p3 = ex2_approx(fmaf(s[c + 3], P.scale_log2, neg_m));
+              rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
+              typename Act<T>::T2 v01 = Act<T>::from_f2(p0, p1), v23 = Act<T>::from_f2(p2, p3);
+              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
+              pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
             }
-            l_sum += rs;
+            l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             // P buffer and O are free once PV of the previous tile has completed
             if (it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(P_EMPTY), (it - 1) & 1, abort_flag, P.err, 301));
             if (!ok) break;
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
               tc_fence_after();
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
+              for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
-                tmem_ld32(tO + lane_base + c * 32, o);
+                tmem_ld32(tO + lane_base + col0 + c * 32, o);
                 tmem_wait_ld();
 #pragma unroll
                 for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-                tmem_st32(tO + lane_base + c * 32, o);
+                tmem_st32(tO + lane_base + col0 + c * 32, o);
               }
               tmem_wait_st();
               tc_fence_before();
             }
-            // P row -> shared memory, K-major with the 128-byte swizzle (two 64-key halves)
+            // this thread's half row of P -> shared memory, K-major with the 128-byte swizzle
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < 8; ++c) {
               uint4 v = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-              *reinterpret_cast<uint4*>(smem + smem_layout::kP + (c >> 3) * kSubTileBytes + swz_off(row, c & 7)) = v;
+              *reinterpret_cast<uint4*>(smem + smem_layout::kP + half * kSubTileBytes + swz_off(row, c)) = v;
             }
             fence_proxy_async_smem();
             mbar_arrive(bar(P_FULL));
@@ -338,17 +379,22 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
         seg_j0 += G.len;
       }
     }
-    // ---- epilogue: O / l -> out, log-sum-exp
+    // ---- epilogue: O / l -> out, log-sum-exp (each half writes its 64 output columns)
+    xsum[half * 128 + row] = l_part;
+    __threadfence_block();
+    xflag[half * 128 + row] = kPairDone;
+    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 304));
+    const float l_sum = l_part + xsum[(half ^ 1) * 128 + row];
     if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(O_FULL), 0, abort_flag, P.err, 302));
     if (ok) {
       tc_fence_after();
       const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
-      T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts;
+      T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts + col0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
         if (it >= 1) {
-          tmem_ld32(tO + lane_base + c * 32, o);
+          tmem_ld32(tO + lane_base + col0 + c * 32, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -369,13 +415,13 @@ __global__ void __launch_bounds__(192, 1) attn_tc_kernel(const __grid_constant__
           }
         }
       }
-      if (row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
+      if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
     }
   }
   // ---- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------ column sums
@@ -570,7 +616,7 @@ int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = attn_tc_kernel<T>;
     INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 192, smem, s>>>(P);
+    kern<<<grid, 320, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("attn_tc_kernel");
   return INFLLM_OK;

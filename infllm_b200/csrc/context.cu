@@ -31,6 +31,8 @@ int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t 
                 float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s);
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
                       int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s);
+int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
+                            int dtype, cudaStream_t s);
 int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
                        int64_t tok0, int n_new, int block_size, int repr_topk, int n_heads, int n_kv_heads,
                        int head_dim, void* out, int dtype, cudaStream_t s);
@@ -170,9 +172,22 @@ struct infllm_ctx {
   CUtensorMap m_qloc, m_qglb, m_krot, m_kraw, m_v, m_cache, m_initk, m_initv;
   int* tc_err = nullptr;
 
-  cudaStream_t copy_stream = nullptr;
-  cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr;
-  bool attn_recorded = false;
+  // look-ahead retrieval inside one append: while exec block t runs, the top-k of t+1 over the units known
+  // so far is computed on a second stream and its misses are staged into spare slots; after t's sealing
+  // only the candidates (that top-k plus the newly sealed units) are re-scored and ranked on the host
+  float* scores_aux = nullptr;
+  int64_t scores_aux_cap = 0;
+  int32_t* h_spec = nullptr;        // pinned: look-ahead ids
+  int32_t* h_cand_rows = nullptr;   // pinned: candidate unit ids
+  float* h_cand_scores = nullptr;   // pinned: their scores
+  int cand_cap = 0;
+  std::unordered_map<int32_t, int> staged;  // unit -> slot holding a prefetched copy
+  bool staged_pending = false;              // staged copies issued since the last wait on them
+
+  cudaStream_t copy_stream = nullptr, aux_stream = nullptr;
+  cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr, ev_spec = nullptr,
+              ev_cand = nullptr, ev_seal = nullptr, ev_stage = nullptr;
+  bool attn_recorded = false, spec_recorded = false;
 
   // optional per-kernel timing (infllm_ctx_profile): CUDA events around the launches on their stream
   bool prof = false;
@@ -242,6 +257,11 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_copy, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_attn, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_spec, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_cand, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_seal, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_stage, cudaEventDisableTiming));
 
   const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
   c->sub_max = round_up(std::max<int64_t>(16384, 2 * g.exc_block_size), g.exc_block_size);
@@ -274,14 +294,20 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
+  c->cand_cap = g.topk + g.exc_block_size / g.block_size + 4;
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_rows, c->cand_cap * sizeof(int32_t), cudaHostAllocDefault));
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_scores, c->cand_cap * sizeof(float), cudaHostAllocDefault));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
   c->max_parts = (int)(dec_keys / 128 + g.topk + 8);
   INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
-  INFLLM_CUDA_OK(cudaMalloc(&c->cache, (int64_t)g.max_cached_block * c->unit_bytes));
-  INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, (int64_t)g.max_cached_block * c->unit_bytes, s));
+  // max_cached_block slots hold the cache proper; topk more hold the look-ahead copies of the next exec block
+  const int64_t n_slots = (int64_t)g.max_cached_block + g.topk;
+  INFLLM_CUDA_OK(cudaMalloc(&c->cache, n_slots * c->unit_bytes));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, n_slots * c->unit_bytes, s));
   c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.reserved[0] & 1);
   if (c->use_tc) {
     INFLLM_TRY(encode_rows_map(&c->m_qloc, g.dtype, c->q_loc, c->sub_max, H, c->sub_max * D, D));
@@ -289,7 +315,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
     INFLLM_TRY(encode_rows_map(&c->m_initk, g.dtype, c->init_k, c->init_cap, HKV, c->init_cap * D, D));
     INFLLM_TRY(encode_rows_map(&c->m_initv, g.dtype, c->init_v, c->init_cap, HKV, c->init_cap * D, D));
     // cache slots as (D, block_size, H_kv, 2 * slots): the last index is slot * 2 + (0 keys | 1 values)
-    uint64_t dims[4] = {128, (uint64_t)g.block_size, (uint64_t)HKV, 2ull * g.max_cached_block};
+    uint64_t dims[4] = {128, (uint64_t)g.block_size, (uint64_t)HKV, 2ull * (uint64_t)n_slots};
     uint64_t strides[3] = {(uint64_t)(D * c->esz), (uint64_t)(g.block_size * D * c->esz),
                            (uint64_t)(c->unit_bytes / 2)};
     uint32_t box[4] = {64, 128, 1, 1};
@@ -297,7 +323,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
     INFLLM_TRY(tc_get_error_ptr(&c->tc_err));
   }
   c->free_slots.clear();
-  for (int i = g.max_cached_block - 1; i >= 0; --i) c->free_slots.push_back(i);
+  for (int i = (int)n_slots - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
   c->initialized = true;
   return INFLLM_OK;
@@ -353,7 +379,10 @@ int ensure_block_k(infllm_ctx* c, int64_t n, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMallocAsync(&nb, cap * c->width * c->esz, s));
   if (c->num_blocks > 0)
     INFLLM_CUDA_OK(cudaMemcpyAsync(nb, c->block_k, c->num_blocks * c->width * c->esz, cudaMemcpyDeviceToDevice, s));
-  if (c->block_k) INFLLM_CUDA_OK(cudaFreeAsync(c->block_k, s));
+  if (c->block_k) {
+    if (c->spec_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_spec, 0));  // look-ahead scoring reads the old rows
+    INFLLM_CUDA_OK(cudaFreeAsync(c->block_k, s));
+  }
   c->block_k = nb;
   c->block_k_cap = cap;
   return INFLLM_OK;
@@ -380,27 +409,120 @@ int ensure_scores(infllm_ctx* c, int64_t n, cudaStream_t s) {
   return INFLLM_OK;
 }
 
-// retrieval + cache plan + refill of one exec block; ids in scorer order
-int retrieve_and_refill(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaStream_t s) {
+// ids of one exec block straight from the device scorer: scoring + top-k, then a host sync on the result
+int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaStream_t s) {
   const infllm_config& g = c->cfg;
   ids->clear();
   const int64_t n = c->num_blocks;
   if (n <= g.topk) {  // context_manager.py:370-371
     for (int64_t b = 0; b < n; ++b) ids->push_back((int32_t)b);
-  } else {
-    INFLLM_TRY(ensure_scores(c, n, s));
-    {
-      ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
-      INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
-                                   g.topk, 0, c->d_topk, nullptr, g.dtype, s));
-    }
-    INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-    INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
-    INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
-    ids->assign(c->h_topk, c->h_topk + g.topk);
+    return INFLLM_OK;
   }
+  INFLLM_TRY(ensure_scores(c, n, s));
+  {
+    ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
+    // the ids land directly in pinned host memory (device-visible under unified addressing)
+    INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
+                                 g.topk, 0, c->h_topk, nullptr, g.dtype, s));
+  }
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
+  INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
+  ids->assign(c->h_topk, c->h_topk + g.topk);
+  return INFLLM_OK;
+}
+
+// look-ahead for the NEXT exec block, on the second stream: top-k over the units sealed so far
+int lookahead_launch(infllm_ctx* c, int eb_next, int64_t* n_spec, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  *n_spec = c->num_blocks;
+  if (*n_spec <= g.topk) return INFLLM_OK;  // every known unit is a candidate; nothing to rank
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));  // representative keys and query means are ordered on s
+  INFLLM_CUDA_OK(cudaStreamWaitEvent(c->aux_stream, c->ev_seal, 0));
+  if (*n_spec > c->scores_aux_cap) {
+    int64_t cap = std::max<int64_t>(1024, c->scores_aux_cap);
+    while (cap < *n_spec) cap *= 2;
+    if (c->scores_aux) INFLLM_CUDA_OK(cudaFreeAsync(c->scores_aux, c->aux_stream));
+    INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->scores_aux, cap * sizeof(float), c->aux_stream));
+    c->scores_aux_cap = cap;
+  }
+  ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)*n_spec * c->width * c->esz);
+  INFLLM_TRY(block_topk_launch(c->block_k, *n_spec, (int)c->width, c->qbar + (int64_t)eb_next * c->width,
+                               c->scores_aux, g.topk, 0, c->h_spec, nullptr, g.dtype, c->aux_stream));
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_spec, c->aux_stream));
+  c->spec_recorded = true;
+  return INFLLM_OK;
+}
+
+// after the look-ahead ids arrived: copy the ones that are not resident into spare slots (side stream)
+int lookahead_stage(infllm_ctx* c, int64_t n_spec, std::vector<int32_t>* spec_ids) {
+  const infllm_config& g = c->cfg;
+  spec_ids->clear();
+  if (n_spec <= g.topk) {
+    for (int64_t b = 0; b < n_spec; ++b) spec_ids->push_back((int32_t)b);
+  } else {
+    INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_spec));
+    spec_ids->assign(c->h_spec, c->h_spec + g.topk);
+  }
+  for (int32_t b : *spec_ids) {
+    if (c->slot_of.count(b) || c->staged.count(b)) continue;
+    if (c->free_slots.empty()) break;  // no spare slot: the unit is fetched at plan time instead
+    int slot = c->free_slots.back();
+    c->free_slots.pop_back();
+    c->staged[b] = slot;
+    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
+                                   cudaMemcpyHostToDevice, c->copy_stream));
+    c->counters.h2d_bytes += c->unit_bytes;
+    c->staged_pending = true;
+  }
+  if (c->staged_pending) INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+  return INFLLM_OK;
+}
+
+// score the candidates of the next exec block (look-ahead ids + units sealed since) on s; results to pinned memory
+int candidates_launch(infllm_ctx* c, int eb_next, int64_t n_spec, const std::vector<int32_t>& spec_ids, int* n_cand,
+                      cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  const int64_t n_now = c->num_blocks;
+  *n_cand = 0;
+  if (n_now <= g.topk) return INFLLM_OK;  // all units, in id order, no scoring (context_manager.py:370-371)
+  int n = 0;
+  for (int32_t b : spec_ids) c->h_cand_rows[n++] = b;
+  for (int64_t b = n_spec; b < n_now && n < c->cand_cap; ++b) c->h_cand_rows[n++] = (int32_t)b;
+  if ((int64_t)spec_ids.size() + (n_now - n_spec) > c->cand_cap)
+    return fail(INFLLM_E_CAPACITY, "look-ahead: %lld candidates exceed %d", (long long)(spec_ids.size() + n_now - n_spec), c->cand_cap);
+  INFLLM_TRY(block_score_rows_launch(c->block_k, c->h_cand_rows, n, (int)c->width,
+                                     c->qbar + (int64_t)eb_next * c->width, c->h_cand_scores, g.dtype, s));
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_cand, s));
+  *n_cand = n;
+  return INFLLM_OK;
+}
+
+// rank the candidates on the host: descending score, ties to the lower id — the device scorer's order
+int candidates_finish(infllm_ctx* c, int n_cand, std::vector<int32_t>* ids) {
+  const infllm_config& g = c->cfg;
+  ids->clear();
+  if (n_cand == 0) {
+    for (int64_t b = 0; b < c->num_blocks; ++b) ids->push_back((int32_t)b);
+    return INFLLM_OK;
+  }
+  INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_cand));
+  std::vector<int> order(n_cand);
+  for (int i = 0; i < n_cand; ++i) order[i] = i;
+  const int32_t* rows = c->h_cand_rows;
+  const float* sc = c->h_cand_scores;
+  std::sort(order.begin(), order.end(), [&](int a, int b) {
+    if (sc[a] != sc[b]) return sc[a] > sc[b];
+    return rows[a] < rows[b];
+  });
+  for (int i = 0; i < g.topk && i < n_cand; ++i) ids->push_back(rows[order[i]]);
+  return INFLLM_OK;
+}
+
+// cache plan for `ids` (LRU eviction, stamps), adoption of staged copies, late fetches; s waits for the copies
+int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
   std::vector<int32_t> evicted;
-  c->lru.plan(ids->data(), (int)ids->size(), &evicted);
+  c->lru.plan(ids.data(), (int)ids.size(), &evicted);
   for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
     auto it = c->slot_of.find(b);
     if (it != c->slot_of.end()) {
@@ -411,64 +533,100 @@ int retrieve_and_refill(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids
   c->counters.evictions += (int64_t)evicted.size();
   if (g.cache_strategy == INFLLM_CACHE_LRU) {
     c->load_count += 1;
-    c->lru.stamp(ids->data(), (int)ids->size(), (double)c->load_count);
+    c->lru.stamp(ids.data(), (int)ids.size(), (double)c->load_count);
   } else {
-    c->lru.stamp(ids->data(), (int)ids->size(), 0.0);
+    c->lru.stamp(ids.data(), (int)ids.size(), 0.0);
   }
-  bool any_miss = false;
-  for (int32_t b : *ids) {
+  bool late = false, adopted = false;
+  for (int32_t b : ids) {
     if (c->slot_of.count(b)) {
       c->counters.cache_hits += 1;
       continue;
     }
-    if (c->free_slots.empty())
-      return fail(INFLLM_E_CAPACITY, "no free cache slot for unit %d (max_cached_block %d)", b, g.max_cached_block);
-    if (!any_miss) {
+    c->counters.cache_misses += 1;
+    auto st = c->staged.find(b);
+    if (st != c->staged.end()) {  // the look-ahead already brought it in
+      c->slot_of[b] = st->second;
+      c->staged.erase(st);
+      adopted = true;
+      continue;
+    }
+    if (c->free_slots.empty()) {
+      // spare slots are all holding look-ahead copies that were not wanted after all: reclaim one
+      if (c->staged.empty())
+        return fail(INFLLM_E_CAPACITY, "no free cache slot for unit %d (max_cached_block %d)", b, g.max_cached_block);
+      auto victim = c->staged.begin();
+      for (auto it2 = c->staged.begin(); it2 != c->staged.end(); ++it2)
+        if (std::find(ids.begin(), ids.end(), it2->first) == ids.end()) { victim = it2; break; }
+      c->free_slots.push_back(victim->second);
+      c->staged.erase(victim);
+    }
+    if (!late) {
       // slots freed above may still be read by the previous exec block's attention
       if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn, 0));
-      any_miss = true;
+      late = true;
     }
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[b] = slot;
     INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
                                    cudaMemcpyHostToDevice, c->copy_stream));
-    c->counters.cache_misses += 1;
     c->counters.h2d_bytes += c->unit_bytes;
   }
-  if (any_miss) {
+  // look-ahead copies that were not wanted: their slots go back to the pool (later copies into them are
+  // ordered behind the unfinished ones on the side stream; no kernel reads them)
+  for (auto& kv : c->staged) c->free_slots.push_back(kv.second);
+  c->staged.clear();
+  if (late) {
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
+  } else if (adopted && c->staged_pending) {
+    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_stage, 0));
   }
+  c->staged_pending = false;
   return INFLLM_OK;
 }
 
-// after an exec block that ended at absolute token `end`: sink fill and sealing (context_manager.py:614-679)
-int seal_after(infllm_ctx* c, int64_t end, cudaStream_t s) {
+// what sealing does after an exec block that ended at absolute token `end` (context_manager.py:614-679):
+// `take` tokens go to the init sink, then `n_new` units are sealed; a pure function of the lengths
+struct SealPlan {
+  int64_t take = 0;
+  int n_new = 0;
+  int64_t new_frontier = 0;
+};
+
+SealPlan plan_seal(const infllm_ctx* c, int64_t end) {
+  const infllm_config& g = c->cfg;
+  SealPlan p;
+  int64_t rem = end - c->frontier;
+  if (!c->init_full && rem > g.n_local) {  // :628-646
+    p.take = std::min<int64_t>(g.n_init - c->init_len, rem - g.n_local);
+    rem -= p.take;
+  }
+  while (rem - g.block_size >= g.n_local) {  // :649
+    rem -= g.block_size;
+    ++p.n_new;
+  }
+  p.new_frontier = c->frontier + p.take + (int64_t)p.n_new * g.block_size;
+  return p;
+}
+
+int seal_apply(infllm_ctx* c, const SealPlan& sp, cudaStream_t s) {
   const infllm_config& g = c->cfg;
   TokenBuffers& tb = c->tb;
   const int64_t D = g.head_dim, HKV = g.n_kv_heads, bs = g.block_size;
-  int64_t rem = end - c->frontier;
-  if (!c->init_full && rem > g.n_local) {
-    int64_t take = std::min<int64_t>(g.n_init - c->init_len, rem - g.n_local);
-    if (take > 0) {
-      const size_t w = take * D * c->esz;
-      const int64_t src = (c->frontier - tb.t0) * D * c->esz, dst = c->init_len * D * c->esz;
-      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_k + dst, c->init_cap * D * c->esz, (char*)tb.k_raw + src,
-                                       tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
-      INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_v + dst, c->init_cap * D * c->esz, (char*)tb.v + src,
-                                       tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
-    }
-    c->init_len += take;
-    c->frontier += take;
-    rem -= take;
-    if (c->init_len == g.n_init) c->init_full = true;
+  if (sp.take > 0) {
+    const size_t w = sp.take * D * c->esz;
+    const int64_t src = (c->frontier - tb.t0) * D * c->esz, dst = c->init_len * D * c->esz;
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_k + dst, c->init_cap * D * c->esz, (char*)tb.k_raw + src,
+                                     tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
+    INFLLM_CUDA_OK(cudaMemcpy2DAsync((char*)c->init_v + dst, c->init_cap * D * c->esz, (char*)tb.v + src,
+                                     tb.cap * D * c->esz, w, HKV, cudaMemcpyDeviceToDevice, s));
+    c->init_len += sp.take;
+    c->frontier += sp.take;
   }
-  int n_new = 0;
-  while (rem - bs >= g.n_local) {
-    rem -= bs;
-    ++n_new;
-  }
+  if (c->init_len == g.n_init) c->init_full = true;
+  const int n_new = sp.n_new;
   if (n_new == 0) return INFLLM_OK;
   INFLLM_TRY(ensure_block_k(c, c->num_blocks + n_new, s));
   INFLLM_TRY(ensure_host_units(c, c->num_blocks + n_new));
@@ -491,6 +649,24 @@ int seal_after(infllm_ctx* c, int64_t end, cudaStream_t s) {
   c->num_blocks += n_new;
   c->frontier += n_new * bs;
   return INFLLM_OK;
+}
+
+// column sums of the local stage for the window keys [j_begin, j_end) (indices relative to the window start ks),
+// added into the score buffer; `work` is the FLOP count attributed to this launch
+int local_scores(infllm_ctx* c, cudaStream_t s, int64_t st, int64_t ks, int64_t lq, int64_t lk, int64_t j_begin,
+                 int64_t j_end, double work) {
+  if (j_end <= j_begin) return INFLLM_OK;
+  const infllm_config& g = c->cfg;
+  TokenBuffers& tb = c->tb;
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
+  const int64_t n = j_end - j_begin, tok = ks - tb.t0 + j_begin, off = (lk - lq) - j_begin;
+  ProfScope ps(c, s, INFLLM_PROF_COLSUM, work);
+  if (c->use_tc && lq > 64)
+    return colsum_tc_launch_maps(c->m_qloc, c->m_krot, (int)st, (int)tok, (int)H, (int)HKV, lq, n, INFLLM_MASK_WINDOW,
+                                 off, g.n_local, c->lse, tb.score + tok, tb.cap, 1, g.dtype, s);
+  return attn_colsum_launch((const char*)c->q_loc + st * D * c->esz, c->sub_max * D, D,
+                            (char*)tb.k_rot + tok * D * c->esz, tb.cap * D, D, (int)H, (int)HKV, lq, n, (int)D,
+                            INFLLM_MASK_WINDOW, off, g.n_local, c->lse, tb.score + tok, tb.cap, 1, g.dtype, s);
 }
 
 // one internal call of at most sub_max tokens whose exec-block boundaries coincide with the caller's
@@ -539,15 +715,20 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
                                g.n_local - 1, 0, g.dtype, s));
   INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
 
-  std::vector<int32_t> ids;
+  std::vector<int32_t> ids, spec_ids;
   std::vector<KvSeg> gsegs;
-  int eb = 0;
+  int eb = 0, n_cand = 0;
+  bool have_ids = false;  // the ids of this exec block were already ranked at the end of the previous one
   for (int64_t st = 0; st < L; st += g.exc_block_size, ++eb) {  // context_manager.py:762
     const int64_t ed = std::min<int64_t>(st + g.exc_block_size, L);
     const int64_t S = T + st, E = T + ed, lq = ed - st;
     const int64_t ks = std::max<int64_t>(S - g.n_local, 0), lk = E - ks;  // local keys [ks, E) (:772-773)
-    INFLLM_TRY(retrieve_and_refill(c, eb, &ids, s));
+    if (!have_ids) INFLLM_TRY(retrieve_now(c, eb, &ids, s));
+    INFLLM_TRY(plan_and_refill(c, ids, s));
     c->trace_topk.push_back(ids);
+    const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
+    int64_t n_spec = 0;
+    if (more) INFLLM_TRY(lookahead_launch(c, eb + 1, &n_spec, s));
     const int64_t ovf = std::max<int64_t>(E - c->frontier - g.n_local, 0);  // :391
     // global key segments: retrieved units (in place in their cache slots), sink, overflow
     gsegs.clear();
@@ -562,7 +743,9 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     char* out_eb = out + st * o_ts * esz;
     const char* qloc_eb = (const char*)c->q_loc + st * D * esz;
     const char* qglb_eb = (const char*)c->q_glb + st * D * esz;
-    if (lq == 1 && D == 128) {
+    const bool decode_path = lq == 1 && D == 128;
+    double local_pairs_eb = 0;
+    if (decode_path) {
       // ---- one-token exec block: split-K decode over [visible window | global segments]
       const int64_t wlo = std::max<int64_t>(E - g.n_local, ks);  // window mask of the single query
       std::vector<KvSeg> segs;
@@ -594,6 +777,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       double local_pairs = 0, all_glk = 0;
       for (int64_t i = 0; i < lq; ++i) local_pairs += (double)std::min<int64_t>(S + i + 1, g.n_local);
       for (auto& sgm : gsegs) all_glk += sgm.len;
+      local_pairs_eb = local_pairs;
       const bool tc_now = c->use_tc && lq > 64 && gsegs.size() + 1 <= (size_t)kMaxSeg;
       if (tc_now) {
         AttnTcParams TP{};
@@ -666,21 +850,29 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         INFLLM_TRY(attn_general_launch(R, (int)D, g.dtype, s));
       }
       }
-      // accumulated local score of every window key (context_manager.py:488, 623-625)
-      ProfScope ps(c, s, INFLLM_PROF_COLSUM, 2.0 * D * H * local_pairs);
-      if (c->use_tc && lq >= 128 && lk >= 128) {
-        INFLLM_TRY(colsum_tc_launch_maps(c->m_qloc, c->m_krot, (int)st, (int)(ks - tb.t0), (int)H, (int)HKV, lq, lk,
-                                         INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse, tb.score + (ks - tb.t0),
-                                         tb.cap, 1, g.dtype, s));
-      } else {
-        INFLLM_TRY(attn_colsum_launch(qloc_eb, q_hs_s, D, (char*)tb.k_rot + (ks - tb.t0) * D * esz, kv_hs, D, (int)H,
-                                      (int)HKV, lq, lk, (int)D, INFLLM_MASK_WINDOW, lk - lq, g.n_local, c->lse,
-                                      tb.score + (ks - tb.t0), tb.cap, 1, g.dtype, s));
-      }
     }
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
     c->attn_recorded = true;
-    INFLLM_TRY(seal_after(c, E, s));
+    const SealPlan sp = plan_seal(c, E);
+    // accumulated local score of every window key (context_manager.py:488, 623-625).  Sealing only needs
+    // the scores of the tokens it is about to seal, so their 128-key tiles go first; the rest of the
+    // window follows behind the sealing and overlaps the host's cache planning for the next exec block.
+    int64_t j_u = 0;
+    if (!decode_path) {
+      j_u = std::min<int64_t>(lk, std::max<int64_t>(sp.new_frontier - ks, 0));
+      j_u = std::min<int64_t>(lk, (j_u + 127) / 128 * 128);
+      if (!more) j_u = lk;  // nothing to overlap with: one launch
+      INFLLM_TRY(local_scores(c, s, st, ks, lq, lk, 0, j_u, local_pairs_eb));
+    }
+    if (more) INFLLM_TRY(lookahead_stage(c, n_spec, &spec_ids));
+    INFLLM_TRY(seal_apply(c, sp, s));
+    if (more) INFLLM_TRY(candidates_launch(c, eb + 1, n_spec, spec_ids, &n_cand, s));
+    if (!decode_path) INFLLM_TRY(local_scores(c, s, st, ks, lq, lk, j_u, lk, 0.0));
+    have_ids = false;
+    if (more) {
+      INFLLM_TRY(candidates_finish(c, n_cand, &ids));
+      have_ids = true;
+    }
   }
   c->length += L;
   c->counters.exec_blocks += eb;
@@ -726,6 +918,7 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   if (c->initialized) {
     INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->copy_stream));
+    INFLLM_CUDA_OK(cudaStreamSynchronize(c->aux_stream));
   }
   c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
   c->init_full = false;
@@ -734,9 +927,12 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->lru.clear();
   c->slot_of.clear();
   c->free_slots.clear();
-  for (int i = c->cfg.max_cached_block - 1; i >= 0; --i) c->free_slots.push_back(i);
+  for (int i = c->cfg.max_cached_block + c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
+  c->staged.clear();
+  c->staged_pending = false;
   c->trace_topk.clear();
   c->attn_recorded = false;
+  c->spec_recorded = false;
   c->counters = infllm_ctx_info{};
   return INFLLM_OK;
 }
@@ -754,6 +950,15 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     if (c->block_k) cudaFreeAsync(c->block_k, nullptr);
     if (c->scores) cudaFreeAsync(c->scores, nullptr);
     if (c->h_topk) cudaFreeHost(c->h_topk);
+    if (c->h_spec) cudaFreeHost(c->h_spec);
+    if (c->h_cand_rows) cudaFreeHost(c->h_cand_rows);
+    if (c->h_cand_scores) cudaFreeHost(c->h_cand_scores);
+    if (c->scores_aux) cudaFreeAsync(c->scores_aux, nullptr);
+    cudaStreamDestroy(c->aux_stream);
+    cudaEventDestroy(c->ev_spec);
+    cudaEventDestroy(c->ev_cand);
+    cudaEventDestroy(c->ev_seal);
+    cudaEventDestroy(c->ev_stage);
     for (void* p : c->slabs) cudaFreeHost(p);
     cudaStreamDestroy(c->copy_stream);
     cudaEventDestroy(c->ev_main);

@@ -2,9 +2,10 @@
 //
 // block_score_kernel  HBM-streaming GEMV (one warp per representative-key row, 16-byte loads,
 //                     query mean staged in shared memory, fp32 accumulation).
-// topk_select_kernel  one CTA: 4-pass 8-bit radix select of the k-th largest score, then an
-//                     index-ordered gather of the winners and a rank sort (descending score,
-//                     ties to the lower id).
+// topk_argmax_kernel  k <= 64 over <= 8192 scores: k rounds of a CTA-wide arg-max on register-resident scores.
+// topk_select_kernel  any size: 4-pass 8-bit radix select of the k-th largest score, then an
+//                     index-ordered gather of the winners and a rank sort.  Both: descending score,
+//                     ties to the lower id.
 // repr_select_kernel  per (new unit, query head): repr_topk arg-max rounds over the accumulated
 //                     local scores, gather + mean of the chosen un-rotated keys.
 #include "common.cuh"
@@ -44,6 +45,41 @@ block_score_kernel(const T* __restrict__ bk, int64_t n, int width, const float* 
   }
   acc = warp_sum(acc);
   if (lane == 0) scores[row] = acc;
+}
+
+// the same dot product for a short list of rows: scores[i] = <bk[rows[i], :], qbar>.  `rows` and `scores` may
+// live in pinned host memory (the list is a few dozen entries; the host reads the scores after an event)
+template <typename T>
+__global__ void __launch_bounds__(kScoreWarps * 32)
+block_score_rows_kernel(const T* __restrict__ bk, const int32_t* __restrict__ rows, int n, int width,
+                        const float* __restrict__ qbar, float* __restrict__ scores) {
+  extern __shared__ float sq[];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) sq[i] = qbar[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int i = blockIdx.x * kScoreWarps + warp;
+  if (i >= n) return;
+  const T* p = bk + (int64_t)rows[i] * width;
+  float acc = 0.f;
+#pragma unroll 4
+  for (int c = lane * 8; c < width; c += 32 * 8) {
+    uint4 raw = __ldg(reinterpret_cast<const uint4*>(p + c));
+    const typename Act<T>::T2* v2 = reinterpret_cast<const typename Act<T>::T2*>(&raw);
+    const float4 qa = *reinterpret_cast<const float4*>(sq + c);
+    const float4 qb = *reinterpret_cast<const float4*>(sq + c + 4);
+    float2 f0 = Act<T>::to_f2(v2[0]), f1 = Act<T>::to_f2(v2[1]), f2 = Act<T>::to_f2(v2[2]),
+           f3 = Act<T>::to_f2(v2[3]);
+    acc = fmaf(f0.x, qa.x, acc);
+    acc = fmaf(f0.y, qa.y, acc);
+    acc = fmaf(f1.x, qa.z, acc);
+    acc = fmaf(f1.y, qa.w, acc);
+    acc = fmaf(f2.x, qb.x, acc);
+    acc = fmaf(f2.y, qb.y, acc);
+    acc = fmaf(f3.x, qb.z, acc);
+    acc = fmaf(f3.y, qb.w, acc);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) scores[i] = acc;
 }
 
 __device__ __forceinline__ uint32_t float_key(float f) {
@@ -163,6 +199,77 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
   }
 }
 
+// Small k (the usual topk of 16-64) over at most 8192 scores: k rounds of a CTA-wide arg-max.  Every thread
+// keeps its strided scores in registers; a round is two warp reductions and two barriers.  Same order
+// as topk_select_kernel: descending score, ties to the lower id.
+constexpr int kArgmaxItems = 8;
+__global__ void __launch_bounds__(kTopkThreads)
+topk_argmax_kernel(const float* __restrict__ scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
+                   float* __restrict__ out_scores) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int s_win;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float v[kArgmaxItems];
+#pragma unroll
+  for (int e = 0; e < kArgmaxItems; ++e) {
+    int i = tid + e * kTopkThreads;
+    v[e] = i < n ? scores[i] : -INFINITY;
+  }
+  // NaN scores never win; -inf scores can, after everything finite (ids ascending)
+  unsigned taken = 0;
+#pragma unroll
+  for (int e = 0; e < kArgmaxItems; ++e)
+    if (tid + e * kTopkThreads >= n || v[e] != v[e]) taken |= 1u << e;
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int e = 0; e < kArgmaxItems; ++e) {
+      int i = tid + e * kTopkThreads;
+      if (!(taken >> e & 1) && (v[e] > bv || (v[e] == bv && i < bi))) {
+        bv = v[e];
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sv[warp] = bv;
+      si[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      bv = sv[lane];
+      bi = si[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      if (lane == 0) {
+        s_win = bi;
+        out_ids[r] = (bi == 0x7fffffff ? 0 : bi) + id_base;
+        if (out_scores) out_scores[r] = bv;
+      }
+    }
+    __syncthreads();
+    const int w = s_win;
+    if (w != 0x7fffffff && (w % kTopkThreads) == tid) taken |= 1u << (w / kTopkThreads);
+  }
+}
+
 template <typename T>
 __global__ void repr_select_kernel(const T* __restrict__ k, int64_t k_hs, int64_t k_ts,
                                    const float* __restrict__ score, int64_t score_hs, int64_t tok0,
@@ -233,8 +340,24 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
         (const T*)bk, n, width, qbar, scores);
   });
   INFLLM_LAUNCH_OK("block_score_kernel");
-  topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
-  INFLLM_LAUNCH_OK("topk_select_kernel");
+  if (k <= 64 && n <= (int64_t)kArgmaxItems * kTopkThreads) {
+    topk_argmax_kernel<<<1, kTopkThreads, 0, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
+    INFLLM_LAUNCH_OK("topk_argmax_kernel");
+  } else {
+    topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
+    INFLLM_LAUNCH_OK("topk_select_kernel");
+  }
+  return INFLLM_OK;
+}
+
+int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
+                            int dtype, cudaStream_t s) {
+  if (n <= 0) return INFLLM_OK;
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    block_score_rows_kernel<T><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
+        (const T*)bk, rows, n, width, qbar, scores);
+  });
+  INFLLM_LAUNCH_OK("block_score_rows_kernel");
   return INFLLM_OK;
 }
 

@@ -66,12 +66,14 @@ def _run(case, dtype=torch.bfloat16):
     return cm, ora, stats
 
 
-@pytest.mark.parametrize("kernels", ["tcgen05", "generic"])
+@pytest.mark.parametrize("kernels", ["tcgen05", "generic", "tcgen05-nolookahead"])
 @pytest.mark.parametrize("name", D128)
 def test_context_memory_matches_oracle(name, kernels, monkeypatch):
-    """Both kernel families behind the exec-block loop: the tcgen05 kernels (default for blocks of more than
-    64 queries) and the shape-generic mma.sync kernels."""
+    """Both kernel families behind the exec-block loop — the tcgen05 kernels (default for blocks of more than
+    64 queries) and the shape-generic mma.sync kernels — and both ways of ranking the units of the next
+    exec block (look-ahead with staged copies, or the device scorer with a host sync every block)."""
     monkeypatch.setenv("INFLLM_B200_NO_TC", "1" if kernels == "generic" else "0")
+    monkeypatch.setenv("INFLLM_B200_NO_LOOKAHEAD", "1" if kernels.endswith("nolookahead") else "0")
     case = C.CASES[name]
     cm, ora, stats = _run(case)
     from infllm_b200 import _lib

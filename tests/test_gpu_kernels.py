@@ -122,7 +122,8 @@ def test_attention_row_without_visible_keys_gives_zero():
 
 
 # -------------------------------------------------------------------------- retrieval kernels
-@pytest.mark.parametrize("n,k,width", [(5, 5, 1024), (40, 4, 4096), (991, 16, 4096), (8192, 32, 4096), (3000, 64, 512)])
+@pytest.mark.parametrize("n,k,width", [(5, 5, 1024), (40, 4, 4096), (991, 16, 4096), (8192, 32, 4096), (3000, 64, 512),
+                                       (5000, 100, 512), (20000, 16, 256)])
 def test_block_topk_matches_torch(n, k, width):
     L = _L()
     g = torch.Generator().manual_seed(n + k)
