@@ -278,12 +278,14 @@ def run_ours(args, rank, world, local_rank):
             prefill_device(layer, hidden)
         layer.pkv.profile(True)
         layer.pkv.get_profile()
+        layer.pkv.host_timers()
         clk_p, clk_f = sample_clocks_start(local_rank)
         l0 = _lib.lib.infllm_launch_count()
         ms = timed(lambda: prefill_device(layer, hidden), args.steps)
         launches = _lib.lib.infllm_launch_count() - l0
         prof = layer.pkv.get_profile()
         info = layer.pkv.info()
+        host_us = layer.pkv.host_timers()
         layer.pkv.profile(False)
         clocks = sample_clocks_stop(clk_p, clk_f)
         for _ in range(min(args.warmup, 1)):
@@ -301,7 +303,7 @@ def run_ours(args, rank, world, local_rank):
         vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload=f"mistral-7b attention layer (hidden 4096, 32q/8kv, d128, rope 1e6), {tokens}-token prefill "
                              "in 8192-token calls, exec 512, n_init 128, n_local 4096, unit 128, topk 16, repr_topk 4, "
-                             "max_cached 32, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
+                             f"max_cached {CFG['max_cached']}, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
                     replicas=world),
         e2e=dict(value=e2e, unit="tokens/s", h2d_bytes_per_step=int(hidden.numel() * 2),
                  d2h_bytes_per_step=int(h_out.numel() * 2), ms_per_step=ms_e2e / args.steps),
@@ -314,6 +316,7 @@ def run_ours(args, rank, world, local_rank):
         kernels={k: dict(ms=v[0], launches=v[2]) for k, v in prof.items()},
         store=dict(h2d_bytes=info["h2d_bytes"], d2h_bytes=info["d2h_bytes"], hits=info["cache_hits"],
                    misses=info["cache_misses"], evictions=info["evictions"]),
+        host_ms_per_step={k: v / 1e3 / args.steps for k, v in host_us.items()},
         clocks=clocks)
     if rank == 0 and world == 1 and not args.no_cpu:
         v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
@@ -331,7 +334,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=CFG["tokens"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--max-cached", type=int, default=CFG["max_cached"], help="max_cached_block (32 in the named config)")
     args = ap.parse_args()
+    CFG["max_cached"] = args.max_cached
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":

@@ -113,6 +113,10 @@ int infllm_attn_colsum(const void* d_q, int64_t q_hs, int64_t q_ts,
 int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int width, const float* d_qbar,
                       float* d_scores, int k, int id_base, int32_t* d_out_ids, float* d_out_scores,
                       int dtype, void* stream);
+/* infllm_block_score_rows: the same scores for a short HOST list of n unit ids only (d_scores[i] = score of unit
+ * h_rows[i]); used to re-rank the look-ahead candidates of the next exec block after new units were sealed. */
+int infllm_block_score_rows(const void* d_block_k, const int32_t* h_rows, int n, int width, const float* d_qbar,
+                            float* d_scores, int dtype, void* stream);
 int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float* d_score, int64_t score_hs,
                        int64_t tok0, int n_new, int block_size, int repr_topk,
                        int n_heads, int n_kv_heads, int head_dim, void* d_block_k_out, int dtype,
@@ -226,6 +230,18 @@ int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
 #define INFLLM_PROF_SLOTS 4
 int infllm_ctx_profile(infllm_ctx* ctx, int enable);
 int infllm_ctx_get_profile(infllm_ctx* ctx, double* ms, double* work, int64_t* launches);
+/* Event trace of the exec-block loop, off by default: when enabled the context records a CUDA event at fixed
+ * points of every stream it uses (labels: 0 attention begin, 1 attention end, 2 urgent score tiles end,
+ * 3 sealing + candidate scoring end, 4 rest of the score pass end, 5/6 look-ahead ranking begin/end,
+ * 7/8 staging copies begin/end).  infllm_ctx_get_trace synchronises, returns (label, exec block, ms since the
+ * first mark) in record order and clears the trace. */
+int infllm_ctx_trace(infllm_ctx* ctx, int enable);
+int infllm_ctx_get_trace(infllm_ctx* ctx, int32_t* labels, int64_t* exec_blocks, float* ms, int cap, int* n);
+/* Host time (microseconds, summed since the last call) the exec-block loop spent in each of its phases:
+ * 0 device ranking + sync, 1 cache plan + late fetches, 2 look-ahead launch, 3 attention launch,
+ * 4 look-ahead wait + staging copies, 5 sealing, 6 candidate wait + ranking, 7 unused.  Diagnostics. */
+#define INFLLM_HOST_TIMERS 8
+int infllm_ctx_get_host_timers(infllm_ctx* ctx, double* us);
 /* The tensor-core kernels bound every wait on a barrier; a wait that runs out makes the kernel record
  * an error and return instead of hanging.  infllm_device_error synchronises the device, reads the
  * record (code 0 = none, 1 = wait ran out; `where` identifies the wait) and clears it. */

@@ -65,6 +65,7 @@ SIGNATURES = {
                                    c_int, c_void_p]),
     "infllm_block_topk": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                   c_int, c_void_p]),
+    "infllm_block_score_rows": (c_int, [c_void_p, POINTER(c_int32), c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "infllm_repr_select": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                                    c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "infllm_attn_decode_max_parts": (c_int64, [c_int, c_int64]),
@@ -86,6 +87,9 @@ SIGNATURES = {
     "infllm_ctx_get_profile": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), POINTER(c_int64)]),
     "infllm_device_error": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "infllm_launch_count": (ctypes.c_longlong, []),
+    "infllm_ctx_trace": (c_int, [c_void_p, c_int]),
+    "infllm_ctx_get_trace": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_float), c_int, POINTER(c_int)]),
+    "infllm_ctx_get_host_timers": (c_int, [c_void_p, POINTER(c_double)]),
     "infllm_ctx_get_cached": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_double), c_int, POINTER(c_int)]),
     "infllm_ctx_get_topk": (c_int, [c_void_p, c_int64, POINTER(c_int32), c_int, POINTER(c_int)]),
     "infllm_ctx_get_block_k": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),

@@ -75,6 +75,8 @@ class ContextManager:
             cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
         if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":
             cfg.reserved[0] |= 2  # debugging aid: rank every exec block's units on the device, no look-ahead staging
+        if os.environ.get("INFLLM_B200_STAGE_KERNEL", "0") == "1":
+            cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))
@@ -193,6 +195,13 @@ class ContextManager:
                 tot[name][1] += work[i]
                 tot[name][2] += n[i]
         return {k: tuple(v) for k, v in tot.items()}
+
+    def host_timers(self, u=0):
+        """Host microseconds per phase of the exec-block loop since the last call (diagnostics)."""
+        us = (ctypes.c_double * 8)()
+        _lib.check(_lib.lib.infllm_ctx_get_host_timers(self._ctx[u], us))
+        names = ("rank_sync", "plan", "lookahead_launch", "attn_launch", "lookahead_stage", "seal", "cand_wait")
+        return {n: us[i] for i, n in enumerate(names)}
 
     def reset(self):
         for h in self._ctx:

@@ -7,8 +7,9 @@
 //                   owning half of the tile's key columns; row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
 //                   TMEM (two buffers), P goes through shared memory as a K-major operand, O stays in
 //                   TMEM for the whole tile with lazy rescaling; K/V tiles are double buffered.
-// colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes, each thread sums
-//                   exp2(s - lse) over the queries that see its key.
+// colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes; a CTA keeps one K tile and streams
+//                   every (head of the group, query tile) through a TMA ring and two TMEM buffers; two
+//                   threads per key sum exp2(s - lse) over the queries that see it.
 // Every mbarrier wait is bounded; a wait that runs out records an error code and the CTA unwinds.
 #include <type_traits>
 
@@ -21,6 +22,14 @@ namespace infllm {
 using namespace tc;
 
 __device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] blockIdx.y
+#ifdef INFLLM_TC_TIMING
+// development aid: per-iteration clock stamps of CTA (0,0): [role][iteration], roles 0 producer issue, 1 operands
+// arrived, 2 MMA committed, 3 accumulator seen by the compute warps, 4 compute done
+__device__ long long g_tc_stamps[5][256];
+#define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
+#else
+#define TC_STAMP(role, it) do { } while (0)
+#endif
 
 __device__ __forceinline__ void record_error(int* err, int code, int where) {
   if (atomicCAS(&err[0], 0, code) == 0) {
@@ -425,30 +434,52 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------ column sums
+// One CTA owns 128 keys of one KV head and walks every (query head of the group, visible 128-query tile)
+// pair: K stays in shared memory, the query tiles stream through a two-stage TMA ring, S^T goes to one of two
+// TMEM buffers, and 8 compute warps (two threads per key row, 64 query columns each) turn it into
+// sum_q exp2(s - lse_q) while the next tile is being loaded and multiplied.
+namespace colsum_smem {
+constexpr int kStages = 4;                    // query tiles in flight (shared-memory ring and TMEM buffers)
+constexpr int kK = 0;
+constexpr int kQ = kK + 2 * kSubTileBytes;
+constexpr int kLse = kQ + kStages * 2 * kSubTileBytes;  // kStages x 128 fp32
+constexpr int kBar = kLse + kStages * 512;
+constexpr int kAcc = kBar + 128;              // per (head of the group, column quarter, key) partial sums: 8 x 4 x 128 fp32
+constexpr int kTotal = kAcc + 8 * 4 * 128 * 4;
+}  // namespace colsum_smem
+
 template <typename T>
-__global__ void __launch_bounds__(128) colsum_tc_kernel(const __grid_constant__ ColsumTcParams P) {
+__global__ void __launch_bounds__(576) colsum_tc_kernel(const __grid_constant__ ColsumTcParams P) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t sK = smem_u32(smem), sQ = sK + 2 * kSubTileBytes;
-  unsigned char* tail = smem + 4 * kSubTileBytes;
-  const uint32_t bar_k = smem_u32(tail), bar_q = bar_k + 8, bar_mma = bar_k + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 24);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 32);
-  float* s_lse = reinterpret_cast<float*>(tail + 64);  // 128 floats
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t sK = s_base + colsum_smem::kK, sQ = s_base + colsum_smem::kQ;
+  const uint32_t bars = s_base + colsum_smem::kBar;
+  // barriers: 0 k_full, then q_full[NS], s_full[NS], free[NS]
+  constexpr int NS = colsum_smem::kStages;
+  constexpr int QF = 1, SF = 1 + NS, FR = 1 + 2 * NS;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + colsum_smem::kBar + 112);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + colsum_smem::kBar + 120);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, hkv = h / P.group;
+  const int hkv = blockIdx.y;
   const int64_t j0 = (int64_t)blockIdx.x * kTile;
   const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
   if (threadIdx.x == 0) {
-    mbar_init(bar_k, 1);
-    mbar_init(bar_q, 1);
-    mbar_init(bar_mma, 1);
+    mbar_init(bar(0), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(bar(QF + i), 1);
+      mbar_init(bar(SF + i), 1);
+      mbar_init(bar(FR + i), 512);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 128);
+  float* s_acc = reinterpret_cast<float*>(smem + colsum_smem::kAcc);
+  for (int i = threadIdx.x; i < 8 * 4 * 128; i += blockDim.x) s_acc[i] = 0.f;
+  if (warp == 17) {
+    tmem_alloc(smem_u32(tmem_slot), 128 * NS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -458,7 +489,7 @@ __global__ void __launch_bounds__(128) colsum_tc_kernel(const __grid_constant__ 
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t idesc = make_idesc(kBf16, 128, 128, false);
 
-  // query rows that can see a key of this tile
+  // query tiles that can see a key of this tile (the same for every head)
   int64_t qi_lo = 0, qi_hi = P.lq - 1;
   if (P.mask_mode == INFLLM_MASK_WINDOW) {
     qi_lo = j0 - P.mask_offset;
@@ -468,86 +499,142 @@ __global__ void __launch_bounds__(128) colsum_tc_kernel(const __grid_constant__ 
   }
   if (qi_lo < 0) qi_lo = 0;
   if (qi_hi > P.lq - 1) qi_hi = P.lq - 1;
-  // this thread's key and the queries that see it
-  const int krow = warp * 32 + lane;
-  const int64_t kj = j0 + krow;
-  int64_t vi_lo = 0, vi_hi = P.lq - 1;
-  if (P.mask_mode == INFLLM_MASK_WINDOW) {
-    vi_lo = kj - P.mask_offset;
-    vi_hi = kj - P.mask_offset + P.mask_size - 1;
-  } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
-    vi_lo = kj - P.mask_offset + P.mask_size;
-  }
-  if (vi_lo < 0) vi_lo = 0;
-  if (vi_hi > P.lq - 1) vi_hi = P.lq - 1;
-  if (kj >= P.lk) vi_hi = -1;
+  const bool any = qi_lo <= qi_hi;
+  const int t_first = any ? (int)(qi_lo / kTile) : 0, t_last = any ? (int)(qi_hi / kTile) : -1;
+  const int n_t = t_last - t_first + 1, n_it = n_t * P.group;
 
-  float total = 0.f;
-  bool ok = true;
-  if (qi_lo <= qi_hi) {
-    const int t_first = (int)(qi_lo / kTile), t_last = (int)(qi_hi / kTile);
-    if (threadIdx.x == 0) {
-      mbar_expect_tx(bar_k, 2 * kSubTileBytes);
-      tma_load_3d(sK, &P.map_k, bar_k, 0, P.k_tok0 + (int)j0, hkv);
-      tma_load_3d(sK + kSubTileBytes, &P.map_k, bar_k, 64, P.k_tok0 + (int)j0, hkv);
+  if (warp == 16) {
+    // ================================================================ producer: K once, then the query tiles
+    bool ok = true;
+    if (any && lane == 0) {
+      mbar_expect_tx(bar(0), 2 * kSubTileBytes);
+      tma_load_3d(sK, &P.map_k, bar(0), 0, P.k_tok0 + (int)j0, hkv);
+      tma_load_3d(sK + kSubTileBytes, &P.map_k, bar(0), 64, P.k_tok0 + (int)j0, hkv);
     }
-    for (int t = t_first; t <= t_last && ok; ++t) {
-      const int n = t - t_first;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int b = it % NS, h = hkv * P.group + it / n_t, t = t_first + it % n_t;
+      if (it >= NS) ok = __all_sync(0xffffffffu, wait_or_abort(bar(FR + b), ((it / NS) - 1) & 1, abort_flag, P.err, 410));
+      if (!ok) break;
       const int64_t q0 = (int64_t)t * kTile;
-      if (threadIdx.x == 0) {
-        mbar_expect_tx(bar_q, 2 * kSubTileBytes);
-        tma_load_3d(sQ, &P.map_q, bar_q, 0, P.q_row0 + (int)q0, h);
-        tma_load_3d(sQ + kSubTileBytes, &P.map_q, bar_q, 64, P.q_row0 + (int)q0, h);
+      if (lane == 0) {
+        TC_STAMP(0, it);
+        mbar_expect_tx(bar(QF + b), 2 * kSubTileBytes);
+        tma_load_3d(sQ + b * 2 * kSubTileBytes, &P.map_q, bar(QF + b), 0, P.q_row0 + (int)q0, h);
+        tma_load_3d(sQ + b * 2 * kSubTileBytes + kSubTileBytes, &P.map_q, bar(QF + b), 64, P.q_row0 + (int)q0, h);
       }
-      s_lse[threadIdx.x] = (q0 + threadIdx.x < P.lq) ? P.lse[(int64_t)h * P.lq + q0 + threadIdx.x] : INFINITY;
-      if (threadIdx.x == 0) {
-        if (n == 0) ok = wait_or_abort(bar_k, 0, abort_flag, P.err, 400);
-        if (ok) ok = wait_or_abort(bar_q, n & 1, abort_flag, P.err, 401);
-        if (ok) {
-          tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            // S^T = K Q^T: keys are the M rows (TMEM lanes), queries the N columns
-            uint64_t ad = make_sdesc(sK + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-            uint64_t bd = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-            mma_ss(tmem, ad, bd, idesc, ks > 0);
-          }
-          tc_commit(bar_mma);
-        }
-      }
-      __syncthreads();  // s_lse visible; thread 0 has issued (or given up)
-      ok = __all_sync(0xffffffffu, wait_or_abort(bar_mma, n & 1, abort_flag, P.err, 402));
-      if (ok) {
-        tc_fence_after();
-        const uint32_t ta = tmem + (((uint32_t)(warp * 32)) << 16);
-        int64_t a = vi_lo > q0 ? vi_lo : q0, e = vi_hi < q0 + kTile - 1 ? vi_hi : q0 + kTile - 1;
-        const int c_lo = (int)(a - q0), c_hi = (int)(e - q0);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(ta + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            int col = c * 32 + k;
-            float ls = s_lse[col];
-            float pv = exp2f(__uint_as_float(r[k]) * P.scale_log2 - ls);
-            total += (col >= c_lo && col <= c_hi && ls != -INFINITY) ? pv : 0.f;
-          }
-        }
-        tc_fence_before();
-      }
-      __syncthreads();  // TMEM tile and the Q buffer may be overwritten by the next iteration
-      ok = !(*abort_flag);
     }
-  }
-  if (ok && kj < P.lk) {
-    float* dst = P.score + (int64_t)h * P.score_hs + kj;
-    *dst = P.accumulate ? *dst + total : total;
+  } else if (warp == 17) {
+    // ======================================================================================= MMA issuer
+    if (lane == 0 && any) {
+      bool ok = wait_or_abort(bar(0), 0, abort_flag, P.err, 411);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int b = it % NS;
+        ok = wait_or_abort(bar(QF + b), (it / NS) & 1, abort_flag, P.err, 412);
+        TC_STAMP(1, it);
+        if (ok && it >= NS) ok = wait_or_abort(bar(FR + b), ((it / NS) - 1) & 1, abort_flag, P.err, 413);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t qt = sQ + b * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // S^T = K Q^T: keys are the M rows (TMEM lanes), queries the N columns
+          uint64_t ad = make_sdesc(sK + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          uint64_t bd = make_sdesc(qt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          mma_ss(tmem + b * 128, ad, bd, idesc, ks > 0);
+        }
+        tc_commit(bar(SF + b));
+        TC_STAMP(2, it);
+      }
+    }
+  } else {
+    // ========================================================================================== compute
+    const int quad = warp & 3, part = warp >> 2;
+    const int krow = quad * 32 + lane;
+    const int64_t kj = j0 + krow;
+    const int col0 = part * 32;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    // queries that see this thread's key
+    int64_t vi_lo = 0, vi_hi = P.lq - 1;
+    if (P.mask_mode == INFLLM_MASK_WINDOW) {
+      vi_lo = kj - P.mask_offset;
+      vi_hi = kj - P.mask_offset + P.mask_size - 1;
+    } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
+      vi_lo = kj - P.mask_offset + P.mask_size;
+    }
+    if (vi_lo < 0) vi_lo = 0;
+    if (vi_hi > P.lq - 1) vi_hi = P.lq - 1;
+    if (kj >= P.lk) vi_hi = -1;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int b = it % NS, g = it / n_t, t = t_first + it % n_t;
+      // the log-sum-exps of this thread's 64 query columns: fetched before the wait so that their latency hides
+      float ls[32];
+      {
+        const int64_t qb = (int64_t)t * kTile + col0;
+        const float* lp = P.lse + (int64_t)(hkv * P.group + g) * P.lq + qb;
+        if (qb + 32 <= P.lq && ((uintptr_t)lp & 15) == 0) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const float4 l4 = __ldg(reinterpret_cast<const float4*>(lp + c));
+            ls[c] = l4.x; ls[c + 1] = l4.y; ls[c + 2] = l4.z; ls[c + 3] = l4.w;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ls[c] = qb + c < P.lq ? __ldg(lp + c) : INFINITY;
+        }
+      }
+      ok = __all_sync(0xffffffffu, wait_or_abort(bar(SF + b), (it / NS) & 1, abort_flag, P.err, 414));
+      if (!ok) break;
+      if (threadIdx.x == 0) TC_STAMP(3, it);
+      tc_fence_after();
+      float sv[32];
+      tmem_ld32(tmem + b * 128 + lane_base + col0, reinterpret_cast<uint32_t*>(sv));
+      tmem_wait_ld();
+      const int64_t q0 = (int64_t)t * kTile + col0;
+      const int64_t a = vi_lo > q0 ? vi_lo : q0, e = vi_hi < q0 + 31 ? vi_hi : q0 + 31;
+      const int c_lo = (int)(a - q0), c_hi = (int)(e - q0);
+      float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (c_lo == 0 && c_hi == 31) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          acc4[0] += ex2_approx(fmaf(sv[c], P.scale_log2, -ls[c]));
+          acc4[1] += ex2_approx(fmaf(sv[c + 1], P.scale_log2, -ls[c + 1]));
+          acc4[2] += ex2_approx(fmaf(sv[c + 2], P.scale_log2, -ls[c + 2]));
+          acc4[3] += ex2_approx(fmaf(sv[c + 3], P.scale_log2, -ls[c + 3]));
+        }
+      } else if (c_lo <= c_hi) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float pv = ex2_approx(fmaf(sv[c], P.scale_log2, -ls[c]));
+          acc4[c & 3] += (c >= c_lo && c <= c_hi) ? pv : 0.f;
+        }
+      }
+      // a query row without any visible key has lse = -inf; it cannot see this key either, so it is masked above.
+      // Every thread owns one slot per head: no atomics, and the final sum below has a fixed order.
+      s_acc[(g * 4 + part) * 128 + krow] += (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+      tc_fence_before();
+      mbar_arrive(bar(FR + b));
+      if (threadIdx.x == 0) TC_STAMP(4, it);
+    }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 128);
+  if (threadIdx.x < 128 && !(*abort_flag) && any) {
+    const int64_t kj = j0 + threadIdx.x;
+    if (kj < P.lk) {
+      for (int g = 0; g < P.group; ++g) {
+        const float* sa = s_acc + (g * 4) * 128 + threadIdx.x;
+        const float v = (sa[0] + sa[128]) + (sa[256] + sa[384]);
+        float* dst = P.score + (int64_t)(hkv * P.group + g) * P.score_hs + kj;
+        *dst = P.accumulate ? *dst + v : v;
+      }
+    }
+  } else if (threadIdx.x < 128 && !any && !P.accumulate) {
+    const int64_t kj = j0 + threadIdx.x;
+    if (kj < P.lk)
+      for (int g = 0; g < P.group; ++g) P.score[(int64_t)(hkv * P.group + g) * P.score_hs + kj] = 0.f;
+  }
+  if (warp == 17) tmem_dealloc(tmem, 128 * NS);
 }
 
 // ---------------------------------------------------------------------------------------- host side
@@ -633,12 +720,13 @@ int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, in
   P.mask_offset = mask_offset; P.mask_size = mask_size; P.lse = lse; P.score = score; P.score_hs = score_hs;
   P.scale_log2 = kLog2e / sqrtf(128.f);
   INFLLM_TRY(tc_get_error_ptr(&P.err));
-  dim3 grid((unsigned)ceil_div(lk, kTile), n_heads);
-  const size_t smem = 4 * kSubTileBytes + 64 + 128 * sizeof(float) + 1024;
+  if (P.group > 8) return fail(INFLLM_E_UNSUPPORTED, "colsum: %d query heads per kv head (at most 8)", P.group);
+  dim3 grid((unsigned)ceil_div(lk, kTile), n_kv_heads);
+  const size_t smem = colsum_smem::kTotal + 1024;
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = colsum_tc_kernel<T>;
     INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 128, smem, s>>>(P);
+    kern<<<grid, 576, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("colsum_tc_kernel");
   return INFLLM_OK;
@@ -671,3 +759,12 @@ extern "C" int infllm_device_error(int* code, int* where) {
   if (where) *where = h[1];
   return INFLLM_OK;
 }
+
+#ifdef INFLLM_TC_TIMING
+extern "C" int infllm_tc_stamps(long long* h_out) {
+  using namespace infllm;
+  INFLLM_CUDA_OK(cudaDeviceSynchronize());
+  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 5 * 256));
+  return INFLLM_OK;
+}
+#endif

@@ -12,6 +12,7 @@
 // Sealed units are copied to a pinned host store on a side stream and come back into one of
 // max_cached_block cache slots with cudaMemcpyAsync when retrieval asks for them.
 #include <algorithm>
+#include <chrono>
 #include <list>
 #include <unordered_map>
 #include <vector>
@@ -27,6 +28,9 @@ int rope_apply_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int6
                       int64_t table_len, int64_t pos0, int pos_step, int dtype, cudaStream_t s);
 int copy_rows_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
                      int n_heads, int64_t len, int head_dim, cudaStream_t s);
+int pack_units_launch(const void* k, const void* v, int64_t hs, int64_t tok0, int n_new, int block_size, int n_kv_heads,
+                      int head_dim, void* out, cudaStream_t s);
+int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int64_t unit_bytes, cudaStream_t s);
 int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t len, int exc, int head_dim,
                 float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s);
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
@@ -177,12 +181,36 @@ struct infllm_ctx {
   // only the candidates (that top-k plus the newly sealed units) are re-scored and ranked on the host
   float* scores_aux = nullptr;
   int64_t scores_aux_cap = 0;
+  struct LookAhead {
+    int64_t target = -1;   // exec block (index inside the current call) this look-ahead is for
+    int64_t n_spec = 0;    // units that existed when it was launched
+    bool launched = false, staged = false;
+    std::vector<int32_t> ids;
+    int32_t* h_ids = nullptr;  // pinned: ids written by the device
+    cudaEvent_t ev = nullptr;
+  };
+  static constexpr int kLookDepth = 2;            // exec blocks ranked ahead
+  LookAhead la[kLookDepth + 1];
+  std::unordered_map<int32_t, int64_t> staged_for;  // staged unit -> latest exec block that wants it
   int32_t* h_spec = nullptr;        // pinned: look-ahead ids
   int32_t* h_cand_rows = nullptr;   // pinned: candidate unit ids
   float* h_cand_scores = nullptr;   // pinned: their scores
+  float* d_cand_scores = nullptr;   // device side of the same mailbox
+  int32_t* d_spec = nullptr;        // device side of the look-ahead id mailboxes, (kLookDepth + 1) x topk
+  cudaStream_t mail_stream = nullptr;  // carries the small result copies to the host, off the main stream
   int cand_cap = 0;
   std::unordered_map<int32_t, int> staged;  // unit -> slot holding a prefetched copy
   bool staged_pending = false;              // staged copies issued since the last wait on them
+
+  // sealed units leave through a packing buffer (two in rotation) and one copy per run of units
+  void* pack_buf[2] = {nullptr, nullptr};
+  cudaEvent_t ev_pack[2] = {nullptr, nullptr};
+  bool pack_used[2] = {false, false};
+  int pack_idx = 0, pack_units = 0;
+  cudaStream_t d2h_stream = nullptr;
+  cudaEvent_t ev_d2h = nullptr, ev_ingest = nullptr;
+  bool d2h_recorded = false;
+  int64_t d2h_synced_upto = 0;  // units below this id are known to be in the host store as far as copy_stream is concerned
 
   cudaStream_t copy_stream = nullptr, aux_stream = nullptr;
   cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr, ev_spec = nullptr,
@@ -198,6 +226,14 @@ struct infllm_ctx {
   double prof_ms[INFLLM_PROF_SLOTS] = {0}, prof_work[INFLLM_PROF_SLOTS] = {0};
   int64_t prof_launches[INFLLM_PROF_SLOTS] = {0};
 
+  // optional event trace of the exec-block loop (infllm_ctx_trace): (label, exec block, event) in record order
+  bool trace_on = false;
+  struct Mark { int label; int64_t eb; cudaEvent_t ev; };
+  std::vector<Mark> marks;
+
+  // host-side time spent in each phase of the exec-block loop, microseconds (diagnostics)
+  double host_us[INFLLM_HOST_TIMERS] = {0};
+
   // trace of the last append
   std::vector<std::vector<int32_t>> trace_topk;
   infllm_ctx_info counters{};
@@ -208,6 +244,25 @@ struct infllm_ctx {
 namespace {
 
 int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// trace labels
+enum { TR_ATTN_BEGIN = 0, TR_ATTN_END, TR_URGENT_END, TR_SEAL_END, TR_REST_END, TR_SPEC_BEGIN, TR_SPEC_END,
+       TR_STAGE_BEGIN, TR_STAGE_END, TR_REPR_END, TR_PACK_END };
+void trace_mark(infllm_ctx* c, cudaStream_t s, int label, int64_t eb);
+void trace_mark(infllm_ctx* c, cudaStream_t s, int label, int64_t eb) {
+  if (!c->trace_on || c->marks.size() > 20000) return;
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, s);
+  c->marks.push_back({label, eb, e});
+}
+
+struct HostTimer {
+  double* acc;
+  std::chrono::steady_clock::time_point t0;
+  explicit HostTimer(double* a) : acc(a), t0(std::chrono::steady_clock::now()) {}
+  ~HostTimer() { *acc += std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count(); }
+};
 
 // timing scope: records an event pair around the launches issued while it lives
 struct ProfScope {
@@ -253,11 +308,23 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
 
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_d2h, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_ingest, cudaEventDisableTiming));
+  c->pack_units = g.exc_block_size / g.block_size + 2;
+  for (int i = 0; i < 2; ++i) {
+    INFLLM_CUDA_OK(cudaMalloc(&c->pack_buf[i], (int64_t)c->pack_units * c->unit_bytes));
+    INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_pack[i], cudaEventDisableTiming));
+  }
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_main, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_copy, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_attn, cudaEventDisableTiming));
-  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;  // the look-ahead kernels are short and latency matters: highest priority
+    INFLLM_CUDA_OK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    INFLLM_CUDA_OK(cudaStreamCreateWithPriority(&c->aux_stream, cudaStreamNonBlocking, hi));
+  }
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_spec, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_cand, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_seal, cudaEventDisableTiming));
@@ -295,17 +362,24 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
-  c->cand_cap = g.topk + g.exc_block_size / g.block_size + 4;
+  c->cand_cap = g.topk + (infllm_ctx::kLookDepth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
+  for (auto& l : c->la) {
+    INFLLM_CUDA_OK(cudaHostAlloc((void**)&l.h_ids, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
+    INFLLM_CUDA_OK(cudaEventCreateWithFlags(&l.ev, cudaEventDisableTiming));
+  }
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_rows, c->cand_cap * sizeof(int32_t), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_scores, c->cand_cap * sizeof(float), cudaHostAllocDefault));
+  INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_cand_scores, c->cand_cap * sizeof(float)));
+  INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_spec, (infllm_ctx::kLookDepth + 1) * std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->mail_stream, cudaStreamNonBlocking));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
   c->max_parts = (int)(dec_keys / 128 + g.topk + 8);
   INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
-  // max_cached_block slots hold the cache proper; topk more hold the look-ahead copies of the next exec block
-  const int64_t n_slots = (int64_t)g.max_cached_block + g.topk;
+  // max_cached_block slots hold the cache proper; topk more per look-ahead step hold the copies staged ahead
+  const int64_t n_slots = (int64_t)g.max_cached_block + (int64_t)infllm_ctx::kLookDepth * g.topk;
   INFLLM_CUDA_OK(cudaMalloc(&c->cache, n_slots * c->unit_bytes));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, n_slots * c->unit_bytes, s));
   c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.reserved[0] & 1);
@@ -357,9 +431,8 @@ int ensure_tokens(infllm_ctx* c, int64_t add, cudaStream_t s) {
                                      tb.cap * sizeof(float), live * sizeof(float), H, cudaMemcpyDeviceToDevice, s));
   }
   if (tb.cap > 0) {
-    // offloads still reading the old buffers run on the copy stream
-    INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
-    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
+    // the packing kernels of sealed units read the old buffers on the device-to-host stream
+    if (c->d2h_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_d2h, 0));
     INFLLM_TRY(free_buffers(tb, s));
   }
   c->tb = nb;
@@ -421,67 +494,104 @@ int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaS
   INFLLM_TRY(ensure_scores(c, n, s));
   {
     ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
-    // the ids land directly in pinned host memory (device-visible under unified addressing)
     INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
-                                 g.topk, 0, c->h_topk, nullptr, g.dtype, s));
+                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s));
   }
+  INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
   INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));  // the ids decide the cache plan (context_manager.py:163)
   ids->assign(c->h_topk, c->h_topk + g.topk);
   return INFLLM_OK;
 }
 
-// look-ahead for the NEXT exec block, on the second stream: top-k over the units sealed so far
-int lookahead_launch(infllm_ctx* c, int eb_next, int64_t* n_spec, cudaStream_t s) {
+// look-ahead for a LATER exec block of the call, on the second stream: top-k over the units sealed so far
+int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   const infllm_config& g = c->cfg;
-  *n_spec = c->num_blocks;
-  if (*n_spec <= g.topk) return INFLLM_OK;  // every known unit is a candidate; nothing to rank
-  INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));  // representative keys and query means are ordered on s
+  infllm_ctx::LookAhead& la = c->la[target % (infllm_ctx::kLookDepth + 1)];
+  la.target = target;
+  la.launched = true;
+  la.staged = false;
+  la.n_spec = c->num_blocks;
+  la.ids.clear();
+  if (la.n_spec <= g.topk) return INFLLM_OK;  // every known unit is a candidate; nothing to rank
+  // ev_seal was recorded on s right after the last sealing (or after the query means at the start of the
+  // call): the look-ahead needs nothing that s enqueued later, in particular not the rest of the score pass
   INFLLM_CUDA_OK(cudaStreamWaitEvent(c->aux_stream, c->ev_seal, 0));
-  if (*n_spec > c->scores_aux_cap) {
+  if (la.n_spec > c->scores_aux_cap) {
     int64_t cap = std::max<int64_t>(1024, c->scores_aux_cap);
-    while (cap < *n_spec) cap *= 2;
+    while (cap < la.n_spec) cap *= 2;
     if (c->scores_aux) INFLLM_CUDA_OK(cudaFreeAsync(c->scores_aux, c->aux_stream));
     INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->scores_aux, cap * sizeof(float), c->aux_stream));
     c->scores_aux_cap = cap;
   }
-  ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)*n_spec * c->width * c->esz);
-  INFLLM_TRY(block_topk_launch(c->block_k, *n_spec, (int)c->width, c->qbar + (int64_t)eb_next * c->width,
-                               c->scores_aux, g.topk, 0, c->h_spec, nullptr, g.dtype, c->aux_stream));
+  trace_mark(c, c->aux_stream, TR_SPEC_BEGIN, target);
+  ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)la.n_spec * c->width * c->esz);
+  int32_t* d_ids = c->d_spec + (target % (infllm_ctx::kLookDepth + 1)) * std::max(1, g.topk);
+  INFLLM_TRY(block_topk_launch(c->block_k, la.n_spec, (int)c->width, c->qbar + target * c->width, c->scores_aux,
+                               g.topk, 0, d_ids, nullptr, g.dtype, c->aux_stream));
+  INFLLM_CUDA_OK(cudaMemcpyAsync(la.h_ids, d_ids, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->aux_stream));
+  trace_mark(c, c->aux_stream, TR_SPEC_END, target);
+  INFLLM_CUDA_OK(cudaEventRecord(la.ev, c->aux_stream));
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_spec, c->aux_stream));
   c->spec_recorded = true;
   return INFLLM_OK;
 }
 
 // after the look-ahead ids arrived: copy the ones that are not resident into spare slots (side stream)
-int lookahead_stage(infllm_ctx* c, int64_t n_spec, std::vector<int32_t>* spec_ids) {
+int lookahead_stage(infllm_ctx* c, int64_t target) {
   const infllm_config& g = c->cfg;
-  spec_ids->clear();
-  if (n_spec <= g.topk) {
-    for (int64_t b = 0; b < n_spec; ++b) spec_ids->push_back((int32_t)b);
+  infllm_ctx::LookAhead& la = c->la[target % (infllm_ctx::kLookDepth + 1)];
+  if (la.n_spec <= g.topk) {
+    for (int64_t b = 0; b < la.n_spec; ++b) la.ids.push_back((int32_t)b);
   } else {
-    INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_spec));
-    spec_ids->assign(c->h_spec, c->h_spec + g.topk);
+    INFLLM_CUDA_OK(cudaEventSynchronize(la.ev));
+    la.ids.assign(la.h_ids, la.h_ids + g.topk);
   }
-  for (int32_t b : *spec_ids) {
-    if (c->slot_of.count(b) || c->staged.count(b)) continue;
+  la.staged = true;
+  trace_mark(c, c->copy_stream, TR_STAGE_BEGIN, target);
+  std::vector<const void*> src;
+  std::vector<void*> dst;
+  for (int32_t b : la.ids) {
+    if (c->slot_of.count(b)) continue;
+    auto sf = c->staged_for.find(b);
+    if (sf != c->staged_for.end()) {  // already on its way for an earlier exec block: keep it until this one
+      sf->second = std::max(sf->second, target);
+      continue;
+    }
     if (c->free_slots.empty()) break;  // no spare slot: the unit is fetched at plan time instead
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->staged[b] = slot;
-    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
-                                   cudaMemcpyHostToDevice, c->copy_stream));
+    c->staged_for[b] = target;
+    if (b >= c->d2h_synced_upto) {  // sealed recently: its copy-out must land in the store first
+      INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
+      c->d2h_synced_upto = c->num_blocks;
+    }
+    src.push_back(c->host_unit(b));
+    dst.push_back((char*)c->cache + (int64_t)slot * c->unit_bytes);
     c->counters.h2d_bytes += c->unit_bytes;
     c->staged_pending = true;
   }
+  if (!src.empty()) {
+    if (!(g.reserved[0] & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
+                                 // SM copy kernel, which is faster alone but slows concurrent attention down
+      for (size_t i = 0; i < src.size(); ++i)
+        INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    } else {
+      INFLLM_TRY(stage_units_launch(src.data(), dst.data(), (int)src.size(), c->unit_bytes, c->copy_stream));
+    }
+  }
   if (c->staged_pending) INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+  trace_mark(c, c->copy_stream, TR_STAGE_END, target);
   return INFLLM_OK;
 }
 
 // score the candidates of the next exec block (look-ahead ids + units sealed since) on s; results to pinned memory
-int candidates_launch(infllm_ctx* c, int eb_next, int64_t n_spec, const std::vector<int32_t>& spec_ids, int* n_cand,
-                      cudaStream_t s) {
+int candidates_launch(infllm_ctx* c, int64_t eb_next, int* n_cand, cudaStream_t s) {
   const infllm_config& g = c->cfg;
+  const infllm_ctx::LookAhead& la = c->la[eb_next % (infllm_ctx::kLookDepth + 1)];
+  const int64_t n_spec = la.n_spec;
+  const std::vector<int32_t>& spec_ids = la.ids;
   const int64_t n_now = c->num_blocks;
   *n_cand = 0;
   if (n_now <= g.topk) return INFLLM_OK;  // all units, in id order, no scoring (context_manager.py:370-371)
@@ -491,8 +601,13 @@ int candidates_launch(infllm_ctx* c, int eb_next, int64_t n_spec, const std::vec
   if ((int64_t)spec_ids.size() + (n_now - n_spec) > c->cand_cap)
     return fail(INFLLM_E_CAPACITY, "look-ahead: %lld candidates exceed %d", (long long)(spec_ids.size() + n_now - n_spec), c->cand_cap);
   INFLLM_TRY(block_score_rows_launch(c->block_k, c->h_cand_rows, n, (int)c->width,
-                                     c->qbar + (int64_t)eb_next * c->width, c->h_cand_scores, g.dtype, s));
-  INFLLM_CUDA_OK(cudaEventRecord(c->ev_cand, s));
+                                     c->qbar + eb_next * c->width, c->d_cand_scores, g.dtype, s));
+  // the scores travel to the host on their own stream so that the main stream goes straight on
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
+  INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
+  INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_cand_scores, c->d_cand_scores, n * sizeof(float), cudaMemcpyDeviceToHost,
+                                 c->mail_stream));
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_cand, c->mail_stream));
   *n_cand = n;
   return INFLLM_OK;
 }
@@ -519,7 +634,7 @@ int candidates_finish(infllm_ctx* c, int n_cand, std::vector<int32_t>* ids) {
 }
 
 // cache plan for `ids` (LRU eviction, stamps), adoption of staged copies, late fetches; s waits for the copies
-int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, cudaStream_t s) {
+int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, cudaStream_t s) {
   const infllm_config& g = c->cfg;
   std::vector<int32_t> evicted;
   c->lru.plan(ids.data(), (int)ids.size(), &evicted);
@@ -548,6 +663,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, cudaStream_t
     if (st != c->staged.end()) {  // the look-ahead already brought it in
       c->slot_of[b] = st->second;
       c->staged.erase(st);
+      c->staged_for.erase(b);
       adopted = true;
       continue;
     }
@@ -559,6 +675,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, cudaStream_t
       for (auto it2 = c->staged.begin(); it2 != c->staged.end(); ++it2)
         if (std::find(ids.begin(), ids.end(), it2->first) == ids.end()) { victim = it2; break; }
       c->free_slots.push_back(victim->second);
+      c->staged_for.erase(victim->first);
       c->staged.erase(victim);
     }
     if (!late) {
@@ -569,21 +686,32 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, cudaStream_t
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[b] = slot;
+    if (b >= c->d2h_synced_upto) {
+      INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
+      c->d2h_synced_upto = c->num_blocks;
+    }
     INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
                                    cudaMemcpyHostToDevice, c->copy_stream));
     c->counters.h2d_bytes += c->unit_bytes;
   }
   // look-ahead copies that were not wanted: their slots go back to the pool (later copies into them are
   // ordered behind the unfinished ones on the side stream; no kernel reads them)
-  for (auto& kv : c->staged) c->free_slots.push_back(kv.second);
-  c->staged.clear();
+  for (auto it = c->staged.begin(); it != c->staged.end();) {
+    if (c->staged_for[it->first] <= eb) {  // staged for this exec block (or an earlier one) and not taken
+      c->free_slots.push_back(it->second);
+      c->staged_for.erase(it->first);
+      it = c->staged.erase(it);
+    } else {
+      ++it;
+    }
+  }
   if (late) {
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
   } else if (adopted && c->staged_pending) {
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_stage, 0));
   }
-  c->staged_pending = false;
+  if (c->staged.empty()) c->staged_pending = false;
   return INFLLM_OK;
 }
 
@@ -633,21 +761,43 @@ int seal_apply(infllm_ctx* c, const SealPlan& sp, cudaStream_t s) {
   INFLLM_TRY(repr_select_launch(tb.k_raw, tb.cap * D, D, tb.score, tb.cap, c->frontier - tb.t0, n_new, (int)bs,
                                 g.repr_topk, g.n_heads, g.n_kv_heads, (int)D,
                                 (char*)c->block_k + c->num_blocks * c->width * c->esz, g.dtype, s));
-  // offload to the host store on the side stream (MemoryUnit.__init__, context_manager.py:39-45)
-  INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
-  INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_main, 0));
-  for (int i = 0; i < n_new; ++i) {
-    const int64_t b = c->num_blocks + i;
-    const int64_t src = (c->frontier + i * bs - tb.t0) * D * c->esz;
-    char* hu = c->host_unit(b);
-    INFLLM_CUDA_OK(cudaMemcpy2DAsync(hu, bs * D * c->esz, (char*)tb.k_raw + src, tb.cap * D * c->esz, bs * D * c->esz,
-                                     HKV, cudaMemcpyDeviceToHost, c->copy_stream));
-    INFLLM_CUDA_OK(cudaMemcpy2DAsync(hu + c->unit_bytes / 2, bs * D * c->esz, (char*)tb.v + src, tb.cap * D * c->esz,
-                                     bs * D * c->esz, HKV, cudaMemcpyDeviceToHost, c->copy_stream));
-    c->counters.d2h_bytes += c->unit_bytes;
-  }
+  trace_mark(c, s, TR_REPR_END, c->num_blocks);
   c->num_blocks += n_new;
   c->frontier += n_new * bs;
+  return INFLLM_OK;
+}
+
+// second half of sealing: the new units' K/V go to the host store.  `first` is the id of the first new unit,
+// `tok0` its first token (absolute); called after the units were counted in.
+int seal_offload(infllm_ctx* c, int64_t first, int n_new, int64_t tok0, cudaStream_t s) {
+  if (n_new <= 0) return INFLLM_OK;
+  const infllm_config& g = c->cfg;
+  TokenBuffers& tb = c->tb;
+  const int64_t D = g.head_dim, HKV = g.n_kv_heads, bs = g.block_size;
+  // offload to the host store (MemoryUnit.__init__, context_manager.py:39-45), entirely on the device-to-host
+  // stream: pack the new units into the store's layout, then one copy per run of units.  The tokens were
+  // final when they were ingested; ev_ingest orders the packing behind that.
+  INFLLM_CUDA_OK(cudaStreamWaitEvent(c->d2h_stream, c->ev_ingest, 0));
+  for (int done = 0; done < n_new;) {
+    const int n = std::min(n_new - done, c->pack_units);
+    const int r = c->pack_idx;
+    c->pack_idx ^= 1;
+    INFLLM_TRY(pack_units_launch(tb.k_raw, tb.v, tb.cap * D, tok0 + (int64_t)done * bs - tb.t0, n, (int)bs, (int)HKV,
+                                 (int)D, c->pack_buf[r], c->d2h_stream));
+    for (int i = 0; i < n;) {  // runs that stay inside one slab of the store are contiguous on the host
+      const int64_t b0 = first + done + i;
+      const int run = (int)std::min<int64_t>(n - i, c->slab_units - b0 % c->slab_units);
+      INFLLM_CUDA_OK(cudaMemcpyAsync(c->host_unit(b0), (char*)c->pack_buf[r] + (int64_t)i * c->unit_bytes,
+                                     (int64_t)run * c->unit_bytes, cudaMemcpyDeviceToHost, c->d2h_stream));
+      i += run;
+    }
+    c->counters.d2h_bytes += (int64_t)n * c->unit_bytes;
+    done += n;
+  }
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_d2h, c->d2h_stream));
+  c->d2h_recorded = true;
+  trace_mark(c, c->d2h_stream, TR_PACK_END, first);
+  (void)s;
   return INFLLM_OK;
 }
 
@@ -661,7 +811,7 @@ int local_scores(infllm_ctx* c, cudaStream_t s, int64_t st, int64_t ks, int64_t 
   const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
   const int64_t n = j_end - j_begin, tok = ks - tb.t0 + j_begin, off = (lk - lq) - j_begin;
   ProfScope ps(c, s, INFLLM_PROF_COLSUM, work);
-  if (c->use_tc && lq > 64)
+  if (c->use_tc && lq > 64 && H / HKV <= 8)
     return colsum_tc_launch_maps(c->m_qloc, c->m_krot, (int)st, (int)tok, (int)H, (int)HKV, lq, n, INFLLM_MASK_WINDOW,
                                  off, g.n_local, c->lse, tb.score + tok, tb.cap, 1, g.dtype, s);
   return attn_colsum_launch((const char*)c->q_loc + st * D * c->esz, c->sub_max * D, D,
@@ -684,6 +834,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
   const int64_t at = T - tb.t0;
   INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
   INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
   INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
   if (c->use_tc) {
     // a 128-row tile that ends the window may reach past the last ingested token: keep those rows finite
@@ -715,7 +866,9 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
                                g.n_local - 1, 0, g.dtype, s));
   INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
 
-  std::vector<int32_t> ids, spec_ids;
+  std::vector<int32_t> ids;
+  for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));
   std::vector<KvSeg> gsegs;
   int eb = 0, n_cand = 0;
   bool have_ids = false;  // the ids of this exec block were already ranked at the end of the previous one
@@ -723,12 +876,27 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     const int64_t ed = std::min<int64_t>(st + g.exc_block_size, L);
     const int64_t S = T + st, E = T + ed, lq = ed - st;
     const int64_t ks = std::max<int64_t>(S - g.n_local, 0), lk = E - ks;  // local keys [ks, E) (:772-773)
-    if (!have_ids) INFLLM_TRY(retrieve_now(c, eb, &ids, s));
-    INFLLM_TRY(plan_and_refill(c, ids, s));
+    if (!have_ids) {
+      HostTimer ht(&c->host_us[0]);
+      INFLLM_TRY(retrieve_now(c, eb, &ids, s));
+    }
+    {
+      HostTimer ht(&c->host_us[1]);
+      INFLLM_TRY(plan_and_refill(c, ids, eb, s));
+    }
     c->trace_topk.push_back(ids);
     const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
-    int64_t n_spec = 0;
-    if (more) INFLLM_TRY(lookahead_launch(c, eb + 1, &n_spec, s));
+    const int64_t n_eb = (L + g.exc_block_size - 1) / g.exc_block_size;
+    if (more) {
+      HostTimer ht(&c->host_us[2]);
+      for (int d = 1; d <= infllm_ctx::kLookDepth; ++d) {
+        const int64_t tgt = eb + d;
+        infllm_ctx::LookAhead& la = c->la[tgt % (infllm_ctx::kLookDepth + 1)];
+        if (tgt < n_eb && !(la.launched && la.target == tgt)) INFLLM_TRY(lookahead_launch(c, tgt, s));
+      }
+    }
+    HostTimer* ht_attn = new HostTimer(&c->host_us[3]);
+    trace_mark(c, s, TR_ATTN_BEGIN, eb);
     const int64_t ovf = std::max<int64_t>(E - c->frontier - g.n_local, 0);  // :391
     // global key segments: retrieved units (in place in their cache slots), sink, overflow
     gsegs.clear();
@@ -853,6 +1021,8 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     }
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
     c->attn_recorded = true;
+    delete ht_attn;
+    trace_mark(c, s, TR_ATTN_END, eb);
     const SealPlan sp = plan_seal(c, E);
     // accumulated local score of every window key (context_manager.py:488, 623-625).  Sealing only needs
     // the scores of the tokens it is about to seal, so their 128-key tiles go first; the rest of the
@@ -864,12 +1034,29 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       if (!more) j_u = lk;  // nothing to overlap with: one launch
       INFLLM_TRY(local_scores(c, s, st, ks, lq, lk, 0, j_u, local_pairs_eb));
     }
-    if (more) INFLLM_TRY(lookahead_stage(c, n_spec, &spec_ids));
-    INFLLM_TRY(seal_apply(c, sp, s));
-    if (more) INFLLM_TRY(candidates_launch(c, eb + 1, n_spec, spec_ids, &n_cand, s));
+    trace_mark(c, s, TR_URGENT_END, eb);
+    if (more) {
+      HostTimer ht(&c->host_us[4]);
+      for (int d = 1; d <= infllm_ctx::kLookDepth; ++d) {
+        const int64_t tgt = eb + d;
+        infllm_ctx::LookAhead& la = c->la[tgt % (infllm_ctx::kLookDepth + 1)];
+        if (tgt < n_eb && la.launched && la.target == tgt && !la.staged) INFLLM_TRY(lookahead_stage(c, tgt));
+      }
+    }
+    const int64_t first_new = c->num_blocks, tok_new = c->frontier + sp.take;
+    {
+      HostTimer ht(&c->host_us[5]);
+      INFLLM_TRY(seal_apply(c, sp, s));
+      if (more) INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));
+    }
+    if (more) INFLLM_TRY(candidates_launch(c, eb + 1, &n_cand, s));
+    trace_mark(c, s, TR_SEAL_END, eb);
+    INFLLM_TRY(seal_offload(c, first_new, sp.n_new, tok_new, s));  // off the ranking's critical path
     if (!decode_path) INFLLM_TRY(local_scores(c, s, st, ks, lq, lk, j_u, lk, 0.0));
+    trace_mark(c, s, TR_REST_END, eb);
     have_ids = false;
     if (more) {
+      HostTimer ht(&c->host_us[6]);
       INFLLM_TRY(candidates_finish(c, n_cand, &ids));
       have_ids = true;
     }
@@ -919,7 +1106,12 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
     INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->copy_stream));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->aux_stream));
+    INFLLM_CUDA_OK(cudaStreamSynchronize(c->d2h_stream));
+    INFLLM_CUDA_OK(cudaStreamSynchronize(c->mail_stream));
   }
+  c->d2h_synced_upto = 0;
+  c->d2h_recorded = false;
+  c->pack_used[0] = c->pack_used[1] = false;
   c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
   c->init_full = false;
   c->rope_origin = -1;
@@ -927,8 +1119,10 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->lru.clear();
   c->slot_of.clear();
   c->free_slots.clear();
-  for (int i = c->cfg.max_cached_block + c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
+  for (int i = c->cfg.max_cached_block + infllm_ctx::kLookDepth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->staged.clear();
+  c->staged_for.clear();
+  for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
   c->staged_pending = false;
   c->trace_topk.clear();
   c->attn_recorded = false;
@@ -951,10 +1145,24 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     if (c->scores) cudaFreeAsync(c->scores, nullptr);
     if (c->h_topk) cudaFreeHost(c->h_topk);
     if (c->h_spec) cudaFreeHost(c->h_spec);
+    for (auto& l : c->la) {
+      if (l.h_ids) cudaFreeHost(l.h_ids);
+      if (l.ev) cudaEventDestroy(l.ev);
+    }
     if (c->h_cand_rows) cudaFreeHost(c->h_cand_rows);
     if (c->h_cand_scores) cudaFreeHost(c->h_cand_scores);
     if (c->scores_aux) cudaFreeAsync(c->scores_aux, nullptr);
     cudaStreamDestroy(c->aux_stream);
+    cudaStreamDestroy(c->mail_stream);
+    if (c->d_cand_scores) cudaFree(c->d_cand_scores);
+    if (c->d_spec) cudaFree(c->d_spec);
+    cudaStreamDestroy(c->d2h_stream);
+    cudaEventDestroy(c->ev_d2h);
+    cudaEventDestroy(c->ev_ingest);
+    for (int i = 0; i < 2; ++i) {
+      if (c->pack_buf[i]) cudaFree(c->pack_buf[i]);
+      if (c->ev_pack[i]) cudaEventDestroy(c->ev_pack[i]);
+    }
     cudaEventDestroy(c->ev_spec);
     cudaEventDestroy(c->ev_cand);
     cudaEventDestroy(c->ev_seal);
@@ -1036,6 +1244,44 @@ extern "C" int infllm_ctx_get_profile(infllm_ctx* c, double* ms, double* work, i
   return INFLLM_OK;
 }
 
+extern "C" int infllm_ctx_trace(infllm_ctx* c, int enable) {
+  if (!c) return fail(INFLLM_E_BADARG, "ctx_trace: null context");
+  c->trace_on = enable != 0;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_trace(infllm_ctx* c, int32_t* labels, int64_t* ebs, float* ms, int cap, int* n) {
+  if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_trace: null pointer");
+  int k = 0;
+  if (!c->marks.empty()) {
+    INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+    INFLLM_CUDA_OK(cudaDeviceSynchronize());
+    for (auto& m : c->marks) {
+      if (k < cap && labels && ebs && ms) {
+        float t = 0.f;
+        cudaEventElapsedTime(&t, c->marks[0].ev, m.ev);
+        labels[k] = m.label;
+        ebs[k] = m.eb;
+        ms[k] = t;
+        ++k;
+      }
+    }
+    for (auto& m : c->marks) cudaEventDestroy(m.ev);
+    c->marks.clear();
+  }
+  *n = k;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_get_host_timers(infllm_ctx* c, double* us) {
+  if (!c || !us) return fail(INFLLM_E_BADARG, "ctx_get_host_timers: null pointer");
+  for (int i = 0; i < INFLLM_HOST_TIMERS; ++i) {
+    us[i] = c->host_us[i];
+    c->host_us[i] = 0;
+  }
+  return INFLLM_OK;
+}
+
 extern "C" int infllm_ctx_get_cached(infllm_ctx* c, int32_t* h_ids, double* h_stamps, int cap, int* n) {
   if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_cached: null pointer");
   int i = 0;
@@ -1094,6 +1340,7 @@ extern "C" int infllm_ctx_load_synthetic(infllm_ctx* c, int64_t n_units, const v
   c->init_len = g.n_init;
   c->init_full = true;
   c->num_blocks = n_units;
+  c->d2h_synced_upto = n_units;  // written into the store by the host just above
   c->frontier = g.n_init + n_units * (int64_t)g.block_size;
   c->length = c->frontier;
   // the local window enters through the ordinary ingest path, without queries: tokens only

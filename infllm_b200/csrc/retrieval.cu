@@ -2,7 +2,7 @@
 //
 // block_score_kernel  HBM-streaming GEMV (one warp per representative-key row, 16-byte loads,
 //                     query mean staged in shared memory, fp32 accumulation).
-// topk_argmax_kernel  k <= 64 over <= 8192 scores: k rounds of a CTA-wide arg-max on register-resident scores.
+// topk_argmax_kernel  k <= 64 over <= 8192 scores: per-thread register sort, per-warp pops, one final warp merge.
 // topk_select_kernel  any size: 4-pass 8-bit radix select of the k-th largest score, then an
 //                     index-ordered gather of the winners and a rank sort.  Both: descending score,
 //                     ties to the lower id.
@@ -13,6 +13,7 @@
 namespace infllm {
 
 constexpr int kScoreWarps = 8;
+constexpr int kMaxScoreRows = 512;  // candidate rows per launch of block_score_rows_kernel
 
 template <typename T>
 __global__ void __launch_bounds__(kScoreWarps * 32)
@@ -47,12 +48,16 @@ block_score_kernel(const T* __restrict__ bk, int64_t n, int width, const float* 
   if (lane == 0) scores[row] = acc;
 }
 
-// the same dot product for a short list of rows: scores[i] = <bk[rows[i], :], qbar>.  `rows` and `scores` may
-// live in pinned host memory (the list is a few dozen entries; the host reads the scores after an event)
+// the same dot product for a short list of rows: scores[i] = <bk[rows[i], :], qbar>.  The list travels in the
+// kernel parameters; `scores` may live in pinned host memory (the host reads it after an event).
+struct RowList {
+  int32_t rows[kMaxScoreRows];
+};
 template <typename T>
 __global__ void __launch_bounds__(kScoreWarps * 32)
-block_score_rows_kernel(const T* __restrict__ bk, const int32_t* __restrict__ rows, int n, int width,
+block_score_rows_kernel(const T* __restrict__ bk, const __grid_constant__ RowList list, int n, int width,
                         const float* __restrict__ qbar, float* __restrict__ scores) {
+  const int32_t* rows = list.rows;
   extern __shared__ float sq[];
   for (int i = threadIdx.x; i < width; i += blockDim.x) sq[i] = qbar[i];
   __syncthreads();
@@ -199,74 +204,95 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
   }
 }
 
-// Small k (the usual topk of 16-64) over at most 8192 scores: k rounds of a CTA-wide arg-max.  Every thread
-// keeps its strided scores in registers; a round is two warp reductions and two barriers.  Same order
-// as topk_select_kernel: descending score, ties to the lower id.
+// Small k (the usual topk of 16-64) over at most 8192 scores, one CTA of 32 warps.  Every thread sorts its 8
+// strided scores in registers; every warp then pops its k best by repeatedly taking the best of the 32 lane
+// heads (warp shuffles only); finally warp 0 pops the k best of the 32 sorted warp lists.  No CTA-wide
+// barrier inside the loops.  Order: descending score, ties to the lower id (NaN scores rank last).
 constexpr int kArgmaxItems = 8;
+struct ScoreId {
+  float v;
+  int i;
+};
+__device__ __forceinline__ bool before(float av, int ai, float bv, int bi) {
+  return av > bv || (av == bv && ai < bi);
+}
 __global__ void __launch_bounds__(kTopkThreads)
 topk_argmax_kernel(const float* __restrict__ scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
                    float* __restrict__ out_scores) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  __shared__ int s_win;
+  extern __shared__ unsigned char dyn[];
+  float* cv = reinterpret_cast<float*>(dyn);           // [32 warps][k] values
+  int* ci = reinterpret_cast<int*>(cv + 32 * k);        // [32 warps][k] ids
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float v[kArgmaxItems];
+  int id[kArgmaxItems];
 #pragma unroll
   for (int e = 0; e < kArgmaxItems; ++e) {
     int i = tid + e * kTopkThreads;
-    v[e] = i < n ? scores[i] : -INFINITY;
+    float x = i < n ? scores[i] : -INFINITY;
+    v[e] = (x == x) ? x : -INFINITY;
+    id[e] = i < n ? i : 0x7fffffff;
   }
-  // NaN scores never win; -inf scores can, after everything finite (ids ascending)
-  unsigned taken = 0;
+  // odd-even transposition sort of the 8 register pairs, best first
 #pragma unroll
-  for (int e = 0; e < kArgmaxItems; ++e)
-    if (tid + e * kTopkThreads >= n || v[e] != v[e]) taken |= 1u << e;
-  for (int r = 0; r < k; ++r) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
+  for (int pass = 0; pass < kArgmaxItems; ++pass) {
 #pragma unroll
-    for (int e = 0; e < kArgmaxItems; ++e) {
-      int i = tid + e * kTopkThreads;
-      if (!(taken >> e & 1) && (v[e] > bv || (v[e] == bv && i < bi))) {
-        bv = v[e];
-        bi = i;
+    for (int e = pass & 1; e + 1 < kArgmaxItems; e += 2) {
+      if (before(v[e + 1], id[e + 1], v[e], id[e])) {
+        float tv = v[e]; v[e] = v[e + 1]; v[e + 1] = tv;
+        int ti = id[e]; id[e] = id[e + 1]; id[e + 1] = ti;
       }
     }
+  }
+  // the warp's k best: pop the best lane head k times
+  for (int r = 0; r < k; ++r) {
+    float bv = v[0];
+    int bi = id[0];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
+      if (before(ov, oi, bv, bi)) {
         bv = ov;
         bi = oi;
       }
     }
     if (lane == 0) {
-      sv[warp] = bv;
-      si[warp] = bi;
+      cv[warp * k + r] = bv;
+      ci[warp * k + r] = bi;
     }
-    __syncthreads();
-    if (warp == 0) {
-      bv = sv[lane];
-      bi = si[lane];
+    if (id[0] == bi && bi != 0x7fffffff) {  // this lane owned the winner: shift its list up
+#pragma unroll
+      for (int e = 0; e + 1 < kArgmaxItems; ++e) {
+        v[e] = v[e + 1];
+        id[e] = id[e + 1];
+      }
+      v[kArgmaxItems - 1] = -INFINITY;
+      id[kArgmaxItems - 1] = 0x7fffffff;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int head = 0;  // lane l walks warp l's sorted list
+    for (int r = 0; r < k; ++r) {
+      float hv = head < k ? cv[lane * k + head] : -INFINITY;
+      int hi = head < k ? ci[lane * k + head] : 0x7fffffff;
+      float bv = hv;
+      int bi = hi;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
+        if (before(ov, oi, bv, bi)) {
           bv = ov;
           bi = oi;
         }
       }
+      if (hi == bi && bi != 0x7fffffff) ++head;
       if (lane == 0) {
-        s_win = bi;
         out_ids[r] = (bi == 0x7fffffff ? 0 : bi) + id_base;
         if (out_scores) out_scores[r] = bv;
       }
     }
-    __syncthreads();
-    const int w = s_win;
-    if (w != 0x7fffffff && (w % kTopkThreads) == tid) taken |= 1u << (w / kTopkThreads);
   }
 }
 
@@ -341,7 +367,7 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
   });
   INFLLM_LAUNCH_OK("block_score_kernel");
   if (k <= 64 && n <= (int64_t)kArgmaxItems * kTopkThreads) {
-    topk_argmax_kernel<<<1, kTopkThreads, 0, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
+    topk_argmax_kernel<<<1, kTopkThreads, 32 * k * 8, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
     INFLLM_LAUNCH_OK("topk_argmax_kernel");
   } else {
     topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
@@ -352,12 +378,16 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
 
 int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
                             int dtype, cudaStream_t s) {
-  if (n <= 0) return INFLLM_OK;
-  INFLLM_DISPATCH_DTYPE(dtype, T, {
-    block_score_rows_kernel<T><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
-        (const T*)bk, rows, n, width, qbar, scores);
-  });
-  INFLLM_LAUNCH_OK("block_score_rows_kernel");
+  for (int done = 0; done < n; done += kMaxScoreRows) {  // `rows` is a host array
+    const int m = n - done < kMaxScoreRows ? n - done : kMaxScoreRows;
+    RowList list;
+    for (int i = 0; i < m; ++i) list.rows[i] = rows[done + i];
+    INFLLM_DISPATCH_DTYPE(dtype, T, {
+      block_score_rows_kernel<T><<<(unsigned)ceil_div(m, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
+          (const T*)bk, list, m, width, qbar, scores + done);
+    });
+    INFLLM_LAUNCH_OK("block_score_rows_kernel");
+  }
   return INFLLM_OK;
 }
 
@@ -397,4 +427,12 @@ extern "C" int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, c
   if (!d_k || !d_score || !d_block_k_out) return fail(INFLLM_E_BADARG, "repr_select: null pointer");
   return repr_select_launch(d_k, k_hs, k_ts, d_score, score_hs, tok0, n_new, block_size, repr_topk, n_heads,
                             n_kv_heads, head_dim, d_block_k_out, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int infllm_block_score_rows(const void* d_block_k, const int32_t* h_rows, int n, int width,
+                                       const float* d_qbar, float* d_scores, int dtype, void* stream) {
+  using namespace infllm;
+  if (!d_block_k || !h_rows || !d_qbar || !d_scores || n < 0) return fail(INFLLM_E_BADARG, "block_score_rows: bad argument");
+  if (width % 8 != 0 || width > 12 * 1024) return fail(INFLLM_E_BADARG, "block_score_rows: width %d", width);
+  return block_score_rows_launch(d_block_k, h_rows, n, width, d_qbar, d_scores, dtype, (cudaStream_t)stream);
 }

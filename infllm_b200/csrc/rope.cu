@@ -2,6 +2,8 @@
 // Follows RotaryEmbeddingESM of the reference (inf_llm/attention/rope.py): half-rotation layout,
 // fp32 tables of angle = (t * scale) * inv_freq, fp32 products added and rounded once to the
 // activation type.  HBM-bound elementwise work: 16-byte loads/stores, one thread per 8+8 elements.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace infllm {
@@ -82,6 +84,74 @@ __global__ void qbar_kernel(const T* __restrict__ q, int64_t q_hs, int64_t q_ts,
   const T* p = q + h * q_hs + d;
   for (int64_t t = st; t < ed; ++t) acc += Act<T>::to_f(p[t * q_ts]);
   qbar[e * qbar_stride + (int64_t)h * head_dim + d] = acc / (float)(ed - st);
+}
+
+// K and V of n_new consecutive units -> the host store's unit layout [unit][K|V][head][token][d], contiguous,
+// so that one device-to-host copy moves all of them
+__global__ void pack_units_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, int64_t hs16, int64_t tok0,
+                                  int n_new, int block_size, int n_kv_heads, int d16, uint4* __restrict__ out) {
+  const int64_t per_head = (int64_t)block_size * d16;  // 16-byte chunks of one head of one unit
+  const int64_t per_half = per_head * n_kv_heads;
+  const int64_t total = 2 * per_half * n_new;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t u = i / (2 * per_half), r = i % (2 * per_half);
+    int is_v = r >= per_half;
+    r -= is_v ? per_half : 0;
+    int64_t hh = r / per_head, w = r % per_head;
+    const uint4* src = (is_v ? v : k) + hh * hs16 + (tok0 + u * block_size) * d16 + w;
+    out[i] = *src;
+  }
+}
+
+int pack_units_launch(const void* k, const void* v, int64_t hs, int64_t tok0, int n_new, int block_size, int n_kv_heads,
+                      int head_dim, void* out, cudaStream_t s) {
+  if (n_new <= 0) return INFLLM_OK;
+  const int64_t total = 2ll * n_new * n_kv_heads * block_size * (head_dim / 8);
+  int blocks = (int)std::min<int64_t>(ceil_div(total, 256), 1184);
+  pack_units_kernel<<<blocks, 256, 0, s>>>((const uint4*)k, (const uint4*)v, hs / 8, tok0, n_new, block_size,
+                                           n_kv_heads, head_dim / 8, (uint4*)out);
+  INFLLM_LAUNCH_OK("pack_units_kernel");
+  return INFLLM_OK;
+}
+
+// Staging copy of whole units from the pinned host store into cache slots by the SMs (the host pointers are
+// device-visible under unified addressing).  Many 512 KiB cudaMemcpyAsync calls reach only about two thirds of
+// the link rate because of their per-copy cost; one kernel that keeps a few hundred KiB of loads in flight
+// does better and costs the host a single launch.
+constexpr int kMaxStageUnits = 64;
+struct StageList {
+  const uint4* src[kMaxStageUnits];
+  uint4* dst[kMaxStageUnits];
+};
+__global__ void __launch_bounds__(512) stage_units_kernel(const __grid_constant__ StageList list, int n16) {
+  // one CTA per unit: few CTAs, so that they land on SMs the attention grid leaves idle, each thread with
+  // eight 16-byte loads in flight (16 units x 512 threads x 128 B = 1 MiB outstanding over the link)
+  const uint4* __restrict__ s = list.src[blockIdx.x];
+  uint4* __restrict__ d = list.dst[blockIdx.x];
+  const int stride = blockDim.x;
+  int i = threadIdx.x;
+  for (; i + 7 * stride < n16; i += 8 * stride) {
+    uint4 r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] = s[i + e * stride];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) d[i + e * stride] = r[e];
+  }
+  for (; i < n16; i += stride) d[i] = s[i];
+}
+
+int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int64_t unit_bytes, cudaStream_t s) {
+  for (int done = 0; done < n; done += kMaxStageUnits) {
+    const int m = n - done < kMaxStageUnits ? n - done : kMaxStageUnits;
+    StageList list;
+    for (int i = 0; i < m; ++i) {
+      list.src[i] = (const uint4*)h_src[done + i];
+      list.dst[i] = (uint4*)d_dst[done + i];
+    }
+    stage_units_kernel<<<m, 512, 0, s>>>(list, (int)(unit_bytes / 16));
+    INFLLM_LAUNCH_OK("stage_units_kernel");
+  }
+  return INFLLM_OK;
 }
 
 int rope_apply_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
