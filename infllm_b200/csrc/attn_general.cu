@@ -550,8 +550,7 @@ extern "C" int infllm_attn_colsum(const void* d_q, int64_t q_hs, int64_t q_ts, c
   INFLLM_TRY(check_rows(d_q, q_hs, q_ts, "attn_colsum q"));
   INFLLM_TRY(check_rows(d_k, k_hs, k_ts, "attn_colsum k"));
   // full 128-row tiles on both sides: the tcgen05 kernel; ragged small shapes: the mma.sync kernel
-  if (head_dim == 128 && lq >= 128 && lk >= 128 && n_heads % n_kv_heads == 0 && n_heads / n_kv_heads <= 8 &&
-      lk < (1ll << 31) && lq < (1ll << 31))
+  if (head_dim == 128 && lq >= 128 && lq <= 512 && lk >= 128 && n_heads % n_kv_heads == 0 && lk < (1ll << 31))
     return colsum_tc_launch(d_q, q_hs, q_ts, d_k, k_hs, k_ts, n_heads, n_kv_heads, lq, lk, mask_mode, mask_offset,
                             mask_size, d_lse, d_score, score_hs, accumulate, dtype, (cudaStream_t)stream);
   return attn_colsum_launch(d_q, q_hs, q_ts, d_k, k_hs, k_ts, n_heads, n_kv_heads, lq, lk, head_dim, mask_mode,

@@ -7,10 +7,11 @@
 //                   owning half of the tile's key columns; row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
 //                   TMEM (two buffers), P goes through shared memory as a K-major operand, O stays in
 //                   TMEM for the whole tile with lazy rescaling; K/V tiles are double buffered.
-// colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes; a CTA keeps one K tile and streams
-//                   every (head of the group, query tile) through a TMA ring and two TMEM buffers; two
+// colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes; a CTA keeps one head's query tiles
+//                   resident and streams a run of key tiles through a TMA ring and four TMEM buffers; four
 //                   threads per key sum exp2(s - lse) over the queries that see it.
 // Every mbarrier wait is bounded; a wait that runs out records an error code and the CTA unwinds.
+#include <algorithm>
 #include <type_traits>
 
 #include "attn_common.cuh"
@@ -56,6 +57,15 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// two exponentials per special-function instruction: exp2 of a pair of fp32 arguments evaluated in fp16
+// (relative error about 5e-4, arguments below -25 give 0), returned as fp32
+__device__ __forceinline__ float2 ex2_pair(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  uint32_t u = *reinterpret_cast<uint32_t*>(&h), r;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(u));
+  return __half22float2(*reinterpret_cast<__half2*>(&r));
 }
 
 // The two threads that share a query row publish a progress counter in shared memory; bounded like every wait.
@@ -434,52 +444,83 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------ column sums
-// One CTA owns 128 keys of one KV head and walks every (query head of the group, visible 128-query tile)
-// pair: K stays in shared memory, the query tiles stream through a two-stage TMA ring, S^T goes to one of two
-// TMEM buffers, and 8 compute warps (two threads per key row, 64 query columns each) turn it into
-// sum_q exp2(s - lse_q) while the next tile is being loaded and multiplied.
+// One CTA owns one query head and a run of 128-key tiles.  The head's query tiles (at most four, 512 queries)
+// and their log-sum-exps stay in shared memory for the whole CTA; the key tiles stream through a two-stage TMA
+// ring; every (key tile, visible query tile) pair is one S^T = K Q^T into one of four TMEM buffers, which 16
+// compute warps (four threads per key row, 32 query columns each) turn into sum_q exp2(s - lse_q).  A key
+// tile is loaded once per head and a query tile once per CTA, which keeps the L2 traffic an order of magnitude
+// below one load per pair.
 namespace colsum_smem {
-constexpr int kStages = 4;                    // query tiles in flight (shared-memory ring and TMEM buffers)
-constexpr int kK = 0;
-constexpr int kQ = kK + 2 * kSubTileBytes;
-constexpr int kLse = kQ + kStages * 2 * kSubTileBytes;  // kStages x 128 fp32
-constexpr int kBar = kLse + kStages * 512;
-constexpr int kAcc = kBar + 128;              // per (head of the group, column quarter, key) partial sums: 8 x 4 x 128 fp32
-constexpr int kTotal = kAcc + 8 * 4 * 128 * 4;
+constexpr int kQTiles = 4;                     // resident query tiles
+constexpr int kMaxKeyTiles = 10;               // key tiles per CTA
+constexpr int kBufs = 4;                       // TMEM accumulators in flight
+constexpr int kQ = 0;
+constexpr int kK = kQ + kQTiles * 2 * kSubTileBytes;   // two stages
+constexpr int kLse = kK + 2 * 2 * kSubTileBytes;       // kQTiles x 128 fp32
+constexpr int kBar = kLse + kQTiles * 512;
+constexpr int kAcc = kBar + 128;               // [key tile][column quarter][key] partial sums
+constexpr int kTotal = kAcc + kMaxKeyTiles * 4 * 128 * 4;
 }  // namespace colsum_smem
 
+// query tiles [tf, tl] that can see a key of the tile starting at j0 (tl < tf: none)
+__device__ __forceinline__ void colsum_q_tiles(const ColsumTcParams& P, int64_t j0, int keys, int* tf, int* tl) {
+  int64_t lo = 0, hi = P.lq - 1;
+  if (P.mask_mode == INFLLM_MASK_WINDOW) {
+    lo = j0 - P.mask_offset;
+    hi = j0 + keys - 1 - P.mask_offset + P.mask_size - 1;
+  } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
+    lo = j0 - P.mask_offset + P.mask_size;
+  }
+  if (lo < 0) lo = 0;
+  if (hi > P.lq - 1) hi = P.lq - 1;
+  if (lo > hi) {
+    *tf = 0;
+    *tl = -1;
+  } else {
+    *tf = (int)(lo / kTile);
+    *tl = (int)(hi / kTile);
+  }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(576) colsum_tc_kernel(const __grid_constant__ ColsumTcParams P) {
+__global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant__ ColsumTcParams P) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t sK = s_base + colsum_smem::kK, sQ = s_base + colsum_smem::kQ;
+  const uint32_t sQ = s_base + colsum_smem::kQ, sK = s_base + colsum_smem::kK;
+  float* s_lse = reinterpret_cast<float*>(smem + colsum_smem::kLse);
+  float* s_acc = reinterpret_cast<float*>(smem + colsum_smem::kAcc);
   const uint32_t bars = s_base + colsum_smem::kBar;
-  // barriers: 0 k_full, then q_full[NS], s_full[NS], free[NS]
-  constexpr int NS = colsum_smem::kStages;
-  constexpr int QF = 1, SF = 1 + NS, FR = 1 + 2 * NS;
+  constexpr int NB = colsum_smem::kBufs;
+  // barriers: 0 q_full, 1-2 k_full, 3-4 k_free, then s_full[NB], free[NB]
+  constexpr int KF = 1, KE = 3, SF = 5, FR = 5 + NB;
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + colsum_smem::kBar + 112);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + colsum_smem::kBar + 120);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hkv = blockIdx.y;
-  const int64_t j0 = (int64_t)blockIdx.x * kTile;
-  const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+  const int h = blockIdx.y, hkv = h / P.group;
+  const int n_key_tiles = (int)((P.lk + kTile - 1) / kTile);
+  const int kt0 = blockIdx.x * P.tiles_per_cta;
+  const int kt1 = kt0 + P.tiles_per_cta < n_key_tiles ? kt0 + P.tiles_per_cta : n_key_tiles;
   if (threadIdx.x == 0) {
     mbar_init(bar(0), 1);
-    for (int i = 0; i < NS; ++i) {
-      mbar_init(bar(QF + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(KF + i), 1);
+      mbar_init(bar(KE + i), 1);
+    }
+    for (int i = 0; i < NB; ++i) {
       mbar_init(bar(SF + i), 1);
       mbar_init(bar(FR + i), 512);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  float* s_acc = reinterpret_cast<float*>(smem + colsum_smem::kAcc);
-  for (int i = threadIdx.x; i < 8 * 4 * 128; i += blockDim.x) s_acc[i] = 0.f;
+  for (int i = threadIdx.x; i < colsum_smem::kMaxKeyTiles * 4 * 128; i += blockDim.x) s_acc[i] = 0.f;
+  for (int i = threadIdx.x; i < colsum_smem::kQTiles * 128; i += blockDim.x)
+    s_lse[i] = i < P.lq ? P.lse[(int64_t)h * P.lq + i] : INFINITY;
   if (warp == 17) {
-    tmem_alloc(smem_u32(tmem_slot), 128 * NS);
+    tmem_alloc(smem_u32(tmem_slot), 128 * NB);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -489,152 +530,165 @@ __global__ void __launch_bounds__(576) colsum_tc_kernel(const __grid_constant__ 
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t idesc = make_idesc(kBf16, 128, 128, false);
 
-  // query tiles that can see a key of this tile (the same for every head)
-  int64_t qi_lo = 0, qi_hi = P.lq - 1;
-  if (P.mask_mode == INFLLM_MASK_WINDOW) {
-    qi_lo = j0 - P.mask_offset;
-    qi_hi = j0 + keys - 1 - P.mask_offset + P.mask_size - 1;
-  } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
-    qi_lo = j0 - P.mask_offset + P.mask_size;
+  // the query tiles any key tile of this CTA needs
+  int q_first = 1 << 30, q_last = -1;
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int64_t j0 = (int64_t)kt * kTile;
+    const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+    int tf, tl;
+    colsum_q_tiles(P, j0, keys, &tf, &tl);
+    if (tl >= tf) {
+      q_first = tf < q_first ? tf : q_first;
+      q_last = tl > q_last ? tl : q_last;
+    }
   }
-  if (qi_lo < 0) qi_lo = 0;
-  if (qi_hi > P.lq - 1) qi_hi = P.lq - 1;
-  const bool any = qi_lo <= qi_hi;
-  const int t_first = any ? (int)(qi_lo / kTile) : 0, t_last = any ? (int)(qi_hi / kTile) : -1;
-  const int n_t = t_last - t_first + 1, n_it = n_t * P.group;
+  const bool any = q_last >= q_first;
 
   if (warp == 16) {
-    // ================================================================ producer: K once, then the query tiles
-    bool ok = true;
-    if (any && lane == 0) {
-      mbar_expect_tx(bar(0), 2 * kSubTileBytes);
-      tma_load_3d(sK, &P.map_k, bar(0), 0, P.k_tok0 + (int)j0, hkv);
-      tma_load_3d(sK + kSubTileBytes, &P.map_k, bar(0), 64, P.k_tok0 + (int)j0, hkv);
-    }
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int b = it % NS, h = hkv * P.group + it / n_t, t = t_first + it % n_t;
-      if (it >= NS) ok = __all_sync(0xffffffffu, wait_or_abort(bar(FR + b), ((it / NS) - 1) & 1, abort_flag, P.err, 410));
-      if (!ok) break;
-      const int64_t q0 = (int64_t)t * kTile;
-      if (lane == 0) {
-        TC_STAMP(0, it);
-        mbar_expect_tx(bar(QF + b), 2 * kSubTileBytes);
-        tma_load_3d(sQ + b * 2 * kSubTileBytes, &P.map_q, bar(QF + b), 0, P.q_row0 + (int)q0, h);
-        tma_load_3d(sQ + b * 2 * kSubTileBytes + kSubTileBytes, &P.map_q, bar(QF + b), 64, P.q_row0 + (int)q0, h);
+    // ============================================================== producer: query tiles once, then key tiles
+    if (lane == 0 && any) {
+      mbar_expect_tx(bar(0), (uint32_t)(q_last - q_first + 1) * 2 * kSubTileBytes);
+      for (int t = q_first; t <= q_last; ++t) {
+        tma_load_3d(sQ + t * 2 * kSubTileBytes, &P.map_q, bar(0), 0, P.q_row0 + t * kTile, h);
+        tma_load_3d(sQ + t * 2 * kSubTileBytes + kSubTileBytes, &P.map_q, bar(0), 64, P.q_row0 + t * kTile, h);
+      }
+      bool ok = true;
+      int n = 0;  // key tiles with work, in order
+      for (int kt = kt0; kt < kt1 && ok; ++kt) {
+        const int64_t j0 = (int64_t)kt * kTile;
+        const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+        int tf, tl;
+        colsum_q_tiles(P, j0, keys, &tf, &tl);
+        if (tl < tf) continue;
+        const int b = n & 1;
+        if (n >= 2) ok = wait_or_abort(bar(KE + b), ((n >> 1) - 1) & 1, abort_flag, P.err, 410);
+        if (!ok) break;
+        TC_STAMP(0, n);
+        mbar_expect_tx(bar(KF + b), 2 * kSubTileBytes);
+        tma_load_3d(sK + b * 2 * kSubTileBytes, &P.map_k, bar(KF + b), 0, P.k_tok0 + (int)j0, hkv);
+        tma_load_3d(sK + b * 2 * kSubTileBytes + kSubTileBytes, &P.map_k, bar(KF + b), 64, P.k_tok0 + (int)j0, hkv);
+        ++n;
       }
     }
   } else if (warp == 17) {
     // ======================================================================================= MMA issuer
     if (lane == 0 && any) {
       bool ok = wait_or_abort(bar(0), 0, abort_flag, P.err, 411);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int b = it % NS;
-        ok = wait_or_abort(bar(QF + b), (it / NS) & 1, abort_flag, P.err, 412);
-        TC_STAMP(1, it);
-        if (ok && it >= NS) ok = wait_or_abort(bar(FR + b), ((it / NS) - 1) & 1, abort_flag, P.err, 413);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t qt = sQ + b * 2 * kSubTileBytes;
+      int n = 0, step = 0;
+      for (int kt = kt0; kt < kt1 && ok; ++kt) {
+        const int64_t j0 = (int64_t)kt * kTile;
+        const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+        int tf, tl;
+        colsum_q_tiles(P, j0, keys, &tf, &tl);
+        if (tl < tf) continue;
+        const int kb = n & 1;
+        ok = wait_or_abort(bar(KF + kb), (n >> 1) & 1, abort_flag, P.err, 412);
+        TC_STAMP(1, n);
+        const uint32_t kt_s = sK + kb * 2 * kSubTileBytes;
+        for (int t = tf; t <= tl && ok; ++t, ++step) {
+          const int b = step % NB;
+          if (step >= NB) ok = wait_or_abort(bar(FR + b), ((step / NB) - 1) & 1, abort_flag, P.err, 413);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t qt = sQ + t * 2 * kSubTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // S^T = K Q^T: keys are the M rows (TMEM lanes), queries the N columns
-          uint64_t ad = make_sdesc(sK + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-          uint64_t bd = make_sdesc(qt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-          mma_ss(tmem + b * 128, ad, bd, idesc, ks > 0);
+          for (int ks = 0; ks < 8; ++ks) {
+            // S^T = K Q^T: keys are the M rows (TMEM lanes), queries the N columns
+            uint64_t ad = make_sdesc(kt_s + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            uint64_t bd = make_sdesc(qt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+            mma_ss(tmem + b * 128, ad, bd, idesc, ks > 0);
+          }
+          tc_commit(bar(SF + b));
         }
-        tc_commit(bar(SF + b));
-        TC_STAMP(2, it);
+        if (ok) tc_commit(bar(KE + kb));  // every product that reads this key tile has been issued
+        TC_STAMP(2, n);
+        ++n;
       }
     }
   } else {
     // ========================================================================================== compute
     const int quad = warp & 3, part = warp >> 2;
     const int krow = quad * 32 + lane;
-    const int64_t kj = j0 + krow;
     const int col0 = part * 32;
     const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
-    // queries that see this thread's key
-    int64_t vi_lo = 0, vi_hi = P.lq - 1;
-    if (P.mask_mode == INFLLM_MASK_WINDOW) {
-      vi_lo = kj - P.mask_offset;
-      vi_hi = kj - P.mask_offset + P.mask_size - 1;
-    } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
-      vi_lo = kj - P.mask_offset + P.mask_size;
-    }
-    if (vi_lo < 0) vi_lo = 0;
-    if (vi_hi > P.lq - 1) vi_hi = P.lq - 1;
-    if (kj >= P.lk) vi_hi = -1;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int b = it % NS, g = it / n_t, t = t_first + it % n_t;
-      // the log-sum-exps of this thread's 64 query columns: fetched before the wait so that their latency hides
-      float ls[32];
-      {
-        const int64_t qb = (int64_t)t * kTile + col0;
-        const float* lp = P.lse + (int64_t)(hkv * P.group + g) * P.lq + qb;
-        if (qb + 32 <= P.lq && ((uintptr_t)lp & 15) == 0) {
+    int step = 0, n = 0;
+    for (int kt = kt0; kt < kt1 && ok; ++kt) {
+      const int64_t j0 = (int64_t)kt * kTile;
+      const int keys = (int)((P.lk - j0) < kTile ? (P.lk - j0) : kTile);
+      int tf, tl;
+      colsum_q_tiles(P, j0, keys, &tf, &tl);
+      if (tl < tf) continue;
+      // queries that see this thread's key
+      const int64_t kj = j0 + krow;
+      int64_t vi_lo = 0, vi_hi = P.lq - 1;
+      if (P.mask_mode == INFLLM_MASK_WINDOW) {
+        vi_lo = kj - P.mask_offset;
+        vi_hi = kj - P.mask_offset + P.mask_size - 1;
+      } else if (P.mask_mode == INFLLM_MASK_COMPLEMENT) {
+        vi_lo = kj - P.mask_offset + P.mask_size;
+      }
+      if (vi_lo < 0) vi_lo = 0;
+      if (vi_hi > P.lq - 1) vi_hi = P.lq - 1;
+      if (kj >= P.lk) vi_hi = -1;
+      float total = 0.f;
+      for (int t = tf; t <= tl && ok; ++t, ++step) {
+        const int b = step % NB;
+        ok = __all_sync(0xffffffffu, wait_or_abort(bar(SF + b), (step / NB) & 1, abort_flag, P.err, 414));
+        if (!ok) break;
+        if (threadIdx.x == 0) TC_STAMP(3, step);
+        tc_fence_after();
+        float sv[32];
+        tmem_ld32(tmem + b * 128 + lane_base + col0, reinterpret_cast<uint32_t*>(sv));
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar(FR + b));  // the accumulator is in registers: the buffer can be overwritten
+        const int64_t q0 = (int64_t)t * kTile + col0;
+        const int64_t a = vi_lo > q0 ? vi_lo : q0, e = vi_hi < q0 + 31 ? vi_hi : q0 + 31;
+        const int c_lo = (int)(a - q0), c_hi = (int)(e - q0);
+        const float* ls = s_lse + t * kTile + col0;
+        float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (c_lo == 0 && c_hi == 31) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            const float4 l4 = __ldg(reinterpret_cast<const float4*>(lp + c));
-            ls[c] = l4.x; ls[c + 1] = l4.y; ls[c + 2] = l4.z; ls[c + 3] = l4.w;
+            const float4 l4 = *reinterpret_cast<const float4*>(ls + c);
+            const float2 p01 = ex2_pair(fmaf(sv[c], P.scale_log2, -l4.x), fmaf(sv[c + 1], P.scale_log2, -l4.y));
+            const float2 p23 = ex2_pair(fmaf(sv[c + 2], P.scale_log2, -l4.z), fmaf(sv[c + 3], P.scale_log2, -l4.w));
+            acc4[0] += p01.x;
+            acc4[1] += p01.y;
+            acc4[2] += p23.x;
+            acc4[3] += p23.y;
           }
-        } else {
+        } else if (c_lo <= c_hi) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) ls[c] = qb + c < P.lq ? __ldg(lp + c) : INFINITY;
+          for (int c = 0; c < 32; ++c) {
+            const float pv = ex2_approx(fmaf(sv[c], P.scale_log2, -ls[c]));
+            acc4[c & 3] += (c >= c_lo && c <= c_hi) ? pv : 0.f;
+          }
         }
+        // a query row without any visible key has lse = -inf; it cannot see this key either, so it is masked above
+        total += (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+        if (threadIdx.x == 0) TC_STAMP(4, step);
       }
-      ok = __all_sync(0xffffffffu, wait_or_abort(bar(SF + b), (it / NS) & 1, abort_flag, P.err, 414));
-      if (!ok) break;
-      if (threadIdx.x == 0) TC_STAMP(3, it);
-      tc_fence_after();
-      float sv[32];
-      tmem_ld32(tmem + b * 128 + lane_base + col0, reinterpret_cast<uint32_t*>(sv));
-      tmem_wait_ld();
-      const int64_t q0 = (int64_t)t * kTile + col0;
-      const int64_t a = vi_lo > q0 ? vi_lo : q0, e = vi_hi < q0 + 31 ? vi_hi : q0 + 31;
-      const int c_lo = (int)(a - q0), c_hi = (int)(e - q0);
-      float acc4[4] = {0.f, 0.f, 0.f, 0.f};
-      if (c_lo == 0 && c_hi == 31) {
-#pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          acc4[0] += ex2_approx(fmaf(sv[c], P.scale_log2, -ls[c]));
-          acc4[1] += ex2_approx(fmaf(sv[c + 1], P.scale_log2, -ls[c + 1]));
-          acc4[2] += ex2_approx(fmaf(sv[c + 2], P.scale_log2, -ls[c + 2]));
-          acc4[3] += ex2_approx(fmaf(sv[c + 3], P.scale_log2, -ls[c + 3]));
-        }
-      } else if (c_lo <= c_hi) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float pv = ex2_approx(fmaf(sv[c], P.scale_log2, -ls[c]));
-          acc4[c & 3] += (c >= c_lo && c <= c_hi) ? pv : 0.f;
-        }
-      }
-      // a query row without any visible key has lse = -inf; it cannot see this key either, so it is masked above.
-      // Every thread owns one slot per head: no atomics, and the final sum below has a fixed order.
-      s_acc[(g * 4 + part) * 128 + krow] += (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
-      tc_fence_before();
-      mbar_arrive(bar(FR + b));
-      if (threadIdx.x == 0) TC_STAMP(4, it);
+      // every thread owns one slot per key tile: no atomics, and the final sum below has a fixed order
+      s_acc[((kt - kt0) * 4 + part) * 128 + krow] = total;
+      ++n;
     }
+    (void)n;
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x < 128 && !(*abort_flag) && any) {
-    const int64_t kj = j0 + threadIdx.x;
-    if (kj < P.lk) {
-      for (int g = 0; g < P.group; ++g) {
-        const float* sa = s_acc + (g * 4) * 128 + threadIdx.x;
-        const float v = (sa[0] + sa[128]) + (sa[256] + sa[384]);
-        float* dst = P.score + (int64_t)(hkv * P.group + g) * P.score_hs + kj;
-        *dst = P.accumulate ? *dst + v : v;
-      }
+  if (threadIdx.x < 128 && !(*abort_flag)) {
+    for (int kt = kt0; kt < kt1; ++kt) {
+      const int64_t kj = (int64_t)kt * kTile + threadIdx.x;
+      if (kj >= P.lk) break;
+      const float* sa = s_acc + ((kt - kt0) * 4) * 128 + threadIdx.x;
+      const float v = (sa[0] + sa[128]) + (sa[256] + sa[384]);
+      float* dst = P.score + (int64_t)h * P.score_hs + kj;
+      *dst = P.accumulate ? *dst + v : v;
     }
-  } else if (threadIdx.x < 128 && !any && !P.accumulate) {
-    const int64_t kj = j0 + threadIdx.x;
-    if (kj < P.lk)
-      for (int g = 0; g < P.group; ++g) P.score[(int64_t)(hkv * P.group + g) * P.score_hs + kj] = 0.f;
   }
-  if (warp == 17) tmem_dealloc(tmem, 128 * NS);
+  if (warp == 17) tmem_dealloc(tmem, 128 * NB);
 }
 
 // ---------------------------------------------------------------------------------------- host side
@@ -690,9 +744,16 @@ bool tc_rows_ok(const void* base, int64_t hs, int64_t ts) {
 }
 
 int tc_get_error_ptr(int** p) {
-  void* d = nullptr;
-  INFLLM_CUDA_OK(cudaGetSymbolAddress(&d, g_tc_error));
-  *p = (int*)d;
+  static int* cached[64] = {nullptr};  // per device ordinal
+  int dev = 0;
+  INFLLM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(INFLLM_E_UNSUPPORTED, "device ordinal %d", dev);
+  if (!cached[dev]) {
+    void* d = nullptr;
+    INFLLM_CUDA_OK(cudaGetSymbolAddress(&d, g_tc_error));
+    cached[dev] = (int*)d;
+  }
+  *p = cached[dev];
   return INFLLM_OK;
 }
 
@@ -713,6 +774,9 @@ int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, in
                           int n_kv_heads, int64_t lq, int64_t lk, int mask_mode, int64_t mask_offset,
                           int64_t mask_size, const float* lse, float* score, int64_t score_hs, int accumulate,
                           int dtype, cudaStream_t s) {
+  if (lq > colsum_smem::kQTiles * kTile)
+    return fail(INFLLM_E_UNSUPPORTED, "colsum (tensor-core kernel): %lld queries, at most %d", (long long)lq,
+                colsum_smem::kQTiles * kTile);
   ColsumTcParams P{};
   P.map_q = map_q; P.map_k = map_k;
   P.q_row0 = q_row0; P.k_tok0 = k_tok0; P.n_heads = n_heads; P.group = n_heads / n_kv_heads;
@@ -720,12 +784,22 @@ int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, in
   P.mask_offset = mask_offset; P.mask_size = mask_size; P.lse = lse; P.score = score; P.score_hs = score_hs;
   P.scale_log2 = kLog2e / sqrtf(128.f);
   INFLLM_TRY(tc_get_error_ptr(&P.err));
-  if (P.group > 8) return fail(INFLLM_E_UNSUPPORTED, "colsum: %d query heads per kv head (at most 8)", P.group);
-  dim3 grid((unsigned)ceil_div(lk, kTile), n_kv_heads);
+  // one CTA per (head, run of key tiles): about one CTA per SM, never more than kMaxKeyTiles tiles each
+  const int n_tiles = (int)ceil_div(lk, kTile);
+  int chunks = std::max(1, 148 / n_heads);
+  chunks = std::min(chunks, n_tiles);
+  int per = (int)ceil_div(n_tiles, chunks);
+  per = std::min(per, colsum_smem::kMaxKeyTiles);
+  P.tiles_per_cta = per;
+  dim3 grid((unsigned)ceil_div(n_tiles, per), n_heads);
   const size_t smem = colsum_smem::kTotal + 1024;
+  static bool attr_set[2] = {false, false};
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = colsum_tc_kernel<T>;
-    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (!attr_set[dtype]) {
+      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set[dtype] = true;
+    }
     kern<<<grid, 576, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("colsum_tc_kernel");

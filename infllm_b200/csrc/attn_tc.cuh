@@ -39,6 +39,7 @@ struct ColsumTcParams {
   int32_t q_row0, k_tok0, n_heads, group;
   int64_t lq, lk;
   int32_t mask_mode, accumulate;
+  int32_t tiles_per_cta, pad;
   int64_t mask_offset, mask_size;
   const float* lse;
   float* score;

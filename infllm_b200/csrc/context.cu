@@ -811,7 +811,7 @@ int local_scores(infllm_ctx* c, cudaStream_t s, int64_t st, int64_t ks, int64_t 
   const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
   const int64_t n = j_end - j_begin, tok = ks - tb.t0 + j_begin, off = (lk - lq) - j_begin;
   ProfScope ps(c, s, INFLLM_PROF_COLSUM, work);
-  if (c->use_tc && lq > 64 && H / HKV <= 8)
+  if (c->use_tc && lq > 64 && lq <= 512)
     return colsum_tc_launch_maps(c->m_qloc, c->m_krot, (int)st, (int)tok, (int)H, (int)HKV, lq, n, INFLLM_MASK_WINDOW,
                                  off, g.n_local, c->lse, tb.score + tok, tb.cap, 1, g.dtype, s);
   return attn_colsum_launch((const char*)c->q_loc + st * D * c->esz, c->sub_max * D, D,
