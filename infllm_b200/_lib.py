@@ -8,7 +8,7 @@ import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libinfllm_b200.so")
+LIB_PATH = os.environ.get("INFLLM_B200_LIB", os.path.join(_HERE, "libinfllm_b200.so"))  # the override is for instrumented builds
 
 OK, E_BADARG, E_CAPACITY, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_NOMEM = 0, -1, -2, -3, -4, -5, -6
 BF16, FP16 = 0, 1

@@ -75,6 +75,8 @@ class ContextManager:
             cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
         if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":
             cfg.reserved[0] |= 2  # debugging aid: rank every exec block's units on the device, no look-ahead staging
+        if os.environ.get("INFLLM_B200_ATTN_TWO_HEAD", "0") == "1":
+            cfg.reserved[0] |= 8  # experimental: two query heads of a KV head per CTA share every K/V tile
         if os.environ.get("INFLLM_B200_STAGE_KERNEL", "0") == "1":
             cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
         for _ in range(self.num_units):

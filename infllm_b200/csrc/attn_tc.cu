@@ -26,8 +26,8 @@ __device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] block
 #ifdef INFLLM_TC_TIMING
 // development aid: per-iteration clock stamps of CTA (0,0): [role][iteration], roles 0 producer issue, 1 operands
 // arrived, 2 MMA committed, 3 accumulator seen by the compute warps, 4 compute done
-__device__ long long g_tc_stamps[5][256];
-#define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
+__device__ long long g_tc_stamps[10][256];
+#define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
 #else
 #define TC_STAMP(role, it) do { } while (0)
 #endif
@@ -443,6 +443,486 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
   if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------
+// attn_tc2_kernel: two query heads of the same KV head per CTA.
+// The exec-block kernel above is bound by the L2 -> shared-memory traffic of its K/V tiles (64 KB per
+// 8.4 MFLOP).  Here every K/V tile feeds two 128-query tiles (heads 2p and 2p+1 of one KV head, same
+// query rows, hence the same masks and tile list), which halves that traffic; the key tiles of a work
+// item are cut into n_split runs so that the grid still covers the SMs, and the runs' partial results
+// are merged by attn_tc_combine_kernel.  P = exp2(S - m) goes back into the TMEM columns of S as packed
+// 16-bit pairs and is the A operand of the P V product straight from TMEM; exponentials are evaluated
+// two per instruction in fp16.  16 softmax warps (2 heads x 128 rows x 2 column halves), 1 TMA warp,
+// 1 MMA warp.
+namespace tc2 {
+constexpr int kQ = 0;                            // Q of head A, then head B
+constexpr int kK = kQ + 4 * kSubTileBytes;       // two stages
+constexpr int kV = kK + 4 * kSubTileBytes;       // two stages
+constexpr int kBar = kV + 4 * kSubTileBytes;
+constexpr int kXmax = kBar + 256;                // row maxima: 2 heads x 2 tile parities x 2 halves x 128 rows
+constexpr int kXsum = kXmax + 4096;              // row sums: 2 heads x 2 halves x 128 rows
+constexpr int kXflag = kXsum + 2048;             // progress counters: 2 heads x 2 halves x 128 rows
+constexpr int kTotal = kXflag + 2048;
+enum { T2_Q_FULL = 0, T2_Q_EMPTY, T2_K_FULL0, T2_K_FULL1, T2_K_EMPTY0, T2_K_EMPTY1, T2_V_FULL0, T2_V_FULL1, T2_V_EMPTY0, T2_V_EMPTY1, T2_S_FULLA, T2_S_FULLB,
+       T2_P_FULLA, T2_P_FULLB, T2_O_FULL, T2_N_BARS };
+}  // namespace tc2
+
+// number of key tiles of stage S that the 128-row query block starting at i0 visits
+__device__ __forceinline__ int stage_tiles(const AttnTcParams& P, const TcStage& S, int64_t vis_lo, int64_t vis_hi) {
+  int n = 0;
+  int64_t j0s = 0;
+  for (int sg = S.seg_begin; sg < S.seg_end; ++sg) {
+    int tf, tl;
+    if (seg_tiles(vis_lo, vis_hi, j0s, P.seg[sg].len, &tf, &tl)) n += tl - tf + 1;
+    j0s += P.seg[sg].len;
+  }
+  return n;
+}
+
+template <typename T>
+__global__ void __maxnreg__(112) attn_tc2_kernel(const __grid_constant__ AttnTcParams P) {
+  using namespace tc2;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t sQ = s_base + kQ, sK = s_base + kK, sV = s_base + kV;
+  const uint32_t bars = s_base + kBar;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBar + T2_N_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBar + T2_N_BARS * 8 + 8);
+  float* xmax = reinterpret_cast<float*>(smem + kXmax);
+  float* xsum = reinterpret_cast<float*>(smem + kXsum);
+  volatile int* xflag = reinterpret_cast<volatile int*>(smem + kXflag);
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hA = 2 * blockIdx.y, hkv = hA / (P.n_heads / P.n_kv_heads);
+  const int64_t i0 = (int64_t)blockIdx.x * kTile;
+  const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
+  const int split = blockIdx.z;
+
+  // this CTA's run [g0, g1) of the work item's key tiles, numbered over all stages
+  int n_total = 0;
+  for (int st = 0; st < P.n_stage; ++st) {
+    const TcStage& S = P.stage[st];
+    int64_t vis_lo, vis_hi;
+    visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+    if (vis_lo <= vis_hi) n_total += stage_tiles(P, S, vis_lo, vis_hi);
+  }
+  const int g0 = (int)((int64_t)n_total * split / P.n_split), g1 = (int)((int64_t)n_total * (split + 1) / P.n_split);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < T2_N_BARS; ++i) mbar_init(bar(i), (i == T2_P_FULLA || i == T2_P_FULLB) ? 256u : 1u);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 512) xflag[threadIdx.x] = 0;
+  if (warp == 17) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns: S/P of head A [0,128), of head B [128,256), O of head A [256,384), of head B [384,512)
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
+  constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
+
+  if (warp == 16) {
+    // ======================================================================== TMA producer
+    if (lane == 0) {
+      int g = 0, it = 0, sidx = 0;
+      bool ok = true;
+      for (int st = 0; st < P.n_stage && ok; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        const int n_st = stage_tiles(P, S, vis_lo, vis_hi);
+        const bool active = (g > g0 ? g : g0) < (g + n_st < g1 ? g + n_st : g1);
+        if (active) {
+          if (sidx >= 1) ok = wait_or_abort(bar(T2_Q_EMPTY), (sidx - 1) & 1, abort_flag, P.err, 500);
+          if (!ok) break;
+          mbar_expect_tx(bar(T2_Q_FULL), 4 * kSubTileBytes);
+          for (int x = 0; x < 2; ++x) {
+            tma_load_3d(sQ + x * 2 * kSubTileBytes, &P.maps[S.map_q], bar(T2_Q_FULL), 0, S.q_row0 + (int)i0, hA + x);
+            tma_load_3d(sQ + x * 2 * kSubTileBytes + kSubTileBytes, &P.maps[S.map_q], bar(T2_Q_FULL), 64,
+                        S.q_row0 + (int)i0, hA + x);
+          }
+          ++sidx;
+        }
+        int64_t seg_j0 = 0;
+        for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+          const TcSeg& G = P.seg[sg];
+          int tf, tl;
+          if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+            for (int t = tf; t <= tl && ok; ++t, ++g) {
+              if (g < g0 || g >= g1) continue;
+              const int b = it & 1, tok = G.tok0 + t * kTile;
+              if (it >= 2) ok = wait_or_abort(bar(T2_K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 501);
+              if (!ok) break;
+              const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
+              mbar_expect_tx(bar(T2_K_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_k < 0) {
+                tma_load_3d(dk, &P.maps[G.map_k], bar(T2_K_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dk + kSubTileBytes, &P.maps[G.map_k], bar(T2_K_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dk, &P.maps[G.map_k], bar(T2_K_FULL0 + b), 0, tok, hkv, G.c3_k);
+                tma_load_4d(dk + kSubTileBytes, &P.maps[G.map_k], bar(T2_K_FULL0 + b), 64, tok, hkv, G.c3_k);
+              }
+              if (it >= 2) ok = wait_or_abort(bar(T2_V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 502);
+              if (!ok) break;
+              mbar_expect_tx(bar(T2_V_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_v < 0) {
+                tma_load_3d(dv, &P.maps[G.map_v], bar(T2_V_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T2_V_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dv, &P.maps[G.map_v], bar(T2_V_FULL0 + b), 0, tok, hkv, G.c3_v);
+                tma_load_4d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T2_V_FULL0 + b), 64, tok, hkv, G.c3_v);
+              }
+              ++it;
+            }
+          }
+          seg_j0 += G.len;
+        }
+      }
+      if (!ok) {
+        // give loads that are still in flight a bounded chance to land before the CTA's memory goes away
+        for (int b = 0; b < 2; ++b) {
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(T2_K_FULL0 + b), 0) && !mbar_try_wait(bar(T2_K_FULL0 + b), 1); ++i) __nanosleep(64);
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(T2_V_FULL0 + b), 0) && !mbar_try_wait(bar(T2_V_FULL0 + b), 1); ++i) __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ========================================================================== MMA issuer
+    if (lane == 0) {
+      int g = 0, it = 0, sidx = 0;
+      bool ok = true;
+      // S(x) = Q(x) K(tile j)^T into head x's S columns
+      auto issue_qk = [&](int x, int j) {
+        const uint32_t kt = sK + (j & 1) * 2 * kSubTileBytes, qt = sQ + x * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint64_t ad = make_sdesc(qt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          uint64_t bd = make_sdesc(kt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          mma_ss(tmem + x * 128, ad, bd, idesc_qk, ks > 0);
+        }
+        tc_commit(bar(T2_S_FULLA + x));
+      };
+      // O(x) += P(x) V(tile j): P from TMEM (keys 0-63 in S columns [0,32), keys 64-127 in [64,96)), V d-contiguous
+      auto issue_pv = [&](int x, int j) -> bool {
+        if (!wait_or_abort(bar(T2_P_FULLA + x), j & 1, abort_flag, P.err, 510)) return false;
+        if (x == 0 && !wait_or_abort(bar(T2_V_FULL0 + (j & 1)), (j >> 1) & 1, abort_flag, P.err, 511)) return false;
+        tc_fence_after();
+        const uint32_t vt = sV + (j & 1) * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t a_t = tmem + x * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
+          uint64_t bd = make_sdesc(vt + ks * 2048, kSubTileBytes, 1024);
+          mma_ts(tmem + 256 + x * 128, a_t, bd, idesc_pv, (j > 0) || (ks > 0));
+        }
+        return true;
+      };
+      for (int st = 0; st < P.n_stage && ok; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        const int n_st = stage_tiles(P, S, vis_lo, vis_hi);
+        const int lo = g > g0 ? g : g0, hi = g + n_st < g1 ? g + n_st : g1;
+        g += n_st;
+        if (lo >= hi) continue;
+        const int n_loc = hi - lo;  // this CTA's tiles of this stage: local indices it .. it + n_loc - 1
+        ok = wait_or_abort(bar(T2_Q_FULL), sidx & 1, abort_flag, P.err, 512);
+        ++sidx;
+        if (!ok) break;
+        // prologue: both heads' S for the first tile
+        ok = wait_or_abort(bar(T2_K_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag, P.err, 513);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(0, it);
+        issue_qk(1, it);
+        tc_commit(bar(T2_K_EMPTY0 + (it & 1)));
+        for (int j = it; j < it + n_loc && ok; ++j) {
+          const bool more = j + 1 < it + n_loc;
+          ok = issue_pv(0, j);
+          if (!ok) break;
+          if (more) {
+            ok = wait_or_abort(bar(T2_K_FULL0 + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag, P.err, 514);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(0, j + 1);  // head A's next S while head B's softmax is still at work
+          }
+          ok = issue_pv(1, j);
+          if (!ok) break;
+          tc_commit(bar(T2_V_EMPTY0 + (j & 1)));
+          if (more) {
+            issue_qk(1, j + 1);
+            tc_commit(bar(T2_K_EMPTY0 + ((j + 1) & 1)));
+          }
+        }
+        tc_commit(bar(T2_Q_EMPTY));  // every product that reads this stage's Q tiles has been issued
+        it += n_loc;
+      }
+      if (ok) tc_commit(bar(T2_O_FULL));
+    }
+  } else {
+    // ===================================================================== softmax / epilogue
+    // warps 0-7 serve head A, 8-15 head B; in each group warp w and w+4 own the same 32 query rows (TMEM lanes)
+    // and split the tile's 128 key columns in halves
+    const int x = warp >> 3, wq = warp & 7;
+    const int quad = wq & 3, half = wq >> 2;
+    const int row = quad * 32 + lane;
+    const int64_t qi = i0 + row;
+    const bool row_valid = qi < P.lq;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    const int col0 = half * 64;
+    const uint32_t tS = tmem + x * 128 + lane_base, tO = tmem + 256 + x * 128 + lane_base;
+    float* gmax = xmax + x * 512;
+    float* gsum = xsum + x * 256;
+    volatile int* gflag = xflag + x * 256;
+    float m_ref = -INFINITY, l_part = 0.f;  // m_ref in the scaled log2 domain; l over this thread's columns
+    int g = 0, it = 0;
+    bool ok = true;
+    for (int st = 0; st < P.n_stage && ok; ++st) {
+      const TcStage& S = P.stage[st];
+      int64_t vis_lo, vis_hi;
+      visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+      if (vis_lo > vis_hi) continue;
+      // keys [jlo, jhi] of this stage are visible to this thread's query row
+      int64_t jlo = 0, jhi = S.lk - 1;
+      if (S.mask_mode == INFLLM_MASK_WINDOW) {
+        jlo = qi + S.mask_offset - S.mask_size + 1;
+        jhi = qi + S.mask_offset;
+      } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
+        jhi = qi + S.mask_offset - S.mask_size;
+      }
+      if (!row_valid) jhi = -1, jlo = 0;
+      int64_t seg_j0 = 0;
+      for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+        const TcSeg& G = P.seg[sg];
+        int tf, tl;
+        if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+          for (int t = tf; t <= tl && ok; ++t, ++g) {
+            if (g < g0 || g >= g1) continue;
+            ok = __all_sync(0xffffffffu, wait_or_abort(bar(T2_S_FULLA + x), it & 1, abort_flag, P.err, 520));
+            if (!ok) break;
+            if (threadIdx.x == 0) TC_STAMP(5, it);
+            tc_fence_after();
+            // visible columns of this tile for this row, relative to this thread's 64 columns
+            const int64_t jt = seg_j0 + (int64_t)t * kTile;
+            const int64_t lim = seg_j0 + G.len - 1;
+            const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
+            const int c_lo = (int)(a - jt) - col0;
+            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt)) - col0;
+            const bool full = c_lo <= 0 && c_hi >= 63;
+            // ---- pass 1: row maximum of the raw scores
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              float s[32];
+              tmem_ld32(tS + col0 + cc * 32, reinterpret_cast<uint32_t*>(s));
+              tmem_wait_ld();
+              if (full) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                  mx4[0] = fmaxf(mx4[0], s[c]);
+                  mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                  mx4[2] = fmaxf(mx4[2], s[c + 2]);
+                  mx4[3] = fmaxf(mx4[3], s[c + 3]);
+                }
+              } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                  const int cg = cc * 32 + c;
+                  mx4[c & 3] = fmaxf(mx4[c & 3], (cg >= c_lo && cg <= c_hi) ? s[c] : -INFINITY);
+                }
+              }
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (threadIdx.x == 0) TC_STAMP(6, it);
+            // the other half's maximum of the same row
+            gmax[(it & 1) * 256 + half * 128 + row] = mx;
+            __threadfence_block();
+            gflag[half * 128 + row] = it + 1;
+            ok = __all_sync(0xffffffffu, pair_wait(&gflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 521));
+            if (!ok) break;
+            mx = fmaxf(mx, gmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
+            if (threadIdx.x == 0) TC_STAMP(7, it);
+            // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
+            float alpha = 1.f;
+            bool resc = false;
+            if (mx > m_ref) {
+              if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated for this row yet
+              } else if (mx - m_ref > 8.f) {
+                alpha = ex2_approx(m_ref - mx);
+                l_part *= alpha;
+                m_ref = mx;
+                resc = true;
+              }
+            }
+            // O of this head is quiet here: S of this tile being complete implies that the previous P V is too
+            if (__any_sync(0xffffffffu, resc) && it >= 1) {
+#pragma unroll
+              for (int cc = 0; cc < 2; ++cc) {
+                uint32_t o[32];
+                tmem_ld32(tO + col0 + cc * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+                tmem_st32(tO + col0 + cc * 32, o);
+              }
+              tmem_wait_st();
+            }
+            // ---- pass 2: P = exp2(S * scale - m), two exponentials per instruction, packed 16-bit pairs
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              float s[32];
+              uint32_t pk[16];
+              tmem_ld32(tS + col0 + cc * 32, reinterpret_cast<uint32_t*>(s));
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; c += 4) {
+                float a0 = fmaf(s[c], P.scale_log2, neg_m), a1 = fmaf(s[c + 1], P.scale_log2, neg_m);
+                float a2 = fmaf(s[c + 2], P.scale_log2, neg_m), a3 = fmaf(s[c + 3], P.scale_log2, neg_m);
+                if (!full) {
+                  const int cg = cc * 32 + c;
+                  a0 = (cg >= c_lo && cg <= c_hi) ? a0 : -INFINITY;
+                  a1 = (cg + 1 >= c_lo && cg + 1 <= c_hi) ? a1 : -INFINITY;
+                  a2 = (cg + 2 >= c_lo && cg + 2 <= c_hi) ? a2 : -INFINITY;
+                  a3 = (cg + 3 >= c_lo && cg + 3 <= c_hi) ? a3 : -INFINITY;
+                }
+                const float2 p01 = ex2_pair(a0, a1), p23 = ex2_pair(a2, a3);
+                rs4[0] += p01.x; rs4[1] += p01.y; rs4[2] += p23.x; rs4[3] += p23.y;
+                typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
+                pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
+                pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
+              }
+              // 32 keys of P, packed, over S columns this thread has already consumed
+              tmem_st16(tS + col0 + cc * 16, pk);
+            }
+            l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            if (threadIdx.x == 0) TC_STAMP(8, it);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(T2_P_FULLA + x));
+            if (threadIdx.x == 0) TC_STAMP(9, it);
+            ++it;
+          }
+        }
+        seg_j0 += G.len;
+      }
+    }
+    // ---- epilogue (each half handles its 64 output columns)
+    gsum[half * 128 + row] = l_part;
+    __threadfence_block();
+    gflag[half * 128 + row] = kPairDone;
+    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&gflag[(half ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 522));
+    const float l_sum = l_part + gsum[(half ^ 1) * 128 + row];
+    if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(T2_O_FULL), 0, abort_flag, P.err, 523));
+    if (ok) {
+      tc_fence_after();
+      const int h = hA + x;
+      if (P.n_split == 1) {
+        const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
+        T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts + col0;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t o[32];
+          if (it >= 1) {
+            tmem_ld32(tO + col0 + cc * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = 0;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 8) {
+              uint4 v;
+              uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                typename Act<T>::T2 v2 = Act<T>::from_f2(__uint_as_float(o[k + 2 * e]) * inv,
+                                                         __uint_as_float(o[k + 2 * e + 1]) * inv);
+                pv[e] = *reinterpret_cast<uint32_t*>(&v2);
+              }
+              *reinterpret_cast<uint4*>(orow + cc * 32 + k) = v;
+            }
+          }
+        }
+        if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
+      } else {
+        // un-normalised partial of this run of key tiles
+        const int64_t prow = ((int64_t)split * P.n_heads + h) * P.lq + qi;
+        float* arow = P.part_acc + prow * 128 + col0;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t o[32];
+          if (it >= 1) {
+            tmem_ld32(tO + col0 + cc * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = 0;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 4)
+              *reinterpret_cast<uint4*>(arow + cc * 32 + k) = make_uint4(o[k], o[k + 1], o[k + 2], o[k + 3]);
+          }
+        }
+        if (half == 0 && row_valid) {
+          P.part_m[prow] = m_ref;
+          P.part_l[prow] = l_sum;
+        }
+      }
+    }
+  }
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) tmem_dealloc(tmem, 512);
+}
+
+// out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), lse = m + log2(denominator); one warp per row
+template <typename T>
+__global__ void attn_tc_combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
+                                       const float* __restrict__ l, int n_split, int n_heads, int64_t lq,
+                                       T* __restrict__ out, int64_t o_hs, int64_t o_ts, float* __restrict__ lse) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // h * lq + i
+  if (row >= (int64_t)n_heads * lq) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t h = row / lq, i = row - h * lq;
+  const int64_t stride = (int64_t)n_heads * lq;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, m[s * stride + row]);
+  float den = 0.f;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (mx != -INFINITY) {
+    for (int s = 0; s < n_split; ++s) {
+      const float ms = m[s * stride + row];
+      if (ms == -INFINITY) continue;
+      const float w = exp2f(ms - mx);
+      den = fmaf(w, l[s * stride + row], den);
+      const float4 a = *reinterpret_cast<const float4*>(acc + (s * stride + row) * 128 + lane * 4);
+      num.x = fmaf(w, a.x, num.x);
+      num.y = fmaf(w, a.y, num.y);
+      num.z = fmaf(w, a.z, num.z);
+      num.w = fmaf(w, a.w, num.w);
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  typename Act<T>::T2 v01 = Act<T>::from_f2(num.x * inv, num.y * inv), v23 = Act<T>::from_f2(num.z * inv, num.w * inv);
+  uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&v01), *reinterpret_cast<uint32_t*>(&v23));
+  *reinterpret_cast<uint2*>(out + h * o_hs + i * o_ts + lane * 4) = v;
+  if (lane == 0 && lse) lse[row] = den > 0.f ? mx + log2f(den) : -INFINITY;
+}
+
 // ------------------------------------------------------------------------------------ column sums
 // One CTA owns one query head and a run of 128-key tiles.  The head's query tiles (at most four, 512 queries)
 // and their log-sum-exps stay in shared memory for the whole CTA; the key tiles stream through a two-stage TMA
@@ -770,6 +1250,39 @@ int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
   return INFLLM_OK;
 }
 
+size_t attn_tc2_scratch_floats(int n_split, int n_heads, int64_t lq) {
+  return n_split > 1 ? (size_t)n_split * n_heads * lq * (128 + 2) : 0;
+}
+
+int attn_tc2_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
+  if (P.lq <= 0) return INFLLM_OK;
+  const int group = P.n_heads / P.n_kv_heads;
+  if (group % 2) return fail(INFLLM_E_UNSUPPORTED, "two-head attention kernel: %d query heads per kv head", group);
+  if (P.n_split < 1 || (P.n_split > 1 && (!P.part_acc || !P.part_m || !P.part_l)))
+    return fail(INFLLM_E_BADARG, "two-head attention kernel: split %d without partial buffers", P.n_split);
+  dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads / 2, P.n_split);
+  const size_t smem = tc2::kTotal + 1024;
+  static bool attr_set[2] = {false, false};
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    auto kern = attn_tc2_kernel<T>;
+    if (!attr_set[dtype]) {
+      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set[dtype] = true;
+    }
+    kern<<<grid, 576, smem, s>>>(P);
+  });
+  INFLLM_LAUNCH_OK("attn_tc2_kernel");
+  if (P.n_split > 1) {
+    const int64_t rows = (int64_t)P.n_heads * P.lq;
+    INFLLM_DISPATCH_DTYPE(dtype, T, {
+      attn_tc_combine_kernel<T><<<(unsigned)ceil_div(rows, 8), 256, 0, s>>>(
+          P.part_acc, P.part_m, P.part_l, P.n_split, P.n_heads, P.lq, (T*)P.out, P.o_hs, P.o_ts, P.lse);
+    });
+    INFLLM_LAUNCH_OK("attn_tc_combine_kernel");
+  }
+  return INFLLM_OK;
+}
+
 int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, int q_row0, int k_tok0, int n_heads,
                           int n_kv_heads, int64_t lq, int64_t lk, int mask_mode, int64_t mask_offset,
                           int64_t mask_size, const float* lse, float* score, int64_t score_hs, int accumulate,
@@ -838,7 +1351,7 @@ extern "C" int infllm_device_error(int* code, int* where) {
 extern "C" int infllm_tc_stamps(long long* h_out) {
   using namespace infllm;
   INFLLM_CUDA_OK(cudaDeviceSynchronize());
-  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 5 * 256));
+  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 10 * 256));
   return INFLLM_OK;
 }
 #endif

@@ -32,6 +32,12 @@ struct AttnTcParams {
   float* lse;
   float scale_log2;
   int* err;
+  // two-head kernel only: the key tiles of a work item are cut into n_split runs; with n_split > 1 every run
+  // writes an un-normalised partial (acc, m, l) and attn_tc_combine merges them
+  int32_t n_split, pad2;
+  float* part_acc;  // (n_split, H, lq, 128)
+  float* part_m;    // (n_split, H, lq)
+  float* part_l;    // (n_split, H, lq)
 };
 
 struct ColsumTcParams {
@@ -53,6 +59,9 @@ int encode_rows_map(CUtensorMap* map, int dtype, const void* base, int64_t rows,
 bool tc_rows_ok(const void* base, int64_t hs, int64_t ts);
 int tc_get_error_ptr(int** p);
 int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s);
+// two query heads of one KV head per CTA (needs an even number of query heads per KV head)
+int attn_tc2_launch(const AttnTcParams& P, int dtype, cudaStream_t s);
+size_t attn_tc2_scratch_floats(int n_split, int n_heads, int64_t lq);
 int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, int q_row0, int k_tok0, int n_heads,
                           int n_kv_heads, int64_t lq, int64_t lk, int mask_mode, int64_t mask_offset,
                           int64_t mask_size, const float* lse, float* score, int64_t score_hs, int accumulate,

@@ -175,6 +175,8 @@ struct infllm_ctx {
   int64_t init_cap = 0;  // rows allocated for the sink buffers (at least one 128-row tile)
   CUtensorMap m_qloc, m_qglb, m_krot, m_kraw, m_v, m_cache, m_initk, m_initv;
   int* tc_err = nullptr;
+  float* tc_part = nullptr;  // partial results of the two-head attention kernel's key-tile runs
+  size_t tc_part_floats = 0;
 
   // look-ahead retrieval inside one append: while exec block t runs, the top-k of t+1 over the units known
   // so far is computed on a second stream and its misses are staged into spare slots; after t's sealing
@@ -970,7 +972,26 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         TP.stage[1].map_q = 1; TP.stage[1].q_row0 = (int)st; TP.stage[1].mask_mode = INFLLM_MASK_NONE;
         TP.stage[1].lk = (int64_t)all_glk; TP.stage[1].seg_begin = 1; TP.stage[1].seg_end = ns;
         ProfScope ps(c, s, INFLLM_PROF_ATTN, 4.0 * D * H * (local_pairs + (double)lq * all_glk));
-        INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
+        if ((H / HKV) % 2 == 0 && (g.reserved[0] & 8)) {  // flag bit 3: the two-heads-per-CTA kernel (see attn_tc.cu)
+          // two heads of a KV head per CTA; cut the key tiles into runs until the grid covers the SMs
+          const int items = (int)((lq + 127) / 128) * (int)(H / 2);
+          TP.n_split = std::max(1, std::min(8, 148 / items));
+          const size_t need = attn_tc2_scratch_floats(TP.n_split, (int)H, lq);
+          if (need > c->tc_part_floats) {
+            if (c->tc_part) INFLLM_CUDA_OK(cudaFreeAsync(c->tc_part, s));
+            INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->tc_part, need * sizeof(float), s));
+            c->tc_part_floats = need;
+          }
+          if (TP.n_split > 1) {
+            TP.part_acc = c->tc_part;
+            TP.part_m = c->tc_part + (size_t)TP.n_split * H * lq * 128;
+            TP.part_l = TP.part_m + (size_t)TP.n_split * H * lq;
+          }
+          INFLLM_TRY(attn_tc2_launch(TP, g.dtype, s));
+        } else {
+          TP.n_split = 1;
+          INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
+        }
       } else {
       AttnParams P{};
       P.n_heads = (int)H; P.n_kv_heads = (int)HKV; P.lq = lq; P.first = 1;
@@ -1152,6 +1173,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     if (c->h_cand_rows) cudaFreeHost(c->h_cand_rows);
     if (c->h_cand_scores) cudaFreeHost(c->h_cand_scores);
     if (c->scores_aux) cudaFreeAsync(c->scores_aux, nullptr);
+    if (c->tc_part) cudaFreeAsync(c->tc_part, nullptr);
     cudaStreamDestroy(c->aux_stream);
     cudaStreamDestroy(c->mail_stream);
     if (c->d_cand_scores) cudaFree(c->d_cand_scores);
