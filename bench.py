@@ -326,6 +326,133 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------ decode workload
+DEC = dict(units=8192, topk=32, max_cached=32, n_local=4096, n_init=128, bs=128, repr_topk=4, exc=512, planted_frac=0.01)
+
+
+def make_decode_memory(dev, rope, seed):
+    """Host tensors of a 1M-token memory for one Mistral-shaped layer: sealed units ~N(0,1), representative keys
+    ~N(0,1) except 1% planted units whose representative keys lean towards the direction the query stream
+    leans towards (after the one-angle rotation that retrieval applies), sink and window ~N(0,1)."""
+    H, HKV, D, n = CFG["H"], CFG["HKV"], CFG["D"], DEC["units"]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    units = torch.empty((n, 2, HKV, DEC["bs"], D), dtype=torch.bfloat16)
+    for s in range(0, n, 512):
+        m = min(512, n - s)
+        units[s:s + m] = torch.randn((m, 2, HKV, DEC["bs"], D), generator=g, device=dev).to(torch.bfloat16).cpu()
+    block_k = torch.randn((n, H * D), generator=g, device=dev)
+    direction = torch.randn((H, 1, D), generator=g, device=dev)
+    direction = direction / direction.norm(dim=-1, keepdim=True)
+    rotated = rope.apply_rotary_pos_emb_one_angle(direction.to(torch.bfloat16)[None], DEC["n_local"])[0].float().reshape(-1)
+    n_plant = max(1, int(n * DEC["planted_frac"]))
+    gc = torch.Generator().manual_seed(seed + 1)
+    planted = torch.randperm(n, generator=gc)[:n_plant].to(dev)
+    block_k[planted] = 0.7 * block_k[planted] + 6.0 * rotated  # clearly above the random scores, still jittered
+    small = lambda *shape: torch.randn(shape, generator=g, device=dev).to(torch.bfloat16).cpu()  # noqa: E731
+    return (units, block_k.to(torch.bfloat16).cpu(), small(HKV, DEC["n_init"], D), small(HKV, DEC["n_init"], D),
+            small(HKV, DEC["n_local"], D), small(HKV, DEC["n_local"], D)), direction
+
+
+def run_decode(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from infllm_b200 import _lib
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    H, HKV, D = CFG["H"], CFG["HKV"], CFG["D"]
+    rope = RotaryEmbeddingESM(D, CFG["base"], 1.0)
+    mem, direction = make_decode_memory(dev, rope, seed=rank)
+    cm = ContextManager(rope, DEC["n_init"], DEC["n_local"], DEC["bs"], DEC["max_cached"], DEC["topk"], DEC["exc"], None,
+                        True, DEC["repr_topk"])
+    cm.load_synthetic(*mem)
+    del mem
+    total = args.warmup + 2 * args.steps + 2
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    qs = (torch.randn((total, 1, H, 1, D), generator=g, device=dev) + 3.0 * direction).to(torch.bfloat16)
+    ks = torch.randn((total, 1, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    vs = torch.randn((total, 1, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    h_q, h_k, h_v = (t.cpu().pin_memory() for t in (qs, ks, vs))
+    h_o = torch.empty((1, H, 1, D), dtype=torch.bfloat16).pin_memory()
+    pos = [0]
+
+    def step_device():
+        i = pos[0]
+        pos[0] += 1
+        return cm.append(qs[i], ks[i], vs[i], qs[i], ks[i], vs[i])
+
+    def step_host():
+        i = pos[0]
+        pos[0] += 1
+        q, k, v = (t[i].to(dev, non_blocking=True) for t in (h_q, h_k, h_v))
+        h_o.copy_(cm.append(q, k, v, q, k, v), non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller consumes every token's output before the next token
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    with torch.inference_mode():
+        for _ in range(args.warmup):
+            step_device()
+        cm.profile(True)
+        cm.get_profile()
+        clk_p, clk_f = sample_clocks_start(local_rank)
+        l0 = _lib.lib.infllm_launch_count()
+        ms = timed(step_device, args.steps)
+        launches = _lib.lib.infllm_launch_count() - l0
+        prof = cm.get_profile()
+        cm.profile(False)
+        clocks = sample_clocks_stop(clk_p, clk_f)
+        step_host()
+        ms_e2e = timed(step_host, args.steps)
+        info = cm.info()
+    _, hbm_peak, which = measured_peaks()
+    us = 1e3 * ms / args.steps
+    topk_ms, topk_bytes, topk_n = prof["topk"]
+    dec_ms, dec_bytes, dec_n = prof["decode"]
+    achieved = topk_bytes / (topk_ms / 1e3) / 1e9 if topk_ms > 0 else None
+    line = dict(
+        metric="decode-attn us/token @1M ctx", value=us, unit="us/token", n_gpus=world, steps=args.steps,
+        warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=False, scaling="weak", vs_baseline=None,
+        dtype="bf16", data="synthetic",
+        config=dict(workload=f"mistral-7b-shaped layer, decode over {DEC['units']} memory units of 128 tokens "
+                             f"({DEC['n_init'] + DEC['units'] * DEC['bs'] + DEC['n_local']} tokens), topk 32, repr_topk 4, "
+                             "max_cached 32, n_local 4096, n_init 128; 1% planted units",
+                    l2="the representative keys read every step (64 MiB) do not fit next to the streamed K/V in L2",
+                    replicas=world),
+        e2e=dict(value=1e3 * ms_e2e / args.steps, unit="us/token", h2d_bytes_per_step=int((H + 2 * HKV) * D * 2),
+                 d2h_bytes_per_step=int(H * D * 2)),
+        gpu_launches=int(launches),
+        roofline=dict(bound="hbm", kernel="unit scoring + top-k", achieved=achieved, peak=hbm_peak, unit="GB/s",
+                      frac=(achieved / hbm_peak if achieved else None), traffic=None, peak_source=f"hbm_gbs of {which}",
+                      launches=int(topk_n), us_per_launch=1e3 * topk_ms / max(topk_n, 1),
+                      bytes_per_launch=topk_bytes / max(topk_n, 1)),
+        kernels={k: dict(ms=v[0], launches=v[2], work=v[1]) for k, v in prof.items()},
+        decode_attention=dict(achieved_gbs=(dec_bytes / (dec_ms / 1e3) / 1e9 if dec_ms > 0 else None),
+                              us_per_launch=1e3 * dec_ms / max(dec_n, 1), bytes_per_launch=dec_bytes / max(dec_n, 1)),
+        store=dict(h2d_bytes=info["h2d_bytes"], hits=info["cache_hits"], misses=info["cache_misses"]),
+        clocks=clocks)
+    if rank == 0:
+        print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -333,10 +460,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=CFG["tokens"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"],
+                    help="prefill: 131072-token prompt (the default, the first half of the metric); decode: 1M-token decode")
+    ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--max-cached", type=int, default=CFG["max_cached"], help="max_cached_block (32 in the named config)")
     args = ap.parse_args()
     CFG["max_cached"] = args.max_cached
+    DEC["units"] = args.units
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -349,7 +480,10 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    run_ours(args, rank, world, local_rank)
+    if args.workload == "decode":
+        run_decode(args, rank, world, local_rank)
+    else:
+        run_ours(args, rank, world, local_rank)
     if world > 1:
         import torch.distributed as dist
 

@@ -205,6 +205,29 @@ class ContextManager:
         names = ("rank_sync", "plan", "lookahead_launch", "attn_launch", "lookahead_stage", "seal", "cand_wait")
         return {n: us[i] for i, n in enumerate(names)}
 
+    def load_synthetic(self, units, block_k, init_k, init_v, win_k, win_v):
+        """Install a ready-made memory without running a prefill (decode-only workloads and tests).
+
+        units (n, 2, H_kv, block_size, D): K and V of n sealed units; block_k (n, H*D) their representative keys;
+        init_k/v (H_kv, n_init, D); win_k/v (H_kv, n_local, D) the local window.  All host tensors of the
+        activation dtype.  Afterwards length = n_init + n*block_size + n_local, batch size 1."""
+        dtype, hkv, d = units.dtype, units.size(2), units.size(4)
+        heads = block_k.size(1) // d
+        if not self.initialized:
+            dev = torch.device("cuda", torch.cuda.current_device())
+            self._init(torch.empty((1, heads, 1, d), dtype=dtype, device=dev),
+                       torch.empty((1, hkv, 1, d), dtype=dtype, device=dev))
+        ts = [t.contiguous() for t in (units, block_k, init_k, init_v, win_k, win_v)]
+        for t in ts:
+            if t.is_cuda or t.dtype != dtype:
+                raise ValueError("load_synthetic takes host tensors of one activation dtype")
+        assert ts[0].shape[1:] == (2, self.unit_size_kv, self.block_size, self.dim_head)
+        assert ts[4].shape == (self.unit_size_kv, self.n_local, self.dim_head)
+        _lib.check(_lib.lib.infllm_ctx_load_synthetic(
+            self._ctx[0], ts[0].size(0), ts[0].data_ptr(), ts[1].data_ptr(), ts[2].data_ptr(), ts[3].data_ptr(),
+            ts[4].data_ptr(), ts[5].data_ptr(), _lib.stream_ptr(self.device)))
+        self.length = self.info()["length"]
+
     def reset(self):
         for h in self._ctx:
             _lib.check(_lib.lib.infllm_ctx_reset(h))

@@ -160,3 +160,59 @@ def test_inf_llm_forward_layer():
     with torch.inference_mode():
         want_o = wo(want.to(torch.bfloat16).to(DEV)[None])
     assert (o.float() - want_o.float()).abs().max().item() < 3e-2
+
+
+def _synthetic_memory(n_units, H, HKV, D, n_init, n_local, bs, seed, planted=()):
+    """Seeded K/V for a memory of n_units sealed units + sink + window, and representative keys."""
+    g = torch.Generator().manual_seed(seed)
+    bf = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16)  # noqa: E731
+    units, block_k = bf(n_units, 2, HKV, bs, D), bf(n_units, H * D)
+    for b, row in planted:
+        block_k[b] = row
+    return units, block_k, bf(HKV, n_init, D), bf(HKV, n_init, D), bf(HKV, n_local, D), bf(HKV, n_local, D)
+
+
+def _oracle_from_synthetic(units, block_k, init_k, init_v, win_k, win_v, cfg):
+    n, _, hkv, bs, d = units.shape
+    ora = FollowerOracle(cfg["n_init"], cfg["n_local"], bs, cfg["max_cached"], cfg["topk"], cfg["exc"], cfg["repr_topk"],
+                         cfg["base"], 1.0)
+    k_units = units[:, 0].permute(1, 0, 2, 3).reshape(hkv, n * bs, d)
+    v_units = units[:, 1].permute(1, 0, 2, 3).reshape(hkv, n * bs, d)
+    ora.k_log = torch.cat((init_k, k_units, win_k), dim=1).float()
+    ora.v_log = torch.cat((init_v, v_units, win_v), dim=1).float()
+    ora.length = ora.k_log.size(1)
+    ora.acc = torch.zeros((block_k.size(1) // d, ora.length))
+    ora.init_len, ora.init_full = cfg["n_init"], True
+    ora.frontier = cfg["n_init"] + n * bs
+    ora.block_k = list(block_k.float())
+    return ora
+
+
+def test_decode_over_a_synthetic_memory_matches_oracle():
+    """Decode-only workload: a memory of sealed units is installed directly (no prefill), then single tokens are
+    appended: retrieval, cache refills from the host store, split-K attention, sealing of new units."""
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    H, HKV, D = 8, 2, 128
+    cfg = dict(n_init=128, n_local=512, max_cached=6, topk=4, exc=128, repr_topk=4, base=1e6)
+    mem = _synthetic_memory(40, H, HKV, D, cfg["n_init"], cfg["n_local"], 128, seed=5)
+    pe = RotaryEmbeddingESM(D, cfg["base"], 1.0)
+    cm = ContextManager(pe, cfg["n_init"], cfg["n_local"], 128, cfg["max_cached"], cfg["topk"], cfg["exc"], None, False,
+                        cfg["repr_topk"])
+    cm.load_synthetic(*mem)
+    ora = _oracle_from_synthetic(*mem, cfg)
+    assert cm.size() == ora.length == 128 + 40 * 128 + 512
+    g = torch.Generator().manual_seed(6)
+    for step in range(140):  # crosses a sealing boundary (one new unit every 128 tokens)
+        q = torch.randn(H, 1, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(HKV, 1, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(HKV, 1, D, generator=g).to(torch.bfloat16)
+        dq, dk, dv = (t[None].to(DEV) for t in (q, k, v))
+        got = cm.append(dq, dk, dv, dq, dk, dv)[0].float().cpu()
+        ora.forced += cm.last_topk()
+        want = ora.append(q.float(), k.float(), v.float())
+        diff = (got - want).abs()
+        assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL, f"step {step}"
+        assert list(cm.cached_blocks[0].items()) == [(b, float(s)) for b, s in ora.lru.entries.items()]
+    assert cm.info()["num_blocks"] == ora.num_blocks == 41
+    assert len({i for i, _, _ in ora.mismatches}) <= 7
