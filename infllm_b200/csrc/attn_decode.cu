@@ -1,18 +1,19 @@
 // Decode attention: one query token per head over a list of key/value segments.
 //
-// HBM-streaming split-K: the keys of all segments are cut into chunks of kDecodeChunk tokens; one CTA
-// handles one chunk of one KV head for all the query heads of its group, reading each K and V row
-// exactly once with 16-byte loads (a half-warp covers one 256-byte row).  Each CTA writes a
+// HBM-streaming split-K: the keys of all segments are cut into chunks (128 tokens through the C entry points,
+// 64 inside the context, which wants more CTAs in flight); one single-warp CTA handles one chunk of one KV
+// head for all the query heads of its group, reading each K and V row exactly once with 16-byte cp.async
+// copies that are all issued before the first is used.  Each CTA writes a
 // normalised partial output and its log-sum-exp; infllm_lse_merge combines partials — the chunks of one
 // GPU and, for unit-range sharding, the partials gathered from other GPUs.
 // Replaces the two attn.append calls of ContextManager._append (context_manager.py:486-489, 526-531)
 // for single-token exec blocks.
 #include "attn_common.cuh"
+#include "mma_common.cuh"
 
 namespace infllm {
 
 constexpr int kDecodeChunk = 128;
-constexpr int kDecodeThreads = 128;
 constexpr int kMaxGroup = 8;  // query heads per KV head
 
 struct DecodeSeg {
@@ -37,184 +38,254 @@ struct DecodeParams {
   float scale_log2;
 };
 
-template <int HD, typename T>
-__global__ void __launch_bounds__(kDecodeThreads)
-attn_decode_kernel(const __grid_constant__ DecodeParams P) {
-  static_assert(HD == 128, "one half-warp covers a 128-element row");
-  __shared__ float s_q[kMaxGroup][HD];
-  __shared__ float s_p[kMaxGroup][kDecodeChunk];
-  __shared__ float s_o[kDecodeThreads / 16][kMaxGroup][HD / 8][8 + 1];  // [half-warp][head][16-byte chunk][element]
-  __shared__ float s_m[kMaxGroup], s_l[kMaxGroup];
+// wait until at most n of this thread's cp.async groups are pending (n is a constant after unrolling)
+__device__ __forceinline__ void cp_wait_upto(int n) {
+  if (n <= 0) mma::cp_async_wait<0>();
+  else if (n == 1) mma::cp_async_wait<1>();
+  else if (n == 2) mma::cp_async_wait<2>();
+  else mma::cp_async_wait<3>();
+  __syncwarp();  // the other lanes' copies are visible too
+}
 
+// One warp per CTA and per chunk of 64 * ROUNDS keys of one KV head.  The warp first issues every 16-byte
+// cp.async of its K and V rows (32 KiB per round, XOR-swizzled tiles in shared memory), so that a full SM holds
+// about 200 KiB of loads in flight, then runs S = Q K^T and O = P V on the tensor cores (mma.sync m16n8k16: the
+// query heads of the group are the first rows of the 16-row operand, the rest is zero) with the softmax of the
+// chunk in registers in between.
+template <int HD, int ROUNDS, typename T>
+__global__ void __launch_bounds__(32) attn_decode_kernel(const __grid_constant__ DecodeParams P) {
+  static_assert(HD == 128, "tiles of 64 keys x 128 elements");
+  using namespace mma;
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int kTileBytes = 64 * HD * 2;
+  constexpr int kChunk = 64 * ROUNDS;
+  const uint32_t s0 = smem_u32(smem);
+  const int lane = threadIdx.x, g = lane >> 2, t4 = lane & 3;
   const int part = blockIdx.x, hkv = blockIdx.y;
   const int group = P.n_heads / P.n_kv_heads;
   int sg = 0;
   while (sg + 1 < P.n_seg && P.part_begin[sg + 1] <= part) ++sg;
   const DecodeSeg& S = P.seg[sg];
-  const int j0 = (part - P.part_begin[sg]) * kDecodeChunk;
-  const int nk = (S.len - j0) < kDecodeChunk ? (S.len - j0) : kDecodeChunk;
-  const T* qsrc = (const T*)P.q[P.qsel[sg]];
-  for (int i = threadIdx.x; i < group * HD; i += kDecodeThreads) {
-    int gi = i / HD, d = i % HD;
-    s_q[gi][d] = Act<T>::to_f(qsrc[(int64_t)(hkv * group + gi) * P.q_hs + d]);
-  }
-  __syncthreads();
-
-  const int hw = threadIdx.x >> 4;  // half-warp index 0..7
-  const int l16 = threadIdx.x & 15; // lane within the half-warp: owns elements [l16*8, l16*8+8)
-  const T* kbase = (const T*)S.k + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts + l16 * 8;
-  const T* vbase = (const T*)S.v + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts + l16 * 8;
-
-  // ---- logits: s[g][j] = <q_g, k_j> * scale
-  for (int j = hw; j < kDecodeChunk; j += kDecodeThreads / 16) {
-    float part_dot[kMaxGroup];
+  const int j0 = (part - P.part_begin[sg]) * kChunk;
+  const int nk = (S.len - j0) < kChunk ? (S.len - j0) : kChunk;
+  const T* kbase = (const T*)S.k + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
+  const T* vbase = (const T*)S.v + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
+  // ---- all loads of the chunk: groups K0, V0, K1, V1 ...; rows past the end are zero-filled
 #pragma unroll
-    for (int gi = 0; gi < kMaxGroup; ++gi) part_dot[gi] = 0.f;
-    if (j < nk) {
-      uint4 raw = __ldg(reinterpret_cast<const uint4*>(kbase + (int64_t)j * S.ts));
-      const typename Act<T>::T2* k2 = reinterpret_cast<const typename Act<T>::T2*>(&raw);
-      float kf[8];
+  for (int r = 0; r < ROUNDS; ++r) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float2 f = Act<T>::to_f2(k2[e]);
-        kf[2 * e] = f.x;
-        kf[2 * e + 1] = f.y;
+    for (int kv = 0; kv < 2; ++kv) {
+      const T* base = kv ? vbase : kbase;
+      const uint32_t dst = s0 + (uint32_t)((2 * r + kv) * kTileBytes);
+#pragma unroll 8
+      for (int i = 0; i < 64 * (HD / 8) / 32; ++i) {
+        const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx % (HD / 8);
+        const int jr = r * 64 + row;
+        const bool ok = jr < nk;
+        cp_async16(dst + tile_off<HD>(row, c), base + (ok ? (int64_t)jr * S.ts : 0) + c * 8, ok);
       }
-#pragma unroll
-      for (int gi = 0; gi < kMaxGroup; ++gi) {
-        if (gi < group) {
-          float a = 0.f;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) a = fmaf(kf[e], s_q[gi][l16 * 8 + e], a);
-          part_dot[gi] = a;
-        }
-      }
-    }
-#pragma unroll
-    for (int gi = 0; gi < kMaxGroup; ++gi) {
-      if (gi < group) {
-        float a = part_dot[gi];
-        a += __shfl_xor_sync(0xffffffffu, a, 1);
-        a += __shfl_xor_sync(0xffffffffu, a, 2);
-        a += __shfl_xor_sync(0xffffffffu, a, 4);
-        a += __shfl_xor_sync(0xffffffffu, a, 8);
-        if (l16 == 0) s_p[gi][j] = j < nk ? a * P.scale_log2 : -INFINITY;
-      }
+      cp_async_commit();
     }
   }
-  __syncthreads();
-  if (sg == P.logit_seg) {
-    for (int i = threadIdx.x; i < group * nk; i += kDecodeThreads) {
-      int gi = i / nk, j = i % nk;
-      P.logits[(int64_t)(hkv * group + gi) * S.len + j0 + j] = s_p[gi][j];
-    }
+  // ---- the group's queries as A fragments: row g of the operand is head hkv * group + g, rows >= group are zero
+  const bool qrow = g < group;
+  const int h = hkv * group + (qrow ? g : 0);
+  const T* qp = (const T*)P.q[P.qsel[sg]] + (int64_t)h * P.q_hs;
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    qf[ks][0] = qrow ? __ldg(reinterpret_cast<const uint32_t*>(qp + ks * 16 + t4 * 2)) : 0u;
+    qf[ks][2] = qrow ? __ldg(reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + t4 * 2)) : 0u;
+    qf[ks][1] = qf[ks][3] = 0u;
   }
-  // ---- softmax over the chunk: one warp per query head (looping if the group is larger than 4)
-  {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int gi = warp; gi < group; gi += kDecodeThreads / 32) {
-      float mx = -INFINITY;
-      for (int j = lane; j < kDecodeChunk; j += 32) mx = fmaxf(mx, s_p[gi][j]);
-      mx = warp_max(mx);
-      float sum = 0.f;
-      for (int j = lane; j < kDecodeChunk; j += 32) {
-        float pv = exp2f(s_p[gi][j] - mx);
-        s_p[gi][j] = pv;
-        sum += pv;
-      }
-      sum = warp_sum(sum);
-      if (lane == 0) {
-        s_m[gi] = mx;
-        s_l[gi] = sum;
-      }
-    }
-  }
-  __syncthreads();
-  // ---- o[g][d] = sum_j p[g][j] v[j][d]
-  float acc[kMaxGroup][8];
+  float o[HD / 8][4];
 #pragma unroll
-  for (int gi = 0; gi < kMaxGroup; ++gi)
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m = -INFINITY, l = 0.f;  // l: this thread's share of the row sum, reduced over the quad at the end
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[gi][e] = 0.f;
-  for (int j = hw; j < nk; j += kDecodeThreads / 16) {
-    uint4 raw = __ldg(reinterpret_cast<const uint4*>(vbase + (int64_t)j * S.ts));
-    const typename Act<T>::T2* v2 = reinterpret_cast<const typename Act<T>::T2*>(&raw);
-    float vf[8];
+  for (int r = 0; r < ROUNDS; ++r) {
+    const uint32_t kt = s0 + (uint32_t)(2 * r * kTileBytes), vt = kt + kTileBytes;
+    cp_wait_upto(2 * ROUNDS - 1 - 2 * r);
+    float sacc[8][4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float2 f = Act<T>::to_f2(v2[e]);
-      vf[2 * e] = f.x;
-      vf[2 * e + 1] = f.y;
-    }
+    for (int i = 0; i < 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
 #pragma unroll
-    for (int gi = 0; gi < kMaxGroup; ++gi) {
-      if (gi < group) {
-        float pv = s_p[gi][j];
+    for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[gi][e] = fmaf(pv, vf[e], acc[gi][e]);
+      for (int np = 0; np < 4; ++np) {
+        const int mid = lane >> 3;
+        const int rr = np * 16 + (mid >> 1) * 8 + (lane & 7), c = ks * 2 + (mid & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kt + tile_off<HD>(rr, c), b0, b1, b2, b3);
+        mma16816<T>(sacc[np * 2], qf[ks], b0, b1);
+        mma16816<T>(sacc[np * 2 + 1], qf[ks], b2, b3);
       }
     }
+    // scale, cut at the end of the segment, softmax of this round against the running maximum
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = r * 64 + i * 8 + t4 * 2 + e;
+        const float v = j < nk ? sacc[i][e] * P.scale_log2 : -INFINITY;
+        sacc[i][e] = v;
+        mx = fmaxf(mx, v);
+        if (sg == P.logit_seg && qrow && j < nk) P.logits[(int64_t)h * S.len + j0 + j] = v;
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m, mx);
+    const float ms = mn == -INFINITY ? 0.f : mn;
+    const float al = exp2f(m - ms);
+    m = mn;
+    float rs = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sacc[i][0] = exp2f(sacc[i][0] - ms);
+      sacc[i][1] = exp2f(sacc[i][1] - ms);
+      rs += sacc[i][0] + sacc[i][1];
+    }
+    l = l * al + rs;
+    if (r > 0) {
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= al;
+        o[i][1] *= al;
+      }
+    }
+    cp_wait_upto(2 * ROUNDS - 2 - 2 * r);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t pa[4];
+      pa[0] = pack2<T>(sacc[2 * ks][0], sacc[2 * ks][1]);
+      pa[2] = pack2<T>(sacc[2 * ks + 1][0], sacc[2 * ks + 1][1]);
+      pa[1] = pa[3] = 0u;
+#pragma unroll
+      for (int dn = 0; dn < HD / 16; ++dn) {
+        const int mid = lane >> 3;
+        const int rr = ks * 16 + (mid & 1) * 8 + (lane & 7), c = dn * 2 + (mid >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vt + tile_off<HD>(rr, c), b0, b1, b2, b3);
+        mma16816<T>(o[dn * 2], pa, b0, b1);
+        mma16816<T>(o[dn * 2 + 1], pa, b2, b3);
+      }
+    }
   }
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (qrow) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float* po = P.part_o + ((int64_t)part * P.n_heads + h) * HD + t4 * 2;
 #pragma unroll
-  for (int gi = 0; gi < kMaxGroup; ++gi)
-    if (gi < group)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s_o[hw][gi][l16][e] = acc[gi][e];
-  __syncthreads();
-  for (int i = threadIdx.x; i < group * HD; i += kDecodeThreads) {
-    int gi = i / HD, d = i % HD;
-    float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < kDecodeThreads / 16; ++w) v += s_o[w][gi][d >> 3][d & 7];
-    int h = hkv * group + gi;
-    P.part_o[((int64_t)part * P.n_heads + h) * HD + d] = v / s_l[gi];
-    if (d == 0) P.part_lse[(int64_t)part * P.n_heads + h] = s_m[gi] + log2f(s_l[gi]);
+    for (int i = 0; i < HD / 8; ++i) *reinterpret_cast<float2*>(po + i * 8) = make_float2(o[i][0] * inv, o[i][1] * inv);
+    if (t4 == 0) P.part_lse[(int64_t)part * P.n_heads + h] = l > 0.f ? m + log2f(l) : -INFINITY;
   }
 }
 
-// out[h, :] = sum_p w_p o_p / sum_p w_p with w_p = exp2(lse_p - max lse); lse = max + log2(sum w)
+// out[h, :] = sum_p w_p o_p / sum_p w_p with w_p = exp2(lse_p - max lse); lse = max + log2(sum w).
+// One CTA per head: kMergeGroups groups of head_dim threads share the partials, eight loads in flight each.
+// With `logits` the CTA then adds this token's local attention row into the accumulated scores:
+// score[h, j] += exp2(logit[h, j] - lse[h]) — the column sums of a one-token exec block.
+constexpr int kMergeGroups = 8;
+constexpr int kMergeUnroll = 20;  // partials a thread keeps in flight: 8 groups x 20 cover 160 partials
+constexpr int kMergeCols = 4;     // score columns a thread keeps in flight: 4 x 1024 cover a 4096-token window
 template <typename T>
-__global__ void lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part,
-                                 int n_heads, int head_dim, T* __restrict__ out, int64_t o_hs,
-                                 float* __restrict__ lse) {
-  const int h = blockIdx.x;
-  float mx = -INFINITY;
-  for (int p = 0; p < n_part; ++p) mx = fmaxf(mx, part_lse[(int64_t)p * n_heads + h]);
-  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-    float num = 0.f, den = 0.f;
-    if (mx != -INFINITY) {
-      for (int p = 0; p < n_part; ++p) {
-        float w = exp2f(part_lse[(int64_t)p * n_heads + h] - mx);
-        den += w;
-        num = fmaf(w, part_o[((int64_t)p * n_heads + h) * head_dim + d], num);
-      }
-    }
-    out[(int64_t)h * o_hs + d] = Act<T>::from_f(den > 0.f ? num / den : 0.f);
-    if (d == 0 && lse) lse[h] = den > 0.f ? mx + log2f(den) : -INFINITY;
+__global__ void __launch_bounds__(1024)
+lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part, int n_heads,
+                 int head_dim, T* __restrict__ out, int64_t o_hs, float* __restrict__ lse,
+                 const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs) {
+  extern __shared__ float s_w[];  // n_part weights
+  __shared__ float s_red[32];
+  __shared__ float s_num[kMergeGroups][128];
+  __shared__ float s_mx, s_den;
+  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const int grp = tid / head_dim, d = tid % head_dim, ngrp = blockDim.x / head_dim;
+  // every global load of the common case is issued before the first one is needed
+  const float* po = part_o + (int64_t)h * head_dim + d;
+  const int64_t ps = (int64_t)n_heads * head_dim;
+  float pv[kMergeUnroll];
+#pragma unroll
+  for (int u = 0; u < kMergeUnroll; ++u) {
+    const int p = grp + u * ngrp;
+    pv[u] = p < n_part ? __ldcs(po + (int64_t)p * ps) : 0.f;
   }
-}
-
-// score[h, j] += exp2(logit[h, j] - lse[h]): the local-stage column sums of a one-token exec block
-__global__ void decode_score_kernel(const float* __restrict__ logits, int64_t len, const float* __restrict__ lse,
-                                    float* __restrict__ score, int64_t score_hs) {
-  int h = blockIdx.y;
-  int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= len) return;
-  score[h * score_hs + j] += exp2f(logits[h * len + j] - lse[h]);
-}
-
-int decode_score_launch(const float* logits, int64_t len, const float* lse, float* score, int64_t score_hs,
-                        int n_heads, cudaStream_t s) {
-  if (len <= 0) return INFLLM_OK;
-  dim3 grid((unsigned)ceil_div(len, 256), n_heads);
-  decode_score_kernel<<<grid, 256, 0, s>>>(logits, len, lse, score, score_hs);
-  INFLLM_LAUNCH_OK("decode_score_kernel");
-  return INFLLM_OK;
+  float lg[kMergeCols], sc[kMergeCols];
+#pragma unroll
+  for (int i = 0; i < kMergeCols; ++i) {
+    const int64_t j = tid + (int64_t)i * blockDim.x;
+    const bool ok = logits != nullptr && j < logit_len;
+    lg[i] = ok ? __ldcs(logits + h * logit_len + j) : 0.f;
+    sc[i] = ok ? score[h * score_hs + j] : 0.f;
+  }
+  float mx = -INFINITY;
+  for (int p = tid; p < n_part; p += blockDim.x) {
+    const float v = part_lse[(int64_t)p * n_heads + h];
+    s_w[p] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) s_red[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < nwarp ? s_red[lane] : -INFINITY;
+    v = warp_max(v);
+    if (lane == 0) s_mx = v;
+  }
+  __syncthreads();
+  mx = s_mx;
+  float den = 0.f;
+  if (mx != -INFINITY)
+    for (int p = tid; p < n_part; p += blockDim.x) {
+      const float w = exp2f(s_w[p] - mx);
+      s_w[p] = w;
+      den += w;
+    }
+  den = warp_sum(den);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = den;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < nwarp ? s_red[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) s_den = v;
+  }
+  __syncthreads();
+  den = s_den;
+  float num = 0.f;
+  if (mx != -INFINITY) {
+#pragma unroll
+    for (int u = 0; u < kMergeUnroll; ++u) {
+      const int p = grp + u * ngrp;
+      if (p < n_part) num = fmaf(s_w[p], pv[u], num);
+    }
+    for (int p = grp + kMergeUnroll * ngrp; p < n_part; p += ngrp) num = fmaf(s_w[p], __ldcs(po + (int64_t)p * ps), num);
+  }
+  s_num[grp][d] = num;
+  __syncthreads();
+  if (tid < head_dim) {
+    float tot = 0.f;
+    for (int g2 = 0; g2 < ngrp; ++g2) tot += s_num[g2][tid];
+    out[(int64_t)h * o_hs + tid] = Act<T>::from_f(den > 0.f ? tot / den : 0.f);
+  }
+  const float l = den > 0.f ? mx + log2f(den) : -INFINITY;
+  if (tid == 0 && lse) lse[h] = l;
+  if (logits) {
+#pragma unroll
+    for (int i = 0; i < kMergeCols; ++i) {
+      const int64_t j = tid + (int64_t)i * blockDim.x;
+      if (j < logit_len) score[h * score_hs + j] = sc[i] + exp2f(lg[i] - l);
+    }
+    for (int64_t j = tid + (int64_t)kMergeCols * blockDim.x; j < logit_len; j += blockDim.x)
+      score[h * score_hs + j] += exp2f(logits[h * logit_len + j] - l);
+  }
 }
 
 int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s) {
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk) {
+  if (chunk != 64 && chunk != 128) return fail(INFLLM_E_BADARG, "decode attention: chunk %d (64 or 128)", chunk);
   if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "decode attention: head_dim %d (128 is built)", head_dim);
   if (n_heads % n_kv_heads || n_heads / n_kv_heads > kMaxGroup)
     return fail(INFLLM_E_UNSUPPORTED, "decode attention: %d query heads per kv head (at most %d)",
@@ -231,7 +302,7 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
     P.qsel[ns] = (uint8_t)(seg_q[i] ? 1 : 0);
     P.part_begin[ns] = parts;
     if (i == logit_seg) logit_seg_packed = ns;
-    parts += (int)ceil_div(segs[i].len, kDecodeChunk);
+    parts += (int)ceil_div(segs[i].len, chunk);
     ++ns;
   }
   P.part_begin[ns] = parts;
@@ -243,16 +314,29 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
   P.part_o = part_o; P.part_lse = part_lse; P.logits = logits;
   P.scale_log2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid(parts, n_kv_heads);
-  INFLLM_DISPATCH_DTYPE(dtype, T, { attn_decode_kernel<128, T><<<grid, kDecodeThreads, 0, s>>>(P); });
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    if (chunk == 64) {
+      attn_decode_kernel<128, 1, T><<<grid, 32, 32 * 1024, s>>>(P);
+    } else {
+      auto kern = attn_decode_kernel<128, 2, T>;
+      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      kern<<<grid, 32, 64 * 1024, s>>>(P);
+    }
+  });
   INFLLM_LAUNCH_OK("attn_decode_kernel");
   return INFLLM_OK;
 }
 
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
-                     int64_t o_hs, float* lse, int dtype, cudaStream_t s) {
+                     int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
+                     float* score, int64_t score_hs) {
   if (n_part <= 0) return fail(INFLLM_E_BADARG, "lse_merge: no partials");
+  if (n_part > 8192) return fail(INFLLM_E_CAPACITY, "lse_merge: %d partials (at most 8192)", n_part);
+  if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
+    return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
   INFLLM_DISPATCH_DTYPE(dtype, T, {
-    lse_merge_kernel<T><<<n_heads, 128, 0, s>>>(part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse);
+    lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
+        part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs);
   });
   INFLLM_LAUNCH_OK("lse_merge_kernel");
   return INFLLM_OK;
@@ -277,7 +361,7 @@ extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_head
   KvSeg segs[kMaxSeg];
   for (int i = 0; i < n_seg; ++i) segs[i] = {h_seg_k[i], h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
   return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o, d_part_lse,
-                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream);
+                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream, kDecodeChunk);
 }
 
 // ------------------------------------------------------------------------ allocation-free variant
@@ -330,8 +414,8 @@ extern "C" int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, in
   // Nothing in the scratch has to start at zero: every partial the merge reads is written by the
   // split-K kernel of this same call, whatever an earlier call left behind.
   INFLLM_TRY(attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, part_o,
-                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s));
-  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s);
+                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, kDecodeChunk));
+  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0);
 }
 
 extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads,
@@ -339,5 +423,5 @@ extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, 
   using namespace infllm;
   if (!d_part_o || !d_part_lse || !d_out) return fail(INFLLM_E_BADARG, "lse_merge: null pointer");
   return lse_merge_launch(d_part_o, d_part_lse, n_part, n_heads, head_dim, d_out, o_hs, d_lse, dtype,
-                          (cudaStream_t)stream);
+                          (cudaStream_t)stream, nullptr, 0, nullptr, 0);
 }

@@ -479,7 +479,7 @@ __device__ __forceinline__ int stage_tiles(const AttnTcParams& P, const TcStage&
 }
 
 template <typename T>
-__global__ void __maxnreg__(112) attn_tc2_kernel(const __grid_constant__ AttnTcParams P) {
+__global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant__ AttnTcParams P) {
   using namespace tc2;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -1270,8 +1270,16 @@ int attn_tc2_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
       attr_set[dtype] = true;
     }
     kern<<<grid, 576, smem, s>>>(P);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+      cudaFuncAttributes fa{};
+      cudaFuncGetAttributes(&fa, kern);
+      return fail(INFLLM_E_CUDA, "launch of attn_tc2_kernel failed: %s (grid %u x %u x %u, 576 threads, %zu bytes dynamic + "
+                  "%zu static shared memory; the kernel uses %d registers, at most %d threads per CTA)",
+                  cudaGetErrorString(le), grid.x, grid.y, grid.z, smem, fa.sharedSizeBytes, fa.numRegs,
+                  fa.maxThreadsPerBlock);
+    }
   });
-  INFLLM_LAUNCH_OK("attn_tc2_kernel");
   if (P.n_split > 1) {
     const int64_t rows = (int64_t)P.n_heads * P.lq;
     INFLLM_DISPATCH_DTYPE(dtype, T, {

@@ -34,7 +34,7 @@ int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int6
 int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t len, int exc, int head_dim,
                 float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s);
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
-                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s);
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket);
 int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
                             int dtype, cudaStream_t s);
 int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
@@ -42,11 +42,15 @@ int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* s
                        int head_dim, void* out, int dtype, cudaStream_t s);
 int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s);
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk);
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
-                     int64_t o_hs, float* lse, int dtype, cudaStream_t s);
-int decode_score_launch(const float* logits, int64_t len, const float* lse, float* score, int64_t score_hs,
-                        int n_heads, cudaStream_t s);
+                     int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len, float* score,
+                     int64_t score_hs);
+int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs, const void* v, int64_t v_hs,
+                        void* q_loc, void* q_glb, int64_t qs_hs, float* qbar, void* k_raw, void* k_rot, void* v_out,
+                        int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
+                        const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
+                        int dtype, cudaStream_t s);
 
 // ------------------------------------------------------------------------------------- LRU table
 // cached_blocks[u] of the reference: a dict id -> stamp whose iteration (insertion) order breaks
@@ -121,6 +125,7 @@ struct TokenBuffers {
   float* score = nullptr; // (H, cap) accumulated local attention mass
   int64_t cap = 0;        // tokens
   int64_t t0 = 0;         // absolute token index of slot 0
+  int64_t zero_upto = 0;  // K and V rows in [end of data, zero_upto) are known to hold zeros
 };
 
 }  // namespace infllm
@@ -158,6 +163,7 @@ struct infllm_ctx {
   float* scores = nullptr;   // (scores_cap) unit scores
   int64_t scores_cap = 0;
   int32_t* d_topk = nullptr; // (topk)
+  unsigned int* tickets = nullptr;  // "last CTA" counters of the fused scoring kernel: [0] main stream, [1] look-ahead stream
   int32_t* h_topk = nullptr; // pinned
   float *part_o = nullptr, *part_lse = nullptr, *dec_logits = nullptr;
   int max_parts = 0;
@@ -362,6 +368,8 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->st_m, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMalloc((void**)&c->tickets, 2 * sizeof(unsigned int)));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->tickets, 0, 2 * sizeof(unsigned int), s));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   c->cand_cap = g.topk + (infllm_ctx::kLookDepth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
@@ -376,7 +384,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->mail_stream, cudaStreamNonBlocking));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
-  c->max_parts = (int)(dec_keys / 128 + g.topk + 8);
+  c->max_parts = (int)(dec_keys / 64 + g.topk + 8);
   INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
@@ -497,7 +505,7 @@ int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaS
   {
     ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
     INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
-                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s));
+                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s, c->tickets));
   }
   INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
@@ -530,7 +538,7 @@ int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)la.n_spec * c->width * c->esz);
   int32_t* d_ids = c->d_spec + (target % (infllm_ctx::kLookDepth + 1)) * std::max(1, g.topk);
   INFLLM_TRY(block_topk_launch(c->block_k, la.n_spec, (int)c->width, c->qbar + target * c->width, c->scores_aux,
-                               g.topk, 0, d_ids, nullptr, g.dtype, c->aux_stream));
+                               g.topk, 0, d_ids, nullptr, g.dtype, c->aux_stream, c->tickets + 1));
   INFLLM_CUDA_OK(cudaMemcpyAsync(la.h_ids, d_ids, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->aux_stream));
   trace_mark(c, c->aux_stream, TR_SPEC_END, target);
   INFLLM_CUDA_OK(cudaEventRecord(la.ev, c->aux_stream));
@@ -834,20 +842,19 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
   const int64_t kv_hs = tb.cap * D;  // head stride of the token buffers, elements
   // ---- ingest the new tokens
   const int64_t at = T - tb.t0;
-  INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
-  INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
-  INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
-  INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
+  const int64_t q_hs_s = c->sub_max * D;
   if (c->use_tc) {
-    // a 128-row tile that ends the window may reach past the last ingested token: keep those rows finite
-    const int64_t pad = std::min<int64_t>(128, tb.cap - (at + L));
-    if (pad > 0) {
+    // a 128-row tile that ends the window may reach past the last ingested token: keep those rows finite.
+    // Rows are zeroed well ahead of the data so that token-by-token appends rarely pay for it.
+    if (tb.zero_upto < std::min<int64_t>(tb.cap, at + L + 128)) {
+      const int64_t upto = std::min<int64_t>(tb.cap, at + L + 128 + 4096), pad = upto - (at + L);
       INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.v + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
       INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.k_rot + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
       INFLLM_CUDA_OK(cudaMemset2DAsync((char*)tb.k_raw + (at + L) * D * esz, kv_hs * esz, 0, pad * D * esz, HKV, s));
+      tb.zero_upto = upto;
     }
   }
-  // ---- RoPE: keys keep the position (token - rope_origin) until the table would run out
+  // RoPE: keys keep the position (token - rope_origin) until the table would run out
   const int64_t win0 = std::max<int64_t>(T - g.n_local, 0);  // oldest key any query of this call can see locally
   if (c->rope_origin < 0 || T + L - c->rope_origin > c->tab_len || win0 < c->rope_origin) {
     c->rope_origin = win0;
@@ -856,17 +863,29 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
                                    (char*)tb.k_rot + (win0 - tb.t0) * D * esz, kv_hs, D, (int)HKV, T - win0, (int)D,
                                    c->cos_t, c->sin_t, c->tab_len, 0, 1, g.dtype, s));
   }
-  INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + at * D * esz, kv_hs, D, (char*)tb.k_rot + at * D * esz, kv_hs, D,
-                               (int)HKV, L, (int)D, c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, 1, g.dtype,
-                               s));
-  // queries: window-relative rotation for the local stage, the single position n_local-1 for the
-  // global stage (context_manager.py:480 and :744-747)
-  const int64_t q_hs_s = c->sub_max * D;
-  INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_loc, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
-                               T - c->rope_origin, 1, g.dtype, s));
-  INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_glb, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
-                               g.n_local - 1, 0, g.dtype, s));
-  INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
+  if (L == 1) {
+    // one token: copies, the three rotations, the query mean and the cleared score column in one launch
+    INFLLM_TRY(ingest_token_launch(q, q_hs, k, k_hs, v, v_hs, c->q_loc, c->q_glb, q_hs_s, c->qbar,
+                                   (char*)tb.k_raw + at * D * esz, (char*)tb.k_rot + at * D * esz,
+                                   (char*)tb.v + at * D * esz, kv_hs, tb.score + at, tb.cap, (int)H, (int)HKV, (int)D,
+                                   c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, g.n_local - 1, g.dtype, s));
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
+  } else {
+    INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
+    INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
+    INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
+    INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + at * D * esz, kv_hs, D, (char*)tb.k_rot + at * D * esz, kv_hs, D,
+                                 (int)HKV, L, (int)D, c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, 1, g.dtype,
+                                 s));
+    // queries: window-relative rotation for the local stage, the single position n_local-1 for the
+    // global stage (context_manager.py:480 and :744-747)
+    INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_loc, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
+                                 T - c->rope_origin, 1, g.dtype, s));
+    INFLLM_TRY(rope_apply_launch(q, q_hs, q_ts, c->q_glb, q_hs_s, D, (int)H, L, (int)D, c->cos_t, c->sin_t, c->tab_len,
+                                 g.n_local - 1, 0, g.dtype, s));
+    INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
+  }
 
   std::vector<int32_t> ids;
   for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
@@ -937,11 +956,12 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
           return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
         INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
                                       qsel.data(), c->part_o, c->part_lse, c->max_parts, &parts, 0, c->dec_logits,
-                                      g.dtype, s));
+                                      g.dtype, s, 64));
         base = segs.size();
       }
-      INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s));
-      INFLLM_TRY(decode_score_launch(c->dec_logits, E - wlo, c->lse, tb.score + (wlo - tb.t0), tb.cap, (int)H, s));
+      // the merge also adds this token's local attention row into the accumulated scores
+      INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s,
+                                  c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap));
     } else {
       // ---- local stage + global stage, jointly normalised (context_manager.py:486-489, 526-533)
       double local_pairs = 0, all_glk = 0;
@@ -1159,7 +1179,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     cudaDeviceSynchronize();
     free_buffers(c->tb, nullptr);
     void* dev[] = {c->init_k, c->init_v, c->cos_t, c->sin_t, c->q_loc, c->q_glb, c->qbar, c->lse, c->st_acc, c->st_m,
-                   c->st_l, c->d_topk, c->part_o, c->part_lse, c->dec_logits, c->cache};
+                   c->st_l, c->d_topk, c->tickets, c->part_o, c->part_lse, c->dec_logits, c->cache};
     for (void* p : dev)
       if (p) cudaFree(p);
     if (c->block_k) cudaFreeAsync(c->block_k, nullptr);

@@ -1,13 +1,16 @@
 // Retrieval kernels: memory-unit scoring + top-k, and representative-key selection at sealing.
 //
-// block_score_kernel  HBM-streaming GEMV (one warp per representative-key row, 16-byte loads,
-//                     query mean staged in shared memory, fp32 accumulation).
-// topk_argmax_kernel  k <= 64 over <= 8192 scores: per-thread register sort, per-warp pops, one final warp merge.
-// topk_select_kernel  any size: 4-pass 8-bit radix select of the k-th largest score, then an
-//                     index-ordered gather of the winners and a rank sort.  Both: descending score,
-//                     ties to the lower id.
+// block_score_topk_kernel  k <= 64 over <= 8192 units, the usual case: HBM-streaming GEMV (one warp per
+//                     representative-key row, 16-byte loads, query mean staged in shared memory, fp32
+//                     accumulation) whose last CTA ranks the scores (bitonic sort of per-thread maxima,
+//                     threshold, rank sort of the few candidates).
+// block_score_kernel + topk_select_kernel  any size: the same GEMV, then a 4-pass 8-bit radix select of the
+//                     k-th largest score, an index-ordered gather of the winners and a rank sort.
+//                     Both: descending score, ties to the lower id.
 // repr_select_kernel  per (new unit, query head): repr_topk arg-max rounds over the accumulated
 //                     local scores, gather + mean of the chosen un-rotated keys.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace infllm {
@@ -204,96 +207,164 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
   }
 }
 
-// Small k (the usual topk of 16-64) over at most 8192 scores, one CTA of 32 warps.  Every thread sorts its 8
-// strided scores in registers; every warp then pops its k best by repeatedly taking the best of the 32 lane
-// heads (warp shuffles only); finally warp 0 pops the k best of the 32 sorted warp lists.  No CTA-wide
-// barrier inside the loops.  Order: descending score, ties to the lower id (NaN scores rank last).
-constexpr int kArgmaxItems = 8;
-struct ScoreId {
-  float v;
-  int i;
-};
-__device__ __forceinline__ bool before(float av, int ai, float bv, int bi) {
-  return av > bv || (av == bv && ai < bi);
+// ---------------------------------------------------------------------------------------------------------
+// Fast path for the usual sizes (k <= 64 over at most 8192 scores), one CTA of 1024 threads.
+//
+// Every score becomes a 64-bit key: (order-preserving bits of the score) << 32 | ~id, so that a larger key
+// means "ranks earlier" (higher score, then lower id) and no two keys are equal.  Thread t keeps the keys of
+// scores t, t + 1024, ... in registers; four neighbouring threads form a group of 32 scores.
+//   1. bitonic sort (descending) of the 256 group maxima by the first eight warps: shuffles for partner
+//      distances below 32, shared memory above.  The k-th of them, tau, is a lower bound of the k-th largest
+//      key overall, and exactly k groups hold a maximum >= tau.
+//   2. every key >= tau is a candidate: at most 32k of them (a few more than k unless the scores are laid out
+//      adversarially), appended to a shared list.
+//   3. rank sort of the candidates; the first k leave in order.
+// No loop waits on data of another CTA.
+constexpr int kFastItems = 8;
+constexpr int kFastMaxK = 64;
+constexpr int kFastMaxN = kFastItems * kTopkThreads;
+constexpr int kFastGroups = kTopkThreads / 4;
+constexpr int kFastCand = 32 * kFastMaxK;
+
+__device__ __forceinline__ unsigned long long topk_key(float v, int id) {
+  if (!(v == v)) v = -INFINITY;  // NaN ranks with -inf
+  return ((unsigned long long)float_key(v) << 32) | (uint32_t)(~(uint32_t)id);
 }
-__global__ void __launch_bounds__(kTopkThreads)
-topk_argmax_kernel(const float* __restrict__ scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
-                   float* __restrict__ out_scores) {
-  extern __shared__ unsigned char dyn[];
-  float* cv = reinterpret_cast<float*>(dyn);           // [32 warps][k] values
-  int* ci = reinterpret_cast<int*>(cv + 32 * k);        // [32 warps][k] ids
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float v[kArgmaxItems];
-  int id[kArgmaxItems];
+__device__ __forceinline__ unsigned long long max64(unsigned long long a, unsigned long long b) { return a > b ? a : b; }
+
+// `gm` holds kFastGroups keys, `cand` kFastCand keys, `s_cnt` one int.  All 1024 threads call.
+__device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
+                              float* __restrict__ out_scores, unsigned long long* gm, unsigned long long* cand,
+                              int* s_cnt) {
+  const int tid = threadIdx.x;
+  unsigned long long key[kFastItems];
 #pragma unroll
-  for (int e = 0; e < kArgmaxItems; ++e) {
-    int i = tid + e * kTopkThreads;
-    float x = i < n ? scores[i] : -INFINITY;
-    v[e] = (x == x) ? x : -INFINITY;
-    id[e] = i < n ? i : 0x7fffffff;
+  for (int e = 0; e < kFastItems; ++e) {
+    const int i = tid + e * kTopkThreads;
+    key[e] = i < n ? topk_key(__ldcg(scores + i), i) : 0ull;  // 0: below every real key
   }
-  // odd-even transposition sort of the 8 register pairs, best first
+  unsigned long long x = key[0];
 #pragma unroll
-  for (int pass = 0; pass < kArgmaxItems; ++pass) {
-#pragma unroll
-    for (int e = pass & 1; e + 1 < kArgmaxItems; e += 2) {
-      if (before(v[e + 1], id[e + 1], v[e], id[e])) {
-        float tv = v[e]; v[e] = v[e + 1]; v[e + 1] = tv;
-        int ti = id[e]; id[e] = id[e + 1]; id[e + 1] = ti;
+  for (int e = 1; e < kFastItems; ++e) x = max64(x, key[e]);
+  x = max64(x, __shfl_xor_sync(0xffffffffu, x, 1));
+  x = max64(x, __shfl_xor_sync(0xffffffffu, x, 2));
+  if ((tid & 3) == 0) gm[tid >> 2] = x;
+  if (tid == 0) *s_cnt = 0;
+  __syncthreads();
+  // ---- 1. bitonic sort of the group maxima, descending in thread order, by threads 0..255
+  if (tid < kFastGroups) {
+    x = gm[tid];
+    for (int size = 2; size <= kFastGroups; size <<= 1) {
+      const bool desc = (tid & size) == 0;  // this run sorts descending
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        unsigned long long y;
+        if (stride >= 32) {
+          asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");  // earlier reads of gm are done
+          gm[tid] = x;
+          asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");
+          y = gm[tid ^ stride];
+        } else {
+          y = __shfl_xor_sync(0xffffffffu, x, stride);
+        }
+        const bool lower = (tid & stride) == 0;  // the partner with the smaller index
+        x = (lower == desc) ? (x > y ? x : y) : (x < y ? x : y);
       }
     }
-  }
-  // the warp's k best: pop the best lane head k times
-  for (int r = 0; r < k; ++r) {
-    float bv = v[0];
-    int bi = id[0];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (before(ov, oi, bv, bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) {
-      cv[warp * k + r] = bv;
-      ci[warp * k + r] = bi;
-    }
-    if (id[0] == bi && bi != 0x7fffffff) {  // this lane owned the winner: shift its list up
-#pragma unroll
-      for (int e = 0; e + 1 < kArgmaxItems; ++e) {
-        v[e] = v[e + 1];
-        id[e] = id[e + 1];
-      }
-      v[kArgmaxItems - 1] = -INFINITY;
-      id[kArgmaxItems - 1] = 0x7fffffff;
-    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");
+    gm[tid] = x;
   }
   __syncthreads();
-  if (warp == 0) {
-    int head = 0;  // lane l walks warp l's sorted list
-    for (int r = 0; r < k; ++r) {
-      float hv = head < k ? cv[lane * k + head] : -INFINITY;
-      int hi = head < k ? ci[lane * k + head] : 0x7fffffff;
-      float bv = hv;
-      int bi = hi;
+  const unsigned long long tau = gm[k - 1];
+  // ---- 2. candidates
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (before(ov, oi, bv, bi)) {
-          bv = ov;
-          bi = oi;
-        }
-      }
-      if (hi == bi && bi != 0x7fffffff) ++head;
-      if (lane == 0) {
-        out_ids[r] = (bi == 0x7fffffff ? 0 : bi) + id_base;
-        if (out_scores) out_scores[r] = bv;
-      }
+  for (int e = 0; e < kFastItems; ++e)
+    if (key[e] >= tau && key[e] != 0ull) {
+      int p = atomicAdd(s_cnt, 1);
+      if (p < kFastCand) cand[p] = key[e];
+    }
+  __syncthreads();
+  const int nc = *s_cnt < kFastCand ? *s_cnt : kFastCand;  // k <= nc <= 32k
+  // ---- 3. rank of every candidate = how many candidates rank before it
+  for (int c = tid; c < nc; c += kTopkThreads) {
+    const unsigned long long mine = cand[c];
+    int rank = 0;
+    for (int j = 0; j < nc; ++j) rank += cand[j] > mine;
+    if (rank < k) {
+      const int id = (int)(~(uint32_t)(mine & 0xffffffffu));
+      out_ids[rank] = id + id_base;
+      if (out_scores) out_scores[rank] = __ldcg(scores + id);
     }
   }
+}
+
+__global__ void __launch_bounds__(kTopkThreads)
+topk_fast_kernel(const float* __restrict__ scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
+                 float* __restrict__ out_scores) {
+  __shared__ unsigned long long sm[kFastGroups];
+  __shared__ unsigned long long cand[kFastCand];
+  __shared__ int s_cnt;
+  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt);
+}
+
+// Scoring and top-k in one launch: CTAs of 32 warps stream the representative keys (one warp per row, the whole
+// row's 16-byte loads in flight at once); the CTA that finishes last — known from a ticket counter, nobody
+// waits — ranks the scores.  `ticket` must be zero at launch and is zero again when the kernel ends.
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads)
+block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float* __restrict__ qbar,
+                        float* __restrict__ scores, int k, int id_base, int32_t* __restrict__ out_ids,
+                        float* __restrict__ out_scores, unsigned int* __restrict__ ticket) {
+  extern __shared__ __align__(16) unsigned char dyn_raw[];
+  float* sq = reinterpret_cast<float*>(dyn_raw);
+  __shared__ unsigned long long sm[kFastGroups];
+  __shared__ unsigned long long cand[kFastCand];
+  __shared__ int s_cnt;
+  __shared__ bool s_last;
+  for (int i = threadIdx.x; i < width; i += kTopkThreads) sq[i] = qbar[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * 32 + warp; row < n; row += gridDim.x * 32) {
+    const T* p = bk + (int64_t)row * width;
+    float acc = 0.f;
+    for (int c0 = 0; c0 < width; c0 += 32 * 8 * 8) {
+      uint4 raw[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + (u * 32 + lane) * 8;
+        raw[u] = c < width ? __ldcs(reinterpret_cast<const uint4*>(p + c)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int c = c0 + (u * 32 + lane) * 8;
+        if (c < width) {
+          const typename Act<T>::T2* v2 = reinterpret_cast<const typename Act<T>::T2*>(&raw[u]);
+          const float4 qa = *reinterpret_cast<const float4*>(sq + c);
+          const float4 qb = *reinterpret_cast<const float4*>(sq + c + 4);
+          float2 f0 = Act<T>::to_f2(v2[0]), f1 = Act<T>::to_f2(v2[1]), f2 = Act<T>::to_f2(v2[2]),
+                 f3 = Act<T>::to_f2(v2[3]);
+          acc = fmaf(f0.x, qa.x, acc);
+          acc = fmaf(f0.y, qa.y, acc);
+          acc = fmaf(f1.x, qa.z, acc);
+          acc = fmaf(f1.y, qa.w, acc);
+          acc = fmaf(f2.x, qb.x, acc);
+          acc = fmaf(f2.y, qb.y, acc);
+          acc = fmaf(f3.x, qb.z, acc);
+          acc = fmaf(f3.y, qb.w, acc);
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) scores[row] = acc;
+  }
+  if (!ticket) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) *ticket = 0;
+  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt);
 }
 
 template <typename T>
@@ -356,23 +427,32 @@ __global__ void repr_select_kernel(const T* __restrict__ k, int64_t k_hs, int64_
 }
 
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
-                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s) {
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket) {
   if (n <= 0 || k <= 0 || k > n) return fail(INFLLM_E_BADARG, "block_topk: need 0 < k <= n_blocks (k=%d n=%lld)", k, (long long)n);
   if (k > 1024) return fail(INFLLM_E_UNSUPPORTED, "block_topk: k=%d > 1024", k);
   if (width % 8 != 0 || width > 12 * 1024 || ((uintptr_t)bk % 16) != 0)
     return fail(INFLLM_E_BADARG, "block_topk: width %d must be a multiple of 8, at most 12288, rows 16-byte aligned", width);
+  if (k <= kFastMaxK && n <= kFastMaxN) {
+    // one launch when the caller lends a ticket counter, else scoring and ranking back to back
+    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(n, 32), 148);
+    INFLLM_DISPATCH_DTYPE(dtype, T, {
+      block_score_topk_kernel<T><<<grid, kTopkThreads, width * sizeof(float), s>>>(
+          (const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores, ticket);
+    });
+    INFLLM_LAUNCH_OK("block_score_topk_kernel");
+    if (!ticket) {
+      topk_fast_kernel<<<1, kTopkThreads, 0, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
+      INFLLM_LAUNCH_OK("topk_fast_kernel");
+    }
+    return INFLLM_OK;
+  }
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     block_score_kernel<T><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
         (const T*)bk, n, width, qbar, scores);
   });
   INFLLM_LAUNCH_OK("block_score_kernel");
-  if (k <= 64 && n <= (int64_t)kArgmaxItems * kTopkThreads) {
-    topk_argmax_kernel<<<1, kTopkThreads, 32 * k * 8, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
-    INFLLM_LAUNCH_OK("topk_argmax_kernel");
-  } else {
-    topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
-    INFLLM_LAUNCH_OK("topk_select_kernel");
-  }
+  topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
+  INFLLM_LAUNCH_OK("topk_select_kernel");
   return INFLLM_OK;
 }
 
@@ -416,7 +496,7 @@ extern "C" int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int wi
   using namespace infllm;
   if (!d_block_k || !d_qbar || !d_scores || !d_out_ids) return fail(INFLLM_E_BADARG, "block_topk: null pointer");
   return block_topk_launch(d_block_k, n_blocks, width, d_qbar, d_scores, k, id_base, d_out_ids, d_out_scores, dtype,
-                           (cudaStream_t)stream);
+                           (cudaStream_t)stream, nullptr);
 }
 
 extern "C" int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float* d_score,

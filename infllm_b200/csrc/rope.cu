@@ -154,6 +154,64 @@ int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int6
   return INFLLM_OK;
 }
 
+// One new token (decode): what the per-token launches of an append do — copy K and V into the token buffers,
+// rotate K to its window position, rotate Q both ways, take the query "mean" of the one-token exec block and
+// clear the token's score column — as one launch.  CTA b < n_heads handles query head b, the others one KV
+// head each; thread i owns the element pair (i, i + head_dim/2).  Same arithmetic as rope_apply_kernel.
+template <typename T>
+__global__ void ingest_token_kernel(const T* __restrict__ q, int64_t q_hs, const T* __restrict__ k, int64_t k_hs,
+                                    const T* __restrict__ v, int64_t v_hs, T* __restrict__ q_loc,
+                                    T* __restrict__ q_glb, int64_t qs_hs, float* __restrict__ qbar,
+                                    T* __restrict__ k_raw, T* __restrict__ k_rot, T* __restrict__ v_out,
+                                    int64_t kv_hs, float* __restrict__ score, int64_t score_hs, int n_heads,
+                                    int head_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                    int64_t pos_loc, int64_t pos_glb) {
+  const int half = head_dim / 2, i = threadIdx.x, b = blockIdx.x;
+  if (i >= half) return;
+  const float cl = cos_t[pos_loc * half + i], sl = sin_t[pos_loc * half + i];
+  if (b < n_heads) {
+    const float x1 = Act<T>::to_f(q[b * q_hs + i]), x2 = Act<T>::to_f(q[b * q_hs + i + half]);
+    const float cg = cos_t[pos_glb * half + i], sg = sin_t[pos_glb * half + i];
+    q_loc[b * qs_hs + i] = Act<T>::from_f(__fadd_rn(__fmul_rn(x1, cl), __fmul_rn(-x2, sl)));
+    q_loc[b * qs_hs + i + half] = Act<T>::from_f(__fadd_rn(__fmul_rn(x2, cl), __fmul_rn(x1, sl)));
+    const T g1 = Act<T>::from_f(__fadd_rn(__fmul_rn(x1, cg), __fmul_rn(-x2, sg)));
+    const T g2 = Act<T>::from_f(__fadd_rn(__fmul_rn(x2, cg), __fmul_rn(x1, sg)));
+    q_glb[b * qs_hs + i] = g1;
+    q_glb[b * qs_hs + i + half] = g2;
+    qbar[(int64_t)b * head_dim + i] = Act<T>::to_f(g1);
+    qbar[(int64_t)b * head_dim + i + half] = Act<T>::to_f(g2);
+    if (i == 0) score[b * score_hs] = 0.f;
+  } else {
+    const int hk = b - n_heads;
+    const T r1 = k[hk * k_hs + i], r2 = k[hk * k_hs + i + half];
+    k_raw[hk * kv_hs + i] = r1;
+    k_raw[hk * kv_hs + i + half] = r2;
+    v_out[hk * kv_hs + i] = v[hk * v_hs + i];
+    v_out[hk * kv_hs + i + half] = v[hk * v_hs + i + half];
+    const float x1 = Act<T>::to_f(r1), x2 = Act<T>::to_f(r2);
+    k_rot[hk * kv_hs + i] = Act<T>::from_f(__fadd_rn(__fmul_rn(x1, cl), __fmul_rn(-x2, sl)));
+    k_rot[hk * kv_hs + i + half] = Act<T>::from_f(__fadd_rn(__fmul_rn(x2, cl), __fmul_rn(x1, sl)));
+  }
+}
+
+int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs, const void* v, int64_t v_hs,
+                        void* q_loc, void* q_glb, int64_t qs_hs, float* qbar, void* k_raw, void* k_rot, void* v_out,
+                        int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
+                        const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
+                        int dtype, cudaStream_t s) {
+  if (head_dim % 2 || head_dim > 2048) return fail(INFLLM_E_BADARG, "ingest: head_dim %d", head_dim);
+  if (pos_loc < 0 || pos_loc >= table_len || pos_glb < 0 || pos_glb >= table_len)
+    return fail(INFLLM_E_BADARG, "ingest: positions %lld / %lld outside the table of %lld rows", (long long)pos_loc,
+                (long long)pos_glb, (long long)table_len);
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    ingest_token_kernel<T><<<n_heads + n_kv_heads, head_dim / 2, 0, s>>>(
+        (const T*)q, q_hs, (const T*)k, k_hs, (const T*)v, v_hs, (T*)q_loc, (T*)q_glb, qs_hs, qbar, (T*)k_raw, (T*)k_rot,
+        (T*)v_out, kv_hs, score, score_hs, n_heads, head_dim, cos_t, sin_t, pos_loc, pos_glb);
+  });
+  INFLLM_LAUNCH_OK("ingest_token_kernel");
+  return INFLLM_OK;
+}
+
 int rope_apply_launch(const void* x, int64_t x_hs, int64_t x_ts, void* out, int64_t o_hs, int64_t o_ts,
                       int n_heads, int64_t len, int head_dim, const float* cos_t, const float* sin_t,
                       int64_t table_len, int64_t pos0, int pos_step, int dtype, cudaStream_t s) {
