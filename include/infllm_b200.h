@@ -186,7 +186,12 @@ typedef struct infllm_config {
   float rope_base, rope_scale;
   int32_t device;         /* CUDA device ordinal */
   int32_t shard_rank, shard_world; /* unit-range sharding of the store; 0,1 = not sharded */
-  int32_t reserved[6];
+  int32_t reserved[6];    /* zero, except reserved[0]: debugging switches, one per bit —
+                           *  1: exec blocks on the shape-generic mma.sync kernels, no tcgen05 kernels
+                           *  2: no look-ahead retrieval: every exec block waits for its ids from the device
+                           *  4: look-ahead units staged by an SM copy kernel instead of one cudaMemcpyAsync each
+                           *  8: the two-heads-per-CTA tcgen05 attention kernel (experimental)
+                           * 16: one-token appends wait for the retrieved ids before launching the attention */
 } infllm_config;
 
 /* Validates the configuration (exc_block_size <= n_local, context_manager.py:219;

@@ -79,6 +79,8 @@ class ContextManager:
             cfg.reserved[0] |= 8  # experimental: two query heads of a KV head per CTA share every K/V tile
         if os.environ.get("INFLLM_B200_STAGE_KERNEL", "0") == "1":
             cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
+        if os.environ.get("INFLLM_B200_NO_DECODE_SPEC", "0") == "1":
+            cfg.reserved[0] |= 16  # debugging aid: one-token appends wait for the retrieved ids before the attention
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))

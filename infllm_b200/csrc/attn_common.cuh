@@ -63,7 +63,28 @@ __device__ __forceinline__ bool mask_keep(int mode, int64_t off, int64_t size, i
   return true;
 }
 
+// Decode attention whose unit segments are resolved on the device: segment first_seg + i of the launch holds
+// the unit ids[i], found in cache slot table[ids[i]].  This lets the attention follow the top-k kernel on the
+// stream before the host has seen the ids; the chunks of a unit that turns out not to be cached get weight
+// zero and *miss = 1, and the host, which learns the same from its own tables, launches those units again
+// after the refill (further partials, part_base on) and merges then.
+struct DecodeIndirect {
+  const int32_t* ids = nullptr;    // n_units unit ids (device memory)
+  const int32_t* table = nullptr;  // unit id -> cache slot, -1 when the unit is not cached (device memory)
+  const char* cache = nullptr;     // slot 0
+  int64_t unit_bytes = 0;          // K then V of one unit
+  int32_t n_units = 0, first_seg = 0;
+  int32_t* miss = nullptr;
+};
+
 int attn_general_launch(const AttnParams& p, int head_dim, int dtype, cudaStream_t s);
+int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
+                       const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk,
+                       const DecodeIndirect* ind, int part_base);
+int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
+                     int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
+                     float* score, int64_t score_hs, const int32_t* skip);
 int attn_colsum_launch(const void* q, int64_t q_hs, int64_t q_ts, const void* k, int64_t k_hs, int64_t k_ts,
                        int n_heads, int n_kv_heads, int64_t lq, int64_t lk, int head_dim, int mask_mode,
                        int64_t mask_offset, int64_t mask_size, const float* lse, float* score, int64_t score_hs,

@@ -36,6 +36,7 @@ struct DecodeParams {
   float* part_lse;    // (n_part, H)
   float* logits;      // (H, seg_len[logit_seg])
   float scale_log2;
+  DecodeIndirect ind; // n_units == 0: every segment carries its own pointers
 };
 
 // wait until at most n of this thread's cp.async groups are pending (n is a constant after unrolling)
@@ -68,8 +69,27 @@ __global__ void __launch_bounds__(32) attn_decode_kernel(const __grid_constant__
   const DecodeSeg& S = P.seg[sg];
   const int j0 = (part - P.part_begin[sg]) * kChunk;
   const int nk = (S.len - j0) < kChunk ? (S.len - j0) : kChunk;
-  const T* kbase = (const T*)S.k + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
-  const T* vbase = (const T*)S.v + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
+  const void* seg_k = S.k;
+  const void* seg_v = S.v;
+  if (P.ind.n_units > 0) {
+    const int u = sg - P.ind.first_seg;
+    if (u >= 0 && u < P.ind.n_units) {
+      const int slot = __ldg(P.ind.table + __ldg(P.ind.ids + u));
+      if (slot < 0) {
+        // not cached: this chunk's partials get weight zero here; the host launches the unit again after the refill
+        if (lane == 0) *P.ind.miss = 1;
+        const int grp = P.n_heads / P.n_kv_heads;
+        for (int i = lane; i < grp * HD; i += 32)
+          P.part_o[((int64_t)part * P.n_heads + hkv * grp + i / HD) * HD + i % HD] = 0.f;
+        if (lane < grp) P.part_lse[(int64_t)part * P.n_heads + hkv * grp + lane] = -INFINITY;
+        return;
+      }
+      seg_k = P.ind.cache + (int64_t)slot * P.ind.unit_bytes;
+      seg_v = (const char*)seg_k + P.ind.unit_bytes / 2;
+    }
+  }
+  const T* kbase = (const T*)seg_k + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
+  const T* vbase = (const T*)seg_v + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
   // ---- all loads of the chunk: groups K0, V0, K1, V1 ...; rows past the end are zero-filled
 #pragma unroll
   for (int r = 0; r < ROUNDS; ++r) {
@@ -195,8 +215,10 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part, int n_heads,
                  int head_dim, T* __restrict__ out, int64_t o_hs, float* __restrict__ lse,
-                 const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs) {
+                 const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs,
+                 const int32_t* __restrict__ skip) {
   extern __shared__ float s_w[];  // n_part weights
+  if (skip && *skip) return;  // the partials were not written: a retrieved unit was not cached
   __shared__ float s_red[32];
   __shared__ float s_num[kMergeGroups][128];
   __shared__ float s_mx, s_den;
@@ -284,7 +306,8 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
 
 int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk) {
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk,
+                       const DecodeIndirect* ind, int part_base) {
   if (chunk != 64 && chunk != 128) return fail(INFLLM_E_BADARG, "decode attention: chunk %d (64 or 128)", chunk);
   if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "decode attention: head_dim %d (128 is built)", head_dim);
   if (n_heads % n_kv_heads || n_heads / n_kv_heads > kMaxGroup)
@@ -292,10 +315,19 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
                 n_kv_heads ? n_heads / n_kv_heads : 0, kMaxGroup);
   if (n_seg <= 0 || n_seg > kMaxSeg) return fail(INFLLM_E_BADARG, "decode attention: %d segments (1..%d)", n_seg, kMaxSeg);
   DecodeParams P{};
+  if (ind && ind->n_units > 0) {
+    if (!ind->ids || !ind->table || !ind->cache || !ind->miss || ind->first_seg < 0 ||
+        ind->first_seg + ind->n_units > n_seg)
+      return fail(INFLLM_E_BADARG, "decode attention: bad device-resolved unit list");
+    for (int i = 0; i < ind->n_units; ++i)
+      if (segs[ind->first_seg + i].len <= 0) return fail(INFLLM_E_BADARG, "decode attention: empty unit segment");
+    P.ind = *ind;
+  }
   int parts = 0, ns = 0;
   int logit_seg_packed = -1;
   for (int i = 0; i < n_seg; ++i) {
     if (segs[i].len <= 0) continue;  // empty segments contribute nothing
+    if (ind && ind->n_units > 0 && i == ind->first_seg) P.ind.first_seg = ns;
     if (((uintptr_t)segs[i].k | (uintptr_t)segs[i].v) % 16 || segs[i].hs % 8 || segs[i].ts % 8)
       return fail(INFLLM_E_BADARG, "decode attention: segment %d rows are not 16-byte aligned", i);
     P.seg[ns] = {segs[i].k, segs[i].v, segs[i].hs, segs[i].ts, segs[i].len};
@@ -308,10 +340,13 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
   P.part_begin[ns] = parts;
   if (n_parts_out) *n_parts_out = parts;
   if (parts == 0) return INFLLM_OK;
-  if (parts > max_parts) return fail(INFLLM_E_CAPACITY, "decode attention: %d partials exceed the scratch for %d", parts, max_parts);
+  if (part_base < 0 || part_base + parts > max_parts)
+    return fail(INFLLM_E_CAPACITY, "decode attention: %d partials exceed the scratch for %d", part_base + parts, max_parts);
   P.n_seg = ns; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.logit_seg = logit_seg_packed;
   P.q[0] = q0; P.q[1] = q1 ? q1 : q0; P.q_hs = q_hs;
-  P.part_o = part_o; P.part_lse = part_lse; P.logits = logits;
+  P.part_o = part_o + (int64_t)part_base * n_heads * head_dim;
+  P.part_lse = part_lse + (int64_t)part_base * n_heads;
+  P.logits = logits;
   P.scale_log2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid(parts, n_kv_heads);
   INFLLM_DISPATCH_DTYPE(dtype, T, {
@@ -329,14 +364,14 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
 
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
                      int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
-                     float* score, int64_t score_hs) {
+                     float* score, int64_t score_hs, const int32_t* skip) {
   if (n_part <= 0) return fail(INFLLM_E_BADARG, "lse_merge: no partials");
   if (n_part > 8192) return fail(INFLLM_E_CAPACITY, "lse_merge: %d partials (at most 8192)", n_part);
   if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
     return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
-        part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs);
+        part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
   });
   INFLLM_LAUNCH_OK("lse_merge_kernel");
   return INFLLM_OK;
@@ -361,7 +396,7 @@ extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_head
   KvSeg segs[kMaxSeg];
   for (int i = 0; i < n_seg; ++i) segs[i] = {h_seg_k[i], h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
   return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o, d_part_lse,
-                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream, kDecodeChunk);
+                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream, kDecodeChunk, nullptr, 0);
 }
 
 // ------------------------------------------------------------------------ allocation-free variant
@@ -414,8 +449,8 @@ extern "C" int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, in
   // Nothing in the scratch has to start at zero: every partial the merge reads is written by the
   // split-K kernel of this same call, whatever an earlier call left behind.
   INFLLM_TRY(attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, part_o,
-                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, kDecodeChunk));
-  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0);
+                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, kDecodeChunk, nullptr, 0));
+  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0, nullptr);
 }
 
 extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads,
@@ -423,5 +458,5 @@ extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, 
   using namespace infllm;
   if (!d_part_o || !d_part_lse || !d_out) return fail(INFLLM_E_BADARG, "lse_merge: null pointer");
   return lse_merge_launch(d_part_o, d_part_lse, n_part, n_heads, head_dim, d_out, o_hs, d_lse, dtype,
-                          (cudaStream_t)stream, nullptr, 0, nullptr, 0);
+                          (cudaStream_t)stream, nullptr, 0, nullptr, 0, nullptr);
 }

@@ -13,6 +13,7 @@
 // max_cached_block cache slots with cudaMemcpyAsync when retrieval asks for them.
 #include <algorithm>
 #include <chrono>
+#include <future>
 #include <list>
 #include <unordered_map>
 #include <vector>
@@ -40,17 +41,12 @@ int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int widt
 int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
                        int64_t tok0, int n_new, int block_size, int repr_topk, int n_heads, int n_kv_heads,
                        int head_dim, void* out, int dtype, cudaStream_t s);
-int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
-                       const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk);
-int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
-                     int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len, float* score,
-                     int64_t score_hs);
 int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs, const void* v, int64_t v_hs,
                         void* q_loc, void* q_glb, int64_t qs_hs, float* qbar, void* k_raw, void* k_rot, void* v_out,
                         int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
                         const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
-                        int dtype, cudaStream_t s);
+                        int dtype, cudaStream_t s, int32_t* clear);
+int slot_table_update_launch(int32_t* table, const int32_t* ids, const int32_t* slots, int n, cudaStream_t s);
 
 // ------------------------------------------------------------------------------------- LRU table
 // cached_blocks[u] of the reference: a dict id -> stamp whose iteration (insertion) order breaks
@@ -172,7 +168,15 @@ struct infllm_ctx {
   void* cache = nullptr;  // (max_cached, 2, H_kv, bs, D)
   std::vector<int> free_slots;
   std::unordered_map<int32_t, int> slot_of;
+  // device copy of slot_of for the decode attention that resolves the retrieved units itself
+  int32_t* d_slot_table = nullptr;
+  int64_t tab_cap = 0;
+  bool table_valid = false;                          // false: rebuild from slot_of before the next use
+  std::unordered_map<int32_t, int32_t> tab_updates;  // entries changed since the last flush
+  int32_t* d_miss = nullptr;                         // set by the attention when a retrieved unit is not cached
   std::vector<void*> slabs;  // pinned host memory
+  std::future<void*> slab_future;  // the next slab, being pinned by a helper thread
+  bool slab_pending = false;
   int64_t slab_units = 0;
   LruTable lru{0};
 
@@ -368,6 +372,8 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->st_m, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_miss, sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->d_miss, 0, sizeof(int32_t), s));
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->tickets, 2 * sizeof(unsigned int)));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->tickets, 0, 2 * sizeof(unsigned int), s));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
@@ -384,7 +390,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->mail_stream, cudaStreamNonBlocking));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
-  c->max_parts = (int)(dec_keys / 64 + g.topk + 8);
+  c->max_parts = (int)(dec_keys / 64 + g.topk + 8 + (int64_t)g.topk * ((g.block_size + 63) / 64));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
@@ -471,13 +477,35 @@ int ensure_block_k(infllm_ctx* c, int64_t n, cudaStream_t s) {
   return INFLLM_OK;
 }
 
+// Pinning a slab takes tens of milliseconds; a helper thread does it ahead of need
+void* alloc_slab(int device, size_t bytes) {
+  void* p = nullptr;
+  if (cudaSetDevice(device) != cudaSuccess || cudaHostAlloc(&p, bytes, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+
 int ensure_host_units(infllm_ctx* c, int64_t n) {
+  const size_t bytes = (size_t)(c->slab_units * c->unit_bytes);
   while ((int64_t)c->slabs.size() * c->slab_units < n) {
     void* p = nullptr;
-    cudaError_t e = cudaHostAlloc(&p, c->slab_units * c->unit_bytes, cudaHostAllocDefault);
-    if (e != cudaSuccess) return fail(INFLLM_E_NOMEM, "pinned host store: cudaHostAlloc of %lld bytes failed: %s",
-                                      (long long)(c->slab_units * c->unit_bytes), cudaGetErrorString(e));
+    if (c->slab_pending) {
+      p = c->slab_future.get();
+      c->slab_pending = false;
+    }
+    if (!p) {
+      cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocDefault);
+      if (e != cudaSuccess) return fail(INFLLM_E_NOMEM, "pinned host store: cudaHostAlloc of %lld bytes failed: %s",
+                                        (long long)bytes, cudaGetErrorString(e));
+    }
     c->slabs.push_back(p);
+  }
+  // once the last slab is half full, the next one is pinned in the background
+  if (!c->slab_pending && n + c->slab_units / 2 > (int64_t)c->slabs.size() * c->slab_units) {
+    c->slab_future = std::async(std::launch::async, alloc_slab, c->cfg.device, bytes);
+    c->slab_pending = true;
   }
   return INFLLM_OK;
 }
@@ -644,8 +672,9 @@ int candidates_finish(infllm_ctx* c, int n_cand, std::vector<int32_t>* ids) {
 }
 
 // cache plan for `ids` (LRU eviction, stamps), adoption of staged copies, late fetches; s waits for the copies
-int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, cudaStream_t s) {
+int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, cudaStream_t s, bool track) {
   const infllm_config& g = c->cfg;
+  if (!track) c->table_valid = false;  // the device copy of the slot table is rebuilt when decode next needs it
   std::vector<int32_t> evicted;
   c->lru.plan(ids.data(), (int)ids.size(), &evicted);
   for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
@@ -653,6 +682,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     if (it != c->slot_of.end()) {
       c->free_slots.push_back(it->second);
       c->slot_of.erase(it);
+      if (track) c->tab_updates[b] = -1;
     }
   }
   c->counters.evictions += (int64_t)evicted.size();
@@ -672,6 +702,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     auto st = c->staged.find(b);
     if (st != c->staged.end()) {  // the look-ahead already brought it in
       c->slot_of[b] = st->second;
+      if (track) c->tab_updates[b] = st->second;
       c->staged.erase(st);
       c->staged_for.erase(b);
       adopted = true;
@@ -696,6 +727,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[b] = slot;
+    if (track) c->tab_updates[b] = slot;
     if (b >= c->d2h_synced_upto) {
       INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
       c->d2h_synced_upto = c->num_blocks;
@@ -723,6 +755,30 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
   }
   if (c->staged.empty()) c->staged_pending = false;
   return INFLLM_OK;
+}
+
+// bring the device copy of the slot table up to date on stream s
+int flush_table(infllm_ctx* c, cudaStream_t s) {
+  if (c->tab_cap < c->block_k_cap || !c->d_slot_table) {
+    if (c->d_slot_table) INFLLM_CUDA_OK(cudaFreeAsync(c->d_slot_table, s));
+    c->tab_cap = std::max<int64_t>(c->block_k_cap, 1024);
+    INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->d_slot_table, c->tab_cap * sizeof(int32_t), s));
+    c->table_valid = false;
+  }
+  if (!c->table_valid) {
+    INFLLM_CUDA_OK(cudaMemsetAsync(c->d_slot_table, 0xff, c->tab_cap * sizeof(int32_t), s));  // every entry -1
+    c->tab_updates.clear();
+    for (auto& kv : c->slot_of) c->tab_updates[kv.first] = kv.second;
+    c->table_valid = true;
+  }
+  if (c->tab_updates.empty()) return INFLLM_OK;
+  std::vector<int32_t> ids, slots;
+  for (auto& kv : c->tab_updates) {
+    ids.push_back(kv.first);
+    slots.push_back(kv.second);
+  }
+  c->tab_updates.clear();
+  return slot_table_update_launch(c->d_slot_table, ids.data(), slots.data(), (int)ids.size(), s);
 }
 
 // what sealing does after an exec block that ended at absolute token `end` (context_manager.py:614-679):
@@ -868,7 +924,8 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     INFLLM_TRY(ingest_token_launch(q, q_hs, k, k_hs, v, v_hs, c->q_loc, c->q_glb, q_hs_s, c->qbar,
                                    (char*)tb.k_raw + at * D * esz, (char*)tb.k_rot + at * D * esz,
                                    (char*)tb.v + at * D * esz, kv_hs, tb.score + at, tb.cap, (int)H, (int)HKV, (int)D,
-                                   c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, g.n_local - 1, g.dtype, s));
+                                   c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, g.n_local - 1, g.dtype, s,
+                                   c->d_miss));
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
   } else {
     INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
@@ -897,15 +954,36 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     const int64_t ed = std::min<int64_t>(st + g.exc_block_size, L);
     const int64_t S = T + st, E = T + ed, lq = ed - st;
     const int64_t ks = std::max<int64_t>(S - g.n_local, 0), lk = E - ks;  // local keys [ks, E) (:772-773)
-    if (!have_ids) {
-      HostTimer ht(&c->host_us[0]);
-      INFLLM_TRY(retrieve_now(c, eb, &ids, s));
+    // One-token exec blocks over more units than a retrieval takes: the attention is launched right behind the
+    // top-k kernel and resolves the retrieved units through the device copy of the slot table, so the GPU does
+    // not idle while the ids travel to the host.  The host still receives the ids (it keeps the LRU order) and,
+    // if one of them is not cached, refills the cache and launches the attention again.
+    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.reserved[0] & 16);
+    if (!spec) {
+      if (!have_ids) {
+        HostTimer ht(&c->host_us[0]);
+        INFLLM_TRY(retrieve_now(c, eb, &ids, s));
+      }
+      {
+        HostTimer ht(&c->host_us[1]);
+        INFLLM_TRY(plan_and_refill(c, ids, eb, s, false));
+      }
+      c->trace_topk.push_back(ids);
+    } else {
+      ids.clear();
+      INFLLM_TRY(ensure_scores(c, c->num_blocks, s));
+      {
+        ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
+        INFLLM_TRY(block_topk_launch(c->block_k, c->num_blocks, (int)c->width, c->qbar, c->scores, g.topk, 0, c->d_topk,
+                                     nullptr, g.dtype, s, c->tickets));
+      }
+      INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
+      INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
+      INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                     c->mail_stream));
+      INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, c->mail_stream));
+      INFLLM_TRY(flush_table(c, s));
     }
-    {
-      HostTimer ht(&c->host_us[1]);
-      INFLLM_TRY(plan_and_refill(c, ids, eb, s));
-    }
-    c->trace_topk.push_back(ids);
     const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
     const int64_t n_eb = (L + g.exc_block_size - 1) / g.exc_block_size;
     if (more) {
@@ -921,6 +999,8 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     const int64_t ovf = std::max<int64_t>(E - c->frontier - g.n_local, 0);  // :391
     // global key segments: retrieved units (in place in their cache slots), sink, overflow
     gsegs.clear();
+    if (spec)  // resolved on the device
+      for (int i = 0; i < g.topk; ++i) gsegs.push_back({nullptr, nullptr, bs * D, (int32_t)D, (int32_t)bs});
     for (int32_t b : ids) {
       const char* base = (const char*)c->cache + (int64_t)c->slot_of[b] * c->unit_bytes;
       gsegs.push_back({base, base + c->unit_bytes / 2, bs * D, (int32_t)D, (int32_t)bs});
@@ -949,19 +1029,64 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       int parts = 0;
       double dec_keys = 0;
       for (auto& sgm : segs) dec_keys += sgm.len;
-      ProfScope ps(c, s, INFLLM_PROF_DECODE, dec_keys * HKV * D * 2 * esz);
-      for (size_t base = 0; base < segs.size();) {
-        // all segments fit one launch in every supported configuration; guard anyway
-        if (segs.size() > (size_t)kMaxSeg)
-          return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
+      if (segs.size() > (size_t)kMaxSeg)
+        return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
+      DecodeIndirect ind;
+      if (spec) {
+        ind.ids = c->d_topk;
+        ind.table = c->d_slot_table;
+        ind.cache = (const char*)c->cache;
+        ind.unit_bytes = c->unit_bytes;
+        ind.n_units = g.topk;
+        ind.first_seg = 1;
+        ind.miss = c->d_miss;
+      }
+      {
+        // the merge also adds this token's local attention row into the accumulated scores
+        ProfScope ps(c, s, INFLLM_PROF_DECODE, dec_keys * HKV * D * 2 * esz);
         INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
                                       qsel.data(), c->part_o, c->part_lse, c->max_parts, &parts, 0, c->dec_logits,
-                                      g.dtype, s, 64));
-        base = segs.size();
+                                      g.dtype, s, 64, spec ? &ind : nullptr, 0));
+        INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s,
+                                    c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap, spec ? c->d_miss : nullptr));
       }
-      // the merge also adds this token's local attention row into the accumulated scores
-      INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s,
-                                  c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap));
+      if (spec) {
+        INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));  // a refill must not overwrite slots these kernels may read
+        c->attn_recorded = true;
+        {
+          HostTimer ht(&c->host_us[0]);
+          INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));
+        }
+        ids.assign(c->h_topk, c->h_topk + g.topk);
+        std::vector<int32_t> missed;
+        for (int32_t b : ids)
+          if (!c->slot_of.count(b)) missed.push_back(b);
+        const bool all_hit = missed.empty();
+        {
+          HostTimer ht(&c->host_us[1]);
+          INFLLM_TRY(plan_and_refill(c, ids, eb, s, true));
+        }
+        c->trace_topk.push_back(ids);
+        if (!all_hit) {
+          // the chunks of the missing units carry weight zero so far and the merge above did nothing: run those
+          // units now that their copies are ordered ahead on the stream, then merge everything
+          INFLLM_TRY(flush_table(c, s));
+          std::vector<KvSeg> late;
+          std::vector<int32_t> late_q;
+          for (int32_t b : missed) {
+            const char* base = (const char*)c->cache + (int64_t)c->slot_of[b] * c->unit_bytes;
+            late.push_back({base, base + c->unit_bytes / 2, bs * D, (int32_t)D, (int32_t)bs});
+            late_q.push_back(1);
+          }
+          int parts2 = 0;
+          ProfScope ps(c, s, INFLLM_PROF_DECODE, 0.0);
+          INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)late.size(), late.data(),
+                                        late_q.data(), c->part_o, c->part_lse, c->max_parts, &parts2, -1, nullptr,
+                                        g.dtype, s, 64, nullptr, parts));
+          INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts + parts2, (int)H, (int)D, out_eb, o_hs, c->lse,
+                                      g.dtype, s, c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap, nullptr));
+        }
+      }
     } else {
       // ---- local stage + global stage, jointly normalised (context_manager.py:486-489, 526-533)
       double local_pairs = 0, all_glk = 0;
@@ -1159,6 +1284,8 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->tb.t0 = 0;
   c->lru.clear();
   c->slot_of.clear();
+  c->table_valid = false;
+  c->tab_updates.clear();
   c->free_slots.clear();
   for (int i = c->cfg.max_cached_block + infllm_ctx::kLookDepth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->staged.clear();
@@ -1179,11 +1306,12 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     cudaDeviceSynchronize();
     free_buffers(c->tb, nullptr);
     void* dev[] = {c->init_k, c->init_v, c->cos_t, c->sin_t, c->q_loc, c->q_glb, c->qbar, c->lse, c->st_acc, c->st_m,
-                   c->st_l, c->d_topk, c->tickets, c->part_o, c->part_lse, c->dec_logits, c->cache};
+                   c->st_l, c->d_topk, c->tickets, c->d_miss, c->part_o, c->part_lse, c->dec_logits, c->cache};
     for (void* p : dev)
       if (p) cudaFree(p);
     if (c->block_k) cudaFreeAsync(c->block_k, nullptr);
     if (c->scores) cudaFreeAsync(c->scores, nullptr);
+    if (c->d_slot_table) cudaFreeAsync(c->d_slot_table, nullptr);
     if (c->h_topk) cudaFreeHost(c->h_topk);
     if (c->h_spec) cudaFreeHost(c->h_spec);
     for (auto& l : c->la) {
@@ -1209,6 +1337,10 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     cudaEventDestroy(c->ev_cand);
     cudaEventDestroy(c->ev_seal);
     cudaEventDestroy(c->ev_stage);
+    if (c->slab_pending) {
+      void* p = c->slab_future.get();
+      if (p) cudaFreeHost(p);
+    }
     for (void* p : c->slabs) cudaFreeHost(p);
     cudaStreamDestroy(c->copy_stream);
     cudaEventDestroy(c->ev_main);

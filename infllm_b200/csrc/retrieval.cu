@@ -2,8 +2,8 @@
 //
 // block_score_topk_kernel  k <= 64 over <= 8192 units, the usual case: HBM-streaming GEMV (one warp per
 //                     representative-key row, 16-byte loads, query mean staged in shared memory, fp32
-//                     accumulation) whose last CTA ranks the scores (bitonic sort of per-thread maxima,
-//                     threshold, rank sort of the few candidates).
+//                     accumulation) whose last CTA ranks the scores (threshold from the maxima of small
+//                     groups, rank sort of the few candidates).
 // block_score_kernel + topk_select_kernel  any size: the same GEMV, then a 4-pass 8-bit radix select of the
 //                     k-th largest score, an index-ordered gather of the winners and a rank sort.
 //                     Both: descending score, ties to the lower id.
@@ -213,13 +213,19 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
 // Every score becomes a 64-bit key: (order-preserving bits of the score) << 32 | ~id, so that a larger key
 // means "ranks earlier" (higher score, then lower id) and no two keys are equal.  Thread t keeps the keys of
 // scores t, t + 1024, ... in registers; four neighbouring threads form a group of 32 scores.
-//   1. bitonic sort (descending) of the 256 group maxima by the first eight warps: shuffles for partner
-//      distances below 32, shared memory above.  The k-th of them, tau, is a lower bound of the k-th largest
-//      key overall, and exactly k groups hold a maximum >= tau.
+//   1. tau = the k-th largest of the 256 group maxima, found by counting for every group how many maxima are
+//      larger.  tau is a lower bound of the k-th largest key overall, and exactly k groups hold a maximum
+//      >= tau.
 //   2. every key >= tau is a candidate: at most 32k of them (a few more than k unless the scores are laid out
 //      adversarially), appended to a shared list.
 //   3. rank sort of the candidates; the first k leave in order.
 // No loop waits on data of another CTA.
+#ifdef INFLLM_TOPK_TIMING
+__device__ long long g_topk_stamps[16];
+#define TK_STAMP(i) do { if (threadIdx.x == 0) g_topk_stamps[i] = clock64(); } while (0)
+#else
+#define TK_STAMP(i) do { } while (0)
+#endif
 constexpr int kFastItems = 8;
 constexpr int kFastMaxK = 64;
 constexpr int kFastMaxN = kFastItems * kTopkThreads;
@@ -232,10 +238,10 @@ __device__ __forceinline__ unsigned long long topk_key(float v, int id) {
 }
 __device__ __forceinline__ unsigned long long max64(unsigned long long a, unsigned long long b) { return a > b ? a : b; }
 
-// `gm` holds kFastGroups keys, `cand` kFastCand keys, `s_cnt` one int.  All 1024 threads call.
+// `gm` holds kFastGroups keys, `cand` kFastCand keys, `s_cnt` one int, `s_tau` one key.  All 1024 threads call.
 __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
                               float* __restrict__ out_scores, unsigned long long* gm, unsigned long long* cand,
-                              int* s_cnt) {
+                              int* s_cnt, unsigned long long* s_tau) {
   const int tid = threadIdx.x;
   unsigned long long key[kFastItems];
 #pragma unroll
@@ -251,30 +257,21 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
   if ((tid & 3) == 0) gm[tid >> 2] = x;
   if (tid == 0) *s_cnt = 0;
   __syncthreads();
-  // ---- 1. bitonic sort of the group maxima, descending in thread order, by threads 0..255
-  if (tid < kFastGroups) {
-    x = gm[tid];
-    for (int size = 2; size <= kFastGroups; size <<= 1) {
-      const bool desc = (tid & size) == 0;  // this run sorts descending
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        unsigned long long y;
-        if (stride >= 32) {
-          asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");  // earlier reads of gm are done
-          gm[tid] = x;
-          asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");
-          y = gm[tid ^ stride];
-        } else {
-          y = __shfl_xor_sync(0xffffffffu, x, stride);
-        }
-        const bool lower = (tid & stride) == 0;  // the partner with the smaller index
-        x = (lower == desc) ? (x > y ? x : y) : (x < y ? x : y);
-      }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kFastGroups) : "memory");
-    gm[tid] = x;
+  TK_STAMP(4);
+  // ---- 1. tau = the k-th largest group maximum: the four threads of a group count, a quarter each, how many
+  //         group maxima are larger than their own; the group that counts k - 1 holds tau
+  {
+    const int q0 = tid & 3;  // interleaved quarters: the four threads read neighbouring words
+    int larger = 0;
+#pragma unroll 8
+    for (int j = 0; j < kFastGroups / 4; ++j) larger += gm[4 * j + q0] > x;
+    larger += __shfl_xor_sync(0xffffffffu, larger, 1);
+    larger += __shfl_xor_sync(0xffffffffu, larger, 2);
+    if ((tid & 3) == 0 && larger == k - 1) *s_tau = x;  // keys are unique (0 only among padding groups, see below)
   }
   __syncthreads();
-  const unsigned long long tau = gm[k - 1];
+  TK_STAMP(5);
+  const unsigned long long tau = *s_tau;
   // ---- 2. candidates
 #pragma unroll
   for (int e = 0; e < kFastItems; ++e)
@@ -283,6 +280,7 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
       if (p < kFastCand) cand[p] = key[e];
     }
   __syncthreads();
+  TK_STAMP(6);
   const int nc = *s_cnt < kFastCand ? *s_cnt : kFastCand;  // k <= nc <= 32k
   // ---- 3. rank of every candidate = how many candidates rank before it
   for (int c = tid; c < nc; c += kTopkThreads) {
@@ -295,6 +293,7 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
       if (out_scores) out_scores[rank] = __ldcg(scores + id);
     }
   }
+  TK_STAMP(7);
 }
 
 __global__ void __launch_bounds__(kTopkThreads)
@@ -303,7 +302,9 @@ topk_fast_kernel(const float* __restrict__ scores, int n, int k, int id_base, in
   __shared__ unsigned long long sm[kFastGroups];
   __shared__ unsigned long long cand[kFastCand];
   __shared__ int s_cnt;
-  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt);
+  __shared__ unsigned long long s_tau;
+  if (threadIdx.x == 0) s_tau = 0ull;
+  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt, &s_tau);
 }
 
 // Scoring and top-k in one launch: CTAs of 32 warps stream the representative keys (one warp per row, the whole
@@ -319,11 +320,15 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
   __shared__ unsigned long long sm[kFastGroups];
   __shared__ unsigned long long cand[kFastCand];
   __shared__ int s_cnt;
+  __shared__ unsigned long long s_tau;
   __shared__ bool s_last;
+  TK_STAMP(0);
   for (int i = threadIdx.x; i < width; i += kTopkThreads) sq[i] = qbar[i];
   __syncthreads();
+  TK_STAMP(1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int row = blockIdx.x * 32 + warp; row < n; row += gridDim.x * 32) {
+  // consecutive rows go to different SMs, so that a short list still draws on every SM's path to memory
+  for (int row = warp * gridDim.x + blockIdx.x; row < n; row += gridDim.x * 32) {
     const T* p = bk + (int64_t)row * width;
     float acc = 0.f;
     for (int c0 = 0; c0 < width; c0 += 32 * 8 * 8) {
@@ -354,17 +359,22 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
       }
     }
     acc = warp_sum(acc);
-    if (lane == 0) scores[row] = acc;
+    if (lane == 0) {
+      scores[row] = acc;
+      __threadfence();  // visible device-wide before this CTA takes its ticket
+    }
   }
   if (!ticket) return;
-  __threadfence();
+  TK_STAMP(2);
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
   __syncthreads();
   if (!s_last) return;
   __threadfence();
   if (threadIdx.x == 0) *ticket = 0;
-  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt);
+  TK_STAMP(3);
+  if (threadIdx.x == 0) s_tau = 0ull;
+  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt, &s_tau);
 }
 
 template <typename T>
@@ -426,6 +436,33 @@ __global__ void repr_select_kernel(const T* __restrict__ k, int64_t k_hs, int64_
   }
 }
 
+// Device copy of the cache's unit -> slot table (-1: not cached), read by the decode attention when it resolves
+// the retrieved units itself.  The host sends the entries that changed as kernel parameters.
+constexpr int kMaxTableUpdates = 128;
+struct TableUpdates {
+  int32_t id[kMaxTableUpdates];
+  int32_t slot[kMaxTableUpdates];
+};
+__global__ void slot_table_update_kernel(int32_t* __restrict__ table, const __grid_constant__ TableUpdates u, int n) {
+  const int i = threadIdx.x;
+  if (i < n) table[u.id[i]] = u.slot[i];
+}
+
+// ids must not repeat within one call
+int slot_table_update_launch(int32_t* table, const int32_t* ids, const int32_t* slots, int n, cudaStream_t s) {
+  for (int done = 0; done < n; done += kMaxTableUpdates) {
+    const int m = n - done < kMaxTableUpdates ? n - done : kMaxTableUpdates;
+    TableUpdates u;
+    for (int i = 0; i < m; ++i) {
+      u.id[i] = ids[done + i];
+      u.slot[i] = slots[done + i];
+    }
+    slot_table_update_kernel<<<1, kMaxTableUpdates, 0, s>>>(table, u, m);
+    INFLLM_LAUNCH_OK("slot_table_update_kernel");
+  }
+  return INFLLM_OK;
+}
+
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
                       int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket) {
   if (n <= 0 || k <= 0 || k > n) return fail(INFLLM_E_BADARG, "block_topk: need 0 < k <= n_blocks (k=%d n=%lld)", k, (long long)n);
@@ -434,7 +471,7 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
     return fail(INFLLM_E_BADARG, "block_topk: width %d must be a multiple of 8, at most 12288, rows 16-byte aligned", width);
   if (k <= kFastMaxK && n <= kFastMaxN) {
     // one launch when the caller lends a ticket counter, else scoring and ranking back to back
-    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(n, 32), 148);
+    const unsigned grid = (unsigned)std::min<int64_t>(n, 148);
     INFLLM_DISPATCH_DTYPE(dtype, T, {
       block_score_topk_kernel<T><<<grid, kTopkThreads, width * sizeof(float), s>>>(
           (const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores, ticket);
@@ -489,6 +526,16 @@ int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* s
 }
 
 }  // namespace infllm
+
+#ifdef INFLLM_TOPK_TIMING
+extern "C" int infllm_topk_stamps(long long* out) {
+  return cudaMemcpyFromSymbol(out, infllm::g_topk_stamps, sizeof(long long) * 16) == cudaSuccess ? 0 : -1;
+}
+extern "C" int infllm_block_topk_ticket(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k,
+                                        int32_t* ids, unsigned int* ticket, int dtype, void* stream) {
+  return infllm::block_topk_launch(bk, n, width, qbar, scores, k, 0, ids, nullptr, dtype, (cudaStream_t)stream, ticket);
+}
+#endif
 
 extern "C" int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int width, const float* d_qbar,
                                  float* d_scores, int k, int id_base, int32_t* d_out_ids, float* d_out_scores,

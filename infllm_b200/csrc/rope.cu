@@ -165,8 +165,9 @@ __global__ void ingest_token_kernel(const T* __restrict__ q, int64_t q_hs, const
                                     T* __restrict__ k_raw, T* __restrict__ k_rot, T* __restrict__ v_out,
                                     int64_t kv_hs, float* __restrict__ score, int64_t score_hs, int n_heads,
                                     int head_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                    int64_t pos_loc, int64_t pos_glb) {
+                                    int64_t pos_loc, int64_t pos_glb, int32_t* __restrict__ clear) {
   const int half = head_dim / 2, i = threadIdx.x, b = blockIdx.x;
+  if (clear && b == 0 && i == 0) *clear = 0;  // the "retrieved unit not cached" flag of this token's attention
   if (i >= half) return;
   const float cl = cos_t[pos_loc * half + i], sl = sin_t[pos_loc * half + i];
   if (b < n_heads) {
@@ -198,7 +199,7 @@ int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs
                         void* q_loc, void* q_glb, int64_t qs_hs, float* qbar, void* k_raw, void* k_rot, void* v_out,
                         int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
                         const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
-                        int dtype, cudaStream_t s) {
+                        int dtype, cudaStream_t s, int32_t* clear) {
   if (head_dim % 2 || head_dim > 2048) return fail(INFLLM_E_BADARG, "ingest: head_dim %d", head_dim);
   if (pos_loc < 0 || pos_loc >= table_len || pos_glb < 0 || pos_glb >= table_len)
     return fail(INFLLM_E_BADARG, "ingest: positions %lld / %lld outside the table of %lld rows", (long long)pos_loc,
@@ -206,7 +207,7 @@ int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     ingest_token_kernel<T><<<n_heads + n_kv_heads, head_dim / 2, 0, s>>>(
         (const T*)q, q_hs, (const T*)k, k_hs, (const T*)v, v_hs, (T*)q_loc, (T*)q_glb, qs_hs, qbar, (T*)k_raw, (T*)k_rot,
-        (T*)v_out, kv_hs, score, score_hs, n_heads, head_dim, cos_t, sin_t, pos_loc, pos_glb);
+        (T*)v_out, kv_hs, score, score_hs, n_heads, head_dim, cos_t, sin_t, pos_loc, pos_glb, clear);
   });
   INFLLM_LAUNCH_OK("ingest_token_kernel");
   return INFLLM_OK;

@@ -66,7 +66,7 @@ def _run(case, dtype=torch.bfloat16):
     return cm, ora, stats
 
 
-@pytest.mark.parametrize("kernels", ["tcgen05", "generic", "tcgen05-nolookahead", "tcgen05-twohead"])
+@pytest.mark.parametrize("kernels", ["tcgen05", "generic", "tcgen05-nolookahead", "tcgen05-twohead", "tcgen05-nospec"])
 @pytest.mark.parametrize("name", D128)
 def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     """Both kernel families behind the exec-block loop — the tcgen05 kernels (default for blocks of more than
@@ -75,6 +75,7 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     monkeypatch.setenv("INFLLM_B200_NO_TC", "1" if kernels == "generic" else "0")
     monkeypatch.setenv("INFLLM_B200_NO_LOOKAHEAD", "1" if kernels.endswith("nolookahead") else "0")
     monkeypatch.setenv("INFLLM_B200_ATTN_TWO_HEAD", "1" if kernels.endswith("twohead") else "0")
+    monkeypatch.setenv("INFLLM_B200_NO_DECODE_SPEC", "1" if kernels.endswith("nospec") else "0")
     case = C.CASES[name]
     cm, ora, stats = _run(case)
     from infllm_b200 import _lib
