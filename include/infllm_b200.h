@@ -36,6 +36,7 @@ extern "C" {
 
 #define INFLLM_BF16 0
 #define INFLLM_FP16 1
+#define INFLLM_F32 2 /* accepted only as the output type of infllm_lse_merge */
 
 #define INFLLM_CACHE_LRU 0   /* cache_strategy "lru"   (context_manager.py:504-508) */
 #define INFLLM_CACHE_LRU_S 1 /* cache_strategy "lru-s" (context_manager.py:454-470, 510-513) */
@@ -134,7 +135,8 @@ int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float*
  * d_part_o (max_parts, n_heads, head_dim) fp32 and log2-domain log-sum-exp d_part_lse (max_parts,
  * n_heads); *n_parts receives how many were written (infllm_attn_decode_max_parts bounds it).
  * logit_seg >= 0 also exports that segment's scaled log2-domain logits to d_logits (n_heads, seg_len).
- * infllm_lse_merge combines n_part partials into out (n_heads, head_dim) in `dtype` (head stride o_hs)
+ * infllm_lse_merge combines n_part partials into out (n_heads, head_dim) in `dtype` (head stride o_hs;
+ * INFLLM_F32 keeps a rank's partial in fp32 for a second merge)
  * and d_lse (n_heads, may be NULL): the same merge serves the chunks of one GPU and the per-rank
  * partials gathered from several GPUs (unit-range sharding). */
 #define INFLLM_MAX_SEGMENTS 80

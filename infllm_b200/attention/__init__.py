@@ -4,6 +4,7 @@ from .context_manager import ContextManager
 from .dot_production_attention import CudaMultiStageDotProductionAttention, get_multi_stage_dot_production_attention
 from .inf_llm import inf_llm_forward
 from .rope import RotaryEmbeddingESM
+from .sharded_decode import ShardedDecodeMemory, UnitRangeShard, global_topk, unit_range
 
 ATTN_FORWRAD = {
     "inf-llm": inf_llm_forward,
@@ -11,4 +12,5 @@ ATTN_FORWRAD = {
 ATTN_FORWARD = ATTN_FORWRAD
 
 __all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward",
-           "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention"]
+           "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention",
+           "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]

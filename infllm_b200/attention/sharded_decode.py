@@ -1,0 +1,345 @@
+"""Single-sequence decode over a context memory that is sharded by memory-unit range across GPUs.
+
+The reference keeps a whole layer's memory on one GPU (inf_llm/attention/context_manager.py); it has no
+multi-GPU path.  Here rank r of G owns the sealed units [N*r/G, N*(r+1)/G) — their K/V in pinned host memory,
+their representative keys, and a GPU cache of max_cached_block units with its own LRU order — while the local
+window, the init sink and the un-sealed remainder (a few thousand tokens) are kept by every rank.  One token:
+
+1. every rank scores its own representative keys and takes its local top-k        (calc_block_topk, :366-383)
+2. all-gather of the (score, id) pairs, 8 bytes each -> the same global top-k on every rank
+3. every rank runs split-K attention over the retrieved units it owns, its 1/G share of the window, and
+   (rank 0) the sink / (last rank) the overflow tokens, and reduces that to one (o, lse) partial
+4. all-gather of the partials, (D + 1) floats per head -> log-sum-exp merge on every rank   (_append, :474-545)
+5. every rank adds its share of the token's local attention row to the accumulated scores; when a unit
+   seals (append_global, :614-679) the ranks all-reduce that unit's 128 score columns, pick the same
+   representative tokens, and the last rank, which owns every unit sealed after the load, stores it.
+
+A `UnitRangeShard` is one rank's state and drives the kernels through the C ABI; `ShardedDecodeMemory` runs the
+five steps over the shards that live in this process (one per process under torch.distributed; all of them in one
+process when the ranks are emulated on a single GPU) and the collectives between processes.
+"""
+import ctypes
+
+import torch
+
+from .. import _lib
+
+F32 = 2  # INFLLM_F32: fp32 output of infllm_lse_merge
+
+
+def unit_range(n_total, rank, world):
+    """Units owned by `rank` at load time: [lo, hi).  Units sealed later all go to the last rank."""
+    return (n_total * rank) // world, (n_total * (rank + 1)) // world
+
+
+def global_topk(scores, ids, k):
+    """The k best of the gathered candidates: descending score, ties to the lower id (the order of the
+    single-GPU scorer).  `ids` < 0 mark padding.  Returns a 1-D int32 tensor of at most k ids."""
+    scores, ids = scores.reshape(-1), ids.reshape(-1)
+    keep = ids >= 0
+    scores, ids = scores[keep], ids[keep]
+    by_id = torch.argsort(ids, stable=True)
+    by_score = torch.argsort(-scores[by_id], stable=True)
+    return ids[by_id[by_score[:k]]].to(torch.int32)
+
+
+def merge_partials(part_o, part_lse, out_dtype):
+    """Log-sum-exp merge of per-rank partials: part_o (G, H, D) fp32, part_lse (G, H) fp32 (log2 domain)
+    -> out (H, D) in out_dtype, lse (H,) fp32."""
+    G, H, D = part_o.shape
+    out = torch.empty((H, D), dtype=out_dtype, device=part_o.device)
+    lse = torch.empty((H,), dtype=torch.float32, device=part_o.device)
+    _lib.check(_lib.lib.infllm_lse_merge(part_o.data_ptr(), part_lse.data_ptr(), G, H, D, out.data_ptr(), D,
+                                         lse.data_ptr(), _lib.dtype_code(out_dtype), _lib.stream_ptr()))
+    return out, lse
+
+
+class UnitRangeShard:
+    """One rank's share of the memory and its decode kernels."""
+
+    def __init__(self, rank, world, position_embedding, n_init, n_local, block_size, max_cached_block, topk, repr_topk,
+                 n_heads, n_kv_heads, head_dim, dtype=torch.bfloat16, device=None, spare_units=64):
+        if head_dim != 128:
+            raise NotImplementedError("the decode kernels are built for head_dim 128")
+        if max_cached_block < topk:  # CudaCache.alloc would assert (context_manager.py:19)
+            raise _lib.InfLLMCapacityError(_lib.E_CAPACITY, "max_cached_block < topk")
+        self.rank, self.world = rank, world
+        self.pe = position_embedding
+        self.n_init, self.n_local, self.bs = n_init, n_local, block_size
+        self.max_cached, self.topk, self.repr_topk = max_cached_block, topk, repr_topk
+        self.H, self.HKV, self.D = n_heads, n_kv_heads, head_dim
+        self.dtype, self.code = dtype, _lib.dtype_code(dtype)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.spare = spare_units
+        self.cap = n_local + max(4096, 2 * block_size)  # token slots: window + remainder + room before a compaction
+        dev, H, HKV, D = self.device, n_heads, n_kv_heads, head_dim
+        self.k_raw = torch.zeros((HKV, self.cap, D), dtype=dtype, device=dev)
+        self.k_rot = torch.zeros_like(self.k_raw)
+        self.v = torch.zeros_like(self.k_raw)
+        self.score = torch.zeros((H, self.cap), dtype=torch.float32, device=dev)
+        self.q_loc = torch.empty((H, D), dtype=dtype, device=dev)
+        self.q_glb = torch.empty((H, D), dtype=dtype, device=dev)
+        self.cos = torch.empty((self.cap, D // 2), dtype=torch.float32, device=dev)
+        self.sin = torch.empty_like(self.cos)
+        inv = (1.0 / (float(self.pe.base) ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).contiguous()
+        arr = (ctypes.c_float * (D // 2))(*inv.tolist())
+        _lib.check(_lib.lib.infllm_rope_table(arr, float(self.pe.distance_scale), D, self.cap, self.cos.data_ptr(),
+                                              self.sin.data_ptr(), _lib.stream_ptr()))
+        self.cache = torch.zeros((max_cached_block, 2, HKV, block_size, D), dtype=dtype, device=dev)
+        self.free_slots = list(range(max_cached_block - 1, -1, -1))
+        self.slot_of = {}
+        self.lru = ctypes.c_void_p()
+        _lib.check(_lib.lib.infllm_lru_create(max_cached_block, ctypes.byref(self.lru)))
+        self.load_count = 0
+        max_keys = n_local + topk * block_size + n_init + block_size
+        self.max_parts = int(_lib.lib.infllm_attn_decode_max_parts(topk + 3, max_keys))
+        self.part_o = torch.empty((self.max_parts, H, D), dtype=torch.float32, device=dev)
+        self.part_lse = torch.empty((self.max_parts, H), dtype=torch.float32, device=dev)
+        self.logits = torch.empty((H, n_local + 1), dtype=torch.float32, device=dev)
+        self.pack = torch.empty((H * (D + 1),), dtype=torch.float32, device=dev)  # [o (H, D) | lse (H)]
+        self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
+        self.scores_buf = None
+        self.hits = self.misses = 0
+        self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
+        self.block_k = self.host_units = self.init_k = self.init_v = None
+        self._share = (0, 0)
+
+    def __del__(self):
+        if getattr(self, "lru", None):
+            _lib.lib.infllm_lru_destroy(self.lru)
+            self.lru = None
+
+    # ------------------------------------------------------------------ state
+    def load_synthetic(self, n_total, units, block_k, init_k, init_v, win_k, win_v):
+        """Install a memory of n_total sealed units of which this rank receives its own range: `units`
+        (n_owned, 2, H_kv, bs, D) and `block_k` (n_owned, H*D) on the host, plus the replicated sink
+        (H_kv, n_init, D) x2 and window (H_kv, n_local, D) x2."""
+        lo, hi = unit_range(n_total, self.rank, self.world)
+        n_owned = hi - lo
+        assert units.shape[0] == n_owned and block_k.shape[0] == n_owned
+        room = n_owned + (self.spare if self.rank == self.world - 1 else 0)
+        self.host_units = torch.empty((max(room, 1),) + tuple(units.shape[1:]), dtype=self.dtype).pin_memory()
+        self.host_units[:n_owned].copy_(units)
+        self.block_k = torch.zeros((max(room, 1), self.H * self.D), dtype=self.dtype, device=self.device)
+        self.block_k[:n_owned].copy_(block_k)
+        self.scores_buf = torch.empty((max(room, 1),), dtype=torch.float32, device=self.device)
+        self.init_k, self.init_v = init_k.to(self.device).contiguous(), init_v.to(self.device).contiguous()
+        self.n_total, self.lo, self.n_owned = n_total, lo, n_owned
+        self.frontier = self.n_init + n_total * self.bs
+        self.length = self.frontier + self.n_local
+        self.t0 = self.frontier
+        n = self.n_local
+        self.k_raw[:, :n].copy_(win_k)
+        self.v[:, :n].copy_(win_v)
+        self.score.zero_()
+        self._rotate(0, n)
+
+    def _rope(self, x, x_hs, x_ts, out, o_hs, o_ts, heads, length, pos0, step):
+        _lib.check(_lib.lib.infllm_rope_apply(x, x_hs, x_ts, out, o_hs, o_ts, heads, length, self.D, self.cos.data_ptr(),
+                                              self.sin.data_ptr(), self.cap, pos0, step, self.code, _lib.stream_ptr()))
+
+    def _rotate(self, slot0, n):
+        """k_rot[slot] = RoPE(k_raw[slot]) at position `slot` (token - t0) for slots [slot0, slot0 + n)."""
+        off = slot0 * self.D * self.k_raw.element_size()
+        self._rope(self.k_raw.data_ptr() + off, self.cap * self.D, self.D, self.k_rot.data_ptr() + off,
+                   self.cap * self.D, self.D, self.HKV, n, slot0, 1)
+
+    def _compact(self):
+        """Move the live tokens [frontier, length) to slot 0 and rotate them anew."""
+        live, s0 = self.length - self.frontier, self.frontier - self.t0
+        for buf in (self.k_raw, self.v):
+            buf[:, :live] = buf[:, s0:s0 + live].clone()
+        self.score[:, :live] = self.score[:, s0:s0 + live].clone()
+        self.t0 = self.frontier
+        self._rotate(0, live)
+
+    # ------------------------------------------------------------------ step 1
+    def begin(self, q, k, v):
+        """Ingest one token (q (H, 1, D), k and v (H_kv, 1, D)); returns this rank's candidates as an int32
+        tensor (2, topk): the scores' bit patterns and the global unit ids, padded with (-inf, -1)."""
+        if self.length - self.t0 >= self.cap:
+            self._compact()
+        T, at, D = self.length, self.length - self.t0, self.D
+        self.k_raw[:, at] = k.reshape(self.HKV, D)
+        self.v[:, at] = v.reshape(self.HKV, D)
+        self.score[:, at] = 0
+        self._rotate(at, 1)
+        qc = q.reshape(self.H, D).contiguous()
+        self._rope(qc.data_ptr(), D, D, self.q_loc.data_ptr(), D, D, self.H, 1, T - self.t0, 1)   # window-relative
+        self._rope(qc.data_ptr(), D, D, self.q_glb.data_ptr(), D, D, self.H, 1, self.n_local - 1, 0)  # one angle
+        cand_scores = self.cand[0].view(torch.float32)
+        cand_scores.fill_(float("-inf"))
+        self.cand[1].fill_(-1)
+        if self.n_owned > 0:
+            kk = min(self.topk, self.n_owned)
+            qbar = self.q_glb.float().reshape(-1)  # the mean over a one-token exec block (context_manager.py:373-375)
+            _lib.check(_lib.lib.infllm_block_topk(self.block_k.data_ptr(), self.n_owned, self.H * D, qbar.data_ptr(),
+                                                  self.scores_buf.data_ptr(), kk, self.lo, self.cand[1].data_ptr(),
+                                                  cand_scores.data_ptr(), self.code, _lib.stream_ptr()))
+        return self.cand
+
+    # ------------------------------------------------------------------ step 3
+    def attend(self, ids):
+        """Partial attention of this rank for the global retrieval `ids` (host list); returns the packed
+        fp32 tensor [o (H, D) | lse (H)]."""
+        E, G, r = self.length + 1, self.world, self.rank
+        owned = [b for b in ids if self.lo <= b < self.lo + self.n_owned]
+        self._refill(owned)
+        segs = []  # (k pointer, v pointer, head stride, length, query variant)
+        esz, D = self.k_raw.element_size(), self.D
+        for b in owned:
+            slot = self.cache[self.slot_of[b]]
+            segs.append((slot[0].data_ptr(), slot[1].data_ptr(), self.bs * D, self.bs, 1))
+        wlo = max(E - self.n_local, 0)
+        W = E - wlo
+        a, b_ = wlo + (W * r) // G, wlo + (W * (r + 1)) // G
+        self._share = (a, b_)
+        logit_seg = -1
+        if b_ > a:
+            off = (a - self.t0) * D * esz
+            logit_seg = len(segs)
+            segs.append((self.k_rot.data_ptr() + off, self.v.data_ptr() + off, self.cap * D, b_ - a, 0))
+        if r == 0 and self.n_init > 0:
+            segs.append((self.init_k.data_ptr(), self.init_v.data_ptr(), self.n_init * D, self.n_init, 1))
+        if r == G - 1 and wlo > self.frontier:  # tokens between the last sealed unit and the window
+            off = (self.frontier - self.t0) * D * esz
+            segs.append((self.k_raw.data_ptr() + off, self.v.data_ptr() + off, self.cap * D, wlo - self.frontier, 1))
+        o = self.pack[:self.H * D].view(self.H, D)
+        lse = self.pack[self.H * D:]
+        if not segs:
+            o.zero_()
+            lse.fill_(float("-inf"))
+            return self.pack
+        n = len(segs)
+        kp = (ctypes.c_void_p * n)(*[s[0] for s in segs])
+        vp = (ctypes.c_void_p * n)(*[s[1] for s in segs])
+        hs = (ctypes.c_int64 * n)(*[s[2] for s in segs])
+        ln = (ctypes.c_int32 * n)(*[s[3] for s in segs])
+        qs = (ctypes.c_int32 * n)(*[s[4] for s in segs])
+        n_parts = ctypes.c_int()
+        _lib.check(_lib.lib.infllm_attn_decode(self.q_loc.data_ptr(), self.q_glb.data_ptr(), self.H, self.HKV, D, n, kp,
+                                               vp, hs, ln, qs, self.part_o.data_ptr(), self.part_lse.data_ptr(),
+                                               self.max_parts, ctypes.byref(n_parts), logit_seg,
+                                               self.logits.data_ptr(), self.code, _lib.stream_ptr()))
+        _lib.check(_lib.lib.infllm_lse_merge(self.part_o.data_ptr(), self.part_lse.data_ptr(), n_parts.value, self.H, D,
+                                             o.data_ptr(), D, lse.data_ptr(), F32, _lib.stream_ptr()))
+        return self.pack
+
+    def _refill(self, owned):
+        """LRU plan for the owned part of a retrieval (context_manager.py:246-265, 495-515) and the copies of
+        the units that are not cached, from the pinned store into free slots."""
+        self.load_count += 1
+        if not owned:
+            return
+        n = len(owned)
+        want = (ctypes.c_int32 * n)(*owned)
+        ev = (ctypes.c_int32 * max(self.max_cached, 1))()
+        n_ev = ctypes.c_int()
+        _lib.check(_lib.lib.infllm_lru_plan(self.lru, want, n, ev, ctypes.byref(n_ev)))
+        for i in range(n_ev.value):
+            self.free_slots.append(self.slot_of.pop(ev[i]))
+        _lib.check(_lib.lib.infllm_lru_stamp(self.lru, want, n, float(self.load_count)))
+        for b in owned:
+            if b in self.slot_of:
+                self.hits += 1
+                continue
+            self.misses += 1
+            slot = self.free_slots.pop()
+            self.slot_of[b] = slot
+            self.cache[slot].copy_(self.host_units[b - self.lo], non_blocking=True)
+
+    # ------------------------------------------------------------------ step 5
+    def finish(self, lse):
+        """Add this rank's share of the token's local attention row to the accumulated scores (lse (H,) is the
+        merged log-sum-exp) and count the token in.  Returns the (H, bs) score columns of the unit that seals
+        now — this rank's partial sums, to be all-reduced — or None."""
+        a, b = self._share
+        if b > a:
+            n = b - a
+            self.score[:, a - self.t0:b - self.t0] += torch.exp2(self.logits.view(-1)[:self.H * n].view(self.H, n)
+                                                                 - lse[:, None])
+        self.length += 1
+        if self.length - self.frontier - self.bs >= self.n_local:  # context_manager.py:649
+            s0 = self.frontier - self.t0
+            return self.score[:, s0:s0 + self.bs].contiguous()
+        return None
+
+    def seal(self, scores):
+        """Seal the oldest un-sealed 128 tokens as a unit, given their all-reduced score columns (H, bs)."""
+        s0, D = self.frontier - self.t0, self.D
+        self.score[:, s0:s0 + self.bs] = scores
+        if self.rank == self.world - 1:
+            if self.n_owned >= self.block_k.shape[0]:
+                self._grow()
+            row = self.block_k[self.n_owned]
+            _lib.check(_lib.lib.infllm_repr_select(self.k_raw.data_ptr(), self.cap * D, D, self.score.data_ptr(), self.cap,
+                                                   s0, 1, self.bs, self.repr_topk, self.H, self.HKV, D, row.data_ptr(),
+                                                   self.code, _lib.stream_ptr()))
+            unit = self.host_units[self.n_owned]
+            unit[0].copy_(self.k_raw[:, s0:s0 + self.bs], non_blocking=True)
+            unit[1].copy_(self.v[:, s0:s0 + self.bs], non_blocking=True)
+            self.n_owned += 1
+        self.frontier += self.bs
+        self.n_total += 1
+
+    def _grow(self):
+        room = self.block_k.shape[0] + max(self.spare, 1)
+        torch.cuda.current_stream().synchronize()  # copies into the old store have landed
+        host = torch.empty((room,) + tuple(self.host_units.shape[1:]), dtype=self.dtype).pin_memory()
+        host[:self.n_owned].copy_(self.host_units[:self.n_owned])
+        self.host_units = host
+        bk = torch.zeros((room, self.H * self.D), dtype=self.dtype, device=self.device)
+        bk[:self.n_owned].copy_(self.block_k[:self.n_owned])
+        self.block_k = bk
+        self.scores_buf = torch.empty((room,), dtype=torch.float32, device=self.device)
+
+
+class ShardedDecodeMemory:
+    """Runs one token through the shards of this process and the collectives between processes.
+
+    shards: the UnitRangeShard objects that live in this process, in rank order — one under torch.distributed
+    (pass `group`, or leave None for the default group), or all G of them when the ranks share one process.
+    """
+
+    def __init__(self, shards, distributed=False, group=None, merge=merge_partials):
+        self.shards, self.distributed, self.group, self.merge = list(shards), distributed, group, merge
+        if not distributed:
+            assert [s.rank for s in self.shards] == list(range(self.shards[0].world)), "emulation needs every rank"
+        self.last_ids = []
+
+    def _all_gather(self, local):
+        """local: (n_local_shards, ...) -> (world, ...) in rank order."""
+        if not self.distributed:
+            return local
+        import torch.distributed as dist
+
+        out = torch.empty((dist.get_world_size(self.group),) + tuple(local.shape[1:]), dtype=local.dtype,
+                          device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
+        return out
+
+    def _all_reduce(self, t):
+        if self.distributed:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def append(self, q, k, v):
+        """q (H, 1, D), k and v (H_kv, 1, D) of one new token -> attention output (H, 1, D)."""
+        s0 = self.shards[0]
+        cand = self._all_gather(torch.stack([s.begin(q, k, v) for s in self.shards]))  # (G, 2, topk) int32
+        if s0.n_total <= s0.topk:  # every unit, in id order, no scoring (context_manager.py:370-371)
+            ids = list(range(s0.n_total))
+        else:
+            ids = global_topk(cand[:, 0].contiguous().view(torch.float32), cand[:, 1], s0.topk).tolist()
+        self.last_ids = ids
+        parts = self._all_gather(torch.stack([s.attend(ids) for s in self.shards]))  # (G, H*(D+1)) fp32
+        H, D = s0.H, s0.D
+        out, lse = self.merge(parts[:, :H * D].reshape(-1, H, D).contiguous(), parts[:, H * D:].contiguous(), s0.dtype)
+        sealing = [s.finish(lse) for s in self.shards]
+        if sealing[0] is not None:
+            total = self._all_reduce(torch.stack(sealing).sum(dim=0))
+            for s in self.shards:
+                s.seal(total)
+        return out.view(H, 1, D)

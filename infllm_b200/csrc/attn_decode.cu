@@ -369,10 +369,15 @@ int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int
   if (n_part > 8192) return fail(INFLLM_E_CAPACITY, "lse_merge: %d partials (at most 8192)", n_part);
   if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
     return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
-  INFLLM_DISPATCH_DTYPE(dtype, T, {
-    lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
-        part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
-  });
+  if (dtype == INFLLM_F32) {
+    lse_merge_kernel<float><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
+        part_o, part_lse, n_part, n_heads, head_dim, (float*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
+  } else {
+    INFLLM_DISPATCH_DTYPE(dtype, T, {
+      lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
+          part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
+    });
+  }
   INFLLM_LAUNCH_OK("lse_merge_kernel");
   return INFLLM_OK;
 }

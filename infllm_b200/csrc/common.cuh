@@ -61,6 +61,13 @@ struct Act<__half> {
   static __device__ __forceinline__ __half2 from_f2(float a, float b) { return __floats2half2_rn(a, b); }
 };
 
+// fp32 as an output type of the log-sum-exp merge (per-rank partials that are merged again)
+template <>
+struct Act<float> {
+  static __device__ __forceinline__ float to_f(float x) { return x; }
+  static __device__ __forceinline__ float from_f(float x) { return x; }
+};
+
 // dispatch a lambda-like macro on the runtime dtype code
 #define INFLLM_DISPATCH_DTYPE(dtype, T, ...)                          \
   do {                                                                \

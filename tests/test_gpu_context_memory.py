@@ -217,3 +217,52 @@ def test_decode_over_a_synthetic_memory_matches_oracle():
         assert list(cm.cached_blocks[0].items()) == [(b, float(s)) for b, s in ora.lru.entries.items()]
     assert cm.info()["num_blocks"] == ora.num_blocks == 41
     assert len({i for i, _, _ in ora.mismatches}) <= 7
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_unit_range_sharded_decode_matches_oracle(world):
+    """The memory split by unit range over `world` ranks (all emulated in this process on one GPU, the gathers
+    being plain stacks): the global retrieval equals the unsharded scorer's and the merged outputs follow the
+    oracle through a sealing."""
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM, ShardedDecodeMemory, UnitRangeShard, unit_range
+
+    H, HKV, D, n_units = 8, 2, 128, 40
+    cfg = dict(n_init=128, n_local=512, max_cached=6, topk=4, exc=128, repr_topk=4, base=1e6)
+    mem = _synthetic_memory(n_units, H, HKV, D, cfg["n_init"], cfg["n_local"], 128, seed=5)
+    units, block_k, init_k, init_v, win_k, win_v = mem
+    pe = RotaryEmbeddingESM(D, cfg["base"], 1.0)
+    shards = []
+    for r in range(world):
+        lo, hi = unit_range(n_units, r, world)
+        sh = UnitRangeShard(r, world, pe, cfg["n_init"], cfg["n_local"], 128, cfg["max_cached"], cfg["topk"],
+                            cfg["repr_topk"], H, HKV, D, torch.bfloat16, DEV, spare_units=1)
+        sh.load_synthetic(n_units, units[lo:hi], block_k[lo:hi], init_k, init_v, win_k, win_v)
+        shards.append(sh)
+    mem_sharded = ShardedDecodeMemory(shards)
+    cm = ContextManager(pe, cfg["n_init"], cfg["n_local"], 128, cfg["max_cached"], cfg["topk"], cfg["exc"], None, False,
+                        cfg["repr_topk"])
+    cm.load_synthetic(*mem)
+    ora = _oracle_from_synthetic(*mem, cfg)
+    g = torch.Generator().manual_seed(6)
+    flips = 0
+    for step in range(260):  # two sealings; the second one makes the last rank's store grow
+        q = torch.randn(H, 1, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(HKV, 1, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(HKV, 1, D, generator=g).to(torch.bfloat16)
+        got = mem_sharded.append(q.to(DEV), k.to(DEV), v.to(DEV)).float().cpu()
+        dq, dk, dv = (t[None].to(DEV) for t in (q, k, v))
+        single = cm.append(dq, dk, dv, dq, dk, dv)[0].float().cpu()
+        ids_single = cm.last_topk()[0]
+        flips += mem_sharded.last_ids != ids_single
+        ora.forced += [mem_sharded.last_ids]
+        want = ora.append(q.float(), k.float(), v.float())
+        diff = (got - want).abs()
+        assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL, f"step {step}"
+        if mem_sharded.last_ids == ids_single:
+            assert (got - single).abs().max().item() <= MAX_ABS_TOL
+    assert flips <= 8, f"{flips} retrievals differ from the unsharded scorer's"
+    assert shards[0].n_total == ora.num_blocks == n_units + 2
+    assert sum(s.n_owned for s in shards) == n_units + 2
+    want_rows = torch.stack(ora.block_k[n_units:])
+    got_rows = shards[-1].block_k[shards[-1].n_owned - 2:shards[-1].n_owned].float().cpu()
+    assert ((got_rows - want_rows).abs().amax(dim=1) < 2e-2).float().mean() >= 0.5
