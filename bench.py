@@ -322,8 +322,7 @@ def run_ours(args, rank, world, local_rank):
         v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
         line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port", seconds=secs,
                                     sample=SAMPLE_DESC.format(n=2048, eb=4))
-    if rank == 0:
-        print(json.dumps(line))
+    return line
 
 
 # ------------------------------------------------------------------------------ decode workload
@@ -481,8 +480,142 @@ def run_decode(args, rank, world, local_rank):
         store=dict(hits=hits, misses=misses, miss_rate=misses / max(hits + misses, 1),
                    h2d_bytes_per_token_layer=misses * 524288 / max(per_layer, 1)),
         clocks=clocks)
-    if rank == 0:
-        print(json.dumps(line))
+    return line
+
+
+def run_decode_sharded(args, rank, world, local_rank):
+    """The 1M-token decode with the memory sharded by unit range over the ranks (strong scaling: one sequence)."""
+    import torch.distributed as dist
+
+    from infllm_b200 import _lib
+    from infllm_b200.attention import RotaryEmbeddingESM, ShardedDecodeMemory, UnitRangeShard, unit_range
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    H, HKV, D, n, bs = CFG["H"], CFG["HKV"], CFG["D"], DEC["units"], DEC["bs"]
+    rope = RotaryEmbeddingESM(D, CFG["base"], 1.0)
+    # per-rank working set of one layer shrinks with the world size: more layers take turns to stay above L2
+    n_layers = DEC["layers"] * world
+    lo, hi = unit_range(n, rank, world)
+    mems, dirs = [], []
+    for li in range(n_layers):
+        gs = torch.Generator(device=dev).manual_seed(7000 + li)  # the same on every rank
+        direction = torch.randn((H, 1, D), generator=gs, device=dev)
+        direction = direction / direction.norm(dim=-1, keepdim=True)
+        rotated = rope.apply_rotary_pos_emb_one_angle(direction.to(torch.bfloat16)[None], DEC["n_local"])[0].float().reshape(-1)
+        small = lambda *shape: torch.randn(shape, generator=gs, device=dev).to(torch.bfloat16).cpu()  # noqa: E731
+        init_k, init_v = small(HKV, DEC["n_init"], D), small(HKV, DEC["n_init"], D)
+        win_k, win_v = small(HKV, DEC["n_local"], D), small(HKV, DEC["n_local"], D)
+        n_plant = max(1, int(n * DEC["planted_frac"]))
+        planted = torch.randperm(n, generator=torch.Generator().manual_seed(7100 + li))[:n_plant]
+        lean = torch.linspace(9.0, 3.0, n_plant)
+        gr = torch.Generator(device=dev).manual_seed(9000 + 131 * li + rank)  # this rank's own units
+        units = torch.empty((hi - lo, 2, HKV, bs, D), dtype=torch.bfloat16)
+        for s0 in range(0, hi - lo, 512):
+            m = min(512, hi - lo - s0)
+            units[s0:s0 + m] = torch.randn((m, 2, HKV, bs, D), generator=gr, device=dev).to(torch.bfloat16).cpu()
+        block_k = torch.randn((hi - lo, H * D), generator=gr, device=dev)
+        for b, a in zip(planted.tolist(), lean.tolist()):
+            if lo <= b < hi:
+                block_k[b - lo] = 0.7 * block_k[b - lo] + a * rotated
+        sh = UnitRangeShard(rank, world, rope, DEC["n_init"], DEC["n_local"], bs, DEC["max_cached"], DEC["topk"],
+                            DEC["repr_topk"], H, HKV, D, torch.bfloat16, dev)
+        sh.load_synthetic(n, units, block_k.to(torch.bfloat16).cpu(), init_k, init_v, win_k, win_v)
+        del units, block_k
+        mems.append(ShardedDecodeMemory([sh], distributed=True))
+        dirs.append(direction)
+    total = (args.warmup + 2 * args.steps + 2) * n_layers
+    g = torch.Generator(device=dev).manual_seed(100)  # the same token stream on every rank
+    lean_q = torch.stack([dirs[i % n_layers] for i in range(total)])
+    qs = (torch.randn((total, H, 1, D), generator=g, device=dev) + 3.0 * lean_q).to(torch.bfloat16)
+    ks = torch.randn((total, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    vs = torch.randn((total, HKV, 1, D), generator=g, device=dev).to(torch.bfloat16)
+    h_q, h_k, h_v = (t.cpu().pin_memory() for t in (qs, ks, vs))
+    h_o = torch.empty((H, 1, D), dtype=torch.bfloat16).pin_memory()
+    pos = [0]
+
+    def step_device():
+        for m in mems:
+            i = pos[0]
+            pos[0] += 1
+            m.append(qs[i], ks[i], vs[i])
+
+    def step_host():
+        for m in mems:
+            i = pos[0]
+            pos[0] += 1
+            q, k, v = (t[i].to(dev, non_blocking=True) for t in (h_q, h_k, h_v))
+            h_o.copy_(m.append(q, k, v), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    with torch.inference_mode():
+        for _ in range(args.warmup):
+            step_device()
+        shards = [m.shards[0] for m in mems]
+        for sh in shards:
+            sh.profile = True
+            sh.hits = sh.misses = 0
+        clk_p, clk_f = sample_clocks_start(local_rank)
+        l0 = _lib.lib.infllm_launch_count()
+        ms = timed(step_device, args.steps)
+        launches = _lib.lib.infllm_launch_count() - l0
+        prof = [sh.get_profile() for sh in shards]
+        for sh in shards:
+            sh.profile = False
+        clocks = sample_clocks_stop(clk_p, clk_f)
+        hits, misses = sum(sh.hits for sh in shards), sum(sh.misses for sh in shards)
+        step_host()
+        ms_e2e = timed(step_host, args.steps)
+    _, hbm_peak, which = measured_peaks()
+    per_layer = args.steps * n_layers
+    topk_ms = sum(p["topk"][0] for p in prof)
+    topk_n = sum(p["topk"][1] for p in prof)
+    dec_ms = sum(p["decode"][0] for p in prof)
+    dec_n = sum(p["decode"][1] for p in prof)
+    topk_bytes = float(hi - lo) * H * D * 2
+    achieved = topk_bytes * topk_n / (topk_ms / 1e3) / 1e9 if topk_ms > 0 else None
+    counts = torch.tensor([hits, misses], dtype=torch.float64, device=dev)
+    dist.all_reduce(counts)
+    line = dict(
+        metric="decode-attn us/token @1M ctx", value=1e3 * ms / per_layer, unit="us/token", n_gpus=world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=False, scaling="strong",
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload=f"mistral-7b-shaped layer, decode over {n} memory units of 128 tokens "
+                             f"({DEC['n_init'] + n * bs + DEC['n_local']} tokens) sharded by unit range over {world} GPUs, "
+                             "topk 32, repr_topk 4, max_cached 32 per GPU, n_local 4096, n_init 128; 1% planted units "
+                             f"with graded lean; a step is one token through {n_layers} layers, value is per layer",
+                    l2=f"{n_layers} layers take turns so that each rank's working set exceeds the 126 MB L2",
+                    parallelism=f"unit-range x{world}: all-gather of (score, id) candidates and of (o, lse) partials "
+                                "per token, all-reduce of 128 score columns per sealed unit (NCCL)"),
+        e2e=dict(value=1e3 * ms_e2e / per_layer, unit="us/token", h2d_bytes_per_step=int((H + 2 * HKV) * D * 2 * n_layers),
+                 d2h_bytes_per_step=int(H * D * 2 * n_layers)),
+        gpu_launches=int(launches),
+        roofline=dict(bound="hbm", kernel="block_score_topk_kernel + topk_fast_kernel (this rank's units)",
+                      achieved=achieved, peak=hbm_peak, unit="GB/s", frac=(achieved / hbm_peak if achieved else None),
+                      traffic=None, peak_source=f"hbm_gbs of {which}", launches=int(topk_n),
+                      us_per_launch=1e3 * topk_ms / max(topk_n, 1), bytes_per_launch=topk_bytes),
+        decode_attention=dict(kernels="attn_decode_kernel + lse_merge_kernel (rank 0)",
+                              us_per_launch=1e3 * dec_ms / max(dec_n, 1)),
+        store=dict(hits=int(counts[0].item()), misses=int(counts[1].item()),
+                   miss_rate=counts[1].item() / max(counts.sum().item(), 1)),
+        clocks=clocks)
+    return line
 
 
 def main():
@@ -492,8 +625,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=None, help="default 3 (prefill) or 16 (decode)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=CFG["tokens"])
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"],
-                    help="prefill: 131072-token prompt (the default, the first half of the metric); decode: 1M-token decode")
+    ap.add_argument("--workload", default="both", choices=["both", "prefill", "decode"],
+                    help="prefill: 131072-token prompt, the first half of the metric and the line's value; decode: the "
+                         "1M-token decode, the second half; both (default): the prefill line with the decode line "
+                         "under its key 'decode'")
+    ap.add_argument("--decode-steps", type=int, default=128, help="decode tokens timed when --workload both")
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
     ap.add_argument("--layers", type=int, default=DEC["layers"], help="layer memories that take turns in the decode workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
@@ -506,6 +642,7 @@ def main():
         args.steps = 256 if args.workload == "decode" else 3
     if args.warmup is None:
         args.warmup = 16 if args.workload == "decode" else 3
+    args.warmup = max(args.warmup, 3)  # fewer warm-up steps would time cold caches and first-use allocations
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -518,10 +655,22 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    decode = run_decode_sharded if world > 1 else run_decode
     if args.workload == "decode":
-        run_decode(args, rank, world, local_rank)
+        line = decode(args, rank, world, local_rank)
     else:
-        run_ours(args, rank, world, local_rank)
+        line = run_ours(args, rank, world, local_rank)
+        if args.workload == "both":
+            import copy
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            dargs = copy.copy(args)
+            dargs.steps, dargs.warmup = args.decode_steps, 16
+            line["decode"] = decode(dargs, rank, world, local_rank)
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
 

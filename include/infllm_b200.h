@@ -123,6 +123,18 @@ int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float*
                        int n_heads, int n_kv_heads, int head_dim, void* d_block_k_out, int dtype,
                        void* stream);
 
+/* One new token (decode), as one launch: K and V rows (n_kv_heads, head_dim; heads k_hs / v_hs elements apart)
+ * are copied to d_k_raw / d_v_out (heads kv_hs apart), K is also rotated to position pos_local into d_k_rot, Q
+ * (n_heads rows, q_hs apart) is rotated to pos_local into d_q_loc and to pos_global into d_q_glb (heads qs_hs
+ * apart), d_qbar (n_heads*head_dim fp32) receives d_q_glb — the query mean of a one-token exec block
+ * (context_manager.py:373-375) — and d_score[h * score_hs] = 0 opens the token's score column.  Replaces the
+ * per-token torch.cat / RoPE calls of ContextManager.append (context_manager.py:700-747) and _append (:480). */
+int infllm_ingest_token(const void* d_q, int64_t q_hs, const void* d_k, int64_t k_hs, const void* d_v, int64_t v_hs,
+                        void* d_q_loc, void* d_q_glb, int64_t qs_hs, float* d_qbar, void* d_k_raw, void* d_k_rot,
+                        void* d_v_out, int64_t kv_hs, float* d_score, int64_t score_hs, int n_heads, int n_kv_heads,
+                        int head_dim, const float* d_cos, const float* d_sin, int64_t table_len, int64_t pos_local,
+                        int64_t pos_global, int dtype, void* stream);
+
 /* ---------------------------------------------------------- decode attention
  * Split-K attention of ONE query token per head over a list of key/value segments, followed by a
  * log-sum-exp merge; replaces the two attn.append calls of ContextManager._append
@@ -148,6 +160,14 @@ int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_heads, int n_kv
                        int logit_seg, float* d_logits, int dtype, void* stream);
 int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads, int head_dim,
                      void* d_out, int64_t o_hs, float* d_lse, int dtype, void* stream);
+/* The same merge over partials that lie part_o_stride / part_lse_stride floats apart (e.g. rows [o | lse] as the
+ * ranks' all-gather delivers them).  With d_logits (n_heads, logit_len), the scaled log2-domain logits that
+ * infllm_attn_decode exported for a window segment, it also adds the token's attention row into the accumulated
+ * local scores: d_score[h * score_hs + j] += exp2(d_logits[h, j] - lse[h]) (context_manager.py:488, 623-625). */
+int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride, const float* d_part_lse,
+                        int64_t part_lse_stride, int n_part, int n_heads, int head_dim, void* d_out, int64_t o_hs,
+                        float* d_lse, int dtype, const float* d_logits, int64_t logit_len, float* d_score,
+                        int64_t score_hs, void* stream);
 
 /* infllm_attn_decode_noalloc has no counterpart in the reference.  It is infllm_attn_decode followed by
  * infllm_lse_merge in one call that allocates nothing: the split-K partials go to a scratch array that is

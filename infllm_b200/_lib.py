@@ -77,6 +77,11 @@ SIGNATURES = {
                                            c_void_p, c_int64, c_void_p, c_int, c_void_p]),
     "infllm_lse_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int,
                                  c_void_p]),
+    "infllm_lse_merge_ex": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                    c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "infllm_ingest_token": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
+                                    c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "infllm_ctx_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),
     "infllm_ctx_destroy": (c_int, [c_void_p]),
     "infllm_ctx_reset": (c_int, [c_void_p]),

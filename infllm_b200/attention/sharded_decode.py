@@ -20,6 +20,7 @@ process when the ranks are emulated on a single GPU) and the collectives between
 """
 import ctypes
 
+import numpy as np
 import torch
 
 from .. import _lib
@@ -34,24 +35,11 @@ def unit_range(n_total, rank, world):
 
 def global_topk(scores, ids, k):
     """The k best of the gathered candidates: descending score, ties to the lower id (the order of the
-    single-GPU scorer).  `ids` < 0 mark padding.  Returns a 1-D int32 tensor of at most k ids."""
-    scores, ids = scores.reshape(-1), ids.reshape(-1)
-    keep = ids >= 0
-    scores, ids = scores[keep], ids[keep]
-    by_id = torch.argsort(ids, stable=True)
-    by_score = torch.argsort(-scores[by_id], stable=True)
-    return ids[by_id[by_score[:k]]].to(torch.int32)
-
-
-def merge_partials(part_o, part_lse, out_dtype):
-    """Log-sum-exp merge of per-rank partials: part_o (G, H, D) fp32, part_lse (G, H) fp32 (log2 domain)
-    -> out (H, D) in out_dtype, lse (H,) fp32."""
-    G, H, D = part_o.shape
-    out = torch.empty((H, D), dtype=out_dtype, device=part_o.device)
-    lse = torch.empty((H,), dtype=torch.float32, device=part_o.device)
-    _lib.check(_lib.lib.infllm_lse_merge(part_o.data_ptr(), part_lse.data_ptr(), G, H, D, out.data_ptr(), D,
-                                         lse.data_ptr(), _lib.dtype_code(out_dtype), _lib.stream_ptr()))
-    return out, lse
+    single-GPU scorer).  `ids` < 0 mark padding.  Host tensors in, a list of at most k ids out."""
+    scores = scores.reshape(-1).numpy()
+    ids = ids.reshape(-1).numpy()
+    order = np.lexsort((ids, -scores))  # last key first: by score descending, then by id ascending
+    return [int(ids[i]) for i in order if ids[i] >= 0][:k]
 
 
 class UnitRangeShard:
@@ -79,6 +67,7 @@ class UnitRangeShard:
         self.score = torch.zeros((H, self.cap), dtype=torch.float32, device=dev)
         self.q_loc = torch.empty((H, D), dtype=dtype, device=dev)
         self.q_glb = torch.empty((H, D), dtype=dtype, device=dev)
+        self.qbar = torch.empty((H * D,), dtype=torch.float32, device=dev)
         self.cos = torch.empty((self.cap, D // 2), dtype=torch.float32, device=dev)
         self.sin = torch.empty_like(self.cos)
         inv = (1.0 / (float(self.pe.base) ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).contiguous()
@@ -97,12 +86,18 @@ class UnitRangeShard:
         self.part_lse = torch.empty((self.max_parts, H), dtype=torch.float32, device=dev)
         self.logits = torch.empty((H, n_local + 1), dtype=torch.float32, device=dev)
         self.pack = torch.empty((H * (D + 1),), dtype=torch.float32, device=dev)  # [o (H, D) | lse (H)]
+        self.lse = torch.empty((H,), dtype=torch.float32, device=dev)
         self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
         self.scores_buf = None
         self.hits = self.misses = 0
+        self.profile = False  # when set, CUDA events bracket the scoring and the attention of every token
+        self._events = {"topk": [], "decode": []}
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
         self.block_k = self.host_units = self.init_k = self.init_v = None
         self._share = (0, 0)
+        m = topk + 3  # retrieved units + window share + sink + overflow
+        self._seg_arrays = ((ctypes.c_void_p * m)(), (ctypes.c_void_p * m)(), (ctypes.c_int64 * m)(),
+                            (ctypes.c_int32 * m)(), (ctypes.c_int32 * m)())
 
     def __del__(self):
         if getattr(self, "lru", None):
@@ -160,23 +155,44 @@ class UnitRangeShard:
         if self.length - self.t0 >= self.cap:
             self._compact()
         T, at, D = self.length, self.length - self.t0, self.D
-        self.k_raw[:, at] = k.reshape(self.HKV, D)
-        self.v[:, at] = v.reshape(self.HKV, D)
-        self.score[:, at] = 0
-        self._rotate(at, 1)
-        qc = q.reshape(self.H, D).contiguous()
-        self._rope(qc.data_ptr(), D, D, self.q_loc.data_ptr(), D, D, self.H, 1, T - self.t0, 1)   # window-relative
-        self._rope(qc.data_ptr(), D, D, self.q_glb.data_ptr(), D, D, self.H, 1, self.n_local - 1, 0)  # one angle
+        esz, row = self.k_raw.element_size(), at * D * self.k_raw.element_size()
+        # copies, the three rotations (keys and queries window-relative, queries at the one global angle), the
+        # query "mean" of the one-token exec block (context_manager.py:373-375) and the new score column
+        _lib.check(_lib.lib.infllm_ingest_token(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), self.q_loc.data_ptr(),
+            self.q_glb.data_ptr(), D, self.qbar.data_ptr(), self.k_raw.data_ptr() + row, self.k_rot.data_ptr() + row,
+            self.v.data_ptr() + row, self.cap * D, self.score.data_ptr() + at * 4, self.cap, self.H, self.HKV, D,
+            self.cos.data_ptr(), self.sin.data_ptr(), self.cap, T - self.t0, self.n_local - 1, self.code,
+            _lib.stream_ptr()))
+        del esz
         cand_scores = self.cand[0].view(torch.float32)
-        cand_scores.fill_(float("-inf"))
-        self.cand[1].fill_(-1)
+        if self.n_owned < self.topk:  # fewer units than a retrieval takes: pad the candidates
+            cand_scores.fill_(float("-inf"))
+            self.cand[1].fill_(-1)
         if self.n_owned > 0:
             kk = min(self.topk, self.n_owned)
-            qbar = self.q_glb.float().reshape(-1)  # the mean over a one-token exec block (context_manager.py:373-375)
-            _lib.check(_lib.lib.infllm_block_topk(self.block_k.data_ptr(), self.n_owned, self.H * D, qbar.data_ptr(),
+            ev = self._mark("topk")
+            _lib.check(_lib.lib.infllm_block_topk(self.block_k.data_ptr(), self.n_owned, self.H * D, self.qbar.data_ptr(),
                                                   self.scores_buf.data_ptr(), kk, self.lo, self.cand[1].data_ptr(),
                                                   cand_scores.data_ptr(), self.code, _lib.stream_ptr()))
+            self._mark("topk", ev)
         return self.cand
+
+    def _mark(self, slot, begin=None):
+        if not self.profile:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        if begin is not None:
+            self._events[slot].append((begin, e))
+        return e
+
+    def get_profile(self):
+        """{slot: (milliseconds, launches)} of the bracketed kernels since the last call; synchronises."""
+        torch.cuda.synchronize(self.device)
+        out = {k: (sum(a.elapsed_time(b) for a, b in v), len(v)) for k, v in self._events.items()}
+        self._events = {k: [] for k in self._events}
+        return out
 
     # ------------------------------------------------------------------ step 3
     def attend(self, ids):
@@ -211,18 +227,19 @@ class UnitRangeShard:
             lse.fill_(float("-inf"))
             return self.pack
         n = len(segs)
-        kp = (ctypes.c_void_p * n)(*[s[0] for s in segs])
-        vp = (ctypes.c_void_p * n)(*[s[1] for s in segs])
-        hs = (ctypes.c_int64 * n)(*[s[2] for s in segs])
-        ln = (ctypes.c_int32 * n)(*[s[3] for s in segs])
-        qs = (ctypes.c_int32 * n)(*[s[4] for s in segs])
+        kp, vp, hs, ln, qs = self._seg_arrays
+        for i, sg in enumerate(segs):
+            kp[i], vp[i], hs[i], ln[i], qs[i] = sg
         n_parts = ctypes.c_int()
+        self.keys_last = sum(s[3] for s in segs)
+        ev = self._mark("decode")
         _lib.check(_lib.lib.infllm_attn_decode(self.q_loc.data_ptr(), self.q_glb.data_ptr(), self.H, self.HKV, D, n, kp,
                                                vp, hs, ln, qs, self.part_o.data_ptr(), self.part_lse.data_ptr(),
                                                self.max_parts, ctypes.byref(n_parts), logit_seg,
                                                self.logits.data_ptr(), self.code, _lib.stream_ptr()))
         _lib.check(_lib.lib.infllm_lse_merge(self.part_o.data_ptr(), self.part_lse.data_ptr(), n_parts.value, self.H, D,
                                              o.data_ptr(), D, lse.data_ptr(), F32, _lib.stream_ptr()))
+        self._mark("decode", ev)
         return self.pack
 
     def _refill(self, owned):
@@ -249,15 +266,23 @@ class UnitRangeShard:
             self.cache[slot].copy_(self.host_units[b - self.lo], non_blocking=True)
 
     # ------------------------------------------------------------------ step 5
-    def finish(self, lse):
-        """Add this rank's share of the token's local attention row to the accumulated scores (lse (H,) is the
-        merged log-sum-exp) and count the token in.  Returns the (H, bs) score columns of the unit that seals
-        now — this rank's partial sums, to be all-reduced — or None."""
+    def merge(self, parts):
+        """Step 4 and the first half of step 5 on this rank: log-sum-exp merge of the gathered partials
+        (G, H*(D+1)) fp32 rows [o | lse] into the token's output (H, D), and this rank's share of the token's local
+        attention row added to the accumulated scores, in one launch."""
+        H, D = self.H, self.D
+        out = torch.empty((H, D), dtype=self.dtype, device=self.device)
         a, b = self._share
-        if b > a:
-            n = b - a
-            self.score[:, a - self.t0:b - self.t0] += torch.exp2(self.logits.view(-1)[:self.H * n].view(self.H, n)
-                                                                 - lse[:, None])
+        off = (a - self.t0) * 4
+        _lib.check(_lib.lib.infllm_lse_merge_ex(
+            parts.data_ptr(), parts.stride(0), parts.data_ptr() + H * D * 4, parts.stride(0), parts.shape[0], H, D,
+            out.data_ptr(), D, self.lse.data_ptr(), self.code, self.logits.data_ptr() if b > a else None, b - a,
+            self.score.data_ptr() + off, self.cap, _lib.stream_ptr()))
+        return out
+
+    def finish(self):
+        """Count the token in.  Returns the (H, bs) score columns of the unit that seals now — this rank's
+        partial sums, to be all-reduced — or None."""
         self.length += 1
         if self.length - self.frontier - self.bs >= self.n_local:  # context_manager.py:649
             s0 = self.frontier - self.t0
@@ -301,8 +326,8 @@ class ShardedDecodeMemory:
     (pass `group`, or leave None for the default group), or all G of them when the ranks share one process.
     """
 
-    def __init__(self, shards, distributed=False, group=None, merge=merge_partials):
-        self.shards, self.distributed, self.group, self.merge = list(shards), distributed, group, merge
+    def __init__(self, shards, distributed=False, group=None):
+        self.shards, self.distributed, self.group = list(shards), distributed, group
         if not distributed:
             assert [s.rank for s in self.shards] == list(range(self.shards[0].world)), "emulation needs every rank"
         self.last_ids = []
@@ -328,18 +353,22 @@ class ShardedDecodeMemory:
     def append(self, q, k, v):
         """q (H, 1, D), k and v (H_kv, 1, D) of one new token -> attention output (H, 1, D)."""
         s0 = self.shards[0]
-        cand = self._all_gather(torch.stack([s.begin(q, k, v) for s in self.shards]))  # (G, 2, topk) int32
+        cand = self._all_gather(self._stack([s.begin(q, k, v) for s in self.shards]))  # (G, 2, topk) int32
         if s0.n_total <= s0.topk:  # every unit, in id order, no scoring (context_manager.py:370-371)
             ids = list(range(s0.n_total))
-        else:
-            ids = global_topk(cand[:, 0].contiguous().view(torch.float32), cand[:, 1], s0.topk).tolist()
+        else:  # the ids go to the host anyway (cache plans); rank the G * topk candidates there
+            c = cand.cpu()
+            ids = global_topk(c[:, 0].contiguous().view(torch.float32), c[:, 1], s0.topk)
         self.last_ids = ids
-        parts = self._all_gather(torch.stack([s.attend(ids) for s in self.shards]))  # (G, H*(D+1)) fp32
-        H, D = s0.H, s0.D
-        out, lse = self.merge(parts[:, :H * D].reshape(-1, H, D).contiguous(), parts[:, H * D:].contiguous(), s0.dtype)
-        sealing = [s.finish(lse) for s in self.shards]
+        parts = self._all_gather(self._stack([s.attend(ids) for s in self.shards]))  # (G, H*(D+1)) fp32
+        outs = [s.merge(parts) for s in self.shards]  # the same on every rank
+        sealing = [s.finish() for s in self.shards]
         if sealing[0] is not None:
-            total = self._all_reduce(torch.stack(sealing).sum(dim=0))
+            total = self._all_reduce(sealing[0] if len(sealing) == 1 else torch.stack(sealing).sum(dim=0))
             for s in self.shards:
                 s.seal(total)
-        return out.view(H, 1, D)
+        return outs[0].view(s0.H, 1, s0.D)
+
+    @staticmethod
+    def _stack(tensors):
+        return tensors[0].unsqueeze(0) if len(tensors) == 1 else torch.stack(tensors)

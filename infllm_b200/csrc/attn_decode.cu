@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(1024)
 lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part, int n_heads,
                  int head_dim, T* __restrict__ out, int64_t o_hs, float* __restrict__ lse,
                  const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs,
-                 const int32_t* __restrict__ skip) {
+                 const int32_t* __restrict__ skip, int64_t o_ps, int64_t lse_ps) {
   extern __shared__ float s_w[];  // n_part weights
   if (skip && *skip) return;  // the partials were not written: a retrieved unit was not cached
   __shared__ float s_red[32];
@@ -226,7 +226,7 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
   const int grp = tid / head_dim, d = tid % head_dim, ngrp = blockDim.x / head_dim;
   // every global load of the common case is issued before the first one is needed
   const float* po = part_o + (int64_t)h * head_dim + d;
-  const int64_t ps = (int64_t)n_heads * head_dim;
+  const int64_t ps = o_ps;  // floats from one partial to the next
   float pv[kMergeUnroll];
 #pragma unroll
   for (int u = 0; u < kMergeUnroll; ++u) {
@@ -243,7 +243,7 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
   }
   float mx = -INFINITY;
   for (int p = tid; p < n_part; p += blockDim.x) {
-    const float v = part_lse[(int64_t)p * n_heads + h];
+    const float v = part_lse[(int64_t)p * lse_ps + h];
     s_w[p] = v;
     mx = fmaxf(mx, v);
   }
@@ -364,18 +364,22 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
 
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
                      int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
-                     float* score, int64_t score_hs, const int32_t* skip) {
+                     float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps, int64_t lse_ps) {
+  if (o_ps <= 0) o_ps = (int64_t)n_heads * head_dim;
+  if (lse_ps <= 0) lse_ps = n_heads;
   if (n_part <= 0) return fail(INFLLM_E_BADARG, "lse_merge: no partials");
   if (n_part > 8192) return fail(INFLLM_E_CAPACITY, "lse_merge: %d partials (at most 8192)", n_part);
   if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
     return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
   if (dtype == INFLLM_F32) {
     lse_merge_kernel<float><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
-        part_o, part_lse, n_part, n_heads, head_dim, (float*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
+        part_o, part_lse, n_part, n_heads, head_dim, (float*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
+        o_ps, lse_ps);
   } else {
     INFLLM_DISPATCH_DTYPE(dtype, T, {
       lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
-          part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip);
+          part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
+          o_ps, lse_ps);
     });
   }
   INFLLM_LAUNCH_OK("lse_merge_kernel");
@@ -455,7 +459,7 @@ extern "C" int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, in
   // split-K kernel of this same call, whatever an earlier call left behind.
   INFLLM_TRY(attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, part_o,
                                 part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, kDecodeChunk, nullptr, 0));
-  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0, nullptr);
+  return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0, nullptr, 0, 0);
 }
 
 extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part, int n_heads,
@@ -463,5 +467,21 @@ extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, 
   using namespace infllm;
   if (!d_part_o || !d_part_lse || !d_out) return fail(INFLLM_E_BADARG, "lse_merge: null pointer");
   return lse_merge_launch(d_part_o, d_part_lse, n_part, n_heads, head_dim, d_out, o_hs, d_lse, dtype,
-                          (cudaStream_t)stream, nullptr, 0, nullptr, 0, nullptr);
+                          (cudaStream_t)stream, nullptr, 0, nullptr, 0, nullptr, 0, 0);
+}
+
+extern "C" int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride, const float* d_part_lse,
+                                   int64_t part_lse_stride, int n_part, int n_heads, int head_dim, void* d_out,
+                                   int64_t o_hs, float* d_lse, int dtype, const float* d_logits, int64_t logit_len,
+                                   float* d_score, int64_t score_hs, void* stream) {
+  using namespace infllm;
+  if (!d_part_o || !d_part_lse || !d_out) return fail(INFLLM_E_BADARG, "lse_merge_ex: null pointer");
+  if (part_o_stride < (int64_t)n_heads * head_dim || part_lse_stride < n_heads)
+    return fail(INFLLM_E_BADARG, "lse_merge_ex: partial strides %lld / %lld are shorter than a partial",
+                (long long)part_o_stride, (long long)part_lse_stride);
+  if (d_logits && (!d_score || !d_lse || logit_len < 0))
+    return fail(INFLLM_E_BADARG, "lse_merge_ex: logits without a score buffer");
+  return lse_merge_launch(d_part_o, d_part_lse, n_part, n_heads, head_dim, d_out, o_hs, d_lse, dtype,
+                          (cudaStream_t)stream, d_logits, d_logits ? logit_len : 0, d_score, score_hs, nullptr,
+                          part_o_stride, part_lse_stride);
 }

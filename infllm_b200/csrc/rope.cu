@@ -284,3 +284,19 @@ extern "C" int infllm_rope_apply(const void* d_x, int64_t x_hs, int64_t x_ts, vo
   return rope_apply_launch(d_x, x_hs, x_ts, d_out, o_hs, o_ts, n_heads, len, head_dim, d_cos, d_sin, table_len,
                            pos0, pos_step, dtype, (cudaStream_t)stream);
 }
+
+extern "C" int infllm_ingest_token(const void* d_q, int64_t q_hs, const void* d_k, int64_t k_hs, const void* d_v,
+                                   int64_t v_hs, void* d_q_loc, void* d_q_glb, int64_t qs_hs, float* d_qbar,
+                                   void* d_k_raw, void* d_k_rot, void* d_v_out, int64_t kv_hs, float* d_score,
+                                   int64_t score_hs, int n_heads, int n_kv_heads, int head_dim, const float* d_cos,
+                                   const float* d_sin, int64_t table_len, int64_t pos_local, int64_t pos_global,
+                                   int dtype, void* stream) {
+  using namespace infllm;
+  if (!d_q || !d_k || !d_v || !d_q_loc || !d_q_glb || !d_qbar || !d_k_raw || !d_k_rot || !d_v_out || !d_score || !d_cos ||
+      !d_sin)
+    return fail(INFLLM_E_BADARG, "ingest_token: null pointer");
+  if (n_heads <= 0 || n_kv_heads <= 0) return fail(INFLLM_E_BADARG, "ingest_token: %d / %d heads", n_heads, n_kv_heads);
+  return ingest_token_launch(d_q, q_hs, d_k, k_hs, d_v, v_hs, d_q_loc, d_q_glb, qs_hs, d_qbar, d_k_raw, d_k_rot, d_v_out,
+                             kv_hs, d_score, score_hs, n_heads, n_kv_heads, head_dim, d_cos, d_sin, table_len, pos_local,
+                             pos_global, dtype, (cudaStream_t)stream, nullptr);
+}

@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) building blocks used by the tensor-core attention kernels:
-// mbarrier with BOUNDED waits, TMA tile loads (no multicast), tcgen05 MMA / TMEM access,
+// mbarrier with BOUNDED waits, TMA tile loads (each into one CTA only), tcgen05 MMA / TMEM access,
 // shared-memory matrix descriptors for 128-byte-swizzled tiles.
 #pragma once
 #include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime at run time)
@@ -52,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
-// tile loads into this CTA's shared memory, completion counted on an mbarrier; never multicast
+// tile loads into this CTA's shared memory, completion counted on an mbarrier; one destination CTA per load
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"

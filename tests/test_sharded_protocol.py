@@ -48,7 +48,7 @@ class CpuShard:
         if self.block_k:
             s = torch.stack(self.block_k) @ self.q.reshape(-1)
             kk = min(TOPK, len(self.block_k))
-            best = global_topk(s, torch.arange(len(self.block_k), dtype=torch.int32), kk).long()
+            best = torch.tensor(global_topk(s, torch.arange(len(self.block_k), dtype=torch.int32), kk))
             cand[0, :kk] = s[best].view(torch.int32)
             cand[1, :kk] = (best + self.lo).to(torch.int32)
         return cand
@@ -79,9 +79,17 @@ class CpuShard:
         o = torch.einsum("hn,hnd->hd", torch.exp2(logit - lse[:, None]), vv)
         return torch.cat((o.reshape(-1), lse))
 
-    def finish(self, lse):
+    def merge(self, parts):
+        part_o, part_lse = parts[:, :H * D].reshape(-1, H, D), parts[:, H * D:]
+        mx = part_lse.max(dim=0).values
+        w = torch.exp2(part_lse - mx)
+        out = (w[:, :, None] * part_o).sum(dim=0) / w.sum(dim=0)[:, None]
+        lse = mx + torch.log2(w.sum(dim=0))
         a, b = self.share
         self.score[:, a:b] += torch.exp2(self.win_logit - lse[:, None])
+        return out
+
+    def finish(self):
         self.length += 1
         if self.length - self.frontier - BS >= N_LOCAL:
             return self.score[:, :BS].contiguous()
@@ -96,13 +104,6 @@ class CpuShard:
         self.k, self.v, self.score = self.k[:, BS:], self.v[:, BS:], self.score[:, BS:]
         self.frontier += BS
         self.n_total += 1
-
-
-def cpu_merge(part_o, part_lse, dtype):
-    mx = part_lse.max(dim=0).values
-    w = torch.exp2(part_lse - mx)
-    out = (w[:, :, None] * part_o).sum(dim=0) / w.sum(dim=0)[:, None]
-    return out.to(dtype), mx + torch.log2(w.sum(dim=0))
 
 
 def token(step):
@@ -121,8 +122,8 @@ def run(memory):
 def test_global_topk_orders_by_score_then_id():
     s = torch.tensor([1.0, 5.0, 5.0, -2.0, 7.0, float("-inf")])
     i = torch.tensor([9, 4, 2, 1, 8, -1], dtype=torch.int32)
-    assert global_topk(s, i, 3).tolist() == [8, 2, 4]
-    assert global_topk(s, i, 10).tolist() == [8, 2, 4, 9, 1]  # padding never comes back
+    assert global_topk(s, i, 3) == [8, 2, 4]
+    assert global_topk(s, i, 10) == [8, 2, 4, 9, 1]  # padding never comes back
 
 
 def test_unit_ranges_cover_every_unit_once():
@@ -134,8 +135,8 @@ def test_unit_ranges_cover_every_unit_once():
 
 @pytest.mark.parametrize("world", [2, 3])
 def test_emulated_ranks_match_one_rank(world):
-    want, want_ids = run(ShardedDecodeMemory([CpuShard(0, 1)], merge=cpu_merge))
-    got, got_ids = run(ShardedDecodeMemory([CpuShard(r, world) for r in range(world)], merge=cpu_merge))
+    want, want_ids = run(ShardedDecodeMemory([CpuShard(0, 1)]))
+    got, got_ids = run(ShardedDecodeMemory([CpuShard(r, world) for r in range(world)]))
     assert got_ids == want_ids
     assert (got - want).abs().max().item() < 1e-4
     assert STEPS // BS >= 4  # several units sealed on the way
@@ -145,14 +146,14 @@ def _worker(rank, world, port, path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        got, ids = run(ShardedDecodeMemory([CpuShard(rank, world)], distributed=True, merge=cpu_merge))
+        got, ids = run(ShardedDecodeMemory([CpuShard(rank, world)], distributed=True))
         torch.save((got, ids), f"{path}.{rank}")
     finally:
         dist.destroy_process_group()
 
 
 def test_two_gloo_ranks_match_one_rank(tmp_path):
-    want, want_ids = run(ShardedDecodeMemory([CpuShard(0, 1)], merge=cpu_merge))
+    want, want_ids = run(ShardedDecodeMemory([CpuShard(0, 1)]))
     path = str(tmp_path / "out")
     mp.spawn(_worker, args=(2, 29500 + os.getpid() % 1000, path), nprocs=2, join=True)
     for rank in range(2):
