@@ -213,7 +213,9 @@ typedef struct infllm_config {
                            *  2: no look-ahead retrieval: every exec block waits for its ids from the device
                            *  4: look-ahead units staged by an SM copy kernel instead of one cudaMemcpyAsync each
                            *  8: the two-heads-per-CTA tcgen05 attention kernel (experimental)
-                           * 16: one-token appends wait for the retrieved ids before launching the attention */
+                           * 16: one-token appends wait for the retrieved ids before launching the attention
+                           * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
+                           * at most 8); the cache gets that many times topk spare slots */
 } infllm_config;
 
 /* Validates the configuration (exc_block_size <= n_local, context_manager.py:219;

@@ -167,6 +167,8 @@ struct infllm_ctx {
   // unit store
   void* cache = nullptr;  // (max_cached, 2, H_kv, bs, D)
   std::vector<int> free_slots;
+  std::vector<cudaEvent_t> slot_ev;   // per slot: behind the last look-ahead copy into it
+  std::vector<char> slot_ev_used;
   std::unordered_map<int32_t, int> slot_of;
   // device copy of slot_of for the decode attention that resolves the retrieved units itself
   int32_t* d_slot_table = nullptr;
@@ -200,15 +202,18 @@ struct infllm_ctx {
     std::vector<int32_t> ids;
     int32_t* h_ids = nullptr;  // pinned: ids written by the device
     cudaEvent_t ev = nullptr;
+    cudaEvent_t ev_staged = nullptr;  // on the copy stream, behind the copies staged for this exec block
+    bool staged_recorded = false;
   };
-  static constexpr int kLookDepth = 2;            // exec blocks ranked ahead
-  LookAhead la[kLookDepth + 1];
+  static constexpr int kMaxLookDepth = 8;
+  int look_depth = 2;                             // exec blocks ranked ahead (cfg.reserved[1] overrides)
+  LookAhead la[kMaxLookDepth + 1];
   std::unordered_map<int32_t, int64_t> staged_for;  // staged unit -> latest exec block that wants it
   int32_t* h_spec = nullptr;        // pinned: look-ahead ids
   int32_t* h_cand_rows = nullptr;   // pinned: candidate unit ids
   float* h_cand_scores = nullptr;   // pinned: their scores
   float* d_cand_scores = nullptr;   // device side of the same mailbox
-  int32_t* d_spec = nullptr;        // device side of the look-ahead id mailboxes, (kLookDepth + 1) x topk
+  int32_t* d_spec = nullptr;        // device side of the look-ahead id mailboxes, (look_depth + 1) x topk
   cudaStream_t mail_stream = nullptr;  // carries the small result copies to the host, off the main stream
   int cand_cap = 0;
   std::unordered_map<int32_t, int> staged;  // unit -> slot holding a prefetched copy
@@ -222,12 +227,14 @@ struct infllm_ctx {
   cudaStream_t d2h_stream = nullptr;
   cudaEvent_t ev_d2h = nullptr, ev_ingest = nullptr;
   bool d2h_recorded = false;
+  int64_t d2h_synced_upto_urgent = 0;  // the same bookkeeping for the urgent stream
   int64_t d2h_synced_upto = 0;  // units below this id are known to be in the host store as far as copy_stream is concerned
 
   cudaStream_t copy_stream = nullptr, aux_stream = nullptr;
-  cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr, ev_spec = nullptr,
+  cudaEvent_t ev_main = nullptr, ev_copy = nullptr, ev_sync = nullptr, ev_attn = nullptr, ev_attn_prev = nullptr, ev_spec = nullptr,
               ev_cand = nullptr, ev_seal = nullptr, ev_stage = nullptr;
-  bool attn_recorded = false, spec_recorded = false;
+  bool attn_recorded = false, attn_prev_recorded = false, spec_recorded = false;
+  cudaStream_t urgent_stream = nullptr;  // copies an exec block is waiting for, past the queue of staged copies
 
   // optional per-kernel timing (infllm_ctx_profile): CUDA events around the launches on their stream
   bool prof = false;
@@ -320,6 +327,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
 
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->urgent_stream, cudaStreamNonBlocking));
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_d2h, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_ingest, cudaEventDisableTiming));
@@ -332,6 +340,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_copy, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_sync, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_attn, cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_attn_prev, cudaEventDisableTiming));
   {
     int lo = 0, hi = 0;  // the look-ahead kernels are short and latency matters: highest priority
     INFLLM_CUDA_OK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -378,15 +387,16 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMemsetAsync(c->tickets, 0, 2 * sizeof(unsigned int), s));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
-  c->cand_cap = g.topk + (infllm_ctx::kLookDepth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
+  c->cand_cap = g.topk + (c->look_depth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
   for (auto& l : c->la) {
     INFLLM_CUDA_OK(cudaHostAlloc((void**)&l.h_ids, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
     INFLLM_CUDA_OK(cudaEventCreateWithFlags(&l.ev, cudaEventDisableTiming));
+    INFLLM_CUDA_OK(cudaEventCreateWithFlags(&l.ev_staged, cudaEventDisableTiming));
   }
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_rows, c->cand_cap * sizeof(int32_t), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_cand_scores, c->cand_cap * sizeof(float), cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_cand_scores, c->cand_cap * sizeof(float)));
-  INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_spec, (infllm_ctx::kLookDepth + 1) * std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_spec, (c->look_depth + 1) * std::max(1, g.topk) * sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->mail_stream, cudaStreamNonBlocking));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
@@ -395,7 +405,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
   // max_cached_block slots hold the cache proper; topk more per look-ahead step hold the copies staged ahead
-  const int64_t n_slots = (int64_t)g.max_cached_block + (int64_t)infllm_ctx::kLookDepth * g.topk;
+  const int64_t n_slots = (int64_t)g.max_cached_block + (int64_t)c->look_depth * g.topk;
   INFLLM_CUDA_OK(cudaMalloc(&c->cache, n_slots * c->unit_bytes));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, n_slots * c->unit_bytes, s));
   c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.reserved[0] & 1);
@@ -414,6 +424,8 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   }
   c->free_slots.clear();
   for (int i = (int)n_slots - 1; i >= 0; --i) c->free_slots.push_back(i);
+  c->slot_ev.assign(n_slots, nullptr);
+  c->slot_ev_used.assign(n_slots, 0);
   c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
   c->initialized = true;
   return INFLLM_OK;
@@ -545,10 +557,11 @@ int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaS
 // look-ahead for a LATER exec block of the call, on the second stream: top-k over the units sealed so far
 int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   const infllm_config& g = c->cfg;
-  infllm_ctx::LookAhead& la = c->la[target % (infllm_ctx::kLookDepth + 1)];
+  infllm_ctx::LookAhead& la = c->la[target % (c->look_depth + 1)];
   la.target = target;
   la.launched = true;
   la.staged = false;
+  la.staged_recorded = false;
   la.n_spec = c->num_blocks;
   la.ids.clear();
   if (la.n_spec <= g.topk) return INFLLM_OK;  // every known unit is a candidate; nothing to rank
@@ -564,7 +577,7 @@ int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   }
   trace_mark(c, c->aux_stream, TR_SPEC_BEGIN, target);
   ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)la.n_spec * c->width * c->esz);
-  int32_t* d_ids = c->d_spec + (target % (infllm_ctx::kLookDepth + 1)) * std::max(1, g.topk);
+  int32_t* d_ids = c->d_spec + (target % (c->look_depth + 1)) * std::max(1, g.topk);
   INFLLM_TRY(block_topk_launch(c->block_k, la.n_spec, (int)c->width, c->qbar + target * c->width, c->scores_aux,
                                g.topk, 0, d_ids, nullptr, g.dtype, c->aux_stream, c->tickets + 1));
   INFLLM_CUDA_OK(cudaMemcpyAsync(la.h_ids, d_ids, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->aux_stream));
@@ -575,10 +588,20 @@ int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   return INFLLM_OK;
 }
 
+// an event behind the copy just issued into a cache slot on the copy stream: whoever later writes the slot from
+// another stream waits for it (the copy may have been abandoned, never awaited, and still be in flight)
+int mark_slot_copy(infllm_ctx* c, void* slot_ptr) {
+  const int slot = (int)(((char*)slot_ptr - (char*)c->cache) / c->unit_bytes);
+  if (!c->slot_ev[slot]) INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->slot_ev[slot], cudaEventDisableTiming));
+  INFLLM_CUDA_OK(cudaEventRecord(c->slot_ev[slot], c->copy_stream));
+  c->slot_ev_used[slot] = 1;
+  return INFLLM_OK;
+}
+
 // after the look-ahead ids arrived: copy the ones that are not resident into spare slots (side stream)
 int lookahead_stage(infllm_ctx* c, int64_t target) {
   const infllm_config& g = c->cfg;
-  infllm_ctx::LookAhead& la = c->la[target % (infllm_ctx::kLookDepth + 1)];
+  infllm_ctx::LookAhead& la = c->la[target % (c->look_depth + 1)];
   if (la.n_spec <= g.topk) {
     for (int64_t b = 0; b < la.n_spec; ++b) la.ids.push_back((int32_t)b);
   } else {
@@ -611,15 +634,25 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     c->staged_pending = true;
   }
   if (!src.empty()) {
+    // the spare slots taken above may have held units that the previous exec block's attention read
+    if (c->attn_prev_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn_prev, 0));
     if (!(g.reserved[0] & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
                                  // SM copy kernel, which is faster alone but slows concurrent attention down
-      for (size_t i = 0; i < src.size(); ++i)
+      for (size_t i = 0; i < src.size(); ++i) {
         INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+        INFLLM_TRY(mark_slot_copy(c, dst[i]));
+      }
     } else {
       INFLLM_TRY(stage_units_launch(src.data(), dst.data(), (int)src.size(), c->unit_bytes, c->copy_stream));
+      for (size_t i = 0; i < src.size(); ++i) INFLLM_TRY(mark_slot_copy(c, dst[i]));
     }
   }
-  if (c->staged_pending) INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+  if (c->staged_pending) {
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+    // the exec block this batch is for waits for this event only, not for batches staged later for later blocks
+    INFLLM_CUDA_OK(cudaEventRecord(la.ev_staged, c->copy_stream));
+    la.staged_recorded = true;
+  }
   trace_mark(c, c->copy_stream, TR_STAGE_END, target);
   return INFLLM_OK;
 }
@@ -627,7 +660,7 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
 // score the candidates of the next exec block (look-ahead ids + units sealed since) on s; results to pinned memory
 int candidates_launch(infllm_ctx* c, int64_t eb_next, int* n_cand, cudaStream_t s) {
   const infllm_config& g = c->cfg;
-  const infllm_ctx::LookAhead& la = c->la[eb_next % (infllm_ctx::kLookDepth + 1)];
+  const infllm_ctx::LookAhead& la = c->la[eb_next % (c->look_depth + 1)];
   const int64_t n_spec = la.n_spec;
   const std::vector<int32_t>& spec_ids = la.ids;
   const int64_t n_now = c->num_blocks;
@@ -680,7 +713,20 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
   for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
     auto it = c->slot_of.find(b);
     if (it != c->slot_of.end()) {
-      c->free_slots.push_back(it->second);
+      // a look-ahead that found this unit cached did not stage it: if a later exec block wants it, the slot keeps
+      // its data as a staged copy instead of going back to the pool
+      int64_t wanted_by = -1;
+      for (int i = 0; i <= c->look_depth; ++i) {
+        const infllm_ctx::LookAhead& l = c->la[i];
+        if (l.launched && l.staged && l.target > eb && std::find(l.ids.begin(), l.ids.end(), b) != l.ids.end())
+          wanted_by = std::max(wanted_by, l.target);
+      }
+      if (wanted_by >= 0) {
+        c->staged[b] = it->second;
+        c->staged_for[b] = wanted_by;
+      } else {
+        c->free_slots.push_back(it->second);
+      }
       c->slot_of.erase(it);
       if (track) c->tab_updates[b] = -1;
     }
@@ -719,21 +765,39 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       c->staged_for.erase(victim->first);
       c->staged.erase(victim);
     }
-    if (!late) {
-      // slots freed above may still be read by the previous exec block's attention
-      if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn, 0));
-      late = true;
-    }
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[b] = slot;
     if (track) c->tab_updates[b] = slot;
-    if (b >= c->d2h_synced_upto) {
-      INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
-      c->d2h_synced_upto = c->num_blocks;
+    const int64_t tok0 = (int64_t)g.n_init + (int64_t)b * g.block_size;  // the unit's first token
+    if (tok0 >= c->tb.t0 && tok0 + g.block_size <= c->length) {
+      // sealed so recently that its tokens are still in the token buffers: copy on the device, on the main stream
+      // (behind the sealing), instead of waiting for the copy-out to land and coming back over PCIe
+      const int64_t D = g.head_dim, row = (int64_t)g.block_size * D * c->esz;
+      char* dst = (char*)c->cache + (int64_t)slot * c->unit_bytes;
+      const int64_t src = (tok0 - c->tb.t0) * D * c->esz, pitch = c->tb.cap * D * c->esz;
+      // a look-ahead copy into this slot that was abandoned may still be in flight on the copy stream
+      if (c->slot_ev_used[slot]) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->slot_ev[slot], 0));
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync(dst, row, (char*)c->tb.k_raw + src, pitch, row, g.n_kv_heads,
+                                       cudaMemcpyDeviceToDevice, s));
+      INFLLM_CUDA_OK(cudaMemcpy2DAsync(dst + c->unit_bytes / 2, row, (char*)c->tb.v + src, pitch, row, g.n_kv_heads,
+                                       cudaMemcpyDeviceToDevice, s));
+      continue;
     }
+    if (!late) {
+      // slots freed above may still be read by the previous exec block's attention
+      if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->ev_attn, 0));
+      late = true;
+    }
+    // an abandoned look-ahead copy into this slot may still be in flight on the copy stream
+    if (c->slot_ev_used[slot]) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->slot_ev[slot], 0));
+    if (b >= c->d2h_synced_upto_urgent) {
+      if (c->d2h_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->ev_d2h, 0));
+      c->d2h_synced_upto_urgent = c->num_blocks;
+    }
+    // on a stream of its own: the exec block must not wait behind the copies staged for later blocks
     INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
-                                   cudaMemcpyHostToDevice, c->copy_stream));
+                                   cudaMemcpyHostToDevice, c->urgent_stream));
     c->counters.h2d_bytes += c->unit_bytes;
   }
   // look-ahead copies that were not wanted: their slots go back to the pool (later copies into them are
@@ -748,10 +812,13 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     }
   }
   if (late) {
-    INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->copy_stream));
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->urgent_stream));
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
-  } else if (adopted && c->staged_pending) {
-    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_stage, 0));
+  }
+  if (adopted && c->staged_pending) {
+    const infllm_ctx::LookAhead& la = c->la[eb % (c->look_depth + 1)];
+    const bool own = la.target == eb && la.staged && la.staged_recorded;
+    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, own ? la.ev_staged : c->ev_stage, 0));
   }
   if (c->staged.empty()) c->staged_pending = false;
   return INFLLM_OK;
@@ -986,14 +1053,6 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     }
     const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
     const int64_t n_eb = (L + g.exc_block_size - 1) / g.exc_block_size;
-    if (more) {
-      HostTimer ht(&c->host_us[2]);
-      for (int d = 1; d <= infllm_ctx::kLookDepth; ++d) {
-        const int64_t tgt = eb + d;
-        infllm_ctx::LookAhead& la = c->la[tgt % (infllm_ctx::kLookDepth + 1)];
-        if (tgt < n_eb && !(la.launched && la.target == tgt)) INFLLM_TRY(lookahead_launch(c, tgt, s));
-      }
-    }
     HostTimer* ht_attn = new HostTimer(&c->host_us[3]);
     trace_mark(c, s, TR_ATTN_BEGIN, eb);
     const int64_t ovf = std::max<int64_t>(E - c->frontier - g.n_local, 0);  // :391
@@ -1185,10 +1244,24 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       }
       }
     }
+    // ev_attn: behind this exec block's attention; ev_attn_prev: behind the previous one's
+    std::swap(c->ev_attn, c->ev_attn_prev);
+    c->attn_prev_recorded = c->attn_recorded;
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
     c->attn_recorded = true;
     delete ht_attn;
     trace_mark(c, s, TR_ATTN_END, eb);
+    // the look-ahead of the next exec blocks goes out behind the attention launch: it runs on its own stream and
+    // the attention is what the main stream waits for
+    if (more) {
+      HostTimer ht(&c->host_us[2]);
+      for (int d = 1; d <= c->look_depth; ++d) {
+        const int64_t tgt = eb + d;
+        infllm_ctx::LookAhead& la = c->la[tgt % (c->look_depth + 1)];
+        if (tgt < n_eb && !(la.launched && la.target == tgt)) INFLLM_TRY(lookahead_launch(c, tgt, s));
+      }
+    }
+
     const SealPlan sp = plan_seal(c, E);
     // accumulated local score of every window key (context_manager.py:488, 623-625).  Sealing only needs
     // the scores of the tokens it is about to seal, so their 128-key tiles go first; the rest of the
@@ -1203,9 +1276,9 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     trace_mark(c, s, TR_URGENT_END, eb);
     if (more) {
       HostTimer ht(&c->host_us[4]);
-      for (int d = 1; d <= infllm_ctx::kLookDepth; ++d) {
+      for (int d = 1; d <= c->look_depth; ++d) {
         const int64_t tgt = eb + d;
-        infllm_ctx::LookAhead& la = c->la[tgt % (infllm_ctx::kLookDepth + 1)];
+        infllm_ctx::LookAhead& la = c->la[tgt % (c->look_depth + 1)];
         if (tgt < n_eb && la.launched && la.target == tgt && !la.staged) INFLLM_TRY(lookahead_stage(c, tgt));
       }
     }
@@ -1262,6 +1335,7 @@ extern "C" int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out) {
   c->unit_elems = (int64_t)g.n_kv_heads * g.block_size * g.head_dim;
   c->unit_bytes = 2 * c->unit_elems * c->esz;
   c->lru = LruTable(g.max_cached_block);
+  if (g.reserved[1] > 0) c->look_depth = std::min<int>(g.reserved[1], infllm_ctx::kMaxLookDepth);
   *out = c;
   return INFLLM_OK;
 }
@@ -1271,11 +1345,13 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   if (c->initialized) {
     INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->copy_stream));
+    INFLLM_CUDA_OK(cudaStreamSynchronize(c->urgent_stream));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->aux_stream));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->d2h_stream));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->mail_stream));
   }
   c->d2h_synced_upto = 0;
+  c->d2h_synced_upto_urgent = 0;
   c->d2h_recorded = false;
   c->pack_used[0] = c->pack_used[1] = false;
   c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
@@ -1287,13 +1363,14 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->table_valid = false;
   c->tab_updates.clear();
   c->free_slots.clear();
-  for (int i = c->cfg.max_cached_block + infllm_ctx::kLookDepth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
+  for (int i = c->cfg.max_cached_block + c->look_depth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->staged.clear();
   c->staged_for.clear();
   for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
   c->staged_pending = false;
   c->trace_topk.clear();
   c->attn_recorded = false;
+  c->attn_prev_recorded = false;
   c->spec_recorded = false;
   c->counters = infllm_ctx_info{};
   return INFLLM_OK;
@@ -1317,6 +1394,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     for (auto& l : c->la) {
       if (l.h_ids) cudaFreeHost(l.h_ids);
       if (l.ev) cudaEventDestroy(l.ev);
+      if (l.ev_staged) cudaEventDestroy(l.ev_staged);
     }
     if (c->h_cand_rows) cudaFreeHost(c->h_cand_rows);
     if (c->h_cand_scores) cudaFreeHost(c->h_cand_scores);
@@ -1341,12 +1419,16 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
       void* p = c->slab_future.get();
       if (p) cudaFreeHost(p);
     }
+    for (cudaEvent_t e : c->slot_ev)
+      if (e) cudaEventDestroy(e);
     for (void* p : c->slabs) cudaFreeHost(p);
     cudaStreamDestroy(c->copy_stream);
     cudaEventDestroy(c->ev_main);
     cudaEventDestroy(c->ev_copy);
     cudaEventDestroy(c->ev_sync);
     cudaEventDestroy(c->ev_attn);
+    cudaEventDestroy(c->ev_attn_prev);
+    cudaStreamDestroy(c->urgent_stream);
     for (cudaEvent_t e : c->ev_pool) cudaEventDestroy(e);
     cudaDeviceSynchronize();
   }

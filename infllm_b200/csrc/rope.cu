@@ -123,21 +123,27 @@ struct StageList {
   const uint4* src[kMaxStageUnits];
   uint4* dst[kMaxStageUnits];
 };
-__global__ void __launch_bounds__(512) stage_units_kernel(const __grid_constant__ StageList list, int n16) {
-  // one CTA per unit: few CTAs, so that they land on SMs the attention grid leaves idle, each thread with
-  // eight 16-byte loads in flight (16 units x 512 threads x 128 B = 1 MiB outstanding over the link)
-  const uint4* __restrict__ s = list.src[blockIdx.x];
-  uint4* __restrict__ d = list.dst[blockIdx.x];
-  const int stride = blockDim.x;
-  int i = threadIdx.x;
-  for (; i + 7 * stride < n16; i += 8 * stride) {
-    uint4 r[8];
+constexpr int kStageCtas = 8;  // few CTAs: they take few SMs away from a concurrent attention grid
+__global__ void __launch_bounds__(1024) stage_units_kernel(const __grid_constant__ StageList list, int n_units, int n16) {
+  // the CTAs walk over all 16-byte words of all units; every thread keeps four loads in flight
+  // (8 CTAs x 1024 threads x 64 B = 512 KiB outstanding over the link)
+  const int64_t total = (int64_t)n_units * n16;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    uint4 r[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) r[e] = s[i + e * stride];
+    for (int e = 0; e < 4; ++e) {
+      const int64_t w = i + e * stride;
+      r[e] = __ldcs(list.src[w / n16] + w % n16);
+    }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) d[i + e * stride] = r[e];
+    for (int e = 0; e < 4; ++e) {
+      const int64_t w = i + e * stride;
+      list.dst[w / n16][w % n16] = r[e];
+    }
   }
-  for (; i < n16; i += stride) d[i] = s[i];
+  for (; i < total; i += stride) list.dst[i / n16][i % n16] = list.src[i / n16][i % n16];
 }
 
 int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int64_t unit_bytes, cudaStream_t s) {
@@ -148,7 +154,7 @@ int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int6
       list.src[i] = (const uint4*)h_src[done + i];
       list.dst[i] = (uint4*)d_dst[done + i];
     }
-    stage_units_kernel<<<m, 512, 0, s>>>(list, (int)(unit_bytes / 16));
+    stage_units_kernel<<<kStageCtas, 1024, 0, s>>>(list, m, (int)(unit_bytes / 16));
     INFLLM_LAUNCH_OK("stage_units_kernel");
   }
   return INFLLM_OK;
