@@ -522,7 +522,7 @@ def run_decode_sharded(args, rank, world, local_rank):
                             DEC["repr_topk"], H, HKV, D, torch.bfloat16, dev)
         sh.load_synthetic(n, units, block_k.to(torch.bfloat16).cpu(), init_k, init_v, win_k, win_v)
         del units, block_k
-        mems.append(ShardedDecodeMemory([sh], distributed=True))
+        mems.append(ShardedDecodeMemory([sh], distributed=world > 1))
         dirs.append(direction)
     total = (args.warmup + 2 * args.steps + 2) * n_layers
     g = torch.Generator(device=dev).manual_seed(100)  # the same token stream on every rank
@@ -548,20 +548,23 @@ def run_decode_sharded(args, rank, world, local_rank):
             h_o.copy_(m.append(q, k, v), non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     def timed(fn, steps):
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
+        barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(steps):
             fn()
         b.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
+        barrier()
         ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
     with torch.inference_mode():
@@ -591,7 +594,8 @@ def run_decode_sharded(args, rank, world, local_rank):
     topk_bytes = float(hi - lo) * H * D * 2
     achieved = topk_bytes * topk_n / (topk_ms / 1e3) / 1e9 if topk_ms > 0 else None
     counts = torch.tensor([hits, misses], dtype=torch.float64, device=dev)
-    dist.all_reduce(counts)
+    if world > 1:
+        dist.all_reduce(counts)
     line = dict(
         metric="decode-attn us/token @1M ctx", value=1e3 * ms / per_layer, unit="us/token", n_gpus=world,
         steps=args.steps, warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=False, scaling="strong",
@@ -630,6 +634,8 @@ def main():
                          "1M-token decode, the second half; both (default): the prefill line with the decode line "
                          "under its key 'decode'")
     ap.add_argument("--decode-steps", type=int, default=128, help="decode tokens timed when --workload both")
+    ap.add_argument("--sharded", action="store_true",
+                    help="decode through the unit-range sharded implementation even on one GPU (it is what N > 1 runs)")
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
     ap.add_argument("--layers", type=int, default=DEC["layers"], help="layer memories that take turns in the decode workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
@@ -655,7 +661,7 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    decode = run_decode_sharded if world > 1 else run_decode
+    decode = run_decode_sharded if (world > 1 or args.sharded) else run_decode
     if args.workload == "decode":
         line = decode(args, rank, world, local_rank)
     else:

@@ -293,6 +293,25 @@ int infllm_ctx_load_synthetic(infllm_ctx* ctx, int64_t n_units, const void* h_un
                               const void* h_init_k, const void* h_init_v, const void* h_win_k,
                               const void* h_win_v, void* stream);
 
+/* ------------------------------------------------ KV-head-group sharding (no counterpart in the reference)
+ * Every rank runs a context on its own slice of the heads (n_heads / n_kv_heads of the config are the LOCAL
+ * counts); the one exchange is the sum over ranks of the retrieval scores, which the reference forms over all
+ * heads at once (context_manager.py:373-378).  After it every rank takes the same top-k and keeps the same LRU
+ * order.  The sums are NCCL all-reduces; NCCL is looked up at run time in the process (PyTorch has loaded it).
+ * infllm_comm_unique_id fills infllm_comm_id_bytes() bytes on one rank; the caller sends them to the others
+ * (any channel), every rank calls infllm_comm_create with them (a collective call), then infllm_ctx_set_comm on
+ * each fresh context.  One communicator serves any number of contexts of the process. */
+typedef struct infllm_comm infllm_comm;
+int infllm_comm_id_bytes(void);
+int infllm_comm_unique_id(void* h_out);
+int infllm_comm_create(const void* h_id, int rank, int world, infllm_comm** out);
+int infllm_comm_destroy(infllm_comm* comm);
+int infllm_ctx_set_comm(infllm_ctx* ctx, infllm_comm* comm);
+
+/* One memory unit from the pinned host store into a cache slot, asynchronously on `stream`: MemoryUnit.load's
+ * host-to-device copy (context_manager.py:57-71) for callers that keep their own cache. */
+int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes, void* stream);
+
 /* ----------------------------------------------------- host logic, GPU-free
  * The LRU table alone (context_manager.py:246-265, 495-515): dict-ordered ids with stamps.
  * Exposed so that the eviction order can be tested without a device. */

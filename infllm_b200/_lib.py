@@ -82,6 +82,12 @@ SIGNATURES = {
     "infllm_ingest_token": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
                                     c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "infllm_unit_fetch": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "infllm_comm_id_bytes": (c_int, []),
+    "infllm_comm_unique_id": (c_int, [c_void_p]),
+    "infllm_comm_create": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
+    "infllm_comm_destroy": (c_int, [c_void_p]),
+    "infllm_ctx_set_comm": (c_int, [c_void_p, c_void_p]),
     "infllm_ctx_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),
     "infllm_ctx_destroy": (c_int, [c_void_p]),
     "infllm_ctx_reset": (c_int, [c_void_p]),

@@ -2,6 +2,7 @@
 the misspelt ATTN_FORWRAD is the reference's public name)."""
 from .context_manager import ContextManager
 from .dot_production_attention import CudaMultiStageDotProductionAttention, get_multi_stage_dot_production_attention
+from .head_groups import HeadGroupComm
 from .inf_llm import inf_llm_forward
 from .rope import RotaryEmbeddingESM
 from .sharded_decode import ShardedDecodeMemory, UnitRangeShard, global_topk, unit_range
@@ -13,4 +14,4 @@ ATTN_FORWARD = ATTN_FORWRAD
 
 __all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward",
            "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention",
-           "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]
+           "HeadGroupComm", "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]

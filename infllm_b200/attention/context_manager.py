@@ -24,8 +24,9 @@ class ContextManager:
     def __init__(self, position_embedding, n_init, n_local, block_size, max_cached_block, topk, exc_block_size,
                  score_decay: Optional[float] = None, fattn: bool = False, repr_topk: int = 1,
                  cache_strategy="lru", chunk_topk_calc: Optional[int] = None, async_global_stream: bool = False,
-                 pin_memory: bool = False, faiss: bool = False, perhead: bool = False):
+                 pin_memory: bool = False, faiss: bool = False, perhead: bool = False, head_group_comm=None):
         self.length = 0
+        self.head_group_comm = head_group_comm  # HeadGroupComm: the heads given to append() are this rank's slice
         self.position_embedding = position_embedding
         self.n_init = n_init
         self.n_local = n_local
@@ -86,6 +87,8 @@ class ContextManager:
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))
+            if self.head_group_comm is not None:
+                _lib.check(_lib.lib.infllm_ctx_set_comm(h, self.head_group_comm.handle))
             self._ctx.append(h)
             if getattr(self, "_profile", False):
                 _lib.check(_lib.lib.infllm_ctx_profile(h, 1))

@@ -95,6 +95,12 @@ class UnitRangeShard:
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
         self.block_k = self.host_units = self.init_k = self.init_v = None
         self._share = (0, 0)
+        # raw addresses of the buffers the per-token calls pass on (tensor indexing costs microseconds a piece)
+        self._p = {name: getattr(self, name).data_ptr() for name in
+                   ("k_raw", "k_rot", "v", "score", "q_loc", "q_glb", "qbar", "cos", "sin", "cache", "part_o", "part_lse",
+                    "logits", "pack", "lse", "cand")}
+        self.unit_bytes = 2 * n_kv_heads * block_size * head_dim * self.k_raw.element_size()
+        self._stream = None
         m = topk + 3  # retrieved units + window share + sink + overflow
         self._seg_arrays = ((ctypes.c_void_p * m)(), (ctypes.c_void_p * m)(), (ctypes.c_int64 * m)(),
                             (ctypes.c_int32 * m)(), (ctypes.c_int32 * m)())
@@ -119,6 +125,7 @@ class UnitRangeShard:
         self.block_k[:n_owned].copy_(block_k)
         self.scores_buf = torch.empty((max(room, 1),), dtype=torch.float32, device=self.device)
         self.init_k, self.init_v = init_k.to(self.device).contiguous(), init_v.to(self.device).contiguous()
+        self._store_pointers()
         self.n_total, self.lo, self.n_owned = n_total, lo, n_owned
         self.frontier = self.n_init + n_total * self.bs
         self.length = self.frontier + self.n_local
@@ -128,6 +135,10 @@ class UnitRangeShard:
         self.v[:, :n].copy_(win_v)
         self.score.zero_()
         self._rotate(0, n)
+
+    def _store_pointers(self):
+        self._p.update(block_k=self.block_k.data_ptr(), host_units=self.host_units.data_ptr(),
+                       scores_buf=self.scores_buf.data_ptr(), init_k=self.init_k.data_ptr(), init_v=self.init_v.data_ptr())
 
     def _rope(self, x, x_hs, x_ts, out, o_hs, o_ts, heads, length, pos0, step):
         _lib.check(_lib.lib.infllm_rope_apply(x, x_hs, x_ts, out, o_hs, o_ts, heads, length, self.D, self.cos.data_ptr(),
@@ -154,27 +165,23 @@ class UnitRangeShard:
         tensor (2, topk): the scores' bit patterns and the global unit ids, padded with (-inf, -1)."""
         if self.length - self.t0 >= self.cap:
             self._compact()
-        T, at, D = self.length, self.length - self.t0, self.D
-        esz, row = self.k_raw.element_size(), at * D * self.k_raw.element_size()
+        T, at, D, p = self.length, self.length - self.t0, self.D, self._p
+        row = at * D * 2
+        self._stream = stream = _lib.stream_ptr()
         # copies, the three rotations (keys and queries window-relative, queries at the one global angle), the
         # query "mean" of the one-token exec block (context_manager.py:373-375) and the new score column
         _lib.check(_lib.lib.infllm_ingest_token(
-            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), self.q_loc.data_ptr(),
-            self.q_glb.data_ptr(), D, self.qbar.data_ptr(), self.k_raw.data_ptr() + row, self.k_rot.data_ptr() + row,
-            self.v.data_ptr() + row, self.cap * D, self.score.data_ptr() + at * 4, self.cap, self.H, self.HKV, D,
-            self.cos.data_ptr(), self.sin.data_ptr(), self.cap, T - self.t0, self.n_local - 1, self.code,
-            _lib.stream_ptr()))
-        del esz
-        cand_scores = self.cand[0].view(torch.float32)
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), p["q_loc"], p["q_glb"], D,
+            p["qbar"], p["k_raw"] + row, p["k_rot"] + row, p["v"] + row, self.cap * D, p["score"] + at * 4, self.cap,
+            self.H, self.HKV, D, p["cos"], p["sin"], self.cap, T - self.t0, self.n_local - 1, self.code, stream))
         if self.n_owned < self.topk:  # fewer units than a retrieval takes: pad the candidates
-            cand_scores.fill_(float("-inf"))
+            self.cand[0].view(torch.float32).fill_(float("-inf"))
             self.cand[1].fill_(-1)
         if self.n_owned > 0:
             kk = min(self.topk, self.n_owned)
             ev = self._mark("topk")
-            _lib.check(_lib.lib.infllm_block_topk(self.block_k.data_ptr(), self.n_owned, self.H * D, self.qbar.data_ptr(),
-                                                  self.scores_buf.data_ptr(), kk, self.lo, self.cand[1].data_ptr(),
-                                                  cand_scores.data_ptr(), self.code, _lib.stream_ptr()))
+            _lib.check(_lib.lib.infllm_block_topk(p["block_k"], self.n_owned, self.H * D, p["qbar"], p["scores_buf"], kk,
+                                                  self.lo, p["cand"] + 4 * self.topk, p["cand"], self.code, stream))
             self._mark("topk", ev)
         return self.cand
 
@@ -202,10 +209,10 @@ class UnitRangeShard:
         owned = [b for b in ids if self.lo <= b < self.lo + self.n_owned]
         self._refill(owned)
         segs = []  # (k pointer, v pointer, head stride, length, query variant)
-        esz, D = self.k_raw.element_size(), self.D
+        esz, D, p = 2, self.D, self._p
         for b in owned:
-            slot = self.cache[self.slot_of[b]]
-            segs.append((slot[0].data_ptr(), slot[1].data_ptr(), self.bs * D, self.bs, 1))
+            base = p["cache"] + self.slot_of[b] * self.unit_bytes
+            segs.append((base, base + self.unit_bytes // 2, self.bs * D, self.bs, 1))
         wlo = max(E - self.n_local, 0)
         W = E - wlo
         a, b_ = wlo + (W * r) // G, wlo + (W * (r + 1)) // G
@@ -214,17 +221,15 @@ class UnitRangeShard:
         if b_ > a:
             off = (a - self.t0) * D * esz
             logit_seg = len(segs)
-            segs.append((self.k_rot.data_ptr() + off, self.v.data_ptr() + off, self.cap * D, b_ - a, 0))
+            segs.append((p["k_rot"] + off, p["v"] + off, self.cap * D, b_ - a, 0))
         if r == 0 and self.n_init > 0:
-            segs.append((self.init_k.data_ptr(), self.init_v.data_ptr(), self.n_init * D, self.n_init, 1))
+            segs.append((p["init_k"], p["init_v"], self.n_init * D, self.n_init, 1))
         if r == G - 1 and wlo > self.frontier:  # tokens between the last sealed unit and the window
             off = (self.frontier - self.t0) * D * esz
-            segs.append((self.k_raw.data_ptr() + off, self.v.data_ptr() + off, self.cap * D, wlo - self.frontier, 1))
-        o = self.pack[:self.H * D].view(self.H, D)
-        lse = self.pack[self.H * D:]
+            segs.append((p["k_raw"] + off, p["v"] + off, self.cap * D, wlo - self.frontier, 1))
         if not segs:
-            o.zero_()
-            lse.fill_(float("-inf"))
+            self.pack[:self.H * D].zero_()
+            self.pack[self.H * D:].fill_(float("-inf"))
             return self.pack
         n = len(segs)
         kp, vp, hs, ln, qs = self._seg_arrays
@@ -233,12 +238,11 @@ class UnitRangeShard:
         n_parts = ctypes.c_int()
         self.keys_last = sum(s[3] for s in segs)
         ev = self._mark("decode")
-        _lib.check(_lib.lib.infllm_attn_decode(self.q_loc.data_ptr(), self.q_glb.data_ptr(), self.H, self.HKV, D, n, kp,
-                                               vp, hs, ln, qs, self.part_o.data_ptr(), self.part_lse.data_ptr(),
-                                               self.max_parts, ctypes.byref(n_parts), logit_seg,
-                                               self.logits.data_ptr(), self.code, _lib.stream_ptr()))
-        _lib.check(_lib.lib.infllm_lse_merge(self.part_o.data_ptr(), self.part_lse.data_ptr(), n_parts.value, self.H, D,
-                                             o.data_ptr(), D, lse.data_ptr(), F32, _lib.stream_ptr()))
+        _lib.check(_lib.lib.infllm_attn_decode(p["q_loc"], p["q_glb"], self.H, self.HKV, D, n, kp, vp, hs, ln, qs,
+                                               p["part_o"], p["part_lse"], self.max_parts, ctypes.byref(n_parts),
+                                               logit_seg, p["logits"], self.code, self._stream))
+        _lib.check(_lib.lib.infllm_lse_merge(p["part_o"], p["part_lse"], n_parts.value, self.H, D, p["pack"], D,
+                                             p["pack"] + self.H * D * 4, F32, self._stream))
         self._mark("decode", ev)
         return self.pack
 
@@ -263,21 +267,22 @@ class UnitRangeShard:
             self.misses += 1
             slot = self.free_slots.pop()
             self.slot_of[b] = slot
-            self.cache[slot].copy_(self.host_units[b - self.lo], non_blocking=True)
+            _lib.check(_lib.lib.infllm_unit_fetch(self._p["cache"] + slot * self.unit_bytes,
+                                                  self._p["host_units"] + (b - self.lo) * self.unit_bytes,
+                                                  self.unit_bytes, self._stream))
 
     # ------------------------------------------------------------------ step 5
     def merge(self, parts):
         """Step 4 and the first half of step 5 on this rank: log-sum-exp merge of the gathered partials
         (G, H*(D+1)) fp32 rows [o | lse] into the token's output (H, D), and this rank's share of the token's local
         attention row added to the accumulated scores, in one launch."""
-        H, D = self.H, self.D
+        H, D, p = self.H, self.D, self._p
         out = torch.empty((H, D), dtype=self.dtype, device=self.device)
         a, b = self._share
-        off = (a - self.t0) * 4
+        base, stride = parts.data_ptr(), parts.stride(0)
         _lib.check(_lib.lib.infllm_lse_merge_ex(
-            parts.data_ptr(), parts.stride(0), parts.data_ptr() + H * D * 4, parts.stride(0), parts.shape[0], H, D,
-            out.data_ptr(), D, self.lse.data_ptr(), self.code, self.logits.data_ptr() if b > a else None, b - a,
-            self.score.data_ptr() + off, self.cap, _lib.stream_ptr()))
+            base, stride, base + H * D * 4, stride, parts.shape[0], H, D, out.data_ptr(), D, p["lse"], self.code,
+            p["logits"] if b > a else None, b - a, p["score"] + (a - self.t0) * 4, self.cap, self._stream))
         return out
 
     def finish(self):
@@ -317,6 +322,7 @@ class UnitRangeShard:
         bk[:self.n_owned].copy_(self.block_k[:self.n_owned])
         self.block_k = bk
         self.scores_buf = torch.empty((room,), dtype=torch.float32, device=self.device)
+        self._store_pointers()
 
 
 class ShardedDecodeMemory:

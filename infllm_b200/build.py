@@ -11,7 +11,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libinfllm_b200.so")
-SOURCES = ["error.cu", "rope.cu", "retrieval.cu", "attn_general.cu", "attn_decode.cu", "attn_tc.cu", "context.cu"]
+SOURCES = ["error.cu", "rope.cu", "retrieval.cu", "attn_general.cu", "attn_decode.cu", "attn_tc.cu", "context.cu",
+           "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -50,7 +51,7 @@ def build(force=False, verbose=False):
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
         objs.append(obj)
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart", "-ldl"]
     subprocess.check_call(cmd)
     return LIB
 

@@ -21,6 +21,8 @@
 #include "attn_common.cuh"
 #include "attn_tc.cuh"
 
+struct infllm_comm;  // comm.cu
+
 namespace infllm {
 
 // kernels of the other translation units
@@ -46,6 +48,11 @@ int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs
                         int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
                         const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
                         int dtype, cudaStream_t s, int32_t* clear);
+int block_score_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int dtype,
+                       cudaStream_t s);
+int topk_launch(const float* scores, int64_t n, int k, int id_base, int32_t* out_ids, float* out_scores,
+                cudaStream_t s);
+int comm_allreduce_sum(infllm_comm* c, int which, float* d_buf, size_t n, cudaStream_t s);
 int slot_table_update_launch(int32_t* table, const int32_t* ids, const int32_t* slots, int n, cudaStream_t s);
 
 // ------------------------------------------------------------------------------------- LRU table
@@ -159,6 +166,7 @@ struct infllm_ctx {
   float* scores = nullptr;   // (scores_cap) unit scores
   int64_t scores_cap = 0;
   int32_t* d_topk = nullptr; // (topk)
+  infllm_comm* comm = nullptr;  // KV-head-group sharding: the retrieval scores are summed over the ranks
   unsigned int* tickets = nullptr;  // "last CTA" counters of the fused scoring kernel: [0] main stream, [1] look-ahead stream
   int32_t* h_topk = nullptr; // pinned
   float *part_o = nullptr, *part_lse = nullptr, *dec_logits = nullptr;
@@ -532,6 +540,19 @@ int ensure_scores(infllm_ctx* c, int64_t n, cudaStream_t s) {
   return INFLLM_OK;
 }
 
+// scoring and top-k of n units on stream s.  Alone, one fused launch; with a communicator (KV-head-group sharding:
+// this context holds a slice of the heads) the scores are summed over the ranks between the two halves, so that
+// every rank ranks the same numbers.  `which` picks the communicator of the stream (0 main, 1 look-ahead).
+int score_topk(infllm_ctx* c, int64_t n, const float* qbar, float* scores, int32_t* d_ids, cudaStream_t s, int which) {
+  const infllm_config& g = c->cfg;
+  if (!c->comm)
+    return block_topk_launch(c->block_k, n, (int)c->width, qbar, scores, g.topk, 0, d_ids, nullptr, g.dtype, s,
+                             c->tickets + which);
+  INFLLM_TRY(block_score_launch(c->block_k, n, (int)c->width, qbar, scores, g.dtype, s));
+  INFLLM_TRY(comm_allreduce_sum(c->comm, which, scores, (size_t)n, s));
+  return topk_launch(scores, n, g.topk, 0, d_ids, nullptr, s);
+}
+
 // ids of one exec block straight from the device scorer: scoring + top-k, then a host sync on the result
 int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaStream_t s) {
   const infllm_config& g = c->cfg;
@@ -544,8 +565,7 @@ int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaS
   INFLLM_TRY(ensure_scores(c, n, s));
   {
     ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)n * c->width * c->esz);
-    INFLLM_TRY(block_topk_launch(c->block_k, n, (int)c->width, c->qbar + (int64_t)eb_in_call * c->width, c->scores,
-                                 g.topk, 0, c->d_topk, nullptr, g.dtype, s, c->tickets));
+    INFLLM_TRY(score_topk(c, n, c->qbar + (int64_t)eb_in_call * c->width, c->scores, c->d_topk, s, 0));
   }
   INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, s));
@@ -578,8 +598,7 @@ int lookahead_launch(infllm_ctx* c, int64_t target, cudaStream_t s) {
   trace_mark(c, c->aux_stream, TR_SPEC_BEGIN, target);
   ProfScope ps(c, c->aux_stream, INFLLM_PROF_TOPK, (double)la.n_spec * c->width * c->esz);
   int32_t* d_ids = c->d_spec + (target % (c->look_depth + 1)) * std::max(1, g.topk);
-  INFLLM_TRY(block_topk_launch(c->block_k, la.n_spec, (int)c->width, c->qbar + target * c->width, c->scores_aux,
-                               g.topk, 0, d_ids, nullptr, g.dtype, c->aux_stream, c->tickets + 1));
+  INFLLM_TRY(score_topk(c, la.n_spec, c->qbar + target * c->width, c->scores_aux, d_ids, c->aux_stream, 1));
   INFLLM_CUDA_OK(cudaMemcpyAsync(la.h_ids, d_ids, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->aux_stream));
   trace_mark(c, c->aux_stream, TR_SPEC_END, target);
   INFLLM_CUDA_OK(cudaEventRecord(la.ev, c->aux_stream));
@@ -673,6 +692,7 @@ int candidates_launch(infllm_ctx* c, int64_t eb_next, int* n_cand, cudaStream_t 
     return fail(INFLLM_E_CAPACITY, "look-ahead: %lld candidates exceed %d", (long long)(spec_ids.size() + n_now - n_spec), c->cand_cap);
   INFLLM_TRY(block_score_rows_launch(c->block_k, c->h_cand_rows, n, (int)c->width,
                                      c->qbar + eb_next * c->width, c->d_cand_scores, g.dtype, s));
+  if (c->comm) INFLLM_TRY(comm_allreduce_sum(c->comm, 0, c->d_cand_scores, (size_t)n, s));
   // the scores travel to the host on their own stream so that the main stream goes straight on
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
   INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
@@ -1041,8 +1061,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       INFLLM_TRY(ensure_scores(c, c->num_blocks, s));
       {
         ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
-        INFLLM_TRY(block_topk_launch(c->block_k, c->num_blocks, (int)c->width, c->qbar, c->scores, g.topk, 0, c->d_topk,
-                                     nullptr, g.dtype, s, c->tickets));
+        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, c->d_topk, s, 0));
       }
       INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
       INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
@@ -1672,5 +1691,18 @@ extern "C" int infllm_lru_items(infllm_lru* t, int32_t* h_ids, double* h_stamps,
     ++i;
   }
   *n = i;
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes, void* stream) {
+  if (!d_slot || !h_unit || bytes <= 0) return fail(INFLLM_E_BADARG, "unit_fetch: bad argument");
+  INFLLM_CUDA_OK(cudaMemcpyAsync(d_slot, h_unit, (size_t)bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_set_comm(infllm_ctx* c, infllm_comm* comm) {
+  if (!c) return fail(INFLLM_E_BADARG, "ctx_set_comm: null context");
+  if (c->length != 0) return fail(INFLLM_E_BADARG, "ctx_set_comm: the context already holds tokens");
+  c->comm = comm;
   return INFLLM_OK;
 }

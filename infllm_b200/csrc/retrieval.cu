@@ -493,6 +493,35 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
   return INFLLM_OK;
 }
 
+// the two halves of block_topk_launch on their own, for callers that put an exchange between them (the sum of the
+// scores over the ranks of a KV-head-group sharding)
+int block_score_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int dtype,
+                       cudaStream_t s) {
+  if (n <= 0) return INFLLM_OK;
+  if (width % 8 != 0 || width > 12 * 1024 || ((uintptr_t)bk % 16) != 0)
+    return fail(INFLLM_E_BADARG, "block_score: width %d must be a multiple of 8, at most 12288, rows 16-byte aligned", width);
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    block_score_kernel<T><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
+        (const T*)bk, n, width, qbar, scores);
+  });
+  INFLLM_LAUNCH_OK("block_score_kernel");
+  return INFLLM_OK;
+}
+
+int topk_launch(const float* scores, int64_t n, int k, int id_base, int32_t* out_ids, float* out_scores,
+                cudaStream_t s) {
+  if (n <= 0 || k <= 0 || k > n) return fail(INFLLM_E_BADARG, "topk: need 0 < k <= n (k=%d n=%lld)", k, (long long)n);
+  if (k > 1024) return fail(INFLLM_E_UNSUPPORTED, "topk: k=%d > 1024", k);
+  if (k <= kFastMaxK && n <= kFastMaxN) {
+    topk_fast_kernel<<<1, kTopkThreads, 0, s>>>(scores, (int)n, k, id_base, out_ids, out_scores);
+    INFLLM_LAUNCH_OK("topk_fast_kernel");
+  } else {
+    topk_select_kernel<<<1, kTopkThreads, k * 8, s>>>(scores, n, k, id_base, out_ids, out_scores);
+    INFLLM_LAUNCH_OK("topk_select_kernel");
+  }
+  return INFLLM_OK;
+}
+
 int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
                             int dtype, cudaStream_t s) {
   for (int done = 0; done < n; done += kMaxScoreRows) {  // `rows` is a host array
@@ -530,6 +559,19 @@ int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* s
 #ifdef INFLLM_TOPK_TIMING
 extern "C" int infllm_topk_stamps(long long* out) {
   return cudaMemcpyFromSymbol(out, infllm::g_topk_stamps, sizeof(long long) * 16) == cudaSuccess ? 0 : -1;
+}
+extern "C" int infllm_score_only(const void* bk, int64_t n, int width, const float* qbar, float* scores, int variant,
+                                 void* stream) {
+  using namespace infllm;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (variant == 0) {
+    block_score_kernel<__nv_bfloat16><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
+        (const __nv_bfloat16*)bk, n, width, qbar, scores);
+  } else {
+    block_score_topk_kernel<__nv_bfloat16><<<148, kTopkThreads, width * sizeof(float), s>>>(
+        (const __nv_bfloat16*)bk, (int)n, width, qbar, scores, 32, 0, nullptr, nullptr, nullptr);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 extern "C" int infllm_block_topk_ticket(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k,
                                         int32_t* ids, unsigned int* ticket, int dtype, void* stream) {
