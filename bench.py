@@ -83,18 +83,37 @@ def make_hidden(tokens, seed, weights, device):
 
 
 class Layer:
-    """The attention layer as a caller of the attention-forward API sees it."""
+    """The attention layer as a caller of the attention-forward API sees it.  With world > 1 this rank holds the
+    projections of its slice of the heads (rows of wq/wk/wv, columns of wo) and sums the output projection's
+    partial results over the ranks: tensor-parallel attention by KV-head groups."""
 
-    def __init__(self, device, forward, rope, dtype=torch.bfloat16):
+    def __init__(self, device, forward, rope, dtype=torch.bfloat16, rank=0, world=1):
         self.wq, self.wk, self.wv, self.wo = make_weights(device, dtype)
+        self.heads, self.kv_heads = CFG["H"] // world, CFG["HKV"] // world
+        if world > 1:
+            import torch.distributed as dist
+
+            nq, nk = self.heads * CFG["D"], self.kv_heads * CFG["D"]
+            self.wq = self.wq[rank * nq:(rank + 1) * nq].contiguous()
+            self.wk = self.wk[rank * nk:(rank + 1) * nk].contiguous()
+            self.wv = self.wv[rank * nk:(rank + 1) * nk].contiguous()
+            self.wo = self.wo[:, rank * nq:(rank + 1) * nq].contiguous()
         self.forward, self.rope, self.pkv = forward, rope, None
         lin = torch.nn.functional.linear
         self.pq, self.pk = (lambda x: lin(x, self.wq)), (lambda x: lin(x, self.wk))
-        self.pv, self.po = (lambda x: lin(x, self.wv)), (lambda x: lin(x, self.wo))
+        self.pv = lambda x: lin(x, self.wv)
+        if world > 1:
+            def out_proj(x):
+                o = lin(x, self.wo)
+                dist.all_reduce(o)
+                return o
+            self.po = out_proj
+        else:
+            self.po = lambda x: lin(x, self.wo)
 
     def __call__(self, x):
         o, self.pkv = self.forward(None, x, x, self.rope, True, self.pkv, self.pq, self.pk, self.pv, self.po,
-                                   CFG["D"], CFG["H"], CFG["HKV"])
+                                   CFG["D"], self.heads, self.kv_heads)
         return o
 
     def reset(self):
@@ -244,11 +263,21 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     tokens = args.tokens
+    groups = world if (args.head_groups and world > 1) else 1  # one layer over all GPUs instead of a replica per GPU
+    comm = None
+    if groups > 1:
+        from infllm_b200.attention import HeadGroupComm
+
+        if CFG["HKV"] % groups:
+            raise SystemExit(f"--head-groups: {CFG['HKV']} KV heads do not split over {groups} GPUs")
+        comm = HeadGroupComm()
     fwd = ATTN_FORWRAD["inf-llm"](n_local=CFG["n_local"], n_init=CFG["n_init"], topk=CFG["topk"], block_size=CFG["bs"],
                                   max_cached_block=CFG["max_cached"], exc_block_size=CFG["exc"], fattn=True,
-                                  repr_topk=CFG["repr_topk"])
-    layer = Layer(dev, fwd, RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0))
-    hidden = make_hidden(tokens, seed=rank, weights=(layer.wq, layer.wk, layer.wv, layer.wo), device=dev)
+                                  repr_topk=CFG["repr_topk"], head_group_comm=comm)
+    full = make_weights(dev, torch.bfloat16)  # the planted directions are built from the whole projections
+    layer = Layer(dev, fwd, RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0), rank=rank if groups > 1 else 0, world=groups)
+    hidden = make_hidden(tokens, seed=0 if groups > 1 else rank, weights=full, device=dev)
+    del full
     h_hidden = torch.empty(hidden.shape, dtype=hidden.dtype, pin_memory=True)
     h_hidden.copy_(hidden)
     h_out = torch.empty((1, tokens, CFG["hidden"]), dtype=hidden.dtype, pin_memory=True)
@@ -292,19 +321,21 @@ def run_ours(args, rank, world, local_rank):
             prefill_host(layer, h_hidden, h_out, d_in)
         ms_e2e = timed(lambda: (prefill_host(layer, h_hidden, h_out, d_in), h_out[0, -1, 0].item()), args.steps)
 
-    value = world * tokens * args.steps / (ms / 1e3)
-    e2e = world * tokens * args.steps / (ms_e2e / 1e3)
+    value = (world // groups) * tokens * args.steps / (ms / 1e3)
+    e2e = (world // groups) * tokens * args.steps / (ms_e2e / 1e3)
     tf_peak, _, which = measured_peaks()
     attn_ms, attn_flops, attn_n = prof["attn"]
     achieved = attn_flops / (attn_ms / 1e3) / 1e12 if attn_ms > 0 else None
     line = dict(
         metric="exec-block prefill tokens/s/GPU @128K ctx", value=value, unit="tokens/s", n_gpus=world,
-        steps=args.steps, warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak",
-        vs_baseline=None, dtype="bf16", data="synthetic",
+        steps=args.steps, warmup=args.warmup, ms_per_step=ms / args.steps, higher_is_better=True,
+        scaling="strong" if groups > 1 else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
         config=dict(workload=f"mistral-7b attention layer (hidden 4096, 32q/8kv, d128, rope 1e6), {tokens}-token prefill "
                              "in 8192-token calls, exec 512, n_init 128, n_local 4096, unit 128, topk 16, repr_topk 4, "
                              f"max_cached {CFG['max_cached']}, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
-                    replicas=world),
+                    replicas=world // groups,
+                    parallelism=(f"kv-head groups x{groups}: one layer over all GPUs, retrieval scores and output "
+                                 "projection all-reduced (NCCL)") if groups > 1 else f"dp{world}: one layer replica per GPU"),
         e2e=dict(value=e2e, unit="tokens/s", h2d_bytes_per_step=int(hidden.numel() * 2),
                  d2h_bytes_per_step=int(h_out.numel() * 2), ms_per_step=ms_e2e / args.steps),
         gpu_launches=int(launches),
@@ -634,6 +665,8 @@ def main():
                          "1M-token decode, the second half; both (default): the prefill line with the decode line "
                          "under its key 'decode'")
     ap.add_argument("--decode-steps", type=int, default=128, help="decode tokens timed when --workload both")
+    ap.add_argument("--head-groups", action="store_true",
+                    help="prefill with N > 1: one layer sharded by KV-head groups over the GPUs instead of N replicas")
     ap.add_argument("--sharded", action="store_true",
                     help="decode through the unit-range sharded implementation even on one GPU (it is what N > 1 runs)")
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
@@ -675,6 +708,14 @@ def main():
             dargs = copy.copy(args)
             dargs.steps, dargs.warmup = args.decode_steps, 16
             line["decode"] = decode(dargs, rank, world, local_rank)
+            if world > 1 and not args.head_groups and CFG["HKV"] % world == 0:
+                # the same prompt through ONE layer sharded by KV-head groups over the GPUs (strong scaling)
+                gc.collect()
+                torch.cuda.empty_cache()
+                hargs = copy.copy(args)
+                hargs.head_groups, hargs.no_cpu, hargs.steps = True, True, min(args.steps, 2)
+                hg = run_ours(hargs, rank, world, local_rank)
+                line["head_groups"] = {k: hg[k] for k in ("value", "unit", "ms_per_step", "scaling", "e2e", "roofline", "config")}
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -1195,7 +1195,11 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         TP.stage[1].map_q = 1; TP.stage[1].q_row0 = (int)st; TP.stage[1].mask_mode = INFLLM_MASK_NONE;
         TP.stage[1].lk = (int64_t)all_glk; TP.stage[1].seg_begin = 1; TP.stage[1].seg_end = ns;
         ProfScope ps(c, s, INFLLM_PROF_ATTN, 4.0 * D * H * (local_pairs + (double)lq * all_glk));
-        if ((H / HKV) % 2 == 0 && (g.reserved[0] & 8)) {  // flag bit 3: the two-heads-per-CTA kernel (see attn_tc.cu)
+        // The one-head kernel runs one CTA per (128-query tile, head): with few heads on this GPU (a KV-head-group
+        // shard) its grid leaves most SMs idle, and the two-head kernel, which also cuts the key tiles into runs,
+        // fills them.  Flag bit 3 forces the two-head kernel.
+        const bool few_ctas = lq >= 256 && ((lq + 127) / 128) * H <= 74;
+        if ((H / HKV) % 2 == 0 && ((g.reserved[0] & 8) || few_ctas)) {
           // two heads of a KV head per CTA; cut the key tiles into runs until the grid covers the SMs
           const int items = (int)((lq + 127) / 128) * (int)(H / 2);
           TP.n_split = std::max(1, std::min(8, 148 / items));
