@@ -519,7 +519,7 @@ def run_decode_sharded(args, rank, world, local_rank):
     import torch.distributed as dist
 
     from infllm_b200 import _lib
-    from infllm_b200.attention import RotaryEmbeddingESM, ShardedDecodeMemory, UnitRangeShard, unit_range
+    from infllm_b200.attention import PeerMailbox, RotaryEmbeddingESM, ShardedDecodeMemory, UnitRangeShard, unit_range
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -529,6 +529,9 @@ def run_decode_sharded(args, rank, world, local_rank):
     n_layers = DEC["layers"] * world
     lo, hi = unit_range(n, rank, world)
     mems, dirs = [], []
+    # one mailbox for all layers: both exchanges of a token run inside kernels over peer memory (--nccl-exchange
+    # keeps them as NCCL all-gathers with a host round trip between them)
+    mailbox = PeerMailbox(DEC["topk"], H, D, device=dev) if (world > 1 and not args.nccl_exchange) else None
     for li in range(n_layers):
         gs = torch.Generator(device=dev).manual_seed(7000 + li)  # the same on every rank
         direction = torch.randn((H, 1, D), generator=gs, device=dev)
@@ -553,7 +556,7 @@ def run_decode_sharded(args, rank, world, local_rank):
                             DEC["repr_topk"], H, HKV, D, torch.bfloat16, dev)
         sh.load_synthetic(n, units, block_k.to(torch.bfloat16).cpu(), init_k, init_v, win_k, win_v)
         del units, block_k
-        mems.append(ShardedDecodeMemory([sh], distributed=world > 1))
+        mems.append(ShardedDecodeMemory([sh], distributed=world > 1, mailbox=mailbox))
         dirs.append(direction)
     total = (args.warmup + 2 * args.steps + 2) * n_layers
     g = torch.Generator(device=dev).manual_seed(100)  # the same token stream on every rank
@@ -636,8 +639,11 @@ def run_decode_sharded(args, rank, world, local_rank):
                              "topk 32, repr_topk 4, max_cached 32 per GPU, n_local 4096, n_init 128; 1% planted units "
                              f"with graded lean; a step is one token through {n_layers} layers, value is per layer",
                     l2=f"{n_layers} layers take turns so that each rank's working set exceeds the 126 MB L2",
-                    parallelism=f"unit-range x{world}: all-gather of (score, id) candidates and of (o, lse) partials "
-                                "per token, all-reduce of 128 score columns per sealed unit (NCCL)"),
+                    parallelism=(f"unit-range x{world}: (score, id) candidates and (o, lse) partials exchanged per token "
+                                 + ("by kernels that write the peers' mailboxes (CUDA IPC), retrieval ranked on the "
+                                    "device" if mailbox is not None else "by NCCL all-gathers")
+                                 + "; all-reduce of 128 score columns per sealed unit (NCCL)"),
+                    tokens_redone=sum(m.redone for m in mems)),
         e2e=dict(value=1e3 * ms_e2e / per_layer, unit="us/token", h2d_bytes_per_step=int((H + 2 * HKV) * D * 2 * n_layers),
                  d2h_bytes_per_step=int(H * D * 2 * n_layers)),
         gpu_launches=int(launches),
@@ -667,6 +673,8 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=128, help="decode tokens timed when --workload both")
     ap.add_argument("--head-groups", action="store_true",
                     help="prefill with N > 1: one layer sharded by KV-head groups over the GPUs instead of N replicas")
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="sharded decode: exchange candidates and partials with NCCL all-gathers instead of peer-memory kernels")
     ap.add_argument("--sharded", action="store_true",
                     help="decode through the unit-range sharded implementation even on one GPU (it is what N > 1 runs)")
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")

@@ -167,7 +167,24 @@ int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, int n_part,
 int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride, const float* d_part_lse,
                         int64_t part_lse_stride, int n_part, int n_heads, int head_dim, void* d_out, int64_t o_hs,
                         float* d_lse, int dtype, const float* d_logits, int64_t logit_len, float* d_score,
-                        int64_t score_hs, void* stream);
+                        int64_t score_hs, const int32_t* d_skip, void* stream);
+/* (d_skip, may be NULL: a device word; when it is non-zero at run time the call does nothing — the partials
+ * were declared invalid by whoever produced them.) */
+
+/* infllm_attn_decode whose segments [first_unit_seg, first_unit_seg + n_units) are memory units named on the
+ * DEVICE: unit i is d_unit_ids[i]; this GPU owns the ids [id_lo, id_lo + n_owned) and finds them in cache slot
+ * d_slot_table[id - id_lo] (K then V, unit_bytes, at d_cache + slot * unit_bytes; -1: not cached).  Units of other
+ * owners and ids < 0 get weight zero; an owned unit that is not cached gets weight zero and sets *d_miss = 1.
+ * h_seg_k / h_seg_v of those segments are ignored.  Lets the attention follow a device-side retrieval without a
+ * host round trip.  infllm_slot_table_update writes d_table[h_ids[i]] = h_slots[i] (ids must not repeat). */
+int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim, int n_seg,
+                             const void* const* h_seg_k, const void* const* h_seg_v, const int64_t* h_seg_hs,
+                             const int32_t* h_seg_len, const int32_t* h_seg_q, int first_unit_seg, int n_units,
+                             const int32_t* d_unit_ids, const int32_t* d_slot_table, int id_lo, int n_owned,
+                             const void* d_cache, int64_t unit_bytes, int32_t* d_miss, float* d_part_o,
+                             float* d_part_lse, int max_parts, int* n_parts, int logit_seg, float* d_logits,
+                             int dtype, void* stream);
+int infllm_slot_table_update(int32_t* d_table, const int32_t* h_ids, const int32_t* h_slots, int n, void* stream);
 
 /* infllm_attn_decode_noalloc has no counterpart in the reference.  It is infllm_attn_decode followed by
  * infllm_lse_merge in one call that allocates nothing: the split-K partials go to a scratch array that is
@@ -307,6 +324,33 @@ int infllm_comm_unique_id(void* h_out);
 int infllm_comm_create(const void* h_id, int rank, int world, infllm_comm** out);
 int infllm_comm_destroy(infllm_comm* comm);
 int infllm_ctx_set_comm(infllm_ctx* ctx, infllm_comm* comm);
+
+/* ------------------------------------------- exchange through peer memory (no counterpart in the reference)
+ * For the unit-range sharded decode: every rank owns a mailbox buffer that every rank of the node can write (CUDA
+ * IPC).  infllm_mailbox_create allocates it and returns its handle (infllm_mailbox_handle_bytes() bytes); the
+ * caller gathers the handles of all ranks and passes them, in rank order, to infllm_mailbox_open.
+ * infllm_mailbox_put copies a message into slot [this rank] of every rank's mailbox (at slot_off + rank *
+ * slot_bytes) with a kernel and then sets the flag word [this rank] at flag_off of every mailbox to `seq`;
+ * infllm_mailbox_wait makes `stream` wait — at most limit_us microseconds — until all ranks' flag words of the
+ * local mailbox show `seq`; a sender that does not arrive leaves 1 + its rank in *d_err, and kernels behind the
+ * wait that are given d_err write nothing.  With miss_off >= 0 the word at that offset of every received message
+ * is OR-ed into *d_any_miss; d_clear (may be NULL) is a device word the same kernel sets to zero.
+ * infllm_topk_pairs ranks the gathered retrieval candidates, world messages
+ * [k score bit patterns | k ids] (sender_stride_words apart), into the k best ids: descending score, ties to the
+ * lower id, ids < 0 are padding.  The exchanges of one token alternate (candidates, partials), which is the
+ * flow control: a mailbox slot is rewritten only after every rank has consumed it. */
+typedef struct infllm_mailbox infllm_mailbox;
+int infllm_mailbox_handle_bytes(void);
+int infllm_mailbox_create(int64_t bytes, int rank, int world, void* h_handle, infllm_mailbox** out);
+int infllm_mailbox_open(infllm_mailbox* m, const void* h_handles);
+void* infllm_mailbox_local(infllm_mailbox* m);
+int infllm_mailbox_destroy(infllm_mailbox* m);
+int infllm_mailbox_put(infllm_mailbox* m, const void* d_src, int64_t bytes, int64_t slot_off, int64_t slot_bytes,
+                       int64_t flag_off, uint32_t seq, void* stream);
+int infllm_mailbox_wait(infllm_mailbox* m, int64_t flag_off, uint32_t seq, int limit_us, int* d_err, int64_t slot_off,
+                        int64_t slot_bytes, int64_t miss_off, int32_t* d_any_miss, int32_t* d_clear, void* stream);
+int infllm_topk_pairs(const int32_t* d_cand, int64_t sender_stride_words, int world, int k, int32_t* d_out_ids,
+                      const int* d_err, void* stream);
 
 /* One memory unit from the pinned host store into a cache slot, asynchronously on `stream`: MemoryUnit.load's
  * host-to-device copy (context_manager.py:57-71) for callers that keep their own cache. */

@@ -78,7 +78,21 @@ SIGNATURES = {
     "infllm_lse_merge": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int,
                                  c_void_p]),
     "infllm_lse_merge_ex": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,
-                                    c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+                                    c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
+    "infllm_attn_decode_units": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(c_void_p),
+                                         POINTER(c_void_p), POINTER(c_int64), POINTER(c_int32), POINTER(c_int32),
+                                         c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                         c_void_p, c_void_p, c_int, POINTER(c_int), c_int, c_void_p, c_int, c_void_p]),
+    "infllm_slot_table_update": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int, c_void_p]),
+    "infllm_mailbox_handle_bytes": (c_int, []),
+    "infllm_mailbox_create": (c_int, [c_int64, c_int, c_int, c_void_p, POINTER(c_void_p)]),
+    "infllm_mailbox_open": (c_int, [c_void_p, c_void_p]),
+    "infllm_mailbox_local": (c_void_p, [c_void_p]),
+    "infllm_mailbox_destroy": (c_int, [c_void_p]),
+    "infllm_mailbox_put": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, ctypes.c_uint32, c_void_p]),
+    "infllm_mailbox_wait": (c_int, [c_void_p, c_int64, ctypes.c_uint32, c_int, c_void_p, c_int64, c_int64, c_int64,
+                                    c_void_p, c_void_p, c_void_p]),
+    "infllm_topk_pairs": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "infllm_ingest_token": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
                                     c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),

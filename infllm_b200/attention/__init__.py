@@ -5,7 +5,7 @@ from .dot_production_attention import CudaMultiStageDotProductionAttention, get_
 from .head_groups import HeadGroupComm
 from .inf_llm import inf_llm_forward
 from .rope import RotaryEmbeddingESM
-from .sharded_decode import ShardedDecodeMemory, UnitRangeShard, global_topk, unit_range
+from .sharded_decode import PeerMailbox, ShardedDecodeMemory, UnitRangeShard, global_topk, unit_range
 
 ATTN_FORWRAD = {
     "inf-llm": inf_llm_forward,
@@ -14,4 +14,4 @@ ATTN_FORWARD = ATTN_FORWRAD
 
 __all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward",
            "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention",
-           "HeadGroupComm", "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]
+           "HeadGroupComm", "PeerMailbox", "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]

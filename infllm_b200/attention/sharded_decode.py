@@ -85,7 +85,13 @@ class UnitRangeShard:
         self.part_o = torch.empty((self.max_parts, H, D), dtype=torch.float32, device=dev)
         self.part_lse = torch.empty((self.max_parts, H), dtype=torch.float32, device=dev)
         self.logits = torch.empty((H, n_local + 1), dtype=torch.float32, device=dev)
-        self.pack = torch.empty((H * (D + 1),), dtype=torch.float32, device=dev)  # [o (H, D) | lse (H)]
+        # [o (H, D) | lse (H) | miss word | pad]: the message a rank sends to its peers
+        self.pack = torch.zeros((H * (D + 1) + 4,), dtype=torch.float32, device=dev)
+        # [global retrieval ranked on the device (topk) | exchange error | any miss | pad]: read by the host per token
+        self.d_status = torch.zeros((topk + 4,), dtype=torch.int32, device=dev)
+        self.d_status[:topk] = -1
+        self.h_status = torch.zeros((topk + 4,), dtype=torch.int32).pin_memory()
+        self.slot_table = None
         self.lse = torch.empty((H,), dtype=torch.float32, device=dev)
         self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
         self.scores_buf = None
@@ -98,12 +104,17 @@ class UnitRangeShard:
         # raw addresses of the buffers the per-token calls pass on (tensor indexing costs microseconds a piece)
         self._p = {name: getattr(self, name).data_ptr() for name in
                    ("k_raw", "k_rot", "v", "score", "q_loc", "q_glb", "qbar", "cos", "sin", "cache", "part_o", "part_lse",
-                    "logits", "pack", "lse", "cand")}
+                    "logits", "pack", "lse", "cand", "d_status")}
         self.unit_bytes = 2 * n_kv_heads * block_size * head_dim * self.k_raw.element_size()
         self._stream = None
         m = topk + 3  # retrieved units + window share + sink + overflow
         self._seg_arrays = ((ctypes.c_void_p * m)(), (ctypes.c_void_p * m)(), (ctypes.c_int64 * m)(),
                             (ctypes.c_int32 * m)(), (ctypes.c_int32 * m)())
+        self._unit_seg_arrays = ((ctypes.c_void_p * m)(), (ctypes.c_void_p * m)(), (ctypes.c_int64 * m)(),
+                                 (ctypes.c_int32 * m)(), (ctypes.c_int32 * m)())
+        for i in range(topk):
+            self._unit_seg_arrays[2][i], self._unit_seg_arrays[3][i], self._unit_seg_arrays[4][i] = (
+                block_size * head_dim, block_size, 1)
 
     def __del__(self):
         if getattr(self, "lru", None):
@@ -124,6 +135,7 @@ class UnitRangeShard:
         self.block_k = torch.zeros((max(room, 1), self.H * self.D), dtype=self.dtype, device=self.device)
         self.block_k[:n_owned].copy_(block_k)
         self.scores_buf = torch.empty((max(room, 1),), dtype=torch.float32, device=self.device)
+        self.slot_table = torch.full((max(room, 1),), -1, dtype=torch.int32, device=self.device)
         self.init_k, self.init_v = init_k.to(self.device).contiguous(), init_v.to(self.device).contiguous()
         self._store_pointers()
         self.n_total, self.lo, self.n_owned = n_total, lo, n_owned
@@ -138,6 +150,7 @@ class UnitRangeShard:
 
     def _store_pointers(self):
         self._p.update(block_k=self.block_k.data_ptr(), host_units=self.host_units.data_ptr(),
+                       slot_table=self.slot_table.data_ptr(),
                        scores_buf=self.scores_buf.data_ptr(), init_k=self.init_k.data_ptr(), init_v=self.init_v.data_ptr())
 
     def _rope(self, x, x_hs, x_ts, out, o_hs, o_ts, heads, length, pos0, step):
@@ -229,7 +242,7 @@ class UnitRangeShard:
             segs.append((p["k_raw"] + off, p["v"] + off, self.cap * D, wlo - self.frontier, 1))
         if not segs:
             self.pack[:self.H * D].zero_()
-            self.pack[self.H * D:].fill_(float("-inf"))
+            self.pack[self.H * D:self.H * (D + 1)].fill_(float("-inf"))
             return self.pack
         n = len(segs)
         kp, vp, hs, ln, qs = self._seg_arrays
@@ -257,8 +270,10 @@ class UnitRangeShard:
         ev = (ctypes.c_int32 * max(self.max_cached, 1))()
         n_ev = ctypes.c_int()
         _lib.check(_lib.lib.infllm_lru_plan(self.lru, want, n, ev, ctypes.byref(n_ev)))
+        changed = {}
         for i in range(n_ev.value):
             self.free_slots.append(self.slot_of.pop(ev[i]))
+            changed[ev[i] - self.lo] = -1
         _lib.check(_lib.lib.infllm_lru_stamp(self.lru, want, n, float(self.load_count)))
         for b in owned:
             if b in self.slot_of:
@@ -267,22 +282,68 @@ class UnitRangeShard:
             self.misses += 1
             slot = self.free_slots.pop()
             self.slot_of[b] = slot
+            changed[b - self.lo] = slot
             _lib.check(_lib.lib.infllm_unit_fetch(self._p["cache"] + slot * self.unit_bytes,
                                                   self._p["host_units"] + (b - self.lo) * self.unit_bytes,
                                                   self.unit_bytes, self._stream))
+        if changed:  # the device copy of the slot table, read by attend_device()
+            m = len(changed)
+            ids = (ctypes.c_int32 * m)(*changed.keys())
+            slots = (ctypes.c_int32 * m)(*changed.values())
+            _lib.check(_lib.lib.infllm_slot_table_update(self._p["slot_table"], ids, slots, m, self._stream))
+
+    def attend_device(self):
+        """attend() for a retrieval that exists only on the device so far (d_gids): the owned units are resolved
+        through the device copy of the slot table.  The message [o | lse | miss word] is left in `pack`; the miss
+        word is 1 when an owned retrieved unit was not cached (its weight is then zero and the token is redone)."""
+        E, G, r = self.length + 1, self.world, self.rank
+        esz, D, p = 2, self.D, self._p
+        kp, vp, hs, ln, qs = self._unit_seg_arrays  # the first topk entries are placeholders the kernel resolves
+        n = self.topk
+        wlo = max(E - self.n_local, 0)
+        W = E - wlo
+        a, b_ = wlo + (W * r) // G, wlo + (W * (r + 1)) // G
+        self._share = (a, b_)
+        logit_seg = -1
+        if b_ > a:
+            off = (a - self.t0) * D * esz
+            logit_seg = n
+            kp[n], vp[n], hs[n], ln[n], qs[n] = p["k_rot"] + off, p["v"] + off, self.cap * D, b_ - a, 0
+            n += 1
+        if r == 0 and self.n_init > 0:
+            kp[n], vp[n], hs[n], ln[n], qs[n] = p["init_k"], p["init_v"], self.n_init * D, self.n_init, 1
+            n += 1
+        if r == G - 1 and wlo > self.frontier:
+            off = (self.frontier - self.t0) * D * esz
+            kp[n], vp[n], hs[n], ln[n], qs[n] = p["k_raw"] + off, p["v"] + off, self.cap * D, wlo - self.frontier, 1
+            n += 1
+        n_parts = ctypes.c_int()
+        miss = p["pack"] + self.H * (D + 1) * 4
+        ev = self._mark("decode")
+        _lib.check(_lib.lib.infllm_attn_decode_units(
+            p["q_loc"], p["q_glb"], self.H, self.HKV, D, n, kp, vp, hs, ln, qs, 0, self.topk, p["d_status"], p["slot_table"],
+            self.lo, self.n_owned, p["cache"], self.unit_bytes, miss, p["part_o"], p["part_lse"], self.max_parts,
+            ctypes.byref(n_parts), logit_seg, p["logits"], self.code, self._stream))
+        _lib.check(_lib.lib.infllm_lse_merge(p["part_o"], p["part_lse"], n_parts.value, self.H, D, p["pack"], D,
+                                             p["pack"] + self.H * D * 4, F32, self._stream))
+        self._mark("decode", ev)
 
     # ------------------------------------------------------------------ step 5
     def merge(self, parts):
         """Step 4 and the first half of step 5 on this rank: log-sum-exp merge of the gathered partials
         (G, H*(D+1)) fp32 rows [o | lse] into the token's output (H, D), and this rank's share of the token's local
         attention row added to the accumulated scores, in one launch."""
+        return self.merge_raw(parts.data_ptr(), parts.stride(0), parts.shape[0], None)
+
+    def merge_raw(self, base, stride, n, skip):
+        """merge() over n messages `stride` floats apart at device address `base`; `skip`: address of a device
+        word that voids the call when it is non-zero (or None)."""
         H, D, p = self.H, self.D, self._p
         out = torch.empty((H, D), dtype=self.dtype, device=self.device)
         a, b = self._share
-        base, stride = parts.data_ptr(), parts.stride(0)
         _lib.check(_lib.lib.infllm_lse_merge_ex(
-            base, stride, base + H * D * 4, stride, parts.shape[0], H, D, out.data_ptr(), D, p["lse"], self.code,
-            p["logits"] if b > a else None, b - a, p["score"] + (a - self.t0) * 4, self.cap, self._stream))
+            base, stride, base + H * D * 4, stride, n, H, D, out.data_ptr(), D, p["lse"], self.code,
+            p["logits"] if b > a else None, b - a, p["score"] + (a - self.t0) * 4, self.cap, skip, self._stream))
         return out
 
     def finish(self):
@@ -322,7 +383,54 @@ class UnitRangeShard:
         bk[:self.n_owned].copy_(self.block_k[:self.n_owned])
         self.block_k = bk
         self.scores_buf = torch.empty((room,), dtype=torch.float32, device=self.device)
+        table = torch.full((room,), -1, dtype=torch.int32, device=self.device)
+        table[:self.slot_table.shape[0]].copy_(self.slot_table)
+        self.slot_table = table
         self._store_pointers()
+
+
+class PeerMailbox:
+    """This rank's mailbox in device memory, writable by every rank of the node (CUDA IPC), for the two
+    exchanges of a token: the retrieval candidates and the attention partials.  Collective: every rank of
+    `group` constructs it.  Layout: [flags of exchange 1 | flags of exchange 2 | candidate slots | partial slots].
+    """
+
+    def __init__(self, topk, n_heads, head_dim, group=None, device=None, wait_us=2000000):
+        import torch.distributed as dist
+
+        self.group, self.rank, self.world = group, dist.get_rank(group), dist.get_world_size(group)
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.wait_us = wait_us
+        self.flag1, self.flag2 = 0, 256
+        self.cand_off, self.cand_bytes = 512, 2 * topk * 4
+        self.cand_slot = (self.cand_bytes + 15) // 16 * 16
+        self.part_off = (self.cand_off + self.world * self.cand_slot + 255) // 256 * 256
+        self.part_bytes = (n_heads * (head_dim + 1) + 4) * 4  # [o | lse | miss word | pad]
+        self.part_slot = (self.part_bytes + 15) // 16 * 16
+        self.miss_off = n_heads * (head_dim + 1) * 4
+        total = self.part_off + self.world * self.part_slot
+        n = int(_lib.lib.infllm_mailbox_handle_bytes())
+        mine = (ctypes.c_ubyte * n)()
+        self.handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib.infllm_mailbox_create(total, self.rank, self.world, mine, ctypes.byref(self.handle)))
+            if self.world > 1:
+                local = torch.tensor(list(mine), dtype=torch.uint8, device=device)
+                every = torch.empty((self.world, n), dtype=torch.uint8, device=device)
+                dist.all_gather_into_tensor(every, local[None], group=group)
+                flat = every.cpu().reshape(-1).tolist()
+                _lib.check(_lib.lib.infllm_mailbox_open(self.handle, (ctypes.c_ubyte * len(flat))(*flat)))
+                dist.barrier(group=group)  # nobody writes before everybody has mapped
+        self.local = int(_lib.lib.infllm_mailbox_local(self.handle))
+        self.seq = 0
+
+    def close(self):
+        if getattr(self, "handle", None):
+            _lib.lib.infllm_mailbox_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        self.close()
 
 
 class ShardedDecodeMemory:
@@ -332,8 +440,13 @@ class ShardedDecodeMemory:
     (pass `group`, or leave None for the default group), or all G of them when the ranks share one process.
     """
 
-    def __init__(self, shards, distributed=False, group=None):
+    def __init__(self, shards, distributed=False, group=None, mailbox=None):
         self.shards, self.distributed, self.group = list(shards), distributed, group
+        # with a PeerMailbox the two exchanges of a token run inside kernels over peer memory and the retrieval is
+        # ranked on the device; the collectives below remain for the rare token that has to be redone (a retrieved
+        # unit was not cached) and for the score columns of a sealing
+        self.mailbox = mailbox if (distributed and mailbox is not None and mailbox.world > 1) else None
+        self.redone = 0
         if not distributed:
             assert [s.rank for s in self.shards] == list(range(self.shards[0].world)), "emulation needs every rank"
         self.last_ids = []
@@ -359,6 +472,8 @@ class ShardedDecodeMemory:
     def append(self, q, k, v):
         """q (H, 1, D), k and v (H_kv, 1, D) of one new token -> attention output (H, 1, D)."""
         s0 = self.shards[0]
+        if self.mailbox is not None and s0.n_total > s0.topk:
+            return self._append_peer(q, k, v)
         cand = self._all_gather(self._stack([s.begin(q, k, v) for s in self.shards]))  # (G, 2, topk) int32
         if s0.n_total <= s0.topk:  # every unit, in id order, no scoring (context_manager.py:370-371)
             ids = list(range(s0.n_total))
@@ -374,6 +489,54 @@ class ShardedDecodeMemory:
             for s in self.shards:
                 s.seal(total)
         return outs[0].view(s0.H, 1, s0.D)
+
+    def _append_peer(self, q, k, v):
+        """append() with both exchanges inside kernels: candidates and partials are written straight into the
+        peers' mailboxes, the global top-k is ranked on the device and the attention resolves the retrieved units
+        it owns through the device copy of its slot table.  The host reads the retrieval afterwards, for the LRU
+        order, and redoes the token through the collectives if any rank reports a unit that was not cached."""
+        s, mb, lib = self.shards[0], self.mailbox, _lib.lib
+        p, H, D = s._p, s.H, s.D
+        if mb.seq == 0 and self.distributed:  # the first exchange: nobody waits on a rank that is still setting up
+            import torch.distributed as dist
+
+            dist.barrier(group=self.group)
+        s.begin(q, k, v)
+        st = s._stream
+        mb.seq += 1
+        err, any_miss = p["d_status"] + 4 * s.topk, p["d_status"] + 4 * s.topk + 4
+        miss_word = p["pack"] + H * (D + 1) * 4
+        _lib.check(lib.infllm_mailbox_put(mb.handle, p["cand"], mb.cand_bytes, mb.cand_off, mb.cand_slot, mb.flag1,
+                                          mb.seq, st))
+        _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag1, mb.seq, mb.wait_us, err, 0, 0, -1, None, miss_word, st))
+        _lib.check(lib.infllm_topk_pairs(mb.local + mb.cand_off, mb.cand_slot // 4, mb.world, s.topk, p["d_status"], err,
+                                         st))
+        s.attend_device()
+        _lib.check(lib.infllm_mailbox_put(mb.handle, p["pack"], mb.part_bytes, mb.part_off, mb.part_slot, mb.flag2,
+                                          mb.seq, st))
+        _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag2, mb.seq, mb.wait_us, err, mb.part_off, mb.part_slot,
+                                           mb.miss_off, any_miss, None, st))
+        out = s.merge_raw(mb.local + mb.part_off, mb.part_slot // 4, mb.world, any_miss)
+        # the retrieval and the two status words, for the host
+        s.h_status.copy_(s.d_status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        status = s.h_status.tolist()
+        ids = [b for b in status[:s.topk] if b >= 0]
+        if status[s.topk]:
+            s.d_status[s.topk:].zero_()
+            raise _lib.InfLLMError(_lib.E_TIMEOUT, f"rank {status[s.topk] - 1} did not arrive at an exchange of the "
+                                                   "sharded decode within the limit")
+        self.last_ids = ids
+        if status[s.topk + 1]:  # some rank lacked a unit: refill, then this token again through the collectives
+            self.redone += 1
+            parts = self._all_gather(s.attend(ids)[None])
+            out = s.merge(parts)
+        else:
+            s._refill([b for b in ids if s.lo <= b < s.lo + s.n_owned])  # all cached: advances the LRU order only
+        sealing = s.finish()
+        if sealing is not None:
+            s.seal(self._all_reduce(sealing))
+        return out.view(H, 1, D)
 
     @staticmethod
     def _stack(tensors):

@@ -75,6 +75,9 @@ struct DecodeIndirect {
   int64_t unit_bytes = 0;          // K then V of one unit
   int32_t n_units = 0, first_seg = 0;
   int32_t* miss = nullptr;
+  // unit-range sharding: this GPU owns the ids [id_lo, id_lo + n_owned) and `table` starts at id_lo; a retrieved
+  // unit of another rank, or a padding id < 0, gets weight zero here and is not a miss
+  int32_t id_lo = 0, n_owned = 0x7fffffff;
 };
 
 int attn_general_launch(const AttnParams& p, int head_dim, int dtype, cudaStream_t s);

@@ -74,10 +74,13 @@ __global__ void __launch_bounds__(32) attn_decode_kernel(const __grid_constant__
   if (P.ind.n_units > 0) {
     const int u = sg - P.ind.first_seg;
     if (u >= 0 && u < P.ind.n_units) {
-      const int slot = __ldg(P.ind.table + __ldg(P.ind.ids + u));
+      const int id = __ldg(P.ind.ids + u) - P.ind.id_lo;
+      const bool mine = id >= 0 && id < P.ind.n_owned;
+      const int slot = mine ? __ldg(P.ind.table + id) : -1;
       if (slot < 0) {
-        // not cached: this chunk's partials get weight zero here; the host launches the unit again after the refill
-        if (lane == 0) *P.ind.miss = 1;
+        // not cached: this chunk's partials get weight zero here; the host launches the unit again after the
+        // refill.  A unit that another rank owns is that rank's business.
+        if (lane == 0 && mine) *P.ind.miss = 1;
         const int grp = P.n_heads / P.n_kv_heads;
         for (int i = lane; i < grp * HD; i += 32)
           P.part_o[((int64_t)part * P.n_heads + hkv * grp + i / HD) * HD + i % HD] = 0.f;
@@ -473,7 +476,7 @@ extern "C" int infllm_lse_merge(const float* d_part_o, const float* d_part_lse, 
 extern "C" int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride, const float* d_part_lse,
                                    int64_t part_lse_stride, int n_part, int n_heads, int head_dim, void* d_out,
                                    int64_t o_hs, float* d_lse, int dtype, const float* d_logits, int64_t logit_len,
-                                   float* d_score, int64_t score_hs, void* stream) {
+                                   float* d_score, int64_t score_hs, const int32_t* d_skip, void* stream) {
   using namespace infllm;
   if (!d_part_o || !d_part_lse || !d_out) return fail(INFLLM_E_BADARG, "lse_merge_ex: null pointer");
   if (part_o_stride < (int64_t)n_heads * head_dim || part_lse_stride < n_heads)
@@ -482,6 +485,37 @@ extern "C" int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride,
   if (d_logits && (!d_score || !d_lse || logit_len < 0))
     return fail(INFLLM_E_BADARG, "lse_merge_ex: logits without a score buffer");
   return lse_merge_launch(d_part_o, d_part_lse, n_part, n_heads, head_dim, d_out, o_hs, d_lse, dtype,
-                          (cudaStream_t)stream, d_logits, d_logits ? logit_len : 0, d_score, score_hs, nullptr,
+                          (cudaStream_t)stream, d_logits, d_logits ? logit_len : 0, d_score, score_hs, d_skip,
                           part_o_stride, part_lse_stride);
+}
+
+// infllm_attn_decode whose segments [first_unit_seg, first_unit_seg + n_units) are memory units named on the
+// DEVICE: unit i is d_unit_ids[i]; this GPU owns the ids [id_lo, id_lo + n_owned) and finds them in cache slot
+// d_slot_table[id - id_lo] (K then V of unit_bytes at d_cache + slot * unit_bytes; -1: not cached).  Units of
+// other owners and ids < 0 get weight zero; an owned unit that is not cached gets weight zero and sets *d_miss.
+// The h_seg_k / h_seg_v entries of those segments are ignored.
+extern "C" int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim,
+                                        int n_seg, const void* const* h_seg_k, const void* const* h_seg_v,
+                                        const int64_t* h_seg_hs, const int32_t* h_seg_len, const int32_t* h_seg_q,
+                                        int first_unit_seg, int n_units, const int32_t* d_unit_ids,
+                                        const int32_t* d_slot_table, int id_lo, int n_owned, const void* d_cache,
+                                        int64_t unit_bytes, int32_t* d_miss, float* d_part_o, float* d_part_lse,
+                                        int max_parts, int* n_parts, int logit_seg, float* d_logits, int dtype,
+                                        void* stream) {
+  using namespace infllm;
+  if (!d_q0 || !h_seg_k || !h_seg_v || !h_seg_hs || !h_seg_len || !h_seg_q || !d_part_o || !d_part_lse)
+    return fail(INFLLM_E_BADARG, "attn_decode_units: null pointer");
+  if (n_seg <= 0 || n_seg > kMaxSeg) return fail(INFLLM_E_BADARG, "attn_decode_units: %d segments (1..%d)", n_seg, kMaxSeg);
+  if (logit_seg >= 0 && !d_logits) return fail(INFLLM_E_BADARG, "attn_decode_units: logits requested without a buffer");
+  KvSeg segs[kMaxSeg];
+  for (int i = 0; i < n_seg; ++i) {
+    const bool unit = i >= first_unit_seg && i < first_unit_seg + n_units;
+    segs[i] = {unit ? nullptr : h_seg_k[i], unit ? nullptr : h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
+  }
+  DecodeIndirect ind;
+  ind.ids = d_unit_ids; ind.table = d_slot_table; ind.cache = (const char*)d_cache; ind.unit_bytes = unit_bytes;
+  ind.n_units = n_units; ind.first_seg = first_unit_seg; ind.miss = d_miss; ind.id_lo = id_lo; ind.n_owned = n_owned;
+  return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o,
+                            d_part_lse, max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream,
+                            kDecodeChunk, n_units > 0 ? &ind : nullptr, 0);
 }

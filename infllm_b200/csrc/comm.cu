@@ -99,3 +99,197 @@ extern "C" int infllm_comm_destroy(infllm_comm* c) {
   delete c;
   return INFLLM_OK;
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Exchange through peer memory for the unit-range sharded decode: every rank owns one mailbox buffer that all
+// ranks can write (CUDA IPC mappings); a message is put straight into slot [sender] of every peer's mailbox by a
+// kernel, followed by a flag word holding the sequence number of the exchange; the receiver's next kernels start
+// behind a kernel that waits — with a bound — until every sender's flag shows that number.  No host round trip,
+// no collective library call on the token's path.
+//
+// The waits are bounded: when a flag does not arrive within the limit (a peer died or fell far behind) the wait
+// kernel records an error word and returns, the kernels behind it see the word and write nothing, and the host
+// reads it with the token's result.
+
+struct infllm_mailbox {
+  void* local = nullptr;        // this rank's buffer
+  void* peer[16] = {nullptr};   // the same buffer of every rank as mapped here (peer[rank] == local)
+  size_t bytes = 0;
+  int rank = 0, world = 1;
+};
+
+namespace infllm {
+
+constexpr int kMaxPeers = 16;
+struct PeerList {
+  void* dst[kMaxPeers];
+  uint32_t* flag[kMaxPeers];
+};
+
+// one CTA per destination: copy n16 16-byte words, make them visible system-wide, then raise the flag
+__global__ void __launch_bounds__(256)
+peer_put_kernel(const uint4* __restrict__ src, int n16, const __grid_constant__ PeerList peers, uint32_t seq) {
+  uint4* dst = reinterpret_cast<uint4*>(peers.dst[blockIdx.x]);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    volatile uint32_t* f = peers.flag[blockIdx.x];
+    *f = seq;
+  }
+}
+
+// lane q waits for flags[q] == seq, at most `limit` polls of ~200 ns; *err = 1 + q when one ran out.
+// With miss_words != nullptr (one word per sender, inside the messages just received) their OR goes to *any_miss.
+__global__ void peer_wait_kernel(const volatile uint32_t* flags, uint32_t seq, int world, uint32_t limit, int* err,
+                                 const volatile int32_t* miss_words, int64_t miss_stride, int32_t* any_miss,
+                                 int32_t* clear_word) {
+  const int q = threadIdx.x;
+  if (clear_word && q == 0) *clear_word = 0;
+  bool ok = true;
+  if (q < world) {
+    uint32_t i = 0;
+    while (flags[q] != seq) {
+      if (++i > limit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!ok) atomicExch(err, 1 + q);
+  }
+  __threadfence_system();
+  const unsigned all_ok = __all_sync(0xffffffffu, ok);
+  if (any_miss) {
+    int m = (q < world && miss_words && all_ok) ? miss_words[q * miss_stride] : 0;
+    m = __any_sync(0xffffffffu, m != 0);
+    if (q == 0) *any_miss = (m || !all_ok) ? 1 : 0;
+  }
+}
+
+// the k best of world * k gathered candidates [sender][score bits (k) | ids (k)]: descending score, ties to the
+// lower id, ids < 0 are padding; one CTA
+__global__ void __launch_bounds__(256)
+topk_pairs_kernel(const int32_t* __restrict__ cand, int64_t sender_stride, int world, int k, int32_t* __restrict__ out_ids,
+                  const int* __restrict__ err) {
+  __shared__ float s_score[1024];
+  __shared__ int32_t s_id[1024];
+  const int n = world * k;
+  if (err && *err) {  // the exchange failed: no retrieval
+    for (int i = threadIdx.x; i < k; i += blockDim.x) out_ids[i] = -1;
+    return;
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int32_t* c = cand + (int64_t)(i / k) * sender_stride;
+    s_score[i] = __int_as_float(c[i % k]);
+    s_id[i] = c[k + i % k];
+  }
+  for (int i = threadIdx.x; i < k; i += blockDim.x) out_ids[i] = -1;  // fewer than k real candidates: padding
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = s_score[i];
+    const int32_t id = s_id[i];
+    if (id < 0) continue;
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const int32_t oj = s_id[j];
+      rank += oj >= 0 && (s_score[j] > v || (s_score[j] == v && oj < id));
+    }
+    if (rank < k) out_ids[rank] = id;
+  }
+}
+
+}  // namespace infllm
+
+extern "C" int infllm_mailbox_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+// allocates this rank's mailbox (zeroed) and writes its IPC handle to h_handle
+extern "C" int infllm_mailbox_create(int64_t bytes, int rank, int world, void* h_handle, infllm_mailbox** out) {
+  if (bytes <= 0 || !h_handle || !out || world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(INFLLM_E_BADARG, "mailbox_create: bad argument (at most %d ranks)", kMaxPeers);
+  infllm_mailbox* m = new (std::nothrow) infllm_mailbox();
+  if (!m) return fail(INFLLM_E_NOMEM, "mailbox_create: out of host memory");
+  m->bytes = (size_t)bytes;
+  m->rank = rank;
+  m->world = world;
+  cudaError_t e = cudaMalloc(&m->local, m->bytes);
+  if (e == cudaSuccess) e = cudaMemset(m->local, 0, m->bytes);
+  if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(h_handle), m->local);
+  if (e != cudaSuccess) {
+    if (m->local) cudaFree(m->local);
+    delete m;
+    return fail(INFLLM_E_CUDA, "mailbox_create: %s", cudaGetErrorString(e));
+  }
+  m->peer[rank] = m->local;
+  *out = m;
+  return INFLLM_OK;
+}
+
+// h_handles: world handles in rank order (as gathered by the caller); maps every peer's mailbox
+extern "C" int infllm_mailbox_open(infllm_mailbox* m, const void* h_handles) {
+  if (!m || !h_handles) return fail(INFLLM_E_BADARG, "mailbox_open: null pointer");
+  const cudaIpcMemHandle_t* hs = reinterpret_cast<const cudaIpcMemHandle_t*>(h_handles);
+  for (int r = 0; r < m->world; ++r) {
+    if (r == m->rank) continue;
+    cudaError_t e = cudaIpcOpenMemHandle(&m->peer[r], hs[r], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(INFLLM_E_CUDA, "mailbox_open: rank %d: %s", r, cudaGetErrorString(e));
+  }
+  return INFLLM_OK;
+}
+
+extern "C" void* infllm_mailbox_local(infllm_mailbox* m) { return m ? m->local : nullptr; }
+
+extern "C" int infllm_mailbox_destroy(infllm_mailbox* m) {
+  if (!m) return INFLLM_OK;
+  for (int r = 0; r < m->world; ++r)
+    if (r != m->rank && m->peer[r]) cudaIpcCloseMemHandle(m->peer[r]);
+  if (m->local) cudaFree(m->local);
+  delete m;
+  return INFLLM_OK;
+}
+
+// d_src (bytes, a multiple of 16) -> offset slot_off + rank * slot_bytes of every rank's mailbox, then the flag word
+// at flag_off + 4 * rank of every mailbox is set to seq
+extern "C" int infllm_mailbox_put(infllm_mailbox* m, const void* d_src, int64_t bytes, int64_t slot_off,
+                                  int64_t slot_bytes, int64_t flag_off, uint32_t seq, void* stream) {
+  if (!m || !d_src || bytes <= 0 || bytes % 16 || bytes > slot_bytes || slot_off % 16 || slot_bytes % 16 ||
+      slot_off + (int64_t)m->world * slot_bytes > (int64_t)m->bytes || flag_off + 4 * m->world > (int64_t)m->bytes)
+    return fail(INFLLM_E_BADARG, "mailbox_put: bad argument");
+  PeerList pl{};
+  for (int r = 0; r < m->world; ++r) {
+    if (!m->peer[r]) return fail(INFLLM_E_BADARG, "mailbox_put: rank %d is not mapped (infllm_mailbox_open)", r);
+    pl.dst[r] = (char*)m->peer[r] + slot_off + (int64_t)m->rank * slot_bytes;
+    pl.flag[r] = reinterpret_cast<uint32_t*>((char*)m->peer[r] + flag_off) + m->rank;
+  }
+  peer_put_kernel<<<m->world, 256, 0, (cudaStream_t)stream>>>((const uint4*)d_src, (int)(bytes / 16), pl, seq);
+  INFLLM_LAUNCH_OK("peer_put_kernel");
+  return INFLLM_OK;
+}
+
+// waits on `stream` until the flag words of all ranks at flag_off show seq (bounded: limit_us microseconds);
+// d_err receives 1 + rank of a sender that did not arrive.  With miss_off >= 0 the word at
+// slot_off + r * slot_bytes + miss_off of every received message is OR-ed into *d_any_miss.  d_clear (may be
+// null): a device word set to zero by the same kernel (the miss word of the message about to be built).
+extern "C" int infllm_mailbox_wait(infllm_mailbox* m, int64_t flag_off, uint32_t seq, int limit_us, int* d_err,
+                                   int64_t slot_off, int64_t slot_bytes, int64_t miss_off, int32_t* d_any_miss,
+                                   int32_t* d_clear, void* stream) {
+  if (!m || !d_err || flag_off < 0 || flag_off + 4 * m->world > (int64_t)m->bytes)
+    return fail(INFLLM_E_BADARG, "mailbox_wait: bad argument");
+  const uint32_t limit = (uint32_t)((limit_us > 0 ? limit_us : 100000) * 5ll);  // polls of ~200 ns
+  const volatile int32_t* mw = miss_off >= 0 ? reinterpret_cast<const volatile int32_t*>((char*)m->local + slot_off + miss_off) : nullptr;
+  peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const volatile uint32_t*>((char*)m->local + flag_off), seq, m->world, limit, d_err, mw,
+      slot_bytes / 4, d_any_miss, d_clear);
+  INFLLM_LAUNCH_OK("peer_wait_kernel");
+  return INFLLM_OK;
+}
+
+// global top-k of the candidates gathered in the local mailbox: world messages [score bits (k) | ids (k)] int32
+extern "C" int infllm_topk_pairs(const int32_t* d_cand, int64_t sender_stride_words, int world, int k,
+                                 int32_t* d_out_ids, const int* d_err, void* stream) {
+  if (!d_cand || !d_out_ids || world < 1 || k < 1 || world * k > 1024)
+    return fail(INFLLM_E_BADARG, "topk_pairs: bad argument (world * k <= 1024)");
+  topk_pairs_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(d_cand, sender_stride_words, world, k, d_out_ids, d_err);
+  INFLLM_LAUNCH_OK("topk_pairs_kernel");
+  return INFLLM_OK;
+}

@@ -605,3 +605,11 @@ extern "C" int infllm_block_score_rows(const void* d_block_k, const int32_t* h_r
   if (width % 8 != 0 || width > 12 * 1024) return fail(INFLLM_E_BADARG, "block_score_rows: width %d", width);
   return block_score_rows_launch(d_block_k, h_rows, n, width, d_qbar, d_scores, dtype, (cudaStream_t)stream);
 }
+
+// d_table[h_ids[i]] = h_slots[i] for i < n on `stream` (ids must not repeat); -1 marks "not cached"
+extern "C" int infllm_slot_table_update(int32_t* d_table, const int32_t* h_ids, const int32_t* h_slots, int n,
+                                        void* stream) {
+  using namespace infllm;
+  if (!d_table || (n > 0 && (!h_ids || !h_slots)) || n < 0) return fail(INFLLM_E_BADARG, "slot_table_update: bad argument");
+  return slot_table_update_launch(d_table, h_ids, h_slots, n, (cudaStream_t)stream);
+}
