@@ -615,6 +615,23 @@ def run_decode_sharded(args, rank, world, local_rank):
         prof = [sh.get_profile() for sh in shards]
         for sh in shards:
             sh.profile = False
+        if sum(p["topk"][1] for p in prof) == 0:
+            # the one-call token path records no events: time this rank's scoring + top-k launches on their own,
+            # rotating over the layers so that the representative keys come from HBM
+            import ctypes
+
+            evs = []
+            for i in range(8 * len(shards)):
+                sh = shards[i % len(shards)]
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                _lib.check(_lib.lib.infllm_block_topk(sh._p["block_k"], sh.n_owned, H * D, sh._p["qbar"], sh._p["scores_buf"],
+                                                      min(sh.topk, sh.n_owned), sh.lo, sh._p["cand"] + 4 * sh.topk,
+                                                      sh._p["cand"], sh.code, _lib.stream_ptr()))
+                b.record()
+                evs.append((a, b))
+            torch.cuda.synchronize()
+            prof = [dict(topk=(sum(a.elapsed_time(b) for a, b in evs[len(shards):]), len(evs) - len(shards)), decode=(0.0, 0))]
         clocks = sample_clocks_stop(clk_p, clk_f)
         hits, misses = sum(sh.hits for sh in shards), sum(sh.misses for sh in shards)
         step_host()

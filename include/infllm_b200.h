@@ -352,6 +352,45 @@ int infllm_mailbox_wait(infllm_mailbox* m, int64_t flag_off, uint32_t seq, int l
 int infllm_topk_pairs(const int32_t* d_cand, int64_t sender_stride_words, int world, int k, int32_t* d_out_ids,
                       const int* d_err, void* stream);
 
+/* One decode token of a unit-range shard, every launch of it in one call (no counterpart in the reference): ingest,
+ * local scoring + top-k, candidate exchange, global top-k, attention over the owned retrieved units and this
+ * rank's share of the window, local merge, partial exchange, final merge with the accumulation of the local
+ * scores, and the copy of [retrieved ids (topk) | exchange error | any miss | pad] to h_status.  All pointers are
+ * device pointers except h_status (pinned host).  Token buffers are (n_kv_heads, cap, head_dim), token slot `at`
+ * holds position `at` of the rotary table (cap rows); the accumulated scores are (n_heads, cap) fp32. */
+typedef struct infllm_shard_token {
+  const void *d_q, *d_k, *d_vin;           /* the token: q (n_heads rows, q_hs apart), k / v (n_kv_heads rows) */
+  int64_t q_hs, k_hs, v_hs;
+  void *d_q_loc, *d_q_glb;                 /* (n_heads, head_dim) rotated queries */
+  float* d_qbar;                           /* (n_heads * head_dim) */
+  void *d_k_raw, *d_k_rot, *d_v;           /* token buffers */
+  float* d_score;
+  const float *d_cos, *d_sin;
+  int64_t cap, at;                         /* slots of the token buffers; the new token's slot */
+  int32_t n_heads, n_kv_heads, head_dim, dtype, n_local, block_size, topk, pad0;
+  const void* d_block_k;                   /* this rank's representative keys (n_owned rows) */
+  float* d_scores;                         /* (n_owned) scratch */
+  int32_t n_owned, id_lo;                  /* this rank owns the ids [id_lo, id_lo + n_owned) */
+  int32_t* d_cand;                         /* (2 * topk) message: score bits, ids */
+  int32_t* d_status;                       /* (topk + 4) */
+  int32_t* h_status;
+  const int32_t* d_slot_table;             /* (n_owned) id - id_lo -> cache slot or -1 */
+  const void* d_cache;
+  int64_t unit_bytes;
+  int64_t share_at, share_len;             /* this rank's share of the window: slots [share_at, share_at + share_len) */
+  const void *d_init_k, *d_init_v;         /* sink (n_kv_heads, init_len, head_dim); init_len 0 on ranks without it */
+  int64_t ovf_at, ovf_len;                 /* tokens between the last sealed unit and the window; len 0 without */
+  int32_t init_len, max_parts;
+  float *d_part_o, *d_part_lse, *d_logits; /* split-K scratch; logits (n_heads, share_len) */
+  float* d_pack;                           /* (n_heads * (head_dim + 1) + 4) message: o, lse, miss word */
+  void* d_out;                             /* (n_heads, head_dim) result */
+  float* d_lse;                            /* (n_heads) */
+  int64_t cand_off, cand_slot, cand_bytes, part_off, part_slot, part_bytes, flag1_off, flag2_off; /* mailbox layout */
+  uint32_t seq;
+  int32_t wait_us;
+} infllm_shard_token;
+int infllm_shard_token_run(const infllm_shard_token* args, infllm_mailbox* mailbox, void* stream);
+
 /* One memory unit from the pinned host store into a cache slot, asynchronously on `stream`: MemoryUnit.load's
  * host-to-device copy (context_manager.py:57-71) for callers that keep their own cache. */
 int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes, void* stream);

@@ -49,6 +49,33 @@ class CtxInfo(ctypes.Structure):
 
 
 # name -> (restype, argtypes); every symbol the header declares
+class ShardToken(ctypes.Structure):
+    """infllm_shard_token of include/infllm_b200.h."""
+    _fields_ = [
+        ("d_q", c_void_p), ("d_k", c_void_p), ("d_vin", c_void_p),
+        ("q_hs", c_int64), ("k_hs", c_int64), ("v_hs", c_int64),
+        ("d_q_loc", c_void_p), ("d_q_glb", c_void_p), ("d_qbar", c_void_p),
+        ("d_k_raw", c_void_p), ("d_k_rot", c_void_p), ("d_v", c_void_p), ("d_score", c_void_p),
+        ("d_cos", c_void_p), ("d_sin", c_void_p),
+        ("cap", c_int64), ("at", c_int64),
+        ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32), ("dtype", c_int32), ("n_local", c_int32),
+        ("block_size", c_int32), ("topk", c_int32), ("pad0", c_int32),
+        ("d_block_k", c_void_p), ("d_scores", c_void_p),
+        ("n_owned", c_int32), ("id_lo", c_int32),
+        ("d_cand", c_void_p), ("d_status", c_void_p), ("h_status", c_void_p), ("d_slot_table", c_void_p),
+        ("d_cache", c_void_p), ("unit_bytes", c_int64),
+        ("share_at", c_int64), ("share_len", c_int64),
+        ("d_init_k", c_void_p), ("d_init_v", c_void_p),
+        ("ovf_at", c_int64), ("ovf_len", c_int64),
+        ("init_len", c_int32), ("max_parts", c_int32),
+        ("d_part_o", c_void_p), ("d_part_lse", c_void_p), ("d_logits", c_void_p),
+        ("d_pack", c_void_p), ("d_out", c_void_p), ("d_lse", c_void_p),
+        ("cand_off", c_int64), ("cand_slot", c_int64), ("cand_bytes", c_int64), ("part_off", c_int64),
+        ("part_slot", c_int64), ("part_bytes", c_int64), ("flag1_off", c_int64), ("flag2_off", c_int64),
+        ("seq", ctypes.c_uint32), ("wait_us", c_int32),
+    ]
+
+
 SIGNATURES = {
     "infllm_last_error": (c_char_p, []),
     "infllm_version": (c_char_p, []),
@@ -93,6 +120,7 @@ SIGNATURES = {
     "infllm_mailbox_wait": (c_int, [c_void_p, c_int64, ctypes.c_uint32, c_int, c_void_p, c_int64, c_int64, c_int64,
                                     c_void_p, c_void_p, c_void_p]),
     "infllm_topk_pairs": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "infllm_shard_token_run": (c_int, [POINTER(ShardToken), c_void_p, c_void_p]),
     "infllm_ingest_token": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
                                     c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),

@@ -101,6 +101,7 @@ class UnitRangeShard:
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
         self.block_k = self.host_units = self.init_k = self.init_v = None
         self._share = (0, 0)
+        self._token_args = None
         # raw addresses of the buffers the per-token calls pass on (tensor indexing costs microseconds a piece)
         self._p = {name: getattr(self, name).data_ptr() for name in
                    ("k_raw", "k_rot", "v", "score", "q_loc", "q_glb", "qbar", "cos", "sin", "cache", "part_o", "part_lse",
@@ -291,6 +292,42 @@ class UnitRangeShard:
             ids = (ctypes.c_int32 * m)(*changed.keys())
             slots = (ctypes.c_int32 * m)(*changed.values())
             _lib.check(_lib.lib.infllm_slot_table_update(self._p["slot_table"], ids, slots, m, self._stream))
+
+    def run_token(self, q, k, v, out, mb):
+        """One token through infllm_shard_token_run: every launch of it in one call (see the header).  Leaves the
+        merged output in `out` and the retrieval + status words in h_status once the stream has drained."""
+        if self.length - self.t0 >= self.cap:
+            self._compact()
+        a, p = self._token_args, self._p
+        if a is None:
+            a = self._token_args = _lib.ShardToken()
+            for name in ("q_loc", "q_glb", "qbar", "k_raw", "k_rot", "v", "score", "cos", "sin", "cand", "part_o",
+                         "part_lse", "logits", "pack", "lse", "cache"):
+                setattr(a, "d_" + name, p[name])
+            a.d_status, a.h_status = p["d_status"], self.h_status.data_ptr()
+            a.cap, a.n_heads, a.n_kv_heads, a.head_dim, a.dtype = self.cap, self.H, self.HKV, self.D, self.code
+            a.n_local, a.block_size, a.topk, a.unit_bytes, a.max_parts = (self.n_local, self.bs, self.topk,
+                                                                          self.unit_bytes, self.max_parts)
+            a.cand_off, a.cand_slot, a.cand_bytes = mb.cand_off, mb.cand_slot, mb.cand_bytes
+            a.part_off, a.part_slot, a.part_bytes = mb.part_off, mb.part_slot, mb.part_bytes
+            a.flag1_off, a.flag2_off, a.wait_us = mb.flag1, mb.flag2, mb.wait_us
+        E, G, r = self.length + 1, self.world, self.rank
+        wlo = max(E - self.n_local, 0)
+        W = E - wlo
+        lo_, hi_ = wlo + (W * r) // G, wlo + (W * (r + 1)) // G
+        self._share = (lo_, hi_)
+        a.d_q, a.d_k, a.d_vin, a.q_hs, a.k_hs, a.v_hs = q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0)
+        a.at = self.length - self.t0
+        a.d_block_k, a.d_scores, a.d_slot_table = p["block_k"], p["scores_buf"], p["slot_table"]
+        a.n_owned, a.id_lo = self.n_owned, self.lo
+        a.share_at, a.share_len = lo_ - self.t0, hi_ - lo_
+        first = r == 0 and self.n_init > 0
+        a.d_init_k, a.d_init_v, a.init_len = (p["init_k"], p["init_v"], self.n_init) if first else (None, None, 0)
+        last = r == G - 1 and wlo > self.frontier
+        a.ovf_at, a.ovf_len = (self.frontier - self.t0, wlo - self.frontier) if last else (0, 0)
+        a.d_out, a.seq = out.data_ptr(), mb.seq
+        self._stream = _lib.stream_ptr()
+        _lib.check(_lib.lib.infllm_shard_token_run(ctypes.byref(a), mb.handle, self._stream))
 
     def attend_device(self):
         """attend() for a retrieval that exists only on the device so far (d_gids): the owned units are resolved
@@ -501,25 +538,29 @@ class ShardedDecodeMemory:
             import torch.distributed as dist
 
             dist.barrier(group=self.group)
-        s.begin(q, k, v)
-        st = s._stream
         mb.seq += 1
-        err, any_miss = p["d_status"] + 4 * s.topk, p["d_status"] + 4 * s.topk + 4
-        miss_word = p["pack"] + H * (D + 1) * 4
-        _lib.check(lib.infllm_mailbox_put(mb.handle, p["cand"], mb.cand_bytes, mb.cand_off, mb.cand_slot, mb.flag1,
-                                          mb.seq, st))
-        _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag1, mb.seq, mb.wait_us, err, 0, 0, -1, None, miss_word, st))
-        _lib.check(lib.infllm_topk_pairs(mb.local + mb.cand_off, mb.cand_slot // 4, mb.world, s.topk, p["d_status"], err,
-                                         st))
-        s.attend_device()
-        _lib.check(lib.infllm_mailbox_put(mb.handle, p["pack"], mb.part_bytes, mb.part_off, mb.part_slot, mb.flag2,
-                                          mb.seq, st))
-        _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag2, mb.seq, mb.wait_us, err, mb.part_off, mb.part_slot,
-                                           mb.miss_off, any_miss, None, st))
-        out = s.merge_raw(mb.local + mb.part_off, mb.part_slot // 4, mb.world, any_miss)
-        # the retrieval and the two status words, for the host
-        s.h_status.copy_(s.d_status, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if s.n_owned >= s.topk:  # the whole token in one call into the library
+            out = torch.empty((H, D), dtype=s.dtype, device=s.device)
+            s.run_token(q, k, v, out, mb)
+        else:  # fewer owned units than a retrieval takes: the candidate message needs padding; piece by piece
+            s.begin(q, k, v)
+            st = s._stream
+            err, any_miss = p["d_status"] + 4 * s.topk, p["d_status"] + 4 * s.topk + 4
+            miss_word = p["pack"] + H * (D + 1) * 4
+            _lib.check(lib.infllm_mailbox_put(mb.handle, p["cand"], mb.cand_bytes, mb.cand_off, mb.cand_slot, mb.flag1,
+                                              mb.seq, st))
+            _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag1, mb.seq, mb.wait_us, err, 0, 0, -1, None, miss_word,
+                                               st))
+            _lib.check(lib.infllm_topk_pairs(mb.local + mb.cand_off, mb.cand_slot // 4, mb.world, s.topk, p["d_status"],
+                                             err, st))
+            s.attend_device()
+            _lib.check(lib.infllm_mailbox_put(mb.handle, p["pack"], mb.part_bytes, mb.part_off, mb.part_slot, mb.flag2,
+                                              mb.seq, st))
+            _lib.check(lib.infllm_mailbox_wait(mb.handle, mb.flag2, mb.seq, mb.wait_us, err, mb.part_off, mb.part_slot,
+                                               mb.miss_off, any_miss, None, st))
+            out = s.merge_raw(mb.local + mb.part_off, mb.part_slot // 4, mb.world, any_miss)
+            s.h_status.copy_(s.d_status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the retrieval and the two status words are on the host now
         status = s.h_status.tolist()
         ids = [b for b in status[:s.topk] if b >= 0]
         if status[s.topk]:

@@ -293,3 +293,87 @@ extern "C" int infllm_topk_pairs(const int32_t* d_cand, int64_t sender_stride_wo
   INFLLM_LAUNCH_OK("topk_pairs_kernel");
   return INFLLM_OK;
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// One decode token of a unit-range shard as ONE call: every launch of the token — ingest, local scoring and top-k,
+// candidate exchange, global top-k, attention over the owned retrieved units and this rank's share of the window,
+// local merge, partial exchange, final merge with the score accumulation, and the copy of the status words to the
+// host — goes onto `stream` without returning to the caller in between.  The caller fills the argument block once
+// and updates the few fields that move with the token.
+#include "attn_common.cuh"
+
+namespace infllm {
+int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs, const void* v, int64_t v_hs,
+                        void* q_loc, void* q_glb, int64_t qs_hs, float* qbar, void* k_raw, void* k_rot, void* v_out,
+                        int64_t kv_hs, float* score, int64_t score_hs, int n_heads, int n_kv_heads, int head_dim,
+                        const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
+                        int dtype, cudaStream_t s, int32_t* clear);
+int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket);
+}  // namespace infllm
+
+extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbox* mb, void* stream) {
+  if (!a || !mb) return fail(INFLLM_E_BADARG, "shard_token_run: null pointer");
+  if (a->topk <= 0 || a->topk > kMaxSeg - 3 || a->n_owned < a->topk)
+    return fail(INFLLM_E_BADARG, "shard_token_run: needs topk <= n_owned (topk %d, owned %d)", a->topk, a->n_owned);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int H = a->n_heads, HKV = a->n_kv_heads, D = a->head_dim, esz = 2;
+  const int64_t row = a->at * D * esz;
+  char *k_raw = (char*)a->d_k_raw, *k_rot = (char*)a->d_k_rot, *vbuf = (char*)a->d_v;
+  // 1. the token: copies, rotations, query mean, score column
+  INFLLM_TRY(ingest_token_launch(a->d_q, a->q_hs, a->d_k, a->k_hs, a->d_vin, a->v_hs, a->d_q_loc, a->d_q_glb, D, a->d_qbar,
+                                 k_raw + row, k_rot + row, vbuf + row, a->cap * D, a->d_score + a->at, a->cap, H, HKV, D,
+                                 a->d_cos, a->d_sin, a->cap, a->at, a->n_local - 1, a->dtype, s, nullptr));
+  // 2. this rank's candidates: [score bits (topk) | ids (topk)]
+  INFLLM_TRY(block_topk_launch(a->d_block_k, a->n_owned, H * D, a->d_qbar, a->d_scores, a->topk, a->id_lo,
+                               a->d_cand + a->topk, reinterpret_cast<float*>(a->d_cand), a->dtype, s, nullptr));
+  // 3. exchange 1, global top-k
+  int* err = a->d_status + a->topk;
+  int32_t* any_miss = a->d_status + a->topk + 1;
+  int32_t* miss_word = reinterpret_cast<int32_t*>(a->d_pack + (int64_t)H * (D + 1));
+  INFLLM_TRY(infllm_mailbox_put(mb, a->d_cand, a->cand_bytes, a->cand_off, a->cand_slot, a->flag1_off, a->seq, stream));
+  INFLLM_TRY(infllm_mailbox_wait(mb, a->flag1_off, a->seq, a->wait_us, err, 0, 0, -1, nullptr, miss_word, stream));
+  INFLLM_TRY(infllm_topk_pairs(reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4,
+                               mb->world, a->topk, a->d_status, err, stream));
+  // 4. attention: [retrieved units, resolved on the device | window share | sink | overflow]
+  KvSeg segs[kMaxSeg];
+  int32_t qsel[kMaxSeg];
+  int n = 0;
+  for (; n < a->topk; ++n) {
+    segs[n] = {nullptr, nullptr, (int64_t)a->block_size * D, D, a->block_size};
+    qsel[n] = 1;
+  }
+  int logit_seg = -1;
+  if (a->share_len > 0) {
+    logit_seg = n;
+    segs[n] = {k_rot + a->share_at * D * esz, vbuf + a->share_at * D * esz, a->cap * D, D, (int32_t)a->share_len};
+    qsel[n++] = 0;
+  }
+  if (a->init_len > 0) {
+    segs[n] = {a->d_init_k, a->d_init_v, (int64_t)a->init_len * D, D, a->init_len};
+    qsel[n++] = 1;
+  }
+  if (a->ovf_len > 0) {
+    segs[n] = {k_raw + a->ovf_at * D * esz, vbuf + a->ovf_at * D * esz, a->cap * D, D, (int32_t)a->ovf_len};
+    qsel[n++] = 1;
+  }
+  DecodeIndirect ind;
+  ind.ids = a->d_status; ind.table = a->d_slot_table; ind.cache = (const char*)a->d_cache; ind.unit_bytes = a->unit_bytes;
+  ind.n_units = a->topk; ind.first_seg = 0; ind.miss = miss_word; ind.id_lo = a->id_lo; ind.n_owned = a->n_owned;
+  int parts = 0;
+  INFLLM_TRY(attn_decode_launch(a->d_q_loc, a->d_q_glb, D, H, HKV, D, n, segs, qsel, a->d_part_o, a->d_part_lse,
+                                a->max_parts, &parts, logit_seg, a->d_logits, a->dtype, s, 128, &ind, 0));
+  INFLLM_TRY(lse_merge_launch(a->d_part_o, a->d_part_lse, parts, H, D, a->d_pack, D, a->d_pack + (int64_t)H * D,
+                              INFLLM_F32, s, nullptr, 0, nullptr, 0, nullptr));
+  // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores
+  INFLLM_TRY(infllm_mailbox_put(mb, a->d_pack, a->part_bytes, a->part_off, a->part_slot, a->flag2_off, a->seq, stream));
+  INFLLM_TRY(infllm_mailbox_wait(mb, a->flag2_off, a->seq, a->wait_us, err, a->part_off, a->part_slot,
+                                 (int64_t)H * (D + 1) * 4, any_miss, nullptr, stream));
+  const float* parts_g = reinterpret_cast<const float*>((char*)mb->local + a->part_off);
+  INFLLM_TRY(lse_merge_launch(parts_g, parts_g + (int64_t)H * D, mb->world, H, D, a->d_out, D, a->d_lse, a->dtype, s,
+                              a->share_len > 0 ? a->d_logits : nullptr, a->share_len, a->d_score + a->share_at, a->cap,
+                              any_miss, a->part_slot / 4, a->part_slot / 4));
+  // 6. retrieval and status words for the host
+  INFLLM_CUDA_OK(cudaMemcpyAsync(a->h_status, a->d_status, (a->topk + 4) * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  return INFLLM_OK;
+}
