@@ -5,13 +5,16 @@ from .dot_production_attention import CudaMultiStageDotProductionAttention, get_
 from .head_groups import HeadGroupComm
 from .inf_llm import inf_llm_forward
 from .rope import RotaryEmbeddingESM
+from .sink_window import infinite_lm_forward, stream_llm_forward
 from .sharded_decode import PeerMailbox, ShardedDecodeMemory, UnitRangeShard, global_topk, unit_range
 
 ATTN_FORWRAD = {
     "inf-llm": inf_llm_forward,
+    "infinite-lm": infinite_lm_forward,
+    "stream-llm": stream_llm_forward,
 }
 ATTN_FORWARD = ATTN_FORWRAD
 
-__all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward",
+__all__ = ["RotaryEmbeddingESM", "ATTN_FORWRAD", "ATTN_FORWARD", "ContextManager", "inf_llm_forward", "infinite_lm_forward", "stream_llm_forward",
            "CudaMultiStageDotProductionAttention", "get_multi_stage_dot_production_attention",
            "HeadGroupComm", "PeerMailbox", "ShardedDecodeMemory", "UnitRangeShard", "global_topk", "unit_range"]

@@ -64,6 +64,17 @@ class RotaryEmbeddingESM(torch.nn.Module):
     def apply_rotary_pos_emb_one_angle(self, x, index):
         return self._rotate(x, index - 1, 0)
 
+    def apply_rotary_pos_emb(self, x, length, right, cos=None, sin=None):
+        """Rows 0..length-1 of x rotated to positions right-length..right-1 (rope.py:35-47).  The reference takes
+        its cached tables as arguments; this class keeps its own, so `cos` and `sin` are ignored."""
+        if x.size(-2) != length:
+            raise ValueError(f"x has {x.size(-2)} rows, length says {length}")
+        return self._rotate(x, right - length, 1)
+
+    # the reference exposes its cached tables under these names (stream_llm.py:74 passes them back in)
+    _cos_cached = None
+    _sin_cached = None
+
     def forward(self, q, k, seq_dim=-2):
         if seq_dim not in (-2, q.dim() - 2):
             raise ValueError("the sequence dimension must be the second to last")

@@ -110,3 +110,24 @@ def rope_inputs():
     q = torch.from_numpy(rng.standard_normal((2, 7, 128), dtype=np.float32))
     k = torch.from_numpy(rng.standard_normal((2, 300, 128), dtype=np.float32))
     return q, k
+
+
+# ---- sink + window attention (the reference's "infinite-lm" and "stream-llm" attention types): one short
+# configuration fed in calls of these lengths (prefill chunks and single tokens; the cache passes
+# n_local + n_init during the second call)
+SINK_WINDOW = dict(H=4, HKV=2, D=128, n_local=96, n_init=8, base=10000.0, seed=4242, lens=(70, 60, 1, 1, 130, 1, 33))
+
+
+def sink_window_inputs():
+    """One fp32 tensor (L, (H + 2 H_kv) D) per call: the "hidden states" whose column blocks the test's
+    projections slice into q, k and v."""
+    c = SINK_WINDOW
+    rng = np.random.default_rng(c["seed"])
+    width = (c["H"] + 2 * c["HKV"]) * c["D"]
+    return [torch.from_numpy(bf16_round(rng.standard_normal((L, width), dtype=np.float32))) for L in c["lens"]]
+
+
+def sink_window_projections():
+    c = SINK_WINDOW
+    nq, nk = c["H"] * c["D"], c["HKV"] * c["D"]
+    return (lambda x: x[..., :nq], lambda x: x[..., nq:nq + nk], lambda x: x[..., nq + nk:], lambda x: x)

@@ -106,6 +106,28 @@ def record_multi_stage(Attn, rope):
     print("multi_stage: recorded", len(C.MULTI_STAGE_SPECS), "cases + rope")
 
 
+def record_sink_window(rope):
+    """The reference's two sink + window attention types (infinite_lm.py, stream_llm.py) over the calls of
+    cases.SINK_WINDOW: the output of every call."""
+    import importlib
+
+    c = C.SINK_WINDOW
+    pq, pk, pv, po = C.sink_window_projections()
+    out = {}
+    for key, mod, fn in (("infinite", "inf_llm.attention.infinite_lm", "infinite_lm_forward"),
+                         ("stream", "inf_llm.attention.stream_llm", "stream_llm_forward")):
+        forward = getattr(importlib.import_module(mod), fn)(c["n_local"], c["n_init"], fattn=False)
+        r = rope.RotaryEmbeddingESM(c["D"], c["base"], 1.0)
+        past = None
+        with torch.inference_mode():
+            for i, x in enumerate(C.sink_window_inputs()):
+                o, past = forward(None, x[None], x[None], r, True, past, pq, pk, pv, po, c["D"], c["H"], c["HKV"])
+                out[f"{key}_{i}"] = o[0].numpy()
+        out[f"{key}_len"] = np.asarray(past[2])
+    np.savez_compressed(os.path.join(HERE, "sink_window.npz"), **out)
+    print("sink_window: recorded", len(c["lens"]), "calls of both attention types")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -119,6 +141,7 @@ def main():
         record_context_manager(cm, rope, name, case)
     if not args.only:
         record_multi_stage(Attn, rope)
+        record_sink_window(rope)
 
 
 if __name__ == "__main__":

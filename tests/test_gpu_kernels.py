@@ -239,3 +239,32 @@ def test_decode_split_k_and_merge_match_oracle(H, HKV, seg_lens):
 def test_tensor_core_kernels_reported_no_timeout():
     """Collected after the kernel tests of this file: no bounded wait may have run out."""
     assert _L().device_error() == (0, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["infinite-lm", "stream-llm"])
+def test_sink_window_attention_types_match_oracle(kind):
+    """The reference's "infinite-lm" and "stream-llm" attention types on the CUDA kernels (window stage + sink stage
+    with a complement mask that hides pairs), call by call against the CPU oracle."""
+    import cases as C
+
+    from infllm_b200.attention import ATTN_FORWRAD, RotaryEmbeddingESM
+    from oracle.sink_window_oracle import SinkWindowMemory
+
+    c = C.SINK_WINDOW
+    pq, pk, pv, po = C.sink_window_projections()
+    forward = ATTN_FORWRAD[kind](c["n_local"], c["n_init"], fattn=True)
+    pe = RotaryEmbeddingESM(c["D"], c["base"], 1.0)
+    mem = SinkWindowMemory(c["n_local"], c["n_init"], c["D"], c["base"], kind)
+    past = None
+    for i, x in enumerate(C.sink_window_inputs()):
+        L = x.size(0)
+        dx = x.to(DEV).to(torch.bfloat16)[None]
+        o, past = forward(None, dx, dx, pe, True, past, pq, pk, pv, po, c["D"], c["H"], c["HKV"])
+        q = pq(x).view(L, c["H"], c["D"]).permute(1, 0, 2)
+        k = pk(x).view(L, c["HKV"], c["D"]).permute(1, 0, 2)
+        v = pv(x).view(L, c["HKV"], c["D"]).permute(1, 0, 2)
+        want = mem.append(q, k, v).permute(1, 0, 2).reshape(L, -1)
+        diff = (o[0].float().cpu() - want).abs()
+        assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL, f"{kind} call {i}"
+    assert past[2] == mem.length == sum(c["lens"])
