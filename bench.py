@@ -176,6 +176,36 @@ def cpu_steady_state_sample(tokens_at=65536, sample_tokens=2048, repeats=1, thre
     return sample_tokens / best, best, cores
 
 
+def cpu_decode_sample(units=2048, steps=32):
+    """Times the CPU oracle on `steps` decode tokens over a memory of `units` sealed units (seeded random keys,
+    values and representative keys; full window and sink).  Returns (us per token, seconds, cores)."""
+    from oracle.infllm_oracle import OracleContextMemory
+
+    cores = torch.get_num_threads()
+    H, HKV, D = CFG["H"], CFG["HKV"], CFG["D"]
+    g = torch.Generator().manual_seed(98)
+    mem = OracleContextMemory(DEC["n_init"], DEC["n_local"], DEC["bs"], DEC["max_cached"], DEC["topk"], DEC["exc"],
+                              DEC["repr_topk"], CFG["base"], 1.0)
+    tokens_at = DEC["n_init"] + units * DEC["bs"] + DEC["n_local"]
+    mem.length = tokens_at
+    mem.init_len, mem.init_full = DEC["n_init"], True
+    mem.frontier = DEC["n_init"] + units * DEC["bs"]
+    mem.k_log = torch.randn((HKV, tokens_at, D), generator=g)
+    mem.v_log = torch.randn((HKV, tokens_at, D), generator=g)
+    mem.acc = torch.zeros((H, tokens_at))
+    mem.block_k = list(torch.randn((units, H * D), generator=g))
+    toks = [(torch.randn((H, 1, D), generator=g), torch.randn((HKV, 1, D), generator=g), torch.randn((HKV, 1, D), generator=g))
+            for _ in range(steps + 2)]
+    with torch.inference_mode():
+        for q, k, v in toks[:2]:
+            mem.append(q, k, v)
+        t0 = time.perf_counter()
+        for q, k, v in toks[2:]:
+            mem.append(q, k, v)
+        dt = time.perf_counter() - t0
+    return 1e6 * dt / steps, dt, cores
+
+
 SAMPLE_DESC = ("{n} tokens ({eb} exec blocks of 512) of the same layer in steady state at 65536 tokens of context "
                "(479 sealed units, full window), projections included, fp32 torch on the host")
 
@@ -511,6 +541,12 @@ def run_decode(args, rank, world, local_rank):
         store=dict(hits=hits, misses=misses, miss_rate=misses / max(hits + misses, 1),
                    h2d_bytes_per_token_layer=misses * 524288 / max(per_layer, 1)),
         clocks=clocks)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, secs, cores = cpu_decode_sample()
+        line["cpu_baseline"] = dict(value=v, unit="us/token", cores=cores, kind="port", seconds=secs,
+                                    sample="32 decode tokens of one layer over a memory of 2048 units (266368 tokens) "
+                                           "instead of 8192, fp32 torch on the host; the unit scoring is a quarter of "
+                                           "the full size's, the attention the same")
     return line
 
 

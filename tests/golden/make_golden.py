@@ -1,8 +1,8 @@
 """Record golden vectors from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run on a machine that has a checkout of the reference (thunlp/InfLLM):
 
-    python tests/golden/make_golden.py [--ref /path/to/InfLLM]
+    python tests/golden/make_golden.py --ref /path/to/InfLLM
 
 It imports the reference's context_manager / rope / torch multi-stage attention through
 ref_shim (device literals rewritten to cpu, nothing else), runs the cases of cases.py in
@@ -130,7 +130,8 @@ def record_sink_window(rope):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("INFLLM_REFERENCE"), required="INFLLM_REFERENCE" not in os.environ,
+                    help="checkout of the reference (or set INFLLM_REFERENCE)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     cm, rope, Attn = ref_shim.install(args.ref)

@@ -84,7 +84,7 @@ class _Stream:
         pass
 
 
-def install(root="/root/reference"):
+def install(root):
     """Make `import inf_llm.attention...` resolve to the CPU-rewritten reference."""
     if not os.path.isdir(os.path.join(root, "inf_llm")):
         raise FileNotFoundError(f"reference checkout not found at {root}")
