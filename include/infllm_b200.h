@@ -231,6 +231,7 @@ typedef struct infllm_config {
                            *  4: look-ahead units staged by an SM copy kernel instead of one cudaMemcpyAsync each
                            *  8: the two-heads-per-CTA tcgen05 attention kernel (experimental)
                            * 16: one-token appends wait for the retrieved ids before launching the attention
+                           * 32: one-token appends do not fetch ahead the units ranked just below the retrieval
                            * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
                            * at most 8); the cache gets that many times topk spare slots */
 } infllm_config;

@@ -82,6 +82,8 @@ class ContextManager:
             cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
         if os.environ.get("INFLLM_B200_LOOK_DEPTH"):
             cfg.reserved[1] = int(os.environ["INFLLM_B200_LOOK_DEPTH"])  # exec blocks ranked and staged ahead (default 2)
+        if os.environ.get("INFLLM_B200_NO_FETCH_AHEAD", "0") == "1":
+            cfg.reserved[0] |= 32  # debugging aid: one-token appends fetch only what they retrieve
         if os.environ.get("INFLLM_B200_NO_DECODE_SPEC", "0") == "1":
             cfg.reserved[0] |= 16  # debugging aid: one-token appends wait for the retrieved ids before the attention
         for _ in range(self.num_units):

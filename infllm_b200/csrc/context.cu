@@ -183,6 +183,7 @@ struct infllm_ctx {
   int64_t tab_cap = 0;
   bool table_valid = false;                          // false: rebuild from slot_of before the next use
   std::unordered_map<int32_t, int32_t> tab_updates;  // entries changed since the last flush
+  std::unordered_map<int32_t, int32_t> dev_table;    // what the device copy holds since the last flush (resident units)
   int32_t* d_miss = nullptr;                         // set by the attention when a retrieved unit is not cached
   std::vector<void*> slabs;  // pinned host memory
   std::future<void*> slab_future;  // the next slab, being pinned by a helper thread
@@ -214,6 +215,9 @@ struct infllm_ctx {
     bool staged_recorded = false;
   };
   static constexpr int kMaxLookDepth = 8;
+  static constexpr int kDecodeAhead = 16;  // decode: units ranked just below the retrieval are fetched ahead
+  std::vector<std::pair<int32_t, int>> unlisted;  // (unit, slot) fetched ahead, copy not yet known to have landed
+  int decode_k = 0;                        // ids asked of the scorer by the last one-token exec block
   int look_depth = 2;                             // exec blocks ranked ahead (cfg.reserved[1] overrides)
   LookAhead la[kMaxLookDepth + 1];
   std::unordered_map<int32_t, int64_t> staged_for;  // staged unit -> latest exec block that wants it
@@ -388,12 +392,13 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->st_acc, H * g.exc_block_size * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_m, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
-  INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, (std::max(1, g.topk) + infllm_ctx::kDecodeAhead) * sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_miss, sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->d_miss, 0, sizeof(int32_t), s));
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->tickets, 2 * sizeof(unsigned int)));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->tickets, 0, 2 * sizeof(unsigned int), s));
-  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, (std::max(1, g.topk) + infllm_ctx::kDecodeAhead) * sizeof(int32_t),
+                               cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   c->cand_cap = g.topk + (c->look_depth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
   for (auto& l : c->la) {
@@ -543,14 +548,16 @@ int ensure_scores(infllm_ctx* c, int64_t n, cudaStream_t s) {
 // scoring and top-k of n units on stream s.  Alone, one fused launch; with a communicator (KV-head-group sharding:
 // this context holds a slice of the heads) the scores are summed over the ranks between the two halves, so that
 // every rank ranks the same numbers.  `which` picks the communicator of the stream (0 main, 1 look-ahead).
-int score_topk(infllm_ctx* c, int64_t n, const float* qbar, float* scores, int32_t* d_ids, cudaStream_t s, int which) {
+int score_topk(infllm_ctx* c, int64_t n, const float* qbar, float* scores, int32_t* d_ids, cudaStream_t s, int which,
+               int k = 0) {
   const infllm_config& g = c->cfg;
+  if (k <= 0) k = g.topk;
   if (!c->comm)
-    return block_topk_launch(c->block_k, n, (int)c->width, qbar, scores, g.topk, 0, d_ids, nullptr, g.dtype, s,
+    return block_topk_launch(c->block_k, n, (int)c->width, qbar, scores, k, 0, d_ids, nullptr, g.dtype, s,
                              c->tickets + which);
   INFLLM_TRY(block_score_launch(c->block_k, n, (int)c->width, qbar, scores, g.dtype, s));
   INFLLM_TRY(comm_allreduce_sum(c->comm, which, scores, (size_t)n, s));
-  return topk_launch(scores, n, g.topk, 0, d_ids, nullptr, s);
+  return topk_launch(scores, n, k, 0, d_ids, nullptr, s);
 }
 
 // ids of one exec block straight from the device scorer: scoring + top-k, then a host sync on the result
@@ -782,6 +789,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       for (auto it2 = c->staged.begin(); it2 != c->staged.end(); ++it2)
         if (std::find(ids.begin(), ids.end(), it2->first) == ids.end()) { victim = it2; break; }
       c->free_slots.push_back(victim->second);
+      if (track) c->tab_updates[victim->first] = -1;
       c->staged_for.erase(victim->first);
       c->staged.erase(victim);
     }
@@ -844,6 +852,53 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
   return INFLLM_OK;
 }
 
+// Decode: fetch ahead the units the scorer ranked just below the retrieval.  Between consecutive tokens the
+// retrieval mostly trades units across that boundary, so the newcomer is usually on the GPU before it is asked
+// for.  The copies go to the spare slots on the copy stream; a fetched unit is adopted by the cache plan like a
+// look-ahead copy of the prefill, and units that fell out of the band give their slots back.
+int decode_fetch_ahead(infllm_ctx* c, const std::vector<int32_t>& retrieval, const int32_t* cand, int n_cand) {
+  if (n_cand <= 0 && c->staged.empty()) return INFLLM_OK;
+  auto wanted = [&](int32_t b) {
+    for (int i = 0; i < n_cand; ++i)
+      if (cand[i] == b) return true;
+    return std::find(retrieval.begin(), retrieval.end(), b) != retrieval.end();
+  };
+  for (auto it = c->staged.begin(); it != c->staged.end();) {
+    if (!wanted(it->first)) {
+      c->free_slots.push_back(it->second);
+      c->tab_updates[it->first] = -1;
+      c->staged_for.erase(it->first);
+      it = c->staged.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  bool issued = false;
+  for (int i = 0; i < n_cand; ++i) {
+    const int32_t b = cand[i];
+    if (c->slot_of.count(b) || c->staged.count(b)) continue;
+    if (c->free_slots.empty()) break;
+    const int slot = c->free_slots.back();
+    c->free_slots.pop_back();
+    if (!issued && c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn, 0));
+    if (b >= c->d2h_synced_upto) {
+      if (c->d2h_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
+      c->d2h_synced_upto = c->num_blocks;
+    }
+    void* dst = (char*)c->cache + (int64_t)slot * c->unit_bytes;
+    INFLLM_CUDA_OK(cudaMemcpyAsync(dst, c->host_unit(b), c->unit_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    INFLLM_TRY(mark_slot_copy(c, dst));
+    c->staged[b] = slot;
+    c->staged_for[b] = INT64_MAX;
+    c->unlisted.push_back({b, slot});
+    c->counters.h2d_bytes += c->unit_bytes;
+    c->staged_pending = true;
+    issued = true;
+  }
+  if (issued) INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+  return INFLLM_OK;
+}
+
 // bring the device copy of the slot table up to date on stream s
 int flush_table(infllm_ctx* c, cudaStream_t s) {
   if (c->tab_cap < c->block_k_cap || !c->d_slot_table) {
@@ -855,7 +910,10 @@ int flush_table(infllm_ctx* c, cudaStream_t s) {
   if (!c->table_valid) {
     INFLLM_CUDA_OK(cudaMemsetAsync(c->d_slot_table, 0xff, c->tab_cap * sizeof(int32_t), s));  // every entry -1
     c->tab_updates.clear();
+    c->dev_table.clear();
+    c->unlisted.clear();
     for (auto& kv : c->slot_of) c->tab_updates[kv.first] = kv.second;
+    for (auto& kv : c->staged) c->unlisted.push_back({kv.first, kv.second});  // listed again once known to have landed
     c->table_valid = true;
   }
   if (c->tab_updates.empty()) return INFLLM_OK;
@@ -863,6 +921,8 @@ int flush_table(infllm_ctx* c, cudaStream_t s) {
   for (auto& kv : c->tab_updates) {
     ids.push_back(kv.first);
     slots.push_back(kv.second);
+    if (kv.second >= 0) c->dev_table[kv.first] = kv.second;
+    else c->dev_table.erase(kv.first);
   }
   c->tab_updates.clear();
   return slot_table_update_launch(c->d_slot_table, ids.data(), slots.data(), (int)ids.size(), s);
@@ -1031,6 +1091,19 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
   }
 
+  if (L > 1) {  // units a previous one-token append fetched ahead are not wanted by a prefill's look-ahead
+    for (auto it = c->staged.begin(); it != c->staged.end();) {
+      if (c->staged_for[it->first] == INT64_MAX) {
+        c->free_slots.push_back(it->second);
+        c->staged_for.erase(it->first);
+        it = c->staged.erase(it);
+      } else {
+        ++it;
+      }
+    }
+    c->unlisted.clear();
+    c->table_valid = false;
+  }
   std::vector<int32_t> ids;
   for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));
@@ -1061,13 +1134,28 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       INFLLM_TRY(ensure_scores(c, c->num_blocks, s));
       {
         ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
-        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, c->d_topk, s, 0));
+        // the scorer also names the units ranked just below the retrieval: they are fetched ahead (below)
+        c->decode_k = (int)std::min<int64_t>(std::min<int64_t>(g.topk + infllm_ctx::kDecodeAhead, 64), c->num_blocks);
+        if (c->decode_k < g.topk || (g.reserved[0] & 32)) c->decode_k = g.topk;
+        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, c->d_topk, s, 0, c->decode_k));
       }
       INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
       INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
-      INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost,
+      INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, c->decode_k * sizeof(int32_t), cudaMemcpyDeviceToHost,
                                      c->mail_stream));
       INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, c->mail_stream));
+      // units fetched ahead whose copies have landed since become visible to the attention's slot table
+      for (auto it = c->unlisted.begin(); it != c->unlisted.end();) {
+        auto st = c->staged.find(it->first);
+        if (st == c->staged.end() || st->second != it->second) {
+          it = c->unlisted.erase(it);  // adopted or dropped meanwhile
+        } else if (cudaEventQuery(c->slot_ev[it->second]) == cudaSuccess) {
+          c->tab_updates[it->first] = it->second;
+          it = c->unlisted.erase(it);
+        } else {
+          ++it;
+        }
+      }
       INFLLM_TRY(flush_table(c, s));
     }
     const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
@@ -1137,14 +1225,15 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         }
         ids.assign(c->h_topk, c->h_topk + g.topk);
         std::vector<int32_t> missed;
-        for (int32_t b : ids)
-          if (!c->slot_of.count(b)) missed.push_back(b);
+        for (int32_t b : ids)  // what the attention above could not resolve: not in the device table it read
+          if (!c->dev_table.count(b)) missed.push_back(b);
         const bool all_hit = missed.empty();
         {
           HostTimer ht(&c->host_us[1]);
           INFLLM_TRY(plan_and_refill(c, ids, eb, s, true));
         }
         c->trace_topk.push_back(ids);
+        INFLLM_TRY(decode_fetch_ahead(c, ids, c->h_topk + g.topk, c->decode_k - g.topk));
         if (!all_hit) {
           // the chunks of the missing units carry weight zero so far and the merge above did nothing: run those
           // units now that their copies are ordered ahead on the stream, then merge everything
@@ -1385,6 +1474,8 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->slot_of.clear();
   c->table_valid = false;
   c->tab_updates.clear();
+  c->dev_table.clear();
+  c->unlisted.clear();
   c->free_slots.clear();
   for (int i = c->cfg.max_cached_block + c->look_depth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->staged.clear();

@@ -1,6 +1,6 @@
 // Retrieval kernels: memory-unit scoring + top-k, and representative-key selection at sealing.
 //
-// block_score_topk_kernel  k <= 64 over <= 8192 units, the usual case: HBM-streaming GEMV (one warp per
+// block_score_topk_kernel  k <= 64 over <= 16384 units, the usual case: HBM-streaming GEMV (one warp per
 //                     representative-key row, 16-byte loads, query mean staged in shared memory, fp32
 //                     accumulation) whose last CTA ranks the scores (threshold from the maxima of small
 //                     groups, rank sort of the few candidates).
@@ -208,15 +208,15 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Fast path for the usual sizes (k <= 64 over at most 8192 scores), one CTA of 1024 threads.
+// Fast path for the usual sizes (k <= 64 over at most 16384 scores), one CTA of 1024 threads.
 //
 // Every score becomes a 64-bit key: (order-preserving bits of the score) << 32 | ~id, so that a larger key
 // means "ranks earlier" (higher score, then lower id) and no two keys are equal.  Thread t keeps the keys of
-// scores t, t + 1024, ... in registers; four neighbouring threads form a group of 32 scores.
+// scores t, t + 1024, ... in registers; four neighbouring threads form a group of 64 scores.
 //   1. tau = the k-th largest of the 256 group maxima, found by counting for every group how many maxima are
 //      larger.  tau is a lower bound of the k-th largest key overall, and exactly k groups hold a maximum
 //      >= tau.
-//   2. every key >= tau is a candidate: at most 32k of them (a few more than k unless the scores are laid out
+//   2. every key >= tau is a candidate: at most 64k of them (a few more than k unless the scores are laid out
 //      adversarially), appended to a shared list.
 //   3. rank sort of the candidates; the first k leave in order.
 // No loop waits on data of another CTA.
@@ -226,11 +226,11 @@ __device__ long long g_topk_stamps[16];
 #else
 #define TK_STAMP(i) do { } while (0)
 #endif
-constexpr int kFastItems = 8;
+constexpr int kFastItems = 16;                   // scores per thread: up to 16384 units (2M tokens of 128-token units)
 constexpr int kFastMaxK = 64;
 constexpr int kFastMaxN = kFastItems * kTopkThreads;
 constexpr int kFastGroups = kTopkThreads / 4;
-constexpr int kFastCand = 32 * kFastMaxK;
+constexpr int kFastCand = 4 * kFastItems * kFastMaxK;  // k groups of 4 threads x kFastItems scores
 
 __device__ __forceinline__ unsigned long long topk_key(float v, int id) {
   if (!(v == v)) v = -INFINITY;  // NaN ranks with -inf
@@ -281,7 +281,7 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
     }
   __syncthreads();
   TK_STAMP(6);
-  const int nc = *s_cnt < kFastCand ? *s_cnt : kFastCand;  // k <= nc <= 32k
+  const int nc = *s_cnt < kFastCand ? *s_cnt : kFastCand;  // k <= nc <= 64k
   // ---- 3. rank of every candidate = how many candidates rank before it
   for (int c = tid; c < nc; c += kTopkThreads) {
     const unsigned long long mine = cand[c];
@@ -472,9 +472,18 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
   if (k <= kFastMaxK && n <= kFastMaxN) {
     // one launch when the caller lends a ticket counter, else scoring and ranking back to back
     const unsigned grid = (unsigned)std::min<int64_t>(n, 148);
+    const size_t smem = width * sizeof(float);
     INFLLM_DISPATCH_DTYPE(dtype, T, {
-      block_score_topk_kernel<T><<<grid, kTopkThreads, width * sizeof(float), s>>>(
-          (const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores, ticket);
+      auto kern = block_score_topk_kernel<T>;
+      // the kernel's static shared memory (ranking scratch) plus the query vector passes the 48 KiB a launch gets
+      // without asking
+      static size_t allowed = 0;  // per instantiation: the largest dynamic size granted so far
+      if (smem > allowed) {
+        INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        allowed = smem;
+      }
+      kern<<<grid, kTopkThreads, smem, s>>>((const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores,
+                                           ticket);
     });
     INFLLM_LAUNCH_OK("block_score_topk_kernel");
     if (!ticket) {

@@ -131,3 +131,9 @@ def sink_window_projections():
     c = SINK_WINDOW
     nq, nk = c["H"] * c["D"], c["HKV"] * c["D"]
     return (lambda x: x[..., :nq], lambda x: x[..., nq:nq + nk], lambda x: x[..., nq + nk:], lambda x: x)
+
+
+# ---- perhead=True (context_manager.py:690-704, 810-811): every query head is a unit of its own, with its own
+# retrieval, cache and representative keys; its KV head is the one of its group
+PERHEAD = dict(H=4, HKV=2, D=128, n_init=64, n_local=256, bs=128, max_cached=4, topk=2, exc=128, repr_topk=2,
+               base=1000000.0, lens=[900, 1, 1, 260], seed=31, strategy="lru", decay=None, qscale=1.0)

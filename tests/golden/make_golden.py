@@ -106,6 +106,43 @@ def record_multi_stage(Attn, rope):
     print("multi_stage: recorded", len(C.MULTI_STAGE_SPECS), "cases + rope")
 
 
+def record_perhead(cm, rope):
+    """cases.PERHEAD through the reference with perhead=True: outputs and the retrieval of every head (unit)."""
+    case = C.PERHEAD
+    inputs = C.make_inputs(case)
+    r = rope.RotaryEmbeddingESM(case["D"], case["base"], 1.0)
+    mgr = cm.ContextManager(r, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
+                            case["exc"], case["decay"], False, case["repr_topk"], case["strategy"], None,
+                            False, False, False, True)
+    topks = []
+    orig_topk = cm.ContextManager.calc_block_topk
+
+    def spy_topk(self, gq):
+        ret = orig_topk(self, gq)
+        topks.append([list(u) for u in ret])  # one list per unit (= head)
+        return ret
+
+    cm.ContextManager.calc_block_topk = spy_topk
+    outs = []
+    try:
+        with torch.inference_mode():
+            for q, k, v in inputs:
+                o = mgr.append(q[None], k[None], v[None], q[None], k[None], v[None])
+                outs.append(o[0].permute(1, 0, 2).contiguous())  # (L, H, D)
+    finally:
+        cm.ContextManager.calc_block_topk = orig_topk
+    o = torch.cat(outs, dim=0)
+    tk = np.full((len(topks), case["H"], case["topk"]), -1, dtype=np.int32)
+    for i, per_unit in enumerate(topks):
+        for u, t in enumerate(per_unit):
+            tk[i, u, : len(t)] = t
+    rows = C.sample_rows(o.shape[0])
+    np.savez_compressed(os.path.join(HERE, "perhead.npz"), digest=C.inputs_digest(inputs), topk=tk, o16_rows=rows.numpy(),
+                        o16=o[rows].to(torch.float16).numpy(), o_proj=C.project_rows(o).numpy(),
+                        n_blocks=int(mgr.num_global_block))
+    print("perhead:", len(topks), "exec blocks,", mgr.num_global_block, "sealed per head, out", tuple(o.shape))
+
+
 def record_sink_window(rope):
     """The reference's two sink + window attention types (infinite_lm.py, stream_llm.py) over the calls of
     cases.SINK_WINDOW: the output of every call."""
@@ -143,6 +180,7 @@ def main():
     if not args.only:
         record_multi_stage(Attn, rope)
         record_sink_window(rope)
+        record_perhead(cm, rope)
 
 
 if __name__ == "__main__":

@@ -266,3 +266,26 @@ def test_unit_range_sharded_decode_matches_oracle(world):
     want_rows = torch.stack(ora.block_k[n_units:])
     got_rows = shards[-1].block_k[shards[-1].n_owned - 2:shards[-1].n_owned].float().cpu()
     assert ((got_rows - want_rows).abs().amax(dim=1) < 2e-2).float().mean() >= 0.5
+
+
+def test_perhead_units_match_oracle():
+    """perhead=True (context_manager.py:690-704): every query head runs as a unit of its own."""
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    case = C.PERHEAD
+    g = case["H"] // case["HKV"]
+    pe = RotaryEmbeddingESM(case["D"], case["base"], 1.0)
+    cm = ContextManager(pe, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"], case["exc"], None,
+                        False, case["repr_topk"], perhead=True)
+    oracles = [FollowerOracle(case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"], case["exc"],
+                              case["repr_topk"], case["base"], 1.0) for _ in range(case["H"])]
+    for q, k, v in C.make_inputs(case):
+        dq, dk, dv = (t[None].to(DEV).to(torch.bfloat16) for t in (q, k, v))
+        got = cm.append(dq, dk, dv, dq, dk, dv)[0].float().cpu()
+        for h, ora in enumerate(oracles):
+            ora.forced += cm.last_topk(h)
+            want = ora.append(q[h:h + 1], k[h // g:h // g + 1], v[h // g:h // g + 1])
+            diff = (got[h:h + 1] - want).abs()
+            assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL, f"head {h}"
+    assert all(len({i for i, _, _ in ora.mismatches}) <= 2 for ora in oracles)
+    assert cm.size() == sum(case["lens"])

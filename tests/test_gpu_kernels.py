@@ -123,7 +123,7 @@ def test_attention_row_without_visible_keys_gives_zero():
 
 # -------------------------------------------------------------------------- retrieval kernels
 @pytest.mark.parametrize("n,k,width", [(5, 5, 1024), (40, 4, 4096), (991, 16, 4096), (8192, 32, 4096), (3000, 64, 512),
-                                       (5000, 100, 512), (20000, 16, 256)])
+                                       (5000, 100, 512), (20000, 16, 256), (12345, 48, 512), (16384, 64, 256)])
 def test_block_topk_matches_torch(n, k, width):
     L = _L()
     g = torch.Generator().manual_seed(n + k)

@@ -69,3 +69,26 @@ def test_lru_tie_order():
     t.entries = {7: 3, 2: 3, 9: 1, 5: 3}
     assert t.plan([5, 11, 12, 13]) == [9, 7, 2]
     assert list(t.entries) == [5]
+
+
+def test_perhead_matches_reference():
+    """perhead=True: one oracle per query head (a unit of its own with the KV head of its group) against the
+    reference's recording."""
+    case = C.PERHEAD
+    z = np.load(os.path.join(GOLDEN, "perhead.npz"))
+    inputs = C.make_inputs(case)
+    assert C.inputs_digest(inputs) == str(z["digest"])
+    g = case["H"] // case["HKV"]
+    mems = [O.OracleContextMemory(case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
+                                  case["exc"], case["repr_topk"], case["base"], 1.0) for _ in range(case["H"])]
+    outs = []
+    for q, k, v in inputs:
+        per_head = [mems[h].append(q[h:h + 1], k[h // g:h // g + 1], v[h // g:h // g + 1]) for h in range(case["H"])]
+        outs.append(torch.cat(per_head, dim=0).permute(1, 0, 2))
+    o = torch.cat(outs, dim=0)
+    for h, mem in enumerate(mems):
+        assert len(mem.trace) == z["topk"].shape[0]
+        for i, tr in enumerate(mem.trace):
+            assert tr.topk_raw == [int(x) for x in z["topk"][i, h] if x >= 0], f"head {h}, exec block {i}"
+        assert mem.num_blocks == int(z["n_blocks"])
+    np.testing.assert_allclose(C.project_rows(o).numpy(), z["o_proj"], rtol=0, atol=2e-4)
