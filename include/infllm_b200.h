@@ -39,7 +39,9 @@ extern "C" {
 #define INFLLM_F32 2 /* accepted only as the output type of infllm_lse_merge */
 
 #define INFLLM_CACHE_LRU 0   /* cache_strategy "lru"   (context_manager.py:504-508) */
-#define INFLLM_CACHE_LRU_S 1 /* cache_strategy "lru-s" (context_manager.py:454-470, 510-513) */
+#define INFLLM_CACHE_LRU_S 1 /* cache_strategy "lru-s" (context_manager.py:454-470, 510-513): a cached unit's stamp is a
+                              * decayed sum of the attention mass its keys received; every exec block then waits for
+                              * the device, so look-ahead retrieval and attend-ahead decode are off */
 
 /* mask modes of one attention stage (torch_impl.py:60-78) */
 #define INFLLM_MASK_NONE 0
@@ -221,7 +223,7 @@ typedef struct infllm_config {
   int32_t n_init, n_local, block_size, max_cached_block, topk, exc_block_size, repr_topk;
   int32_t cache_strategy; /* INFLLM_CACHE_* */
   int32_t dtype;          /* INFLLM_BF16 / INFLLM_FP16 */
-  float score_decay;      /* lru-s only */
+  double score_decay;     /* lru-s only; a double because the reference multiplies Python floats by it */
   float rope_base, rope_scale;
   int32_t device;         /* CUDA device ordinal */
   int32_t shard_rank, shard_world; /* unit-range sharding of the store; 0,1 = not sharded */
@@ -395,6 +397,14 @@ int infllm_shard_token_run(const infllm_shard_token* args, infllm_mailbox* mailb
 /* One memory unit from the pinned host store into a cache slot, asynchronously on `stream`: MemoryUnit.load's
  * host-to-device copy (context_manager.py:57-71) for callers that keep their own cache. */
 int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes, void* stream);
+
+/* Persistence (the reference keeps a layer's memory only live, in past_key_values, greedy_search.py:99):
+ * infllm_ctx_save writes the whole memory of a context — sink, sealed units, representative keys, un-sealed tokens
+ * with their accumulated scores, LRU table and counters — to a file; infllm_ctx_load brings it back into a
+ * context created with the same configuration, refills the cache as the LRU table lists it, and the next append
+ * continues as if nothing had happened.  Both synchronise `stream`. */
+int infllm_ctx_save(infllm_ctx* ctx, const char* path, void* stream);
+int infllm_ctx_load(infllm_ctx* ctx, const char* path, void* stream);
 
 /* ----------------------------------------------------- host logic, GPU-free
  * The LRU table alone (context_manager.py:246-265, 495-515): dict-ordered ids with stamps.

@@ -36,7 +36,7 @@ class Config(ctypes.Structure):
         ("n_init", c_int32), ("n_local", c_int32), ("block_size", c_int32), ("max_cached_block", c_int32),
         ("topk", c_int32), ("exc_block_size", c_int32), ("repr_topk", c_int32),
         ("cache_strategy", c_int32), ("dtype", c_int32),
-        ("score_decay", c_float), ("rope_base", c_float), ("rope_scale", c_float),
+        ("score_decay", c_double), ("rope_base", c_float), ("rope_scale", c_float),
         ("device", c_int32), ("shard_rank", c_int32), ("shard_world", c_int32),
         ("reserved", c_int32 * 6),
     ]
@@ -130,6 +130,8 @@ SIGNATURES = {
     "infllm_comm_create": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
     "infllm_comm_destroy": (c_int, [c_void_p]),
     "infllm_ctx_set_comm": (c_int, [c_void_p, c_void_p]),
+    "infllm_ctx_save": (c_int, [c_void_p, c_char_p, c_void_p]),
+    "infllm_ctx_load": (c_int, [c_void_p, c_char_p, c_void_p]),
     "infllm_ctx_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),
     "infllm_ctx_destroy": (c_int, [c_void_p]),
     "infllm_ctx_reset": (c_int, [c_void_p]),

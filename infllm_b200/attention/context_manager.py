@@ -4,6 +4,7 @@ The state and the exec-block loop live in libinfllm_b200 (one native context per
 see include/infllm_b200.h); this class validates arguments the way the reference does, feeds
 tensors in and exposes the reference's observable attributes."""
 import ctypes
+import json
 import os
 from typing import Optional
 
@@ -236,6 +237,37 @@ class ContextManager:
             self._ctx[0], ts[0].size(0), ts[0].data_ptr(), ts[1].data_ptr(), ts[2].data_ptr(), ts[3].data_ptr(),
             ts[4].data_ptr(), ts[5].data_ptr(), _lib.stream_ptr(self.device)))
         self.length = self.info()["length"]
+
+    # -- persistence (the reference keeps the memory only live, in past_key_values)
+    def save(self, path):
+        """Write the whole memory (sink, sealed units, representative keys, un-sealed tokens, LRU tables) to
+        `path`.json plus one `path`.u<i> file per unit; load() on a manager built with the same arguments resumes
+        the stream exactly where this one stands."""
+        if not self.initialized:
+            raise RuntimeError("nothing to save: the memory has seen no tokens")
+        meta = dict(batch=self.batch_size, heads=self.num_heads, heads_kv=self.num_heads_kv, dim=self.dim_head,
+                    dtype=str(self.dtype).split(".")[-1], length=self.length, units=self.num_units)
+        stream = _lib.stream_ptr(self.device)
+        for i, h in enumerate(self._ctx):
+            _lib.check(_lib.lib.infllm_ctx_save(h, f"{path}.u{i}".encode(), stream))
+        with open(f"{path}.json", "w") as f:
+            json.dump(meta, f)
+
+    def load(self, path, device=None):
+        with open(f"{path}.json") as f:
+            meta = json.load(f)
+        dtype = getattr(torch, meta["dtype"])
+        if not self.initialized:
+            dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+            self._init(torch.empty((meta["batch"], meta["heads"], 1, meta["dim"]), dtype=dtype, device=dev),
+                       torch.empty((meta["batch"], meta["heads_kv"], 1, meta["dim"]), dtype=dtype, device=dev))
+        if (self.batch_size, self.num_heads, self.num_heads_kv, self.dim_head, self.dtype, self.num_units) != (
+                meta["batch"], meta["heads"], meta["heads_kv"], meta["dim"], dtype, meta["units"]):
+            raise ValueError("the saved memory has other shapes than this manager")
+        stream = _lib.stream_ptr(self.device)
+        for i, h in enumerate(self._ctx):
+            _lib.check(_lib.lib.infllm_ctx_load(h, f"{path}.u{i}".encode(), stream))
+        self.length = meta["length"]
 
     def reset(self):
         for h in self._ctx:

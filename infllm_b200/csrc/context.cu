@@ -164,6 +164,8 @@ struct infllm_ctx {
   float* lse = nullptr;      // (H, exc)
   float *st_acc = nullptr, *st_m = nullptr, *st_l = nullptr;  // carried attention state (H, exc, D) / (H, exc)
   float* scores = nullptr;   // (scores_cap) unit scores
+  float* unit_prob = nullptr;    // lru-s: (H, topk * block_size) attention mass of the retrieved units' keys
+  float* h_unit_prob = nullptr;  // its pinned host copy
   int64_t scores_cap = 0;
   int32_t* d_topk = nullptr; // (topk)
   infllm_comm* comm = nullptr;  // KV-head-group sharding: the retrieval scores are summed over the ranks
@@ -1032,6 +1034,38 @@ int local_scores(infllm_ctx* c, cudaStream_t s, int64_t st, int64_t ks, int64_t 
                             INFLLM_MASK_WINDOW, off, g.n_local, c->lse, tb.score + tok, tb.cap, 1, g.dtype, s);
 }
 
+// lru-s (context_manager.py:454-470): every cached unit's score decays, and each retrieved unit gains the attention
+// mass its keys received from this exec block's queries, summed over heads.  The host needs the sums before it plans
+// the next exec block, as in the reference (a blocking copy there too).
+int unit_score_update(infllm_ctx* c, const std::vector<int32_t>& ids, const char* qglb, int64_t lq, cudaStream_t s) {
+  const infllm_config& g = c->cfg;
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads, bs = g.block_size;
+  const int64_t cols = (int64_t)g.topk * bs, n = (int64_t)ids.size();
+  if (!c->unit_prob) {
+    INFLLM_CUDA_OK(cudaMalloc((void**)&c->unit_prob, H * cols * sizeof(float)));
+    INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_unit_prob, H * cols * sizeof(float), cudaHostAllocDefault));
+  }
+  for (int64_t i = 0; i < n; ++i) {
+    const char* base = (const char*)c->cache + (int64_t)c->slot_of[ids[i]] * c->unit_bytes;
+    INFLLM_TRY(attn_colsum_launch(qglb, c->sub_max * D, D, base, bs * D, D, (int)H, (int)HKV, lq, bs, (int)D,
+                                  INFLLM_MASK_NONE, 0, 0, c->lse, c->unit_prob + i * bs, cols, 0, g.dtype, s));
+  }
+  INFLLM_CUDA_OK(cudaMemcpy2DAsync(c->h_unit_prob, n * bs * sizeof(float), c->unit_prob, cols * sizeof(float),
+                                   n * bs * sizeof(float), H, cudaMemcpyDeviceToHost, s));
+  INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  c->lru.scale(g.score_decay);
+  for (int64_t i = 0; i < n; ++i) {
+    float sum = 0.f;  // the reference sums in fp32: over a unit's keys, then over the heads
+    for (int64_t h = 0; h < H; ++h) {
+      float row = 0.f;
+      for (int64_t j = 0; j < bs; ++j) row += c->h_unit_prob[(h * n + i) * bs + j];
+      sum += row;
+    }
+    c->lru.add(ids[i], (double)sum);
+  }
+  return INFLLM_OK;
+}
+
 // one internal call of at most sub_max tokens whose exec-block boundaries coincide with the caller's
 int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const char* k, int64_t k_hs, int64_t k_ts,
                const char* v, int64_t v_hs, int64_t v_ts, char* out, int64_t o_hs, int64_t o_ts, int64_t L,
@@ -1356,6 +1390,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       }
       }
     }
+    if (g.cache_strategy == INFLLM_CACHE_LRU_S && !ids.empty()) INFLLM_TRY(unit_score_update(c, ids, qglb_eb, lq, s));
     // ev_attn: behind this exec block's attention; ev_attn_prev: behind the previous one's
     std::swap(c->ev_attn, c->ev_attn_prev);
     c->attn_prev_recorded = c->attn_recorded;
@@ -1436,12 +1471,15 @@ extern "C" int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out) {
   if (g.repr_topk > g.block_size) return fail(INFLLM_E_BADARG, "ctx_create: repr_topk %d > block_size %d", g.repr_topk, g.block_size);
   if (g.block_size % 8) return fail(INFLLM_E_BADARG, "ctx_create: block_size %d must be a multiple of 8", g.block_size);
   if (g.dtype != INFLLM_BF16 && g.dtype != INFLLM_FP16) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: dtype code %d", g.dtype);
-  if (g.cache_strategy != INFLLM_CACHE_LRU)
-    return fail(INFLLM_E_UNSUPPORTED, "ctx_create: cache strategy code %d (only lru is built)", g.cache_strategy);
+  if (g.cache_strategy != INFLLM_CACHE_LRU && g.cache_strategy != INFLLM_CACHE_LRU_S)
+    return fail(INFLLM_E_UNSUPPORTED, "ctx_create: cache strategy code %d", g.cache_strategy);
   if (g.topk > 1024) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: topk %d > 1024", g.topk);
   infllm_ctx* c = new (std::nothrow) infllm_ctx();
   if (!c) return fail(INFLLM_E_NOMEM, "ctx_create: out of host memory");
   c->cfg = g;
+  // lru-s: the cache plan of an exec block depends on the attention of the one before it (context_manager.py:
+  // 454-470), so nothing is ranked, staged or attended ahead of the host
+  if (g.cache_strategy == INFLLM_CACHE_LRU_S) c->cfg.reserved[0] |= 2 | 16 | 32;
   c->esz = 2;
   c->width = (int64_t)g.n_heads * g.head_dim;
   c->unit_elems = (int64_t)g.n_kv_heads * g.block_size * g.head_dim;
@@ -1503,6 +1541,8 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     if (c->block_k) cudaFreeAsync(c->block_k, nullptr);
     if (c->scores) cudaFreeAsync(c->scores, nullptr);
     if (c->d_slot_table) cudaFreeAsync(c->d_slot_table, nullptr);
+    if (c->unit_prob) cudaFree(c->unit_prob);
+    if (c->h_unit_prob) cudaFreeHost(c->h_unit_prob);
     if (c->h_topk) cudaFreeHost(c->h_topk);
     if (c->h_spec) cudaFreeHost(c->h_spec);
     for (auto& l : c->la) {
@@ -1799,5 +1839,141 @@ extern "C" int infllm_ctx_set_comm(infllm_ctx* c, infllm_comm* comm) {
   if (!c) return fail(INFLLM_E_BADARG, "ctx_set_comm: null context");
   if (c->length != 0) return fail(INFLLM_E_BADARG, "ctx_set_comm: the context already holds tokens");
   c->comm = comm;
+  return INFLLM_OK;
+}
+
+// ------------------------------------------------------------------------------------------- persistence
+// The reference keeps a layer's memory only live, inside past_key_values (inf_llm/utils/greedy_search.py:99);
+// these two calls write it to a file and bring it back, so that a session can be resumed in another process.
+// File: a header of int64 words, then the LRU table (id, stamp) in dict order, the sink, the representative keys,
+// the un-sealed tokens (raw keys, values, accumulated scores) and the sealed units as the host store holds them.
+// The rotated keys are not stored: they are rotated anew on the next append.
+namespace {
+constexpr int64_t kStateMagic = 0x314d454d4c464e49ll;  // "INFLMEM1"
+
+bool put(FILE* f, const void* p, size_t n) { return n == 0 || fwrite(p, 1, n, f) == n; }
+bool get(FILE* f, void* p, size_t n) { return n == 0 || fread(p, 1, n, f) == n; }
+}  // namespace
+
+extern "C" int infllm_ctx_save(infllm_ctx* c, const char* path, void* stream) {
+  if (!c || !path) return fail(INFLLM_E_BADARG, "ctx_save: null pointer");
+  if (!c->initialized) return fail(INFLLM_E_BADARG, "ctx_save: the context holds nothing yet");
+  const infllm_config& g = c->cfg;
+  cudaStream_t s = (cudaStream_t)stream;
+  INFLLM_CUDA_OK(cudaSetDevice(g.device));
+  // every copy-out of a sealed unit must have landed in the host store
+  INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  INFLLM_CUDA_OK(cudaStreamSynchronize(c->d2h_stream));
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
+  const int64_t live = c->length - c->frontier, n_lru = (int64_t)c->lru.items.size();
+  FILE* f = fopen(path, "wb");
+  if (!f) return fail(INFLLM_E_BADARG, "ctx_save: cannot open %s", path);
+  const int64_t hdr[16] = {kStateMagic, H, HKV, D, g.n_init, g.n_local, g.block_size, g.dtype, c->length, c->frontier,
+                           c->num_blocks, c->init_len, c->init_full ? 1 : 0, c->load_count, n_lru, g.cache_strategy};
+  bool ok = put(f, hdr, sizeof(hdr));
+  for (auto& kv : c->lru.items) {
+    const int64_t id = kv.first;
+    ok = ok && put(f, &id, sizeof(id)) && put(f, &kv.second, sizeof(double));
+  }
+  std::vector<char> buf;
+  auto dump2d = [&](const void* dev, int64_t pitch, int64_t width, int64_t rows) -> bool {  // strided device rows
+    if (width * rows == 0) return true;
+    buf.resize((size_t)(width * rows));
+    if (cudaMemcpy2D(buf.data(), width, dev, pitch, width, rows, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+    return put(f, buf.data(), buf.size());
+  };
+  ok = ok && dump2d(c->init_k, c->init_cap * D * c->esz, c->init_len * D * c->esz, HKV);
+  ok = ok && dump2d(c->init_v, c->init_cap * D * c->esz, c->init_len * D * c->esz, HKV);
+  ok = ok && dump2d(c->block_k, c->width * c->esz, c->width * c->esz, c->num_blocks);
+  const TokenBuffers& tb = c->tb;
+  const int64_t off = (c->frontier - tb.t0) * D * c->esz, pitch = tb.cap * D * c->esz;
+  ok = ok && dump2d((char*)tb.k_raw + off, pitch, live * D * c->esz, HKV);
+  ok = ok && dump2d((char*)tb.v + off, pitch, live * D * c->esz, HKV);
+  ok = ok && dump2d(tb.score + (c->frontier - tb.t0), tb.cap * sizeof(float), live * sizeof(float), H);
+  for (int64_t b = 0; ok && b < c->num_blocks; ++b) ok = put(f, c->host_unit(b), (size_t)c->unit_bytes);
+  ok = (fclose(f) == 0) && ok;
+  if (!ok) return fail(INFLLM_E_CUDA, "ctx_save: writing %s failed", path);
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
+  if (!c || !path) return fail(INFLLM_E_BADARG, "ctx_load: null pointer");
+  const infllm_config& g = c->cfg;
+  cudaStream_t s = (cudaStream_t)stream;
+  INFLLM_CUDA_OK(cudaSetDevice(g.device));
+  FILE* f = fopen(path, "rb");
+  if (!f) return fail(INFLLM_E_BADARG, "ctx_load: cannot open %s", path);
+  int64_t hdr[16];
+  if (!get(f, hdr, sizeof(hdr)) || hdr[0] != kStateMagic) {
+    fclose(f);
+    return fail(INFLLM_E_BADARG, "ctx_load: %s is not a saved context memory", path);
+  }
+  if (hdr[1] != g.n_heads || hdr[2] != g.n_kv_heads || hdr[3] != g.head_dim || hdr[4] != g.n_init || hdr[5] != g.n_local ||
+      hdr[6] != g.block_size || hdr[7] != g.dtype || hdr[15] != g.cache_strategy) {
+    fclose(f);
+    return fail(INFLLM_E_BADARG, "ctx_load: %s was saved with another configuration", path);
+  }
+  if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
+  INFLLM_TRY(infllm_ctx_reset(c));
+  const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
+  const int64_t length = hdr[8], frontier = hdr[9], n_units = hdr[10], init_len = hdr[11], n_lru = hdr[14];
+  const int64_t live = length - frontier;
+  bool ok = true;
+  std::vector<std::pair<int32_t, double>> lru;
+  for (int64_t i = 0; ok && i < n_lru; ++i) {
+    int64_t id;
+    double stamp;
+    ok = get(f, &id, sizeof(id)) && get(f, &stamp, sizeof(stamp));
+    lru.push_back({(int32_t)id, stamp});
+  }
+  std::vector<char> buf;
+  auto fill2d = [&](void* dev, int64_t pitch, int64_t width, int64_t rows) -> bool {
+    if (width * rows == 0) return true;
+    buf.resize((size_t)(width * rows));
+    if (!get(f, buf.data(), buf.size())) return false;
+    return cudaMemcpy2D(dev, pitch, buf.data(), width, width, rows, cudaMemcpyHostToDevice) == cudaSuccess;
+  };
+  ok = ok && fill2d(c->init_k, c->init_cap * D * c->esz, init_len * D * c->esz, HKV);
+  ok = ok && fill2d(c->init_v, c->init_cap * D * c->esz, init_len * D * c->esz, HKV);
+  if (ok && ensure_block_k(c, std::max<int64_t>(n_units, 1), s) != INFLLM_OK) ok = false;
+  if (ok) INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  ok = ok && fill2d(c->block_k, c->width * c->esz, c->width * c->esz, n_units);
+  // the un-sealed tokens go to the start of fresh token buffers
+  c->length = c->frontier = frontier;
+  if (ok && ensure_tokens(c, live, s) != INFLLM_OK) ok = false;
+  if (ok) INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  if (ok) {
+    TokenBuffers& tb = c->tb;
+    const int64_t pitch = tb.cap * D * c->esz, off = (frontier - tb.t0) * D * c->esz;
+    ok = fill2d((char*)tb.k_raw + off, pitch, live * D * c->esz, HKV) &&
+         fill2d((char*)tb.v + off, pitch, live * D * c->esz, HKV) &&
+         fill2d(tb.score + (frontier - tb.t0), tb.cap * sizeof(float), live * sizeof(float), H);
+  }
+  if (ok && ensure_host_units(c, n_units) != INFLLM_OK) ok = false;
+  for (int64_t b = 0; ok && b < n_units; ++b) ok = get(f, c->host_unit(b), (size_t)c->unit_bytes);
+  fclose(f);
+  if (!ok) {
+    infllm_ctx_reset(c);
+    return fail(INFLLM_E_CUDA, "ctx_load: reading %s failed", path);
+  }
+  c->length = length;
+  c->num_blocks = n_units;
+  c->init_len = init_len;
+  c->init_full = hdr[12] != 0;
+  c->load_count = hdr[13];
+  c->d2h_synced_upto = n_units;
+  c->d2h_synced_upto_urgent = n_units;
+  c->rope_origin = -1;  // the window is rotated anew by the next append
+  // the cache comes back as the LRU table lists it
+  for (auto& kv : lru) {
+    if (c->free_slots.empty()) return fail(INFLLM_E_CAPACITY, "ctx_load: the saved cache holds more units than this one");
+    const int slot = c->free_slots.back();
+    c->free_slots.pop_back();
+    c->slot_of[kv.first] = slot;
+    c->lru.set(kv.first, kv.second);
+    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(kv.first), c->unit_bytes,
+                                   cudaMemcpyHostToDevice, s));
+  }
+  INFLLM_CUDA_OK(cudaStreamSynchronize(s));
   return INFLLM_OK;
 }

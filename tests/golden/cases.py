@@ -32,6 +32,10 @@ CASES = {
     "d128_decode": dict(H=8, HKV=2, D=128, n_init=128, n_local=256, bs=128, max_cached=8, topk=4, exc=128,
                         repr_topk=4, base=1000000.0, lens=[1400] + [1] * 150, seed=23, strategy="lru",
                         decay=None, qscale=1.0),
+    # score-based replacement at the CUDA path's shapes: prefill chunks, then single tokens, cache larger than topk
+    "d128_lru_s": dict(H=4, HKV=2, D=128, n_init=64, n_local=256, bs=128, max_cached=5, topk=3, exc=128,
+                       repr_topk=2, base=1000000.0, lens=[1300, 1, 1, 1, 300] + [1] * 20, seed=24, strategy="lru-s",
+                       decay=0.9, qscale=1.2),
 }
 
 PROJ_SEED = 12345

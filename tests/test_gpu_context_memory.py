@@ -44,7 +44,7 @@ def _run(case, dtype=torch.bfloat16):
     inputs = C.make_inputs(case)
     pe = RotaryEmbeddingESM(case["D"], case["base"], 1.0)
     cm = ContextManager(pe, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
-                        case["exc"], None, False, case["repr_topk"], case["strategy"])
+                        case["exc"], case["decay"], False, case["repr_topk"], case["strategy"])
     ora = FollowerOracle(case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"], case["exc"],
                          case["repr_topk"], case["base"], 1.0, case["strategy"], case["decay"])
     stats = dict(max_abs=0.0, mean_abs=[], exec_blocks=0)
@@ -59,7 +59,13 @@ def _run(case, dtype=torch.bfloat16):
         assert diff.max().item() <= MAX_ABS_TOL, f"max-abs {diff.max().item():.4g} at length {cm.length}"
         assert diff.mean().item() <= MEAN_ABS_TOL, f"mean-abs {diff.mean().item():.4g} at length {cm.length}"
         # the cache table after the call: same ids in the same (dict) order with the same stamps
-        assert list(cm.cached_blocks[0].items()) == [(b, float(s)) for b, s in ora.lru.entries.items()]
+        have, want_tab = list(cm.cached_blocks[0].items()), [(b, float(s)) for b, s in ora.lru.entries.items()]
+        if case["strategy"] == "lru":
+            assert have == want_tab
+        else:  # lru-s: the stamps are sums of attention probabilities, computed here from bf16 operands
+            assert [b for b, _ in have] == [b for b, _ in want_tab]
+            for (_, x), (_, y) in zip(have, want_tab):
+                assert abs(x - y) <= 2e-2 * max(1.0, abs(y)), (have, want_tab)
         info = cm.info()
         assert (info["length"], info["frontier"], info["num_blocks"], info["init_len"]) == (
             ora.length, ora.frontier, ora.num_blocks, ora.init_len)
@@ -77,6 +83,8 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     monkeypatch.setenv("INFLLM_B200_ATTN_TWO_HEAD", "1" if kernels.endswith("twohead") else "0")
     monkeypatch.setenv("INFLLM_B200_NO_DECODE_SPEC", "1" if kernels.endswith("nospec") else "0")
     case = C.CASES[name]
+    if case["strategy"] == "lru-s" and kernels not in ("tcgen05", "generic"):
+        pytest.skip("lru-s ranks, fetches and attends nothing ahead: the switches change nothing")
     cm, ora, stats = _run(case)
     from infllm_b200 import _lib
 
@@ -89,7 +97,9 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     if not flips:
         for i, tr in enumerate(ora.trace):
             assert tr.topk_raw == [int(x) for x in z["topk"][i] if x >= 0]
-            assert tr.cached_after == golden_cached(z, i)
+            want_c = golden_cached(z, i)
+            assert [b for b, _ in tr.cached_after] == [b for b, _ in want_c]
+            assert all(abs(x - y) <= 1e-5 * max(1.0, abs(y)) for (_, x), (_, y) in zip(tr.cached_after, want_c))
     # representative keys: rows equal to the oracle's up to bf16 rounding, except where the accumulated
     # local scores of two tokens tie within kernel precision
     bk = cm.block_k_rows().float()
@@ -115,6 +125,58 @@ def test_reset_reproduces_the_same_outputs():
         runs.append(torch.cat(outs, dim=2))
         cm.reset()
     assert torch.equal(runs[0], runs[1])
+
+
+@pytest.mark.parametrize("name,cut", [("d128_ragged", 5), ("d128_ragged", 7), ("d128_decode", 60), ("d128_prefill", 1)])
+def test_saved_memory_resumes_like_an_uninterrupted_one(name, cut, tmp_path):
+    """save() after `cut` appends, load() into a fresh manager, feed the rest: same retrieval, same cache tables and
+    counters, outputs equal up to the rounding of keys rotated from another origin."""
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    case = C.CASES[name]
+    inputs = C.make_inputs(case)
+    pe = RotaryEmbeddingESM(case["D"], case["base"], 1.0)
+    mk = lambda: ContextManager(pe, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],  # noqa: E731
+                                case["exc"], None, False, case["repr_topk"])
+    dev = lambda t: t[None].to(torch.bfloat16).to(DEV)  # noqa: E731
+    whole, resumed = mk(), None
+    for i, (q, k, v) in enumerate(inputs):
+        if i == cut:
+            whole.save(str(tmp_path / "mem"))
+            resumed = mk()
+            resumed.load(str(tmp_path / "mem"))
+            assert resumed.length == whole.length and resumed.cached_blocks == whole.cached_blocks
+            assert torch.equal(resumed.block_k_rows(), whole.block_k_rows())
+        dq, dk, dv = dev(q), dev(k), dev(v)
+        want = whole.append(dq, dk, dv, dq, dk, dv).float()
+        if resumed is None:
+            continue
+        got = resumed.append(dq, dk, dv, dq, dk, dv).float()
+        assert resumed.last_topk() == whole.last_topk()
+        assert list(resumed.cached_blocks[0].items()) == list(whole.cached_blocks[0].items())
+        a, b = resumed.info(), whole.info()
+        for key in ("length", "frontier", "num_blocks", "init_len"):
+            assert a[key] == b[key]
+        diff = (got - want).abs()
+        assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL
+    assert torch.allclose(resumed.block_k_rows().float(), whole.block_k_rows().float(), atol=2e-2)
+
+
+def test_load_refuses_another_configuration(tmp_path):
+    from infllm_b200 import _lib
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    case = C.CASES["d128_ragged"]
+    q, k, v = (t[None].to(torch.bfloat16).to(DEV) for t in C.make_inputs(case)[0])
+    pe = RotaryEmbeddingESM(case["D"], case["base"], 1.0)
+    a = ContextManager(pe, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"], case["exc"],
+                       None, False, case["repr_topk"])
+    a.append(q, k, v, q, k, v)
+    a.save(str(tmp_path / "mem"))
+    b = ContextManager(pe, case["n_init"], case["n_local"] * 2, case["bs"], case["max_cached"], case["topk"], case["exc"],
+                       None, False, case["repr_topk"])
+    with pytest.raises(_lib.InfLLMError):
+        b.load(str(tmp_path / "mem"))
 
 
 def test_batch_of_two_equals_two_single_sequences():
