@@ -235,7 +235,10 @@ typedef struct infllm_config {
                            * 16: one-token appends wait for the retrieved ids before launching the attention
                            * 32: one-token appends do not fetch ahead the units ranked just below the retrieval
                            * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
-                           * at most 8); the cache gets that many times topk spare slots */
+                           * at most 8); the cache gets that many times topk spare slots
+                           * reserved[2] > 0: chunk_topk_calc (context_manager.py:749-770, 548-610), in tokens: a call
+                           * of more than one token is cut into chunks of this size rounded down to whole exec blocks,
+                           * and every exec block of a chunk retrieves among the units sealed when the chunk started */
 } infllm_config;
 
 /* Validates the configuration (exc_block_size <= n_local, context_manager.py:219;

@@ -20,7 +20,7 @@ class ContextManager:
 
     Constructor arguments are those of the reference (context_manager.py:197-209).  `fattn` and
     `async_global_stream` are accepted and ignored: there is one attention implementation, and the
-    host store always refills on a side stream.  `faiss` and `chunk_topk_calc` are not built."""
+    host store always refills on a side stream.  `faiss` is not built."""
 
     def __init__(self, position_embedding, n_init, n_local, block_size, max_cached_block, topk, exc_block_size,
                  score_decay: Optional[float] = None, fattn: bool = False, repr_topk: int = 1,
@@ -49,8 +49,9 @@ class ContextManager:
         assert cache_strategy in ["lru", "lru-s"]  # context_manager.py:238
         if faiss:
             raise NotImplementedError("faiss retrieval is not built (the reference needs the faiss package for it)")
-        if chunk_topk_calc is not None:
-            raise NotImplementedError("chunk_topk_calc (batched top-k) is not built")
+        if chunk_topk_calc is not None and chunk_topk_calc < exc_block_size:
+            raise ValueError("chunk_topk_calc must hold at least one exec block")  # the reference divides by zero
+        self.chunk_topk_calc = chunk_topk_calc
         self._ctx = []  # native contexts, one per unit
 
     # -- native contexts
@@ -73,6 +74,8 @@ class ContextManager:
             dtype=_lib.dtype_code(q.dtype), score_decay=float(self.score_decay or 0.0), rope_base=float(pe.base),
             rope_scale=float(pe.distance_scale), device=q.device.index if q.device.index is not None else
             torch.cuda.current_device(), shard_rank=0, shard_world=1)
+        if self.chunk_topk_calc is not None:
+            cfg.reserved[2] = int(self.chunk_topk_calc)  # context_manager.py:749-770
         if os.environ.get("INFLLM_B200_NO_TC", "0") == "1":
             cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
         if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":

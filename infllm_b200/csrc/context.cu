@@ -164,6 +164,11 @@ struct infllm_ctx {
   float* lse = nullptr;      // (H, exc)
   float *st_acc = nullptr, *st_m = nullptr, *st_l = nullptr;  // carried attention state (H, exc, D) / (H, exc)
   float* scores = nullptr;   // (scores_cap) unit scores
+  // chunk_topk_calc (context_manager.py:749-770): in a call of more than one token every exec block of a chunk is
+  // ranked over the units that were sealed when the chunk started
+  bool chunk_mode = false;
+  int64_t call_off = 0;   // where the running internal call starts within the caller's tokens
+  int64_t chunk_n0 = 0;   // units sealed at the start of the running chunk
   float* unit_prob = nullptr;    // lru-s: (H, topk * block_size) attention mass of the retrieved units' keys
   float* h_unit_prob = nullptr;  // its pinned host copy
   int64_t scores_cap = 0;
@@ -566,8 +571,8 @@ int score_topk(infllm_ctx* c, int64_t n, const float* qbar, float* scores, int32
 int retrieve_now(infllm_ctx* c, int eb_in_call, std::vector<int32_t>* ids, cudaStream_t s) {
   const infllm_config& g = c->cfg;
   ids->clear();
-  const int64_t n = c->num_blocks;
-  if (n <= g.topk) {  // context_manager.py:370-371
+  const int64_t n = c->chunk_mode ? c->chunk_n0 : c->num_blocks;
+  if (n <= g.topk) {  // context_manager.py:370-371, :553-559
     for (int64_t b = 0; b < n; ++b) ids->push_back((int32_t)b);
     return INFLLM_OK;
   }
@@ -1152,7 +1157,12 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     // top-k kernel and resolves the retrieved units through the device copy of the slot table, so the GPU does
     // not idle while the ids travel to the host.  The host still receives the ids (it keeps the LRU order) and,
     // if one of them is not cached, refills the cache and launches the attention again.
-    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.reserved[0] & 16);
+    if (c->chunk_mode) {
+      const int64_t chunk = (int64_t)(g.reserved[2] / g.exc_block_size) * g.exc_block_size;
+      if ((c->call_off + st) % chunk == 0) c->chunk_n0 = c->num_blocks;
+    }
+    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.reserved[0] & 16) &&
+                      !c->chunk_mode;
     if (!spec) {
       if (!have_ids) {
         HostTimer ht(&c->host_us[0]);
@@ -1192,7 +1202,8 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       }
       INFLLM_TRY(flush_table(c, s));
     }
-    const bool more = ed < L && !(g.reserved[0] & 2);  // bit 1 of the flags turns the look-ahead off
+    // bit 1 of the flags turns the look-ahead off; a chunk's retrievals are fixed when it starts, so they need none
+    const bool more = ed < L && !(g.reserved[0] & 2) && !c->chunk_mode;
     const int64_t n_eb = (L + g.exc_block_size - 1) / g.exc_block_size;
     HostTimer* ht_attn = new HostTimer(&c->host_us[3]);
     trace_mark(c, s, TR_ATTN_BEGIN, eb);
@@ -1474,6 +1485,8 @@ extern "C" int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out) {
   if (g.cache_strategy != INFLLM_CACHE_LRU && g.cache_strategy != INFLLM_CACHE_LRU_S)
     return fail(INFLLM_E_UNSUPPORTED, "ctx_create: cache strategy code %d", g.cache_strategy);
   if (g.topk > 1024) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: topk %d > 1024", g.topk);
+  if (g.reserved[2] != 0 && g.reserved[2] < g.exc_block_size)
+    return fail(INFLLM_E_BADARG, "ctx_create: chunk_topk_calc %d < exc_block_size %d", g.reserved[2], g.exc_block_size);
   infllm_ctx* c = new (std::nothrow) infllm_ctx();
   if (!c) return fail(INFLLM_E_NOMEM, "ctx_create: out of host memory");
   c->cfg = g;
@@ -1604,8 +1617,10 @@ extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, i
   c->trace_topk.clear();
   c->counters.exec_blocks = 0;
   const int esz = c->esz;
+  c->chunk_mode = c->cfg.reserved[2] > 0 && len > 1;  // context_manager.py:749
   for (int64_t off = 0; off < len; off += c->sub_max) {
     const int64_t n = std::min<int64_t>(c->sub_max, len - off);
+    c->call_off = off;
     INFLLM_TRY(append_sub(c, (const char*)d_q + off * q_ts * esz, q_hs, q_ts, (const char*)d_k + off * k_ts * esz, k_hs,
                           k_ts, (const char*)d_v + off * v_ts * esz, v_hs, v_ts, (char*)d_out + off * o_ts * esz, o_hs,
                           o_ts, n, s));

@@ -181,14 +181,14 @@ class ExecBlockTrace:
 class OracleContextMemory:
     """One batch element (one `unit`) of the reference's ContextManager
     (inf_llm/attention/context_manager.py:196-816) for cache_strategy "lru" / "lru-s",
-    fattn=False, faiss=False, perhead=False, chunk_topk_calc=None.
+    fattn=False, faiss=False, perhead=False, with or without chunk_topk_calc.
 
     A batch of B sequences is B independent instances: the reference shares only the cursor
     arithmetic between units, and that depends on lengths alone."""
 
     def __init__(self, n_init, n_local, block_size, max_cached_block, topk, exc_block_size,
                  repr_topk=1, rope_base=10000.0, rope_scale=1.0, cache_strategy="lru",
-                 score_decay=None, keep_scores=False):
+                 score_decay=None, keep_scores=False, chunk_topk_calc=None):
         assert exc_block_size <= n_local  # context_manager.py:219
         assert cache_strategy in ("lru", "lru-s")  # :238
         self.n_init, self.n_local, self.bs = n_init, n_local, block_size
@@ -196,6 +196,10 @@ class OracleContextMemory:
         self.repr_topk, self.base, self.scale = repr_topk, rope_base, rope_scale
         self.strategy, self.decay = cache_strategy, score_decay
         self.keep_scores = keep_scores
+        # chunk_topk_calc (:749-757, 548-610): a call of more than one token is cut into chunks of this many tokens
+        # and every exec block of a chunk is ranked when the chunk starts, i.e. over the units sealed by then
+        self.chunk_topk_calc = chunk_topk_calc
+        self._unit_limit: Optional[int] = None
         self.length = 0  # tokens consumed (context_manager.py:211, :793)
         self.k_log: Optional[torch.Tensor] = None  # (H_kv, T, D) un-rotated keys of every token
         self.v_log: Optional[torch.Tensor] = None
@@ -220,11 +224,11 @@ class OracleContextMemory:
 
     def _retrieve(self, gq: torch.Tensor):
         """context_manager.py:366-383 and VectorTensor.get_topk :159-163."""
-        n = self.num_blocks
+        n = self.num_blocks if self._unit_limit is None else self._unit_limit  # :553-559 for a chunk
         if n <= self.topk:
             return list(range(n)), None
         qbar = gq.mean(dim=1).reshape(-1)  # (H*D,)
-        scores = torch.matmul(torch.stack(self.block_k), qbar[:, None]).squeeze(-1)
+        scores = torch.matmul(torch.stack(self.block_k[:n]), qbar[:, None]).squeeze(-1)
         return scores.topk(self.topk, dim=0).indices.tolist(), scores
 
     def _seal(self, end: int) -> None:
@@ -267,8 +271,14 @@ class OracleContextMemory:
         rem_total = t0 + L - rem_start  # its length after the cat at :728-731
         gq_all = rope_one_angle(q, self.n_local, d, self.base, self.scale)  # :744-747
         outs = []
+        chunk = None
+        if self.chunk_topk_calc is not None and L > 1:  # :749-757
+            chunk = (self.chunk_topk_calc // self.exc) * self.exc
+        self._unit_limit = None
         for st in range(0, L, self.exc):  # :762
             ed = min(st + self.exc, L)
+            if chunk is not None and st % chunk == 0:
+                self._unit_limit = self.num_blocks  # :764-770: ranked now for the whole chunk
             s_abs, e_abs = t0 + st, t0 + ed
             ks = max(s_abs - self.n_local, 0)  # :772-773 in absolute token indices
             lq, lk = rope_local(q[:, st:ed], self.k_log[:, ks:e_abs], d, self.base, self.scale)  # :480
@@ -318,6 +328,7 @@ class OracleContextMemory:
                 list(self.lru.entries.items()),
                 scores.clone() if (scores is not None and self.keep_scores) else None))
             self._seal(e_abs)  # :784-785
+        self._unit_limit = None
         self.length += L
         return torch.cat(outs, dim=1)
 

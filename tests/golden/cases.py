@@ -36,6 +36,12 @@ CASES = {
     "d128_lru_s": dict(H=4, HKV=2, D=128, n_init=64, n_local=256, bs=128, max_cached=5, topk=3, exc=128,
                        repr_topk=2, base=1000000.0, lens=[1300, 1, 1, 1, 300] + [1] * 20, seed=24, strategy="lru-s",
                        decay=0.9, qscale=1.2),
+    # chunk_topk_calc: every exec block of a 384-token chunk is ranked over the units sealed when the chunk starts
+    # (the seed leaves 7% between the last retrieved score and the next at every exec block: representative keys held
+    # in bf16 move scores by a few 1e-3 relative at these small widths, more than the near-tie rule allows)
+    "d128_chunk_topk": dict(H=4, HKV=2, D=128, n_init=64, n_local=256, bs=128, max_cached=6, topk=3, exc=128,
+                            repr_topk=2, base=1000000.0, lens=[1500, 1, 1, 1000, 1, 700], seed=26, strategy="lru",
+                            decay=None, qscale=1.0, chunk_topk=384),
 }
 
 PROJ_SEED = 12345

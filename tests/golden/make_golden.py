@@ -29,8 +29,8 @@ def record_context_manager(cm, rope, name, case):
     inputs = C.make_inputs(case)
     r = rope.RotaryEmbeddingESM(case["D"], case["base"], 1.0)
     mgr = cm.ContextManager(r, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
-                            case["exc"], case["decay"], False, case["repr_topk"], case["strategy"], None,
-                            False, False, False, False)
+                            case["exc"], case["decay"], False, case["repr_topk"], case["strategy"],
+                            case.get("chunk_topk"), False, False, False, False)
     topks, cached = [], []
     orig_topk = cm.ContextManager.calc_block_topk
     orig_append = cm.ContextManager._append

@@ -1,5 +1,7 @@
 """GPU parity of the whole context-memory path (ContextManager.append through the C ABI)
 against the CPU oracle on the golden cases' seeded inputs."""
+import itertools
+
 import pytest
 import torch
 
@@ -22,6 +24,37 @@ class FollowerOracle(O.OracleContextMemory):
         self.forced = []
         self.cursor = 0
         self.mismatches = []
+        self.gpu_rows = None  # the CUDA path's representative keys, set before every append
+        self.adopted = []
+
+    def _seal(self, end):
+        """Representative keys: the same rule as for retrieval.  Where the CUDA path picked other tokens of a unit
+        than the oracle, the accumulated scores of the tokens involved must tie (within 5e-3 relative of the last
+        selected one: they are sums of bf16-operand probabilities there), and the oracle then carries on with the
+        CUDA path's row so that later retrievals stay comparable."""
+        n0 = self.num_blocks
+        super()._seal(end)
+        for b in range(n0, self.num_blocks if self.gpu_rows is not None else n0):
+            row = self.gpu_rows[b]
+            if (row - self.block_k[b]).abs().max().item() <= 2e-2:
+                continue
+            h, r, d = self.acc.size(0), self.repr_topk, self.k_log.size(-1)
+            g = h // self.k_log.size(0)
+            st, ed = self._block_range(b)
+            for head in range(h):
+                got = row[head * d:(head + 1) * d]
+                if (got - self.block_k[b][head * d:(head + 1) * d]).abs().max().item() <= 2e-2:
+                    continue
+                sc = self.acc[head, st:ed]
+                kth = sc.topk(r).values[-1].item()
+                cand = torch.nonzero(sc >= kth - 5e-3 * abs(kth)).flatten().tolist()
+                assert len(cand) <= 12, f"unit {b} head {head}: {len(cand)} tokens tie"
+                keys = self.k_log[head // g, st:ed]
+                ok = any((keys[list(c)].mean(dim=0) - got).abs().max().item() <= 2e-2
+                         for c in itertools.combinations(cand, r))
+                assert ok, f"unit {b} head {head}: the representative key is not a mean of {r} top-scored tokens"
+            self.adopted.append(b)
+            self.block_k[b] = row.clone()
 
     def _retrieve(self, gq):
         own, scores = super()._retrieve(gq)
@@ -44,14 +77,16 @@ def _run(case, dtype=torch.bfloat16):
     inputs = C.make_inputs(case)
     pe = RotaryEmbeddingESM(case["D"], case["base"], 1.0)
     cm = ContextManager(pe, case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
-                        case["exc"], case["decay"], False, case["repr_topk"], case["strategy"])
+                        case["exc"], case["decay"], False, case["repr_topk"], case["strategy"], case.get("chunk_topk"))
     ora = FollowerOracle(case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"], case["exc"],
-                         case["repr_topk"], case["base"], 1.0, case["strategy"], case["decay"])
+                         case["repr_topk"], case["base"], 1.0, case["strategy"], case["decay"],
+                         chunk_topk_calc=case.get("chunk_topk"))
     stats = dict(max_abs=0.0, mean_abs=[], exec_blocks=0)
     for q, k, v in inputs:
         dq, dk, dv = (t[None].to(dtype).to(DEV) for t in (q, k, v))
         got = cm.append(dq, dk, dv, dq, dk, dv)[0].float().cpu()
         ora.forced += cm.last_topk()
+        ora.gpu_rows = cm.block_k_rows().float()
         want = ora.append(q, k, v)
         diff = (got - want).abs()
         stats["max_abs"] = max(stats["max_abs"], diff.max().item())
@@ -83,8 +118,8 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     monkeypatch.setenv("INFLLM_B200_ATTN_TWO_HEAD", "1" if kernels.endswith("twohead") else "0")
     monkeypatch.setenv("INFLLM_B200_NO_DECODE_SPEC", "1" if kernels.endswith("nospec") else "0")
     case = C.CASES[name]
-    if case["strategy"] == "lru-s" and kernels not in ("tcgen05", "generic"):
-        pytest.skip("lru-s ranks, fetches and attends nothing ahead: the switches change nothing")
+    if (case["strategy"] == "lru-s" or case.get("chunk_topk")) and kernels not in ("tcgen05", "generic"):
+        pytest.skip("lru-s and chunk_topk_calc rank, fetch and attend nothing ahead: the switches change nothing")
     cm, ora, stats = _run(case)
     from infllm_b200 import _lib
 
@@ -94,18 +129,18 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     meta, z = load_golden(name)
     flips = {i for i, _, _ in ora.mismatches}
     assert len(flips) <= max(1, len(ora.trace) // 10), f"{len(flips)} near-tie flips in {len(ora.trace)} exec blocks"
-    if not flips:
+    if not flips and not ora.adopted:
         for i, tr in enumerate(ora.trace):
             assert tr.topk_raw == [int(x) for x in z["topk"][i] if x >= 0]
             want_c = golden_cached(z, i)
             assert [b for b, _ in tr.cached_after] == [b for b, _ in want_c]
             assert all(abs(x - y) <= 1e-5 * max(1.0, abs(y)) for (_, x), (_, y) in zip(tr.cached_after, want_c))
-    # representative keys: rows equal to the oracle's up to bf16 rounding, except where the accumulated
-    # local scores of two tokens tie within kernel precision
+    # representative keys: rows equal to the oracle's up to bf16 rounding, except where the accumulated local scores
+    # of two tokens tie within kernel precision (checked row by row in FollowerOracle._seal)
     bk = cm.block_k_rows().float()
     want = torch.stack(ora.block_k) if ora.block_k else torch.zeros_like(bk)
-    row_err = (bk - want).abs().amax(dim=1)
-    assert (row_err < 2e-2).float().mean() >= 0.9, f"{(row_err >= 2e-2).sum().item()} of {len(row_err)} rows differ"
+    assert (bk - want).abs().max().item() <= 2e-2 if len(bk) else True
+    assert len(ora.adopted) <= max(2, ora.num_blocks // 5), f"{len(ora.adopted)} of {ora.num_blocks} rows picked on a tie"
 
 
 def test_reset_reproduces_the_same_outputs():

@@ -19,7 +19,8 @@ def test_context_memory_matches_reference(name):
     inputs = C.make_inputs(case)
     assert C.inputs_digest(inputs) == meta["digest"], "input generator drifted; re-record the fixtures"
     mem = O.OracleContextMemory(case["n_init"], case["n_local"], case["bs"], case["max_cached"], case["topk"],
-                                case["exc"], case["repr_topk"], case["base"], 1.0, case["strategy"], case["decay"])
+                                case["exc"], case["repr_topk"], case["base"], 1.0, case["strategy"], case["decay"],
+                                chunk_topk_calc=case.get("chunk_topk"))
     outs = [mem.append(q, k, v).permute(1, 0, 2) for q, k, v in inputs]
     o = torch.cat(outs, dim=0)
     # retrieval order and LRU table of every exec block: exact
