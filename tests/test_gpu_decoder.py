@@ -1,0 +1,114 @@
+"""The minimal decoder over the attention-forward API (infllm_b200/utils/decoder.py).
+
+One GPU: while the sequence fits the local window the context-memory attention is plain causal attention, so the
+decoder must reproduce a textbook fp32 Llama forward built from the same weights.  Two GPUs: the decoder split by
+KV-head groups must reproduce the one-GPU decoder on a prompt long enough to seal and retrieve memory units."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = dict(n_layers=2, hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=512)
+ATTN = dict(n_local=512, n_init=128, topk=4, block_size=128, max_cached_block=8, exc_block_size=128, fattn=True,
+            repr_topk=4)
+BASE = 500000.0
+
+
+def _rope(x, base):  # x (H, L, D), positions 0..L-1, rotate-half convention (inf_llm/attention/rope.py:35-47)
+    _, L, D = x.shape
+    inv = 1.0 / (base ** (torch.arange(0, D, 2, dtype=torch.float32, device=x.device) / D))
+    f = torch.outer(torch.arange(L, dtype=torch.float32, device=x.device), inv)
+    cos, sin = torch.cat((f, f), dim=-1).cos(), torch.cat((f, f), dim=-1).sin()
+    x1, x2 = x[..., : D // 2], x[..., D // 2:]
+    return x * cos + torch.cat((-x2, x1), dim=-1) * sin
+
+
+def _plain_forward(dec, ids):
+    """fp32 causal Llama forward over the decoder's weights: logits (L, vocab)."""
+    f = lambda t: t.float()  # noqa: E731
+    H, HKV, D = SHAPE["n_heads"], SHAPE["n_kv_heads"], SHAPE["head_dim"]
+    norm = lambda x: x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + dec.eps)  # noqa: E731
+    h = f(dec.embed)[ids]
+    L = h.size(0)
+    mask = torch.ones(L, L, dtype=torch.bool, device=h.device).tril()
+    for layer in dec.layers:
+        x = norm(h)
+        q = _rope((x @ f(layer["wq"]).T).view(L, H, D).transpose(0, 1), BASE)
+        k = _rope((x @ f(layer["wk"]).T).view(L, HKV, D).transpose(0, 1), BASE)
+        v = (x @ f(layer["wv"]).T).view(L, HKV, D).transpose(0, 1)
+        k, v = k.repeat_interleave(H // HKV, dim=0), v.repeat_interleave(H // HKV, dim=0)
+        s = (q @ k.transpose(1, 2)) / D ** 0.5
+        p = s.masked_fill(~mask, float("-inf")).softmax(dim=-1)
+        h = h + (p @ v).transpose(0, 1).reshape(L, H * D) @ f(layer["wo"]).T
+        x = norm(h)
+        h = h + (torch.nn.functional.silu(x @ f(layer["gate"]).T) * (x @ f(layer["up"]).T)) @ f(layer["down"]).T
+    return norm(h) @ f(dec.lm_head).T
+
+
+def test_decoder_equals_plain_causal_model_inside_the_window():
+    from infllm_b200.utils import HeadGroupDecoder
+
+    torch.cuda.set_device(0)
+    dec = HeadGroupDecoder(**SHAPE, attn_kwargs=ATTN, seed=3, rope_base=BASE, init_std=0.05)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, SHAPE["vocab"], (1, 300), generator=g).cuda()
+    out, trail = dec.generate(ids, max_length=4, chunk_size=128)
+    full = torch.cat((ids[0], torch.tensor(out[:-1], device=ids.device, dtype=ids.dtype)))
+    want = _plain_forward(dec, full)[-4:]
+    scale = want.abs().max().item()
+    assert (trail - want).abs().max().item() <= 3e-2 * scale, ((trail - want).abs().max().item(), scale)
+
+
+def _rank(rank, world, port, path, n_prompt, n_new):
+    import torch.distributed as dist
+
+    from infllm_b200.attention import HeadGroupComm
+    from infllm_b200.utils import HeadGroupDecoder
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        comm = HeadGroupComm()
+        dec = HeadGroupDecoder(**SHAPE, attn_kwargs=ATTN, rank=rank, world=world, comm=comm, seed=3, rope_base=BASE,
+                               init_std=0.05)
+        g = torch.Generator().manual_seed(6)
+        ids = torch.randint(0, SHAPE["vocab"], (1, n_prompt), generator=g).cuda()
+        out, trail = dec.generate(ids, max_length=n_new, chunk_size=1024)
+        torch.save((out, trail.cpu(), [layer["past"].last_topk() for layer in dec.layers]), f"{path}.{rank}")
+        del dec
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_decoder_over_two_head_groups_matches_one_gpu(tmp_path):
+    from infllm_b200.utils import HeadGroupDecoder
+
+    n_prompt, n_new, path = 3000, 6, str(tmp_path / "out")
+    mp.spawn(_rank, args=(2, 29300 + os.getpid() % 300, path, n_prompt, n_new), nprocs=2, join=True)
+    parts = [torch.load(f"{path}.{r}") for r in range(2)]
+    assert parts[0][0] == parts[1][0], "the ranks generated different tokens"
+    assert parts[0][2] == parts[1][2], "the ranks retrieved different units"
+    torch.cuda.set_device(0)
+    dec = HeadGroupDecoder(**SHAPE, attn_kwargs=ATTN, seed=3, rope_base=BASE, init_std=0.05)
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, SHAPE["vocab"], (1, n_prompt), generator=g).cuda()
+    out, trail = dec.generate(ids, max_length=n_new, chunk_size=1024)
+    # the first generated position depends on the prompt alone: its logits must agree closely; later positions
+    # are compared while the generated prefixes agree
+    scale = trail[0].abs().max().item()
+    assert (parts[0][1][0] - trail[0].cpu()).abs().max().item() <= 3e-2 * scale
+    agree = 0
+    while agree < n_new and out[agree] == parts[0][0][agree]:
+        agree += 1
+    assert agree >= 1
+    for i in range(1, agree):
+        assert (parts[0][1][i] - trail[i].cpu()).abs().max().item() <= 5e-2 * scale
