@@ -65,7 +65,21 @@ def test_decoder_equals_plain_causal_model_inside_the_window():
     assert (trail - want).abs().max().item() <= 3e-2 * scale, ((trail - want).abs().max().item(), scale)
 
 
-def _rank(rank, world, port, path, n_prompt, n_new):
+def _feed(dec, n_prompt, n_new, chunk):
+    """Chunked prefill then greedy tokens; per step the last position's logits and every layer's retrievals."""
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, SHAPE["vocab"], (1, n_prompt), generator=g).cuda()
+    logits, retrieved = [], []
+    for st in range(0, n_prompt, chunk):
+        logits.append(dec.step(ids[:, st:st + chunk])[0].cpu())
+        retrieved.append([layer["past"].last_topk() for layer in dec.layers])
+    for _ in range(n_new):
+        logits.append(dec.step(logits[-1].argmax()[None, None].cuda())[0].cpu())
+        retrieved.append([layer["past"].last_topk() for layer in dec.layers])
+    return logits, retrieved
+
+
+def _rank(rank, world, port, path, n_prompt, n_new, chunk):
     import torch.distributed as dist
 
     from infllm_b200.attention import HeadGroupComm
@@ -78,10 +92,7 @@ def _rank(rank, world, port, path, n_prompt, n_new):
         comm = HeadGroupComm()
         dec = HeadGroupDecoder(**SHAPE, attn_kwargs=ATTN, rank=rank, world=world, comm=comm, seed=3, rope_base=BASE,
                                init_std=0.05)
-        g = torch.Generator().manual_seed(6)
-        ids = torch.randint(0, SHAPE["vocab"], (1, n_prompt), generator=g).cuda()
-        out, trail = dec.generate(ids, max_length=n_new, chunk_size=1024)
-        torch.save((out, trail.cpu(), [layer["past"].last_topk() for layer in dec.layers]), f"{path}.{rank}")
+        torch.save(_feed(dec, n_prompt, n_new, chunk), f"{path}.{rank}")
         del dec
         comm.close()
     finally:
@@ -90,25 +101,28 @@ def _rank(rank, world, port, path, n_prompt, n_new):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_decoder_over_two_head_groups_matches_one_gpu(tmp_path):
+    """Both ranks must agree exactly (same logits after the all-reduces, same retrievals).  Against the one-GPU
+    model the activations differ by bf16 rounding (other summation order), which with random weights (attention
+    close to uniform, unit scores close to each other) sometimes moves a retrieval in the second layer: steps with
+    equal retrievals must agree within 2 % of the logit range, all steps within 8 %, and most steps must be
+    comparable."""
     from infllm_b200.utils import HeadGroupDecoder
 
-    n_prompt, n_new, path = 3000, 6, str(tmp_path / "out")
-    mp.spawn(_rank, args=(2, 29300 + os.getpid() % 300, path, n_prompt, n_new), nprocs=2, join=True)
+    n_prompt, n_new, chunk, path = 3000, 4, 256, str(tmp_path / "out")
+    mp.spawn(_rank, args=(2, 29300 + os.getpid() % 300, path, n_prompt, n_new, chunk), nprocs=2, join=True)
     parts = [torch.load(f"{path}.{r}") for r in range(2)]
-    assert parts[0][0] == parts[1][0], "the ranks generated different tokens"
-    assert parts[0][2] == parts[1][2], "the ranks retrieved different units"
+    assert parts[0][1] == parts[1][1], "the ranks retrieved different units"
+    assert all(torch.equal(a, b) for a, b in zip(parts[0][0], parts[1][0])), "the ranks' logits differ"
     torch.cuda.set_device(0)
     dec = HeadGroupDecoder(**SHAPE, attn_kwargs=ATTN, seed=3, rope_base=BASE, init_std=0.05)
-    g = torch.Generator().manual_seed(6)
-    ids = torch.randint(0, SHAPE["vocab"], (1, n_prompt), generator=g).cuda()
-    out, trail = dec.generate(ids, max_length=n_new, chunk_size=1024)
-    # the first generated position depends on the prompt alone: its logits must agree closely; later positions
-    # are compared while the generated prefixes agree
-    scale = trail[0].abs().max().item()
-    assert (parts[0][1][0] - trail[0].cpu()).abs().max().item() <= 3e-2 * scale
-    agree = 0
-    while agree < n_new and out[agree] == parts[0][0][agree]:
-        agree += 1
-    assert agree >= 1
-    for i in range(1, agree):
-        assert (parts[0][1][i] - trail[i].cpu()).abs().max().item() <= 5e-2 * scale
+    logits, retrieved = _feed(dec, n_prompt, n_new, chunk)
+    comparable = 0
+    for i, (want, got) in enumerate(zip(logits, parts[0][0])):
+        scale, err = want.abs().max().item(), (want - got).abs().max().item()
+        if retrieved[i] == parts[0][1][i]:
+            comparable += 1
+            assert err <= 2e-2 * scale, f"step {i}: {err} of {scale}"
+        assert err <= 8e-2 * scale, f"step {i}: {err} of {scale}"
+        if want.argmax() != got.argmax():
+            break  # the greedy continuations part ways here
+    assert comparable >= len(logits) // 2
