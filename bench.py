@@ -712,6 +712,68 @@ def run_decode_sharded(args, rank, world, local_rank):
     return line
 
 
+def run_model(args, rank, world, local_rank):
+    """A Llama-3-8B-shaped random-init decoder (32 layers, 32/8 heads of 128, FFN 14336) over the attention-forward
+    API: chunked prefill of a synthetic prompt, then greedy tokens.  With N > 1 the model is split by KV-head groups
+    (strong scaling).  Not part of the default run: the headline metric is the layer's."""
+    from infllm_b200.attention import HeadGroupComm
+    from infllm_b200.utils import HeadGroupDecoder
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = HeadGroupComm() if world > 1 else None
+    attn = dict(n_local=CFG["n_local"], n_init=CFG["n_init"], topk=CFG["topk"], block_size=CFG["bs"],
+                max_cached_block=CFG["max_cached"], exc_block_size=CFG["exc"], fattn=True, repr_topk=CFG["repr_topk"])
+    dec = HeadGroupDecoder(32, 4096, CFG["H"], CFG["HKV"], CFG["D"], 14336, 128256, attn, rank=rank, world=world,
+                           comm=comm, seed=0, device=dev, rope_base=500000.0)
+    g = torch.Generator().manual_seed(0)
+    h_ids = torch.randint(0, 128256, (1, args.tokens), generator=g).pin_memory()
+    n_new = 16
+
+    def prompt():
+        dec.reset()
+        logits = None
+        for st in range(0, args.tokens, CFG["chunk"]):
+            logits = dec.step(h_ids[:, st:st + CFG["chunk"]].to(dev, non_blocking=True))
+        return logits
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        prompt()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ms_prefill = ms_decode = 0.0
+    tokens = []
+    for _ in range(args.steps):
+        ev[0].record()
+        logits = prompt()
+        ev[1].record()
+        for _ in range(n_new):
+            nxt = logits.argmax(dim=-1)
+            tokens.append(int(nxt))
+            logits = dec.step(nxt[:, None])
+        ev[2].record()
+        torch.cuda.synchronize()
+        ms_prefill += ev[0].elapsed_time(ev[1])
+        ms_decode += ev[1].elapsed_time(ev[2])
+    t = torch.tensor([ms_prefill, ms_decode], device=dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_prefill, ms_decode = (t / args.steps).tolist()
+    del dec
+    if comm is not None:
+        comm.close()
+    return dict(metric="whole-model chunked prefill tokens/s (Llama-3-8B shape, random weights)",
+                value=args.tokens / (ms_prefill / 1e3), unit="tokens/s", n_gpus=world, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms_prefill, higher_is_better=True,
+                scaling="strong" if world > 1 else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                config=dict(workload=f"32-layer decoder, {args.tokens}-token prompt in chunks of {CFG['chunk']}, "
+                                     f"exec blocks of {CFG['exc']}, then {n_new} greedy tokens; host token ids",
+                            parallelism=f"kv-head-groups{world}" if world > 1 else "single"),
+                decode_ms_per_token=ms_decode / n_new, first_tokens=tokens[:n_new])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -721,7 +783,7 @@ def main():
                          "representative-key array would otherwise sit in the timed region)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=CFG["tokens"])
-    ap.add_argument("--workload", default="both", choices=["both", "prefill", "decode"],
+    ap.add_argument("--workload", default="both", choices=["both", "prefill", "decode", "model"],
                     help="prefill: 131072-token prompt, the first half of the metric and the line's value; decode: the "
                          "1M-token decode, the second half; both (default): the prefill line with the decode line "
                          "under its key 'decode'")
@@ -760,6 +822,8 @@ def main():
     decode = run_decode_sharded if (world > 1 or args.sharded) else run_decode
     if args.workload == "decode":
         line = decode(args, rank, world, local_rank)
+    elif args.workload == "model":
+        line = run_model(args, rank, world, local_rank)
     else:
         line = run_ours(args, rank, world, local_rank)
         if args.workload == "both":

@@ -889,6 +889,398 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
   if (warp == 17) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------
+// attn_tc3_kernel: one 128-query tile of one head per CTA, like attn_tc_kernel, with another softmax.
+// In attn_tc_kernel all eight softmax warps work on the same key tile in lock-step (two threads per query row),
+// so the phases of a tile — TMEM load, row maximum, exchange, exponentials, P store — run one after another
+// and the tile period is their sum (about 3300 cycles against 1030 for the tile's two products).  Here the
+// eight warps are two teams of four: one thread per query row, a team takes every second key tile, and the
+// only thing a tile needs from its predecessor is the row's reference maximum, which the other team publishes
+// in shared memory right after its maximum pass, before its exponentials.  The long phases of consecutive
+// tiles therefore overlap.  Measured, it does not pay: 168 us per exec block against 104 us.  Each thread now runs
+// twice the instructions per tile with the same two warps per scheduler to hide their latency, the unrolled code
+// is several times larger (instruction-fetch stalls of 3 cycles per issue against 0.6), and the kernel executes
+// 36 M instructions per launch against 29 M.  It stays as an option for experiments.  S is double-buffered in TMEM; P = exp2(S - m) goes back into the columns of its S
+// buffer as packed 16-bit pairs and feeds the P V product from TMEM; a thread's row sum lives in the scale of the
+// last reference maximum it saw and the two teams' sums are merged at the end.
+namespace tc3 {
+constexpr int kQ = 0;
+constexpr int kK = kQ + 2 * kSubTileBytes;       // two stages
+constexpr int kV = kK + 4 * kSubTileBytes;       // two stages
+constexpr int kBar = kV + 4 * kSubTileBytes;
+constexpr int kXm = kBar + 256;                  // reference maximum after a tile: 2 tile parities x 128 rows
+constexpr int kXflag = kXm + 1024;               // tiles published: 2 teams x 128 rows
+constexpr int kXsum = kXflag + 1024;             // final (row sum, its scale): 2 teams x 128 rows
+constexpr int kTotal = kXsum + 2048;
+enum { T3_Q_FULL = 0, T3_Q_EMPTY, T3_K_FULL0, T3_K_FULL1, T3_K_EMPTY0, T3_K_EMPTY1, T3_V_FULL0, T3_V_FULL1, T3_V_EMPTY0,
+       T3_V_EMPTY1, T3_S_FULL0, T3_S_FULL1, T3_P_FULL0, T3_P_FULL1, T3_PV_DONE0, T3_PV_DONE1, T3_O_FULL, T3_N_BARS };
+}  // namespace tc3
+
+template <typename T>
+__global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant__ AttnTcParams P) {
+  using namespace tc3;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t sQ = s_base + kQ, sK = s_base + kK, sV = s_base + kV;
+  const uint32_t bars = s_base + kBar;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBar + T3_N_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBar + T3_N_BARS * 8 + 8);
+  volatile float* xm = reinterpret_cast<volatile float*>(smem + kXm);
+  volatile int* xflag = reinterpret_cast<volatile int*>(smem + kXflag);
+  volatile float* xsum = reinterpret_cast<volatile float*>(smem + kXsum);
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, hkv = h / (P.n_heads / P.n_kv_heads);
+  const int64_t i0 = (int64_t)blockIdx.x * kTile;
+  const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < T3_N_BARS; ++i) mbar_init(bar(i), (i == T3_P_FULL0 || i == T3_P_FULL1) ? 128u : 1u);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 256) xflag[threadIdx.x] = 0;
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tO = tmem + 256;  // S/P buffers at columns [0,128) and [128,256)
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
+  constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
+
+  if (warp == 8) {
+    // ======================================================================== TMA producer
+    if (lane == 0) {
+      int it = 0, sidx = 0;
+      bool ok = true;
+      for (int st = 0; st < P.n_stage && ok; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        if (stage_tiles(P, S, vis_lo, vis_hi) == 0) continue;
+        if (sidx >= 1) ok = wait_or_abort(bar(T3_Q_EMPTY), (sidx - 1) & 1, abort_flag, P.err, 600);
+        if (!ok) break;
+        mbar_expect_tx(bar(T3_Q_FULL), 2 * kSubTileBytes);
+        tma_load_3d(sQ, &P.maps[S.map_q], bar(T3_Q_FULL), 0, S.q_row0 + (int)i0, h);
+        tma_load_3d(sQ + kSubTileBytes, &P.maps[S.map_q], bar(T3_Q_FULL), 64, S.q_row0 + (int)i0, h);
+        ++sidx;
+        int64_t seg_j0 = 0;
+        for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+          const TcSeg& G = P.seg[sg];
+          int tf, tl;
+          if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+            for (int t = tf; t <= tl && ok; ++t, ++it) {
+              const int b = it & 1, tok = G.tok0 + t * kTile;
+              if (it >= 2) ok = wait_or_abort(bar(T3_K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 601);
+              if (!ok) break;
+              const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
+              mbar_expect_tx(bar(T3_K_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_k < 0) {
+                tma_load_3d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dk + kSubTileBytes, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv, G.c3_k);
+                tma_load_4d(dk + kSubTileBytes, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 64, tok, hkv, G.c3_k);
+              }
+              if (it >= 2) ok = wait_or_abort(bar(T3_V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 602);
+              if (!ok) break;
+              mbar_expect_tx(bar(T3_V_FULL0 + b), 2 * kSubTileBytes);
+              if (G.c3_v < 0) {
+                tma_load_3d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv);
+                tma_load_3d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 64, tok, hkv);
+              } else {
+                tma_load_4d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv, G.c3_v);
+                tma_load_4d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 64, tok, hkv, G.c3_v);
+              }
+            }
+          }
+          seg_j0 += G.len;
+        }
+      }
+      if (!ok) {
+        // give loads that are still in flight a bounded chance to land before the CTA's memory goes away
+        for (int b = 0; b < 2; ++b) {
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(T3_K_FULL0 + b), 0) && !mbar_try_wait(bar(T3_K_FULL0 + b), 1); ++i) __nanosleep(64);
+          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(T3_V_FULL0 + b), 0) && !mbar_try_wait(bar(T3_V_FULL0 + b), 1); ++i) __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ========================================================================== MMA issuer
+    if (lane == 0) {
+      // tiles per stage that has any, in order
+      int nt[kMaxStage], n_act = 0, n = 0;
+      for (int st = 0; st < P.n_stage; ++st) {
+        const TcStage& S = P.stage[st];
+        int64_t vis_lo, vis_hi;
+        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+        if (vis_lo > vis_hi) continue;
+        const int c = stage_tiles(P, S, vis_lo, vis_hi);
+        if (c > 0) nt[n_act++] = c, n += c;
+      }
+      bool ok = true;
+      int iq = 0, sq = 0, tq = 0;  // next S = Q K^T to issue: tile iq = tile tq of active stage sq
+      auto issue_qk = [&]() -> bool {
+        if (tq == 0 && !wait_or_abort(bar(T3_Q_FULL), sq & 1, abort_flag, P.err, 610)) return false;
+        const int b = iq & 1;
+        if (!wait_or_abort(bar(T3_K_FULL0 + b), (iq >> 1) & 1, abort_flag, P.err, 611)) return false;
+        tc_fence_after();
+        const uint32_t kt = sK + b * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint64_t ad = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          uint64_t bd = make_sdesc(kt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
+          mma_ss(tmem + b * 128, ad, bd, idesc_qk, ks > 0);
+        }
+        tc_commit(bar(T3_S_FULL0 + b));
+        tc_commit(bar(T3_K_EMPTY0 + b));
+        if (++tq == nt[sq]) {
+          tc_commit(bar(T3_Q_EMPTY));  // the last product that reads this stage's Q tile
+          ++sq;
+          tq = 0;
+        }
+        ++iq;
+        return true;
+      };
+      if (n >= 1) ok = issue_qk();
+      if (ok && n >= 2) ok = issue_qk();
+      for (int ip = 0; ip < n && ok; ++ip) {
+        const int b = ip & 1;
+        ok = wait_or_abort(bar(T3_P_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 612) &&
+             wait_or_abort(bar(T3_V_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 613);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t vt = sV + b * 2 * kSubTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A = P from TMEM: keys 0-63 in the buffer's columns [0,32), keys 64-127 in [64,96)
+          const uint32_t a_t = tmem + b * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
+          uint64_t bd = make_sdesc(vt + ks * 2048, kSubTileBytes, 1024);
+          mma_ts(tO, a_t, bd, idesc_pv, (ip > 0) || (ks > 0));
+        }
+        tc_commit(bar(T3_V_EMPTY0 + b));
+        tc_commit(bar(T3_PV_DONE0 + b));
+        // the tensor pipe runs in issue order: this S overwrites the P that the product above has read
+        if (iq < n) ok = issue_qk();
+      }
+      if (ok) tc_commit(bar(T3_O_FULL));
+    }
+  } else {
+    // ===================================================================== softmax / epilogue
+    const int team = warp >> 2, quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int64_t qi = i0 + row;
+    const bool row_valid = qi < P.lq;
+    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
+    float m_seen = -INFINITY, l_part = 0.f;  // l_part is in the scale of m_seen (scaled log2 domain)
+    int it = 0;
+    bool ok = true;
+    for (int st = 0; st < P.n_stage && ok; ++st) {
+      const TcStage& S = P.stage[st];
+      int64_t vis_lo, vis_hi;
+      visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
+      if (vis_lo > vis_hi) continue;
+      int64_t jlo = 0, jhi = S.lk - 1;  // keys of this stage visible to this thread's query row
+      if (S.mask_mode == INFLLM_MASK_WINDOW) {
+        jlo = qi + S.mask_offset - S.mask_size + 1;
+        jhi = qi + S.mask_offset;
+      } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
+        jhi = qi + S.mask_offset - S.mask_size;
+      }
+      if (!row_valid) jhi = -1, jlo = 0;
+      int64_t seg_j0 = 0;
+      for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
+        const TcSeg& G = P.seg[sg];
+        int tf, tl;
+        if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
+          for (int t = tf; t <= tl && ok; ++t, ++it) {
+            if ((it & 1) != team) continue;
+            const int b = it & 1;
+            const uint32_t tS = tmem + b * 128 + lane_base;
+            ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 620));
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t jt = seg_j0 + (int64_t)t * kTile;
+            const int64_t lim = seg_j0 + G.len - 1;
+            const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
+            const int c_lo = (int)(a - jt);
+            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt));
+            const bool full = c_lo <= 0 && c_hi >= kTile - 1;
+            // ---- pass 1: row maximum of the raw scores.  Two 32-column loads are in flight at a time; the last
+            // two chunks stay in registers for pass 2
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            auto max_chunk = [&](const float* s, int cc) {
+              if (full) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                  mx4[0] = fmaxf(mx4[0], s[c]);
+                  mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                  mx4[2] = fmaxf(mx4[2], s[c + 2]);
+                  mx4[3] = fmaxf(mx4[3], s[c + 3]);
+                }
+              } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                  const int cg = cc * 32 + c;
+                  mx4[c & 3] = fmaxf(mx4[c & 3], (cg >= c_lo && cg <= c_hi) ? s[c] : -INFINITY);
+                }
+              }
+            };
+            float s0[32], s1[32];
+            tmem_ld32(tS, reinterpret_cast<uint32_t*>(s0));
+            tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s1));
+            tmem_wait_ld();
+            max_chunk(s0, 0);
+            tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s0));
+            max_chunk(s1, 1);
+            tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s1));
+            tmem_wait_ld();
+            max_chunk(s0, 2);
+            max_chunk(s1, 3);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
+            // ---- the row's reference maximum after the previous tile, from the other team
+            float m_prev = -INFINITY;
+            if (it >= 1) {
+              ok = __all_sync(0xffffffffu, pair_wait(&xflag[(team ^ 1) * 128 + row], it, abort_flag, P.err, 621));
+              if (!ok) break;
+              m_prev = xm[((it - 1) & 1) * 128 + row];
+            }
+            // lazy rescaling: the reference only moves when the row maximum grew by more than 2^8
+            float m_new = m_prev, alpha = 1.f;
+            bool resc = false;
+            if (mx > m_prev) {
+              if (m_prev == -INFINITY) {
+                m_new = mx;  // nothing accumulated for this row yet
+              } else if (mx - m_prev > 8.f) {
+                m_new = mx;
+                alpha = ex2_approx(m_prev - mx);
+                resc = true;
+              }
+            }
+            xm[(it & 1) * 128 + row] = m_new;
+            __threadfence_block();
+            xflag[team * 128 + row] = it + 1;
+            if (m_seen != m_new) {
+              if (l_part != 0.f) l_part *= ex2_approx(m_seen - m_new);
+              m_seen = m_new;
+            }
+            if (__any_sync(0xffffffffu, resc) && it >= 1) {
+              // O holds the products up to tile it-1: wait for the last of them, then scale this row
+              ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) & 1)), ((it - 1) >> 1) & 1, abort_flag,
+                                                         P.err, 622));
+              if (!ok) break;
+              tc_fence_after();
+#pragma unroll
+              for (int cc = 0; cc < 4; ++cc) {
+                uint32_t o[32];
+                tmem_ld32(tO + lane_base + cc * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+                tmem_st32(tO + lane_base + cc * 32, o);
+              }
+              tmem_wait_st();
+            }
+            // ---- pass 2: P = exp2(S * scale - m), two exponentials per instruction, packed 16-bit pairs; 32 keys of P
+            // go over S columns this thread has already consumed: keys 0-63 -> [0,32), keys 64-127 -> [64,96)
+            const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            auto exp_chunk = [&](const float* s, int cc) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int c = 0; c < 32; c += 4) {
+                float a0 = fmaf(s[c], P.scale_log2, neg_m), a1 = fmaf(s[c + 1], P.scale_log2, neg_m);
+                float a2 = fmaf(s[c + 2], P.scale_log2, neg_m), a3 = fmaf(s[c + 3], P.scale_log2, neg_m);
+                if (!full) {
+                  const int cg = cc * 32 + c;
+                  a0 = (cg >= c_lo && cg <= c_hi) ? a0 : -INFINITY;
+                  a1 = (cg + 1 >= c_lo && cg + 1 <= c_hi) ? a1 : -INFINITY;
+                  a2 = (cg + 2 >= c_lo && cg + 2 <= c_hi) ? a2 : -INFINITY;
+                  a3 = (cg + 3 >= c_lo && cg + 3 <= c_hi) ? a3 : -INFINITY;
+                }
+                const float2 p01 = ex2_pair(a0, a1), p23 = ex2_pair(a2, a3);
+                rs4[0] += p01.x; rs4[1] += p01.y; rs4[2] += p23.x; rs4[3] += p23.y;
+                typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
+                pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
+                pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
+              }
+              tmem_st16(tS + (cc < 2 ? 16 * cc : 64 + 16 * (cc - 2)), pk);
+            };
+            exp_chunk(s0, 2);  // chunks 2 and 3 are still in registers
+            tmem_ld32(tS, reinterpret_cast<uint32_t*>(s0));
+            exp_chunk(s1, 3);
+            tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s1));
+            tmem_wait_ld();
+            exp_chunk(s0, 0);
+            exp_chunk(s1, 1);
+            l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(T3_P_FULL0 + b));
+          }
+        }
+        seg_j0 += G.len;
+      }
+    }
+    // ---- epilogue: merge the two teams' row sums, O / l -> out (each team writes 64 columns), log-sum-exp
+    xsum[(team * 128 + row) * 2] = l_part;
+    xsum[(team * 128 + row) * 2 + 1] = m_seen;
+    __threadfence_block();
+    xflag[team * 128 + row] = kPairDone;
+    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(team ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 623));
+    const float l_o = xsum[((team ^ 1) * 128 + row) * 2], m_o = xsum[((team ^ 1) * 128 + row) * 2 + 1];
+    const float m_fin = fmaxf(m_seen, m_o);
+    float l_sum = 0.f;
+    if (l_part > 0.f) l_sum += l_part * ex2_approx(m_seen - m_fin);
+    if (l_o > 0.f) l_sum += l_o * ex2_approx(m_o - m_fin);
+    if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_O_FULL), 0, abort_flag, P.err, 624));
+    if (ok) {
+      tc_fence_after();
+      const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
+      const int col0 = team * 64;
+      T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts + col0;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        if (it >= 1) {
+          tmem_ld32(tO + lane_base + col0 + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] = 0;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int k = 0; k < 32; k += 8) {
+            uint4 v;
+            uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              typename Act<T>::T2 v2 = Act<T>::from_f2(__uint_as_float(o[k + 2 * e]) * inv,
+                                                       __uint_as_float(o[k + 2 * e + 1]) * inv);
+              pv[e] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
+          }
+        }
+      }
+      if (team == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_fin + log2f(l_sum) : -INFINITY;
+    }
+  }
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, 512);
+}
+
 // out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), lse = m + log2(denominator); one warp per row
 template <typename T>
 __global__ void attn_tc_combine_kernel(const float* __restrict__ acc, const float* __restrict__ m,
@@ -1247,6 +1639,23 @@ int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
     kern<<<grid, 320, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("attn_tc_kernel");
+  return INFLLM_OK;
+}
+
+int attn_tc3_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
+  if (P.lq <= 0) return INFLLM_OK;
+  dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads);
+  const size_t smem = tc3::kTotal + 1024;
+  static bool attr_set[2] = {false, false};
+  INFLLM_DISPATCH_DTYPE(dtype, T, {
+    auto kern = attn_tc3_kernel<T>;
+    if (!attr_set[dtype]) {
+      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set[dtype] = true;
+    }
+    kern<<<grid, 320, smem, s>>>(P);
+  });
+  INFLLM_LAUNCH_OK("attn_tc3_kernel");
   return INFLLM_OK;
 }
 
