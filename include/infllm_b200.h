@@ -234,8 +234,8 @@ typedef struct infllm_config {
                            *  8: the two-heads-per-CTA tcgen05 attention kernel (experimental)
                            * 16: one-token appends wait for the retrieved ids before launching the attention
                            * 32: one-token appends do not fetch ahead the units ranked just below the retrieval
-                           * 64: the experimental exec-block attention kernel whose softmax warps work as two teams
-                           *     of four on alternate key tiles (default: all eight on one key tile; it is faster)
+                           * 64: the older exec-block attention kernel that passes P through shared memory
+                           *     (default: P stays in TMEM and feeds the P V product from there)
                            * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
                            * at most 8); the cache gets that many times topk spare slots
                            * reserved[2] > 0: chunk_topk_calc (context_manager.py:749-770, 548-610), in tokens: a call

@@ -82,8 +82,8 @@ class ContextManager:
             cfg.reserved[0] |= 2  # debugging aid: rank every exec block's units on the device, no look-ahead staging
         if os.environ.get("INFLLM_B200_ATTN_TWO_HEAD", "0") == "1":
             cfg.reserved[0] |= 8  # experimental: two query heads of a KV head per CTA share every K/V tile
-        if os.environ.get("INFLLM_B200_ATTN_TWO_TEAMS", "0") == "1":
-            cfg.reserved[0] |= 64  # experimental: softmax warps as two teams on alternate key tiles (slower so far)
+        if os.environ.get("INFLLM_B200_ATTN_P_IN_SMEM", "0") == "1":
+            cfg.reserved[0] |= 64  # the older exec-block attention kernel that passes P through shared memory
         if os.environ.get("INFLLM_B200_STAGE_KERNEL", "0") == "1":
             cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
         if os.environ.get("INFLLM_B200_LOOK_DEPTH"):

@@ -26,7 +26,7 @@ __device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] block
 #ifdef INFLLM_TC_TIMING
 // development aid: per-iteration clock stamps of CTA (0,0): [role][iteration], roles 0 producer issue, 1 operands
 // arrived, 2 MMA committed, 3 accumulator seen by the compute warps, 4 compute done
-__device__ long long g_tc_stamps[10][256];
+__device__ long long g_tc_stamps[20][256];
 #define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
 #else
 #define TC_STAMP(role, it) do { } while (0)
@@ -57,6 +57,26 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Blackwell's packed fp32 pairs and three-input maximum: half the instructions of the scalar forms
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float a0, float a1, float2 b, float2 c) {
+  float2 d;
+  asm("{ .reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mov.b64 rc, {%6,%7}; "
+      "fma.rn.f32x2 rd, ra, rb, rc; mov.b64 {%0,%1}, rd; }"
+      : "=f"(d.x), "=f"(d.y) : "f"(a0), "f"(a1), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{ .reg .b64 ra, rb, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; add.rn.f32x2 rd, ra, rb; mov.b64 {%0,%1}, rd; }"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
 }
 
 // two exponentials per special-function instruction: exp2 of a pair of fp32 arguments evaluated in fp16
@@ -214,19 +234,23 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
     if (lane == 0) {
       int it = 0, sidx = 0;
       bool ok = true;
+      // descriptors are built once; a K-major operand advances by 32 bytes per 16-element step and jumps to its
+      // second 64-column sub-tile after four steps
+      const uint64_t qd0 = make_sdesc(sQ, 16, 1024), pd0 = make_sdesc(sP, 16, 1024);
+      const uint64_t kd0[2] = {make_sdesc(sK, 16, 1024), make_sdesc(sK + 2 * kSubTileBytes, 16, 1024)};
+      const uint64_t vd0[2] = {make_sdesc(sV, kSubTileBytes, 1024), make_sdesc(sV + 2 * kSubTileBytes, kSubTileBytes, 1024)};
       auto issue_pv = [&](int j) -> bool {
         const int b = j & 1;
         if (!wait_or_abort(bar(P_FULL), j & 1, abort_flag, P.err, 200)) return false;
+        TC_STAMP(9, j);
         if (!wait_or_abort(bar(V_FULL0 + b), (j >> 1) & 1, abort_flag, P.err, 201)) return false;
+        TC_STAMP(11, j);
         tc_fence_after();
-        const uint32_t vt = sV + b * 2 * kSubTileBytes;
+        // A = P [128 queries x 16 keys], K-major; B = V [16 keys x 128 d], d contiguous (MN-major)
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // A = P [128 queries x 16 keys], K-major; B = V [16 keys x 128 d], d contiguous (MN-major)
-          uint64_t ad = make_sdesc(sP + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-          uint64_t bd = make_sdesc(vt + ks * 2048, kSubTileBytes, 1024);
-          mma_ss(tO, ad, bd, idesc_pv, (j > 0) || (ks > 0));
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tO, pd0 + (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4), vd0[b] + (uint64_t)((ks * 2048) >> 4),
+                 idesc_pv, (j > 0) || (ks > 0));
         tc_commit(bar(V_EMPTY0 + b));
         tc_commit(bar(P_EMPTY));
         return true;
@@ -250,19 +274,22 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
         }
         for (int t = 0; t < n_tiles && ok; ++t, ++it) {
           const int b = it & 1;
+          TC_STAMP(8, it);
           ok = wait_or_abort(bar(K_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 203);
+          TC_STAMP(18, it);
           if (ok && it >= 2) ok = wait_or_abort(bar(S_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 204);
+          TC_STAMP(19, it);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t kt = sK + b * 2 * kSubTileBytes;
+          const uint32_t ts = b ? tS1 : tS0;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            uint64_t ad = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-            uint64_t bd = make_sdesc(kt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-            mma_ss(b ? tS1 : tS0, ad, bd, idesc_qk, ks > 0);
+            const uint64_t off = (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4);
+            mma_ss(ts, qd0 + off, kd0[b] + off, idesc_qk, ks > 0);
           }
           tc_commit(bar(S_FULL0 + b));
           tc_commit(bar(K_EMPTY0 + b));
+          TC_STAMP(10, it);
           if (t == n_tiles - 1) tc_commit(bar(Q_EMPTY));
           if (it >= 1) ok = issue_pv(it - 1);
         }
@@ -306,12 +333,14 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
             const int b = it & 1;
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 300));
             if (!ok) break;
+            if (threadIdx.x == 0) TC_STAMP(12, it);
             tc_fence_after();
             float s[64];
             const uint32_t ts = (b ? tS1 : tS0) + lane_base + col0;
             tmem_ld32(ts, reinterpret_cast<uint32_t*>(s));
             tmem_ld32(ts + 32, reinterpret_cast<uint32_t*>(s) + 32);
             tmem_wait_ld();
+            if (threadIdx.x == 0) TC_STAMP(13, it);
             tc_fence_before();
             mbar_arrive(bar(S_EMPTY0 + b));
             // visible columns of this tile for this row: [c_lo, c_hi] in tile coordinates
@@ -326,11 +355,11 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-              mx4[0] = fmaxf(mx4[0], s[c]);
-              mx4[1] = fmaxf(mx4[1], s[c + 1]);
-              mx4[2] = fmaxf(mx4[2], s[c + 2]);
-              mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            for (int c = 0; c < 64; c += 8) {
+              mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
+              mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
+              mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
+              mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the other half's maximum of the same row
@@ -340,6 +369,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
             ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 303));
             if (!ok) break;
             mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
+            if (threadIdx.x == 0) TC_STAMP(14, it);
             // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
             float alpha = 1.f;
             bool resc = false;
@@ -355,22 +385,25 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
             }
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             uint32_t pk[32];
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            float2 rs01 = make_float2(0.f, 0.f), rs23 = make_float2(0.f, 0.f);
+            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
-              float p0 = ex2_approx(fmaf(s[c], P.scale_log2, neg_m));
-              float p1 = ex2_approx(fmaf(s[c + 1], P.scale_log2, neg_m));
-              float p2 = ex2_approx(fmaf(s[c + 2], P.scale_log2, neg_m));
-              float p3 = ex2_approx(fmaf(s[c + 3], P.scale_log2, neg_m));
-              rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
-              typename Act<T>::T2 v01 = Act<T>::from_f2(p0, p1), v23 = Act<T>::from_f2(p2, p3);
+              const float2 a01 = ffma2(s[c], s[c + 1], sc2, nm2), a23 = ffma2(s[c + 2], s[c + 3], sc2, nm2);
+              const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
+              const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+              rs01 = fadd2(rs01, p01);
+              rs23 = fadd2(rs23, p23);
+              typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
               pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
               pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
             }
-            l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
+            if (threadIdx.x == 0) TC_STAMP(15, it);
             // P buffer and O are free once PV of the previous tile has completed
             if (it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(P_EMPTY), (it - 1) & 1, abort_flag, P.err, 301));
             if (!ok) break;
+            if (threadIdx.x == 0) TC_STAMP(16, it);
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
               tc_fence_after();
 #pragma unroll
@@ -393,6 +426,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__
             }
             fence_proxy_async_smem();
             mbar_arrive(bar(P_FULL));
+            if (threadIdx.x == 0) TC_STAMP(17, it);
           }
         }
         seg_j0 += G.len;
@@ -890,28 +924,24 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
-// attn_tc3_kernel: one 128-query tile of one head per CTA, like attn_tc_kernel, with another softmax.
-// In attn_tc_kernel all eight softmax warps work on the same key tile in lock-step (two threads per query row),
-// so the phases of a tile — TMEM load, row maximum, exchange, exponentials, P store — run one after another
-// and the tile period is their sum (about 3300 cycles against 1030 for the tile's two products).  Here the
-// eight warps are two teams of four: one thread per query row, a team takes every second key tile, and the
-// only thing a tile needs from its predecessor is the row's reference maximum, which the other team publishes
-// in shared memory right after its maximum pass, before its exponentials.  The long phases of consecutive
-// tiles therefore overlap.  Measured, it does not pay: 168 us per exec block against 104 us.  Each thread now runs
-// twice the instructions per tile with the same two warps per scheduler to hide their latency, the unrolled code
-// is several times larger (instruction-fetch stalls of 3 cycles per issue against 0.6), and the kernel executes
-// 36 M instructions per launch against 29 M.  It stays as an option for experiments.  S is double-buffered in TMEM; P = exp2(S - m) goes back into the columns of its S
-// buffer as packed 16-bit pairs and feeds the P V product from TMEM; a thread's row sum lives in the scale of the
-// last reference maximum it saw and the two teams' sums are merged at the end.
+// attn_tc3_kernel: one 128-query tile of one head per CTA and the softmax of attn_tc_kernel (eight warps on one key
+// tile, two threads per query row), but P never touches shared memory.  Clock stamps in attn_tc_kernel show that
+// its tile period (about 3000 cycles) is set as much by shared-memory bandwidth as by the softmax: a 128x128x16
+// product with both operands in shared memory reads 8 KB per 64 cycles, which is all the 128 B/clk an SM has, and
+// a key tile moves 224 KB through shared memory (Q, K and P, V operand reads, the TMA fill of K and V, the P store)
+// - 1750 cycles at best, and the products slow down to 130-160 cycles each.  Here P = exp2(S - m) goes back into
+// the TMEM columns of its S buffer as packed 16-bit pairs and is the A operand of the P V product from there
+// (160 KB per tile), S stays double-buffered, and S of tile t+2 is issued right behind the P V product of tile t, so
+// it is ready long before the softmax asks for it.
 namespace tc3 {
 constexpr int kQ = 0;
 constexpr int kK = kQ + 2 * kSubTileBytes;       // two stages
 constexpr int kV = kK + 4 * kSubTileBytes;       // two stages
 constexpr int kBar = kV + 4 * kSubTileBytes;
-constexpr int kXm = kBar + 256;                  // reference maximum after a tile: 2 tile parities x 128 rows
-constexpr int kXflag = kXm + 1024;               // tiles published: 2 teams x 128 rows
-constexpr int kXsum = kXflag + 1024;             // final (row sum, its scale): 2 teams x 128 rows
-constexpr int kTotal = kXsum + 2048;
+constexpr int kXmax = kBar + 256;                // row maxima: 2 tile parities x 2 halves x 128 rows of fp32
+constexpr int kXsum = kXmax + 2048;              // row sums: 2 halves x 128 rows
+constexpr int kXflag = kXsum + 1024;             // progress counters: 2 halves x 128 rows
+constexpr int kTotal = kXflag + 1024;
 enum { T3_Q_FULL = 0, T3_Q_EMPTY, T3_K_FULL0, T3_K_FULL1, T3_K_EMPTY0, T3_K_EMPTY1, T3_V_FULL0, T3_V_FULL1, T3_V_EMPTY0,
        T3_V_EMPTY1, T3_S_FULL0, T3_S_FULL1, T3_P_FULL0, T3_P_FULL1, T3_PV_DONE0, T3_PV_DONE1, T3_O_FULL, T3_N_BARS };
 }  // namespace tc3
@@ -926,9 +956,9 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
   const uint32_t bars = s_base + kBar;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBar + T3_N_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBar + T3_N_BARS * 8 + 8);
-  volatile float* xm = reinterpret_cast<volatile float*>(smem + kXm);
+  float* xmax = reinterpret_cast<float*>(smem + kXmax);
+  float* xsum = reinterpret_cast<float*>(smem + kXsum);
   volatile int* xflag = reinterpret_cast<volatile int*>(smem + kXflag);
-  volatile float* xsum = reinterpret_cast<volatile float*>(smem + kXsum);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -937,7 +967,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
   const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < T3_N_BARS; ++i) mbar_init(bar(i), (i == T3_P_FULL0 || i == T3_P_FULL1) ? 128u : 1u);
+    for (int i = 0; i < T3_N_BARS; ++i) mbar_init(bar(i), (i == T3_P_FULL0 || i == T3_P_FULL1) ? 256u : 1u);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -1075,12 +1105,15 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
     }
   } else {
     // ===================================================================== softmax / epilogue
-    const int team = warp >> 2, quad = warp & 3;
+    // Eight warps: warp w and warp w+4 own the same 32 query rows (TMEM lanes) and split the tile's 128 key columns
+    // in halves; they exchange their partial row maxima through shared memory.
+    const int quad = warp & 3, half = warp >> 2;
     const int row = quad * 32 + lane;
     const int64_t qi = i0 + row;
     const bool row_valid = qi < P.lq;
     const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
-    float m_seen = -INFINITY, l_part = 0.f;  // l_part is in the scale of m_seen (scaled log2 domain)
+    const int col0 = half * 64;
+    float m_ref = -INFINITY, l_part = 0.f;  // m_ref in the scaled log2 domain; l over this thread's columns
     int it = 0;
     bool ok = true;
     for (int st = 0; st < P.n_stage && ok; ++st) {
@@ -1102,126 +1135,89 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
         int tf, tl;
         if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
           for (int t = tf; t <= tl && ok; ++t, ++it) {
-            if ((it & 1) != team) continue;
             const int b = it & 1;
             const uint32_t tS = tmem + b * 128 + lane_base;
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 620));
             if (!ok) break;
             tc_fence_after();
+            float s[64];
+            tmem_ld32(tS + col0, reinterpret_cast<uint32_t*>(s));
+            tmem_ld32(tS + col0 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+            tmem_wait_ld();
+            // visible columns of this tile for this row: [c_lo, c_hi] in this thread's 64 columns
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
-            const int64_t lim = seg_j0 + G.len - 1;
+            const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
             const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
-            const int c_lo = (int)(a - jt);
-            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt));
-            const bool full = c_lo <= 0 && c_hi >= kTile - 1;
-            // ---- pass 1: row maximum of the raw scores.  Two 32-column loads are in flight at a time; the last
-            // two chunks stay in registers for pass 2
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            auto max_chunk = [&](const float* s, int cc) {
-              if (full) {
+            const int c_lo = (int)(a - jt) - col0;
+            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt)) - col0;
+            if (!(c_lo <= 0 && c_hi >= 63)) {
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                  mx4[0] = fmaxf(mx4[0], s[c]);
-                  mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                  mx4[2] = fmaxf(mx4[2], s[c + 2]);
-                  mx4[3] = fmaxf(mx4[3], s[c + 3]);
-                }
-              } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                  const int cg = cc * 32 + c;
-                  mx4[c & 3] = fmaxf(mx4[c & 3], (cg >= c_lo && cg <= c_hi) ? s[c] : -INFINITY);
-                }
-              }
-            };
-            float s0[32], s1[32];
-            tmem_ld32(tS, reinterpret_cast<uint32_t*>(s0));
-            tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s1));
-            tmem_wait_ld();
-            max_chunk(s0, 0);
-            tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s0));
-            max_chunk(s1, 1);
-            tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s1));
-            tmem_wait_ld();
-            max_chunk(s0, 2);
-            max_chunk(s1, 3);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * P.scale_log2;
-            // ---- the row's reference maximum after the previous tile, from the other team
-            float m_prev = -INFINITY;
-            if (it >= 1) {
-              ok = __all_sync(0xffffffffu, pair_wait(&xflag[(team ^ 1) * 128 + row], it, abort_flag, P.err, 621));
-              if (!ok) break;
-              m_prev = xm[((it - 1) & 1) * 128 + row];
+              for (int c = 0; c < 64; ++c) s[c] = (c >= c_lo && c <= c_hi) ? s[c] : -INFINITY;
             }
-            // lazy rescaling: the reference only moves when the row maximum grew by more than 2^8
-            float m_new = m_prev, alpha = 1.f;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+              mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
+              mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
+              mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
+              mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the other half's maximum of the same row
+            xmax[(it & 1) * 256 + half * 128 + row] = mx;
+            __threadfence_block();
+            xflag[half * 128 + row] = it + 1;
+            ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 621));
+            if (!ok) break;
+            mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
+            // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
+            float alpha = 1.f;
             bool resc = false;
-            if (mx > m_prev) {
-              if (m_prev == -INFINITY) {
-                m_new = mx;  // nothing accumulated for this row yet
-              } else if (mx - m_prev > 8.f) {
-                m_new = mx;
-                alpha = ex2_approx(m_prev - mx);
+            if (mx > m_ref) {
+              if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated for this row yet
+              } else if (mx - m_ref > 8.f) {
+                alpha = ex2_approx(m_ref - mx);
+                l_part *= alpha;
+                m_ref = mx;
                 resc = true;
               }
             }
-            xm[(it & 1) * 128 + row] = m_new;
-            __threadfence_block();
-            xflag[team * 128 + row] = it + 1;
-            if (m_seen != m_new) {
-              if (l_part != 0.f) l_part *= ex2_approx(m_seen - m_new);
-              m_seen = m_new;
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+            uint32_t pk[32];
+            float2 rs01 = make_float2(0.f, 0.f), rs23 = make_float2(0.f, 0.f);
+            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(neg_m, neg_m);
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+              const float2 a01 = ffma2(s[c], s[c + 1], sc2, nm2), a23 = ffma2(s[c + 2], s[c + 3], sc2, nm2);
+              const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
+              const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+              rs01 = fadd2(rs01, p01);
+              rs23 = fadd2(rs23, p23);
+              typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
+              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
+              pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
             }
+            l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
-              // O holds the products up to tile it-1: wait for the last of them, then scale this row
+              // O holds the products up to tile it-1: wait for the last of them, then scale this thread's 64 columns
               ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) & 1)), ((it - 1) >> 1) & 1, abort_flag,
                                                          P.err, 622));
               if (!ok) break;
               tc_fence_after();
 #pragma unroll
-              for (int cc = 0; cc < 4; ++cc) {
+              for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
-                tmem_ld32(tO + lane_base + cc * 32, o);
+                tmem_ld32(tO + lane_base + col0 + c * 32, o);
                 tmem_wait_ld();
 #pragma unroll
                 for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-                tmem_st32(tO + lane_base + cc * 32, o);
+                tmem_st32(tO + lane_base + col0 + c * 32, o);
               }
-              tmem_wait_st();
             }
-            // ---- pass 2: P = exp2(S * scale - m), two exponentials per instruction, packed 16-bit pairs; 32 keys of P
-            // go over S columns this thread has already consumed: keys 0-63 -> [0,32), keys 64-127 -> [64,96)
-            const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            auto exp_chunk = [&](const float* s, int cc) {
-              uint32_t pk[16];
-#pragma unroll
-              for (int c = 0; c < 32; c += 4) {
-                float a0 = fmaf(s[c], P.scale_log2, neg_m), a1 = fmaf(s[c + 1], P.scale_log2, neg_m);
-                float a2 = fmaf(s[c + 2], P.scale_log2, neg_m), a3 = fmaf(s[c + 3], P.scale_log2, neg_m);
-                if (!full) {
-                  const int cg = cc * 32 + c;
-                  a0 = (cg >= c_lo && cg <= c_hi) ? a0 : -INFINITY;
-                  a1 = (cg + 1 >= c_lo && cg + 1 <= c_hi) ? a1 : -INFINITY;
-                  a2 = (cg + 2 >= c_lo && cg + 2 <= c_hi) ? a2 : -INFINITY;
-                  a3 = (cg + 3 >= c_lo && cg + 3 <= c_hi) ? a3 : -INFINITY;
-                }
-                const float2 p01 = ex2_pair(a0, a1), p23 = ex2_pair(a2, a3);
-                rs4[0] += p01.x; rs4[1] += p01.y; rs4[2] += p23.x; rs4[3] += p23.y;
-                typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
-                pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
-                pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
-              }
-              tmem_st16(tS + (cc < 2 ? 16 * cc : 64 + 16 * (cc - 2)), pk);
-            };
-            exp_chunk(s0, 2);  // chunks 2 and 3 are still in registers
-            tmem_ld32(tS, reinterpret_cast<uint32_t*>(s0));
-            exp_chunk(s1, 3);
-            tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s1));
-            tmem_wait_ld();
-            exp_chunk(s0, 0);
-            exp_chunk(s1, 1);
-            l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            // this thread's 64 keys of P, packed, over the first half of the S columns it has consumed:
+            // keys 0-63 -> buffer columns [0,32), keys 64-127 -> [64,96)
+            tmem_st32(tS + col0, pk);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(T3_P_FULL0 + b));
@@ -1230,22 +1226,16 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
         seg_j0 += G.len;
       }
     }
-    // ---- epilogue: merge the two teams' row sums, O / l -> out (each team writes 64 columns), log-sum-exp
-    xsum[(team * 128 + row) * 2] = l_part;
-    xsum[(team * 128 + row) * 2 + 1] = m_seen;
+    // ---- epilogue: O / l -> out, log-sum-exp (each half writes its 64 output columns)
+    xsum[half * 128 + row] = l_part;
     __threadfence_block();
-    xflag[team * 128 + row] = kPairDone;
-    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(team ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 623));
-    const float l_o = xsum[((team ^ 1) * 128 + row) * 2], m_o = xsum[((team ^ 1) * 128 + row) * 2 + 1];
-    const float m_fin = fmaxf(m_seen, m_o);
-    float l_sum = 0.f;
-    if (l_part > 0.f) l_sum += l_part * ex2_approx(m_seen - m_fin);
-    if (l_o > 0.f) l_sum += l_o * ex2_approx(m_o - m_fin);
+    xflag[half * 128 + row] = kPairDone;
+    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 623));
+    const float l_sum = l_part + xsum[(half ^ 1) * 128 + row];
     if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_O_FULL), 0, abort_flag, P.err, 624));
     if (ok) {
       tc_fence_after();
       const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
-      const int col0 = team * 64;
       T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts + col0;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -1272,7 +1262,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
           }
         }
       }
-      if (team == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_fin + log2f(l_sum) : -INFINITY;
+      if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
     }
   }
   // ---- teardown
@@ -1768,7 +1758,7 @@ extern "C" int infllm_device_error(int* code, int* where) {
 extern "C" int infllm_tc_stamps(long long* h_out) {
   using namespace infllm;
   INFLLM_CUDA_OK(cudaDeviceSynchronize());
-  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 10 * 256));
+  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 20 * 256));
   return INFLLM_OK;
 }
 #endif

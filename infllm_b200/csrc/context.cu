@@ -1351,9 +1351,9 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
           INFLLM_TRY(attn_tc2_launch(TP, g.dtype, s));
         } else {
           TP.n_split = 1;
-          // flag bit 6 selects the experimental kernel whose softmax warps work as two teams on alternate key tiles
-          if (g.reserved[0] & 64) INFLLM_TRY(attn_tc3_launch(TP, g.dtype, s));
-          else INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
+          // default: P stays in TMEM; flag bit 6 selects the older kernel that passes P through shared memory
+          if (g.reserved[0] & 64) INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
+          else INFLLM_TRY(attn_tc3_launch(TP, g.dtype, s));
         }
       } else {
       AttnParams P{};

@@ -108,18 +108,18 @@ def _run(case, dtype=torch.bfloat16):
 
 
 @pytest.mark.parametrize("kernels", ["tcgen05", "generic", "tcgen05-nolookahead", "tcgen05-twohead", "tcgen05-nospec",
-                                     "tcgen05-twoteams"])
+                                     "tcgen05-psmem"])
 @pytest.mark.parametrize("name", D128)
 def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     """Both kernel families behind the exec-block loop — the tcgen05 kernels (default for blocks of more than
-    64 queries; three attention kernels: one head per CTA, the same with two softmax teams, two heads per CTA) and the shape-generic
+    64 queries; three attention kernels: one head per CTA with P through shared memory or kept in TMEM, two heads per CTA) and the shape-generic
     mma.sync kernels — and both ways of ranking the units of the next
     exec block (look-ahead with staged copies, or the device scorer with a host sync every block)."""
     monkeypatch.setenv("INFLLM_B200_NO_TC", "1" if kernels == "generic" else "0")
     monkeypatch.setenv("INFLLM_B200_NO_LOOKAHEAD", "1" if kernels.endswith("nolookahead") else "0")
     monkeypatch.setenv("INFLLM_B200_ATTN_TWO_HEAD", "1" if kernels.endswith("twohead") else "0")
     monkeypatch.setenv("INFLLM_B200_NO_DECODE_SPEC", "1" if kernels.endswith("nospec") else "0")
-    monkeypatch.setenv("INFLLM_B200_ATTN_TWO_TEAMS", "1" if kernels.endswith("twoteams") else "0")
+    monkeypatch.setenv("INFLLM_B200_ATTN_P_IN_SMEM", "1" if kernels.endswith("psmem") else "0")
     case = C.CASES[name]
     if (case["strategy"] == "lru-s" or case.get("chunk_topk")) and kernels not in ("tcgen05", "generic"):
         pytest.skip("lru-s and chunk_topk_calc rank, fetch and attend nothing ahead: the switches change nothing")
