@@ -26,7 +26,7 @@ __device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] block
 #ifdef INFLLM_TC_TIMING
 // development aid: per-iteration clock stamps of CTA (0,0): [role][iteration], roles 0 producer issue, 1 operands
 // arrived, 2 MMA committed, 3 accumulator seen by the compute warps, 4 compute done
-__device__ long long g_tc_stamps[20][256];
+__device__ long long g_tc_stamps[40][256];
 #define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
 #else
 #define TC_STAMP(role, it) do { } while (0)
@@ -77,6 +77,23 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   asm("{ .reg .b64 ra, rb, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; add.rn.f32x2 rd, ra, rb; mov.b64 {%0,%1}, rd; }"
       : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
+}
+
+// exp2 of a pair on the FMA and integer pipes (the special-function unit does 16 per clock per SM, which bounds the
+// softmax when every exponential goes there): x = n + f with n the nearest integer (magic-number rounding) and f in
+// [-0.5, 0.5], 2^f by a cubic (relative error 7e-4, below the rounding of a 16-bit P), n added into the exponent
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f), neg_magic = make_float2(-12582912.f, -12582912.f);
+  const float2 t = fadd2(x, magic);
+  const float2 n = fadd2(t, neg_magic);
+  const float2 f = fadd2(x, make_float2(-n.x, -n.y));
+  float2 p = ffma2(f.x, f.y, make_float2(0.0555041f, 0.0555041f), make_float2(0.2402265f, 0.2402265f));
+  p = ffma2(p.x, p.y, f, make_float2(0.6931472f, 0.6931472f));
+  p = ffma2(p.x, p.y, f, make_float2(1.f, 1.f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
 
 // two exponentials per special-function instruction: exp2 of a pair of fp32 arguments evaluated in fp16
@@ -947,7 +964,7 @@ enum { T3_Q_FULL = 0, T3_Q_EMPTY, T3_K_FULL0, T3_K_FULL1, T3_K_EMPTY0, T3_K_EMPT
 }  // namespace tc3
 
 template <typename T>
-__global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant__ AttnTcParams P) {
+__global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant__ AttnTcParams P) {
   using namespace tc3;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -1043,11 +1060,15 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
         }
       }
     }
-  } else if (warp == 9) {
-    // ========================================================================== MMA issuer
+  } else if (warp == 9 || warp == 10) {
+    // ========================================================================== MMA issuers
+    // Two threads: warp 10 issues S = Q K^T, warp 9 issues O += P V.  One thread doing both was the longest serial
+    // chain of a key tile (waits, 16 products that each hold the thread while the pipe is busy, commits: about
+    // 2500 cycles); apart they take about 1100 each and the softmax sets the pace.  What the tensor pipe ordered
+    // before - S of tile t+2 may overwrite its buffer only when P V of tile t has read P from it - is now the
+    // wait for that product's commit.
     if (lane == 0) {
-      // tiles per stage that has any, in order
-      int nt[kMaxStage], n_act = 0, n = 0;
+      int nt[kMaxStage], n_act = 0, n = 0;  // tiles per stage that has any, in order
       for (int st = 0; st < P.n_stage; ++st) {
         const TcStage& S = P.stage[st];
         int64_t vis_lo, vis_hi;
@@ -1057,51 +1078,53 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
         if (c > 0) nt[n_act++] = c, n += c;
       }
       bool ok = true;
-      int iq = 0, sq = 0, tq = 0;  // next S = Q K^T to issue: tile iq = tile tq of active stage sq
-      auto issue_qk = [&]() -> bool {
-        if (tq == 0 && !wait_or_abort(bar(T3_Q_FULL), sq & 1, abort_flag, P.err, 610)) return false;
-        const int b = iq & 1;
-        if (!wait_or_abort(bar(T3_K_FULL0 + b), (iq >> 1) & 1, abort_flag, P.err, 611)) return false;
-        tc_fence_after();
-        const uint32_t kt = sK + b * 2 * kSubTileBytes;
+      if (warp == 10) {
+        const uint64_t qd0 = make_sdesc(sQ, 16, 1024);
+        const uint64_t kd0[2] = {make_sdesc(sK, 16, 1024), make_sdesc(sK + 2 * kSubTileBytes, 16, 1024)};
+        int sq = 0, tq = 0;
+        for (int iq = 0; iq < n && ok; ++iq) {
+          const int b = iq & 1;
+          if (tq == 0) ok = wait_or_abort(bar(T3_Q_FULL), sq & 1, abort_flag, P.err, 610);
+          if (ok) ok = wait_or_abort(bar(T3_K_FULL0 + b), (iq >> 1) & 1, abort_flag, P.err, 611);
+          if (ok && iq >= 2) ok = wait_or_abort(bar(T3_PV_DONE0 + b), ((iq >> 1) - 1) & 1, abort_flag, P.err, 614);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          uint64_t ad = make_sdesc(sQ + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-          uint64_t bd = make_sdesc(kt + (ks >> 2) * kSubTileBytes + (ks & 3) * 32, 16, 1024);
-          mma_ss(tmem + b * 128, ad, bd, idesc_qk, ks > 0);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t off = (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4);
+            mma_ss(tmem + b * 128, qd0 + off, kd0[b] + off, idesc_qk, ks > 0);
+          }
+          tc_commit(bar(T3_S_FULL0 + b));
+          tc_commit(bar(T3_K_EMPTY0 + b));
+          TC_STAMP(10, iq);
+          if (++tq == nt[sq]) {
+            tc_commit(bar(T3_Q_EMPTY));  // the last product that reads this stage's Q tile
+            ++sq;
+            tq = 0;
+          }
         }
-        tc_commit(bar(T3_S_FULL0 + b));
-        tc_commit(bar(T3_K_EMPTY0 + b));
-        if (++tq == nt[sq]) {
-          tc_commit(bar(T3_Q_EMPTY));  // the last product that reads this stage's Q tile
-          ++sq;
-          tq = 0;
-        }
-        ++iq;
-        return true;
-      };
-      if (n >= 1) ok = issue_qk();
-      if (ok && n >= 2) ok = issue_qk();
-      for (int ip = 0; ip < n && ok; ++ip) {
-        const int b = ip & 1;
-        ok = wait_or_abort(bar(T3_P_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 612) &&
-             wait_or_abort(bar(T3_V_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 613);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t vt = sV + b * 2 * kSubTileBytes;
+      } else {
+        const uint64_t vd0[2] = {make_sdesc(sV, kSubTileBytes, 1024), make_sdesc(sV + 2 * kSubTileBytes, kSubTileBytes, 1024)};
+        for (int ip = 0; ip < n && ok; ++ip) {
+          const int b = ip & 1;
+          ok = wait_or_abort(bar(T3_P_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 612);
+          TC_STAMP(9, ip);
+          ok = ok && wait_or_abort(bar(T3_V_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 613);
+          if (!ok) break;
+          TC_STAMP(11, ip);
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // A = P from TMEM: keys 0-63 in the buffer's columns [0,32), keys 64-127 in [64,96)
-          const uint32_t a_t = tmem + b * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
-          uint64_t bd = make_sdesc(vt + ks * 2048, kSubTileBytes, 1024);
-          mma_ts(tO, a_t, bd, idesc_pv, (ip > 0) || (ks > 0));
+          for (int ks = 0; ks < 8; ++ks) {
+            // A = P from TMEM: keys 0-63 in the buffer's columns [0,32), keys 64-127 in [64,96)
+            const uint32_t a_t = tmem + b * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
+            mma_ts(tO, a_t, vd0[b] + (uint64_t)((ks * 2048) >> 4), idesc_pv, (ip > 0) || (ks > 0));
+          }
+          tc_commit(bar(T3_V_EMPTY0 + b));
+          tc_commit(bar(T3_PV_DONE0 + b));
+          TC_STAMP(19, ip);
         }
-        tc_commit(bar(T3_V_EMPTY0 + b));
-        tc_commit(bar(T3_PV_DONE0 + b));
-        // the tensor pipe runs in issue order: this S overwrites the P that the product above has read
-        if (iq < n) ok = issue_qk();
+        if (ok) tc_commit(bar(T3_O_FULL));
       }
-      if (ok) tc_commit(bar(T3_O_FULL));
     }
   } else {
     // ===================================================================== softmax / epilogue
@@ -1139,11 +1162,14 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
             const uint32_t tS = tmem + b * 128 + lane_base;
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 620));
             if (!ok) break;
+            if (threadIdx.x == 0) TC_STAMP(12, it);
+            if (lane == 0) TC_STAMP(28 + warp, it);
             tc_fence_after();
             float s[64];
             tmem_ld32(tS + col0, reinterpret_cast<uint32_t*>(s));
             tmem_ld32(tS + col0 + 32, reinterpret_cast<uint32_t*>(s) + 32);
             tmem_wait_ld();
+            if (threadIdx.x == 0) TC_STAMP(13, it);
             // visible columns of this tile for this row: [c_lo, c_hi] in this thread's 64 columns
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
             const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
@@ -1170,6 +1196,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
             ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 621));
             if (!ok) break;
             mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
+            if (threadIdx.x == 0) TC_STAMP(14, it);
             // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
             float alpha = 1.f;
             bool resc = false;
@@ -1191,7 +1218,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
             for (int c = 0; c < 64; c += 4) {
               const float2 a01 = ffma2(s[c], s[c + 1], sc2, nm2), a23 = ffma2(s[c + 2], s[c + 3], sc2, nm2);
               const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
-              const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
+              const float2 p23 = ex2_poly2(a23);  // every second pair off the special-function unit
               rs01 = fadd2(rs01, p01);
               rs23 = fadd2(rs23, p23);
               typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
@@ -1199,6 +1226,7 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
               pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
             }
             l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
+            if (threadIdx.x == 0) TC_STAMP(15, it);
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
               // O holds the products up to tile it-1: wait for the last of them, then scale this thread's 64 columns
               ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) & 1)), ((it - 1) >> 1) & 1, abort_flag,
@@ -1219,8 +1247,11 @@ __global__ void __launch_bounds__(320, 1) attn_tc3_kernel(const __grid_constant_
             // keys 0-63 -> buffer columns [0,32), keys 64-127 -> [64,96)
             tmem_st32(tS + col0, pk);
             tmem_wait_st();
+            if (threadIdx.x == 0) TC_STAMP(16, it);
             tc_fence_before();
             mbar_arrive(bar(T3_P_FULL0 + b));
+            if (threadIdx.x == 0) TC_STAMP(17, it);
+            if (lane == 0) TC_STAMP(20 + warp, it);
           }
         }
         seg_j0 += G.len;
@@ -1643,7 +1674,7 @@ int attn_tc3_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
       INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       attr_set[dtype] = true;
     }
-    kern<<<grid, 320, smem, s>>>(P);
+    kern<<<grid, 352, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("attn_tc3_kernel");
   return INFLLM_OK;
@@ -1758,7 +1789,7 @@ extern "C" int infllm_device_error(int* code, int* where) {
 extern "C" int infllm_tc_stamps(long long* h_out) {
   using namespace infllm;
   INFLLM_CUDA_OK(cudaDeviceSynchronize());
-  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 20 * 256));
+  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 40 * 256));
   return INFLLM_OK;
 }
 #endif
