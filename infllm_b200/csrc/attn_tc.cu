@@ -948,8 +948,8 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
 // a key tile moves 224 KB through shared memory (Q, K and P, V operand reads, the TMA fill of K and V, the P store)
 // - 1750 cycles at best, and the products slow down to 130-160 cycles each.  Here P = exp2(S - m) goes back into
 // the TMEM columns of its S buffer as packed 16-bit pairs and is the A operand of the P V product from there
-// (160 KB per tile), S stays double-buffered, and S of tile t+2 is issued right behind the P V product of tile t, so
-// it is ready long before the softmax asks for it.
+// (160 KB per tile), and there are three S/P buffers in TMEM, so that S of tile t+2 does not have to wait for the P V
+// product of tile t and is ready long before the softmax asks for it.
 namespace tc3 {
 constexpr int kQ = 0;
 constexpr int kK = kQ + 2 * kSubTileBytes;       // two stages
@@ -960,7 +960,8 @@ constexpr int kXsum = kXmax + 2048;              // row sums: 2 halves x 128 row
 constexpr int kXflag = kXsum + 1024;             // progress counters: 2 halves x 128 rows
 constexpr int kTotal = kXflag + 1024;
 enum { T3_Q_FULL = 0, T3_Q_EMPTY, T3_K_FULL0, T3_K_FULL1, T3_K_EMPTY0, T3_K_EMPTY1, T3_V_FULL0, T3_V_FULL1, T3_V_EMPTY0,
-       T3_V_EMPTY1, T3_S_FULL0, T3_S_FULL1, T3_P_FULL0, T3_P_FULL1, T3_PV_DONE0, T3_PV_DONE1, T3_O_FULL, T3_N_BARS };
+       T3_V_EMPTY1, T3_S_FULL0, T3_S_FULL1, T3_S_FULL2, T3_P_FULL0, T3_P_FULL1, T3_P_FULL2, T3_PV_DONE0, T3_PV_DONE1, T3_PV_DONE2,
+       T3_O_FULL, T3_N_BARS };
 }  // namespace tc3
 
 template <typename T>
@@ -984,7 +985,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
   const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < T3_N_BARS; ++i) mbar_init(bar(i), (i == T3_P_FULL0 || i == T3_P_FULL1) ? 256u : 1u);
+    for (int i = 0; i < T3_N_BARS; ++i) mbar_init(bar(i), (i >= T3_P_FULL0 && i <= T3_P_FULL2) ? 256u : 1u);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -997,7 +998,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tO = tmem + 256;  // S/P buffers at columns [0,128) and [128,256)
+  const uint32_t tO = tmem + 384;  // three S/P buffers at columns [0,128), [128,256), [256,384)
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
   constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
@@ -1029,6 +1030,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               if (it >= 2) ok = wait_or_abort(bar(T3_K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 601);
               if (!ok) break;
               const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
+              TC_STAMP(37, it);
               mbar_expect_tx(bar(T3_K_FULL0 + b), 2 * kSubTileBytes);
               if (G.c3_k < 0) {
                 tma_load_3d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv);
@@ -1039,6 +1041,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               }
               if (it >= 2) ok = wait_or_abort(bar(T3_V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 602);
               if (!ok) break;
+              TC_STAMP(38, it);
               mbar_expect_tx(bar(T3_V_FULL0 + b), 2 * kSubTileBytes);
               if (G.c3_v < 0) {
                 tma_load_3d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv);
@@ -1084,17 +1087,21 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         int sq = 0, tq = 0;
         for (int iq = 0; iq < n && ok; ++iq) {
           const int b = iq & 1;
+          TC_STAMP(8, iq);
           if (tq == 0) ok = wait_or_abort(bar(T3_Q_FULL), sq & 1, abort_flag, P.err, 610);
           if (ok) ok = wait_or_abort(bar(T3_K_FULL0 + b), (iq >> 1) & 1, abort_flag, P.err, 611);
-          if (ok && iq >= 2) ok = wait_or_abort(bar(T3_PV_DONE0 + b), ((iq >> 1) - 1) & 1, abort_flag, P.err, 614);
+          TC_STAMP(18, iq);
+          const int b3 = iq % 3;  // S/P buffer: free once the P V product of tile iq-3 has read P from it
+          if (ok && iq >= 3) ok = wait_or_abort(bar(T3_PV_DONE0 + b3), ((iq / 3) - 1) & 1, abort_flag, P.err, 614);
           if (!ok) break;
+          TC_STAMP(36, iq);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t off = (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4);
-            mma_ss(tmem + b * 128, qd0 + off, kd0[b] + off, idesc_qk, ks > 0);
+            mma_ss(tmem + b3 * 128, qd0 + off, kd0[b] + off, idesc_qk, ks > 0);
           }
-          tc_commit(bar(T3_S_FULL0 + b));
+          tc_commit(bar(T3_S_FULL0 + b3));
           tc_commit(bar(T3_K_EMPTY0 + b));
           TC_STAMP(10, iq);
           if (++tq == nt[sq]) {
@@ -1107,7 +1114,8 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         const uint64_t vd0[2] = {make_sdesc(sV, kSubTileBytes, 1024), make_sdesc(sV + 2 * kSubTileBytes, kSubTileBytes, 1024)};
         for (int ip = 0; ip < n && ok; ++ip) {
           const int b = ip & 1;
-          ok = wait_or_abort(bar(T3_P_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 612);
+          const int b3 = ip % 3;
+          ok = wait_or_abort(bar(T3_P_FULL0 + b3), (ip / 3) & 1, abort_flag, P.err, 612);
           TC_STAMP(9, ip);
           ok = ok && wait_or_abort(bar(T3_V_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 613);
           if (!ok) break;
@@ -1116,11 +1124,11 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A = P from TMEM: keys 0-63 in the buffer's columns [0,32), keys 64-127 in [64,96)
-            const uint32_t a_t = tmem + b * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
+            const uint32_t a_t = tmem + b3 * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
             mma_ts(tO, a_t, vd0[b] + (uint64_t)((ks * 2048) >> 4), idesc_pv, (ip > 0) || (ks > 0));
           }
           tc_commit(bar(T3_V_EMPTY0 + b));
-          tc_commit(bar(T3_PV_DONE0 + b));
+          tc_commit(bar(T3_PV_DONE0 + b3));
           TC_STAMP(19, ip);
         }
         if (ok) tc_commit(bar(T3_O_FULL));
@@ -1158,9 +1166,9 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         int tf, tl;
         if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
           for (int t = tf; t <= tl && ok; ++t, ++it) {
-            const int b = it & 1;
-            const uint32_t tS = tmem + b * 128 + lane_base;
-            ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 620));
+            const int b3 = it % 3;
+            const uint32_t tS = tmem + b3 * 128 + lane_base;
+            ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b3), (it / 3) & 1, abort_flag, P.err, 620));
             if (!ok) break;
             if (threadIdx.x == 0) TC_STAMP(12, it);
             if (lane == 0) TC_STAMP(28 + warp, it);
@@ -1229,7 +1237,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             if (threadIdx.x == 0) TC_STAMP(15, it);
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
               // O holds the products up to tile it-1: wait for the last of them, then scale this thread's 64 columns
-              ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) & 1)), ((it - 1) >> 1) & 1, abort_flag,
+              ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) % 3)), ((it - 1) / 3) & 1, abort_flag,
                                                          P.err, 622));
               if (!ok) break;
               tc_fence_after();
@@ -1249,7 +1257,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             tmem_wait_st();
             if (threadIdx.x == 0) TC_STAMP(16, it);
             tc_fence_before();
-            mbar_arrive(bar(T3_P_FULL0 + b));
+            mbar_arrive(bar(T3_P_FULL0 + b3));
             if (threadIdx.x == 0) TC_STAMP(17, it);
             if (lane == 0) TC_STAMP(20 + warp, it);
           }
