@@ -372,7 +372,7 @@ def run_ours(args, rank, world, local_rank):
         roofline=dict(bound="tensor", kernel="exec-block attention (local + global stage)", achieved=achieved,
                       peak=tf_peak, unit="TFLOP/s", frac=(achieved / tf_peak if achieved else None),
                       # DRAM bytes per launch of a steady-state exec block from an ncu capture of this kernel on a
-                      # 32768-token prompt (profiles/attn_tc3_kernel_exec_block.md); a launch at 131072 tokens
+                      # 32768-token prompt (its summary is kept with the other profiles); a launch at 131072 tokens
                       # reads the same operands.  None when the heads are sharded (other shapes per launch).
                       traffic=(37.45e6 if groups == 1 else None), traffic_source="ncu, 32768-token case",
                       peak_source=f"bf16_tflops_sustained of {which}", launches=int(attn_n),
