@@ -364,6 +364,9 @@ def run_ours(args, rank, world, local_rank):
                              "in 8192-token calls, exec 512, n_init 128, n_local 4096, unit 128, topk 16, repr_topk 4, "
                              f"max_cached {CFG['max_cached']}, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
                     replicas=world // groups,
+                    store=("pinned host store + a device copy of its first "
+                           f"{os.environ.get('INFLLM_B200_DEVICE_STORE_MB', '4096')} MiB per layer (cache refills of "
+                           "those units are device-to-device copies; 0 = host store only)"),
                     parallelism=(f"kv-head groups x{groups}: one layer over all GPUs, retrieval scores and output "
                                  "projection all-reduced (NCCL)") if groups > 1 else f"dp{world}: one layer replica per GPU"),
         e2e=dict(value=e2e, unit="tokens/s", h2d_bytes_per_step=int(hidden.numel() * 2),

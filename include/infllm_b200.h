@@ -238,6 +238,9 @@ typedef struct infllm_config {
                            *     (default: P stays in TMEM and feeds the P V product from there)
                            * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
                            * at most 8); the cache gets that many times topk spare slots
+                           * reserved[3] > 0: MiB of device memory for a copy of the store's first units (512 KiB per
+                           * unit at 8 KV heads); a cache refill of such a unit is a device-to-device copy instead of a
+                           * copy over PCIe.  0: every refill comes from the pinned host store, as in the reference
                            * reserved[2] > 0: chunk_topk_calc (context_manager.py:749-770, 548-610), in tokens: a call
                            * of more than one token is cut into chunks of this size rounded down to whole exec blocks,
                            * and every exec block of a chunk retrieves among the units sealed when the chunk started */

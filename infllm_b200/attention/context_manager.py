@@ -76,6 +76,9 @@ class ContextManager:
             torch.cuda.current_device(), shard_rank=0, shard_world=1)
         if self.chunk_topk_calc is not None:
             cfg.reserved[2] = int(self.chunk_topk_calc)  # context_manager.py:749-770
+        # a copy of the store's first units in device memory (MiB per batch element and layer): refills of those
+        # units do not cross PCIe.  0 keeps every sealed unit on the host only, as the reference does.
+        cfg.reserved[3] = int(os.environ.get("INFLLM_B200_DEVICE_STORE_MB", "4096"))
         if os.environ.get("INFLLM_B200_NO_TC", "0") == "1":
             cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
         if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":

@@ -277,6 +277,15 @@ struct infllm_ctx {
   infllm_ctx_info counters{};
 
   char* host_unit(int64_t b) { return (char*)slabs[b / slab_units] + (b % slab_units) * unit_bytes; }
+  // Device copy of the store.  The reference keeps sealed units on the host because its GPUs have tens of GB; with
+  // 180 GB of HBM a copy of the first dev_cap units stays on the device as well, and a cache refill of such a unit is
+  // a device-to-device copy instead of a trip over PCIe.  Nothing else changes: the cache, its LRU order and the host
+  // store are what they were.  Units [0, dev_units) have a device copy.
+  std::vector<void*> dev_slabs;
+  int64_t dev_cap = 0, dev_units = 0;
+  bool dev_resident(int64_t b) const { return b < dev_units; }
+  char* dev_unit(int64_t b) { return (char*)dev_slabs[b / slab_units] + (b % slab_units) * unit_bytes; }
+  const char* unit_src(int64_t b) { return dev_resident(b) ? dev_unit(b) : host_unit(b); }
 };
 
 namespace {
@@ -447,6 +456,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   c->slot_ev.assign(n_slots, nullptr);
   c->slot_ev_used.assign(n_slots, 0);
   c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
+  c->dev_cap = (int64_t)g.reserved[3] * (1ll << 20) / c->unit_bytes;  // device copy of the store, in units
   c->initialized = true;
   return INFLLM_OK;
 }
@@ -661,9 +671,9 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
       INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
       c->d2h_synced_upto = c->num_blocks;
     }
-    src.push_back(c->host_unit(b));
+    src.push_back(c->unit_src(b));
     dst.push_back((char*)c->cache + (int64_t)slot * c->unit_bytes);
-    c->counters.h2d_bytes += c->unit_bytes;
+    if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
     c->staged_pending = true;
   }
   if (!src.empty()) {
@@ -672,7 +682,7 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     if (!(g.reserved[0] & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
                                  // SM copy kernel, which is faster alone but slows concurrent attention down
       for (size_t i = 0; i < src.size(); ++i) {
-        INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+        INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyDefault, c->copy_stream));
         INFLLM_TRY(mark_slot_copy(c, dst[i]));
       }
     } else {
@@ -831,9 +841,9 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       c->d2h_synced_upto_urgent = c->num_blocks;
     }
     // on a stream of its own: the exec block must not wait behind the copies staged for later blocks
-    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->host_unit(b), c->unit_bytes,
-                                   cudaMemcpyHostToDevice, c->urgent_stream));
-    c->counters.h2d_bytes += c->unit_bytes;
+    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->unit_src(b), c->unit_bytes,
+                                   cudaMemcpyDefault, c->urgent_stream));
+    if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
   }
   // look-ahead copies that were not wanted: their slots go back to the pool (later copies into them are
   // ordered behind the unfinished ones on the side stream; no kernel reads them)
@@ -893,7 +903,7 @@ int decode_fetch_ahead(infllm_ctx* c, const std::vector<int32_t>& retrieval, con
       c->d2h_synced_upto = c->num_blocks;
     }
     void* dst = (char*)c->cache + (int64_t)slot * c->unit_bytes;
-    INFLLM_CUDA_OK(cudaMemcpyAsync(dst, c->host_unit(b), c->unit_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+    INFLLM_CUDA_OK(cudaMemcpyAsync(dst, c->unit_src(b), c->unit_bytes, cudaMemcpyDefault, c->copy_stream));
     INFLLM_TRY(mark_slot_copy(c, dst));
     c->staged[b] = slot;
     c->staged_for[b] = INT64_MAX;
@@ -989,6 +999,35 @@ int seal_apply(infllm_ctx* c, const SealPlan& sp, cudaStream_t s) {
 
 // second half of sealing: the new units' K/V go to the host store.  `first` is the id of the first new unit,
 // `tok0` its first token (absolute); called after the units were counted in.
+// device slabs for units [0, n): allocated as the store grows; when the device has no room the copy stops growing
+int ensure_dev_units(infllm_ctx* c, int64_t n) {
+  const size_t bytes = (size_t)(c->slab_units * c->unit_bytes);
+  while ((int64_t)c->dev_slabs.size() * c->slab_units < n) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      c->dev_cap = c->dev_units;
+      return INFLLM_E_NOMEM;
+    }
+    c->dev_slabs.push_back(p);
+  }
+  return INFLLM_OK;
+}
+
+// after the host store was filled by the host (synthetic load, restore from a file): the device copy of its head
+int fill_dev_store(infllm_ctx* c, int64_t n_units) {
+  const int64_t n = std::min(n_units, c->dev_cap);
+  c->dev_units = 0;
+  if (n <= 0 || ensure_dev_units(c, n) != INFLLM_OK) return INFLLM_OK;
+  for (int64_t b0 = 0; b0 < n;) {
+    const int64_t run = std::min(n - b0, c->slab_units - b0 % c->slab_units);
+    INFLLM_CUDA_OK(cudaMemcpy(c->dev_unit(b0), c->host_unit(b0), (size_t)(run * c->unit_bytes), cudaMemcpyHostToDevice));
+    b0 += run;
+  }
+  c->dev_units = n;
+  return INFLLM_OK;
+}
+
 int seal_offload(infllm_ctx* c, int64_t first, int n_new, int64_t tok0, cudaStream_t s) {
   if (n_new <= 0) return INFLLM_OK;
   const infllm_config& g = c->cfg;
@@ -1009,6 +1048,13 @@ int seal_offload(infllm_ctx* c, int64_t first, int n_new, int64_t tok0, cudaStre
       const int run = (int)std::min<int64_t>(n - i, c->slab_units - b0 % c->slab_units);
       INFLLM_CUDA_OK(cudaMemcpyAsync(c->host_unit(b0), (char*)c->pack_buf[r] + (int64_t)i * c->unit_bytes,
                                      (int64_t)run * c->unit_bytes, cudaMemcpyDeviceToHost, c->d2h_stream));
+      // the device copy of the store grows with the same runs while it has room (readers order themselves behind
+      // ev_d2h exactly as they do for the host copy)
+      if (b0 == c->dev_units && b0 + run <= c->dev_cap && ensure_dev_units(c, b0 + run) == INFLLM_OK) {
+        INFLLM_CUDA_OK(cudaMemcpyAsync(c->dev_unit(b0), (char*)c->pack_buf[r] + (int64_t)i * c->unit_bytes,
+                                       (int64_t)run * c->unit_bytes, cudaMemcpyDeviceToDevice, c->d2h_stream));
+        c->dev_units = b0 + run;
+      }
       i += run;
     }
     c->counters.d2h_bytes += (int64_t)n * c->unit_bytes;
@@ -1517,6 +1563,8 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   }
   c->d2h_synced_upto = 0;
   c->d2h_synced_upto_urgent = 0;
+  c->dev_units = 0;
+  c->dev_cap = (int64_t)c->cfg.reserved[3] * (1ll << 20) / std::max<int64_t>(c->unit_bytes, 1);
   c->d2h_recorded = false;
   c->pack_used[0] = c->pack_used[1] = false;
   c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
@@ -1591,6 +1639,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     for (cudaEvent_t e : c->slot_ev)
       if (e) cudaEventDestroy(e);
     for (void* p : c->slabs) cudaFreeHost(p);
+    for (void* p : c->dev_slabs) cudaFree(p);
     cudaStreamDestroy(c->copy_stream);
     cudaEventDestroy(c->ev_main);
     cudaEventDestroy(c->ev_copy);
@@ -1756,6 +1805,7 @@ extern "C" int infllm_ctx_load_synthetic(infllm_ctx* c, int64_t n_units, const v
   const int64_t D = g.head_dim, HKV = g.n_kv_heads;
   INFLLM_TRY(ensure_host_units(c, n_units));
   for (int64_t b = 0; b < n_units; ++b) memcpy(c->host_unit(b), (const char*)h_units + b * c->unit_bytes, c->unit_bytes);
+  INFLLM_TRY(fill_dev_store(c, n_units));
   INFLLM_TRY(ensure_block_k(c, n_units, s));
   INFLLM_CUDA_OK(cudaMemcpyAsync(c->block_k, h_block_k, n_units * c->width * c->esz, cudaMemcpyHostToDevice, s));
   if (g.n_init > 0) {
@@ -1969,6 +2019,7 @@ extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
   if (ok && ensure_host_units(c, n_units) != INFLLM_OK) ok = false;
   for (int64_t b = 0; ok && b < n_units; ++b) ok = get(f, c->host_unit(b), (size_t)c->unit_bytes);
   fclose(f);
+  if (ok && fill_dev_store(c, n_units) != INFLLM_OK) ok = false;
   if (!ok) {
     infllm_ctx_reset(c);
     return fail(INFLLM_E_CUDA, "ctx_load: reading %s failed", path);

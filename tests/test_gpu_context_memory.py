@@ -108,7 +108,7 @@ def _run(case, dtype=torch.bfloat16):
 
 
 @pytest.mark.parametrize("kernels", ["tcgen05", "generic", "tcgen05-nolookahead", "tcgen05-twohead", "tcgen05-nospec",
-                                     "tcgen05-psmem"])
+                                     "tcgen05-psmem", "tcgen05-hoststore"])
 @pytest.mark.parametrize("name", D128)
 def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     """Both kernel families behind the exec-block loop — the tcgen05 kernels (default for blocks of more than
@@ -120,8 +120,10 @@ def test_context_memory_matches_oracle(name, kernels, monkeypatch):
     monkeypatch.setenv("INFLLM_B200_ATTN_TWO_HEAD", "1" if kernels.endswith("twohead") else "0")
     monkeypatch.setenv("INFLLM_B200_NO_DECODE_SPEC", "1" if kernels.endswith("nospec") else "0")
     monkeypatch.setenv("INFLLM_B200_ATTN_P_IN_SMEM", "1" if kernels.endswith("psmem") else "0")
+    # default: refills come from the device copy of the store; "hoststore": from the pinned host store only
+    monkeypatch.setenv("INFLLM_B200_DEVICE_STORE_MB", "0" if kernels.endswith("hoststore") else "4096")
     case = C.CASES[name]
-    if (case["strategy"] == "lru-s" or case.get("chunk_topk")) and kernels not in ("tcgen05", "generic"):
+    if (case["strategy"] == "lru-s" or case.get("chunk_topk")) and kernels not in ("tcgen05", "generic", "tcgen05-hoststore"):
         pytest.skip("lru-s and chunk_topk_calc rank, fetch and attend nothing ahead: the switches change nothing")
     cm, ora, stats = _run(case)
     from infllm_b200 import _lib
