@@ -584,7 +584,9 @@ def run_decode(args, rank, world, local_rank):
                               achieved_gbs=(dec_bytes / (dec_ms / 1e3) / 1e9 if dec_ms > 0 else None),
                               us_per_launch=1e3 * dec_ms / max(dec_n, 1), bytes_per_launch=dec_bytes / max(dec_n, 1)),
         store=dict(hits=hits, misses=misses, miss_rate=misses / max(hits + misses, 1),
-                   h2d_bytes_per_token_layer=misses * 524288 / max(per_layer, 1)),
+                   refill_bytes_per_token_layer=misses * 524288 / max(per_layer, 1),
+                   refill_source=("device copy of the store (INFLLM_B200_DEVICE_STORE_MB="
+                                  f"{os.environ.get('INFLLM_B200_DEVICE_STORE_MB', '4096')}); host store beyond it")),
         clocks=clocks)
     if rank == 0 and world == 1 and not args.no_cpu:
         v, secs, cores = cpu_decode_sample()
