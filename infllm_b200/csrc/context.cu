@@ -997,8 +997,6 @@ int seal_apply(infllm_ctx* c, const SealPlan& sp, cudaStream_t s) {
   return INFLLM_OK;
 }
 
-// second half of sealing: the new units' K/V go to the host store.  `first` is the id of the first new unit,
-// `tok0` its first token (absolute); called after the units were counted in.
 // device slabs for units [0, n): allocated as the store grows; when the device has no room the copy stops growing
 int ensure_dev_units(infllm_ctx* c, int64_t n) {
   const size_t bytes = (size_t)(c->slab_units * c->unit_bytes);
@@ -1028,6 +1026,8 @@ int fill_dev_store(infllm_ctx* c, int64_t n_units) {
   return INFLLM_OK;
 }
 
+// second half of sealing: the new units' K/V go to the host store.  `first` is the id of the first new unit,
+// `tok0` its first token (absolute); called after the units were counted in.
 int seal_offload(infllm_ctx* c, int64_t first, int n_new, int64_t tok0, cudaStream_t s) {
   if (n_new <= 0) return INFLLM_OK;
   const infllm_config& g = c->cfg;
