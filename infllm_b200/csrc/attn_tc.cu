@@ -949,7 +949,9 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
 // - 1750 cycles at best, and the products slow down to 130-160 cycles each.  Here P = exp2(S - m) goes back into
 // the TMEM columns of its S buffer as packed 16-bit pairs and is the A operand of the P V product from there
 // (160 KB per tile), and there are three S/P buffers in TMEM, so that S of tile t+2 does not have to wait for the P V
-// product of tile t and is ready long before the softmax asks for it.
+// product of tile t.  Eleven warps: eight softmax warps, the TMA producer, and one issuing thread per product (one
+// thread for both was the longest serial chain of a tile).  Every second pair of exponentials is a cubic on the FMA
+// pipe.  88 us per exec block of the 128K prefill against 104 us for attn_tc_kernel.
 namespace tc3 {
 constexpr int kQ = 0;
 constexpr int kK = kQ + 2 * kSubTileBytes;       // two stages
