@@ -314,6 +314,24 @@ def sample_clocks_stop(p, f):
     return dict(sm_mhz=med, sm_max_mhz=mx or None, reasons=sorted(reasons), samples=len(sm))
 
 
+def profile_traffic(name):
+    """DRAM bytes per launch (read + write) from the ncu summary kept under profiles/<name>.md, or None."""
+    import re
+
+    try:
+        text = open(os.path.join(ROOT, "profiles", name + ".md")).read()
+    except OSError:
+        return None
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    total = 0.0
+    for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        m = re.search(re.escape(key) + r" \[(\w+)\] = ([0-9.]+)", text)
+        if not m or m.group(1) not in unit:
+            return None
+        total += float(m.group(2)) * unit[m.group(1)]
+    return total
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -322,11 +340,15 @@ def measured_peaks():
     return 1400.0, 6650.0, "fallback"
 
 
-def run_ours(args, rank, world, local_rank):
+def run_ours(args, rank, world, local_rank, device_store_mb=0, light=False):
+    """The prefill workload.  device_store_mb = 0 (the headline): sealed units live in the pinned host store only and
+    every cache refill is a cudaMemcpyAsync over PCIe on a side stream, as in the reference.  > 0: the variant that
+    also keeps a device copy of the store (refills are device-to-device copies).  `light` skips the end-to-end pass,
+    the overlap trace and the CPU sample."""
     import torch.distributed as dist
 
     from infllm_b200 import _lib
-    from infllm_b200.attention import ATTN_FORWRAD, RotaryEmbeddingESM
+    from infllm_b200.attention import ATTN_FORWRAD, ContextManager, RotaryEmbeddingESM, device_store_reserve
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -341,7 +363,9 @@ def run_ours(args, rank, world, local_rank):
         comm = HeadGroupComm()
     fwd = ATTN_FORWRAD["inf-llm"](n_local=CFG["n_local"], n_init=CFG["n_init"], topk=CFG["topk"], block_size=CFG["bs"],
                                   max_cached_block=CFG["max_cached"], exc_block_size=CFG["exc"], fattn=True,
-                                  repr_topk=CFG["repr_topk"], head_group_comm=comm)
+                                  repr_topk=CFG["repr_topk"], head_group_comm=comm, device_store_mb=device_store_mb)
+    if device_store_mb:
+        device_store_reserve(device_store_mb, dev)
     full = make_weights(dev, torch.bfloat16)  # the planted directions are built from the whole projections
     layer = Layer(dev, fwd, RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0), rank=rank if groups > 1 else 0, world=groups)
     hidden = make_hidden(tokens, seed=0 if groups > 1 else rank, weights=full, device=dev)
@@ -385,11 +409,26 @@ def run_ours(args, rank, world, local_rank):
         host_us = layer.pkv.host_timers()
         layer.pkv.profile(False)
         clocks = sample_clocks_stop(clk_p, clk_f)
-        for _ in range(min(args.warmup, 1)):
-            prefill_host(layer, h_hidden, h_out, pipe)
-        ms_e2e = timed(lambda: (prefill_host(layer, h_hidden, h_out, pipe), h_out[0, -1, 0].item()), args.steps)
+        overlap = None
+        if not light:
+            # one more prompt with the event trace on (untimed): where the refill copies ran relative to the attention
+            layer.pkv.trace(True)
+            prefill_device(layer, hidden)
+            overlap = ContextManager.refill_overlap(layer.pkv.get_trace())
+            layer.pkv.trace(False)
+        ms_e2e = None
+        if not light:
+            for _ in range(min(args.warmup, 1)):
+                prefill_host(layer, h_hidden, h_out, pipe)
+            ms_e2e = timed(lambda: (prefill_host(layer, h_hidden, h_out, pipe), h_out[0, -1, 0].item()), args.steps)
 
     value = (world // groups) * tokens * args.steps / (ms / 1e3)
+    if light:
+        return dict(value=value, unit="tokens/s", ms_per_step=ms / args.steps, steps=args.steps,
+                    store=dict(device_store_mb=device_store_mb, h2d_bytes=info["h2d_bytes"], d2h_bytes=info["d2h_bytes"],
+                               hits=info["cache_hits"], misses=info["cache_misses"]),
+                    kernels={k: dict(ms=v[0], launches=v[2]) for k, v in prof.items()},
+                    note="the same prompt and layer with a device copy of the store: refills are device-to-device copies")
     e2e = (world // groups) * tokens * args.steps / (ms_e2e / 1e3)
     tf_peak, _, which = measured_peaks()
     attn_ms, attn_flops, attn_n = prof["attn"]
@@ -402,9 +441,7 @@ def run_ours(args, rank, world, local_rank):
                              "in 8192-token calls, exec 512, n_init 128, n_local 4096, unit 128, topk 16, repr_topk 4, "
                              f"max_cached {CFG['max_cached']}, lru; 64 planted units", l2="inputs (1 GiB of hidden states per step) exceed L2",
                     replicas=world // groups,
-                    store=("pinned host store + a device copy of its first "
-                           f"{os.environ.get('INFLLM_B200_DEVICE_STORE_MB', '4096')} MiB per layer (cache refills of "
-                           "those units are device-to-device copies; 0 = host store only)"),
+                    store="pinned host store; every cache refill is a 512 KiB cudaMemcpyAsync over PCIe on a side stream",
                     parallelism=(f"kv-head groups x{groups}: one layer over all GPUs, retrieval scores and output "
                                  "projection all-reduced (NCCL)") if groups > 1 else f"dp{world}: one layer replica per GPU"),
         e2e=dict(value=e2e, unit="tokens/s", h2d_bytes_per_step=int(hidden.numel() * 2),
@@ -415,13 +452,19 @@ def run_ours(args, rank, world, local_rank):
                       # DRAM bytes per launch of a steady-state exec block from an ncu capture of this kernel on a
                       # 32768-token prompt (its summary is kept with the other profiles); a launch at 131072 tokens
                       # reads the same operands.  None when the heads are sharded (other shapes per launch).
-                      traffic=(37.45e6 if groups == 1 else None), traffic_source="ncu, 32768-token case",
+                      traffic=(profile_traffic("attn_tc3_kernel_exec_block") if groups == 1 else None),
+                      traffic_source="ncu summary profiles/attn_tc3_kernel_exec_block.md (32768-token case)",
                       peak_source=f"bf16_tflops_sustained of {which}", launches=int(attn_n),
                       us_per_launch=1e3 * attn_ms / max(attn_n, 1),
                       flops_per_launch=attn_flops / max(attn_n, 1)),
         kernels={k: dict(ms=v[0], launches=v[2]) for k, v in prof.items()},
-        store=dict(h2d_bytes=info["h2d_bytes"], d2h_bytes=info["d2h_bytes"], hits=info["cache_hits"],
-                   misses=info["cache_misses"], evictions=info["evictions"]),
+        store=dict(h2d_bytes=info["h2d_bytes"], h2d_late_bytes=info["h2d_late_bytes"], d2h_bytes=info["d2h_bytes"],
+                   hits=info["cache_hits"], misses=info["cache_misses"], evictions=info["evictions"],
+                   h2d_overlap_frac=(overlap or {}).get("overlap_frac"), h2d_hidden_frac=(overlap or {}).get("hidden_frac"),
+                   refill_copy_ms_per_step=(overlap or {}).get("copy_ms"),
+                   note="counters since the context was created (warm-up and timed prompts); overlap_frac = share of the "
+                        "refill-copy time during which an exec-block attention kernel was running, hidden_frac = share "
+                        "that no exec block waited for (event trace of one untimed prompt)"),
         host_ms_per_step={k: v / 1e3 / args.steps for k, v in host_us.items()},
         clocks=clocks)
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -585,8 +628,7 @@ def run_decode(args, rank, world, local_rank):
                               us_per_launch=1e3 * dec_ms / max(dec_n, 1), bytes_per_launch=dec_bytes / max(dec_n, 1)),
         store=dict(hits=hits, misses=misses, miss_rate=misses / max(hits + misses, 1),
                    refill_bytes_per_token_layer=misses * 524288 / max(per_layer, 1),
-                   refill_source=("device copy of the store (INFLLM_B200_DEVICE_STORE_MB="
-                                  f"{os.environ.get('INFLLM_B200_DEVICE_STORE_MB', '4096')}); host store beyond it")),
+                   refill_source="pinned host store (cudaMemcpyAsync over PCIe)"),
         clocks=clocks)
     if rank == 0 and world == 1 and not args.no_cpu:
         v, secs, cores = cpu_decode_sample()
@@ -873,9 +915,16 @@ def main():
         line = run_model(args, rank, world, local_rank)
     else:
         line = run_ours(args, rank, world, local_rank)
+        import copy
+        import gc
+
+        if not args.head_groups:
+            gc.collect()
+            torch.cuda.empty_cache()
+            vargs = copy.copy(args)
+            vargs.steps = min(args.steps, 2)
+            line["device_store"] = run_ours(vargs, rank, world, local_rank, device_store_mb=1024, light=True)
         if args.workload == "both":
-            import copy
-            import gc
 
             gc.collect()
             torch.cuda.empty_cache()

@@ -227,24 +227,36 @@ typedef struct infllm_config {
   float rope_base, rope_scale;
   int32_t device;         /* CUDA device ordinal */
   int32_t shard_rank, shard_world; /* unit-range sharding of the store; 0,1 = not sharded */
-  int32_t reserved[6];    /* zero, except reserved[0]: debugging switches, one per bit —
+  int32_t debug_flags;    /* 0 in production; test switches, one per bit —
                            *  1: exec blocks on the shape-generic mma.sync kernels, no tcgen05 kernels
                            *  2: no look-ahead retrieval: every exec block waits for its ids from the device
                            *  4: look-ahead units staged by an SM copy kernel instead of one cudaMemcpyAsync each
-                           *  8: the two-heads-per-CTA tcgen05 attention kernel (experimental)
+                           *  8: the two-heads-per-CTA tcgen05 attention kernel whatever the head count
                            * 16: one-token appends wait for the retrieved ids before launching the attention
-                           * 32: one-token appends do not fetch ahead the units ranked just below the retrieval
-                           * 64: the older exec-block attention kernel that passes P through shared memory
-                           *     (default: P stays in TMEM and feeds the P V product from there)
-                           * reserved[1] > 0: exec blocks ranked and staged ahead of the running one (default 2,
-                           * at most 8); the cache gets that many times topk spare slots
-                           * reserved[3] > 0: MiB of device memory for a copy of the store's first units (512 KiB per
-                           * unit at 8 KV heads); a cache refill of such a unit is a device-to-device copy instead of a
-                           * copy over PCIe.  0: every refill comes from the pinned host store, as in the reference
-                           * reserved[2] > 0: chunk_topk_calc (context_manager.py:749-770, 548-610), in tokens: a call
-                           * of more than one token is cut into chunks of this size rounded down to whole exec blocks,
-                           * and every exec block of a chunk retrieves among the units sealed when the chunk started */
+                           * 32: one-token appends do not fetch ahead the units ranked just below the retrieval */
+  int32_t look_depth;     /* exec blocks ranked and staged ahead of the running one; 0 = default (2), at most 8; the
+                           * cache gets that many times topk spare slots */
+  int32_t chunk_topk_calc; /* chunk_topk_calc of the reference (context_manager.py:749-770, 548-610), in tokens; 0 = off:
+                           * a call of more than one token is cut into chunks of this size rounded down to whole exec
+                           * blocks, and every exec block of a chunk retrieves among the units sealed when it started */
+  int32_t device_store_mb; /* 0 (default): sealed units live in the pinned host store only and every cache refill is a
+                           * host-to-device copy, as in the reference (MemoryUnit.load, context_manager.py:57-71).
+                           * > 0: up to this many MiB of the store's first units are ALSO kept in device memory taken
+                           * from the pool of infllm_device_store_reserve, and a refill of such a unit is a
+                           * device-to-device copy.  The cache, its LRU order and the host store are unchanged. */
+  int32_t reserved[2];    /* zero */
 } infllm_config;
+
+/* Device copy of the store: one pool per device, shared by every context of the process whose configuration asks
+ * for a device copy (device_store_mb > 0).  infllm_device_store_reserve allocates `bytes` of device memory on
+ * `device` (rounded down to whole 128 MiB slabs) — the only allocation the device copy ever makes, done here and
+ * not inside append; contexts take slabs from it as their stores grow and hand them back when they are reset or
+ * destroyed, and a context that finds the pool empty simply keeps refilling from the host.  Calling it again
+ * grows the pool.  infllm_device_store_release frees the slabs no context holds; infllm_device_store_info reports
+ * the pool's size and what is handed out.  No counterpart in the reference, whose sealed units live on the host only. */
+int infllm_device_store_reserve(int device, int64_t bytes);
+int infllm_device_store_release(int device);
+int infllm_device_store_info(int device, int64_t* total_bytes, int64_t* used_bytes);
 
 /* Validates the configuration (exc_block_size <= n_local, context_manager.py:219;
  * max_cached_block >= topk, context_manager.py:19 -> INFLLM_E_CAPACITY) and allocates nothing
@@ -274,6 +286,7 @@ typedef struct infllm_ctx_info {
   int64_t exec_blocks;   /* exec blocks run by the last append */
   int64_t h2d_bytes, d2h_bytes; /* store traffic since create/reset */
   int64_t cache_hits, cache_misses, evictions;
+  int64_t h2d_late_bytes; /* the part of h2d_bytes that an exec block had to wait for (not staged ahead of it) */
 } infllm_ctx_info;
 int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
 /* Per-kernel timing, off by default.  When enabled, the context records a CUDA event pair around each
@@ -290,8 +303,10 @@ int infllm_ctx_get_profile(infllm_ctx* ctx, double* ms, double* work, int64_t* l
 /* Event trace of the exec-block loop, off by default: when enabled the context records a CUDA event at fixed
  * points of every stream it uses (labels: 0 attention begin, 1 attention end, 2 urgent score tiles end,
  * 3 sealing + candidate scoring end, 4 rest of the score pass end, 5/6 look-ahead ranking begin/end,
- * 7/8 staging copies begin/end).  infllm_ctx_get_trace synchronises, returns (label, exec block, ms since the
- * first mark) in record order and clears the trace. */
+ * 7/8 begin/end of the refill copies staged ahead for a later exec block (copy stream), 9 representative keys end,
+ * 10 packing of sealed units end, 11/12 begin/end of the refill copies an exec block waits for (urgent stream)).
+ * infllm_ctx_get_trace synchronises, returns (label, exec block, ms since the first mark) in record order and
+ * clears the trace. */
 int infllm_ctx_trace(infllm_ctx* ctx, int enable);
 int infllm_ctx_get_trace(infllm_ctx* ctx, int32_t* labels, int64_t* exec_blocks, float* ms, int cap, int* n);
 /* Host time (microseconds, summed since the last call) the exec-block loop spent in each of its phases:
@@ -303,6 +318,10 @@ int infllm_ctx_get_host_timers(infllm_ctx* ctx, double* us);
  * an error and return instead of hanging.  infllm_device_error synchronises the device, reads the
  * record (code 0 = none, 1 = wait ran out; `where` identifies the wait) and clears it. */
 int infllm_device_error(int* code, int* where);
+/* Writes the record from the host (code 0 clears it): lets a host-side test check that the product path reports a
+ * recorded error — infllm_ctx_append returns INFLLM_E_TIMEOUT at the latest on the call after the one whose kernel
+ * recorded it — without making a wait run out on the GPU. */
+int infllm_device_error_set(int code, int where);
 /* Number of kernels this library has launched in the process so far. */
 long long infllm_launch_count(void);
 

@@ -38,14 +38,15 @@ class Config(ctypes.Structure):
         ("cache_strategy", c_int32), ("dtype", c_int32),
         ("score_decay", c_double), ("rope_base", c_float), ("rope_scale", c_float),
         ("device", c_int32), ("shard_rank", c_int32), ("shard_world", c_int32),
-        ("reserved", c_int32 * 6),
+        ("debug_flags", c_int32), ("look_depth", c_int32), ("chunk_topk_calc", c_int32), ("device_store_mb", c_int32),
+        ("reserved", c_int32 * 2),
     ]
 
 
 class CtxInfo(ctypes.Structure):
     _fields_ = [(n, c_int64) for n in (
         "length", "frontier", "num_blocks", "init_len", "num_cached", "load_count", "exec_blocks",
-        "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions")]
+        "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions", "h2d_late_bytes")]
 
 
 # name -> (restype, argtypes); every symbol the header declares
@@ -141,6 +142,10 @@ SIGNATURES = {
     "infllm_ctx_profile": (c_int, [c_void_p, c_int]),
     "infllm_ctx_get_profile": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), POINTER(c_int64)]),
     "infllm_device_error": (c_int, [POINTER(c_int), POINTER(c_int)]),
+    "infllm_device_error_set": (c_int, [c_int, c_int]),
+    "infllm_device_store_reserve": (c_int, [c_int, c_int64]),
+    "infllm_device_store_release": (c_int, [c_int]),
+    "infllm_device_store_info": (c_int, [c_int, POINTER(c_int64), POINTER(c_int64)]),
     "infllm_launch_count": (ctypes.c_longlong, []),
     "infllm_ctx_trace": (c_int, [c_void_p, c_int]),
     "infllm_ctx_get_trace": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_int64), POINTER(c_float), c_int, POINTER(c_int)]),

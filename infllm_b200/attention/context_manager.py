@@ -5,12 +5,39 @@ see include/infllm_b200.h); this class validates arguments the way the reference
 tensors in and exposes the reference's observable attributes."""
 import ctypes
 import json
-import os
 from typing import Optional
 
 import torch
 
 from .. import _lib
+
+
+# Test hook: {field of infllm_config: value} written into the native configuration of every context created while
+# it is set (debug_flags selects kernel families and turns look-ahead off, look_depth sets the look-ahead depth).
+# The test-suite sets it with monkeypatch; nothing else does.
+TEST_OVERRIDES: dict = {}
+
+
+def device_store_reserve(mib: int, device=None):
+    """Reserve `mib` MiB of device memory on `device` for device copies of the stores (ContextManager(...,
+    device_store_mb=...)).  This is the only allocation the device copy makes: contexts take 128 MiB slabs from this
+    pool as their stores grow, give them back on reset, and keep refilling from the host when it is empty."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    _lib.check(_lib.lib.infllm_device_store_reserve(int(dev), int(mib) << 20))
+
+
+def device_store_release(device=None):
+    """Free the pool's slabs that no context holds."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    _lib.check(_lib.lib.infllm_device_store_release(int(dev)))
+
+
+def device_store_info(device=None):
+    """(MiB reserved, MiB handed out to contexts) of the device's pool."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    tot, used = ctypes.c_int64(), ctypes.c_int64()
+    _lib.check(_lib.lib.infllm_device_store_info(int(dev), ctypes.byref(tot), ctypes.byref(used)))
+    return tot.value >> 20, used.value >> 20
 
 
 class ContextManager:
@@ -20,13 +47,19 @@ class ContextManager:
 
     Constructor arguments are those of the reference (context_manager.py:197-209).  `fattn` and
     `async_global_stream` are accepted and ignored: there is one attention implementation, and the
-    host store always refills on a side stream.  `faiss` is not built."""
+    host store always refills on a side stream.  `faiss` is not built.
+
+    `device_store_mb` (not in the reference; default 0) keeps up to that many MiB of this memory's sealed units in
+    device memory as well, taken from the pool of device_store_reserve(): refills of those units are
+    device-to-device copies.  With 0 every refill comes from the pinned host store, as in the reference."""
 
     def __init__(self, position_embedding, n_init, n_local, block_size, max_cached_block, topk, exc_block_size,
                  score_decay: Optional[float] = None, fattn: bool = False, repr_topk: int = 1,
                  cache_strategy="lru", chunk_topk_calc: Optional[int] = None, async_global_stream: bool = False,
-                 pin_memory: bool = False, faiss: bool = False, perhead: bool = False, head_group_comm=None):
+                 pin_memory: bool = False, faiss: bool = False, perhead: bool = False, head_group_comm=None,
+                 device_store_mb: int = 0):
         self.length = 0
+        self.device_store_mb = int(device_store_mb)
         self.head_group_comm = head_group_comm  # HeadGroupComm: the heads given to append() are this rank's slice
         self.position_embedding = position_embedding
         self.n_init = n_init
@@ -75,26 +108,10 @@ class ContextManager:
             rope_scale=float(pe.distance_scale), device=q.device.index if q.device.index is not None else
             torch.cuda.current_device(), shard_rank=0, shard_world=1)
         if self.chunk_topk_calc is not None:
-            cfg.reserved[2] = int(self.chunk_topk_calc)  # context_manager.py:749-770
-        # a copy of the store's first units in device memory (MiB per batch element and layer): refills of those
-        # units do not cross PCIe.  0 keeps every sealed unit on the host only, as the reference does.
-        cfg.reserved[3] = int(os.environ.get("INFLLM_B200_DEVICE_STORE_MB", "4096"))
-        if os.environ.get("INFLLM_B200_NO_TC", "0") == "1":
-            cfg.reserved[0] |= 1  # debugging aid: run exec blocks on the shape-generic kernels instead of tcgen05
-        if os.environ.get("INFLLM_B200_NO_LOOKAHEAD", "0") == "1":
-            cfg.reserved[0] |= 2  # debugging aid: rank every exec block's units on the device, no look-ahead staging
-        if os.environ.get("INFLLM_B200_ATTN_TWO_HEAD", "0") == "1":
-            cfg.reserved[0] |= 8  # experimental: two query heads of a KV head per CTA share every K/V tile
-        if os.environ.get("INFLLM_B200_ATTN_P_IN_SMEM", "0") == "1":
-            cfg.reserved[0] |= 64  # the older exec-block attention kernel that passes P through shared memory
-        if os.environ.get("INFLLM_B200_STAGE_KERNEL", "0") == "1":
-            cfg.reserved[0] |= 4  # stage look-ahead units with the SM copy kernel instead of cudaMemcpyAsync per unit
-        if os.environ.get("INFLLM_B200_LOOK_DEPTH"):
-            cfg.reserved[1] = int(os.environ["INFLLM_B200_LOOK_DEPTH"])  # exec blocks ranked and staged ahead (default 2)
-        if os.environ.get("INFLLM_B200_NO_FETCH_AHEAD", "0") == "1":
-            cfg.reserved[0] |= 32  # debugging aid: one-token appends fetch only what they retrieve
-        if os.environ.get("INFLLM_B200_NO_DECODE_SPEC", "0") == "1":
-            cfg.reserved[0] |= 16  # debugging aid: one-token appends wait for the retrieved ids before the attention
+            cfg.chunk_topk_calc = int(self.chunk_topk_calc)  # context_manager.py:749-770
+        cfg.device_store_mb = int(self.device_store_mb)
+        for name, value in TEST_OVERRIDES.items():  # empty outside the test-suite
+            setattr(cfg, name, int(value))
         for _ in range(self.num_units):
             h = ctypes.c_void_p()
             _lib.check(_lib.lib.infllm_ctx_create(ctypes.byref(cfg), ctypes.byref(h)))
@@ -215,6 +232,49 @@ class ContextManager:
                 tot[name][1] += work[i]
                 tot[name][2] += n[i]
         return {k: tuple(v) for k, v in tot.items()}
+
+    def trace(self, enable=True, u=0):
+        """Event trace of the exec-block loop (off by default): CUDA events at fixed points of every stream."""
+        _lib.check(_lib.lib.infllm_ctx_trace(self._ctx[u], int(enable)))
+
+    def get_trace(self, u=0, cap=65536):
+        """[(label, exec block, ms since the first mark)] in record order; clears the trace.  Labels as in
+        include/infllm_b200.h (0/1 attention begin/end, 7/8 staged refill copies, 11/12 refill copies waited for)."""
+        labels, ebs, ms, n = (ctypes.c_int32 * cap)(), (ctypes.c_int64 * cap)(), (ctypes.c_float * cap)(), ctypes.c_int()
+        _lib.check(_lib.lib.infllm_ctx_get_trace(self._ctx[u], labels, ebs, ms, cap, ctypes.byref(n)))
+        return [(int(labels[i]), int(ebs[i]), float(ms[i])) for i in range(n.value)]
+
+    @staticmethod
+    def refill_overlap(trace):
+        """From a trace: how the refill copies of the cache overlapped the attention kernels.
+
+        Returns dict(copy_ms, staged_ms, late_ms, under_attention_ms, overlap_frac, hidden_frac): copy_ms is the time
+        refill copies were running (staged ahead on the copy stream + waited for on the urgent stream),
+        under_attention_ms the part of it during which an exec-block attention kernel was running, overlap_frac
+        their ratio, and hidden_frac the share of the copy time that no exec block waited for."""
+        def intervals(begin, end):
+            out, open_at = [], None
+            for label, _, t in trace:
+                if label == begin:
+                    open_at = t
+                elif label == end and open_at is not None:
+                    out.append((open_at, t))
+                    open_at = None
+            return out
+
+        attn = sorted(intervals(0, 1))
+        staged, late = intervals(7, 8), intervals(11, 12)
+
+        def under(iv):
+            a, b = iv
+            return sum(max(0.0, min(b, y) - max(a, x)) for x, y in attn if y > a and x < b)
+
+        staged_ms, late_ms = sum(b - a for a, b in staged), sum(b - a for a, b in late)
+        copy_ms = staged_ms + late_ms
+        hidden = sum(under(iv) for iv in staged) + sum(under(iv) for iv in late)
+        return dict(copy_ms=copy_ms, staged_ms=staged_ms, late_ms=late_ms, under_attention_ms=hidden,
+                    overlap_frac=(hidden / copy_ms if copy_ms > 0 else None),
+                    hidden_frac=(staged_ms / copy_ms if copy_ms > 0 else None))
 
     def host_timers(self, u=0):
         """Host microseconds per phase of the exec-block loop since the last call (diagnostics)."""

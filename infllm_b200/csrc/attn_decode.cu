@@ -313,9 +313,11 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
                        const DecodeIndirect* ind, int part_base) {
   if (chunk != 64 && chunk != 128) return fail(INFLLM_E_BADARG, "decode attention: chunk %d (64 or 128)", chunk);
   if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "decode attention: head_dim %d (128 is built)", head_dim);
+  if (n_heads <= 0 || n_kv_heads <= 0)
+    return fail(INFLLM_E_BADARG, "decode attention: %d query heads / %d kv heads", n_heads, n_kv_heads);
   if (n_heads % n_kv_heads || n_heads / n_kv_heads > kMaxGroup)
     return fail(INFLLM_E_UNSUPPORTED, "decode attention: %d query heads per kv head (at most %d)",
-                n_kv_heads ? n_heads / n_kv_heads : 0, kMaxGroup);
+                n_heads / n_kv_heads, kMaxGroup);
   if (n_seg <= 0 || n_seg > kMaxSeg) return fail(INFLLM_E_BADARG, "decode attention: %d segments (1..%d)", n_seg, kMaxSeg);
   DecodeParams P{};
   if (ind && ind->n_units > 0) {

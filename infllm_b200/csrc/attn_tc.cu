@@ -1,12 +1,14 @@
 // Tensor-core (tcgen05 + TMEM + TMA) attention kernels for head_dim 128.
 //
-// attn_tc_kernel    one 128-query tile of one head per CTA, all stages of an exec block fused:
+// attn_tc3_kernel   one 128-query tile of one head per CTA, all stages of an exec block fused:
 //                   local window stage (window-relative rotated q/k, causal window mask) and global
 //                   stage (one-angle q; retrieved units in their cache slots, init sink, overflow),
 //                   jointly normalised.  Warp-specialised: 8 softmax warps (two threads per query row, each
-//                   owning half of the tile's key columns; row = TMEM lane), 1 TMA producer warp, 1 MMA issuer warp.  S = Q K^T accumulates in
-//                   TMEM (two buffers), P goes through shared memory as a K-major operand, O stays in
-//                   TMEM for the whole tile with lazy rescaling; K/V tiles are double buffered.
+//                   owning half of the tile's key columns; row = TMEM lane), 1 TMA producer warp, two issuing
+//                   threads (S = Q K^T and O += P V).  S accumulates in TMEM (three buffers), P is written back
+//                   over its S columns and feeds the P V product from TMEM, O stays in TMEM for the whole tile
+//                   with lazy rescaling; K/V tiles are double buffered.
+// attn_tc2_kernel   the same for two query heads of one KV head per CTA, key tiles cut into runs (few heads per GPU).
 // colsum_tc_kernel  per-key score pass: S^T = K Q^T with keys as TMEM lanes; a CTA keeps one head's query tiles
 //                   resident and streams a run of key tiles through a TMA ring and four TMEM buffers; four
 //                   threads per key sum exp2(s - lse) over the queries that see it.
@@ -23,14 +25,6 @@ namespace infllm {
 using namespace tc;
 
 __device__ int g_tc_error[4];  // [0] code, [1] where, [2] blockIdx.x, [3] blockIdx.y
-#ifdef INFLLM_TC_TIMING
-// development aid: per-iteration clock stamps of CTA (0,0): [role][iteration], roles 0 producer issue, 1 operands
-// arrived, 2 MMA committed, 3 accumulator seen by the compute warps, 4 compute done
-__device__ long long g_tc_stamps[40][256];
-#define TC_STAMP(role, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 256) g_tc_stamps[role][it] = clock64(); } while (0)
-#else
-#define TC_STAMP(role, it) do { } while (0)
-#endif
 
 __device__ __forceinline__ void record_error(int* err, int code, int where) {
   if (atomicCAS(&err[0], 0, code) == 0) {
@@ -128,370 +122,6 @@ __device__ __forceinline__ bool seg_tiles(int64_t vis_lo, int64_t vis_hi, int64_
   *first = (int)(a / kTile);
   *last = (int)(b / kTile);
   return true;
-}
-
-// ------------------------------------------------------------------------------------------------
-namespace smem_layout {
-constexpr int kQ = 0;
-constexpr int kK = kQ + 2 * kSubTileBytes;      // two stages
-constexpr int kV = kK + 4 * kSubTileBytes;      // two stages
-constexpr int kP = kV + 4 * kSubTileBytes;
-constexpr int kBar = kP + 2 * kSubTileBytes;    // barriers + tmem slot + abort flag
-constexpr int kXmax = kBar + 256;                // row maxima: 2 tile parities x 2 halves x 128 rows of fp32
-constexpr int kXsum = kXmax + 2048;              // row sums: 2 halves x 128 rows
-constexpr int kXflag = kXsum + 1024;             // progress counters: 2 halves x 128 rows
-constexpr int kTotal = kXflag + 1024;
-}  // namespace smem_layout
-
-enum Bar { Q_FULL = 0, Q_EMPTY, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1, S_FULL0,
-           S_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, P_EMPTY, O_FULL, N_BARS };
-
-template <typename T>
-__global__ void __launch_bounds__(320, 1) attn_tc_kernel(const __grid_constant__ AttnTcParams P) {
-  extern __shared__ unsigned char smem_raw[];
-  // 1024-byte alignment for the swizzled tiles
-  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t s_base = smem_u32(smem);
-  const uint32_t sQ = s_base + smem_layout::kQ, sK = s_base + smem_layout::kK, sV = s_base + smem_layout::kV,
-                 sP = s_base + smem_layout::kP;
-  const uint32_t bars = s_base + smem_layout::kBar;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + smem_layout::kBar + N_BARS * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + smem_layout::kBar + N_BARS * 8 + 8);
-  float* xmax = reinterpret_cast<float*>(smem + smem_layout::kXmax);
-  float* xsum = reinterpret_cast<float*>(smem + smem_layout::kXsum);
-  volatile int* xflag = reinterpret_cast<volatile int*>(smem + smem_layout::kXflag);
-  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, hkv = h / (P.n_heads / P.n_kv_heads);
-  const int64_t i0 = (int64_t)blockIdx.x * kTile;
-  const int rows_q = (int)((P.lq - i0) < kTile ? (P.lq - i0) : kTile);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) {
-      uint32_t cnt = (i == S_EMPTY0 || i == S_EMPTY1 || i == P_FULL) ? 256u : 1u;
-      mbar_init(bar(i), cnt);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (threadIdx.x < 256) xflag[threadIdx.x] = 0;
-  if (warp == 9) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t tS0 = tmem, tS1 = tmem + 128, tO = tmem + 256;
-  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
-  constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false);
-  constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, 128, true);
-
-  if (warp == 8) {
-    // ======================================================================== TMA producer
-    if (lane == 0) {
-      int it = 0, sidx = 0;
-      bool ok = true;
-      for (int st = 0; st < P.n_stage && ok; ++st) {
-        const TcStage& S = P.stage[st];
-        int64_t vis_lo, vis_hi;
-        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
-        if (vis_lo > vis_hi) continue;
-        if (sidx >= 1) ok = wait_or_abort(bar(Q_EMPTY), (sidx - 1) & 1, abort_flag, P.err, 100);
-        if (!ok) break;
-        mbar_expect_tx(bar(Q_FULL), 2 * kSubTileBytes);
-        tma_load_3d(sQ, &P.maps[S.map_q], bar(Q_FULL), 0, S.q_row0 + (int)i0, h);
-        tma_load_3d(sQ + kSubTileBytes, &P.maps[S.map_q], bar(Q_FULL), 64, S.q_row0 + (int)i0, h);
-        ++sidx;
-        int64_t seg_j0 = 0;
-        for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
-          const TcSeg& G = P.seg[sg];
-          int tf, tl;
-          if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
-            for (int t = tf; t <= tl && ok; ++t, ++it) {
-              const int b = it & 1, tok = G.tok0 + t * kTile;
-              if (it >= 2) ok = wait_or_abort(bar(K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 101);
-              if (!ok) break;
-              const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
-              mbar_expect_tx(bar(K_FULL0 + b), 2 * kSubTileBytes);
-              if (G.c3_k < 0) {
-                tma_load_3d(dk, &P.maps[G.map_k], bar(K_FULL0 + b), 0, tok, hkv);
-                tma_load_3d(dk + kSubTileBytes, &P.maps[G.map_k], bar(K_FULL0 + b), 64, tok, hkv);
-              } else {
-                tma_load_4d(dk, &P.maps[G.map_k], bar(K_FULL0 + b), 0, tok, hkv, G.c3_k);
-                tma_load_4d(dk + kSubTileBytes, &P.maps[G.map_k], bar(K_FULL0 + b), 64, tok, hkv, G.c3_k);
-              }
-              if (it >= 2) ok = wait_or_abort(bar(V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 102);
-              if (!ok) break;
-              mbar_expect_tx(bar(V_FULL0 + b), 2 * kSubTileBytes);
-              if (G.c3_v < 0) {
-                tma_load_3d(dv, &P.maps[G.map_v], bar(V_FULL0 + b), 0, tok, hkv);
-                tma_load_3d(dv + kSubTileBytes, &P.maps[G.map_v], bar(V_FULL0 + b), 64, tok, hkv);
-              } else {
-                tma_load_4d(dv, &P.maps[G.map_v], bar(V_FULL0 + b), 0, tok, hkv, G.c3_v);
-                tma_load_4d(dv + kSubTileBytes, &P.maps[G.map_v], bar(V_FULL0 + b), 64, tok, hkv, G.c3_v);
-              }
-            }
-          }
-          seg_j0 += G.len;
-        }
-      }
-      if (!ok) {
-        // give loads that are still in flight a bounded chance to land before the CTA's memory goes away
-        for (int b = 0; b < 2; ++b) {
-          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(K_FULL0 + b), 0) && !mbar_try_wait(bar(K_FULL0 + b), 1); ++i) __nanosleep(64);
-          for (uint32_t i = 0; i < 4096 && !mbar_try_wait(bar(V_FULL0 + b), 0) && !mbar_try_wait(bar(V_FULL0 + b), 1); ++i) __nanosleep(64);
-        }
-      }
-    }
-  } else if (warp == 9) {
-    // ========================================================================== MMA issuer
-    if (lane == 0) {
-      int it = 0, sidx = 0;
-      bool ok = true;
-      // descriptors are built once; a K-major operand advances by 32 bytes per 16-element step and jumps to its
-      // second 64-column sub-tile after four steps
-      const uint64_t qd0 = make_sdesc(sQ, 16, 1024), pd0 = make_sdesc(sP, 16, 1024);
-      const uint64_t kd0[2] = {make_sdesc(sK, 16, 1024), make_sdesc(sK + 2 * kSubTileBytes, 16, 1024)};
-      const uint64_t vd0[2] = {make_sdesc(sV, kSubTileBytes, 1024), make_sdesc(sV + 2 * kSubTileBytes, kSubTileBytes, 1024)};
-      auto issue_pv = [&](int j) -> bool {
-        const int b = j & 1;
-        if (!wait_or_abort(bar(P_FULL), j & 1, abort_flag, P.err, 200)) return false;
-        TC_STAMP(9, j);
-        if (!wait_or_abort(bar(V_FULL0 + b), (j >> 1) & 1, abort_flag, P.err, 201)) return false;
-        TC_STAMP(11, j);
-        tc_fence_after();
-        // A = P [128 queries x 16 keys], K-major; B = V [16 keys x 128 d], d contiguous (MN-major)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tO, pd0 + (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4), vd0[b] + (uint64_t)((ks * 2048) >> 4),
-                 idesc_pv, (j > 0) || (ks > 0));
-        tc_commit(bar(V_EMPTY0 + b));
-        tc_commit(bar(P_EMPTY));
-        return true;
-      };
-      for (int st = 0; st < P.n_stage && ok; ++st) {
-        const TcStage& S = P.stage[st];
-        int64_t vis_lo, vis_hi;
-        visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
-        if (vis_lo > vis_hi) continue;
-        ok = wait_or_abort(bar(Q_FULL), sidx & 1, abort_flag, P.err, 202);
-        ++sidx;
-        // total tiles of this stage, to know the last QK that reads the stage's Q tile
-        int n_tiles = 0;
-        {
-          int64_t j0s = 0;
-          for (int sg = S.seg_begin; sg < S.seg_end; ++sg) {
-            int tf, tl;
-            if (seg_tiles(vis_lo, vis_hi, j0s, P.seg[sg].len, &tf, &tl)) n_tiles += tl - tf + 1;
-            j0s += P.seg[sg].len;
-          }
-        }
-        for (int t = 0; t < n_tiles && ok; ++t, ++it) {
-          const int b = it & 1;
-          TC_STAMP(8, it);
-          ok = wait_or_abort(bar(K_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 203);
-          TC_STAMP(18, it);
-          if (ok && it >= 2) ok = wait_or_abort(bar(S_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 204);
-          TC_STAMP(19, it);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t ts = b ? tS1 : tS0;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t off = (uint64_t)(((ks >> 2) * kSubTileBytes + (ks & 3) * 32) >> 4);
-            mma_ss(ts, qd0 + off, kd0[b] + off, idesc_qk, ks > 0);
-          }
-          tc_commit(bar(S_FULL0 + b));
-          tc_commit(bar(K_EMPTY0 + b));
-          TC_STAMP(10, it);
-          if (t == n_tiles - 1) tc_commit(bar(Q_EMPTY));
-          if (it >= 1) ok = issue_pv(it - 1);
-        }
-      }
-      if (ok && it >= 1) ok = issue_pv(it - 1);
-      if (ok) tc_commit(bar(O_FULL));
-    }
-  } else {
-    // ===================================================================== softmax / epilogue
-    // Eight warps: warp w and warp w+4 own the same 32 query rows (TMEM lanes) and split the tile's
-    // 128 key columns in halves; they exchange their partial row maxima through shared memory.
-    const int quad = warp & 3, half = warp >> 2;
-    const int row = quad * 32 + lane;
-    const int64_t qi = i0 + row;
-    const bool row_valid = qi < P.lq;
-    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
-    const int col0 = half * 64;
-    float m_ref = -INFINITY, l_part = 0.f;  // m_ref in the scaled log2 domain; l over this thread's columns
-    int it = 0;
-    bool ok = true;
-    for (int st = 0; st < P.n_stage && ok; ++st) {
-      const TcStage& S = P.stage[st];
-      int64_t vis_lo, vis_hi;
-      visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
-      if (vis_lo > vis_hi) continue;
-      // keys [jlo, jhi] of this stage are visible to this thread's query row
-      int64_t jlo = 0, jhi = S.lk - 1;
-      if (S.mask_mode == INFLLM_MASK_WINDOW) {
-        jlo = qi + S.mask_offset - S.mask_size + 1;
-        jhi = qi + S.mask_offset;
-      } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
-        jhi = qi + S.mask_offset - S.mask_size;
-      }
-      if (!row_valid) jhi = -1, jlo = 0;
-      int64_t seg_j0 = 0;
-      for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
-        const TcSeg& G = P.seg[sg];
-        int tf, tl;
-        if (seg_tiles(vis_lo, vis_hi, seg_j0, G.len, &tf, &tl)) {
-          for (int t = tf; t <= tl && ok; ++t, ++it) {
-            const int b = it & 1;
-            ok = __all_sync(0xffffffffu, wait_or_abort(bar(S_FULL0 + b), (it >> 1) & 1, abort_flag, P.err, 300));
-            if (!ok) break;
-            if (threadIdx.x == 0) TC_STAMP(12, it);
-            tc_fence_after();
-            float s[64];
-            const uint32_t ts = (b ? tS1 : tS0) + lane_base + col0;
-            tmem_ld32(ts, reinterpret_cast<uint32_t*>(s));
-            tmem_ld32(ts + 32, reinterpret_cast<uint32_t*>(s) + 32);
-            tmem_wait_ld();
-            if (threadIdx.x == 0) TC_STAMP(13, it);
-            tc_fence_before();
-            mbar_arrive(bar(S_EMPTY0 + b));
-            // visible columns of this tile for this row: [c_lo, c_hi] in tile coordinates
-            const int64_t jt = seg_j0 + (int64_t)t * kTile;
-            const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
-            const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
-            const int c_lo = (int)(a - jt) - col0;
-            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt)) - col0;
-            if (!(c_lo <= 0 && c_hi >= 63)) {
-#pragma unroll
-              for (int c = 0; c < 64; ++c) s[c] = (c >= c_lo && c <= c_hi) ? s[c] : -INFINITY;
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < 64; c += 8) {
-              mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
-              mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
-              mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
-              mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
-            }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the other half's maximum of the same row
-            xmax[(it & 1) * 256 + half * 128 + row] = mx;
-            __threadfence_block();
-            xflag[half * 128 + row] = it + 1;
-            ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 303));
-            if (!ok) break;
-            mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
-            if (threadIdx.x == 0) TC_STAMP(14, it);
-            // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
-            float alpha = 1.f;
-            bool resc = false;
-            if (mx > m_ref) {
-              if (m_ref == -INFINITY) {
-                m_ref = mx;  // nothing accumulated for this row yet
-              } else if (mx - m_ref > 8.f) {
-                alpha = ex2_approx(m_ref - mx);
-                l_part *= alpha;
-                m_ref = mx;
-                resc = true;
-              }
-            }
-            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-            uint32_t pk[32];
-            float2 rs01 = make_float2(0.f, 0.f), rs23 = make_float2(0.f, 0.f);
-            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(neg_m, neg_m);
-#pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-              const float2 a01 = ffma2(s[c], s[c + 1], sc2, nm2), a23 = ffma2(s[c + 2], s[c + 3], sc2, nm2);
-              const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
-              const float2 p23 = make_float2(ex2_approx(a23.x), ex2_approx(a23.y));
-              rs01 = fadd2(rs01, p01);
-              rs23 = fadd2(rs23, p23);
-              typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
-              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
-              pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
-            }
-            l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
-            if (threadIdx.x == 0) TC_STAMP(15, it);
-            // P buffer and O are free once PV of the previous tile has completed
-            if (it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(P_EMPTY), (it - 1) & 1, abort_flag, P.err, 301));
-            if (!ok) break;
-            if (threadIdx.x == 0) TC_STAMP(16, it);
-            if (__any_sync(0xffffffffu, resc) && it >= 1) {
-              tc_fence_after();
-#pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tO + lane_base + col0 + c * 32, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-                tmem_st32(tO + lane_base + col0 + c * 32, o);
-              }
-              tmem_wait_st();
-              tc_fence_before();
-            }
-            // this thread's half row of P -> shared memory, K-major with the 128-byte swizzle
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              uint4 v = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-              *reinterpret_cast<uint4*>(smem + smem_layout::kP + half * kSubTileBytes + swz_off(row, c)) = v;
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(bar(P_FULL));
-            if (threadIdx.x == 0) TC_STAMP(17, it);
-          }
-        }
-        seg_j0 += G.len;
-      }
-    }
-    // ---- epilogue: O / l -> out, log-sum-exp (each half writes its 64 output columns)
-    xsum[half * 128 + row] = l_part;
-    __threadfence_block();
-    xflag[half * 128 + row] = kPairDone;
-    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 304));
-    const float l_sum = l_part + xsum[(half ^ 1) * 128 + row];
-    if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(O_FULL), 0, abort_flag, P.err, 302));
-    if (ok) {
-      tc_fence_after();
-      const float inv = (it >= 1 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
-      T* orow = (T*)P.out + (int64_t)h * P.o_hs + qi * P.o_ts + col0;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t o[32];
-        if (it >= 1) {
-          tmem_ld32(tO + lane_base + col0 + c * 32, o);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) o[k] = 0;
-        }
-        if (row_valid) {
-#pragma unroll
-          for (int k = 0; k < 32; k += 8) {
-            uint4 v;
-            uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              typename Act<T>::T2 v2 = Act<T>::from_f2(__uint_as_float(o[k + 2 * e]) * inv,
-                                                       __uint_as_float(o[k + 2 * e + 1]) * inv);
-              pv[e] = *reinterpret_cast<uint32_t*>(&v2);
-            }
-            *reinterpret_cast<uint4*>(orow + c * 32 + k) = v;
-          }
-        }
-      }
-      if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
-    }
-  }
-  // ---- teardown
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -759,7 +389,6 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
             if (g < g0 || g >= g1) continue;
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(T2_S_FULLA + x), it & 1, abort_flag, P.err, 520));
             if (!ok) break;
-            if (threadIdx.x == 0) TC_STAMP(5, it);
             tc_fence_after();
             // visible columns of this tile for this row, relative to this thread's 64 columns
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
@@ -792,7 +421,6 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
               }
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            if (threadIdx.x == 0) TC_STAMP(6, it);
             // the other half's maximum of the same row
             gmax[(it & 1) * 256 + half * 128 + row] = mx;
             __threadfence_block();
@@ -800,7 +428,6 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
             ok = __all_sync(0xffffffffu, pair_wait(&gflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 521));
             if (!ok) break;
             mx = fmaxf(mx, gmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
-            if (threadIdx.x == 0) TC_STAMP(7, it);
             // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
             float alpha = 1.f;
             bool resc = false;
@@ -857,11 +484,9 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
               tmem_st16(tS + col0 + cc * 16, pk);
             }
             l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            if (threadIdx.x == 0) TC_STAMP(8, it);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(T2_P_FULLA + x));
-            if (threadIdx.x == 0) TC_STAMP(9, it);
             ++it;
           }
         }
@@ -1032,7 +657,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               if (it >= 2) ok = wait_or_abort(bar(T3_K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 601);
               if (!ok) break;
               const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
-              TC_STAMP(37, it);
               mbar_expect_tx(bar(T3_K_FULL0 + b), 2 * kSubTileBytes);
               if (G.c3_k < 0) {
                 tma_load_3d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv);
@@ -1043,7 +667,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               }
               if (it >= 2) ok = wait_or_abort(bar(T3_V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 602);
               if (!ok) break;
-              TC_STAMP(38, it);
               mbar_expect_tx(bar(T3_V_FULL0 + b), 2 * kSubTileBytes);
               if (G.c3_v < 0) {
                 tma_load_3d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv);
@@ -1089,14 +712,11 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         int sq = 0, tq = 0;
         for (int iq = 0; iq < n && ok; ++iq) {
           const int b = iq & 1;
-          TC_STAMP(8, iq);
           if (tq == 0) ok = wait_or_abort(bar(T3_Q_FULL), sq & 1, abort_flag, P.err, 610);
           if (ok) ok = wait_or_abort(bar(T3_K_FULL0 + b), (iq >> 1) & 1, abort_flag, P.err, 611);
-          TC_STAMP(18, iq);
           const int b3 = iq % 3;  // S/P buffer: free once the P V product of tile iq-3 has read P from it
           if (ok && iq >= 3) ok = wait_or_abort(bar(T3_PV_DONE0 + b3), ((iq / 3) - 1) & 1, abort_flag, P.err, 614);
           if (!ok) break;
-          TC_STAMP(36, iq);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -1105,7 +725,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
           }
           tc_commit(bar(T3_S_FULL0 + b3));
           tc_commit(bar(T3_K_EMPTY0 + b));
-          TC_STAMP(10, iq);
           if (++tq == nt[sq]) {
             tc_commit(bar(T3_Q_EMPTY));  // the last product that reads this stage's Q tile
             ++sq;
@@ -1118,10 +737,8 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
           const int b = ip & 1;
           const int b3 = ip % 3;
           ok = wait_or_abort(bar(T3_P_FULL0 + b3), (ip / 3) & 1, abort_flag, P.err, 612);
-          TC_STAMP(9, ip);
           ok = ok && wait_or_abort(bar(T3_V_FULL0 + b), (ip >> 1) & 1, abort_flag, P.err, 613);
           if (!ok) break;
-          TC_STAMP(11, ip);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -1131,7 +748,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
           }
           tc_commit(bar(T3_V_EMPTY0 + b));
           tc_commit(bar(T3_PV_DONE0 + b3));
-          TC_STAMP(19, ip);
         }
         if (ok) tc_commit(bar(T3_O_FULL));
       }
@@ -1172,14 +788,11 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             const uint32_t tS = tmem + b3 * 128 + lane_base;
             ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_S_FULL0 + b3), (it / 3) & 1, abort_flag, P.err, 620));
             if (!ok) break;
-            if (threadIdx.x == 0) TC_STAMP(12, it);
-            if (lane == 0) TC_STAMP(28 + warp, it);
             tc_fence_after();
             float s[64];
             tmem_ld32(tS + col0, reinterpret_cast<uint32_t*>(s));
             tmem_ld32(tS + col0 + 32, reinterpret_cast<uint32_t*>(s) + 32);
             tmem_wait_ld();
-            if (threadIdx.x == 0) TC_STAMP(13, it);
             // visible columns of this tile for this row: [c_lo, c_hi] in this thread's 64 columns
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
             const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
@@ -1206,7 +819,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 621));
             if (!ok) break;
             mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
-            if (threadIdx.x == 0) TC_STAMP(14, it);
             // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
             float alpha = 1.f;
             bool resc = false;
@@ -1236,7 +848,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
             }
             l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
-            if (threadIdx.x == 0) TC_STAMP(15, it);
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
               // O holds the products up to tile it-1: wait for the last of them, then scale this thread's 64 columns
               ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) % 3)), ((it - 1) / 3) & 1, abort_flag,
@@ -1257,11 +868,8 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             // keys 0-63 -> buffer columns [0,32), keys 64-127 -> [64,96)
             tmem_st32(tS + col0, pk);
             tmem_wait_st();
-            if (threadIdx.x == 0) TC_STAMP(16, it);
             tc_fence_before();
             mbar_arrive(bar(T3_P_FULL0 + b3));
-            if (threadIdx.x == 0) TC_STAMP(17, it);
-            if (lane == 0) TC_STAMP(20 + warp, it);
           }
         }
         seg_j0 += G.len;
@@ -1466,7 +1074,6 @@ __global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant
         const int b = n & 1;
         if (n >= 2) ok = wait_or_abort(bar(KE + b), ((n >> 1) - 1) & 1, abort_flag, P.err, 410);
         if (!ok) break;
-        TC_STAMP(0, n);
         mbar_expect_tx(bar(KF + b), 2 * kSubTileBytes);
         tma_load_3d(sK + b * 2 * kSubTileBytes, &P.map_k, bar(KF + b), 0, P.k_tok0 + (int)j0, hkv);
         tma_load_3d(sK + b * 2 * kSubTileBytes + kSubTileBytes, &P.map_k, bar(KF + b), 64, P.k_tok0 + (int)j0, hkv);
@@ -1486,7 +1093,6 @@ __global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant
         if (tl < tf) continue;
         const int kb = n & 1;
         ok = wait_or_abort(bar(KF + kb), (n >> 1) & 1, abort_flag, P.err, 412);
-        TC_STAMP(1, n);
         const uint32_t kt_s = sK + kb * 2 * kSubTileBytes;
         for (int t = tf; t <= tl && ok; ++t, ++step) {
           const int b = step % NB;
@@ -1504,7 +1110,6 @@ __global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant
           tc_commit(bar(SF + b));
         }
         if (ok) tc_commit(bar(KE + kb));  // every product that reads this key tile has been issued
-        TC_STAMP(2, n);
         ++n;
       }
     }
@@ -1539,7 +1144,6 @@ __global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant
         const int b = step % NB;
         ok = __all_sync(0xffffffffu, wait_or_abort(bar(SF + b), (step / NB) & 1, abort_flag, P.err, 414));
         if (!ok) break;
-        if (threadIdx.x == 0) TC_STAMP(3, step);
         tc_fence_after();
         float sv[32];
         tmem_ld32(tmem + b * 128 + lane_base + col0, reinterpret_cast<uint32_t*>(sv));
@@ -1571,7 +1175,6 @@ __global__ void __launch_bounds__(576, 1) colsum_tc_kernel(const __grid_constant
         }
         // a query row without any visible key has lse = -inf; it cannot see this key either, so it is masked above
         total += (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
-        if (threadIdx.x == 0) TC_STAMP(4, step);
       }
       // every thread owns one slot per key tile: no atomics, and the final sum below has a fixed order
       s_acc[((kt - kt0) * 4 + part) * 128 + krow] = total;
@@ -1660,30 +1263,14 @@ int tc_get_error_ptr(int** p) {
   return INFLLM_OK;
 }
 
-int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
-  if (P.lq <= 0) return INFLLM_OK;
-  dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads);
-  const size_t smem = smem_layout::kTotal + 1024;
-  INFLLM_DISPATCH_DTYPE(dtype, T, {
-    auto kern = attn_tc_kernel<T>;
-    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 320, smem, s>>>(P);
-  });
-  INFLLM_LAUNCH_OK("attn_tc_kernel");
-  return INFLLM_OK;
-}
-
 int attn_tc3_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
   if (P.lq <= 0) return INFLLM_OK;
   dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads);
   const size_t smem = tc3::kTotal + 1024;
-  static bool attr_set[2] = {false, false};
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = attn_tc3_kernel<T>;
-    if (!attr_set[dtype]) {
-      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set[dtype] = true;
-    }
+    // the opt-in holds for the current device only, and a process may drive several: asked for at every launch
+    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 352, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("attn_tc3_kernel");
@@ -1702,13 +1289,10 @@ int attn_tc2_launch(const AttnTcParams& P, int dtype, cudaStream_t s) {
     return fail(INFLLM_E_BADARG, "two-head attention kernel: split %d without partial buffers", P.n_split);
   dim3 grid((unsigned)ceil_div(P.lq, kTile), P.n_heads / 2, P.n_split);
   const size_t smem = tc2::kTotal + 1024;
-  static bool attr_set[2] = {false, false};
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = attn_tc2_kernel<T>;
-    if (!attr_set[dtype]) {
-      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set[dtype] = true;
-    }
+    // the opt-in holds for the current device only, and a process may drive several: asked for at every launch
+    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 576, smem, s>>>(P);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) {
@@ -1754,13 +1338,10 @@ int colsum_tc_launch_maps(const CUtensorMap& map_q, const CUtensorMap& map_k, in
   P.tiles_per_cta = per;
   dim3 grid((unsigned)ceil_div(n_tiles, per), n_heads);
   const size_t smem = colsum_smem::kTotal + 1024;
-  static bool attr_set[2] = {false, false};
   INFLLM_DISPATCH_DTYPE(dtype, T, {
     auto kern = colsum_tc_kernel<T>;
-    if (!attr_set[dtype]) {
-      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set[dtype] = true;
-    }
+    // the opt-in holds for the current device only, and a process may drive several: asked for at every launch
+    INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 576, smem, s>>>(P);
   });
   INFLLM_LAUNCH_OK("colsum_tc_kernel");
@@ -1795,11 +1376,11 @@ extern "C" int infllm_device_error(int* code, int* where) {
   return INFLLM_OK;
 }
 
-#ifdef INFLLM_TC_TIMING
-extern "C" int infllm_tc_stamps(long long* h_out) {
+extern "C" int infllm_device_error_set(int code, int where) {
   using namespace infllm;
+  const int h[4] = {code, where, 0, 0};
   INFLLM_CUDA_OK(cudaDeviceSynchronize());
-  INFLLM_CUDA_OK(cudaMemcpyFromSymbol(h_out, g_tc_stamps, sizeof(long long) * 40 * 256));
+  INFLLM_CUDA_OK(cudaMemcpyToSymbol(g_tc_error, h, sizeof(h)));
   return INFLLM_OK;
 }
-#endif
+

@@ -58,8 +58,7 @@ struct ColsumTcParams {
 int encode_rows_map(CUtensorMap* map, int dtype, const void* base, int64_t rows, int64_t heads, int64_t hs, int64_t ts);
 bool tc_rows_ok(const void* base, int64_t hs, int64_t ts);
 int tc_get_error_ptr(int** p);
-int attn_tc_launch(const AttnTcParams& P, int dtype, cudaStream_t s);
-// same grid as attn_tc_launch; the softmax warps work as two teams on alternate key tiles
+// one CTA per (128-query tile, head)
 int attn_tc3_launch(const AttnTcParams& P, int dtype, cudaStream_t s);
 // two query heads of one KV head per CTA (needs an even number of query heads per KV head)
 int attn_tc2_launch(const AttnTcParams& P, int dtype, cudaStream_t s);

@@ -13,8 +13,10 @@
 // max_cached_block cache slots with cudaMemcpyAsync when retrieval asks for them.
 #include <algorithm>
 #include <chrono>
+#include <cstring>
 #include <future>
 #include <list>
+#include <mutex>
 #include <unordered_map>
 #include <vector>
 
@@ -203,6 +205,12 @@ struct infllm_ctx {
   int64_t init_cap = 0;  // rows allocated for the sink buffers (at least one 128-row tile)
   CUtensorMap m_qloc, m_qglb, m_krot, m_kraw, m_v, m_cache, m_initk, m_initv;
   int* tc_err = nullptr;
+  // The tensor-core kernels record a bounded wait that ran out in a device-side record; a copy of it travels to
+  // h_tc_err with the candidate scores of every exec block and at the end of every call, and the host reads it
+  // behind a wait it performs anyway: infllm_ctx_append then returns INFLLM_E_TIMEOUT.
+  int32_t* h_tc_err = nullptr;   // pinned, 4 words
+  cudaEvent_t ev_err = nullptr;  // behind the last copy of the record
+  bool err_pending = false;
   float* tc_part = nullptr;  // partial results of the two-head attention kernel's key-tile runs
   size_t tc_part_floats = 0;
 
@@ -225,7 +233,7 @@ struct infllm_ctx {
   static constexpr int kDecodeAhead = 16;  // decode: units ranked just below the retrieval are fetched ahead
   std::vector<std::pair<int32_t, int>> unlisted;  // (unit, slot) fetched ahead, copy not yet known to have landed
   int decode_k = 0;                        // ids asked of the scorer by the last one-token exec block
-  int look_depth = 2;                             // exec blocks ranked ahead (cfg.reserved[1] overrides)
+  int look_depth = 2;                             // exec blocks ranked ahead (cfg.look_depth overrides)
   LookAhead la[kMaxLookDepth + 1];
   std::unordered_map<int32_t, int64_t> staged_for;  // staged unit -> latest exec block that wants it
   int32_t* h_spec = nullptr;        // pinned: look-ahead ids
@@ -294,7 +302,7 @@ int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 
 // trace labels
 enum { TR_ATTN_BEGIN = 0, TR_ATTN_END, TR_URGENT_END, TR_SEAL_END, TR_REST_END, TR_SPEC_BEGIN, TR_SPEC_END,
-       TR_STAGE_BEGIN, TR_STAGE_END, TR_REPR_END, TR_PACK_END };
+       TR_STAGE_BEGIN, TR_STAGE_END, TR_REPR_END, TR_PACK_END, TR_LATE_BEGIN, TR_LATE_END };
 void trace_mark(infllm_ctx* c, cudaStream_t s, int label, int64_t eb);
 void trace_mark(infllm_ctx* c, cudaStream_t s, int label, int64_t eb) {
   if (!c->trace_on || c->marks.size() > 20000) return;
@@ -437,7 +445,7 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   const int64_t n_slots = (int64_t)g.max_cached_block + (int64_t)c->look_depth * g.topk;
   INFLLM_CUDA_OK(cudaMalloc(&c->cache, n_slots * c->unit_bytes));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->cache, 0, n_slots * c->unit_bytes, s));
-  c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.reserved[0] & 1);
+  c->use_tc = D == 128 && g.block_size % 128 == 0 && !(g.debug_flags & 1);
   if (c->use_tc) {
     INFLLM_TRY(encode_rows_map(&c->m_qloc, g.dtype, c->q_loc, c->sub_max, H, c->sub_max * D, D));
     INFLLM_TRY(encode_rows_map(&c->m_qglb, g.dtype, c->q_glb, c->sub_max, H, c->sub_max * D, D));
@@ -450,15 +458,48 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
     uint32_t box[4] = {64, 128, 1, 1};
     INFLLM_TRY(encode_tensor_map(&c->m_cache, g.dtype, c->cache, 4, dims, strides, box));
     INFLLM_TRY(tc_get_error_ptr(&c->tc_err));
+    INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_tc_err, 4 * sizeof(int32_t), cudaHostAllocDefault));
+    c->h_tc_err[0] = c->h_tc_err[1] = c->h_tc_err[2] = c->h_tc_err[3] = 0;
+    INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_err, cudaEventDisableTiming));
   }
   c->free_slots.clear();
   for (int i = (int)n_slots - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->slot_ev.assign(n_slots, nullptr);
   c->slot_ev_used.assign(n_slots, 0);
   c->slab_units = std::max<int64_t>(16, (128ll << 20) / c->unit_bytes);
-  c->dev_cap = (int64_t)g.reserved[3] * (1ll << 20) / c->unit_bytes;  // device copy of the store, in units
+  c->dev_cap = (int64_t)g.device_store_mb * (1ll << 20) / c->unit_bytes;  // device copy of the store, in units
   c->initialized = true;
   return INFLLM_OK;
+}
+
+// Sends a copy of the tensor-core kernels' error record to the host on `copy_on`, ordered behind what stream s has
+// enqueued so far (copy_on == s: no extra ordering needed).
+int send_device_error(infllm_ctx* c, cudaStream_t s, cudaStream_t copy_on) {
+  if (!c->tc_err || !c->h_tc_err) return INFLLM_OK;
+  if (copy_on != s) {
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
+    INFLLM_CUDA_OK(cudaStreamWaitEvent(copy_on, c->ev_main, 0));
+  }
+  INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_tc_err, c->tc_err, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, copy_on));
+  INFLLM_CUDA_OK(cudaEventRecord(c->ev_err, copy_on));
+  c->err_pending = true;
+  return INFLLM_OK;
+}
+
+// Reads the last copy of the record if it has landed (never waits): a recorded error becomes INFLLM_E_TIMEOUT,
+// and the device-side record is cleared on s so that the next report names a new event.
+int poll_device_error(infllm_ctx* c, cudaStream_t s) {
+  if (!c->err_pending || cudaEventQuery(c->ev_err) != cudaSuccess) {
+    cudaGetLastError();  // cudaErrorNotReady is not an error of ours
+    return INFLLM_OK;
+  }
+  c->err_pending = false;
+  if (c->h_tc_err[0] == 0) return INFLLM_OK;
+  const int code = c->h_tc_err[0], where = c->h_tc_err[1], bx = c->h_tc_err[2], by = c->h_tc_err[3];
+  c->h_tc_err[0] = 0;
+  INFLLM_CUDA_OK(cudaMemsetAsync(c->tc_err, 0, 4 * sizeof(int32_t), s));
+  return fail(INFLLM_E_TIMEOUT, "a bounded wait of a tensor-core kernel ran out (code %d, wait %d, CTA %d,%d): the rows "
+              "that CTA was to write are not valid", code, where, bx, by);
 }
 
 // make room for tokens [frontier, length + add) in the token buffers
@@ -652,7 +693,6 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     la.ids.assign(la.h_ids, la.h_ids + g.topk);
   }
   la.staged = true;
-  trace_mark(c, c->copy_stream, TR_STAGE_BEGIN, target);
   std::vector<const void*> src;
   std::vector<void*> dst;
   for (int32_t b : la.ids) {
@@ -679,7 +719,8 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
   if (!src.empty()) {
     // the spare slots taken above may have held units that the previous exec block's attention read
     if (c->attn_prev_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn_prev, 0));
-    if (!(g.reserved[0] & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
+    trace_mark(c, c->copy_stream, TR_STAGE_BEGIN, target);  // behind the waits: the interval is copy time only
+    if (!(g.debug_flags & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
                                  // SM copy kernel, which is faster alone but slows concurrent attention down
       for (size_t i = 0; i < src.size(); ++i) {
         INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyDefault, c->copy_stream));
@@ -696,7 +737,7 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     INFLLM_CUDA_OK(cudaEventRecord(la.ev_staged, c->copy_stream));
     la.staged_recorded = true;
   }
-  trace_mark(c, c->copy_stream, TR_STAGE_END, target);
+  if (!src.empty()) trace_mark(c, c->copy_stream, TR_STAGE_END, target);
   return INFLLM_OK;
 }
 
@@ -722,6 +763,7 @@ int candidates_launch(infllm_ctx* c, int64_t eb_next, int* n_cand, cudaStream_t 
   INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
   INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_cand_scores, c->d_cand_scores, n * sizeof(float), cudaMemcpyDeviceToHost,
                                  c->mail_stream));
+  INFLLM_TRY(send_device_error(c, c->mail_stream, c->mail_stream));  // this exec block's attention is behind ev_main
   INFLLM_CUDA_OK(cudaEventRecord(c->ev_cand, c->mail_stream));
   *n_cand = n;
   return INFLLM_OK;
@@ -736,6 +778,7 @@ int candidates_finish(infllm_ctx* c, int n_cand, std::vector<int32_t>* ids) {
     return INFLLM_OK;
   }
   INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_cand));
+  INFLLM_TRY(poll_device_error(c, c->mail_stream));
   std::vector<int> order(n_cand);
   for (int i = 0; i < n_cand; ++i) order[i] = i;
   const int32_t* rows = c->h_cand_rows;
@@ -833,6 +876,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       // slots freed above may still be read by the previous exec block's attention
       if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->ev_attn, 0));
       late = true;
+      trace_mark(c, c->urgent_stream, TR_LATE_BEGIN, eb);
     }
     // an abandoned look-ahead copy into this slot may still be in flight on the copy stream
     if (c->slot_ev_used[slot]) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->slot_ev[slot], 0));
@@ -843,7 +887,10 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     // on a stream of its own: the exec block must not wait behind the copies staged for later blocks
     INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->unit_src(b), c->unit_bytes,
                                    cudaMemcpyDefault, c->urgent_stream));
-    if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
+    if (!c->dev_resident(b)) {
+      c->counters.h2d_bytes += c->unit_bytes;
+      c->counters.h2d_late_bytes += c->unit_bytes;
+    }
   }
   // look-ahead copies that were not wanted: their slots go back to the pool (later copies into them are
   // ordered behind the unfinished ones on the side stream; no kernel reads them)
@@ -857,6 +904,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     }
   }
   if (late) {
+    trace_mark(c, c->urgent_stream, TR_LATE_END, eb);
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->urgent_stream));
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
   }
@@ -997,13 +1045,48 @@ int seal_apply(infllm_ctx* c, const SealPlan& sp, cudaStream_t s) {
   return INFLLM_OK;
 }
 
-// device slabs for units [0, n): allocated as the store grows; when the device has no room the copy stops growing
+// Pool of device memory for the device copies of the stores, one per device ordinal: filled by
+// infllm_device_store_reserve (the only place that allocates), handed out in slabs of kPoolSlabBytes.
+constexpr size_t kPoolSlabBytes = 128ull << 20;
+struct DevicePool {
+  std::mutex mu;
+  std::vector<void*> free_slabs;
+  int64_t total = 0, used = 0;  // slabs
+};
+DevicePool g_pool[64];
+
+void* pool_take(int dev) {
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_pool[dev].mu);
+  if (g_pool[dev].free_slabs.empty()) return nullptr;
+  void* p = g_pool[dev].free_slabs.back();
+  g_pool[dev].free_slabs.pop_back();
+  g_pool[dev].used += 1;
+  return p;
+}
+
+void pool_give(int dev, void* p) {
+  if (dev < 0 || dev >= 64 || !p) return;
+  std::lock_guard<std::mutex> lk(g_pool[dev].mu);
+  g_pool[dev].free_slabs.push_back(p);
+  g_pool[dev].used -= 1;
+}
+
+void release_dev_slabs(infllm_ctx* c) {
+  for (void* p : c->dev_slabs) pool_give(c->cfg.device, p);
+  c->dev_slabs.clear();
+  c->dev_units = 0;
+}
+
+// device slabs for units [0, n): taken from the pool as the store grows; when the pool is empty the copy stops growing
 int ensure_dev_units(infllm_ctx* c, int64_t n) {
-  const size_t bytes = (size_t)(c->slab_units * c->unit_bytes);
+  if ((size_t)(c->slab_units * c->unit_bytes) > kPoolSlabBytes) {
+    c->dev_cap = c->dev_units;
+    return INFLLM_E_NOMEM;
+  }
   while ((int64_t)c->dev_slabs.size() * c->slab_units < n) {
-    void* p = nullptr;
-    if (cudaMalloc(&p, bytes) != cudaSuccess) {
-      cudaGetLastError();
+    void* p = pool_take(c->cfg.device);
+    if (!p) {
       c->dev_cap = c->dev_units;
       return INFLLM_E_NOMEM;
     }
@@ -1204,10 +1287,10 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     // not idle while the ids travel to the host.  The host still receives the ids (it keeps the LRU order) and,
     // if one of them is not cached, refills the cache and launches the attention again.
     if (c->chunk_mode) {
-      const int64_t chunk = (int64_t)(g.reserved[2] / g.exc_block_size) * g.exc_block_size;
+      const int64_t chunk = (int64_t)(g.chunk_topk_calc / g.exc_block_size) * g.exc_block_size;
       if ((c->call_off + st) % chunk == 0) c->chunk_n0 = c->num_blocks;
     }
-    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.reserved[0] & 16) &&
+    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.debug_flags & 16) &&
                       !c->chunk_mode;
     if (!spec) {
       if (!have_ids) {
@@ -1226,7 +1309,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
         // the scorer also names the units ranked just below the retrieval: they are fetched ahead (below)
         c->decode_k = (int)std::min<int64_t>(std::min<int64_t>(g.topk + infllm_ctx::kDecodeAhead, 64), c->num_blocks);
-        if (c->decode_k < g.topk || (g.reserved[0] & 32)) c->decode_k = g.topk;
+        if (c->decode_k < g.topk || (g.debug_flags & 32)) c->decode_k = g.topk;
         INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, c->d_topk, s, 0, c->decode_k));
       }
       INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
@@ -1249,7 +1332,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       INFLLM_TRY(flush_table(c, s));
     }
     // bit 1 of the flags turns the look-ahead off; a chunk's retrievals are fixed when it starts, so they need none
-    const bool more = ed < L && !(g.reserved[0] & 2) && !c->chunk_mode;
+    const bool more = ed < L && !(g.debug_flags & 2) && !c->chunk_mode;
     const int64_t n_eb = (L + g.exc_block_size - 1) / g.exc_block_size;
     HostTimer* ht_attn = new HostTimer(&c->host_us[3]);
     trace_mark(c, s, TR_ATTN_BEGIN, eb);
@@ -1379,7 +1462,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         // shard) its grid leaves most SMs idle, and the two-head kernel, which also cuts the key tiles into runs,
         // fills them.  Flag bit 3 forces the two-head kernel.
         const bool few_ctas = lq >= 256 && ((lq + 127) / 128) * H <= 74;
-        if ((H / HKV) % 2 == 0 && ((g.reserved[0] & 8) || few_ctas)) {
+        if ((H / HKV) % 2 == 0 && ((g.debug_flags & 8) || few_ctas)) {
           // two heads of a KV head per CTA; cut the key tiles into runs until the grid covers the SMs
           const int items = (int)((lq + 127) / 128) * (int)(H / 2);
           TP.n_split = std::max(1, std::min(8, 148 / items));
@@ -1397,9 +1480,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
           INFLLM_TRY(attn_tc2_launch(TP, g.dtype, s));
         } else {
           TP.n_split = 1;
-          // default: P stays in TMEM; flag bit 6 selects the older kernel that passes P through shared memory
-          if (g.reserved[0] & 64) INFLLM_TRY(attn_tc_launch(TP, g.dtype, s));
-          else INFLLM_TRY(attn_tc3_launch(TP, g.dtype, s));
+          INFLLM_TRY(attn_tc3_launch(TP, g.dtype, s));
         }
       } else {
       AttnParams P{};
@@ -1533,20 +1614,20 @@ extern "C" int infllm_ctx_create(const infllm_config* cfg, infllm_ctx** out) {
   if (g.cache_strategy != INFLLM_CACHE_LRU && g.cache_strategy != INFLLM_CACHE_LRU_S)
     return fail(INFLLM_E_UNSUPPORTED, "ctx_create: cache strategy code %d", g.cache_strategy);
   if (g.topk > 1024) return fail(INFLLM_E_UNSUPPORTED, "ctx_create: topk %d > 1024", g.topk);
-  if (g.reserved[2] != 0 && g.reserved[2] < g.exc_block_size)
-    return fail(INFLLM_E_BADARG, "ctx_create: chunk_topk_calc %d < exc_block_size %d", g.reserved[2], g.exc_block_size);
+  if (g.chunk_topk_calc != 0 && g.chunk_topk_calc < g.exc_block_size)
+    return fail(INFLLM_E_BADARG, "ctx_create: chunk_topk_calc %d < exc_block_size %d", g.chunk_topk_calc, g.exc_block_size);
   infllm_ctx* c = new (std::nothrow) infllm_ctx();
   if (!c) return fail(INFLLM_E_NOMEM, "ctx_create: out of host memory");
   c->cfg = g;
   // lru-s: the cache plan of an exec block depends on the attention of the one before it (context_manager.py:
   // 454-470), so nothing is ranked, staged or attended ahead of the host
-  if (g.cache_strategy == INFLLM_CACHE_LRU_S) c->cfg.reserved[0] |= 2 | 16 | 32;
+  if (g.cache_strategy == INFLLM_CACHE_LRU_S) c->cfg.debug_flags |= 2 | 16 | 32;
   c->esz = 2;
   c->width = (int64_t)g.n_heads * g.head_dim;
   c->unit_elems = (int64_t)g.n_kv_heads * g.block_size * g.head_dim;
   c->unit_bytes = 2 * c->unit_elems * c->esz;
   c->lru = LruTable(g.max_cached_block);
-  if (g.reserved[1] > 0) c->look_depth = std::min<int>(g.reserved[1], infllm_ctx::kMaxLookDepth);
+  if (g.look_depth > 0) c->look_depth = std::min<int>(g.look_depth, infllm_ctx::kMaxLookDepth);
   *out = c;
   return INFLLM_OK;
 }
@@ -1563,8 +1644,8 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   }
   c->d2h_synced_upto = 0;
   c->d2h_synced_upto_urgent = 0;
-  c->dev_units = 0;
-  c->dev_cap = (int64_t)c->cfg.reserved[3] * (1ll << 20) / std::max<int64_t>(c->unit_bytes, 1);
+  release_dev_slabs(c);
+  c->dev_cap = (int64_t)c->cfg.device_store_mb * (1ll << 20) / std::max<int64_t>(c->unit_bytes, 1);
   c->d2h_recorded = false;
   c->pack_used[0] = c->pack_used[1] = false;
   c->length = c->frontier = c->num_blocks = c->init_len = c->load_count = 0;
@@ -1607,6 +1688,8 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     if (c->unit_prob) cudaFree(c->unit_prob);
     if (c->h_unit_prob) cudaFreeHost(c->h_unit_prob);
     if (c->h_topk) cudaFreeHost(c->h_topk);
+    if (c->h_tc_err) cudaFreeHost(c->h_tc_err);
+    if (c->ev_err) cudaEventDestroy(c->ev_err);
     if (c->h_spec) cudaFreeHost(c->h_spec);
     for (auto& l : c->la) {
       if (l.h_ids) cudaFreeHost(l.h_ids);
@@ -1639,7 +1722,7 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
     for (cudaEvent_t e : c->slot_ev)
       if (e) cudaEventDestroy(e);
     for (void* p : c->slabs) cudaFreeHost(p);
-    for (void* p : c->dev_slabs) cudaFree(p);
+    release_dev_slabs(c);
     cudaStreamDestroy(c->copy_stream);
     cudaEventDestroy(c->ev_main);
     cudaEventDestroy(c->ev_copy);
@@ -1665,10 +1748,11 @@ extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, i
   cudaStream_t s = (cudaStream_t)stream;
   INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
   if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
+  INFLLM_TRY(poll_device_error(c, s));
   c->trace_topk.clear();
   c->counters.exec_blocks = 0;
   const int esz = c->esz;
-  c->chunk_mode = c->cfg.reserved[2] > 0 && len > 1;  // context_manager.py:749
+  c->chunk_mode = c->cfg.chunk_topk_calc > 0 && len > 1;  // context_manager.py:749
   for (int64_t off = 0; off < len; off += c->sub_max) {
     const int64_t n = std::min<int64_t>(c->sub_max, len - off);
     c->call_off = off;
@@ -1676,6 +1760,7 @@ extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, i
                           k_ts, (const char*)d_v + off * v_ts * esz, v_hs, v_ts, (char*)d_out + off * o_ts * esz, o_hs,
                           o_ts, n, s));
   }
+  if (c->use_tc && len > 64) INFLLM_TRY(send_device_error(c, s, s));  // read by the next call (or by get_info)
   return INFLLM_OK;
 }
 
@@ -1916,10 +2001,24 @@ extern "C" int infllm_ctx_set_comm(infllm_ctx* c, infllm_comm* comm) {
 // the un-sealed tokens (raw keys, values, accumulated scores) and the sealed units as the host store holds them.
 // The rotated keys are not stored: they are rotated anew on the next append.
 namespace {
-constexpr int64_t kStateMagic = 0x314d454d4c464e49ll;  // "INFLMEM1"
+constexpr int64_t kStateMagic = 0x324d454d4c464e49ll;  // "INFLMEM2"
+constexpr int kStateHdrWords = 24;
 
 bool put(FILE* f, const void* p, size_t n) { return n == 0 || fwrite(p, 1, n, f) == n; }
 bool get(FILE* f, void* p, size_t n) { return n == 0 || fread(p, 1, n, f) == n; }
+
+int64_t decay_bits(double d) {
+  int64_t b;
+  memcpy(&b, &d, sizeof(b));
+  return b;
+}
+
+struct FileCloser {
+  FILE* f;
+  ~FileCloser() {
+    if (f) fclose(f);
+  }
+};
 }  // namespace
 
 extern "C" int infllm_ctx_save(infllm_ctx* c, const char* path, void* stream) {
@@ -1935,8 +2034,10 @@ extern "C" int infllm_ctx_save(infllm_ctx* c, const char* path, void* stream) {
   const int64_t live = c->length - c->frontier, n_lru = (int64_t)c->lru.items.size();
   FILE* f = fopen(path, "wb");
   if (!f) return fail(INFLLM_E_BADARG, "ctx_save: cannot open %s", path);
-  const int64_t hdr[16] = {kStateMagic, H, HKV, D, g.n_init, g.n_local, g.block_size, g.dtype, c->length, c->frontier,
-                           c->num_blocks, c->init_len, c->init_full ? 1 : 0, c->load_count, n_lru, g.cache_strategy};
+  const int64_t hdr[kStateHdrWords] = {
+      kStateMagic, H, HKV, D, g.n_init, g.n_local, g.block_size, g.dtype, c->length, c->frontier,
+      c->num_blocks, c->init_len, c->init_full ? 1 : 0, c->load_count, n_lru, g.cache_strategy,
+      g.max_cached_block, g.topk, g.exc_block_size, g.repr_topk, g.chunk_topk_calc, decay_bits(g.score_decay), 0, 0};
   bool ok = put(f, hdr, sizeof(hdr));
   for (auto& kv : c->lru.items) {
     const int64_t id = kv.first;
@@ -1963,36 +2064,59 @@ extern "C" int infllm_ctx_save(infllm_ctx* c, const char* path, void* stream) {
   return INFLLM_OK;
 }
 
+// Everything the file says is checked before any state of the context (or the GPU) is touched: the header
+// against the configuration, the lengths against each other, the LRU entries against the unit count and the cache
+// size, and the file's size against what those lengths imply.
 extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
   if (!c || !path) return fail(INFLLM_E_BADARG, "ctx_load: null pointer");
   const infllm_config& g = c->cfg;
   cudaStream_t s = (cudaStream_t)stream;
-  INFLLM_CUDA_OK(cudaSetDevice(g.device));
-  FILE* f = fopen(path, "rb");
+  FileCloser fc{fopen(path, "rb")};
+  FILE* f = fc.f;
   if (!f) return fail(INFLLM_E_BADARG, "ctx_load: cannot open %s", path);
-  int64_t hdr[16];
-  if (!get(f, hdr, sizeof(hdr)) || hdr[0] != kStateMagic) {
-    fclose(f);
+  int64_t hdr[kStateHdrWords];
+  if (!get(f, hdr, sizeof(hdr)) || hdr[0] != kStateMagic)
     return fail(INFLLM_E_BADARG, "ctx_load: %s is not a saved context memory", path);
-  }
   if (hdr[1] != g.n_heads || hdr[2] != g.n_kv_heads || hdr[3] != g.head_dim || hdr[4] != g.n_init || hdr[5] != g.n_local ||
-      hdr[6] != g.block_size || hdr[7] != g.dtype || hdr[15] != g.cache_strategy) {
-    fclose(f);
+      hdr[6] != g.block_size || hdr[7] != g.dtype || hdr[15] != g.cache_strategy || hdr[16] != g.max_cached_block ||
+      hdr[17] != g.topk || hdr[18] != g.exc_block_size || hdr[19] != g.repr_topk || hdr[20] != g.chunk_topk_calc ||
+      hdr[21] != decay_bits(g.score_decay))
     return fail(INFLLM_E_BADARG, "ctx_load: %s was saved with another configuration", path);
-  }
-  if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
-  INFLLM_TRY(infllm_ctx_reset(c));
   const int64_t D = g.head_dim, H = g.n_heads, HKV = g.n_kv_heads;
   const int64_t length = hdr[8], frontier = hdr[9], n_units = hdr[10], init_len = hdr[11], n_lru = hdr[14];
   const int64_t live = length - frontier;
-  bool ok = true;
+  if (length < 0 || frontier < 0 || n_units < 0 || n_units > INT32_MAX || init_len < 0 || init_len > g.n_init ||
+      live < 0 || frontier != init_len + n_units * (int64_t)g.block_size || (hdr[12] != 0) != (init_len == g.n_init) ||
+      (n_units > 0 && init_len != g.n_init) || hdr[13] < 0)
+    return fail(INFLLM_E_BADARG, "ctx_load: %s holds inconsistent lengths (length %lld, frontier %lld, %lld units, sink %lld)",
+                path, (long long)length, (long long)frontier, (long long)n_units, (long long)init_len);
+  if (n_lru < 0 || n_lru > g.max_cached_block)
+    return fail(INFLLM_E_BADARG, "ctx_load: %s lists %lld cached units, the cache holds %d", path, (long long)n_lru,
+                g.max_cached_block);
+  const int64_t esz = 2, unit_bytes = 2 * (int64_t)HKV * g.block_size * D * esz;
+  const int64_t expect = (int64_t)sizeof(hdr) + n_lru * 16 + 2 * HKV * init_len * D * esz + n_units * H * D * esz +
+                         2 * HKV * live * D * esz + H * live * (int64_t)sizeof(float) + n_units * unit_bytes;
+  if (fseek(f, 0, SEEK_END) != 0 || (int64_t)ftell(f) != expect || fseek(f, (long)sizeof(hdr), SEEK_SET) != 0)
+    return fail(INFLLM_E_BADARG, "ctx_load: %s has not the %lld bytes its header implies", path, (long long)expect);
   std::vector<std::pair<int32_t, double>> lru;
-  for (int64_t i = 0; ok && i < n_lru; ++i) {
-    int64_t id;
-    double stamp;
-    ok = get(f, &id, sizeof(id)) && get(f, &stamp, sizeof(stamp));
-    lru.push_back({(int32_t)id, stamp});
+  {
+    std::vector<char> seen((size_t)n_units, 0);
+    for (int64_t i = 0; i < n_lru; ++i) {
+      int64_t id;
+      double stamp;
+      if (!get(f, &id, sizeof(id)) || !get(f, &stamp, sizeof(stamp)))
+        return fail(INFLLM_E_BADARG, "ctx_load: %s ends inside the cache table", path);
+      if (id < 0 || id >= n_units || seen[(size_t)id] || !(stamp == stamp))
+        return fail(INFLLM_E_BADARG, "ctx_load: %s lists cached unit %lld (of %lld units) wrongly", path, (long long)id,
+                    (long long)n_units);
+      seen[(size_t)id] = 1;
+      lru.push_back({(int32_t)id, stamp});
+    }
   }
+  INFLLM_CUDA_OK(cudaSetDevice(g.device));
+  if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
+  INFLLM_TRY(infllm_ctx_reset(c));
+  bool ok = true;
   std::vector<char> buf;
   auto fill2d = [&](void* dev, int64_t pitch, int64_t width, int64_t rows) -> bool {
     if (width * rows == 0) return true;
@@ -2003,12 +2127,12 @@ extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
   ok = ok && fill2d(c->init_k, c->init_cap * D * c->esz, init_len * D * c->esz, HKV);
   ok = ok && fill2d(c->init_v, c->init_cap * D * c->esz, init_len * D * c->esz, HKV);
   if (ok && ensure_block_k(c, std::max<int64_t>(n_units, 1), s) != INFLLM_OK) ok = false;
-  if (ok) INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  if (ok && cudaStreamSynchronize(s) != cudaSuccess) ok = false;
   ok = ok && fill2d(c->block_k, c->width * c->esz, c->width * c->esz, n_units);
   // the un-sealed tokens go to the start of fresh token buffers
   c->length = c->frontier = frontier;
   if (ok && ensure_tokens(c, live, s) != INFLLM_OK) ok = false;
-  if (ok) INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  if (ok && cudaStreamSynchronize(s) != cudaSuccess) ok = false;
   if (ok) {
     TokenBuffers& tb = c->tb;
     const int64_t pitch = tb.cap * D * c->esz, off = (frontier - tb.t0) * D * c->esz;
@@ -2018,7 +2142,6 @@ extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
   }
   if (ok && ensure_host_units(c, n_units) != INFLLM_OK) ok = false;
   for (int64_t b = 0; ok && b < n_units; ++b) ok = get(f, c->host_unit(b), (size_t)c->unit_bytes);
-  fclose(f);
   if (ok && fill_dev_store(c, n_units) != INFLLM_OK) ok = false;
   if (!ok) {
     infllm_ctx_reset(c);
@@ -2032,9 +2155,8 @@ extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
   c->d2h_synced_upto = n_units;
   c->d2h_synced_upto_urgent = n_units;
   c->rope_origin = -1;  // the window is rotated anew by the next append
-  // the cache comes back as the LRU table lists it
+  // the cache comes back as the LRU table lists it (n_lru <= max_cached_block slots were checked above)
   for (auto& kv : lru) {
-    if (c->free_slots.empty()) return fail(INFLLM_E_CAPACITY, "ctx_load: the saved cache holds more units than this one");
     const int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[kv.first] = slot;
@@ -2043,5 +2165,44 @@ extern "C" int infllm_ctx_load(infllm_ctx* c, const char* path, void* stream) {
                                    cudaMemcpyHostToDevice, s));
   }
   INFLLM_CUDA_OK(cudaStreamSynchronize(s));
+  return INFLLM_OK;
+}
+
+// ------------------------------------------------------------------------------- device-store pool
+extern "C" int infllm_device_store_reserve(int device, int64_t bytes) {
+  if (device < 0 || device >= 64 || bytes < 0) return fail(INFLLM_E_BADARG, "device_store_reserve: bad argument");
+  INFLLM_CUDA_OK(cudaSetDevice(device));
+  const int64_t n = bytes / (int64_t)kPoolSlabBytes;
+  for (int64_t i = 0; i < n; ++i) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, kPoolSlabBytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(INFLLM_E_NOMEM, "device_store_reserve: cudaMalloc failed after %lld of %lld slabs of 128 MiB: %s",
+                  (long long)i, (long long)n, cudaGetErrorString(e));
+    }
+    std::lock_guard<std::mutex> lk(g_pool[device].mu);
+    g_pool[device].free_slabs.push_back(p);
+    g_pool[device].total += 1;
+  }
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_device_store_release(int device) {
+  if (device < 0 || device >= 64) return fail(INFLLM_E_BADARG, "device_store_release: bad device");
+  INFLLM_CUDA_OK(cudaSetDevice(device));
+  INFLLM_CUDA_OK(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lk(g_pool[device].mu);
+  for (void* p : g_pool[device].free_slabs) cudaFree(p);
+  g_pool[device].total -= (int64_t)g_pool[device].free_slabs.size();
+  g_pool[device].free_slabs.clear();
+  return INFLLM_OK;
+}
+
+extern "C" int infllm_device_store_info(int device, int64_t* total_bytes, int64_t* used_bytes) {
+  if (device < 0 || device >= 64) return fail(INFLLM_E_BADARG, "device_store_info: bad device");
+  std::lock_guard<std::mutex> lk(g_pool[device].mu);
+  if (total_bytes) *total_bytes = g_pool[device].total * (int64_t)kPoolSlabBytes;
+  if (used_bytes) *used_bytes = g_pool[device].used * (int64_t)kPoolSlabBytes;
   return INFLLM_OK;
 }

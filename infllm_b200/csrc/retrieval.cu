@@ -220,12 +220,6 @@ topk_select_kernel(const float* __restrict__ scores, int64_t n, int k, int id_ba
 //      adversarially), appended to a shared list.
 //   3. rank sort of the candidates; the first k leave in order.
 // No loop waits on data of another CTA.
-#ifdef INFLLM_TOPK_TIMING
-__device__ long long g_topk_stamps[16];
-#define TK_STAMP(i) do { if (threadIdx.x == 0) g_topk_stamps[i] = clock64(); } while (0)
-#else
-#define TK_STAMP(i) do { } while (0)
-#endif
 constexpr int kFastItems = 16;                   // scores per thread: up to 16384 units (2M tokens of 128-token units)
 constexpr int kFastMaxK = 64;
 constexpr int kFastMaxN = kFastItems * kTopkThreads;
@@ -257,7 +251,6 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
   if ((tid & 3) == 0) gm[tid >> 2] = x;
   if (tid == 0) *s_cnt = 0;
   __syncthreads();
-  TK_STAMP(4);
   // ---- 1. tau = the k-th largest group maximum: the four threads of a group count, a quarter each, how many
   //         group maxima are larger than their own; the group that counts k - 1 holds tau
   {
@@ -270,7 +263,6 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
     if ((tid & 3) == 0 && larger == k - 1) *s_tau = x;  // keys are unique (0 only among padding groups, see below)
   }
   __syncthreads();
-  TK_STAMP(5);
   const unsigned long long tau = *s_tau;
   // ---- 2. candidates
 #pragma unroll
@@ -280,7 +272,6 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
       if (p < kFastCand) cand[p] = key[e];
     }
   __syncthreads();
-  TK_STAMP(6);
   const int nc = *s_cnt < kFastCand ? *s_cnt : kFastCand;  // k <= nc <= 64k
   // ---- 3. rank of every candidate = how many candidates rank before it
   for (int c = tid; c < nc; c += kTopkThreads) {
@@ -293,7 +284,6 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
       if (out_scores) out_scores[rank] = __ldcg(scores + id);
     }
   }
-  TK_STAMP(7);
 }
 
 __global__ void __launch_bounds__(kTopkThreads)
@@ -322,10 +312,8 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
   __shared__ int s_cnt;
   __shared__ unsigned long long s_tau;
   __shared__ bool s_last;
-  TK_STAMP(0);
   for (int i = threadIdx.x; i < width; i += kTopkThreads) sq[i] = qbar[i];
   __syncthreads();
-  TK_STAMP(1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // consecutive rows go to different SMs, so that a short list still draws on every SM's path to memory
   for (int row = warp * gridDim.x + blockIdx.x; row < n; row += gridDim.x * 32) {
@@ -365,14 +353,12 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
     }
   }
   if (!ticket) return;
-  TK_STAMP(2);
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
   __syncthreads();
   if (!s_last) return;
   __threadfence();
   if (threadIdx.x == 0) *ticket = 0;
-  TK_STAMP(3);
   if (threadIdx.x == 0) s_tau = 0ull;
   cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt, &s_tau);
 }
@@ -477,11 +463,8 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
       auto kern = block_score_topk_kernel<T>;
       // the kernel's static shared memory (ranking scratch) plus the query vector passes the 48 KiB a launch gets
       // without asking
-      static size_t allowed = 0;  // per instantiation: the largest dynamic size granted so far
-      if (smem > allowed) {
-        INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        allowed = smem;
-      }
+      // (asked for at every launch: the opt-in holds for the current device only)
+      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       kern<<<grid, kTopkThreads, smem, s>>>((const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores,
                                            ticket);
     });
@@ -564,29 +547,6 @@ int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* s
 }
 
 }  // namespace infllm
-
-#ifdef INFLLM_TOPK_TIMING
-extern "C" int infllm_topk_stamps(long long* out) {
-  return cudaMemcpyFromSymbol(out, infllm::g_topk_stamps, sizeof(long long) * 16) == cudaSuccess ? 0 : -1;
-}
-extern "C" int infllm_score_only(const void* bk, int64_t n, int width, const float* qbar, float* scores, int variant,
-                                 void* stream) {
-  using namespace infllm;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (variant == 0) {
-    block_score_kernel<__nv_bfloat16><<<(unsigned)ceil_div(n, kScoreWarps), kScoreWarps * 32, width * sizeof(float), s>>>(
-        (const __nv_bfloat16*)bk, n, width, qbar, scores);
-  } else {
-    block_score_topk_kernel<__nv_bfloat16><<<148, kTopkThreads, width * sizeof(float), s>>>(
-        (const __nv_bfloat16*)bk, (int)n, width, qbar, scores, 32, 0, nullptr, nullptr, nullptr);
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
-}
-extern "C" int infllm_block_topk_ticket(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k,
-                                        int32_t* ids, unsigned int* ticket, int dtype, void* stream) {
-  return infllm::block_topk_launch(bk, n, width, qbar, scores, k, 0, ids, nullptr, dtype, (cudaStream_t)stream, ticket);
-}
-#endif
 
 extern "C" int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int width, const float* d_qbar,
                                  float* d_scores, int k, int id_base, int32_t* d_out_ids, float* d_out_scores,

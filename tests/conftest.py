@@ -26,3 +26,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    from helpers import REPORT
+
+    if REPORT:
+        terminalreporter.write_line("observed counts (parity tests):")
+        for line in REPORT:
+            terminalreporter.write_line("  " + line)

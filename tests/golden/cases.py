@@ -42,7 +42,28 @@ CASES = {
     "d128_chunk_topk": dict(H=4, HKV=2, D=128, n_init=64, n_local=256, bs=128, max_cached=6, topk=3, exc=128,
                             repr_topk=2, base=1000000.0, lens=[1500, 1, 1, 1000, 1, 700], seed=26, strategy="lru",
                             decay=None, qscale=1.0, chunk_topk=384),
+    # ---- the shapes the benchmark configurations name (32 query heads; tcgen05 exec blocks of several query tiles)
+    # the attention-layer configuration of the headline metric, truncated to 32768 tokens: exec blocks of 512 queries
+    # (4 query tiles per head), a 4096-token window, 16 retrieved units + 128 sink + up to 512 overflow keys per exec
+    # block, cache of 32; fed in 8192-token calls; 24 planted units that later exec blocks' queries lean towards
+    "cfg2_32k": dict(H=32, HKV=8, D=128, n_init=128, n_local=4096, bs=128, max_cached=32, topk=16, exc=512,
+                     repr_topk=4, base=1000000.0, lens=[8192] * 4, seed=43, strategy="lru", decay=None, qscale=1.0,
+                     plant=dict(kind="relevant", units=24, lean=0.6, seed=5)),
+    # the CPU-runnable configuration, exact: 8192 tokens in ONE call = 64 exec blocks of 128, window 1024, topk 4,
+    # cache of 16; q, k, v are projections (weights ~N(0, 0.02), seeds 1-3) of N(0,1) hidden states of width 4096, seed 0
+    "cfg1_8k": dict(H=32, HKV=8, D=128, n_init=128, n_local=1024, bs=128, max_cached=16, topk=4, exc=128,
+                    repr_topk=4, base=1000000.0, lens=[8192], seed=0, strategy="lru", decay=None, qscale=1.0,
+                    hidden=4096),
+    # cache thrash at 32 query / 32 KV heads: max_cached == topk == 16, repr_topk 8, exec blocks of 256; the units form
+    # 3 groups and consecutive exec blocks' queries lean towards consecutive groups, so that every exec block evicts
+    # the whole cache and refills it (worst case of the LRU order) once every group has 16 sealed units
+    "cfg5_thrash": dict(H=32, HKV=32, D=128, n_init=128, n_local=4096, bs=128, max_cached=16, topk=16, exc=256,
+                        repr_topk=8, base=1000000.0, lens=[8192, 8192, 4096], seed=47, strategy="lru", decay=None,
+                        qscale=1.0, plant=dict(kind="rotate", groups=3, lean=0.6, seed=7)),
 }
+
+# cases whose recording keeps the per-row fingerprint in fp32 and whose oracle run takes about a minute
+LARGE = ("cfg2_32k", "cfg1_8k", "cfg5_thrash")
 
 PROJ_SEED = 12345
 N_PROJ = 8
@@ -53,8 +74,99 @@ def bf16_round(x: np.ndarray) -> np.ndarray:
     return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
 
 
+def _one_angle_inverse(u: np.ndarray, index: int, base: float) -> np.ndarray:
+    """The direction that the one-angle rotation to position index-1 (inf_llm/attention/rope.py:89-104) turns into u:
+    u rotated by the negative angles.  u is (..., D); halves are paired as rotate_half pairs them."""
+    d = u.shape[-1]
+    inv = 1.0 / (base ** (np.arange(0, d, 2, dtype=np.float64) / d))
+    ang = (index - 1) * inv
+    cos, sin = np.cos(ang), np.sin(ang)
+    x1, x2 = u[..., : d // 2], u[..., d // 2:]
+    return np.concatenate((x1 * cos + x2 * sin, x2 * cos - x1 * sin), axis=-1)
+
+
+def _plant(case, q, k):
+    """Plants directions into whole-prompt q (H, T, D) and k (H_kv, T, D) float32 arrays, in place.
+
+    "relevant": `units` memory units get a direction of their own in every KV head (their keys lean towards it with
+    cosine `lean`); for each, one later exec block's queries lean towards the direction that retrieval's one-angle
+    rotation turns into it, so that the unit wins that exec block's top-k.
+    "rotate": unit b belongs to group b % groups and leans towards its group's direction, newer units a little more
+    (graded, so that the order inside a group does not hang on noise); the queries of exec block t lean towards
+    group t % groups: consecutive exec blocks retrieve disjoint groups."""
+    p = case["plant"]
+    H, HKV, D = case["H"], case["HKV"], case["D"]
+    g = H // HKV
+    T = q.shape[1]
+    rng = np.random.default_rng(p["seed"])
+    n_units = (T - case["n_init"] - case["n_local"]) // case["bs"]
+    n_eb = T // case["exc"]
+    amp = np.float32(p["lean"] * np.sqrt(D))
+    keep = np.float32(np.sqrt(1.0 - p["lean"] ** 2))
+
+    def directions(n):
+        u = rng.standard_normal((n, HKV, D))
+        return u / np.linalg.norm(u, axis=-1, keepdims=True)
+
+    def lean_keys(b, u, scale=1.0):
+        st = case["n_init"] + b * case["bs"]
+        k[:, st:st + case["bs"]] = keep * k[:, st:st + case["bs"]] + (np.float32(scale) * amp) * u[:, None, :].astype(np.float32)
+
+    def lean_queries(eb, u, scale=1.0):
+        w = np.repeat(_one_angle_inverse(u, case["n_local"], case["base"]), g, axis=0)  # (H, D)
+        a, b = eb * case["exc"], (eb + 1) * case["exc"]
+        q[:, a:b] = keep * q[:, a:b] + (np.float32(scale) * amp) * w[:, None, :].astype(np.float32)
+
+    if p["kind"] == "relevant":
+        units = rng.permutation(n_units)[: p["units"]]
+        u = directions(len(units))
+        for i, b in enumerate(units.tolist()):
+            lean_keys(b, u[i])
+            first = (case["n_init"] + (b + 1) * case["bs"] + case["n_local"]) // case["exc"] + 2
+            if first < n_eb:
+                lean_queries(first + int(rng.integers(0, n_eb - first)), u[i])
+    elif p["kind"] == "rotate":
+        u = directions(p["groups"])
+        for b in range(n_units):
+            lean_keys(b, u[b % p["groups"]], 1.0 + 0.03 * (b // p["groups"]))
+        for eb in range(n_eb):
+            lean_queries(eb, u[eb % p["groups"]])
+    else:
+        raise ValueError(p["kind"])
+
+
+def _projected_inputs(case):
+    """q, k, v of the whole prompt as projections of seeded hidden states: hidden (T, width) ~N(0,1) from seed
+    `seed`, weights ~N(0, 0.02) from seeds 1, 2, 3 (torch generators), fp32 matmuls."""
+    T, width = sum(case["lens"]), case["hidden"]
+    x = torch.randn((T, width), generator=torch.Generator().manual_seed(case["seed"]))
+    out = []
+    for seed, heads in ((1, case["H"]), (2, case["HKV"]), (3, case["HKV"])):
+        w = torch.randn((heads * case["D"], width), generator=torch.Generator().manual_seed(seed)) * 0.02
+        out.append((x @ w.T).view(T, heads, case["D"]).permute(1, 0, 2).contiguous().numpy())
+    return out
+
+
 def make_inputs(case: dict):
-    """List of (q (H,L,D), k (H_kv,L,D), v (H_kv,L,D)) fp32 torch tensors, one per append."""
+    """List of (q (H, L, D), k (H_kv, L, D), v (H_kv, L, D)) fp32 torch tensors, one per append."""
+    if "hidden" in case or "plant" in case:
+        # generated for the whole prompt at once (planting addresses absolute tokens), then cut into the calls
+        T = sum(case["lens"])
+        if "hidden" in case:
+            q, k, v = _projected_inputs(case)
+        else:
+            rng = np.random.default_rng(case["seed"])
+            q = rng.standard_normal((case["H"], T, case["D"]), dtype=np.float32) * np.float32(case["qscale"])
+            k = rng.standard_normal((case["HKV"], T, case["D"]), dtype=np.float32)
+            v = rng.standard_normal((case["HKV"], T, case["D"]), dtype=np.float32)
+        if "plant" in case:
+            _plant(case, q, k)
+        q, k, v = (torch.from_numpy(bf16_round(a)) for a in (q, k, v))
+        out, st = [], 0
+        for L in case["lens"]:
+            out.append(tuple(t[:, st:st + L].contiguous() for t in (q, k, v)))
+            st += L
+        return out
     rng = np.random.default_rng(case["seed"])
     out = []
     for L in case["lens"]:

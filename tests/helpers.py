@@ -35,3 +35,11 @@ def near_tie_ok(ref_ids, got_ids, scores, rel=1e-3):
     kth = torch.sort(s, descending=True).values[len(ref_ids) - 1].item()
     scale = max(abs(kth), 1e-30)
     return all(abs(s[i].item() - kth) <= rel * scale for i in ref_set ^ got_set)
+
+
+# lines for the end-of-run summary (tests/conftest.py prints them): observed counts behind the tests' caps
+REPORT = []
+
+
+def report(line):
+    REPORT.append(line)

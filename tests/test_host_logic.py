@@ -58,6 +58,68 @@ def test_ctx_create_validates_like_the_reference():
     assert L.lib.infllm_ctx_create(ctypes.byref(_cfg(L, dtype=7)), ctypes.byref(h)) == L.E_UNSUPPORTED
 
 
+def test_decode_attention_rejects_zero_kv_heads():
+    """Argument checks come before any division by the head counts and before any launch (no GPU needed)."""
+    L = _lib()
+    one = lambda t, x: (t * 1)(x)  # noqa: E731
+    n = ctypes.c_int()
+    for heads, kv in ((8, 0), (0, 2), (8, -1)):
+        rc = L.lib.infllm_attn_decode(1 << 20, 1 << 20, heads, kv, 128, 1, one(ctypes.c_void_p, 1 << 20),
+                                      one(ctypes.c_void_p, 1 << 20), one(ctypes.c_int64, 128 * 128), one(ctypes.c_int32, 128),
+                                      one(ctypes.c_int32, 0), 1 << 20, 1 << 20, 4, ctypes.byref(n), -1, None, L.BF16, None)
+        assert rc == L.E_BADARG, (heads, kv)
+
+
+def _saved_header(L, **kw):
+    """A header as infllm_ctx_save writes it for _cfg(L), with fields overridden."""
+    import struct
+
+    f = dict(magic=0x324d454d4c464e49, H=8, HKV=2, D=128, n_init=128, n_local=512, bs=128, dtype=L.BF16, length=128 + 128 + 512,
+             frontier=256, n_units=1, init_len=128, init_full=1, load_count=3, n_lru=1, strategy=L.CACHE_LRU, max_cached=8,
+             topk=4, exc=128, repr_topk=4, chunk=0, decay=0, pad0=0, pad1=0)
+    f.update(kw)
+    return struct.pack("<24q", *f.values()), f
+
+
+def _saved_file(L, path, lru=((0, 3.0),), truncate=0, **kw):
+    import struct
+
+    hdr, f = _saved_header(L, **kw)
+    live = f["length"] - f["frontier"]
+    unit = 2 * f["HKV"] * f["bs"] * f["D"] * 2
+    body = b"".join(struct.pack("<qd", i, s) for i, s in lru)
+    body += bytes(2 * f["HKV"] * f["init_len"] * f["D"] * 2 + f["n_units"] * f["H"] * f["D"] * 2
+                  + 2 * f["HKV"] * live * f["D"] * 2 + f["H"] * live * 4 + f["n_units"] * unit)
+    data = hdr + body
+    with open(path, "wb") as fh:
+        fh.write(data[:len(data) - truncate] if truncate else data)
+
+
+@pytest.mark.parametrize("why,kw", [
+    ("not a saved context memory", dict(magic=1)),
+    ("another configuration", dict(topk=5)),
+    ("another configuration", dict(max_cached=16)),
+    ("inconsistent lengths", dict(frontier=300)),
+    ("inconsistent lengths", dict(length=100)),
+    ("inconsistent lengths", dict(init_len=200)),
+    ("cached units", dict(n_lru=9)),
+    ("bytes its header implies", dict(truncate=100)),
+    ("wrongly", dict(lru=((5, 3.0),))),
+    ("wrongly", dict(n_lru=2, lru=((0, 3.0), (0, 4.0)))),
+])
+def test_ctx_load_refuses_corrupt_files_before_touching_anything(tmp_path, why, kw):
+    """Every field of a saved memory is checked against the configuration and against the file's size before the
+    context (or a GPU) is touched: these loads fail on a machine without a device."""
+    L = _lib()
+    h = ctypes.c_void_p()
+    L.check(L.lib.infllm_ctx_create(ctypes.byref(_cfg(L)), ctypes.byref(h)))
+    path = str(tmp_path / "mem.u0")
+    _saved_file(L, path, **kw)
+    assert L.lib.infllm_ctx_load(h, path.encode(), None) == L.E_BADARG
+    assert why.encode() in L.lib.infllm_last_error(), L.lib.infllm_last_error()
+    L.lib.infllm_ctx_destroy(h)
+
+
 class _NativeLru:
     def __init__(self, L, cap):
         self.L, self.h = L, ctypes.c_void_p()

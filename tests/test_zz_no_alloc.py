@@ -12,6 +12,7 @@ import pytest
 import torch
 
 from helpers import MAX_ABS_TOL, MEAN_ABS_TOL
+from oracle import infllm_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -44,22 +45,32 @@ def _decode_both(L, H, HKV, seg_lens, seed):
     # the allocation-free entry point: inputs and outputs only
     got = torch.empty(H, D, dtype=torch.bfloat16, device=DEV)
     got_lse = torch.empty(H, dtype=torch.float32, device=DEV)
+    call = lambda: L.check(L.lib.infllm_attn_decode_noalloc(  # noqa: E731
+        q0.data_ptr(), q1.data_ptr(), H, HKV, D, n, seg_k, seg_v, seg_hs, seg_len, seg_q, got.data_ptr(), D,
+        got_lse.data_ptr(), L.BF16, L.stream_ptr()))
+    call()  # the first call on a device looks the scratch address up (and makes the module resident)
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
-    L.check(L.lib.infllm_attn_decode_noalloc(q0.data_ptr(), q1.data_ptr(), H, HKV, D, n, seg_k, seg_v, seg_hs, seg_len,
-                                             seg_q, got.data_ptr(), D, got_lse.data_ptr(), L.BF16, L.stream_ptr()))
+    before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
+    got.zero_()
+    call()
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
-    return got.float().cpu(), want.float().cpu(), got_lse.cpu(), want_lse.cpu()
+    assert torch.cuda.memory_allocated() == before, "torch's allocator was used"
+    assert torch.cuda.mem_get_info()[0] == free_before, "the device's free memory changed: something allocated"
+    # the CPU oracle on the same inputs: first segment with the local query, the others with the global one
+    stages = [O.Stage((q0 if i == 0 else q1).float().cpu()[:, None, :], k.float().cpu(), v.float().cpu())
+              for i, (k, v) in enumerate(zip(ks, vs))]
+    ora, _ = O.multi_stage_attention(stages)
+    return got.float().cpu(), want.float().cpu(), got_lse.cpu(), want_lse.cpu(), ora[:, 0, :]
 
 
 def test_noalloc_decode_matches_the_buffered_entry_point_twice_in_a_row():
     from infllm_b200 import _lib as L
 
     for seed, (H, HKV, seg_lens) in enumerate([(32, 8, [4096, 128, 128, 128, 128, 77, 300]), (8, 2, [200, 128, 5])]):
-        got, want, got_lse, want_lse = _decode_both(L, H, HKV, seg_lens, 100 + seed)
-        diff = (got - want).abs()
-        assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL
+        got, want, got_lse, want_lse, ora = _decode_both(L, H, HKV, seg_lens, 100 + seed)
+        for ref in (want, ora):  # the buffered entry point (same kernels) and the CPU oracle
+            diff = (got - ref).abs()
+            assert diff.max().item() <= MAX_ABS_TOL and diff.mean().item() <= MEAN_ABS_TOL
         torch.testing.assert_close(got_lse, want_lse, atol=1e-4, rtol=1e-5)
 
 
