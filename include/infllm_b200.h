@@ -230,7 +230,9 @@ typedef struct infllm_config {
   int32_t debug_flags;    /* 0 in production; test switches, one per bit —
                            *  1: exec blocks on the shape-generic mma.sync kernels, no tcgen05 kernels
                            *  2: no look-ahead retrieval: every exec block waits for its ids from the device
-                           *  4: look-ahead units staged by an SM copy kernel instead of one cudaMemcpyAsync each
+                           *  4: refills from a device copy of the store by one cudaMemcpyAsync per unit as well
+                           *     (refills from the pinned host store always are, like MemoryUnit.load,
+                           *     context_manager.py:57-71), not by the copy kernel
                            *  8: the two-heads-per-CTA tcgen05 attention kernel whatever the head count
                            * 16: one-token appends wait for the retrieved ids before launching the attention
                            * 32: one-token appends do not fetch ahead the units ranked just below the retrieval */

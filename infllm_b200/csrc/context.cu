@@ -362,8 +362,14 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   uint64_t keep = UINT64_MAX;
   INFLLM_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
 
-  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
-  INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->urgent_stream, cudaStreamNonBlocking));
+  {
+    // refills from a device copy of the store are kernels of a few small CTAs: on high-priority streams they are
+    // placed ahead of the CTAs of the main stream's grids that have not started yet
+    int lo = 0, hi = 0;
+    INFLLM_CUDA_OK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    INFLLM_CUDA_OK(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
+    INFLLM_CUDA_OK(cudaStreamCreateWithPriority(&c->urgent_stream, cudaStreamNonBlocking, hi));
+  }
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_d2h, cudaEventDisableTiming));
   INFLLM_CUDA_OK(cudaEventCreateWithFlags(&c->ev_ingest, cudaEventDisableTiming));
@@ -695,6 +701,7 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
   la.staged = true;
   std::vector<const void*> src;
   std::vector<void*> dst;
+  std::vector<char> on_device;
   for (int32_t b : la.ids) {
     if (c->slot_of.count(b)) continue;
     auto sf = c->staged_for.find(b);
@@ -713,6 +720,7 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     }
     src.push_back(c->unit_src(b));
     dst.push_back((char*)c->cache + (int64_t)slot * c->unit_bytes);
+    on_device.push_back(c->dev_resident(b));
     if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
     c->staged_pending = true;
   }
@@ -720,16 +728,22 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     // the spare slots taken above may have held units that the previous exec block's attention read
     if (c->attn_prev_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn_prev, 0));
     trace_mark(c, c->copy_stream, TR_STAGE_BEGIN, target);  // behind the waits: the interval is copy time only
-    if (!(g.debug_flags & 4)) {  // default: one cudaMemcpyAsync per unit on the copy engine; flag bit 2 selects the
-                                 // SM copy kernel, which is faster alone but slows concurrent attention down
-      for (size_t i = 0; i < src.size(); ++i) {
+    // Units that have a device copy are gathered by the copy kernel (one launch for the batch); units that only the
+    // pinned host store holds travel by one cudaMemcpyAsync each on the copy engine: a kernel that reads host memory
+    // gets more out of the link (49 against 38 GB/s) but its CTAs sit on SMs for the whole transfer and slowed the
+    // exec-block attention by a tenth when measured, so that the prompt took longer.  Flag bit 2: no copy kernel.
+    std::vector<const void*> ksrc;
+    std::vector<void*> kdst;
+    for (size_t i = 0; i < src.size(); ++i) {
+      if (!on_device[i] || (g.debug_flags & 4)) {
         INFLLM_CUDA_OK(cudaMemcpyAsync(dst[i], src[i], c->unit_bytes, cudaMemcpyDefault, c->copy_stream));
-        INFLLM_TRY(mark_slot_copy(c, dst[i]));
+      } else {
+        ksrc.push_back(src[i]);
+        kdst.push_back(dst[i]);
       }
-    } else {
-      INFLLM_TRY(stage_units_launch(src.data(), dst.data(), (int)src.size(), c->unit_bytes, c->copy_stream));
-      for (size_t i = 0; i < src.size(); ++i) INFLLM_TRY(mark_slot_copy(c, dst[i]));
     }
+    if (!ksrc.empty()) INFLLM_TRY(stage_units_launch(ksrc.data(), kdst.data(), (int)ksrc.size(), c->unit_bytes, c->copy_stream));
+    for (size_t i = 0; i < src.size(); ++i) INFLLM_TRY(mark_slot_copy(c, dst[i]));
   }
   if (c->staged_pending) {
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
@@ -825,7 +839,9 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
   } else {
     c->lru.stamp(ids.data(), (int)ids.size(), 0.0);
   }
-  bool late = false, adopted = false;
+  bool late = false;
+  std::vector<const void*> late_src;
+  std::vector<void*> late_dst;
   for (int32_t b : ids) {
     if (c->slot_of.count(b)) {
       c->counters.cache_hits += 1;
@@ -836,9 +852,11 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     if (st != c->staged.end()) {  // the look-ahead already brought it in
       c->slot_of[b] = st->second;
       if (track) c->tab_updates[b] = st->second;
+      // s waits for THIS unit's copy: a unit sealed a moment ago can be staged for a later exec block and still be
+      // retrieved by this one, so the event of "this exec block's batch" would not cover it
+      if (c->slot_ev_used[st->second]) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->slot_ev[st->second], 0));
       c->staged.erase(st);
       c->staged_for.erase(b);
-      adopted = true;
       continue;
     }
     if (c->free_slots.empty()) {
@@ -885,8 +903,13 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       c->d2h_synced_upto_urgent = c->num_blocks;
     }
     // on a stream of its own: the exec block must not wait behind the copies staged for later blocks
-    INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->unit_src(b), c->unit_bytes,
-                                   cudaMemcpyDefault, c->urgent_stream));
+    if ((g.debug_flags & 4) || !c->dev_resident(b)) {
+      INFLLM_CUDA_OK(cudaMemcpyAsync((char*)c->cache + (int64_t)slot * c->unit_bytes, c->unit_src(b), c->unit_bytes,
+                                     cudaMemcpyDefault, c->urgent_stream));
+    } else {
+      late_src.push_back(c->unit_src(b));
+      late_dst.push_back((char*)c->cache + (int64_t)slot * c->unit_bytes);
+    }
     if (!c->dev_resident(b)) {
       c->counters.h2d_bytes += c->unit_bytes;
       c->counters.h2d_late_bytes += c->unit_bytes;
@@ -903,15 +926,12 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       ++it;
     }
   }
+  if (!late_src.empty())
+    INFLLM_TRY(stage_units_launch(late_src.data(), late_dst.data(), (int)late_src.size(), c->unit_bytes, c->urgent_stream));
   if (late) {
     trace_mark(c, c->urgent_stream, TR_LATE_END, eb);
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_copy, c->urgent_stream));
     INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_copy, 0));
-  }
-  if (adopted && c->staged_pending) {
-    const infllm_ctx::LookAhead& la = c->la[eb % (c->look_depth + 1)];
-    const bool own = la.target == eb && la.staged && la.staged_recorded;
-    INFLLM_CUDA_OK(cudaStreamWaitEvent(s, own ? la.ev_staged : c->ev_stage, 0));
   }
   if (c->staged.empty()) c->staged_pending = false;
   return INFLLM_OK;
@@ -956,7 +976,7 @@ int decode_fetch_ahead(infllm_ctx* c, const std::vector<int32_t>& retrieval, con
     c->staged[b] = slot;
     c->staged_for[b] = INT64_MAX;
     c->unlisted.push_back({b, slot});
-    c->counters.h2d_bytes += c->unit_bytes;
+    if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
     c->staged_pending = true;
     issued = true;
   }

@@ -114,36 +114,31 @@ int pack_units_launch(const void* k, const void* v, int64_t hs, int64_t tok0, in
   return INFLLM_OK;
 }
 
-// Staging copy of whole units from the pinned host store into cache slots by the SMs (the host pointers are
-// device-visible under unified addressing).  Many 512 KiB cudaMemcpyAsync calls reach only about two thirds of
-// the link rate because of their per-copy cost; one kernel that keeps a few hundred KiB of loads in flight
-// does better and costs the host a single launch.
+// Refill copy of whole units into cache slots by the SMs: one CTA of 256 threads per unit, four 16-byte loads in
+// flight per thread, one launch per batch.  The context uses it for units that have a copy in device memory.  It
+// also works on the pinned host store (the host pointers are device-visible under unified addressing) and gets
+// 49 GB/s out of the link where one 512 KiB cudaMemcpyAsync per unit gets 38 GB/s, but its CTAs then hold SM
+// resources for the length of the transfer, which cost a concurrent exec-block attention more than the faster
+// copies gained; host-resident units therefore go through the copy engine.
 constexpr int kMaxStageUnits = 64;
 struct StageList {
   const uint4* src[kMaxStageUnits];
   uint4* dst[kMaxStageUnits];
 };
-constexpr int kStageCtas = 8;  // few CTAs: they take few SMs away from a concurrent attention grid
-__global__ void __launch_bounds__(1024) stage_units_kernel(const __grid_constant__ StageList list, int n_units, int n16) {
-  // the CTAs walk over all 16-byte words of all units; every thread keeps four loads in flight
-  // (8 CTAs x 1024 threads x 64 B = 512 KiB outstanding over the link)
-  const int64_t total = (int64_t)n_units * n16;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < total; i += 4 * stride) {
-    uint4 r[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t w = i + e * stride;
-      r[e] = __ldcs(list.src[w / n16] + w % n16);
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t w = i + e * stride;
-      list.dst[w / n16][w % n16] = r[e];
-    }
+constexpr int kStageThreads = 256;
+__global__ void __launch_bounds__(kStageThreads) stage_units_kernel(const __grid_constant__ StageList list, int n16) {
+  const uint4* __restrict__ src = list.src[blockIdx.x];
+  uint4* __restrict__ dst = list.dst[blockIdx.x];
+  int i = threadIdx.x;
+  for (; i + 3 * kStageThreads < n16; i += 4 * kStageThreads) {
+    const uint4 a = __ldcs(src + i), b = __ldcs(src + i + kStageThreads), c = __ldcs(src + i + 2 * kStageThreads),
+                d = __ldcs(src + i + 3 * kStageThreads);
+    dst[i] = a;
+    dst[i + kStageThreads] = b;
+    dst[i + 2 * kStageThreads] = c;
+    dst[i + 3 * kStageThreads] = d;
   }
-  for (; i < total; i += stride) list.dst[i / n16][i % n16] = list.src[i / n16][i % n16];
+  for (; i < n16; i += kStageThreads) dst[i] = __ldcs(src + i);
 }
 
 int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int64_t unit_bytes, cudaStream_t s) {
@@ -154,7 +149,7 @@ int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int6
       list.src[i] = (const uint4*)h_src[done + i];
       list.dst[i] = (uint4*)d_dst[done + i];
     }
-    stage_units_kernel<<<kStageCtas, 1024, 0, s>>>(list, m, (int)(unit_bytes / 16));
+    stage_units_kernel<<<m, kStageThreads, 0, s>>>(list, (int)(unit_bytes / 16));
     INFLLM_LAUNCH_OK("stage_units_kernel");
   }
   return INFLLM_OK;
