@@ -352,7 +352,7 @@ def run_ours(args, rank, world, local_rank, device_store_mb=0, light=False):
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    tokens = args.tokens
+    tokens = args.tokens or CFG["tokens"]
     groups = world if (args.head_groups and world > 1) else 1  # one layer over all GPUs instead of a replica per GPU
     comm = None
     if groups > 1:
@@ -505,11 +505,13 @@ def make_decode_memory(dev, rope, seed):
             small(HKV, DEC["n_local"], D), small(HKV, DEC["n_local"], D)), direction
 
 
-def run_decode(args, rank, world, local_rank):
+def run_decode(args, rank, world, local_rank, device_store_mb=0):
+    """The decode workload on one GPU per rank.  device_store_mb = 0 (the headline): the 8192 units of a layer live in
+    the pinned host store and every cache refill crosses PCIe.  > 0: the variant with a device copy of the store."""
     import torch.distributed as dist
 
     from infllm_b200 import _lib
-    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM, device_store_reserve
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -521,8 +523,10 @@ def run_decode(args, rank, world, local_rank):
     cms, dirs = [], []
     for li in range(n_layers):
         mem, direction = make_decode_memory(dev, rope, seed=17 * rank + li)
+        if device_store_mb and li == 0:
+            device_store_reserve(device_store_mb * n_layers, dev)
         cm = ContextManager(rope, DEC["n_init"], DEC["n_local"], DEC["bs"], DEC["max_cached"], DEC["topk"], DEC["exc"],
-                            None, True, DEC["repr_topk"])
+                            None, True, DEC["repr_topk"], device_store_mb=device_store_mb)
         cm.load_synthetic(*mem)
         del mem
         cms.append(cm)
@@ -537,11 +541,13 @@ def run_decode(args, rank, world, local_rank):
     h_o = torch.empty((1, H, 1, D), dtype=torch.bfloat16).pin_memory()
     pos = [0]
 
+    toks = [(qs[i], ks[i], vs[i]) for i in range(total)]  # views made once: the timed loop is the library's
+
     def step_device():  # one token through every layer
         for cm in cms:
-            i = pos[0]
+            q, k, v = toks[pos[0]]
             pos[0] += 1
-            cm.append(qs[i], ks[i], vs[i], qs[i], ks[i], vs[i])
+            cm.append(q, k, v, q, k, v)
 
     def step_host():
         for cm in cms:
@@ -627,8 +633,10 @@ def run_decode(args, rank, world, local_rank):
                               achieved_gbs=(dec_bytes / (dec_ms / 1e3) / 1e9 if dec_ms > 0 else None),
                               us_per_launch=1e3 * dec_ms / max(dec_n, 1), bytes_per_launch=dec_bytes / max(dec_n, 1)),
         store=dict(hits=hits, misses=misses, miss_rate=misses / max(hits + misses, 1),
-                   refill_bytes_per_token_layer=misses * 524288 / max(per_layer, 1),
-                   refill_source="pinned host store (cudaMemcpyAsync over PCIe)"),
+                   h2d_bytes_per_token_layer=sum(y["h2d_bytes"] - x["h2d_bytes"] for x, y in zip(info0, info1)) / max(per_layer, 1),
+                   units_read_in_place_per_token_layer=sum(y["inplace_units"] - x["inplace_units"]
+                                                           for x, y in zip(info0, info1)) / max(per_layer, 1),
+                   refill_source=("device copy of the store" if device_store_mb else "pinned host store over PCIe")),
         clocks=clocks)
     if rank == 0 and world == 1 and not args.no_cpu:
         v, secs, cores = cpu_decode_sample()
@@ -637,6 +645,132 @@ def run_decode(args, rank, world, local_rank):
                                            "instead of 8192, fp32 torch on the host; the unit scoring is a quarter of "
                                            "the full size's, the attention the same")
     return line
+
+
+THRASH = dict(H=32, HKV=32, D=128, base=1e6, n_init=128, n_local=4096, bs=128, topk=16, repr_topk=8, max_cached=16, exc=256,
+              chunk=8192, tokens=524288, groups=8)
+
+
+def thrash_chunk(dev, start, n, dirs_k, dirs_q, unit_gain, gen):
+    """q, k, v (heads, n, D) bf16 of tokens [start, start + n) of the cache-thrash prompt: N(0,1), the keys of memory
+    unit b leaning (cos 0.6, times a per-unit gain) towards the direction of group b % G, the queries of exec block t
+    leaning towards the direction that retrieval's one-angle rotation turns into group t % G's."""
+    T = THRASH
+    H, D, G = T["H"], T["D"], T["groups"]
+    q = torch.randn((H, n, D), generator=gen, device=dev)
+    k = torch.randn((H, n, D), generator=gen, device=dev)
+    v = torch.randn((H, n, D), generator=gen, device=dev)
+    tok = torch.arange(start, start + n, device=dev)
+    amp, keep = 0.6 * math.sqrt(D), 0.8
+    unit = ((tok - T["n_init"]).clamp(min=0) // T["bs"]).clamp(max=unit_gain.numel() - 1)
+    in_unit = (tok >= T["n_init"]).float()
+    k = keep * k + (amp * in_unit * unit_gain[unit])[None, :, None] * dirs_k[unit % G].permute(1, 0, 2)
+    eb = tok // T["exc"]
+    q = keep * q + amp * dirs_q[eb % G].permute(1, 0, 2)
+    return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def run_thrash(args, rank, world, local_rank):
+    """Cache-thrash stress: a Qwen-1.5-7B-shaped layer (32 query / 32 KV heads), 524288 tokens = 4096 memory units of
+    2 MiB, topk 16, repr_topk 8, exec blocks of 256, and a cache of exactly one retrieval (max_cached_block 16: the
+    configuration's literal 8 cannot hold a retrieval and is refused, as the reference asserts).  Consecutive exec
+    blocks retrieve disjoint groups of units, so every exec block evicts the whole cache and refills it from the
+    pinned host store: 32 MiB over PCIe per 256 tokens."""
+    from infllm_b200 import _lib
+    from infllm_b200.attention import ContextManager, RotaryEmbeddingESM
+
+    T = THRASH
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    tokens = args.tokens or T["tokens"]
+    H, D, G = T["H"], T["D"], T["groups"]
+    rope = RotaryEmbeddingESM(D, T["base"], 1.0)
+    refused = None
+    try:
+        probe = ContextManager(rope, T["n_init"], T["n_local"], T["bs"], 8, T["topk"], T["exc"], None, True, T["repr_topk"])
+        z = torch.zeros((1, H, T["exc"], D), dtype=torch.bfloat16, device=dev)
+        probe.append(z, z, z, z, z, z)
+    except _lib.InfLLMCapacityError as e:
+        refused = str(e)
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    dirs = torch.randn((G, H, D), generator=gen, device=dev)
+    dirs_k = dirs / dirs.norm(dim=-1, keepdim=True)
+    # the direction that the one-angle rotation to position n_local - 1 (rope.py:89-104) turns into dirs_k
+    inv = 1.0 / (T["base"] ** (torch.arange(0, D, 2, device=dev, dtype=torch.float64) / D))
+    ang = (T["n_local"] - 1) * inv
+    x1, x2 = dirs_k[..., :D // 2].double(), dirs_k[..., D // 2:].double()
+    dirs_q = torch.cat((x1 * ang.cos() + x2 * ang.sin(), x2 * ang.cos() - x1 * ang.sin()), dim=-1).float()
+    n_units = (tokens - T["n_init"]) // T["bs"] + 1
+    unit_gain = 1.0 + 0.3 * torch.rand((n_units,), generator=gen, device=dev)
+    chunks = [thrash_chunk(dev, s0, min(T["chunk"], tokens - s0), dirs_k, dirs_q, unit_gain, gen)
+              for s0 in range(0, tokens, T["chunk"])]
+    cm = ContextManager(rope, T["n_init"], T["n_local"], T["bs"], T["max_cached"], T["topk"], T["exc"], None, True,
+                        T["repr_topk"])
+
+    def prompt():
+        cm.reset()
+        o = None
+        for q, k, v in chunks:
+            o = cm.append(q[None], k[None], v[None], q[None], k[None], v[None])
+        return o
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warm = max(1, min(args.steps, 2)), 3
+    with torch.inference_mode():
+        for _ in range(warm):
+            prompt()
+        barrier()
+        clk_p, clk_f = sample_clocks_start(local_rank)
+        l0 = _lib.lib.infllm_launch_count()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            prompt()
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b)
+        launches = _lib.lib.infllm_launch_count() - l0
+        info = cm.info()
+        clocks = sample_clocks_stop(clk_p, clk_f)
+        cm.trace(True)
+        prompt()
+        trace = cm.get_trace()
+        overlap = ContextManager.refill_overlap(trace)
+        cm.trace(False)
+        # how many of the exec blocks past the first 2 * G * topk units evicted the whole cache
+        last = cm.last_topk()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    n_eb = tokens // T["exc"]
+    groups_last = sorted({b % G for b in last[-1]}) if last else []
+    return dict(
+        metric="cache-thrash prefill tokens/s/GPU (max_cached == topk)", value=world * tokens * steps / (ms / 1e3),
+        unit="tokens/s", n_gpus=world, steps=steps, warmup=warm, ms_per_step=ms / steps, higher_is_better=True,
+        scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload=f"qwen-1.5-7b-shaped attention layer (32q/32kv, d128, rope 1e6), {tokens}-token prefill in "
+                             f"8192-token calls, exec 256, n_local 4096, unit 128 (2 MiB), topk 16, repr_topk 8, "
+                             f"max_cached 16; {G} unit groups, exec block t retrieves group t % {G}",
+                    literal_max_cached_8=("refused: " + refused) if refused else "NOT refused",
+                    l2="16 units x 2 MiB refilled per exec block exceed nothing by themselves; the 4 GiB of q/k/v per "
+                       "131072 tokens do", replicas=world),
+        gpu_launches=int(launches),
+        store=dict(misses_per_exec_block=info["cache_misses"] / max(n_eb, 1), evictions_per_exec_block=info["evictions"] / max(n_eb, 1),
+                   h2d_bytes_per_exec_block=info["h2d_bytes"] / max(n_eb, 1), h2d_late_bytes=info["h2d_late_bytes"],
+                   h2d_gbs=info["h2d_bytes"] / (ms / steps / 1e3) / 1e9,
+                   h2d_overlap_frac=overlap["overlap_frac"], h2d_hidden_frac=overlap["hidden_frac"],
+                   refill_copy_ms_per_step=overlap["copy_ms"], groups_in_last_retrieval=groups_last),
+        clocks=clocks)
 
 
 def run_decode_sharded(args, rank, world, local_rank):
@@ -816,13 +950,14 @@ def run_model(args, rank, world, local_rank):
     dec = HeadGroupDecoder(32, 4096, CFG["H"], CFG["HKV"], CFG["D"], 14336, 128256, attn, rank=rank, world=world,
                            comm=comm, seed=0, device=dev, rope_base=500000.0)
     g = torch.Generator().manual_seed(0)
-    h_ids = torch.randint(0, 128256, (1, args.tokens), generator=g).pin_memory()
+    tokens = args.tokens or CFG["tokens"]
+    h_ids = torch.randint(0, 128256, (1, tokens), generator=g).pin_memory()
     n_new = 16
 
     def prompt():
         dec.reset()
         logits = None
-        for st in range(0, args.tokens, CFG["chunk"]):
+        for st in range(0, tokens, CFG["chunk"]):
             logits = dec.step(h_ids[:, st:st + CFG["chunk"]].to(dev, non_blocking=True))
         return logits
 
@@ -854,10 +989,10 @@ def run_model(args, rank, world, local_rank):
     if comm is not None:
         comm.close()
     return dict(metric="whole-model chunked prefill tokens/s (Llama-3-8B shape, random weights)",
-                value=args.tokens / (ms_prefill / 1e3), unit="tokens/s", n_gpus=world, steps=args.steps,
+                value=tokens / (ms_prefill / 1e3), unit="tokens/s", n_gpus=world, steps=args.steps,
                 warmup=args.warmup, ms_per_step=ms_prefill, higher_is_better=True,
                 scaling="strong" if world > 1 else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
-                config=dict(workload=f"32-layer decoder, {args.tokens}-token prompt in chunks of {CFG['chunk']}, "
+                config=dict(workload=f"32-layer decoder, {tokens}-token prompt in chunks of {CFG['chunk']}, "
                                      f"exec blocks of {CFG['exc']}, then {n_new} greedy tokens; host token ids",
                             parallelism=f"kv-head-groups{world}" if world > 1 else "single"),
                 decode_ms_per_token=ms_decode / n_new, first_tokens=tokens[:n_new])
@@ -871,8 +1006,9 @@ def main():
                     help="default 3 (prefill) or 136 (decode: past the first sealing, whose one-time growth of the "
                          "representative-key array would otherwise sit in the timed region)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tokens", type=int, default=CFG["tokens"])
-    ap.add_argument("--workload", default="both", choices=["both", "prefill", "decode", "model"],
+    ap.add_argument("--tokens", type=int, default=None,
+                    help="prompt length: default 131072 (prefill, model) or 524288 (thrash)")
+    ap.add_argument("--workload", default="both", choices=["both", "prefill", "decode", "model", "thrash"],
                     help="prefill: 131072-token prompt, the first half of the metric and the line's value; decode: the "
                          "1M-token decode, the second half; both (default): the prefill line with the decode line "
                          "under its key 'decode'")
@@ -886,6 +1022,8 @@ def main():
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
     ap.add_argument("--layers", type=int, default=DEC["layers"], help="layer memories that take turns in the decode workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--device-store-mb", type=int, default=0,
+                    help="decode workload alone: MiB per layer of device copy of the store (0 = pinned host store only)")
     ap.add_argument("--max-cached", type=int, default=CFG["max_cached"], help="max_cached_block (32 in the named config)")
     args = ap.parse_args()
     CFG["max_cached"] = args.max_cached
@@ -908,11 +1046,18 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    decode = run_decode_sharded if (world > 1 or args.sharded) else run_decode
+    if args.device_store_mb and not (world > 1 or args.sharded):
+        import functools
+
+        decode = functools.partial(run_decode, device_store_mb=args.device_store_mb)
+    else:
+        decode = run_decode_sharded if (world > 1 or args.sharded) else run_decode
     if args.workload == "decode":
         line = decode(args, rank, world, local_rank)
     elif args.workload == "model":
         line = run_model(args, rank, world, local_rank)
+    elif args.workload == "thrash":
+        line = run_thrash(args, rank, world, local_rank)
     else:
         line = run_ours(args, rank, world, local_rank)
         import copy
@@ -931,6 +1076,16 @@ def main():
             dargs = copy.copy(args)
             dargs.steps, dargs.warmup = args.decode_steps, 136
             line["decode"] = decode(dargs, rank, world, local_rank)
+            if world == 1 and not args.sharded and not args.device_store_mb:
+                # the same decode with a device copy of the store (refills do not cross PCIe), beside the headline
+                gc.collect()
+                torch.cuda.empty_cache()
+                dv = run_decode(dargs, rank, world, local_rank, device_store_mb=4096)
+                line["decode"]["device_store"] = {k: dv[k] for k in ("value", "unit", "ms_per_step", "roofline",
+                                                                     "decode_attention", "store")}
+                gc.collect()
+                torch.cuda.empty_cache()
+                line["thrash"] = run_thrash(args, rank, world, local_rank)
             if world > 1 and not args.head_groups and CFG["HKV"] % world == 0:
                 # the same prompt through ONE layer sharded by KV-head groups over the GPUs (strong scaling)
                 gc.collect()
@@ -938,7 +1093,19 @@ def main():
                 hargs = copy.copy(args)
                 hargs.head_groups, hargs.no_cpu, hargs.steps = True, True, min(args.steps, 2)
                 hg = run_ours(hargs, rank, world, local_rank)
-                line["head_groups"] = {k: hg[k] for k in ("value", "unit", "ms_per_step", "scaling", "e2e", "roofline", "config")}
+                line["head_groups"] = {k: hg[k] for k in ("value", "unit", "ms_per_step", "scaling", "e2e", "roofline", "config",
+                                                           "host_ms_per_step", "parity")}
+    # the record of a run may keep only the end of this line: the figures that matter most, once more, last
+    dec = line.get("decode", line if line.get("unit") == "us/token" else {})
+    hg = line.get("head_groups", {})
+    line["summary"] = dict(
+        prefill_tokens_s=line.get("value") if line.get("unit") == "tokens/s" else None,
+        prefill_e2e_tokens_s=(line.get("e2e") or {}).get("value") if line.get("unit") == "tokens/s" else None,
+        prefill_roofline_frac=(line.get("roofline") or {}).get("frac") if line.get("unit") == "tokens/s" else None,
+        decode_us=dec.get("value"), decode_roofline_frac=(dec.get("roofline") or {}).get("frac"),
+        decode_parity_ok=(dec.get("parity") or {}).get("ok"),
+        head_groups_ms=hg.get("ms_per_step"), head_groups_parity_ok=(hg.get("parity") or {}).get("ok"),
+        thrash_tokens_s=(line.get("thrash") or {}).get("value"), n_gpus=world)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -145,9 +145,10 @@ int infllm_ingest_token(const void* d_q, int64_t q_hs, const void* d_k, int64_t 
  * (device pointers) with head stride h_seg_hs[s] elements; h_seg_q[s] selects the query variant
  * (0: d_q0, 1: d_q1) — the local stage uses the window-relative rotation, the global stage the
  * one-angle rotation.  The h_seg_* arrays are HOST arrays of n_seg <= INFLLM_MAX_SEGMENTS entries.
- * The keys are cut into chunks of 128; every chunk yields one partial: normalised output
- * d_part_o (max_parts, n_heads, head_dim) fp32 and log2-domain log-sum-exp d_part_lse (max_parts,
- * n_heads); *n_parts receives how many were written (infllm_attn_decode_max_parts bounds it).
+ * The key list of every KV head is cut into at most max_parts runs (two CTAs per SM over all KV heads, fewer
+ * for short lists); every run yields one partial per head: normalised output d_part_o (max_parts, n_heads,
+ * head_dim) fp32 and log2-domain log-sum-exp d_part_lse (max_parts, n_heads); *n_parts receives how many were
+ * written (infllm_attn_decode_max_parts bounds it; any max_parts >= 1 works).
  * logit_seg >= 0 also exports that segment's scaled log2-domain logits to d_logits (n_heads, seg_len).
  * infllm_lse_merge combines n_part partials into out (n_heads, head_dim) in `dtype` (head stride o_hs;
  * INFLLM_F32 keeps a rank's partial in fp32 for a second merge)
@@ -234,8 +235,7 @@ typedef struct infllm_config {
                            *     (refills from the pinned host store always are, like MemoryUnit.load,
                            *     context_manager.py:57-71), not by the copy kernel
                            *  8: the two-heads-per-CTA tcgen05 attention kernel whatever the head count
-                           * 16: one-token appends wait for the retrieved ids before launching the attention
-                           * 32: one-token appends do not fetch ahead the units ranked just below the retrieval */
+                           * 16: one-token appends wait for the retrieved ids before launching the attention */
   int32_t look_depth;     /* exec blocks ranked and staged ahead of the running one; 0 = default (2), at most 8; the
                            * cache gets that many times topk spare slots */
   int32_t chunk_topk_calc; /* chunk_topk_calc of the reference (context_manager.py:749-770, 548-610), in tokens; 0 = off:
@@ -289,6 +289,9 @@ typedef struct infllm_ctx_info {
   int64_t h2d_bytes, d2h_bytes; /* store traffic since create/reset */
   int64_t cache_hits, cache_misses, evictions;
   int64_t h2d_late_bytes; /* the part of h2d_bytes that an exec block had to wait for (not staged ahead of it) */
+  int64_t inplace_units;  /* one-token appends: retrieved units whose keys the attention read in place from the store
+                           * (over PCIe from the pinned host store, or from its device copy) because their refill had
+                           * not landed in a cache slot yet */
 } infllm_ctx_info;
 int infllm_ctx_get_info(infllm_ctx* ctx, infllm_ctx_info* info);
 /* Per-kernel timing, off by default.  When enabled, the context records a CUDA event pair around each

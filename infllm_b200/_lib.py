@@ -46,7 +46,7 @@ class Config(ctypes.Structure):
 class CtxInfo(ctypes.Structure):
     _fields_ = [(n, c_int64) for n in (
         "length", "frontier", "num_blocks", "init_len", "num_cached", "load_count", "exec_blocks",
-        "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions", "h2d_late_bytes")]
+        "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions", "h2d_late_bytes", "inplace_units")]
 
 
 # name -> (restype, argtypes); every symbol the header declares

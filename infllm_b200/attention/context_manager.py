@@ -135,6 +135,8 @@ class ContextManager:
         """context_manager.py:682-813.  q (B, H, L, D); k, v (B, H_kv, L, D); returns (B, H, L, D).
         The global tensors must be the local ones (inf_llm/attention/inf_llm.py:58-59 passes the same
         projections twice); the kernels rotate them per stage themselves."""
+        if self.initialized and local_q.shape[2] == 1 and not self.perhead and local_q.shape[0] == 1 and local_q.is_cuda:
+            return self._append_token(local_q, local_k, local_v, global_q)
         for t in (local_q, local_k, local_v):
             _lib.require_cuda(t, "ContextManager.append input")
         if global_q is not local_q and global_q.data_ptr() != local_q.data_ptr():
@@ -163,6 +165,24 @@ class ContextManager:
             for b in range(batch):
                 self._append_unit(self._ctx[b], q[b], k[b], v[b], out[b], length, stream)
         self.length += length
+        return out
+
+    def _append_token(self, q, k, v, global_q):
+        """One token of one sequence: the same call with the checks that cannot fail for this shape left out (the
+        host's share of a decode step is a few tens of microseconds, of the order of the GPU's)."""
+        if global_q is not q and global_q.data_ptr() != q.data_ptr():
+            raise NotImplementedError("distinct global_q/k/v tensors are not supported: pass the local ones")
+        if q.shape[1] != self.num_heads or k.shape[1] != self.num_heads_kv or q.dtype != self.dtype or \
+                q.stride(-1) != 1 or k.stride(-1) != 1 or k.stride() != v.stride() or not (k.is_cuda and v.is_cuda):
+            raise ValueError("ContextManager.append: a one-token call with other shapes, strides or dtype than the memory's")
+        out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        rc = _lib.lib.infllm_ctx_append(
+            self._ctx[0], q.data_ptr(), q.stride(1), q.stride(2), k.data_ptr(), k.stride(1), k.stride(2), v.data_ptr(),
+            v.stride(1), v.stride(2), out.data_ptr(), out.stride(1), out.stride(2), 1,
+            torch.cuda.current_stream(q.device).cuda_stream)
+        if rc:
+            _lib.check(rc)
+        self.length += 1
         return out
 
     @staticmethod

@@ -64,18 +64,23 @@ __device__ __forceinline__ bool mask_keep(int mode, int64_t off, int64_t size, i
 }
 
 // Decode attention whose unit segments are resolved on the device: segment first_seg + i of the launch holds
-// the unit ids[i], found in cache slot table[ids[i]].  This lets the attention follow the top-k kernel on the
-// stream before the host has seen the ids; the chunks of a unit that turns out not to be cached get weight
-// zero and *miss = 1, and the host, which learns the same from its own tables, launches those units again
-// after the refill (further partials, part_base on) and merges then.
+// the unit ids[i].  This lets the attention follow the top-k kernel on the stream before the host has seen the ids.
+// Two ways to find a unit: `ptrs`, a table of addresses (unit id -> where its K block lives right now: a cache
+// slot, a device copy of the store, or the pinned host store, which the GPU reads in place; 0 = nowhere), or
+// `table`, unit id -> cache slot (-1 when not cached) with the cache's base address.  A unit that cannot be found
+// contributes nothing and sets *miss.
 struct DecodeIndirect {
   const int32_t* ids = nullptr;    // n_units unit ids (device memory)
   const int32_t* table = nullptr;  // unit id -> cache slot, -1 when the unit is not cached (device memory)
+  const unsigned long long* ptrs = nullptr;  // unit id -> address of its K block (V follows at unit_bytes / 2)
   const char* cache = nullptr;     // slot 0
+  const unsigned long long* landing = nullptr;  // with ptrs: n_units addresses of landing slots (0 = none); a unit whose
+                                   // address has bit 0 set (it lives in the store) is also written to the slot of
+                                   // its place in ids
   int64_t unit_bytes = 0;          // K then V of one unit
   int32_t n_units = 0, first_seg = 0;
   int32_t* miss = nullptr;
-  // unit-range sharding: this GPU owns the ids [id_lo, id_lo + n_owned) and `table` starts at id_lo; a retrieved
+  // unit-range sharding: this GPU owns the ids [id_lo, id_lo + n_owned) and the tables start at id_lo; a retrieved
   // unit of another rank, or a padding id < 0, gets weight zero here and is not a miss
   int32_t id_lo = 0, n_owned = 0x7fffffff;
 };
@@ -83,8 +88,8 @@ struct DecodeIndirect {
 int attn_general_launch(const AttnParams& p, int head_dim, int dtype, cudaStream_t s);
 int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk,
-                       const DecodeIndirect* ind, int part_base);
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s,
+                       const DecodeIndirect* ind);
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
                      int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
                      float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps = 0, int64_t lse_ps = 0);

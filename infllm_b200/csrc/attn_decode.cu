@@ -1,20 +1,40 @@
 // Decode attention: one query token per head over a list of key/value segments.
 //
-// HBM-streaming split-K: the keys of all segments are cut into chunks (128 tokens through the C entry points,
-// 64 inside the context, which wants more CTAs in flight); one single-warp CTA handles one chunk of one KV
-// head for all the query heads of its group, reading each K and V row exactly once with 16-byte cp.async
-// copies that are all issued before the first is used.  Each CTA writes a
-// normalised partial output and its log-sum-exp; infllm_lse_merge combines partials — the chunks of one
-// GPU and, for unit-range sharding, the partials gathered from other GPUs.
-// Replaces the two attn.append calls of ContextManager._append (context_manager.py:486-489, 526-531)
-// for single-token exec blocks.
+// HBM-streaming split-K without shared-memory staging.  The keys of one KV head — all segments laid end to end —
+// are cut into groups of 16; a CTA of 6 warps takes a contiguous run of groups (the grid is two CTAs per SM: every
+// SM streams from the first cycle, nobody waits for a second wave), and a warp handles one group at a time, all the
+// query heads of the KV head at once:
+//   * every K and V byte goes from global memory straight into the registers of the thread that needs it as an
+//     mma.sync operand — sixteen 16-byte loads per thread and group, all issued before the first is used, each warp
+//     instruction covering whole 64- or 128-byte runs of a row.  The tensor-core fragments do not care in which
+//     order the head dimension is summed, nor which output column stands for which dimension, so the loads can be
+//     laid out for the memory system and the fragments follow (the permutation is the same for Q and K, and undone
+//     when O is written);
+//   * S = Q K^T as m16n8k16 products with the group's query heads as rows (rows past the group size are zero), the
+//     softmax of the group in registers, then O^T += V^T P^T with the head dimension as rows and the query heads as
+//     columns, whose A operand pairs the same dimension of two consecutive keys with one byte permute each.
+// The warps of a CTA merge their (m, l, O) through shared memory into one normalised partial per CTA and head plus
+// its log-sum-exp; infllm_lse_merge combines the partials — the runs of one GPU and, for unit-range sharding, the
+// partials gathered from other GPUs.  (Folding that merge into the CTA that finishes last for a KV head was tried:
+// its serial tail — 37 partials and 4 x 4096 score columns behind 192 threads — cost 50 us; a second launch of one
+// wide CTA per head with every load issued up front costs 4.)
+// A unit that the table of unit addresses places in the store (not in a cache slot) is read in place — over PCIe
+// when the store is pinned host memory — and the rows are also written to a landing slot on the device, from where
+// the host later refills the cache without a second trip over the link.
+// Replaces the two attn.append calls of ContextManager._append (context_manager.py:486-489, 526-531) for
+// single-token exec blocks.
+#include <algorithm>
+
 #include "attn_common.cuh"
 #include "mma_common.cuh"
 
 namespace infllm {
 
-constexpr int kDecodeChunk = 128;
-constexpr int kMaxGroup = 8;  // query heads per KV head
+constexpr int kDecodeChunk = 128;  // keys per unit of the capacity rule of the allocation-free entry point
+constexpr int kMaxGroup = 8;       // query heads per KV head
+constexpr int kDecWarps = 6;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kDecMaxRuns = 2 * 148;  // CTAs of one launch over all KV heads: two per SM
 
 struct DecodeSeg {
   const void* k;
@@ -26,194 +46,253 @@ struct DecodeSeg {
 
 struct DecodeParams {
   DecodeSeg seg[kMaxSeg];
-  int32_t part_begin[kMaxSeg + 1];  // first partial index of each segment
+  int32_t item_begin[kMaxSeg + 1];  // first 16-key group of each segment within one KV head's list
   uint8_t qsel[kMaxSeg];            // query variant per segment
-  int32_t n_seg, n_heads, n_kv_heads;
-  int32_t logit_seg;  // segment whose raw logits are exported, or -1
+  int32_t n_seg, n_heads, n_kv_heads, n_items, n_runs;
+  int32_t logit_seg;  // segment whose scaled logits are exported, or -1
   const void* q[2];   // (H, D) each, heads q_hs elements apart
   int64_t q_hs;
-  float* part_o;      // (n_part, H, D)
-  float* part_lse;    // (n_part, H)
+  float* part_o;      // (n_runs, H, D)
+  float* part_lse;    // (n_runs, H)
   float* logits;      // (H, seg_len[logit_seg])
   float scale_log2;
   DecodeIndirect ind; // n_units == 0: every segment carries its own pointers
 };
 
-// wait until at most n of this thread's cp.async groups are pending (n is a constant after unrolling)
-__device__ __forceinline__ void cp_wait_upto(int n) {
-  if (n <= 0) mma::cp_async_wait<0>();
-  else if (n == 1) mma::cp_async_wait<1>();
-  else if (n == 2) mma::cp_async_wait<2>();
-  else mma::cp_async_wait<3>();
-  __syncwarp();  // the other lanes' copies are visible too
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
 }
 
-// One warp per CTA and per chunk of 64 * ROUNDS keys of one KV head.  The warp first issues every 16-byte
-// cp.async of its K and V rows (32 KiB per round, XOR-swizzled tiles in shared memory), so that a full SM holds
-// about 200 KiB of loads in flight, then runs S = Q K^T and O = P V on the tensor cores (mma.sync m16n8k16: the
-// query heads of the group are the first rows of the 16-row operand, the rest is zero) with the softmax of the
-// chunk in registers in between.
-template <int HD, int ROUNDS, typename T>
-__global__ void __launch_bounds__(32) attn_decode_kernel(const __grid_constant__ DecodeParams P) {
-  static_assert(HD == 128, "tiles of 64 keys x 128 elements");
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __grid_constant__ DecodeParams P) {
   using namespace mma;
-  extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int kTileBytes = 64 * HD * 2;
-  constexpr int kChunk = 64 * ROUNDS;
-  const uint32_t s0 = smem_u32(smem);
-  const int lane = threadIdx.x, g = lane >> 2, t4 = lane & 3;
-  const int part = blockIdx.x, hkv = blockIdx.y;
+  constexpr int HD = 128;
+  __shared__ __align__(16) float sm_o[kDecWarps][kMaxGroup][HD];
+  __shared__ float sm_m[kDecWarps][kMaxGroup], sm_l[kDecWarps][kMaxGroup];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int run = blockIdx.x, hkv = blockIdx.y;
   const int group = P.n_heads / P.n_kv_heads;
-  int sg = 0;
-  while (sg + 1 < P.n_seg && P.part_begin[sg + 1] <= part) ++sg;
-  const DecodeSeg& S = P.seg[sg];
-  const int j0 = (part - P.part_begin[sg]) * kChunk;
-  const int nk = (S.len - j0) < kChunk ? (S.len - j0) : kChunk;
-  const void* seg_k = S.k;
-  const void* seg_v = S.v;
-  if (P.ind.n_units > 0) {
-    const int u = sg - P.ind.first_seg;
-    if (u >= 0 && u < P.ind.n_units) {
-      const int id = __ldg(P.ind.ids + u) - P.ind.id_lo;
-      const bool mine = id >= 0 && id < P.ind.n_owned;
-      const int slot = mine ? __ldg(P.ind.table + id) : -1;
-      if (slot < 0) {
-        // not cached: this chunk's partials get weight zero here; the host launches the unit again after the
-        // refill.  A unit that another rank owns is that rank's business.
-        if (lane == 0 && mine) *P.ind.miss = 1;
-        const int grp = P.n_heads / P.n_kv_heads;
-        for (int i = lane; i < grp * HD; i += 32)
-          P.part_o[((int64_t)part * P.n_heads + hkv * grp + i / HD) * HD + i % HD] = 0.f;
-        if (lane < grp) P.part_lse[(int64_t)part * P.n_heads + hkv * grp + lane] = -INFINITY;
-        return;
+  const int lo = (int)((int64_t)run * P.n_items / P.n_runs), hi = (int)((int64_t)(run + 1) * P.n_items / P.n_runs);
+  const bool qrow = g < group;          // this thread's S row is a real query head
+  const int hq = hkv * group + (qrow ? g : 0);
+
+  uint4 qf[4];  // Q of head hq: elements j*32 + t*8 .. +7 for j = 0..3 (zero for rows past the group)
+  int cur_q = -1;
+  float ot[8][4];  // O^T tile i: [0],[1] = dim g*8+i of heads 2t, 2t+1; [2],[3] = dim 64+g*8+i
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+  float m = -INFINITY, l = 0.f;  // running maximum of head g; this thread's share of its row sum
+
+  int sg = 0, sg_resolved = -1;
+  const char *kbase = nullptr, *vbase = nullptr;
+  char* deposit = nullptr;  // != nullptr: the segment is a unit read in place; its K block's copy in the landing slot
+  bool seg_ok = true;
+  for (int it = lo + warp; it < hi; it += kDecWarps) {
+    while (it >= P.item_begin[sg + 1]) ++sg;
+    const DecodeSeg& S = P.seg[sg];
+    if (sg != sg_resolved) {  // pointers of the segment; a memory unit named on the device is looked up here
+      sg_resolved = sg;
+      seg_ok = true;
+      deposit = nullptr;
+      const void* sk = S.k;
+      const void* sv = S.v;
+      const int u = sg - P.ind.first_seg;
+      if (P.ind.n_units > 0 && u >= 0 && u < P.ind.n_units) {
+        const int id = __ldg(P.ind.ids + u) - P.ind.id_lo;
+        const bool mine = id >= 0 && id < P.ind.n_owned;
+        if (P.ind.ptrs) {  // table of addresses: wherever the unit lives (cache slot, device copy, pinned host store)
+          const unsigned long long a = mine ? __ldg(P.ind.ptrs + id) : 0ull;
+          seg_ok = a != 0ull;
+          sk = reinterpret_cast<const void*>(a & ~1ull);
+          // bit 0: the address is the unit's place in the store, not a cache slot
+          if ((a & 1ull) && P.ind.landing) {
+            const unsigned long long la = __ldg(P.ind.landing + u);
+            if (la) deposit = reinterpret_cast<char*>(la) + (int64_t)hkv * S.hs * 2;
+          }
+          sv = reinterpret_cast<const char*>(sk) + P.ind.unit_bytes / 2;
+        } else {
+          const int slot = mine ? __ldg(P.ind.table + id) : -1;
+          seg_ok = slot >= 0;
+          sk = P.ind.cache + (int64_t)(slot < 0 ? 0 : slot) * P.ind.unit_bytes;
+          sv = reinterpret_cast<const char*>(sk) + P.ind.unit_bytes / 2;
+        }
+        // not cached: the unit contributes nothing here and the host, which learns the same from its own tables,
+        // attends to it after the refill.  A unit that another rank owns is that rank's business.
+        if (!seg_ok && mine && P.ind.miss && lane == 0) *P.ind.miss = 1;
       }
-      seg_k = P.ind.cache + (int64_t)slot * P.ind.unit_bytes;
-      seg_v = (const char*)seg_k + P.ind.unit_bytes / 2;
-    }
-  }
-  const T* kbase = (const T*)seg_k + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
-  const T* vbase = (const T*)seg_v + (int64_t)hkv * S.hs + (int64_t)j0 * S.ts;
-  // ---- all loads of the chunk: groups K0, V0, K1, V1 ...; rows past the end are zero-filled
+      kbase = reinterpret_cast<const char*>(sk) + (int64_t)hkv * S.hs * 2;
+      vbase = reinterpret_cast<const char*>(sv) + (int64_t)hkv * S.hs * 2;
+      if ((int)P.qsel[sg] != cur_q) {
+        cur_q = P.qsel[sg];
+        const char* qp = reinterpret_cast<const char*>(P.q[cur_q]) + (int64_t)hq * P.q_hs * 2;
 #pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
-#pragma unroll
-    for (int kv = 0; kv < 2; ++kv) {
-      const T* base = kv ? vbase : kbase;
-      const uint32_t dst = s0 + (uint32_t)((2 * r + kv) * kTileBytes);
-#pragma unroll 8
-      for (int i = 0; i < 64 * (HD / 8) / 32; ++i) {
-        const int idx = lane + 32 * i, row = idx / (HD / 8), c = idx % (HD / 8);
-        const int jr = r * 64 + row;
-        const bool ok = jr < nk;
-        cp_async16(dst + tile_off<HD>(row, c), base + (ok ? (int64_t)jr * S.ts : 0) + c * 8, ok);
-      }
-      cp_async_commit();
-    }
-  }
-  // ---- the group's queries as A fragments: row g of the operand is head hkv * group + g, rows >= group are zero
-  const bool qrow = g < group;
-  const int h = hkv * group + (qrow ? g : 0);
-  const T* qp = (const T*)P.q[P.qsel[sg]] + (int64_t)h * P.q_hs;
-  uint32_t qf[HD / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < HD / 16; ++ks) {
-    qf[ks][0] = qrow ? __ldg(reinterpret_cast<const uint32_t*>(qp + ks * 16 + t4 * 2)) : 0u;
-    qf[ks][2] = qrow ? __ldg(reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + t4 * 2)) : 0u;
-    qf[ks][1] = qf[ks][3] = 0u;
-  }
-  float o[HD / 8][4];
-#pragma unroll
-  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m = -INFINITY, l = 0.f;  // l: this thread's share of the row sum, reduced over the quad at the end
-#pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
-    const uint32_t kt = s0 + (uint32_t)(2 * r * kTileBytes), vt = kt + kTileBytes;
-    cp_wait_upto(2 * ROUNDS - 1 - 2 * r);
-    float sacc[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        const int mid = lane >> 3;
-        const int rr = np * 16 + (mid >> 1) * 8 + (lane & 7), c = ks * 2 + (mid & 1);
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(kt + tile_off<HD>(rr, c), b0, b1, b2, b3);
-        mma16816<T>(sacc[np * 2], qf[ks], b0, b1);
-        mma16816<T>(sacc[np * 2 + 1], qf[ks], b2, b3);
+        for (int j = 0; j < 4; ++j)
+          qf[j] = qrow ? __ldg(reinterpret_cast<const uint4*>(qp + j * 64 + t * 16)) : make_uint4(0, 0, 0, 0);
       }
     }
-    // scale, cut at the end of the segment, softmax of this round against the running maximum
+    if (!seg_ok) continue;
+    const int j0 = (it - P.item_begin[sg]) * 16;
+    const int nk = S.len - j0 < 16 ? S.len - j0 : 16;
+    const int64_t row_bytes = (int64_t)S.ts * 2;
+    // ---- every load of the group.  K: keys j0 + nt*8 + g (this thread's B-fragment column), 64 bytes of the row in
+    //      four pieces j*64 + t*16; V: keys j0 + {2t, 2t+1, 2t+8, 2t+9}, 32 bytes in two pieces p*128 + g*16.
+    //      Rows past the end of the segment are read from its last row and masked below.
+    uint4 kr[2][4], vr[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int r = nt * 8 + g;
+      const char* rp = kbase + (int64_t)(j0 + (r < nk ? r : nk - 1)) * row_bytes + t * 16;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kr[nt][j] = ld_stream16(rp + j * 64);
+    }
+#pragma unroll
+    for (int ki = 0; ki < 4; ++ki) {
+      const int r = 2 * t + (ki & 1) + (ki >> 1) * 8;
+      const char* rp = vbase + (int64_t)(j0 + (r < nk ? r : nk - 1)) * row_bytes + g * 16;
+      vr[ki][0] = ld_stream16(rp);
+      vr[ki][1] = ld_stream16(rp + 128);
+    }
+    if (deposit) {  // what was just read, to the same place of the landing slot (K block, then V block)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int r = nt * 8 + g;
+        if (r < nk) {
+          char* wp = deposit + (int64_t)(j0 + r) * row_bytes + t * 16;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(wp + j * 64) = kr[nt][j];
+        }
+      }
+#pragma unroll
+      for (int ki = 0; ki < 4; ++ki) {
+        const int r = 2 * t + (ki & 1) + (ki >> 1) * 8;
+        if (r < nk) {
+          char* wp = deposit + P.ind.unit_bytes / 2 + (int64_t)(j0 + r) * row_bytes + g * 16;
+          *reinterpret_cast<uint4*>(wp) = vr[ki][0];
+          *reinterpret_cast<uint4*>(wp + 128) = vr[ki][1];
+        }
+      }
+    }
+    // ---- S = Q K^T: rows = query heads, columns = the 16 keys (two n-tiles), 8 k-steps of 16 elements
+    float sacc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t a0[4] = {qf[j].x, 0u, qf[j].y, 0u};
+        mma16816<T>(sacc[nt], a0, kr[nt][j].x, kr[nt][j].y);
+        const uint32_t a1[4] = {qf[j].z, 0u, qf[j].w, 0u};
+        mma16816<T>(sacc[nt], a1, kr[nt][j].z, kr[nt][j].w);
+      }
+    }
+    // ---- softmax of the group against the running maximum: this thread holds keys nt*8 + 2t + e of head g
+    float sv[4];
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int j = r * 64 + i * 8 + t4 * 2 + e;
-        const float v = j < nk ? sacc[i][e] * P.scale_log2 : -INFINITY;
-        sacc[i][e] = v;
+        const int key = nt * 8 + 2 * t + e;
+        const float v = (qrow && key < nk) ? sacc[nt][e] * P.scale_log2 : -INFINITY;
+        sv[nt * 2 + e] = v;
         mx = fmaxf(mx, v);
-        if (sg == P.logit_seg && qrow && j < nk) P.logits[(int64_t)h * S.len + j0 + j] = v;
+        if (sg == P.logit_seg && qrow && key < nk) P.logits[(int64_t)hq * S.len + j0 + key] = v;
       }
     }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float mn = fmaxf(m, mx);
     const float ms = mn == -INFINITY ? 0.f : mn;
-    const float al = exp2f(m - ms);
+    const float al = exp2f(m - ms);  // 0 for the first group of a row
     m = mn;
-    float rs = 0.f;
+    float p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = exp2f(sv[i] - ms);
+    l = l * al + (p[0] + p[1]) + (p[2] + p[3]);
+    // the O^T columns of this thread are heads 2t and 2t+1: their factors come from the lanes that own those rows
+    const float a0 = __shfl_sync(0xffffffffu, al, (2 * t) * 4), a1 = __shfl_sync(0xffffffffu, al, (2 * t + 1) * 4);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      sacc[i][0] = exp2f(sacc[i][0] - ms);
-      sacc[i][1] = exp2f(sacc[i][1] - ms);
-      rs += sacc[i][0] + sacc[i][1];
+      ot[i][0] *= a0;
+      ot[i][1] *= a1;
+      ot[i][2] *= a0;
+      ot[i][3] *= a1;
     }
-    l = l * al + rs;
-    if (r > 0) {
+    // ---- O^T += V^T P^T: B = P^T (this thread: head g, keys 2t, 2t+1 | 2t+8, 2t+9), A = V^T built by byte permutes
+    const uint32_t b0 = pack2<T>(p[0], p[1]), b1 = pack2<T>(p[2], p[3]);
+    const uint32_t* v00 = reinterpret_cast<const uint32_t*>(&vr[0][0]);
+    const uint32_t* v10 = reinterpret_cast<const uint32_t*>(&vr[1][0]);
+    const uint32_t* v20 = reinterpret_cast<const uint32_t*>(&vr[2][0]);
+    const uint32_t* v30 = reinterpret_cast<const uint32_t*>(&vr[3][0]);
+    const uint32_t* v01 = reinterpret_cast<const uint32_t*>(&vr[0][1]);
+    const uint32_t* v11 = reinterpret_cast<const uint32_t*>(&vr[1][1]);
+    const uint32_t* v21 = reinterpret_cast<const uint32_t*>(&vr[2][1]);
+    const uint32_t* v31 = reinterpret_cast<const uint32_t*>(&vr[3][1]);
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
-        o[i][0] *= al;
-        o[i][1] *= al;
-      }
+    for (int i = 0; i < 8; ++i) {
+      const int r = i >> 1;
+      const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;  // the high or the low 16 bits of both words
+      uint32_t a[4];
+      a[0] = __byte_perm(v00[r], v10[r], sel);  // dim g*8+i of keys 2t, 2t+1
+      a[1] = __byte_perm(v01[r], v11[r], sel);  // dim 64+g*8+i
+      a[2] = __byte_perm(v20[r], v30[r], sel);  // keys 2t+8, 2t+9
+      a[3] = __byte_perm(v21[r], v31[r], sel);
+      mma16816<T>(ot[i], a, b0, b1);
     }
-    cp_wait_upto(2 * ROUNDS - 2 - 2 * r);
+  }
+  // ---- the warps' results meet in shared memory
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (qrow && t == 0) {
+    sm_m[warp][g] = m;
+    sm_l[warp][g] = l;
+  }
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      uint32_t pa[4];
-      pa[0] = pack2<T>(sacc[2 * ks][0], sacc[2 * ks][1]);
-      pa[2] = pack2<T>(sacc[2 * ks + 1][0], sacc[2 * ks + 1][1]);
-      pa[1] = pa[3] = 0u;
+  for (int i = 0; i < 8; ++i) {
 #pragma unroll
-      for (int dn = 0; dn < HD / 16; ++dn) {
-        const int mid = lane >> 3;
-        const int rr = ks * 16 + (mid & 1) * 8 + (lane & 7), c = dn * 2 + (mid >> 1);
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(vt + tile_off<HD>(rr, c), b0, b1, b2, b3);
-        mma16816<T>(o[dn * 2], pa, b0, b1);
-        mma16816<T>(o[dn * 2 + 1], pa, b2, b3);
+    for (int e = 0; e < 2; ++e) {
+      const int head = 2 * t + e;
+      if (head < group) {
+        sm_o[warp][head][g * 8 + i] = ot[i][e];
+        sm_o[warp][head][64 + g * 8 + i] = ot[i][2 + e];
       }
     }
   }
-  l += __shfl_xor_sync(0xffffffffu, l, 1);
-  l += __shfl_xor_sync(0xffffffffu, l, 2);
-  if (qrow) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    float* po = P.part_o + ((int64_t)part * P.n_heads + h) * HD + t4 * 2;
+  __syncthreads();
+  const int64_t prow = (int64_t)run * P.n_heads + hkv * group;  // first head row of this CTA's partial
+  for (int idx = tid; idx < group * HD; idx += kDecThreads) {
+    const int h = idx / HD, d = idx % HD;
+    float mxw = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) *reinterpret_cast<float2*>(po + i * 8) = make_float2(o[i][0] * inv, o[i][1] * inv);
-    if (t4 == 0) P.part_lse[(int64_t)part * P.n_heads + h] = l > 0.f ? m + log2f(l) : -INFINITY;
+    for (int w = 0; w < kDecWarps; ++w) mxw = fmaxf(mxw, sm_m[w][h]);
+    float den = 0.f, num = 0.f;
+    if (mxw != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kDecWarps; ++w) {
+        const float wt = exp2f(sm_m[w][h] - mxw);
+        den = fmaf(wt, sm_l[w][h], den);
+        num = fmaf(wt, sm_o[w][h][d], num);
+      }
+    }
+    P.part_o[(prow + h) * HD + d] = den > 0.f ? num / den : 0.f;
+    if (d == 0) P.part_lse[prow + h] = den > 0.f ? mxw + log2f(den) : -INFINITY;
   }
 }
 
 // out[h, :] = sum_p w_p o_p / sum_p w_p with w_p = exp2(lse_p - max lse); lse = max + log2(sum w).
-// One CTA per head: kMergeGroups groups of head_dim threads share the partials, eight loads in flight each.
-// With `logits` the CTA then adds this token's local attention row into the accumulated scores:
+// One CTA per head.  Every global load of the common case is issued before anything waits: eight groups of
+// head_dim threads share the partials (group g takes partials g, g + 8, ...: 40 of them in a single round of
+// loads), and every thread also owns four score columns of the window; meanwhile warp 0 turns the partials'
+// log-sum-exps into weights.  Two barriers in all.
+// With `logits` the CTA adds this token's local attention row into the accumulated scores:
 // score[h, j] += exp2(logit[h, j] - lse[h]) — the column sums of a one-token exec block.
 constexpr int kMergeGroups = 8;
-constexpr int kMergeUnroll = 20;  // partials a thread keeps in flight: 8 groups x 20 cover 160 partials
-constexpr int kMergeCols = 4;     // score columns a thread keeps in flight: 4 x 1024 cover a 4096-token window
+constexpr int kMergeUnroll = 5;  // partials a thread has in flight: 8 groups x 5 cover 40 partials in one round
+constexpr int kMergeCols = 4;    // score columns a thread keeps in flight: 4 x 1024 cover a 4096-token window
 template <typename T>
 __global__ void __launch_bounds__(1024)
 lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part, int n_heads,
@@ -221,20 +300,17 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
                  const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs,
                  const int32_t* __restrict__ skip, int64_t o_ps, int64_t lse_ps) {
   extern __shared__ float s_w[];  // n_part weights
-  if (skip && *skip) return;  // the partials were not written: a retrieved unit was not cached
-  __shared__ float s_red[32];
   __shared__ float s_num[kMergeGroups][128];
   __shared__ float s_mx, s_den;
-  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  if (skip && *skip) return;  // the partials were not written: a retrieved unit was not cached
+  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grp = tid / head_dim, d = tid % head_dim, ngrp = blockDim.x / head_dim;
-  // every global load of the common case is issued before the first one is needed
   const float* po = part_o + (int64_t)h * head_dim + d;
-  const int64_t ps = o_ps;  // floats from one partial to the next
   float pv[kMergeUnroll];
 #pragma unroll
   for (int u = 0; u < kMergeUnroll; ++u) {
     const int p = grp + u * ngrp;
-    pv[u] = p < n_part ? __ldcs(po + (int64_t)p * ps) : 0.f;
+    pv[u] = p < n_part ? __ldcs(po + (int64_t)p * o_ps) : 0.f;
   }
   float lg[kMergeCols], sc[kMergeCols];
 #pragma unroll
@@ -244,59 +320,38 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
     lg[i] = ok ? __ldcs(logits + h * logit_len + j) : 0.f;
     sc[i] = ok ? score[h * score_hs + j] : 0.f;
   }
-  float mx = -INFINITY;
-  for (int p = tid; p < n_part; p += blockDim.x) {
-    const float v = part_lse[(int64_t)p * lse_ps + h];
-    s_w[p] = v;
-    mx = fmaxf(mx, v);
-  }
-  mx = warp_max(mx);
-  if (lane == 0) s_red[warp] = mx;
-  __syncthreads();
   if (warp == 0) {
-    float v = lane < nwarp ? s_red[lane] : -INFINITY;
-    v = warp_max(v);
-    if (lane == 0) s_mx = v;
-  }
-  __syncthreads();
-  mx = s_mx;
-  float den = 0.f;
-  if (mx != -INFINITY)
-    for (int p = tid; p < n_part; p += blockDim.x) {
-      const float w = exp2f(s_w[p] - mx);
+    float mx = -INFINITY;
+    for (int p = lane; p < n_part; p += 32) {
+      const float v = part_lse[(int64_t)p * lse_ps + h];
+      s_w[p] = v;
+      mx = fmaxf(mx, v);
+    }
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int p = lane; p < n_part; p += 32) {
+      const float w = mx == -INFINITY ? 0.f : exp2f(s_w[p] - mx);
       s_w[p] = w;
       den += w;
     }
-  den = warp_sum(den);
-  __syncthreads();
-  if (lane == 0) s_red[warp] = den;
-  __syncthreads();
-  if (warp == 0) {
-    float v = lane < nwarp ? s_red[lane] : 0.f;
-    v = warp_sum(v);
-    if (lane == 0) s_den = v;
-  }
-  __syncthreads();
-  den = s_den;
-  float num = 0.f;
-  if (mx != -INFINITY) {
-#pragma unroll
-    for (int u = 0; u < kMergeUnroll; ++u) {
-      const int p = grp + u * ngrp;
-      if (p < n_part) num = fmaf(s_w[p], pv[u], num);
+    den = warp_sum(den);
+    if (lane == 0) {
+      s_mx = mx;
+      s_den = den;
     }
-    for (int p = grp + kMergeUnroll * ngrp; p < n_part; p += ngrp) num = fmaf(s_w[p], __ldcs(po + (int64_t)p * ps), num);
   }
-  s_num[grp][d] = num;
   __syncthreads();
-  if (tid < head_dim) {
-    float tot = 0.f;
-    for (int g2 = 0; g2 < ngrp; ++g2) tot += s_num[g2][tid];
-    out[(int64_t)h * o_hs + tid] = Act<T>::from_f(den > 0.f ? tot / den : 0.f);
+  const float den = s_den;
+  const float l = den > 0.f ? s_mx + log2f(den) : -INFINITY;
+  float num = 0.f;
+#pragma unroll
+  for (int u = 0; u < kMergeUnroll; ++u) {
+    const int p = grp + u * ngrp;
+    if (p < n_part) num = fmaf(s_w[p], pv[u], num);
   }
-  const float l = den > 0.f ? mx + log2f(den) : -INFINITY;
-  if (tid == 0 && lse) lse[h] = l;
-  if (logits) {
+  for (int p = grp + kMergeUnroll * ngrp; p < n_part; p += ngrp) num = fmaf(s_w[p], __ldcs(po + (int64_t)p * o_ps), num);
+  s_num[grp][d] = num;
+  if (logits) {  // the score columns need no one else's result
 #pragma unroll
     for (int i = 0; i < kMergeCols; ++i) {
       const int64_t j = tid + (int64_t)i * blockDim.x;
@@ -305,13 +360,19 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
     for (int64_t j = tid + (int64_t)kMergeCols * blockDim.x; j < logit_len; j += blockDim.x)
       score[h * score_hs + j] += exp2f(logits[h * logit_len + j] - l);
   }
+  if (tid == 0 && lse) lse[h] = l;
+  __syncthreads();
+  if (tid < head_dim) {
+    float tot = 0.f;
+    for (int g2 = 0; g2 < ngrp; ++g2) tot += s_num[g2][tid];
+    out[(int64_t)h * o_hs + tid] = Act<T>::from_f(den > 0.f ? tot / den : 0.f);
+  }
 }
 
 int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
-                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s, int chunk,
-                       const DecodeIndirect* ind, int part_base) {
-  if (chunk != 64 && chunk != 128) return fail(INFLLM_E_BADARG, "decode attention: chunk %d (64 or 128)", chunk);
+                       int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s,
+                       const DecodeIndirect* ind) {
   if (head_dim != 128) return fail(INFLLM_E_UNSUPPORTED, "decode attention: head_dim %d (128 is built)", head_dim);
   if (n_heads <= 0 || n_kv_heads <= 0)
     return fail(INFLLM_E_BADARG, "decode attention: %d query heads / %d kv heads", n_heads, n_kv_heads);
@@ -319,16 +380,18 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
     return fail(INFLLM_E_UNSUPPORTED, "decode attention: %d query heads per kv head (at most %d)",
                 n_heads / n_kv_heads, kMaxGroup);
   if (n_seg <= 0 || n_seg > kMaxSeg) return fail(INFLLM_E_BADARG, "decode attention: %d segments (1..%d)", n_seg, kMaxSeg);
+  if (q_hs % 8 || ((uintptr_t)q0 | (uintptr_t)(q1 ? q1 : q0)) % 16)
+    return fail(INFLLM_E_BADARG, "decode attention: query rows are not 16-byte aligned");
   DecodeParams P{};
   if (ind && ind->n_units > 0) {
-    if (!ind->ids || !ind->table || !ind->cache || !ind->miss || ind->first_seg < 0 ||
+    if (!ind->ids || (!ind->table && !ind->ptrs) || (ind->table && !ind->cache) || ind->first_seg < 0 ||
         ind->first_seg + ind->n_units > n_seg)
       return fail(INFLLM_E_BADARG, "decode attention: bad device-resolved unit list");
     for (int i = 0; i < ind->n_units; ++i)
       if (segs[ind->first_seg + i].len <= 0) return fail(INFLLM_E_BADARG, "decode attention: empty unit segment");
     P.ind = *ind;
   }
-  int parts = 0, ns = 0;
+  int items = 0, ns = 0;
   int logit_seg_packed = -1;
   for (int i = 0; i < n_seg; ++i) {
     if (segs[i].len <= 0) continue;  // empty segments contribute nothing
@@ -337,32 +400,28 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
       return fail(INFLLM_E_BADARG, "decode attention: segment %d rows are not 16-byte aligned", i);
     P.seg[ns] = {segs[i].k, segs[i].v, segs[i].hs, segs[i].ts, segs[i].len};
     P.qsel[ns] = (uint8_t)(seg_q[i] ? 1 : 0);
-    P.part_begin[ns] = parts;
+    P.item_begin[ns] = items;
     if (i == logit_seg) logit_seg_packed = ns;
-    parts += (int)ceil_div(segs[i].len, chunk);
+    items += (int)ceil_div(segs[i].len, 16);
     ++ns;
   }
-  P.part_begin[ns] = parts;
-  if (n_parts_out) *n_parts_out = parts;
-  if (parts == 0) return INFLLM_OK;
-  if (part_base < 0 || part_base + parts > max_parts)
-    return fail(INFLLM_E_CAPACITY, "decode attention: %d partials exceed the scratch for %d", part_base + parts, max_parts);
+  P.item_begin[ns] = items;
+  // one run of 16-key groups per CTA, two CTAs per SM over all KV heads
+  int runs = std::max(1, kDecMaxRuns / n_kv_heads);
+  runs = std::min(runs, std::max(items, 1));
+  runs = std::min(runs, max_parts);
+  if (n_parts_out) *n_parts_out = items > 0 ? runs : 0;
+  if (items == 0) return INFLLM_OK;
+  if (runs <= 0) return fail(INFLLM_E_CAPACITY, "decode attention: no room for partials (max_parts %d)", max_parts);
   P.n_seg = ns; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.logit_seg = logit_seg_packed;
+  P.n_items = items; P.n_runs = runs;
   P.q[0] = q0; P.q[1] = q1 ? q1 : q0; P.q_hs = q_hs;
-  P.part_o = part_o + (int64_t)part_base * n_heads * head_dim;
-  P.part_lse = part_lse + (int64_t)part_base * n_heads;
+  P.part_o = part_o;
+  P.part_lse = part_lse;
   P.logits = logits;
   P.scale_log2 = kLog2e / sqrtf((float)head_dim);
-  dim3 grid(parts, n_kv_heads);
-  INFLLM_DISPATCH_DTYPE(dtype, T, {
-    if (chunk == 64) {
-      attn_decode_kernel<128, 1, T><<<grid, 32, 32 * 1024, s>>>(P);
-    } else {
-      auto kern = attn_decode_kernel<128, 2, T>;
-      INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-      kern<<<grid, 32, 64 * 1024, s>>>(P);
-    }
-  });
+  dim3 grid(runs, n_kv_heads);
+  INFLLM_DISPATCH_DTYPE(dtype, T, { attn_decode_kernel<T><<<grid, kDecThreads, 0, s>>>(P); });
   INFLLM_LAUNCH_OK("attn_decode_kernel");
   return INFLLM_OK;
 }
@@ -394,7 +453,8 @@ int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int
 }  // namespace infllm
 
 extern "C" int64_t infllm_attn_decode_max_parts(int n_seg, int64_t total_keys) {
-  return total_keys / infllm::kDecodeChunk + n_seg + 1;
+  const int64_t groups = total_keys / 16 + n_seg + 1;
+  return groups < infllm::kDecMaxRuns ? groups : infllm::kDecMaxRuns;
 }
 
 extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim,
@@ -410,7 +470,7 @@ extern "C" int infllm_attn_decode(const void* d_q0, const void* d_q1, int n_head
   KvSeg segs[kMaxSeg];
   for (int i = 0; i < n_seg; ++i) segs[i] = {h_seg_k[i], h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
   return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o, d_part_lse,
-                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream, kDecodeChunk, nullptr, 0);
+                            max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream, nullptr);
 }
 
 // ------------------------------------------------------------------------ allocation-free variant
@@ -463,7 +523,7 @@ extern "C" int infllm_attn_decode_noalloc(const void* d_q0, const void* d_q1, in
   // Nothing in the scratch has to start at zero: every partial the merge reads is written by the
   // split-K kernel of this same call, whatever an earlier call left behind.
   INFLLM_TRY(attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, part_o,
-                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, kDecodeChunk, nullptr, 0));
+                                part_lse, kStaticMaxParts, &n_parts, -1, nullptr, dtype, s, nullptr));
   return lse_merge_launch(part_o, part_lse, n_parts, n_heads, head_dim, d_out, o_hs, d_lse, dtype, s, nullptr, 0, nullptr, 0, nullptr, 0, 0);
 }
 
@@ -519,5 +579,5 @@ extern "C" int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int 
   ind.n_units = n_units; ind.first_seg = first_unit_seg; ind.miss = d_miss; ind.id_lo = id_lo; ind.n_owned = n_owned;
   return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o,
                             d_part_lse, max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream,
-                            kDecodeChunk, n_units > 0 ? &ind : nullptr, 0);
+                            n_units > 0 ? &ind : nullptr);
 }

@@ -362,7 +362,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   ind.n_units = a->topk; ind.first_seg = 0; ind.miss = miss_word; ind.id_lo = a->id_lo; ind.n_owned = a->n_owned;
   int parts = 0;
   INFLLM_TRY(attn_decode_launch(a->d_q_loc, a->d_q_glb, D, H, HKV, D, n, segs, qsel, a->d_part_o, a->d_part_lse,
-                                a->max_parts, &parts, logit_seg, a->d_logits, a->dtype, s, 128, &ind, 0));
+                                a->max_parts, &parts, logit_seg, a->d_logits, a->dtype, s, &ind));
   INFLLM_TRY(lse_merge_launch(a->d_part_o, a->d_part_lse, parts, H, D, a->d_pack, D, a->d_pack + (int64_t)H * D,
                               INFLLM_F32, s, nullptr, 0, nullptr, 0, nullptr));
   // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores

@@ -56,6 +56,8 @@ int topk_launch(const float* scores, int64_t n, int k, int id_base, int32_t* out
                 cudaStream_t s);
 int comm_allreduce_sum(infllm_comm* c, int which, float* d_buf, size_t n, cudaStream_t s);
 int slot_table_update_launch(int32_t* table, const int32_t* ids, const int32_t* slots, int n, cudaStream_t s);
+int ptr_table_update_launch(unsigned long long* table, const int32_t* ids, const unsigned long long* vals, int n,
+                            cudaStream_t s);
 
 // ------------------------------------------------------------------------------------- LRU table
 // cached_blocks[u] of the reference: a dict id -> stamp whose iteration (insertion) order breaks
@@ -187,13 +189,39 @@ struct infllm_ctx {
   std::vector<cudaEvent_t> slot_ev;   // per slot: behind the last look-ahead copy into it
   std::vector<char> slot_ev_used;
   std::unordered_map<int32_t, int> slot_of;
-  // device copy of slot_of for the decode attention that resolves the retrieved units itself
-  int32_t* d_slot_table = nullptr;
+  // Device table "where unit b lives right now" for the decode attention that resolves the retrieved units
+  // itself: the address of the unit's K block — its cache slot once a refill is known to have landed, else its place
+  // in the device copy of the store or in the pinned host store (which the GPU reads in place over PCIe).  Every
+  // sealed unit has an address, so a one-token attention never has to wait for the host.
+  unsigned long long* d_unit_ptrs = nullptr;
   int64_t tab_cap = 0;
-  bool table_valid = false;                          // false: rebuild from slot_of before the next use
-  std::unordered_map<int32_t, int32_t> tab_updates;  // entries changed since the last flush
-  std::unordered_map<int32_t, int32_t> dev_table;    // what the device copy holds since the last flush (resident units)
-  int32_t* d_miss = nullptr;                         // set by the attention when a retrieved unit is not cached
+  bool table_valid = false;                          // false: rebuild before the next use
+  std::unordered_map<int32_t, int32_t> tab_updates;  // entries changed since the last flush: slot, or -1 = the store
+  std::unordered_map<int32_t, int32_t> dev_table;    // units whose entry points to a cache slot since the last flush
+  int32_t* d_miss = nullptr;                         // cleared with every token (kept for the ingest kernel)
+  // One-token appends run ahead of the host: the retrieval of token t is launched, its ids travel to the host on the
+  // mail stream, and the host applies them to the LRU order (evictions, refills) only when token t+1 or t+2 is
+  // appended — or when somebody asks for the tables.  Ring of the tokens whose ids have not been applied yet.
+  struct PendingToken {
+    int32_t* h_ids = nullptr;  // pinned: topk ids
+    cudaEvent_t ev = nullptr;  // on the mail stream, behind the copy of the ids
+    int64_t serial = 0;        // the append call it belongs to
+    std::vector<int32_t> listed;  // units the device table showed in a cache slot when the token was launched
+    std::vector<int> landing;     // the landing slot of every retrieval position at that time (-1: none)
+  };
+  static constexpr int kPendSlots = 4, kMaxOutstanding = 1;
+  // A retrieved unit that is not in a cache slot is read in place from the store by the one-token attention, which
+  // also writes what it read to a landing slot: a free cache slot set aside for retrieval position i.  When the
+  // retrieval is applied, that slot simply becomes the unit's cache slot — the refill costs no copy and the unit
+  // crosses PCIe once — and another free slot is set aside for position i.
+  std::vector<int> landing_slots;   // per retrieval position: the slot set aside, -1 = none
+  std::vector<int> landing_listed;  // what the device table (entries tab_cap + i) shows
+  std::vector<int> settle_landing;  // per id of the retrieval being applied: the slot it was deposited in, or -1
+  PendingToken pend[kPendSlots];
+  int pend_head = 0, pend_count = 0;
+  int32_t* d_topk_ring = nullptr;  // kPendSlots x topk
+  int64_t call_serial = 0;
+  cudaStream_t last_stream = nullptr;  // stream of the last append (for calls that take none)
   std::vector<void*> slabs;  // pinned host memory
   std::future<void*> slab_future;  // the next slab, being pinned by a helper thread
   bool slab_pending = false;
@@ -230,9 +258,6 @@ struct infllm_ctx {
     bool staged_recorded = false;
   };
   static constexpr int kMaxLookDepth = 8;
-  static constexpr int kDecodeAhead = 16;  // decode: units ranked just below the retrieval are fetched ahead
-  std::vector<std::pair<int32_t, int>> unlisted;  // (unit, slot) fetched ahead, copy not yet known to have landed
-  int decode_k = 0;                        // ids asked of the scorer by the last one-token exec block
   int look_depth = 2;                             // exec blocks ranked ahead (cfg.look_depth overrides)
   LookAhead la[kMaxLookDepth + 1];
   std::unordered_map<int32_t, int64_t> staged_for;  // staged unit -> latest exec block that wants it
@@ -422,12 +447,20 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaMalloc(&c->st_acc, H * g.exc_block_size * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_m, H * g.exc_block_size * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->st_l, H * g.exc_block_size * sizeof(float)));
-  INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, (std::max(1, g.topk) + infllm_ctx::kDecodeAhead) * sizeof(int32_t)));
+  INFLLM_CUDA_OK(cudaMalloc(&c->d_topk, std::max(1, g.topk) * sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_miss, sizeof(int32_t)));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->d_miss, 0, sizeof(int32_t), s));
+  {
+    const int per = std::max(1, g.topk);
+    INFLLM_CUDA_OK(cudaMalloc((void**)&c->d_topk_ring, (size_t)infllm_ctx::kPendSlots * per * sizeof(int32_t)));
+    for (auto& pt : c->pend) {
+      INFLLM_CUDA_OK(cudaHostAlloc((void**)&pt.h_ids, per * sizeof(int32_t), cudaHostAllocDefault));
+      INFLLM_CUDA_OK(cudaEventCreateWithFlags(&pt.ev, cudaEventDisableTiming));
+    }
+  }
   INFLLM_CUDA_OK(cudaMalloc((void**)&c->tickets, 2 * sizeof(unsigned int)));
   INFLLM_CUDA_OK(cudaMemsetAsync(c->tickets, 0, 2 * sizeof(unsigned int), s));
-  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, (std::max(1, g.topk) + infllm_ctx::kDecodeAhead) * sizeof(int32_t),
+  INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_topk, std::max(1, g.topk) * sizeof(int32_t),
                                cudaHostAllocDefault));
   INFLLM_CUDA_OK(cudaHostAlloc((void**)&c->h_spec, std::max(1, g.topk) * sizeof(int32_t), cudaHostAllocDefault));
   c->cand_cap = g.topk + (c->look_depth + 1) * (g.exc_block_size / g.block_size + 2) + 4;
@@ -443,7 +476,8 @@ int lazy_init(infllm_ctx* c, cudaStream_t s) {
   INFLLM_CUDA_OK(cudaStreamCreateWithFlags(&c->mail_stream, cudaStreamNonBlocking));
   // decode partials: window + units + sink + overflow, each segment may add one ragged chunk
   int64_t dec_keys = (int64_t)g.n_local + (int64_t)g.topk * g.block_size + g.n_init + g.block_size + g.exc_block_size;
-  c->max_parts = (int)(dec_keys / 64 + g.topk + 8 + (int64_t)g.topk * ((g.block_size + 63) / 64));
+  (void)dec_keys;
+  c->max_parts = 2 * 148;  // the decode attention launches at most two CTAs per SM, one partial each
   INFLLM_CUDA_OK(cudaMalloc(&c->part_o, (int64_t)c->max_parts * H * D * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->part_lse, (int64_t)c->max_parts * H * sizeof(float)));
   INFLLM_CUDA_OK(cudaMalloc(&c->dec_logits, H * ((int64_t)g.n_local + 1) * sizeof(float)));
@@ -806,9 +840,18 @@ int candidates_finish(infllm_ctx* c, int n_cand, std::vector<int32_t>* ids) {
 }
 
 // cache plan for `ids` (LRU eviction, stamps), adoption of staged copies, late fetches; s waits for the copies
-int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, cudaStream_t s, bool track) {
+enum PlanMode {
+  PLAN_PREFILL = 0,       // the device table is not kept up to date (rebuilt when decode next needs it)
+  PLAN_DECODE_SYNC = 1,   // one-token append that waited for its ids: s waits for the refills
+  PLAN_DECODE_ASYNC = 2,  // ids of an earlier token applied late: refills go to the copy stream and nobody waits;
+                          // a unit is listed in the device table once its copy is known to have landed
+};
+int mark_slot_copy(infllm_ctx* c, void* slot_ptr);
+
+int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, cudaStream_t s, int mode) {
   const infllm_config& g = c->cfg;
-  if (!track) c->table_valid = false;  // the device copy of the slot table is rebuilt when decode next needs it
+  const bool track = mode != PLAN_PREFILL;
+  if (!track) c->table_valid = false;
   std::vector<int32_t> evicted;
   c->lru.plan(ids.data(), (int)ids.size(), &evicted);
   for (int32_t b : evicted) {  // MemoryUnit.offload -> CudaCache.delete (context_manager.py:104-109)
@@ -859,6 +902,18 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
       c->staged_for.erase(b);
       continue;
     }
+    if (mode == PLAN_DECODE_ASYNC) {
+      int ls = -1;
+      for (size_t i = 0; i < ids.size() && i < c->settle_landing.size(); ++i)
+        if (ids[i] == b) ls = c->settle_landing[i];
+      if (ls >= 0) {
+        // the token's attention read this unit in place and left it in a landing slot: that slot is its cache slot now
+        c->slot_of[b] = ls;
+        c->tab_updates[b] = ls;
+        if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;  // crossed PCIe inside the attention
+        continue;
+      }
+    }
     if (c->free_slots.empty()) {
       // spare slots are all holding look-ahead copies that were not wanted after all: reclaim one
       if (c->staged.empty())
@@ -874,7 +929,7 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
     int slot = c->free_slots.back();
     c->free_slots.pop_back();
     c->slot_of[b] = slot;
-    if (track) c->tab_updates[b] = slot;
+    if (mode == PLAN_DECODE_SYNC) c->tab_updates[b] = slot;
     const int64_t tok0 = (int64_t)g.n_init + (int64_t)b * g.block_size;  // the unit's first token
     if (tok0 >= c->tb.t0 && tok0 + g.block_size <= c->length) {
       // sealed so recently that its tokens are still in the token buffers: copy on the device, on the main stream
@@ -888,8 +943,10 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
                                        cudaMemcpyDeviceToDevice, s));
       INFLLM_CUDA_OK(cudaMemcpy2DAsync(dst + c->unit_bytes / 2, row, (char*)c->tb.v + src, pitch, row, g.n_kv_heads,
                                        cudaMemcpyDeviceToDevice, s));
+      if (mode == PLAN_DECODE_ASYNC) c->tab_updates[b] = slot;  // ordered on s ahead of the next attention
       continue;
     }
+    if (mode == PLAN_DECODE_ASYNC) c->tab_updates[b] = slot;  // no landing slot was free: fetched like a waited-for refill
     if (!late) {
       // slots freed above may still be read by the previous exec block's attention
       if (c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->urgent_stream, c->ev_attn, 0));
@@ -937,80 +994,109 @@ int plan_and_refill(infllm_ctx* c, const std::vector<int32_t>& ids, int64_t eb, 
   return INFLLM_OK;
 }
 
-// Decode: fetch ahead the units the scorer ranked just below the retrieval.  Between consecutive tokens the
-// retrieval mostly trades units across that boundary, so the newcomer is usually on the GPU before it is asked
-// for.  The copies go to the spare slots on the copy stream; a fetched unit is adopted by the cache plan like a
-// look-ahead copy of the prefill, and units that fell out of the band give their slots back.
-int decode_fetch_ahead(infllm_ctx* c, const std::vector<int32_t>& retrieval, const int32_t* cand, int n_cand) {
-  if (n_cand <= 0 && c->staged.empty()) return INFLLM_OK;
-  auto wanted = [&](int32_t b) {
-    for (int i = 0; i < n_cand; ++i)
-      if (cand[i] == b) return true;
-    return std::find(retrieval.begin(), retrieval.end(), b) != retrieval.end();
-  };
-  for (auto it = c->staged.begin(); it != c->staged.end();) {
-    if (!wanted(it->first)) {
-      c->free_slots.push_back(it->second);
-      c->tab_updates[it->first] = -1;
-      c->staged_for.erase(it->first);
-      it = c->staged.erase(it);
-    } else {
-      ++it;
-    }
+// bring the device table of unit addresses up to date on stream s
+int flush_table(infllm_ctx* c, cudaStream_t s) {
+  const int topk = c->cfg.topk;
+  if (c->tab_cap < c->block_k_cap || !c->d_unit_ptrs) {
+    if (c->d_unit_ptrs) INFLLM_CUDA_OK(cudaFreeAsync(c->d_unit_ptrs, s));
+    c->tab_cap = std::max<int64_t>(c->block_k_cap, 1024);
+    // entries [tab_cap, tab_cap + topk): the landing slot of every retrieval position
+    INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->d_unit_ptrs, (c->tab_cap + topk) * sizeof(unsigned long long), s));
+    c->table_valid = false;
   }
-  bool issued = false;
-  for (int i = 0; i < n_cand; ++i) {
-    const int32_t b = cand[i];
-    if (c->slot_of.count(b) || c->staged.count(b)) continue;
-    if (c->free_slots.empty()) break;
+  // a free slot set aside for every retrieval position (fewer when the pool runs dry: those positions deposit nothing)
+  c->landing_slots.resize(topk, -1);
+  for (int i = 0; i < topk; ++i) {
+    if (c->landing_slots[i] >= 0 || c->free_slots.empty()) continue;
     const int slot = c->free_slots.back();
     c->free_slots.pop_back();
-    if (!issued && c->attn_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_attn, 0));
-    if (b >= c->d2h_synced_upto) {
-      if (c->d2h_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(c->copy_stream, c->ev_d2h, 0));
-      c->d2h_synced_upto = c->num_blocks;
-    }
-    void* dst = (char*)c->cache + (int64_t)slot * c->unit_bytes;
-    INFLLM_CUDA_OK(cudaMemcpyAsync(dst, c->unit_src(b), c->unit_bytes, cudaMemcpyDefault, c->copy_stream));
-    INFLLM_TRY(mark_slot_copy(c, dst));
-    c->staged[b] = slot;
-    c->staged_for[b] = INT64_MAX;
-    c->unlisted.push_back({b, slot});
-    if (!c->dev_resident(b)) c->counters.h2d_bytes += c->unit_bytes;
-    c->staged_pending = true;
-    issued = true;
+    // an abandoned look-ahead copy of an earlier prefill may still be on its way into this slot
+    if (c->slot_ev_used[slot]) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->slot_ev[slot], 0));
+    c->landing_slots[i] = slot;
   }
-  if (issued) INFLLM_CUDA_OK(cudaEventRecord(c->ev_stage, c->copy_stream));
+  auto slot_addr = [&](int slot) { return (unsigned long long)(uintptr_t)((char*)c->cache + (int64_t)slot * c->unit_bytes); };
+  if (!c->table_valid) {
+    // every sealed unit at its place in the store; the cached ones whose copies are known to have landed at their
+    // slots.  The upload is ordered on s (the runtime stages a pageable source before it returns).
+    std::vector<unsigned long long> all((size_t)(c->tab_cap + topk), 0ull);
+    for (int i = 0; i < topk; ++i)
+      if (c->landing_slots[i] >= 0) all[(size_t)(c->tab_cap + i)] = slot_addr(c->landing_slots[i]);
+    c->landing_listed = c->landing_slots;
+    // (bit 0 of an address in the store says "read in place and deposit in the landing slot")
+    for (int64_t b = 0; b < c->num_blocks; ++b) all[(size_t)b] = (unsigned long long)(uintptr_t)c->unit_src(b) | 1ull;
+    c->tab_updates.clear();
+    c->dev_table.clear();
+    // every cached unit got there by a copy that s waited for (a prefill exec block's plan) or that ran on s
+    for (auto& kv : c->slot_of) {
+      all[(size_t)kv.first] = slot_addr(kv.second);
+      c->dev_table[kv.first] = kv.second;
+    }
+    if (c->d2h_recorded) INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_d2h, 0));   // the store holds every sealed unit
+    INFLLM_CUDA_OK(cudaMemcpyAsync(c->d_unit_ptrs, all.data(), all.size() * sizeof(unsigned long long),
+                                   cudaMemcpyHostToDevice, s));
+    c->table_valid = true;
+    return INFLLM_OK;
+  }
+  std::vector<int32_t> ids;
+  std::vector<unsigned long long> vals;
+  c->landing_listed.resize(topk, -1);
+  for (int i = 0; i < topk; ++i)
+    if (c->landing_listed[i] != c->landing_slots[i]) {
+      ids.push_back((int32_t)(c->tab_cap + i));
+      vals.push_back(c->landing_slots[i] >= 0 ? slot_addr(c->landing_slots[i]) : 0ull);
+      c->landing_listed[i] = c->landing_slots[i];
+    }
+  for (auto& kv : c->tab_updates) {
+    if (kv.first < 0 || kv.first >= c->num_blocks) continue;
+    ids.push_back(kv.first);
+    if (kv.second >= 0) {
+      vals.push_back(slot_addr(kv.second));
+      c->dev_table[kv.first] = kv.second;
+    } else {
+      vals.push_back((unsigned long long)(uintptr_t)c->unit_src(kv.first) | 1ull);
+      c->dev_table.erase(kv.first);
+    }
+  }
+  c->tab_updates.clear();
+  if (ids.empty()) return INFLLM_OK;
+  return ptr_table_update_launch(c->d_unit_ptrs, ids.data(), vals.data(), (int)ids.size(), s);
+}
+
+// Apply the oldest pending retrieval of a one-token append to the cache: wait for its ids (they left the device
+// right behind the scorer, long ago as a rule) and evict and refill as the reference does at that token.
+int settle_one(infllm_ctx* c, cudaStream_t s) {
+  if (c->pend_count <= 0) return INFLLM_OK;
+  const infllm_config& g = c->cfg;
+  infllm_ctx::PendingToken& p = c->pend[c->pend_head];
+  {
+    HostTimer ht(&c->host_us[0]);
+    INFLLM_CUDA_OK(cudaEventSynchronize(p.ev));
+  }
+  std::vector<int32_t> ids(p.h_ids, p.h_ids + g.topk);
+  // the units that token's attention did not find in a cache slot were read in place and sit in the landing slots
+  c->settle_landing.assign(ids.size(), -1);
+  for (size_t i = 0; i < ids.size(); ++i)
+    if (std::find(p.listed.begin(), p.listed.end(), ids[i]) == p.listed.end()) {
+      c->counters.inplace_units += 1;
+      if (i < p.landing.size() && p.landing[i] >= 0 && c->landing_slots[i] == p.landing[i]) {
+        c->settle_landing[i] = p.landing[i];
+        c->landing_slots[i] = -1;  // handed to the unit; flush_table sets another slot aside
+      }
+    }
+  c->pend_head = (c->pend_head + 1) % infllm_ctx::kPendSlots;
+  c->pend_count -= 1;
+  {
+    HostTimer ht(&c->host_us[1]);
+    INFLLM_TRY(plan_and_refill(c, ids, 0, s, PLAN_DECODE_ASYNC));
+  }
+  c->settle_landing.clear();
+  if (p.serial == c->call_serial) c->trace_topk.push_back(ids);
   return INFLLM_OK;
 }
 
-// bring the device copy of the slot table up to date on stream s
-int flush_table(infllm_ctx* c, cudaStream_t s) {
-  if (c->tab_cap < c->block_k_cap || !c->d_slot_table) {
-    if (c->d_slot_table) INFLLM_CUDA_OK(cudaFreeAsync(c->d_slot_table, s));
-    c->tab_cap = std::max<int64_t>(c->block_k_cap, 1024);
-    INFLLM_CUDA_OK(cudaMallocAsync((void**)&c->d_slot_table, c->tab_cap * sizeof(int32_t), s));
-    c->table_valid = false;
-  }
-  if (!c->table_valid) {
-    INFLLM_CUDA_OK(cudaMemsetAsync(c->d_slot_table, 0xff, c->tab_cap * sizeof(int32_t), s));  // every entry -1
-    c->tab_updates.clear();
-    c->dev_table.clear();
-    c->unlisted.clear();
-    for (auto& kv : c->slot_of) c->tab_updates[kv.first] = kv.second;
-    for (auto& kv : c->staged) c->unlisted.push_back({kv.first, kv.second});  // listed again once known to have landed
-    c->table_valid = true;
-  }
-  if (c->tab_updates.empty()) return INFLLM_OK;
-  std::vector<int32_t> ids, slots;
-  for (auto& kv : c->tab_updates) {
-    ids.push_back(kv.first);
-    slots.push_back(kv.second);
-    if (kv.second >= 0) c->dev_table[kv.first] = kv.second;
-    else c->dev_table.erase(kv.first);
-  }
-  c->tab_updates.clear();
-  return slot_table_update_launch(c->d_slot_table, ids.data(), slots.data(), (int)ids.size(), s);
+int settle_all(infllm_ctx* c, cudaStream_t s) {
+  while (c->pend_count > 0) INFLLM_TRY(settle_one(c, s));
+  return INFLLM_OK;
 }
 
 // what sealing does after an exec block that ended at absolute token `end` (context_manager.py:614-679):
@@ -1279,6 +1365,11 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     INFLLM_TRY(qbar_launch(c->q_glb, q_hs_s, D, (int)H, L, g.exc_block_size, (int)D, c->qbar, c->width, g.dtype, s));
   }
 
+  // one-token appends whose retrieval has not been applied to the cache yet: a call that is not itself such a token
+  // needs the cache as the reference would have it
+  const bool run_ahead = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.debug_flags & 16) &&
+                         g.chunk_topk_calc == 0 && g.cache_strategy == INFLLM_CACHE_LRU;
+  if (!run_ahead) INFLLM_TRY(settle_all(c, s));
   if (L > 1) {  // units a previous one-token append fetched ahead are not wanted by a prefill's look-ahead
     for (auto it = c->staged.begin(); it != c->staged.end();) {
       if (c->staged_for[it->first] == INT64_MAX) {
@@ -1289,7 +1380,11 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         ++it;
       }
     }
-    c->unlisted.clear();
+    // the slots set aside for one-token attentions to deposit in go back to the pool
+    for (int slot : c->landing_slots)
+      if (slot >= 0) c->free_slots.push_back(slot);
+    c->landing_slots.clear();
+    c->landing_listed.clear();
     c->table_valid = false;
   }
   std::vector<int32_t> ids;
@@ -1302,16 +1397,18 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     const int64_t ed = std::min<int64_t>(st + g.exc_block_size, L);
     const int64_t S = T + st, E = T + ed, lq = ed - st;
     const int64_t ks = std::max<int64_t>(S - g.n_local, 0), lk = E - ks;  // local keys [ks, E) (:772-773)
-    // One-token exec blocks over more units than a retrieval takes: the attention is launched right behind the
-    // top-k kernel and resolves the retrieved units through the device copy of the slot table, so the GPU does
-    // not idle while the ids travel to the host.  The host still receives the ids (it keeps the LRU order) and,
-    // if one of them is not cached, refills the cache and launches the attention again.
+    // One-token exec blocks over more units than a retrieval takes run ahead of the host: the attention is launched
+    // right behind the top-k kernel and finds the retrieved units through the device table of unit addresses —
+    // in their cache slots, or in place in the store when they are not (yet) cached — so neither the GPU nor the
+    // host waits for the other.  The ids reach the host on the mail stream and are applied to the LRU order when
+    // one of the next tokens arrives (settle_one): same evictions and refills as the reference, one or two tokens
+    // later in wall-clock time.
     if (c->chunk_mode) {
       const int64_t chunk = (int64_t)(g.chunk_topk_calc / g.exc_block_size) * g.exc_block_size;
       if ((c->call_off + st) % chunk == 0) c->chunk_n0 = c->num_blocks;
     }
-    const bool spec = L == 1 && D == 128 && c->num_blocks > g.topk && g.topk <= kMaxSeg - 4 && !(g.debug_flags & 16) &&
-                      !c->chunk_mode;
+    const bool spec = run_ahead;
+    int32_t* d_ids_tok = nullptr;  // the device-side ids of a run-ahead token
     if (!spec) {
       if (!have_ids) {
         HostTimer ht(&c->host_us[0]);
@@ -1319,37 +1416,31 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       }
       {
         HostTimer ht(&c->host_us[1]);
-        INFLLM_TRY(plan_and_refill(c, ids, eb, s, false));
+        INFLLM_TRY(plan_and_refill(c, ids, eb, s, L == 1 ? PLAN_DECODE_SYNC : PLAN_PREFILL));
       }
       c->trace_topk.push_back(ids);
     } else {
       ids.clear();
+      // at most kMaxOutstanding tokens ahead of the cache: apply the older retrievals first
+      while (c->pend_count >= infllm_ctx::kMaxOutstanding) INFLLM_TRY(settle_one(c, s));
       INFLLM_TRY(ensure_scores(c, c->num_blocks, s));
+      const int slot = (c->pend_head + c->pend_count) % infllm_ctx::kPendSlots;
+      infllm_ctx::PendingToken& pt = c->pend[slot];
+      d_ids_tok = c->d_topk_ring + (int64_t)slot * std::max(1, g.topk);
       {
         ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
-        // the scorer also names the units ranked just below the retrieval: they are fetched ahead (below)
-        c->decode_k = (int)std::min<int64_t>(std::min<int64_t>(g.topk + infllm_ctx::kDecodeAhead, 64), c->num_blocks);
-        if (c->decode_k < g.topk || (g.debug_flags & 32)) c->decode_k = g.topk;
-        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, c->d_topk, s, 0, c->decode_k));
+        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, d_ids_tok, s, 0, g.topk));
       }
       INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
       INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
-      INFLLM_CUDA_OK(cudaMemcpyAsync(c->h_topk, c->d_topk, c->decode_k * sizeof(int32_t), cudaMemcpyDeviceToHost,
-                                     c->mail_stream));
-      INFLLM_CUDA_OK(cudaEventRecord(c->ev_sync, c->mail_stream));
-      // units fetched ahead whose copies have landed since become visible to the attention's slot table
-      for (auto it = c->unlisted.begin(); it != c->unlisted.end();) {
-        auto st = c->staged.find(it->first);
-        if (st == c->staged.end() || st->second != it->second) {
-          it = c->unlisted.erase(it);  // adopted or dropped meanwhile
-        } else if (cudaEventQuery(c->slot_ev[it->second]) == cudaSuccess) {
-          c->tab_updates[it->first] = it->second;
-          it = c->unlisted.erase(it);
-        } else {
-          ++it;
-        }
-      }
+      INFLLM_CUDA_OK(cudaMemcpyAsync(pt.h_ids, d_ids_tok, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->mail_stream));
+      INFLLM_CUDA_OK(cudaEventRecord(pt.ev, c->mail_stream));
+      pt.serial = c->call_serial;
+      c->pend_count += 1;
       INFLLM_TRY(flush_table(c, s));
+      pt.listed.clear();
+      for (auto& kv : c->dev_table) pt.listed.push_back(kv.first);
+      pt.landing = c->landing_slots;
     }
     // bit 1 of the flags turns the look-ahead off; a chunk's retrievals are fixed when it starts, so they need none
     const bool more = ed < L && !(g.debug_flags & 2) && !c->chunk_mode;
@@ -1392,61 +1483,22 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       if (segs.size() > (size_t)kMaxSeg)
         return fail(INFLLM_E_UNSUPPORTED, "decode: %zu key segments exceed %d", segs.size(), kMaxSeg);
       DecodeIndirect ind;
-      if (spec) {
-        ind.ids = c->d_topk;
-        ind.table = c->d_slot_table;
-        ind.cache = (const char*)c->cache;
+      if (spec) {  // the retrieved units are named on the device and found through the table of unit addresses
+        ind.ids = d_ids_tok;
+        ind.ptrs = c->d_unit_ptrs;
         ind.unit_bytes = c->unit_bytes;
         ind.n_units = g.topk;
         ind.first_seg = 1;
-        ind.miss = c->d_miss;
+        ind.landing = c->d_unit_ptrs + c->tab_cap;
       }
       {
         // the merge also adds this token's local attention row into the accumulated scores
         ProfScope ps(c, s, INFLLM_PROF_DECODE, dec_keys * HKV * D * 2 * esz);
         INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)segs.size(), segs.data(),
                                       qsel.data(), c->part_o, c->part_lse, c->max_parts, &parts, 0, c->dec_logits,
-                                      g.dtype, s, 64, spec ? &ind : nullptr, 0));
+                                      g.dtype, s, spec ? &ind : nullptr));
         INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts, (int)H, (int)D, out_eb, o_hs, c->lse, g.dtype, s,
-                                    c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap, spec ? c->d_miss : nullptr));
-      }
-      if (spec) {
-        INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));  // a refill must not overwrite slots these kernels may read
-        c->attn_recorded = true;
-        {
-          HostTimer ht(&c->host_us[0]);
-          INFLLM_CUDA_OK(cudaEventSynchronize(c->ev_sync));
-        }
-        ids.assign(c->h_topk, c->h_topk + g.topk);
-        std::vector<int32_t> missed;
-        for (int32_t b : ids)  // what the attention above could not resolve: not in the device table it read
-          if (!c->dev_table.count(b)) missed.push_back(b);
-        const bool all_hit = missed.empty();
-        {
-          HostTimer ht(&c->host_us[1]);
-          INFLLM_TRY(plan_and_refill(c, ids, eb, s, true));
-        }
-        c->trace_topk.push_back(ids);
-        INFLLM_TRY(decode_fetch_ahead(c, ids, c->h_topk + g.topk, c->decode_k - g.topk));
-        if (!all_hit) {
-          // the chunks of the missing units carry weight zero so far and the merge above did nothing: run those
-          // units now that their copies are ordered ahead on the stream, then merge everything
-          INFLLM_TRY(flush_table(c, s));
-          std::vector<KvSeg> late;
-          std::vector<int32_t> late_q;
-          for (int32_t b : missed) {
-            const char* base = (const char*)c->cache + (int64_t)c->slot_of[b] * c->unit_bytes;
-            late.push_back({base, base + c->unit_bytes / 2, bs * D, (int32_t)D, (int32_t)bs});
-            late_q.push_back(1);
-          }
-          int parts2 = 0;
-          ProfScope ps(c, s, INFLLM_PROF_DECODE, 0.0);
-          INFLLM_TRY(attn_decode_launch(qloc_eb, qglb_eb, q_hs_s, (int)H, (int)HKV, (int)D, (int)late.size(), late.data(),
-                                        late_q.data(), c->part_o, c->part_lse, c->max_parts, &parts2, -1, nullptr,
-                                        g.dtype, s, 64, nullptr, parts));
-          INFLLM_TRY(lse_merge_launch(c->part_o, c->part_lse, parts + parts2, (int)H, (int)D, out_eb, o_hs, c->lse,
-                                      g.dtype, s, c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap, nullptr));
-        }
+                                    c->dec_logits, E - wlo, tb.score + (wlo - tb.t0), tb.cap, nullptr));
       }
     } else {
       // ---- local stage + global stage, jointly normalised (context_manager.py:486-489, 526-533)
@@ -1598,6 +1650,13 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     if (more) INFLLM_TRY(candidates_launch(c, eb + 1, &n_cand, s));
     trace_mark(c, s, TR_SEAL_END, eb);
     INFLLM_TRY(seal_offload(c, first_new, sp.n_new, tok_new, s));  // off the ranking's critical path
+    if (L == 1 && sp.n_new > 0) {
+      // a one-token attention finds a unit through the table of unit addresses: the new units are listed at their
+      // place in the store, which the copy-out must have reached first (once per block_size tokens)
+      INFLLM_CUDA_OK(cudaStreamWaitEvent(s, c->ev_d2h, 0));
+      c->d2h_synced_upto = c->d2h_synced_upto_urgent = c->num_blocks;
+      for (int64_t b = first_new; b < c->num_blocks; ++b) c->tab_updates[(int32_t)b] = -1;
+    }
     if (!decode_path) INFLLM_TRY(local_scores(c, s, st, ks, lq, lk, j_u, lk, 0.0));
     trace_mark(c, s, TR_REST_END, eb);
     have_ids = false;
@@ -1662,6 +1721,9 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->d2h_stream));
     INFLLM_CUDA_OK(cudaStreamSynchronize(c->mail_stream));
   }
+  c->pend_head = c->pend_count = 0;  // retrievals not yet applied belong to the tokens that are forgotten
+  c->landing_slots.clear();
+  c->landing_listed.clear();
   c->d2h_synced_upto = 0;
   c->d2h_synced_upto_urgent = 0;
   release_dev_slabs(c);
@@ -1677,7 +1739,6 @@ extern "C" int infllm_ctx_reset(infllm_ctx* c) {
   c->table_valid = false;
   c->tab_updates.clear();
   c->dev_table.clear();
-  c->unlisted.clear();
   c->free_slots.clear();
   for (int i = c->cfg.max_cached_block + c->look_depth * c->cfg.topk - 1; i >= 0; --i) c->free_slots.push_back(i);
   c->staged.clear();
@@ -1704,7 +1765,13 @@ extern "C" int infllm_ctx_destroy(infllm_ctx* c) {
       if (p) cudaFree(p);
     if (c->block_k) cudaFreeAsync(c->block_k, nullptr);
     if (c->scores) cudaFreeAsync(c->scores, nullptr);
-    if (c->d_slot_table) cudaFreeAsync(c->d_slot_table, nullptr);
+    if (c->d_unit_ptrs) cudaFreeAsync(c->d_unit_ptrs, nullptr);
+
+    if (c->d_topk_ring) cudaFree(c->d_topk_ring);
+    for (auto& pt : c->pend) {
+      if (pt.h_ids) cudaFreeHost(pt.h_ids);
+      if (pt.ev) cudaEventDestroy(pt.ev);
+    }
     if (c->unit_prob) cudaFree(c->unit_prob);
     if (c->h_unit_prob) cudaFreeHost(c->h_unit_prob);
     if (c->h_topk) cudaFreeHost(c->h_topk);
@@ -1769,6 +1836,8 @@ extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, i
   INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
   if (!c->initialized) INFLLM_TRY(lazy_init(c, s));
   INFLLM_TRY(poll_device_error(c, s));
+  c->call_serial += 1;
+  c->last_stream = s;
   c->trace_topk.clear();
   c->counters.exec_blocks = 0;
   const int esz = c->esz;
@@ -1784,8 +1853,16 @@ extern "C" int infllm_ctx_append(infllm_ctx* c, const void* d_q, int64_t q_hs, i
   return INFLLM_OK;
 }
 
+// the tables the host keeps lag behind one-token appends by design: anyone who asks for them gets them up to date
+static int settle_for_caller(infllm_ctx* c) {
+  if (!c->initialized || c->pend_count == 0) return INFLLM_OK;
+  INFLLM_CUDA_OK(cudaSetDevice(c->cfg.device));
+  return settle_all(c, c->last_stream);
+}
+
 extern "C" int infllm_ctx_get_info(infllm_ctx* c, infllm_ctx_info* info) {
   if (!c || !info) return fail(INFLLM_E_BADARG, "ctx_get_info: null pointer");
+  INFLLM_TRY(settle_for_caller(c));
   *info = c->counters;
   info->length = c->length;
   info->frontier = c->frontier;
@@ -1865,6 +1942,7 @@ extern "C" int infllm_ctx_get_host_timers(infllm_ctx* c, double* us) {
 
 extern "C" int infllm_ctx_get_cached(infllm_ctx* c, int32_t* h_ids, double* h_stamps, int cap, int* n) {
   if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_cached: null pointer");
+  INFLLM_TRY(settle_for_caller(c));
   int i = 0;
   for (auto& kv : c->lru.items) {
     if (i < cap) {
@@ -1879,6 +1957,7 @@ extern "C" int infllm_ctx_get_cached(infllm_ctx* c, int32_t* h_ids, double* h_st
 
 extern "C" int infllm_ctx_get_topk(infllm_ctx* c, int64_t eb, int32_t* h_ids, int cap, int* n) {
   if (!c || !n) return fail(INFLLM_E_BADARG, "ctx_get_topk: null pointer");
+  INFLLM_TRY(settle_for_caller(c));
   if (eb < 0 || eb >= (int64_t)c->trace_topk.size())
     return fail(INFLLM_E_BADARG, "ctx_get_topk: exec block %lld of %zu", (long long)eb, c->trace_topk.size());
   const auto& t = c->trace_topk[eb];
@@ -2044,6 +2123,7 @@ struct FileCloser {
 extern "C" int infllm_ctx_save(infllm_ctx* c, const char* path, void* stream) {
   if (!c || !path) return fail(INFLLM_E_BADARG, "ctx_save: null pointer");
   if (!c->initialized) return fail(INFLLM_E_BADARG, "ctx_save: the context holds nothing yet");
+  INFLLM_TRY(settle_for_caller(c));
   const infllm_config& g = c->cfg;
   cudaStream_t s = (cudaStream_t)stream;
   INFLLM_CUDA_OK(cudaSetDevice(g.device));

@@ -312,46 +312,66 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
   __shared__ int s_cnt;
   __shared__ unsigned long long s_tau;
   __shared__ bool s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Rows of up to 2048 elements (the usual 4096 needs two rounds of it) live in a rolling buffer of eight 16-byte
+  // loads per lane: a piece is consumed and at once replaced by the matching piece of the warp's next row, so that
+  // the loads never drain between rows.  The first row's loads go out before the query vector is staged.
+  // Consecutive rows go to different SMs, so that a short list still draws on every SM's path to memory.
+  const int stride_rows = gridDim.x * 32;
+  const int pieces = (width + 2047) / 2048;  // pieces of 32 lanes x 8 loads x 8 elements per row
+  int row = warp * gridDim.x + blockIdx.x, piece = 0;
+  uint4 raw[8];
+  auto issue = [&](int r, int pc) {
+    const T* p = bk + (int64_t)r * width + pc * 2048;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = pc * 2048 + (u * 32 + lane) * 8;
+      raw[u] = (r < n && c < width) ? __ldcs(reinterpret_cast<const uint4*>(p + (u * 32 + lane) * 8)) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  issue(row, 0);
   for (int i = threadIdx.x; i < width; i += kTopkThreads) sq[i] = qbar[i];
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // consecutive rows go to different SMs, so that a short list still draws on every SM's path to memory
-  for (int row = warp * gridDim.x + blockIdx.x; row < n; row += gridDim.x * 32) {
-    const T* p = bk + (int64_t)row * width;
-    float acc = 0.f;
-    for (int c0 = 0; c0 < width; c0 += 32 * 8 * 8) {
-      uint4 raw[8];
+  float acc = 0.f;
+  while (row < n) {
+    int nrow = row, npiece = piece + 1;
+    if (npiece == pieces) {
+      npiece = 0;
+      nrow = row + stride_rows;
+    }
+    const bool more = nrow < n;
+    const T* np = bk + (int64_t)(more ? nrow : 0) * width + npiece * 2048 + lane * 8;
+    const int c0 = piece * 2048 + lane * 8, cn0 = npiece * 2048 + lane * 8;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int c = c0 + (u * 32 + lane) * 8;
-        raw[u] = c < width ? __ldcs(reinterpret_cast<const uint4*>(p + c)) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int c = c0 + (u * 32 + lane) * 8;
-        if (c < width) {
-          const typename Act<T>::T2* v2 = reinterpret_cast<const typename Act<T>::T2*>(&raw[u]);
-          const float4 qa = *reinterpret_cast<const float4*>(sq + c);
-          const float4 qb = *reinterpret_cast<const float4*>(sq + c + 4);
-          float2 f0 = Act<T>::to_f2(v2[0]), f1 = Act<T>::to_f2(v2[1]), f2 = Act<T>::to_f2(v2[2]),
-                 f3 = Act<T>::to_f2(v2[3]);
-          acc = fmaf(f0.x, qa.x, acc);
-          acc = fmaf(f0.y, qa.y, acc);
-          acc = fmaf(f1.x, qa.z, acc);
-          acc = fmaf(f1.y, qa.w, acc);
-          acc = fmaf(f2.x, qb.x, acc);
-          acc = fmaf(f2.y, qb.y, acc);
-          acc = fmaf(f3.x, qb.z, acc);
-          acc = fmaf(f3.y, qb.w, acc);
-        }
+    for (int u = 0; u < 8; ++u) {
+      const int c = c0 + u * 256;
+      const typename Act<T>::T2* v2 = reinterpret_cast<const typename Act<T>::T2*>(&raw[u]);
+      const float2 f0 = Act<T>::to_f2(v2[0]), f1 = Act<T>::to_f2(v2[1]), f2 = Act<T>::to_f2(v2[2]),
+                   f3 = Act<T>::to_f2(v2[3]);
+      // the slot is free: the matching piece of what comes next is requested before this one is summed
+      raw[u] = (more && cn0 + u * 256 < width) ? __ldcs(reinterpret_cast<const uint4*>(np + u * 256)) : make_uint4(0, 0, 0, 0);
+      if (c < width) {
+        const float4 qa = *reinterpret_cast<const float4*>(sq + c);
+        const float4 qb = *reinterpret_cast<const float4*>(sq + c + 4);
+        acc = fmaf(f0.x, qa.x, acc);
+        acc = fmaf(f0.y, qa.y, acc);
+        acc = fmaf(f1.x, qa.z, acc);
+        acc = fmaf(f1.y, qa.w, acc);
+        acc = fmaf(f2.x, qb.x, acc);
+        acc = fmaf(f2.y, qb.y, acc);
+        acc = fmaf(f3.x, qb.z, acc);
+        acc = fmaf(f3.y, qb.w, acc);
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      scores[row] = acc;
-      __threadfence();  // visible device-wide before this CTA takes its ticket
+    if (npiece == 0) {  // the row is complete
+      acc = warp_sum(acc);
+      if (lane == 0) scores[row] = acc;
+      acc = 0.f;
     }
+    row = nrow;
+    piece = npiece;
   }
+  __threadfence();  // this warp's scores are visible device-wide before the CTA takes its ticket
   if (!ticket) return;
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
@@ -445,6 +465,31 @@ int slot_table_update_launch(int32_t* table, const int32_t* ids, const int32_t* 
     }
     slot_table_update_kernel<<<1, kMaxTableUpdates, 0, s>>>(table, u, m);
     INFLLM_LAUNCH_OK("slot_table_update_kernel");
+  }
+  return INFLLM_OK;
+}
+
+// the same for the table of unit addresses (unit id -> where its K block lives)
+struct PtrUpdates {
+  int32_t id[kMaxTableUpdates];
+  unsigned long long val[kMaxTableUpdates];
+};
+__global__ void ptr_table_update_kernel(unsigned long long* __restrict__ table, const __grid_constant__ PtrUpdates u, int n) {
+  const int i = threadIdx.x;
+  if (i < n) table[u.id[i]] = u.val[i];
+}
+
+int ptr_table_update_launch(unsigned long long* table, const int32_t* ids, const unsigned long long* vals, int n,
+                            cudaStream_t s) {
+  for (int done = 0; done < n; done += kMaxTableUpdates) {
+    const int m = n - done < kMaxTableUpdates ? n - done : kMaxTableUpdates;
+    PtrUpdates u;
+    for (int i = 0; i < m; ++i) {
+      u.id[i] = ids[done + i];
+      u.val[i] = vals[done + i];
+    }
+    ptr_table_update_kernel<<<1, kMaxTableUpdates, 0, s>>>(table, u, m);
+    INFLLM_LAUNCH_OK("ptr_table_update_kernel");
   }
   return INFLLM_OK;
 }

@@ -211,7 +211,7 @@ def test_decode_split_k_and_merge_match_oracle(H, HKV, seg_lens):
         arr(ctypes.c_void_p, [v.data_ptr() for v in dv]), arr(ctypes.c_int64, [x * D for x in seg_lens]),
         arr(ctypes.c_int32, seg_lens), arr(ctypes.c_int32, qsel), part_o.data_ptr(), part_lse.data_ptr(), mp,
         ctypes.byref(nparts), 0, logits.data_ptr(), L.BF16, L.stream_ptr()))
-    assert nparts.value == sum((x + 127) // 128 for x in seg_lens)
+    assert 1 <= nparts.value <= mp  # one partial per run of 16-key groups: two CTAs per SM, fewer for short lists
     out = torch.empty(H, D, dtype=torch.bfloat16, device=DEV)
     lse = torch.empty(H, dtype=torch.float32, device=DEV)
     L.check(L.lib.infllm_lse_merge(part_o.data_ptr(), part_lse.data_ptr(), nparts.value, H, D, out.data_ptr(), D,
