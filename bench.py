@@ -246,28 +246,117 @@ def cpu_decode_sample(units=2048, steps=32):
 
 SAMPLE_DESC = ("{n} tokens ({eb} exec blocks of 512) of the same layer in steady state at 65536 tokens of context "
                "(479 sealed units, full window), projections included, fp32 torch on the host")
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_SETUP, REF_SAMPLE = 12288, 2048
+
+
+class ReferenceLayer:
+    """The reference's own ContextManager (unmodified copy under baseline/_ref, device literals rewritten to cpu at
+    import by tests/golden/ref_shim.py) behind the same projections as the GPU arm, fp32 on the host cores.  The
+    memory is brought to steady state once (REF_SETUP tokens: full window, 62 sealed units, retrieval of 16 active);
+    every sample() then appends the next REF_SAMPLE tokens (4 exec blocks of 512) and returns the seconds it took."""
+
+    def __init__(self):
+        sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+        import ref_shim
+
+        cm, rope, _ = ref_shim.install(REF_DIR)
+        self.w = make_weights("cpu", torch.float32)
+        self.g = torch.Generator().manual_seed(99)
+        self.mgr = cm.ContextManager(rope.RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0), CFG["n_init"], CFG["n_local"],
+                                     CFG["bs"], CFG["max_cached"], CFG["topk"], CFG["exc"], None, False, CFG["repr_topk"],
+                                     "lru", None, False, False, False, False)
+        with torch.inference_mode():
+            for _ in range(0, REF_SETUP, 4096):
+                self._feed(4096)
+
+    def _feed(self, n):
+        wq, wk, wv, wo = self.w
+        x = torch.randn((n, CFG["hidden"]), generator=self.g)
+        q = (x @ wq.T).view(n, CFG["H"], CFG["D"]).permute(1, 0, 2)[None]
+        k = (x @ wk.T).view(n, CFG["HKV"], CFG["D"]).permute(1, 0, 2)[None]
+        v = (x @ wv.T).view(n, CFG["HKV"], CFG["D"]).permute(1, 0, 2)[None]
+        o = self.mgr.append(q, k, v, q, k, v)
+        return o[0].permute(1, 0, 2).reshape(n, -1) @ wo.T
+
+    def sample(self):
+        t0 = time.perf_counter()
+        with torch.inference_mode():
+            self._feed(REF_SAMPLE)
+        return time.perf_counter() - t0
+
+
+def triton_exec_block_timing(dev):
+    """The reference's GPU kernel for the same exec block (its Triton _attn_fwd two-stage append with fattn=True,
+    triton_impl.py:430-478 and :520-556): 512 queries x 32 heads over a 4608-key window stage and a 2688-key global
+    stage, bf16, with the score pass of the local stage.  Returns microseconds per exec block, or the error."""
+    try:
+        sys.path.insert(0, REF_DIR)
+        from inf_llm.attention.dot_production_attention.triton_impl import TritonMultiStageDotProductionAttention as Att
+
+        H, HKV, D, lq = CFG["H"], CFG["HKV"], CFG["D"], CFG["exc"]
+        g = torch.Generator(device=dev).manual_seed(3)
+        mk = lambda h, n: torch.randn((1, h, n, D), generator=g, device=dev).to(torch.bfloat16)  # noqa: E731
+        q, kl, vl = mk(H, lq), mk(HKV, CFG["n_local"] + lq), mk(HKV, CFG["n_local"] + lq)
+        glk = CFG["topk"] * CFG["bs"] + CFG["n_init"] + lq
+        kg, vg = mk(HKV, glk), mk(HKV, glk)
+
+        def block():
+            att = Att(q.shape, q.dtype, q.device)
+            att.append(q, kl, vl, get_score=True, sliding_window=CFG["n_local"])
+            att.append(q, kg, vg, end=True, get_score=False, sliding_window=(glk + lq, CFG["n_local"]),
+                       complement_sliding_window=True)
+            return att.get_result()
+
+        for _ in range(3):
+            block()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            block()
+        b.record()
+        torch.cuda.synchronize()
+        us = 1e3 * a.elapsed_time(b) / 10
+        flops = 4.0 * D * H * (sum(min(CFG["n_local"], CFG["n_local"] + i + 1) for i in range(lq)) + lq * glk)
+        return dict(us_per_exec_block=us, tflops=flops / us / 1e6, includes="attention of both stages + the local score pass",
+                    triton=__import__("triton").__version__)
+    except Exception as e:  # the reference pins an older Triton
+        return dict(error=f"{type(e).__name__}: {str(e)[:300]}")
 
 
 def run_reference(args, rank):
+    """The reference arm: rank 0 alone, on every host core it can use."""
     if rank != 0:
         return
-    n = 2048
+    torch.set_num_threads(os.cpu_count() or 1)  # a launcher may have set OMP_NUM_THREADS=1
+    cores = torch.get_num_threads()
+    have_ref = os.path.isdir(os.path.join(REF_DIR, "inf_llm"))
+    n = REF_SAMPLE
+    if have_ref:
+        layer = ReferenceLayer()
+        sample, kind = layer.sample, "reference"
+        desc = (f"{n} tokens (4 exec blocks of 512) appended to the reference's own ContextManager (inf_llm/attention/"
+                f"context_manager.py, torch path, fattn=False) in steady state after {REF_SETUP} tokens (full 4096-token "
+                "window, retrieval of 16 units active; context grows by 2048 tokens per step), projections included, "
+                "fp32 on the host cores")
+    else:
+        sample = lambda: cpu_steady_state_sample(sample_tokens=n, threads=cores)[1]  # noqa: E731
+        kind, desc = "port", SAMPLE_DESC.format(n=n, eb=n // 512)
     for _ in range(args.warmup):
-        cpu_steady_state_sample(sample_tokens=n)
-    t0 = time.perf_counter()
-    cores = 0
-    for _ in range(args.steps):
-        _, _, cores = cpu_steady_state_sample(sample_tokens=n)
-    dt = time.perf_counter() - t0
+        sample()
+    secs = [sample() for _ in range(args.steps)]
+    dt = sum(secs)
     val = n * args.steps / dt
     line = dict(metric="exec-block prefill tokens/s/GPU @128K ctx", value=val, unit="tokens/s", n_gpus=args.gpus,
                 steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps, higher_is_better=True,
                 scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
                 config=dict(workload="mistral-7b attention layer, 131072-token prefill, exec 512, n_local 4096, "
                                      "topk 16, repr_topk 4, max_cached 32 (CPU arm: steady-state sample)"),
-                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port",
-                                  sample=SAMPLE_DESC.format(n=n, eb=n // 512)),
+                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind=kind, sample=desc),
                 e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    if have_ref and torch.cuda.is_available():
+        line["reference_gpu_kernel"] = triton_exec_block_timing(torch.device("cuda", 0))
     print(json.dumps(line))
 
 
@@ -394,6 +483,7 @@ def run_ours(args, rank, world, local_rank, device_store_mb=0, light=False):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
+    parity = head_groups_selfcheck(rank, world, dev, comm) if groups > 1 else None
     with torch.inference_mode():
         for _ in range(max(args.warmup, 1)):  # the first pass also creates the context memory
             prefill_device(layer, hidden)
@@ -467,10 +557,22 @@ def run_ours(args, rank, world, local_rank, device_store_mb=0, light=False):
                         "that no exec block waited for (event trace of one untimed prompt)"),
         host_ms_per_step={k: v / 1e3 / args.steps for k, v in host_us.items()},
         clocks=clocks)
+    if parity is not None:
+        line["parity"] = parity
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
-        line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port", seconds=secs,
-                                    sample=SAMPLE_DESC.format(n=2048, eb=4))
+        torch.set_num_threads(os.cpu_count() or 1)
+        if os.path.isdir(os.path.join(REF_DIR, "inf_llm")):  # the reference itself, from its unmodified copy
+            ref = ReferenceLayer()
+            ref.sample()
+            secs = min(ref.sample() for _ in range(2))
+            line["cpu_baseline"] = dict(value=REF_SAMPLE / secs, unit="tokens/s", cores=torch.get_num_threads(), kind="reference",
+                                        seconds=secs, sample=f"{REF_SAMPLE} tokens (4 exec blocks of 512) appended to the "
+                                        f"reference's own ContextManager (torch path) in steady state after {REF_SETUP}+ "
+                                        "tokens, projections included, fp32 on the host cores; best of 2")
+        else:
+            v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
+            line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port", seconds=secs,
+                                        sample=SAMPLE_DESC.format(n=2048, eb=4))
     return line
 
 
@@ -773,6 +875,94 @@ def run_thrash(args, rank, world, local_rank):
         clocks=clocks)
 
 
+def sharded_decode_selfcheck(rank, world, dev, mailbox_on=True, tokens=48):
+    """Untimed: a small memory (64 units per rank, bench head shape) decoded for `tokens` tokens through the unit-range
+    shards of all ranks, and on rank 0 also through one unsharded context: same retrievals (a flip or two on a near-tie
+    allowed) and outputs within 2e-2 wherever the retrievals agree.  Returns {ok, tokens, flips, max_abs} on every rank."""
+    import torch.distributed as dist
+
+    from infllm_b200.attention import (ContextManager, PeerMailbox, RotaryEmbeddingESM, ShardedDecodeMemory, UnitRangeShard,
+                                       unit_range)
+
+    H, HKV, D, bs, topk = CFG["H"], CFG["HKV"], CFG["D"], DEC["bs"], DEC["topk"]
+    n, n_local, n_init = 64 * world, 1024, DEC["n_init"]
+    rope = RotaryEmbeddingESM(D, CFG["base"], 1.0)
+    g = torch.Generator().manual_seed(4321)  # the same on every rank
+    bf = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16)  # noqa: E731
+    units, block_k = bf(n, 2, HKV, bs, D), torch.randn(n, H * D, generator=g)
+    direction = torch.randn(H, 1, D, generator=g)
+    direction = direction / direction.norm(dim=-1, keepdim=True)
+    rot = rope.apply_rotary_pos_emb_one_angle(direction.to(torch.bfloat16)[None].to(dev), n_local)[0].float().cpu().reshape(-1)
+    planted = torch.randperm(n, generator=g)[:topk + 8]
+    block_k[planted] = 0.7 * block_k[planted] + torch.linspace(9.0, 3.0, topk + 8)[:, None] * rot
+    block_k = block_k.to(torch.bfloat16)
+    init_k, init_v, win_k, win_v = bf(HKV, n_init, D), bf(HKV, n_init, D), bf(HKV, n_local, D), bf(HKV, n_local, D)
+    toks = [((torch.randn(H, 1, D, generator=g) + 3.0 * direction).to(torch.bfloat16), bf(HKV, 1, D), bf(HKV, 1, D))
+            for _ in range(tokens)]
+    lo, hi = unit_range(n, rank, world)
+    sh = UnitRangeShard(rank, world, rope, n_init, n_local, bs, DEC["max_cached"], topk, DEC["repr_topk"], H, HKV, D,
+                        torch.bfloat16, dev)
+    sh.load_synthetic(n, units[lo:hi], block_k[lo:hi], init_k, init_v, win_k, win_v)
+    mb = PeerMailbox(topk, H, D, device=dev) if (world > 1 and mailbox_on) else None
+    mem = ShardedDecodeMemory([sh], distributed=world > 1, mailbox=mb)
+    outs, ids = [], []
+    for q, k, v in toks:
+        outs.append(mem.append(q.to(dev), k.to(dev), v.to(dev)).float())
+        ids.append(list(mem.last_ids))
+    torch.cuda.synchronize()
+    res = torch.zeros(3, dtype=torch.float64, device=dev)  # ok, flips, max_abs
+    if rank == 0:
+        cm = ContextManager(rope, n_init, n_local, bs, DEC["max_cached"], topk, DEC["exc"], None, True, DEC["repr_topk"])
+        cm.load_synthetic(units, block_k, init_k, init_v, win_k, win_v)
+        flips, worst = 0, 0.0
+        for i, (q, k, v) in enumerate(toks):
+            dq, dk, dv = (t[None].to(dev) for t in (q, k, v))
+            want = cm.append(dq, dk, dv, dq, dk, dv)[0].float()
+            if sorted(cm.last_topk()[0]) != sorted(ids[i]):
+                flips += 1
+                continue
+            worst = max(worst, (outs[i] - want).abs().max().item())
+        res[0], res[1], res[2] = float(flips <= 2 and worst <= 2e-2), flips, worst
+    if world > 1:
+        dist.broadcast(res, 0)
+        dist.barrier()
+    if mb is not None:
+        mb.close()
+    return dict(ok=bool(res[0].item()), tokens=tokens, retrieval_flips=int(res[1].item()), max_abs=res[2].item(),
+                against="one unsharded context on rank 0 over the same 64-units-per-rank memory")
+
+
+def head_groups_selfcheck(rank, world, dev, comm, tokens=16384):
+    """Untimed: a `tokens`-token prompt through one layer sharded by KV-head groups over all ranks, and on rank 0 also
+    through the whole layer: same retrieval in every exec block and outputs within 2 % of their range."""
+    import torch.distributed as dist
+
+    from infllm_b200.attention import ATTN_FORWRAD, RotaryEmbeddingESM
+
+    mk = lambda c: ATTN_FORWRAD["inf-llm"](  # noqa: E731
+        n_local=CFG["n_local"], n_init=CFG["n_init"], topk=CFG["topk"], block_size=CFG["bs"], max_cached_block=CFG["max_cached"],
+        exc_block_size=CFG["exc"], fattn=True, repr_topk=CFG["repr_topk"], head_group_comm=c)
+    full = make_weights(dev, torch.bfloat16)
+    hidden = make_hidden(tokens, seed=77, weights=full, device=dev)
+    rope = RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0)
+    sharded = Layer(dev, mk(comm), rope, rank=rank, world=world)
+    with torch.inference_mode():
+        outs = [sharded(hidden[:, s0:s0 + CFG["chunk"]]) for s0 in range(0, tokens, CFG["chunk"])]
+        ids = sharded.pkv.last_topk()
+        res = torch.zeros(3, dtype=torch.float64, device=dev)
+        if rank == 0:
+            whole = Layer(dev, mk(None), rope)
+            want = [whole(hidden[:, s0:s0 + CFG["chunk"]]) for s0 in range(0, tokens, CFG["chunk"])]
+            same = whole.pkv.last_topk() == ids
+            scale = max(w.float().abs().max().item() for w in want)
+            worst = max((a.float() - b.float()).abs().max().item() for a, b in zip(outs, want))
+            res[0], res[1], res[2] = float(same and worst <= 0.02 * scale), float(same), worst / scale
+    dist.broadcast(res, 0)
+    dist.barrier()
+    return dict(ok=bool(res[0].item()), tokens=tokens, same_retrievals=bool(res[1].item()),
+                max_abs_over_range=res[2].item(), against="the whole layer on rank 0")
+
+
 def run_decode_sharded(args, rank, world, local_rank):
     """The 1M-token decode with the memory sharded by unit range over the ranks (strong scaling: one sequence)."""
     import torch.distributed as dist
@@ -827,11 +1017,13 @@ def run_decode_sharded(args, rank, world, local_rank):
     h_o = torch.empty((H, 1, D), dtype=torch.bfloat16).pin_memory()
     pos = [0]
 
+    toks = [(qs[i], ks[i], vs[i]) for i in range(total)]  # views made once: the timed loop is the library's
+
     def step_device():
         for m in mems:
-            i = pos[0]
+            q, k, v = toks[pos[0]]
             pos[0] += 1
-            m.append(qs[i], ks[i], vs[i])
+            m.append(q, k, v)
 
     def step_host():
         for m in mems:
@@ -861,6 +1053,7 @@ def run_decode_sharded(args, rank, world, local_rank):
         return ms.item()
 
     with torch.inference_mode():
+        parity = sharded_decode_selfcheck(rank, world, dev, mailbox_on=not args.nccl_exchange) if world > 1 else None
         for _ in range(args.warmup):
             step_device()
         shards = [m.shards[0] for m in mems]
@@ -920,6 +1113,7 @@ def run_decode_sharded(args, rank, world, local_rank):
                                     "device" if mailbox is not None else "by NCCL all-gathers")
                                  + "; all-reduce of 128 score columns per sealed unit (NCCL)"),
                     tokens_redone=sum(m.redone for m in mems)),
+        parity=parity,
         e2e=dict(value=1e3 * ms_e2e / per_layer, unit="us/token", h2d_bytes_per_step=int((H + 2 * HKV) * D * 2 * n_layers),
                  d2h_bytes_per_step=int(H * D * 2 * n_layers)),
         gpu_launches=int(launches),
@@ -1094,7 +1288,7 @@ def main():
                 hargs.head_groups, hargs.no_cpu, hargs.steps = True, True, min(args.steps, 2)
                 hg = run_ours(hargs, rank, world, local_rank)
                 line["head_groups"] = {k: hg[k] for k in ("value", "unit", "ms_per_step", "scaling", "e2e", "roofline", "config",
-                                                           "host_ms_per_step", "parity")}
+                                                           "host_ms_per_step", "parity") if k in hg}
     # the record of a run may keep only the end of this line: the figures that matter most, once more, last
     dec = line.get("decode", line if line.get("unit") == "us/token" else {})
     hg = line.get("head_groups", {})
@@ -1108,6 +1302,9 @@ def main():
         thrash_tokens_s=(line.get("thrash") or {}).get("value"), n_gpus=world)
     if rank == 0:
         print(json.dumps(line))
+    bad = [k for k in ("decode_parity_ok", "head_groups_parity_ok") if line["summary"].get(k) is False]
+    if bad:
+        raise SystemExit(f"self-check failed: {bad}")
     if world > 1:
         import torch.distributed as dist
 

@@ -179,7 +179,9 @@ int infllm_lse_merge_ex(const float* d_part_o, int64_t part_o_stride, const floa
  * d_slot_table[id - id_lo] (K then V, unit_bytes, at d_cache + slot * unit_bytes; -1: not cached).  Units of other
  * owners and ids < 0 get weight zero; an owned unit that is not cached gets weight zero and sets *d_miss = 1.
  * h_seg_k / h_seg_v of those segments are ignored.  Lets the attention follow a device-side retrieval without a
- * host round trip.  infllm_slot_table_update writes d_table[h_ids[i]] = h_slots[i] (ids must not repeat). */
+ * host round trip.  With d_cache == NULL, d_slot_table is read as a table of 64-bit unit ADDRESSES instead (id - id_lo
+ * -> where the unit's K block lives, V at + unit_bytes / 2; 0 = nowhere): the unit is then attended wherever it is,
+ * for instance in place in pinned host memory.  infllm_slot_table_update writes d_table[h_ids[i]] = h_slots[i] (ids must not repeat). */
 int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int n_heads, int n_kv_heads, int head_dim, int n_seg,
                              const void* const* h_seg_k, const void* const* h_seg_v, const int64_t* h_seg_hs,
                              const int32_t* h_seg_len, const int32_t* h_seg_q, int first_unit_seg, int n_units,
@@ -188,6 +190,11 @@ int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int n_heads, in
                              float* d_part_lse, int max_parts, int* n_parts, int logit_seg, float* d_logits,
                              int dtype, void* stream);
 int infllm_slot_table_update(int32_t* d_table, const int32_t* h_ids, const int32_t* h_slots, int n, void* stream);
+/* The same for a table of unit ADDRESSES (unit id -> where its K block lives right now; V follows at unit_bytes / 2):
+ * d_table[h_ids[i]] = h_addrs[i].  infllm_shard_token_run reads such a table when its d_unit_ptrs is set: a
+ * retrieved unit is then found wherever it lives — in a cache slot, or in place in the pinned host store, which the
+ * GPU reads over PCIe — so that no token ever has to wait for a refill. */
+int infllm_ptr_table_update(uint64_t* d_table, const int32_t* h_ids, const uint64_t* h_addrs, int n, void* stream);
 
 /* infllm_attn_decode_noalloc has no counterpart in the reference.  It is infllm_attn_decode followed by
  * infllm_lse_merge in one call that allocates nothing: the split-K partials go to a scratch array that is
@@ -423,6 +430,8 @@ typedef struct infllm_shard_token {
   int64_t cand_off, cand_slot, cand_bytes, part_off, part_slot, part_bytes, flag1_off, flag2_off; /* mailbox layout */
   uint32_t seq;
   int32_t wait_us;
+  const uint64_t* d_unit_ptrs;             /* (n_owned) id - id_lo -> address of the unit's K block; NULL: the slot table */
+  uint32_t* d_ticket;                      /* one zeroed word: scoring and top-k as ONE launch; NULL: two launches */
 } infllm_shard_token;
 int infllm_shard_token_run(const infllm_shard_token* args, infllm_mailbox* mailbox, void* stream);
 

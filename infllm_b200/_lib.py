@@ -74,6 +74,7 @@ class ShardToken(ctypes.Structure):
         ("cand_off", c_int64), ("cand_slot", c_int64), ("cand_bytes", c_int64), ("part_off", c_int64),
         ("part_slot", c_int64), ("part_bytes", c_int64), ("flag1_off", c_int64), ("flag2_off", c_int64),
         ("seq", ctypes.c_uint32), ("wait_us", c_int32),
+        ("d_unit_ptrs", c_void_p), ("d_ticket", c_void_p),
     ]
 
 
@@ -112,6 +113,7 @@ SIGNATURES = {
                                          c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p,
                                          c_void_p, c_void_p, c_int, POINTER(c_int), c_int, c_void_p, c_int, c_void_p]),
     "infllm_slot_table_update": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int, c_void_p]),
+    "infllm_ptr_table_update": (c_int, [c_void_p, POINTER(c_int32), POINTER(ctypes.c_uint64), c_int, c_void_p]),
     "infllm_mailbox_handle_bytes": (c_int, []),
     "infllm_mailbox_create": (c_int, [c_int64, c_int, c_int, c_void_p, POINTER(c_void_p)]),
     "infllm_mailbox_open": (c_int, [c_void_p, c_void_p]),

@@ -137,6 +137,10 @@ class UnitRangeShard:
         self.block_k[:n_owned].copy_(block_k)
         self.scores_buf = torch.empty((max(room, 1),), dtype=torch.float32, device=self.device)
         self.slot_table = torch.full((max(room, 1),), -1, dtype=torch.int32, device=self.device)
+        # where every owned unit lives right now: its cache slot, else its place in the pinned host store (which the
+        # attention reads in place over PCIe, so that no token waits for a refill)
+        self.ptr_table = self._store_addresses(max(room, 1))
+        self.ticket = torch.zeros((4,), dtype=torch.int32, device=self.device)
         self.init_k, self.init_v = init_k.to(self.device).contiguous(), init_v.to(self.device).contiguous()
         self._store_pointers()
         self.n_total, self.lo, self.n_owned = n_total, lo, n_owned
@@ -149,9 +153,14 @@ class UnitRangeShard:
         self.score.zero_()
         self._rotate(0, n)
 
+    def _store_addresses(self, room):
+        base = self.host_units.data_ptr()
+        return (base + torch.arange(room, dtype=torch.int64) * self.unit_bytes).to(self.device)
+
     def _store_pointers(self):
         self._p.update(block_k=self.block_k.data_ptr(), host_units=self.host_units.data_ptr(),
-                       slot_table=self.slot_table.data_ptr(),
+                       slot_table=self.slot_table.data_ptr(), ptr_table=self.ptr_table.data_ptr(),
+                       ticket=self.ticket.data_ptr(),
                        scores_buf=self.scores_buf.data_ptr(), init_k=self.init_k.data_ptr(), init_v=self.init_v.data_ptr())
 
     def _rope(self, x, x_hs, x_ts, out, o_hs, o_ts, heads, length, pos0, step):
@@ -287,11 +296,15 @@ class UnitRangeShard:
             _lib.check(_lib.lib.infllm_unit_fetch(self._p["cache"] + slot * self.unit_bytes,
                                                   self._p["host_units"] + (b - self.lo) * self.unit_bytes,
                                                   self.unit_bytes, self._stream))
-        if changed:  # the device copy of the slot table, read by attend_device()
+        if changed:  # the device copies of the slot table (attend_device) and of the unit addresses (run_token)
             m = len(changed)
             ids = (ctypes.c_int32 * m)(*changed.keys())
             slots = (ctypes.c_int32 * m)(*changed.values())
             _lib.check(_lib.lib.infllm_slot_table_update(self._p["slot_table"], ids, slots, m, self._stream))
+            addrs = (ctypes.c_uint64 * m)(*[
+                self._p["cache"] + sl * self.unit_bytes if sl >= 0 else self._p["host_units"] + i * self.unit_bytes
+                for i, sl in changed.items()])
+            _lib.check(_lib.lib.infllm_ptr_table_update(self._p["ptr_table"], ids, addrs, m, self._stream))
 
     def run_token(self, q, k, v, out, mb):
         """One token through infllm_shard_token_run: every launch of it in one call (see the header).  Leaves the
@@ -319,6 +332,7 @@ class UnitRangeShard:
         a.d_q, a.d_k, a.d_vin, a.q_hs, a.k_hs, a.v_hs = q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0)
         a.at = self.length - self.t0
         a.d_block_k, a.d_scores, a.d_slot_table = p["block_k"], p["scores_buf"], p["slot_table"]
+        a.d_unit_ptrs, a.d_ticket = p["ptr_table"], p["ticket"]
         a.n_owned, a.id_lo = self.n_owned, self.lo
         a.share_at, a.share_len = lo_ - self.t0, hi_ - lo_
         first = r == 0 and self.n_init > 0
@@ -330,9 +344,9 @@ class UnitRangeShard:
         _lib.check(_lib.lib.infllm_shard_token_run(ctypes.byref(a), mb.handle, self._stream))
 
     def attend_device(self):
-        """attend() for a retrieval that exists only on the device so far (d_gids): the owned units are resolved
-        through the device copy of the slot table.  The message [o | lse | miss word] is left in `pack`; the miss
-        word is 1 when an owned retrieved unit was not cached (its weight is then zero and the token is redone)."""
+        """attend() for a retrieval that exists only on the device so far (d_gids): the owned units are found through
+        the device table of unit addresses — in their cache slots, or in place in the pinned store.  The message
+        [o | lse | miss word] is left in `pack` (the miss word stays 0: every owned unit has an address)."""
         E, G, r = self.length + 1, self.world, self.rank
         esz, D, p = 2, self.D, self._p
         kp, vp, hs, ln, qs = self._unit_seg_arrays  # the first topk entries are placeholders the kernel resolves
@@ -358,8 +372,8 @@ class UnitRangeShard:
         miss = p["pack"] + self.H * (D + 1) * 4
         ev = self._mark("decode")
         _lib.check(_lib.lib.infllm_attn_decode_units(
-            p["q_loc"], p["q_glb"], self.H, self.HKV, D, n, kp, vp, hs, ln, qs, 0, self.topk, p["d_status"], p["slot_table"],
-            self.lo, self.n_owned, p["cache"], self.unit_bytes, miss, p["part_o"], p["part_lse"], self.max_parts,
+            p["q_loc"], p["q_glb"], self.H, self.HKV, D, n, kp, vp, hs, ln, qs, 0, self.topk, p["d_status"], p["ptr_table"],
+            self.lo, self.n_owned, None, self.unit_bytes, miss, p["part_o"], p["part_lse"], self.max_parts,
             ctypes.byref(n_parts), logit_seg, p["logits"], self.code, self._stream))
         _lib.check(_lib.lib.infllm_lse_merge(p["part_o"], p["part_lse"], n_parts.value, self.H, D, p["pack"], D,
                                              p["pack"] + self.H * D * 4, F32, self._stream))
@@ -423,6 +437,10 @@ class UnitRangeShard:
         table = torch.full((room,), -1, dtype=torch.int32, device=self.device)
         table[:self.slot_table.shape[0]].copy_(self.slot_table)
         self.slot_table = table
+        ptrs = self._store_addresses(room)  # the store moved: cached units keep their slots
+        for b, slot in self.slot_of.items():
+            ptrs[b - self.lo] = self._p["cache"] + slot * self.unit_bytes
+        self.ptr_table = ptrs
         self._store_pointers()
 
 
@@ -483,10 +501,39 @@ class ShardedDecodeMemory:
         # ranked on the device; the collectives below remain for the rare token that has to be redone (a retrieved
         # unit was not cached) and for the score columns of a sealing
         self.mailbox = mailbox if (distributed and mailbox is not None and mailbox.world > 1) else None
-        self.redone = 0
+        self.redone = 0  # tokens that had to be run again (none since retrieved units are read wherever they live)
+        self._pending = None  # (event behind the token's status copy,) of the token whose retrieval is not applied yet
+        self._last_ids = []
         if not distributed:
             assert [s.rank for s in self.shards] == list(range(self.shards[0].world)), "emulation needs every rank"
-        self.last_ids = []
+
+    @property
+    def last_ids(self):
+        """The global retrieval of the last token (applies it to the cache tables first if that is still due)."""
+        self._settle()
+        return self._last_ids
+
+    @last_ids.setter
+    def last_ids(self, ids):
+        self._last_ids = ids
+
+    def _settle(self):
+        """The token launched last ran ahead of the host: read its retrieval and status words now (they left the
+        device right behind its kernels), check the exchange status and advance this rank's LRU order; a retrieved
+        unit that is not cached is refilled on the token stream — the token itself read it in place."""
+        if self._pending is None:
+            return
+        s = self.shards[0]
+        self._pending.synchronize()
+        self._pending = None
+        status = s.h_status.tolist()
+        if status[s.topk]:
+            s.d_status[s.topk:].zero_()
+            raise _lib.InfLLMError(_lib.E_TIMEOUT, f"rank {status[s.topk] - 1} did not arrive at an exchange of the "
+                                                   "sharded decode within the limit")
+        ids = [b for b in status[:s.topk] if b >= 0]
+        self._last_ids = ids
+        s._refill([b for b in ids if s.lo <= b < s.lo + s.n_owned])
 
     def _all_gather(self, local):
         """local: (n_local_shards, ...) -> (world, ...) in rank order."""
@@ -538,6 +585,7 @@ class ShardedDecodeMemory:
             import torch.distributed as dist
 
             dist.barrier(group=self.group)
+        self._settle()  # the previous token's retrieval: LRU order, refills (stream-ordered ahead of this token)
         mb.seq += 1
         if s.n_owned >= s.topk:  # the whole token in one call into the library
             out = torch.empty((H, D), dtype=s.dtype, device=s.device)
@@ -560,20 +608,10 @@ class ShardedDecodeMemory:
                                                mb.miss_off, any_miss, None, st))
             out = s.merge_raw(mb.local + mb.part_off, mb.part_slot // 4, mb.world, any_miss)
             s.h_status.copy_(s.d_status, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the retrieval and the two status words are on the host now
-        status = s.h_status.tolist()
-        ids = [b for b in status[:s.topk] if b >= 0]
-        if status[s.topk]:
-            s.d_status[s.topk:].zero_()
-            raise _lib.InfLLMError(_lib.E_TIMEOUT, f"rank {status[s.topk] - 1} did not arrive at an exchange of the "
-                                                   "sharded decode within the limit")
-        self.last_ids = ids
-        if status[s.topk + 1]:  # some rank lacked a unit: refill, then this token again through the collectives
-            self.redone += 1
-            parts = self._all_gather(s.attend(ids)[None])
-            out = s.merge(parts)
-        else:
-            s._refill([b for b in ids if s.lo <= b < s.lo + s.n_owned])  # all cached: advances the LRU order only
+        # the host does not wait: the status words and the retrieval are read when the next token arrives (or when
+        # somebody asks for last_ids), and the LRU order is advanced then
+        self._pending = torch.cuda.Event()
+        self._pending.record()
         sealing = s.finish()
         if sealing is not None:
             s.seal(self._all_reduce(sealing))

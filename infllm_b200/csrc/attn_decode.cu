@@ -575,7 +575,9 @@ extern "C" int infllm_attn_decode_units(const void* d_q0, const void* d_q1, int 
     segs[i] = {unit ? nullptr : h_seg_k[i], unit ? nullptr : h_seg_v[i], h_seg_hs[i], head_dim, h_seg_len[i]};
   }
   DecodeIndirect ind;
-  ind.ids = d_unit_ids; ind.table = d_slot_table; ind.cache = (const char*)d_cache; ind.unit_bytes = unit_bytes;
+  ind.ids = d_unit_ids; ind.cache = (const char*)d_cache; ind.unit_bytes = unit_bytes;
+  if (d_cache) ind.table = d_slot_table;
+  else ind.ptrs = reinterpret_cast<const unsigned long long*>(d_slot_table);  // a table of unit addresses
   ind.n_units = n_units; ind.first_seg = first_unit_seg; ind.miss = d_miss; ind.id_lo = id_lo; ind.n_owned = n_owned;
   return attn_decode_launch(d_q0, d_q1, head_dim, n_heads, n_kv_heads, head_dim, n_seg, segs, h_seg_q, d_part_o,
                             d_part_lse, max_parts, n_parts, logit_seg, d_logits, dtype, (cudaStream_t)stream,

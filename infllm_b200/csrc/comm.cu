@@ -326,7 +326,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
                                  a->d_cos, a->d_sin, a->cap, a->at, a->n_local - 1, a->dtype, s, nullptr));
   // 2. this rank's candidates: [score bits (topk) | ids (topk)]
   INFLLM_TRY(block_topk_launch(a->d_block_k, a->n_owned, H * D, a->d_qbar, a->d_scores, a->topk, a->id_lo,
-                               a->d_cand + a->topk, reinterpret_cast<float*>(a->d_cand), a->dtype, s, nullptr));
+                               a->d_cand + a->topk, reinterpret_cast<float*>(a->d_cand), a->dtype, s, a->d_ticket));
   // 3. exchange 1, global top-k
   int* err = a->d_status + a->topk;
   int32_t* any_miss = a->d_status + a->topk + 1;
@@ -359,6 +359,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   }
   DecodeIndirect ind;
   ind.ids = a->d_status; ind.table = a->d_slot_table; ind.cache = (const char*)a->d_cache; ind.unit_bytes = a->unit_bytes;
+  ind.ptrs = reinterpret_cast<const unsigned long long*>(a->d_unit_ptrs);  // set: found wherever the unit lives
   ind.n_units = a->topk; ind.first_seg = 0; ind.miss = miss_word; ind.id_lo = a->id_lo; ind.n_owned = a->n_owned;
   int parts = 0;
   INFLLM_TRY(attn_decode_launch(a->d_q_loc, a->d_q_glb, D, H, HKV, D, n, segs, qsel, a->d_part_o, a->d_part_lse,

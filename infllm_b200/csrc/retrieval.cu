@@ -620,6 +620,14 @@ extern "C" int infllm_block_score_rows(const void* d_block_k, const int32_t* h_r
   return block_score_rows_launch(d_block_k, h_rows, n, width, d_qbar, d_scores, dtype, (cudaStream_t)stream);
 }
 
+extern "C" int infllm_ptr_table_update(uint64_t* d_table, const int32_t* h_ids, const uint64_t* h_addrs, int n, void* stream) {
+  using namespace infllm;
+  if (!d_table || (n > 0 && (!h_ids || !h_addrs)) || n < 0) return fail(INFLLM_E_BADARG, "ptr_table_update: bad argument");
+  static_assert(sizeof(uint64_t) == sizeof(unsigned long long), "64-bit table entries");
+  return ptr_table_update_launch(reinterpret_cast<unsigned long long*>(d_table), h_ids,
+                                 reinterpret_cast<const unsigned long long*>(h_addrs), n, (cudaStream_t)stream);
+}
+
 // d_table[h_ids[i]] = h_slots[i] for i < n on `stream` (ids must not repeat); -1 marks "not cached"
 extern "C" int infllm_slot_table_update(int32_t* d_table, const int32_t* h_ids, const int32_t* h_slots, int n,
                                         void* stream) {

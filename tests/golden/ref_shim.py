@@ -1,8 +1,10 @@
 """Import the Python reference (thunlp/InfLLM) on a machine without a GPU.
 
-Used ONLY by make_golden.py, on a machine that has the reference checkout; the
-fixtures it writes are what travels.  Nothing under the package, the GPU tests
-or bench.py imports this file.
+Used by make_golden.py, on a machine that has the reference checkout (the
+fixtures it writes are what travels), and by the reference arm of bench.py
+(`--impl reference`), which times the reference's own ContextManager on the
+host cores from an unmodified copy of its package.  Nothing under the package
+and none of the GPU tests imports this file.
 
 The reference hard-codes CUDA in a few places (inf_llm/attention/rope.py:23,
 inf_llm/attention/context_manager.py:13,122,133,306) and calls

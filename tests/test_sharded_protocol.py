@@ -160,3 +160,40 @@ def test_two_gloo_ranks_match_one_rank(tmp_path):
         got, ids = torch.load(f"{path}.{rank}")
         assert ids == want_ids
         assert (got - want).abs().max().item() < 1e-4
+
+
+def _worker_that_leaves(rank, world, port, path):
+    """Rank 1 takes part in three tokens and then leaves between steps; rank 0 goes on to a fourth token."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    mem = ShardedDecodeMemory([CpuShard(rank, world)], distributed=True)
+    g = torch.Generator().manual_seed(1)
+    toks = [(torch.randn(H, 1, D, generator=g), torch.randn(HKV, 1, D, generator=g), torch.randn(HKV, 1, D, generator=g))
+            for _ in range(4)]
+    outs = [mem.append(*t) for t in toks[:3]]
+    if rank == 1:
+        torch.save("left", f"{path}.1")
+        os._exit(0)  # no goodbye: the peer finds out at its next collective
+    try:
+        mem.append(*toks[3])
+        verdict = "no error"
+    except Exception as e:  # the gather of the candidates cannot complete: a timeout or a closed connection
+        verdict = f"error: {type(e).__name__}"
+    torch.save((verdict, torch.stack(outs)), f"{path}.0")
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_ends_the_next_exchange_with_an_error(tmp_path):
+    """Failure detection on the host: when a rank is gone, the other rank's next collective ends with an error
+    within the process group's (short) timeout instead of hanging, and what was computed before stays valid."""
+    path = str(tmp_path / "out")
+    mp.spawn(_worker_that_leaves, args=(2, 30500 + os.getpid() % 1000, path), nprocs=2, join=True)
+    verdict, outs = torch.load(f"{path}.0")
+    assert verdict.startswith("error"), verdict
+    want = ShardedDecodeMemory([CpuShard(0, 1)])
+    g = torch.Generator().manual_seed(1)
+    for i in range(3):
+        t = (torch.randn(H, 1, D, generator=g), torch.randn(HKV, 1, D, generator=g), torch.randn(HKV, 1, D, generator=g))
+        assert (want.append(*t) - outs[i]).abs().max().item() < 1e-4
