@@ -323,6 +323,12 @@ def triton_exec_block_timing(dev):
                     triton=__import__("triton").__version__)
     except Exception as e:  # the reference pins an older Triton
         return dict(error=f"{type(e).__name__}: {str(e)[:300]}")
+    finally:
+        # the package was imported as it is on disk: forget it, the CPU arm imports it again through its shim
+        for name in [m for m in sys.modules if m == "inf_llm" or m.startswith("inf_llm.")]:
+            del sys.modules[name]
+        if REF_DIR in sys.path:
+            sys.path.remove(REF_DIR)
 
 
 def run_reference(args, rank):
@@ -333,6 +339,9 @@ def run_reference(args, rank):
     cores = torch.get_num_threads()
     have_ref = os.path.isdir(os.path.join(REF_DIR, "inf_llm"))
     n = REF_SAMPLE
+    # the reference's GPU kernel first: the CPU shim below replaces torch.cuda's stream and event classes for good
+    gpu_kernel = triton_exec_block_timing(torch.device("cuda", 0)) if (have_ref and torch.cuda.is_available() and
+                                                                      not args.no_ref_gpu) else None
     if have_ref:
         layer = ReferenceLayer()
         sample, kind = layer.sample, "reference"
@@ -355,8 +364,8 @@ def run_reference(args, rank):
                                      "topk 16, repr_topk 4, max_cached 32 (CPU arm: steady-state sample)"),
                 cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind=kind, sample=desc),
                 e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
-    if have_ref and torch.cuda.is_available():
-        line["reference_gpu_kernel"] = triton_exec_block_timing(torch.device("cuda", 0))
+    if gpu_kernel is not None:
+        line["reference_gpu_kernel"] = gpu_kernel
     print(json.dumps(line))
 
 
@@ -561,14 +570,17 @@ def run_ours(args, rank, world, local_rank, device_store_mb=0, light=False):
         line["parity"] = parity
     if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
-        if os.path.isdir(os.path.join(REF_DIR, "inf_llm")):  # the reference itself, from its unmodified copy
-            ref = ReferenceLayer()
-            ref.sample()
-            secs = min(ref.sample() for _ in range(2))
-            line["cpu_baseline"] = dict(value=REF_SAMPLE / secs, unit="tokens/s", cores=torch.get_num_threads(), kind="reference",
-                                        seconds=secs, sample=f"{REF_SAMPLE} tokens (4 exec blocks of 512) appended to the "
-                                        f"reference's own ContextManager (torch path) in steady state after {REF_SETUP}+ "
-                                        "tokens, projections included, fp32 on the host cores; best of 2")
+        ref = None
+        if os.path.isdir(os.path.join(REF_DIR, "inf_llm")):
+            # the reference itself, in a process of its own (its CPU shim replaces torch.cuda's stream classes)
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "2", "--warmup", "1",
+                                "--no-ref-gpu"], capture_output=True, text=True,
+                               env=dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS=str(os.cpu_count() or 1)))
+            for ln in r.stdout.splitlines():
+                if ln.startswith("{"):
+                    ref = json.loads(ln)["cpu_baseline"]
+        if ref is not None:
+            line["cpu_baseline"] = ref
         else:
             v, secs, cores = cpu_steady_state_sample(sample_tokens=2048)
             line["cpu_baseline"] = dict(value=v, unit="tokens/s", cores=cores, kind="port", seconds=secs,
@@ -1146,7 +1158,7 @@ def run_model(args, rank, world, local_rank):
     g = torch.Generator().manual_seed(0)
     tokens = args.tokens or CFG["tokens"]
     h_ids = torch.randint(0, 128256, (1, tokens), generator=g).pin_memory()
-    n_new = 16
+    n_new = 64
 
     def prompt():
         dec.reset()
@@ -1155,19 +1167,23 @@ def run_model(args, rank, world, local_rank):
             logits = dec.step(h_ids[:, st:st + CFG["chunk"]].to(dev, non_blocking=True))
         return logits
 
-    for _ in range(max(1, min(args.warmup, 2))):
+    for _ in range(1 if tokens >= 131072 else max(1, min(args.warmup, 2))):
         prompt()
     torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     ms_prefill = ms_decode = 0.0
-    tokens = []
+    out_ids, prints = [], []
     for _ in range(args.steps):
         ev[0].record()
         logits = prompt()
         ev[1].record()
-        for _ in range(n_new):
+        for i in range(n_new):
             nxt = logits.argmax(dim=-1)
-            tokens.append(int(nxt))
+            out_ids.append(int(nxt))
+            if i < 4 and len(prints) < 4:  # to compare runs on other GPU counts with: the chosen token and its margin
+                top = logits.float().flatten().topk(2).values
+                prints.append(dict(token=int(nxt), logit=round(top[0].item(), 4), margin=round((top[0] - top[1]).item(), 4),
+                                   logit_range=round((logits.float().max() - logits.float().min()).item(), 3)))
             logits = dec.step(nxt[:, None])
         ev[2].record()
         torch.cuda.synchronize()
@@ -1189,7 +1205,8 @@ def run_model(args, rank, world, local_rank):
                 config=dict(workload=f"32-layer decoder, {tokens}-token prompt in chunks of {CFG['chunk']}, "
                                      f"exec blocks of {CFG['exc']}, then {n_new} greedy tokens; host token ids",
                             parallelism=f"kv-head-groups{world}" if world > 1 else "single"),
-                decode_ms_per_token=ms_decode / n_new, first_tokens=tokens[:n_new])
+                decode_ms_per_token=ms_decode / n_new, greedy_tokens=out_ids[:n_new], first_steps=prints,
+                pinned_store_gib=32 * (tokens - CFG["n_init"] - CFG["n_local"]) // CFG["bs"] * 524288 / world / 2 ** 30)
 
 
 def main():
@@ -1216,6 +1233,7 @@ def main():
     ap.add_argument("--units", type=int, default=DEC["units"], help="memory units of the decode workload")
     ap.add_argument("--layers", type=int, default=DEC["layers"], help="layer memories that take turns in the decode workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="reference arm: skip the timing of the reference's Triton kernel")
     ap.add_argument("--device-store-mb", type=int, default=0,
                     help="decode workload alone: MiB per layer of device copy of the store (0 = pinned host store only)")
     ap.add_argument("--max-cached", type=int, default=CFG["max_cached"], help="max_cached_block (32 in the named config)")
@@ -1224,7 +1242,7 @@ def main():
     DEC["units"] = args.units
     DEC["layers"] = max(1, args.layers)
     if args.steps is None:
-        args.steps = 256 if args.workload == "decode" else 3
+        args.steps = 256 if args.workload == "decode" else (1 if args.workload == "model" else 3)
     if args.warmup is None:
         args.warmup = 136 if args.workload == "decode" else 3
     args.warmup = max(args.warmup, 3)  # fewer warm-up steps would time cold caches and first-use allocations
