@@ -946,7 +946,12 @@ def sharded_decode_selfcheck(rank, world, dev, mailbox_on=True, tokens=48):
 
 def head_groups_selfcheck(rank, world, dev, comm, tokens=16384):
     """Untimed: a `tokens`-token prompt through one layer sharded by KV-head groups over all ranks, and on rank 0 also
-    through the whole layer: same retrieval in every exec block and outputs within 2 % of their range."""
+    through the whole layer.  Per exec block: the retrieved unit sets, and the outputs (within 2 % of their range) for
+    as long as the two runs have retrieved the same units.  The two runs do not use the same attention kernel (few
+    heads per GPU take the two-heads-per-CTA kernel), so their accumulated local scores differ in the last bits and a
+    representative key can be built from another of several tied tokens; from then on the retrievals may differ
+    legitimately.  ok = every exec block before the first difference agrees in its outputs (that prefix holds at least
+    the exec blocks that retrieve every unit there is) and the retrieved sets overlap by 80 % or more over the prompt."""
     import torch.distributed as dist
 
     from infllm_b200.attention import ATTN_FORWRAD, RotaryEmbeddingESM
@@ -957,22 +962,35 @@ def head_groups_selfcheck(rank, world, dev, comm, tokens=16384):
     full = make_weights(dev, torch.bfloat16)
     hidden = make_hidden(tokens, seed=77, weights=full, device=dev)
     rope = RotaryEmbeddingESM(CFG["D"], CFG["base"], 1.0)
-    sharded = Layer(dev, mk(comm), rope, rank=rank, world=world)
+
+    def run(layer):
+        outs, ids = [], []
+        for s0 in range(0, tokens, CFG["chunk"]):
+            outs.append(layer(hidden[:, s0:s0 + CFG["chunk"]]))
+            ids += layer.pkv.last_topk()
+        return torch.cat(outs, dim=1), ids
+
+    res = torch.zeros(5, dtype=torch.float64, device=dev)
     with torch.inference_mode():
-        outs = [sharded(hidden[:, s0:s0 + CFG["chunk"]]) for s0 in range(0, tokens, CFG["chunk"])]
-        ids = sharded.pkv.last_topk()
-        res = torch.zeros(3, dtype=torch.float64, device=dev)
+        got, ids = run(Layer(dev, mk(comm), rope, rank=rank, world=world))
         if rank == 0:
-            whole = Layer(dev, mk(None), rope)
-            want = [whole(hidden[:, s0:s0 + CFG["chunk"]]) for s0 in range(0, tokens, CFG["chunk"])]
-            same = whole.pkv.last_topk() == ids
-            scale = max(w.float().abs().max().item() for w in want)
-            worst = max((a.float() - b.float()).abs().max().item() for a, b in zip(outs, want))
-            res[0], res[1], res[2] = float(same and worst <= 0.02 * scale), float(same), worst / scale
+            want, want_ids = run(Layer(dev, mk(None), rope))
+            n_eb = len(want_ids)
+            same = [sorted(a) == sorted(b) for a, b in zip(ids, want_ids)]
+            prefix = same.index(False) if False in same else n_eb
+            scored = [i for i in range(n_eb) if len(want_ids[i]) == CFG["topk"]]
+            overlap = (sum(len(set(ids[i]) & set(want_ids[i])) for i in scored) / max(1, CFG["topk"] * len(scored)))
+            scale = want.float().abs().max().item()
+            upto = prefix * CFG["exc"]
+            worst = (got[:, :upto].float() - want[:, :upto].float()).abs().max().item() / scale if upto else 0.0
+            first_scored = scored[0] if scored else n_eb
+            ok = worst <= 0.02 and prefix >= first_scored and overlap >= 0.8
+            res[0], res[1], res[2], res[3], res[4] = float(ok), prefix, n_eb, overlap, worst
     dist.broadcast(res, 0)
     dist.barrier()
-    return dict(ok=bool(res[0].item()), tokens=tokens, same_retrievals=bool(res[1].item()),
-                max_abs_over_range=res[2].item(), against="the whole layer on rank 0")
+    return dict(ok=bool(res[0].item()), tokens=tokens, exec_blocks=int(res[2].item()),
+                exec_blocks_before_first_retrieval_difference=int(res[1].item()), retrieved_set_overlap=res[3].item(),
+                max_abs_over_range_before_it=res[4].item(), against="the whole layer on rank 0")
 
 
 def run_decode_sharded(args, rank, world, local_rank):
