@@ -324,6 +324,11 @@ class UnitRangeShard:
             a.cand_off, a.cand_slot, a.cand_bytes = mb.cand_off, mb.cand_slot, mb.cand_bytes
             a.part_off, a.part_slot, a.part_bytes = mb.part_off, mb.part_slot, mb.part_bytes
             a.flag1_off, a.flag2_off, a.wait_us = mb.flag1, mb.flag2, mb.wait_us
+            # (the store's addresses change only when it grows, which drops this block)
+            a.d_block_k, a.d_scores, a.d_slot_table = p["block_k"], p["scores_buf"], p["slot_table"]
+            a.d_unit_ptrs, a.d_ticket = p["ptr_table"], p["ticket"]
+            first = self.rank == 0 and self.n_init > 0
+            a.d_init_k, a.d_init_v, a.init_len = (p["init_k"], p["init_v"], self.n_init) if first else (None, None, 0)
         E, G, r = self.length + 1, self.world, self.rank
         wlo = max(E - self.n_local, 0)
         W = E - wlo
@@ -331,12 +336,8 @@ class UnitRangeShard:
         self._share = (lo_, hi_)
         a.d_q, a.d_k, a.d_vin, a.q_hs, a.k_hs, a.v_hs = q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0)
         a.at = self.length - self.t0
-        a.d_block_k, a.d_scores, a.d_slot_table = p["block_k"], p["scores_buf"], p["slot_table"]
-        a.d_unit_ptrs, a.d_ticket = p["ptr_table"], p["ticket"]
         a.n_owned, a.id_lo = self.n_owned, self.lo
         a.share_at, a.share_len = lo_ - self.t0, hi_ - lo_
-        first = r == 0 and self.n_init > 0
-        a.d_init_k, a.d_init_v, a.init_len = (p["init_k"], p["init_v"], self.n_init) if first else (None, None, 0)
         last = r == G - 1 and wlo > self.frontier
         a.ovf_at, a.ovf_len = (self.frontier - self.t0, wlo - self.frontier) if last else (0, 0)
         a.d_out, a.seq = out.data_ptr(), mb.seq
@@ -442,6 +443,7 @@ class UnitRangeShard:
             ptrs[b - self.lo] = self._p["cache"] + slot * self.unit_bytes
         self.ptr_table = ptrs
         self._store_pointers()
+        self._token_args = None
 
 
 class PeerMailbox:
@@ -502,7 +504,8 @@ class ShardedDecodeMemory:
         # unit was not cached) and for the score columns of a sealing
         self.mailbox = mailbox if (distributed and mailbox is not None and mailbox.world > 1) else None
         self.redone = 0  # tokens that had to be run again (none since retrieved units are read wherever they live)
-        self._pending = None  # (event behind the token's status copy,) of the token whose retrieval is not applied yet
+        self._pending = None  # the event behind the status copy of the token whose retrieval is not applied yet
+        self._events = None
         self._last_ids = []
         if not distributed:
             assert [s.rank for s in self.shards] == list(range(self.shards[0].world)), "emulation needs every rank"
@@ -581,6 +584,8 @@ class ShardedDecodeMemory:
         order, and redoes the token through the collectives if any rank reports a unit that was not cached."""
         s, mb, lib = self.shards[0], self.mailbox, _lib.lib
         p, H, D = s._p, s.H, s.D
+        if self._events is None:
+            self._events = (torch.cuda.Event(), torch.cuda.Event())
         if mb.seq == 0 and self.distributed:  # the first exchange: nobody waits on a rank that is still setting up
             import torch.distributed as dist
 
@@ -610,7 +615,7 @@ class ShardedDecodeMemory:
             s.h_status.copy_(s.d_status, non_blocking=True)
         # the host does not wait: the status words and the retrieval are read when the next token arrives (or when
         # somebody asks for last_ids), and the LRU order is advanced then
-        self._pending = torch.cuda.Event()
+        self._pending = self._events[mb.seq & 1]
         self._pending.record()
         sealing = s.finish()
         if sealing is not None:

@@ -90,9 +90,19 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
                        const KvSeg* segs, const int32_t* seg_q, float* part_o, float* part_lse, int max_parts,
                        int* n_parts_out, int logit_seg, float* logits, int dtype, cudaStream_t s,
                        const DecodeIndirect* ind);
+// Optional first step of the merge: wait (bounded) until `world` senders' flag words show `seq` — the partials being
+// merged were put into this GPU's mailbox by peers.  A flag that does not arrive within `limit` polls leaves
+// 1 + its rank in *err and the kernel writes nothing.
+struct MergeWait {
+  const volatile uint32_t* flags = nullptr;
+  uint32_t seq = 0, limit = 0;
+  int32_t world = 0;
+  int* err = nullptr;
+};
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
                      int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
-                     float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps = 0, int64_t lse_ps = 0);
+                     float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps = 0, int64_t lse_ps = 0,
+                     const MergeWait* wait = nullptr);
 int attn_colsum_launch(const void* q, int64_t q_hs, int64_t q_ts, const void* k, int64_t k_hs, int64_t k_ts,
                        int n_heads, int n_kv_heads, int64_t lq, int64_t lk, int head_dim, int mask_mode,
                        int64_t mask_offset, int64_t mask_size, const float* lse, float* score, int64_t score_hs,

@@ -298,12 +298,28 @@ __global__ void __launch_bounds__(1024)
 lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_part, int n_heads,
                  int head_dim, T* __restrict__ out, int64_t o_hs, float* __restrict__ lse,
                  const float* __restrict__ logits, int64_t logit_len, float* __restrict__ score, int64_t score_hs,
-                 const int32_t* __restrict__ skip, int64_t o_ps, int64_t lse_ps) {
+                 const int32_t* __restrict__ skip, int64_t o_ps, int64_t lse_ps, const MergeWait wait) {
   extern __shared__ float s_w[];  // n_part weights
   __shared__ float s_num[kMergeGroups][128];
   __shared__ float s_mx, s_den;
-  if (skip && *skip) return;  // the partials were not written: a retrieved unit was not cached
   const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (wait.flags) {  // the partials come from peers: every CTA waits for every sender's flag, with a bound
+    bool ok = true;
+    if (tid < wait.world) {
+      uint32_t i = 0;
+      while (wait.flags[tid] != wait.seq) {
+        if (++i > wait.limit) {
+          ok = false;
+          break;
+        }
+        __nanosleep(200);
+      }
+      if (!ok) atomicExch(wait.err, 1 + tid);
+      __threadfence_system();
+    }
+    if (__syncthreads_or(!ok)) return;  // a sender did not arrive: nothing is written
+  }
+  if (skip && *skip) return;  // the partials were declared invalid by whoever produced them
   const int grp = tid / head_dim, d = tid % head_dim, ngrp = blockDim.x / head_dim;
   const float* po = part_o + (int64_t)h * head_dim + d;
   float pv[kMergeUnroll];
@@ -428,7 +444,9 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
 
 int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int n_heads, int head_dim, void* out,
                      int64_t o_hs, float* lse, int dtype, cudaStream_t s, const float* logits, int64_t logit_len,
-                     float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps, int64_t lse_ps) {
+                     float* score, int64_t score_hs, const int32_t* skip, int64_t o_ps, int64_t lse_ps,
+                     const MergeWait* wait) {
+  const MergeWait w = wait ? *wait : MergeWait{};
   if (o_ps <= 0) o_ps = (int64_t)n_heads * head_dim;
   if (lse_ps <= 0) lse_ps = n_heads;
   if (n_part <= 0) return fail(INFLLM_E_BADARG, "lse_merge: no partials");
@@ -438,12 +456,12 @@ int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int
   if (dtype == INFLLM_F32) {
     lse_merge_kernel<float><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
         part_o, part_lse, n_part, n_heads, head_dim, (float*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
-        o_ps, lse_ps);
+        o_ps, lse_ps, w);
   } else {
     INFLLM_DISPATCH_DTYPE(dtype, T, {
       lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
           part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
-          o_ps, lse_ps);
+          o_ps, lse_ps, w);
     });
   }
   INFLLM_LAUNCH_OK("lse_merge_kernel");

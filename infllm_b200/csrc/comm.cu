@@ -167,6 +167,70 @@ __global__ void peer_wait_kernel(const volatile uint32_t* flags, uint32_t seq, i
   }
 }
 
+// The candidate exchange of a sharded token as ONE kernel of one CTA: put this rank's message into every peer's
+// mailbox and raise the flags, wait (bounded) for every sender's flag here, rank the gathered candidates.  Nobody
+// waits before it has put, so the ranks cannot block one another.
+__device__ void rank_candidates(const int32_t* __restrict__ cand, int64_t sender_stride, int world, int k,
+                                int32_t* __restrict__ out_ids, float* s_score, int32_t* s_id);
+
+__global__ void __launch_bounds__(256)
+exchange_rank_kernel(const uint4* __restrict__ src, int n16, const __grid_constant__ PeerList peers, int world, uint32_t seq,
+                     const volatile uint32_t* flags, uint32_t limit, int* err, int32_t* clear_word,
+                     const int32_t* __restrict__ cand, int64_t sender_stride, int k, int32_t* __restrict__ out_ids) {
+  __shared__ float s_score[1024];
+  __shared__ int32_t s_id[1024];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < world * n16; i += blockDim.x) reinterpret_cast<uint4*>(peers.dst[i / n16])[i % n16] = src[i % n16];
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world) {
+    volatile uint32_t* f = peers.flag[tid];
+    *f = seq;
+  }
+  if (clear_word && tid == 0) *clear_word = 0;
+  bool ok = true;
+  if (tid < world) {
+    uint32_t i = 0;
+    while (flags[tid] != seq) {
+      if (++i > limit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!ok) atomicExch(err, 1 + tid);
+    __threadfence_system();
+  }
+  if (__syncthreads_or(!ok)) {  // the exchange failed: no retrieval
+    for (int i = tid; i < k; i += blockDim.x) out_ids[i] = -1;
+    return;
+  }
+  rank_candidates(cand, sender_stride, world, k, out_ids, s_score, s_id);
+}
+
+__device__ void rank_candidates(const int32_t* __restrict__ cand, int64_t sender_stride, int world, int k,
+                                int32_t* __restrict__ out_ids, float* s_score, int32_t* s_id) {
+  const int n = world * k;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int32_t* c = cand + (int64_t)(i / k) * sender_stride;
+    s_score[i] = __int_as_float(__ldcv(c + i % k));  // written by peers a moment ago: not through a stale cache line
+    s_id[i] = __ldcv(c + k + i % k);
+  }
+  for (int i = threadIdx.x; i < k; i += blockDim.x) out_ids[i] = -1;  // fewer than k real candidates: padding
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = s_score[i];
+    const int32_t id = s_id[i];
+    if (id < 0) continue;
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const int32_t oj = s_id[j];
+      rank += oj >= 0 && (s_score[j] > v || (s_score[j] == v && oj < id));
+    }
+    if (rank < k) out_ids[rank] = id;
+  }
+}
+
 // the k best of world * k gathered candidates [sender][score bits (k) | ids (k)]: descending score, ties to the
 // lower id, ids < 0 are padding; one CTA
 __global__ void __launch_bounds__(256)
@@ -331,10 +395,22 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   int* err = a->d_status + a->topk;
   int32_t* any_miss = a->d_status + a->topk + 1;
   int32_t* miss_word = reinterpret_cast<int32_t*>(a->d_pack + (int64_t)H * (D + 1));
-  INFLLM_TRY(infllm_mailbox_put(mb, a->d_cand, a->cand_bytes, a->cand_off, a->cand_slot, a->flag1_off, a->seq, stream));
-  INFLLM_TRY(infllm_mailbox_wait(mb, a->flag1_off, a->seq, a->wait_us, err, 0, 0, -1, nullptr, miss_word, stream));
-  INFLLM_TRY(infllm_topk_pairs(reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4,
-                               mb->world, a->topk, a->d_status, err, stream));
+  const uint32_t limit = (uint32_t)((a->wait_us > 0 ? a->wait_us : 100000) * 5ll);  // polls of ~200 ns
+  {
+    if (a->cand_bytes % 16 || a->cand_bytes > a->cand_slot || mb->world * a->topk > 1024)
+      return fail(INFLLM_E_BADARG, "shard_token_run: candidate message of %lld bytes", (long long)a->cand_bytes);
+    PeerList pl{};
+    for (int r = 0; r < mb->world; ++r) {
+      if (!mb->peer[r]) return fail(INFLLM_E_BADARG, "shard_token_run: rank %d is not mapped (infllm_mailbox_open)", r);
+      pl.dst[r] = (char*)mb->peer[r] + a->cand_off + (int64_t)mb->rank * a->cand_slot;
+      pl.flag[r] = reinterpret_cast<uint32_t*>((char*)mb->peer[r] + a->flag1_off) + mb->rank;
+    }
+    exchange_rank_kernel<<<1, 256, 0, s>>>(
+        reinterpret_cast<const uint4*>(a->d_cand), (int)(a->cand_bytes / 16), pl, mb->world, a->seq,
+        reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag1_off), limit, err, miss_word,
+        reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4, a->topk, a->d_status);
+    INFLLM_LAUNCH_OK("exchange_rank_kernel");
+  }
   // 4. attention: [retrieved units, resolved on the device | window share | sink | overflow]
   KvSeg segs[kMaxSeg];
   int32_t qsel[kMaxSeg];
@@ -368,12 +444,15 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
                               INFLLM_F32, s, nullptr, 0, nullptr, 0, nullptr));
   // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores
   INFLLM_TRY(infllm_mailbox_put(mb, a->d_pack, a->part_bytes, a->part_off, a->part_slot, a->flag2_off, a->seq, stream));
-  INFLLM_TRY(infllm_mailbox_wait(mb, a->flag2_off, a->seq, a->wait_us, err, a->part_off, a->part_slot,
-                                 (int64_t)H * (D + 1) * 4, any_miss, nullptr, stream));
+  // the final merge waits for the peers' partials itself (every CTA polls the flag words, with the bound)
+  (void)any_miss;
+  MergeWait mw;
+  mw.flags = reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag2_off);
+  mw.seq = a->seq; mw.limit = limit; mw.world = mb->world; mw.err = err;
   const float* parts_g = reinterpret_cast<const float*>((char*)mb->local + a->part_off);
   INFLLM_TRY(lse_merge_launch(parts_g, parts_g + (int64_t)H * D, mb->world, H, D, a->d_out, D, a->d_lse, a->dtype, s,
                               a->share_len > 0 ? a->d_logits : nullptr, a->share_len, a->d_score + a->share_at, a->cap,
-                              any_miss, a->part_slot / 4, a->part_slot / 4));
+                              nullptr, a->part_slot / 4, a->part_slot / 4, &mw));
   // 6. retrieval and status words for the host
   INFLLM_CUDA_OK(cudaMemcpyAsync(a->h_status, a->d_status, (a->topk + 4) * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   return INFLLM_OK;
