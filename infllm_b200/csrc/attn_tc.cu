@@ -566,26 +566,33 @@ __global__ void __launch_bounds__(576, 1) attn_tc2_kernel(const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
-// attn_tc3_kernel: one 128-query tile of one head per CTA and the softmax of attn_tc_kernel (eight warps on one key
-// tile, two threads per query row), but P never touches shared memory.  Clock stamps in attn_tc_kernel show that
-// its tile period (about 3000 cycles) is set as much by shared-memory bandwidth as by the softmax: a 128x128x16
-// product with both operands in shared memory reads 8 KB per 64 cycles, which is all the 128 B/clk an SM has, and
-// a key tile moves 224 KB through shared memory (Q, K and P, V operand reads, the TMA fill of K and V, the P store)
-// - 1750 cycles at best, and the products slow down to 130-160 cycles each.  Here P = exp2(S - m) goes back into
-// the TMEM columns of its S buffer as packed 16-bit pairs and is the A operand of the P V product from there
-// (160 KB per tile), and there are three S/P buffers in TMEM, so that S of tile t+2 does not have to wait for the P V
-// product of tile t.  Eleven warps: eight softmax warps, the TMA producer, and one issuing thread per product (one
-// thread for both was the longest serial chain of a tile).  Every second pair of exponentials is a cubic on the FMA
-// pipe.  88 us per exec block of the 128K prefill against 104 us for attn_tc_kernel.
+// attn_tc3_kernel: one 128-query tile of one head per CTA; P never touches shared memory.  P = exp2(S - m) goes back
+// into the TMEM columns of its S buffer as packed 16-bit pairs and is the A operand of the P V product from there
+// (a key tile moves 160 KB through shared memory: Q, K, V operand reads and the TMA fill of K and V), and there are
+// three S/P buffers in TMEM, so that S runs a tile ahead of the softmax.  Eleven warps: eight softmax warps, the TMA
+// producer, and one issuing thread per product (one thread for both was the longest serial chain of a tile).
+// The softmax warps read S in the 16-lane shape: warps w and w+4 share a TMEM lane quarter and take 16 of its rows
+// each with all 128 key columns, a row is spread over the four threads of a quad, so a row maximum is two shuffles
+// and no thread waits for another warp.  Every fourth pair of exponentials is a cubic on the FMA pipe.  The producer
+// asks for K one tile ahead of V (the V buffer frees late in a tile's cycle and K(t+1) queued behind that wait).
+// What the clock stamps of one CTA say (cycles per 128-key tile, 131072-token prefill): the period is 2100-2200 and
+// it is the softmax warps' (1700 of work, 400 of waits and loop); S is ready 2000 cycles before they come for it; a
+// K or V tile takes 900-1000 cycles from request to arrival, which is also what the loads alone allow (a CTA whose
+// softmax does nothing and whose P V products are left out still needs 1600 per tile: four 16 KB boxes at about 40
+// bytes per clock and SM from L2).  Tried and not kept: a second softmax team on alternate tiles with its own S
+// buffer and accumulator (the chain S -> softmax -> P V -> next S of one team is as long as two tiles; 94 us),
+// asking TMEM for the next tile's scores before this tile's exponentials (111 us), an L2 prefetch of the key tiles
+// four to eight tiles ahead (no change), all exponentials or half of them on the special-function unit (87, 86 us).
+// 83 us per exec block of the 128K prefill.
 namespace tc3 {
 constexpr int kQ = 0;
 constexpr int kK = kQ + 2 * kSubTileBytes;       // two stages
 constexpr int kV = kK + 4 * kSubTileBytes;       // two stages
 constexpr int kBar = kV + 4 * kSubTileBytes;
-constexpr int kXmax = kBar + 256;                // row maxima: 2 tile parities x 2 halves x 128 rows of fp32
-constexpr int kXsum = kXmax + 2048;              // row sums: 2 halves x 128 rows
-constexpr int kXflag = kXsum + 1024;             // progress counters: 2 halves x 128 rows
-constexpr int kTotal = kXflag + 1024;
+constexpr int kXmax = kBar + 256;                // reference maxima of the 128 rows, for the epilogue's layout
+constexpr int kXsum = kXmax + 512;               // row sums of the 128 rows
+constexpr int kTotal = kXsum + 512;
+constexpr int kPolyEvery = 4;
 enum { T3_Q_FULL = 0, T3_Q_EMPTY, T3_K_FULL0, T3_K_FULL1, T3_K_EMPTY0, T3_K_EMPTY1, T3_V_FULL0, T3_V_FULL1, T3_V_EMPTY0,
        T3_V_EMPTY1, T3_S_FULL0, T3_S_FULL1, T3_S_FULL2, T3_P_FULL0, T3_P_FULL1, T3_P_FULL2, T3_PV_DONE0, T3_PV_DONE1, T3_PV_DONE2,
        T3_O_FULL, T3_N_BARS };
@@ -603,7 +610,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kBar + T3_N_BARS * 8 + 8);
   float* xmax = reinterpret_cast<float*>(smem + kXmax);
   float* xsum = reinterpret_cast<float*>(smem + kXsum);
-  volatile int* xflag = reinterpret_cast<volatile int*>(smem + kXflag);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -616,7 +622,6 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (threadIdx.x < 256) xflag[threadIdx.x] = 0;
   if (warp == 9) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -632,9 +637,28 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
 
   if (warp == 8) {
     // ======================================================================== TMA producer
+    // K runs one tile ahead of V: the buffer of K(t+1) is free as soon as S(t-1) has been formed, that of V(t) only
+    // when the P V product of tile t-2 has run, late in the tile's cycle; asked for in tile order, K(t+1) queued
+    // behind that wait and S(t+1) was not ready when the softmax warps came for it.
     if (lane == 0) {
       int it = 0, sidx = 0;
       bool ok = true;
+      struct { int it, tok, c3, map; } pend = {-1, 0, 0, 0};  // the V tile that has not been asked for yet
+      auto load_v = [&]() {
+        const int b = pend.it & 1;
+        if (pend.it >= 2) ok = wait_or_abort(bar(T3_V_EMPTY0 + b), ((pend.it >> 1) - 1) & 1, abort_flag, P.err, 602);
+        if (!ok) return;
+        const uint32_t dv = sV + b * 2 * kSubTileBytes;
+        mbar_expect_tx(bar(T3_V_FULL0 + b), 2 * kSubTileBytes);
+        if (pend.c3 < 0) {
+          tma_load_3d(dv, &P.maps[pend.map], bar(T3_V_FULL0 + b), 0, pend.tok, hkv);
+          tma_load_3d(dv + kSubTileBytes, &P.maps[pend.map], bar(T3_V_FULL0 + b), 64, pend.tok, hkv);
+        } else {
+          tma_load_4d(dv, &P.maps[pend.map], bar(T3_V_FULL0 + b), 0, pend.tok, hkv, pend.c3);
+          tma_load_4d(dv + kSubTileBytes, &P.maps[pend.map], bar(T3_V_FULL0 + b), 64, pend.tok, hkv, pend.c3);
+        }
+        pend.it = -1;
+      };
       for (int st = 0; st < P.n_stage && ok; ++st) {
         const TcStage& S = P.stage[st];
         int64_t vis_lo, vis_hi;
@@ -656,7 +680,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
               const int b = it & 1, tok = G.tok0 + t * kTile;
               if (it >= 2) ok = wait_or_abort(bar(T3_K_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 601);
               if (!ok) break;
-              const uint32_t dk = sK + b * 2 * kSubTileBytes, dv = sV + b * 2 * kSubTileBytes;
+              const uint32_t dk = sK + b * 2 * kSubTileBytes;
               mbar_expect_tx(bar(T3_K_FULL0 + b), 2 * kSubTileBytes);
               if (G.c3_k < 0) {
                 tma_load_3d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv);
@@ -665,21 +689,15 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
                 tma_load_4d(dk, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 0, tok, hkv, G.c3_k);
                 tma_load_4d(dk + kSubTileBytes, &P.maps[G.map_k], bar(T3_K_FULL0 + b), 64, tok, hkv, G.c3_k);
               }
-              if (it >= 2) ok = wait_or_abort(bar(T3_V_EMPTY0 + b), ((it >> 1) - 1) & 1, abort_flag, P.err, 602);
+              if (pend.it >= 0) load_v();
               if (!ok) break;
-              mbar_expect_tx(bar(T3_V_FULL0 + b), 2 * kSubTileBytes);
-              if (G.c3_v < 0) {
-                tma_load_3d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv);
-                tma_load_3d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 64, tok, hkv);
-              } else {
-                tma_load_4d(dv, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 0, tok, hkv, G.c3_v);
-                tma_load_4d(dv + kSubTileBytes, &P.maps[G.map_v], bar(T3_V_FULL0 + b), 64, tok, hkv, G.c3_v);
-              }
+              pend.it = it, pend.tok = tok, pend.c3 = G.c3_v, pend.map = G.map_v;
             }
           }
           seg_j0 += G.len;
         }
       }
+      if (ok && pend.it >= 0) load_v();
       if (!ok) {
         // give loads that are still in flight a bounded chance to land before the CTA's memory goes away
         for (int b = 0; b < 2; ++b) {
@@ -743,7 +761,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A = P from TMEM: keys 0-63 in the buffer's columns [0,32), keys 64-127 in [64,96)
-            const uint32_t a_t = tmem + b3 * 128 + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4));
+            const uint32_t a_t = tmem + b3 * 128 + 8 * ks;
             mma_ts(tO, a_t, vd0[b] + (uint64_t)((ks * 2048) >> 4), idesc_pv, (ip > 0) || (ks > 0));
           }
           tc_commit(bar(T3_V_EMPTY0 + b));
@@ -752,17 +770,18 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         if (ok) tc_commit(bar(T3_O_FULL));
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ===================================================================== softmax / epilogue
-    // Eight warps: warp w and warp w+4 own the same 32 query rows (TMEM lanes) and split the tile's 128 key columns
-    // in halves; they exchange their partial row maxima through shared memory.
-    const int quad = warp & 3, half = warp >> 2;
-    const int row = quad * 32 + lane;
-    const int64_t qi = i0 + row;
-    const bool row_valid = qi < P.lq;
-    const uint32_t lane_base = ((uint32_t)(quad * 32)) << 16;
-    const int col0 = half * 64;
-    float m_ref = -INFINITY, l_part = 0.f;  // m_ref in the scaled log2 domain; l over this thread's columns
+    // Eight warps: warps w and w+4 share a TMEM lane quarter and take 16 of its query rows each, with all 128 key
+    // columns of those rows: the 16x256b load spreads a row over the four threads of a quad, so a row maximum is two
+    // shuffles and no thread waits for another warp.  A thread holds rows r and r+8, two columns of every block of 8.
+    const int quad = warp & 3, rh = warp >> 2;
+    const int rbase = quad * 32 + rh * 16 + (lane >> 2);
+    const int cq = 2 * (lane & 3);
+    const uint32_t lane_base = ((uint32_t)(quad * 32 + rh * 16)) << 16;
+    const int64_t qrow[2] = {i0 + rbase, i0 + rbase + 8};
+    const bool valid[2] = {qrow[0] < P.lq, qrow[1] < P.lq};
+    float m_ref[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
     int it = 0;
     bool ok = true;
     for (int st = 0; st < P.n_stage && ok; ++st) {
@@ -770,14 +789,18 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
       int64_t vis_lo, vis_hi;
       visible_key_range(S.mask_mode, S.mask_offset, S.mask_size, i0, i0 + rows_q - 1, S.lk, &vis_lo, &vis_hi);
       if (vis_lo > vis_hi) continue;
-      int64_t jlo = 0, jhi = S.lk - 1;  // keys of this stage visible to this thread's query row
-      if (S.mask_mode == INFLLM_MASK_WINDOW) {
-        jlo = qi + S.mask_offset - S.mask_size + 1;
-        jhi = qi + S.mask_offset;
-      } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
-        jhi = qi + S.mask_offset - S.mask_size;
+      int64_t jlo[2], jhi[2];  // keys of this stage visible to this thread's two query rows
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        jlo[r] = 0, jhi[r] = S.lk - 1;
+        if (S.mask_mode == INFLLM_MASK_WINDOW) {
+          jlo[r] = qrow[r] + S.mask_offset - S.mask_size + 1;
+          jhi[r] = qrow[r] + S.mask_offset;
+        } else if (S.mask_mode == INFLLM_MASK_COMPLEMENT) {
+          jhi[r] = qrow[r] + S.mask_offset - S.mask_size;
+        }
+        if (!valid[r]) jhi[r] = -1, jlo[r] = 0;
       }
-      if (!row_valid) jhi = -1, jlo = 0;
       int64_t seg_j0 = 0;
       for (int sg = S.seg_begin; sg < S.seg_end && ok; ++sg) {
         const TcSeg& G = P.seg[sg];
@@ -790,83 +813,87 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
             if (!ok) break;
             tc_fence_after();
             float s[64];
-            tmem_ld32(tS + col0, reinterpret_cast<uint32_t*>(s));
-            tmem_ld32(tS + col0 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+            tmem_ld_16x256b_x16(tS, reinterpret_cast<uint32_t*>(s));
             tmem_wait_ld();
-            // visible columns of this tile for this row: [c_lo, c_hi] in this thread's 64 columns
             const int64_t jt = seg_j0 + (int64_t)t * kTile;
             const int64_t lim = seg_j0 + G.len - 1;  // last key of the segment
-            const int64_t a = jlo > jt ? jlo : jt, e = jhi < lim ? jhi : lim;
-            const int c_lo = (int)(a - jt) - col0;
-            const int c_hi = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt)) - col0;
-            if (!(c_lo <= 0 && c_hi >= 63)) {
+            int c_lo[2], c_hi[2];
 #pragma unroll
-              for (int c = 0; c < 64; ++c) s[c] = (c >= c_lo && c <= c_hi) ? s[c] : -INFINITY;
+            for (int r = 0; r < 2; ++r) {
+              const int64_t a = jlo[r] > jt ? jlo[r] : jt, e = jhi[r] < lim ? jhi[r] : lim;
+              c_lo[r] = (int)(a - jt);
+              c_hi[r] = (int)((e - jt) > (kTile - 1) ? (kTile - 1) : (e - jt));
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (!(c_lo[0] <= 0 && c_hi[0] >= kTile - 1 && c_lo[1] <= 0 && c_hi[1] >= kTile - 1)) {
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
-              mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
-              mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
-              mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
-              mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
-            }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the other half's maximum of the same row
-            xmax[(it & 1) * 256 + half * 128 + row] = mx;
-            __threadfence_block();
-            xflag[half * 128 + row] = it + 1;
-            ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], it + 1, abort_flag, P.err, 621));
-            if (!ok) break;
-            mx = fmaxf(mx, xmax[(it & 1) * 256 + (half ^ 1) * 128 + row]) * P.scale_log2;
-            // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
-            float alpha = 1.f;
-            bool resc = false;
-            if (mx > m_ref) {
-              if (m_ref == -INFINITY) {
-                m_ref = mx;  // nothing accumulated for this row yet
-              } else if (mx - m_ref > 8.f) {
-                alpha = ex2_approx(m_ref - mx);
-                l_part *= alpha;
-                m_ref = mx;
-                resc = true;
+              for (int i = 0; i < 64; ++i) {
+                const int col = 8 * (i >> 2) + cq + (i & 1), r = (i >> 1) & 1;
+                s[i] = (col >= c_lo[r] && col <= c_hi[r]) ? s[i] : -INFINITY;
               }
             }
-            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-            uint32_t pk[32];
-            float2 rs01 = make_float2(0.f, 0.f), rs23 = make_float2(0.f, 0.f);
-            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2), nm2 = make_float2(neg_m, neg_m);
+            float mxa[2] = {-INFINITY, -INFINITY}, mxb[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-              const float2 a01 = ffma2(s[c], s[c + 1], sc2, nm2), a23 = ffma2(s[c + 2], s[c + 3], sc2, nm2);
-              const float2 p01 = make_float2(ex2_approx(a01.x), ex2_approx(a01.y));
-              const float2 p23 = ex2_poly2(a23);  // every second pair off the special-function unit
-              rs01 = fadd2(rs01, p01);
-              rs23 = fadd2(rs23, p23);
-              typename Act<T>::T2 v01 = Act<T>::from_f2(p01.x, p01.y), v23 = Act<T>::from_f2(p23.x, p23.y);
-              pk[c >> 1] = *reinterpret_cast<uint32_t*>(&v01);
-              pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&v23);
+            for (int j = 0; j < 16; j += 2) {
+              mxa[0] = fmax3(mxa[0], s[4 * j], s[4 * j + 1]);
+              mxa[1] = fmax3(mxa[1], s[4 * j + 2], s[4 * j + 3]);
+              mxb[0] = fmax3(mxb[0], s[4 * j + 4], s[4 * j + 5]);
+              mxb[1] = fmax3(mxb[1], s[4 * j + 6], s[4 * j + 7]);
             }
-            l_part += (rs01.x + rs01.y) + (rs23.x + rs23.y);
+            float alpha[2] = {1.f, 1.f}, neg_m[2];
+            bool resc = false;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              float mx = fmaxf(mxa[r], mxb[r]);
+              mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+              mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2)) * P.scale_log2;
+              // lazy rescaling: the reference maximum only moves when the row maximum grew by more than 2^8
+              if (mx > m_ref[r]) {
+                if (m_ref[r] == -INFINITY) {
+                  m_ref[r] = mx;  // nothing accumulated for this row yet
+                } else if (mx - m_ref[r] > 8.f) {
+                  alpha[r] = ex2_approx(m_ref[r] - mx);
+                  l_part[r] *= alpha[r];
+                  m_ref[r] = mx;
+                  resc = true;
+                }
+              }
+              neg_m[r] = m_ref[r] == -INFINITY ? 0.f : -m_ref[r];
+            }
+            uint32_t pk[32];
+            float2 rs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            const float2 sc2 = make_float2(P.scale_log2, P.scale_log2);
+            const float2 nm2[2] = {make_float2(neg_m[0], neg_m[0]), make_float2(neg_m[1], neg_m[1])};
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {  // pair k: block k/2, row k%2 - which is where the 16x128b store wants it
+              const int r = k & 1;
+              const float2 a = ffma2(s[2 * k], s[2 * k + 1], sc2, nm2[r]);
+              float2 p;
+              if ((k % kPolyEvery) == kPolyEvery - 1) {
+                p = ex2_poly2(a);  // one pair in kPolyEvery off the special-function unit
+              } else {
+                p = make_float2(ex2_approx(a.x), ex2_approx(a.y));
+              }
+              rs[r] = fadd2(rs[r], p);
+              typename Act<T>::T2 v = Act<T>::from_f2(p.x, p.y);
+              pk[k] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            l_part[0] += rs[0].x + rs[0].y;
+            l_part[1] += rs[1].x + rs[1].y;
             if (__any_sync(0xffffffffu, resc) && it >= 1) {
-              // O holds the products up to tile it-1: wait for the last of them, then scale this thread's 64 columns
+              // O holds the products up to tile it-1: wait for the last of them, then scale this warp's 16 rows
               ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_PV_DONE0 + ((it - 1) % 3)), ((it - 1) / 3) & 1, abort_flag,
                                                          P.err, 622));
               if (!ok) break;
               tc_fence_after();
+              uint32_t o[64];
+              tmem_ld_16x256b_x16(tO + lane_base, o);
+              tmem_wait_ld();
 #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tO + lane_base + col0 + c * 32, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-                tmem_st32(tO + lane_base + col0 + c * 32, o);
-              }
+              for (int i = 0; i < 64; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[(i >> 1) & 1]);
+              tmem_st_16x256b_x16(tO + lane_base, o);
             }
-            // this thread's 64 keys of P, packed, over the first half of the S columns it has consumed:
-            // keys 0-63 -> buffer columns [0,32), keys 64-127 -> [64,96)
-            tmem_st32(tS + col0, pk);
+            // P, packed, over the first 64 columns of the S buffer: column c holds keys 2c, 2c+1
+            tmem_st_16x128b_x16(tS, pk);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(T3_P_FULL0 + b3));
@@ -875,12 +902,24 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
         seg_j0 += G.len;
       }
     }
-    // ---- epilogue: O / l -> out, log-sum-exp (each half writes its 64 output columns)
-    xsum[half * 128 + row] = l_part;
-    __threadfence_block();
-    xflag[half * 128 + row] = kPairDone;
-    if (ok) ok = __all_sync(0xffffffffu, pair_wait(&xflag[(half ^ 1) * 128 + row], kPairDone, abort_flag, P.err, 623));
-    const float l_sum = l_part + xsum[(half ^ 1) * 128 + row];
+    // ---- epilogue: row sums and reference maxima go through shared memory to the thread-per-row layout, in which
+    // each warp writes 64 output columns of 32 rows
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float l = l_part[r];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if ((lane & 3) == 0) {
+        xsum[rbase + 8 * r] = l;
+        xmax[rbase + 8 * r] = m_ref[r];
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const int half = warp >> 2, row = quad * 32 + lane, col0 = half * 64;
+    const int64_t qi = i0 + row;
+    const bool row_valid = qi < P.lq;
+    const uint32_t row_base = ((uint32_t)(quad * 32)) << 16;
+    const float l_sum = xsum[row], m_row = xmax[row];
     if (ok && it >= 1) ok = __all_sync(0xffffffffu, wait_or_abort(bar(T3_O_FULL), 0, abort_flag, P.err, 624));
     if (ok) {
       tc_fence_after();
@@ -890,7 +929,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
       for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
         if (it >= 1) {
-          tmem_ld32(tO + lane_base + col0 + c * 32, o);
+          tmem_ld32(tO + row_base + col0 + c * 32, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -911,7 +950,7 @@ __global__ void __launch_bounds__(352, 1) attn_tc3_kernel(const __grid_constant_
           }
         }
       }
-      if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
+      if (half == 0 && row_valid && P.lse) P.lse[(int64_t)h * P.lq + qi] = l_sum > 0.f ? m_row + log2f(l_sum) : -INFINITY;
     }
   }
   // ---- teardown
