@@ -645,7 +645,7 @@ def run_decode(args, rank, world, local_rank, device_store_mb=0):
         del mem
         cms.append(cm)
         dirs.append(direction)
-    total = (args.warmup + 2 * args.steps + 2) * n_layers
+    total = (args.warmup + 3 * args.steps + 2) * n_layers
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     lean = torch.stack([dirs[i % n_layers] for i in range(total)])[:, None]  # (total, 1, H, 1, D)
     qs = (torch.randn((total, 1, H, 1, D), generator=g, device=dev) + 3.0 * lean).to(torch.bfloat16)
@@ -700,19 +700,22 @@ def run_decode(args, rank, world, local_rank, device_store_mb=0):
     with torch.inference_mode():
         for _ in range(args.warmup):
             step_device()
-        for cm in cms:
-            cm.profile(True)
-            cm.get_profile()
         info0 = [cm.info() for cm in cms]
         clk_p, clk_f = sample_clocks_start(local_rank)
         l0 = _lib.lib.infllm_launch_count()
         ms = timed(step_device, args.steps)
         launches = _lib.lib.infllm_launch_count() - l0
+        info1 = [cm.info() for cm in cms]
+        # the kernels' own durations: the same K steps once more with CUDA events around the scoring and the
+        # attention of every token.  Kept out of `value`'s region: four event records per 50 us token cost 14 us of it
+        for cm in cms:
+            cm.profile(True)
+            cm.get_profile()
+        ms_events = timed(step_device, args.steps)
         prof = merged([cm.get_profile() for cm in cms])
         for cm in cms:
             cm.profile(False)
         clocks = sample_clocks_stop(clk_p, clk_f)
-        info1 = [cm.info() for cm in cms]
         step_host()
         ms_e2e = timed(step_host, args.steps)
     _, hbm_peak, which = measured_peaks()
@@ -741,7 +744,9 @@ def run_decode(args, rank, world, local_rank, device_store_mb=0):
         roofline=dict(bound="hbm", kernel="block_score_topk_kernel (unit scoring + top-k)", achieved=achieved,
                       peak=hbm_peak, unit="GB/s", frac=(achieved / hbm_peak if achieved else None), traffic=None,
                       peak_source=f"hbm_gbs of {which}", launches=int(topk_n),
-                      us_per_launch=1e3 * topk_ms / max(topk_n, 1), bytes_per_launch=topk_bytes / max(topk_n, 1)),
+                      us_per_launch=1e3 * topk_ms / max(topk_n, 1), bytes_per_launch=topk_bytes / max(topk_n, 1),
+                      timed_in="a second pass of the same K steps with CUDA events around the kernel on its stream",
+                      us_per_token_with_events=1e3 * ms_events / per_layer),
         kernels={k: dict(ms=v[0], launches=v[2], work=v[1]) for k, v in prof.items()},
         decode_attention=dict(kernels="attn_decode_kernel + lse_merge_kernel",
                               achieved_gbs=(dec_bytes / (dec_ms / 1e3) / 1e9 if dec_ms > 0 else None),

@@ -439,6 +439,26 @@ int infllm_shard_token_run(const infllm_shard_token* args, infllm_mailbox* mailb
  * host-to-device copy (context_manager.py:57-71) for callers that keep their own cache. */
 int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes, void* stream);
 
+/* The cache of a caller that keeps its own units (the unit-range shard of the sharded decode), in one call per
+ * retrieval: of `ids` (n <= 256; negative entries and ids outside [id_lo, id_lo + n_owned) are skipped) the LRU
+ * table plans the evictions and takes the stamp load_count (context_manager.py:246-265, 495-515), units that are
+ * not cached go from the pinned store into free slots on `stream` (MemoryUnit.load, context_manager.py:57-71), and
+ * the device tables learn the changes (slot, or -1; address of the slot, or of the unit in the pinned store).
+ * All fields are the caller's; the library keeps nothing between calls. */
+typedef struct infllm_shard_cache {
+  struct infllm_lru* lru;
+  int32_t* slot_of;        /* (n_owned) cache slot of unit id_lo + i, -1: not cached */
+  int32_t* free_slots;     /* stack of free slots; n_free of them are valid */
+  int32_t n_free, id_lo, n_owned, pad;
+  int64_t load_count, hits, misses;
+  void* d_cache;           /* slots of unit_bytes */
+  const void* h_units;     /* pinned store: unit id_lo + i at i * unit_bytes */
+  int64_t unit_bytes;
+  int32_t* d_slot_table;   /* may be NULL */
+  uint64_t* d_ptr_table;   /* may be NULL */
+} infllm_shard_cache;
+int infllm_shard_refill(infllm_shard_cache* cache, const int32_t* ids, int n, void* stream);
+
 /* Persistence (the reference keeps a layer's memory only live, in past_key_values, greedy_search.py:99):
  * infllm_ctx_save writes the whole memory of a context — sink, sealed units, representative keys, un-sealed tokens
  * with their accumulated scores, LRU table and counters — to a file; infllm_ctx_load brings it back into a

@@ -49,6 +49,17 @@ class CtxInfo(ctypes.Structure):
         "h2d_bytes", "d2h_bytes", "cache_hits", "cache_misses", "evictions", "h2d_late_bytes", "inplace_units")]
 
 
+class ShardCache(ctypes.Structure):
+    """infllm_shard_cache of include/infllm_b200.h."""
+    _fields_ = [
+        ("lru", c_void_p), ("slot_of", c_void_p), ("free_slots", c_void_p),
+        ("n_free", c_int32), ("id_lo", c_int32), ("n_owned", c_int32), ("pad", c_int32),
+        ("load_count", c_int64), ("hits", c_int64), ("misses", c_int64),
+        ("d_cache", c_void_p), ("h_units", c_void_p), ("unit_bytes", c_int64),
+        ("d_slot_table", c_void_p), ("d_ptr_table", c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 class ShardToken(ctypes.Structure):
     """infllm_shard_token of include/infllm_b200.h."""
@@ -113,6 +124,7 @@ SIGNATURES = {
                                          c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p,
                                          c_void_p, c_void_p, c_int, POINTER(c_int), c_int, c_void_p, c_int, c_void_p]),
     "infllm_slot_table_update": (c_int, [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int, c_void_p]),
+    "infllm_shard_refill": (c_int, [POINTER(ShardCache), c_void_p, c_int, c_void_p]),
     "infllm_ptr_table_update": (c_int, [c_void_p, POINTER(c_int32), POINTER(ctypes.c_uint64), c_int, c_void_p]),
     "infllm_mailbox_handle_bytes": (c_int, []),
     "infllm_mailbox_create": (c_int, [c_int64, c_int, c_int, c_void_p, POINTER(c_void_p)]),

@@ -75,11 +75,15 @@ class UnitRangeShard:
         _lib.check(_lib.lib.infllm_rope_table(arr, float(self.pe.distance_scale), D, self.cap, self.cos.data_ptr(),
                                               self.sin.data_ptr(), _lib.stream_ptr()))
         self.cache = torch.zeros((max_cached_block, 2, HKV, block_size, D), dtype=dtype, device=dev)
-        self.free_slots = list(range(max_cached_block - 1, -1, -1))
-        self.slot_of = {}
         self.lru = ctypes.c_void_p()
         _lib.check(_lib.lib.infllm_lru_create(max_cached_block, ctypes.byref(self.lru)))
-        self.load_count = 0
+        # the cache's bookkeeping lives in one structure that infllm_shard_refill works on: which slot holds which
+        # owned unit, the stack of free slots, the LRU table, the counters
+        self._free_arr = np.arange(max_cached_block - 1, -1, -1, dtype=np.int32)
+        self._slot_arr = np.full((1,), -1, dtype=np.int32)
+        cs = self._cs = _lib.ShardCache()
+        cs.lru, cs.n_free, cs.free_slots = self.lru, max_cached_block, self._free_arr.ctypes.data
+        cs.slot_of = self._slot_arr.ctypes.data
         max_keys = n_local + topk * block_size + n_init + block_size
         self.max_parts = int(_lib.lib.infllm_attn_decode_max_parts(topk + 3, max_keys))
         self.part_o = torch.empty((self.max_parts, H, D), dtype=torch.float32, device=dev)
@@ -91,11 +95,11 @@ class UnitRangeShard:
         self.d_status = torch.zeros((topk + 4,), dtype=torch.int32, device=dev)
         self.d_status[:topk] = -1
         self.h_status = torch.zeros((topk + 4,), dtype=torch.int32).pin_memory()
+        self._status_np, self._status_ptr = self.h_status.numpy(), self.h_status.data_ptr()
         self.slot_table = None
         self.lse = torch.empty((H,), dtype=torch.float32, device=dev)
         self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
         self.scores_buf = None
-        self.hits = self.misses = 0
         self.profile = False  # when set, CUDA events bracket the scoring and the attention of every token
         self._events = {"topk": [], "decode": []}
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
@@ -122,6 +126,28 @@ class UnitRangeShard:
             _lib.lib.infllm_lru_destroy(self.lru)
             self.lru = None
 
+    @property
+    def slot_of(self):
+        """{owned unit id: cache slot} (a copy, for callers off the per-token path)."""
+        a = self._slot_arr[:self.n_owned]
+        return {self.lo + int(i): int(a[i]) for i in np.nonzero(a >= 0)[0]}
+
+    hits = property(lambda self: self._cs.hits, lambda self, v: setattr(self._cs, "hits", v))
+    misses = property(lambda self: self._cs.misses, lambda self, v: setattr(self._cs, "misses", v))
+    load_count = property(lambda self: self._cs.load_count, lambda self, v: setattr(self._cs, "load_count", v))
+
+    def _sync_cache_state(self):
+        """The structure follows the tensors it points into (after a load or a growth of the store)."""
+        cs, room = self._cs, self.block_k.shape[0]
+        if self._slot_arr.shape[0] < room:
+            grown = np.full((room,), -1, dtype=np.int32)
+            grown[:self._slot_arr.shape[0]] = self._slot_arr
+            self._slot_arr = grown
+        cs.slot_of = self._slot_arr.ctypes.data
+        cs.id_lo, cs.n_owned = self.lo, self.n_owned
+        cs.d_cache, cs.h_units, cs.unit_bytes = self._p["cache"], self.host_units.data_ptr(), self.unit_bytes
+        cs.d_slot_table, cs.d_ptr_table = self.slot_table.data_ptr(), self.ptr_table.data_ptr()
+
     # ------------------------------------------------------------------ state
     def load_synthetic(self, n_total, units, block_k, init_k, init_v, win_k, win_v):
         """Install a memory of n_total sealed units of which this rank receives its own range: `units`
@@ -144,6 +170,7 @@ class UnitRangeShard:
         self.init_k, self.init_v = init_k.to(self.device).contiguous(), init_v.to(self.device).contiguous()
         self._store_pointers()
         self.n_total, self.lo, self.n_owned = n_total, lo, n_owned
+        self._sync_cache_state()
         self.frontier = self.n_init + n_total * self.bs
         self.length = self.frontier + self.n_local
         self.t0 = self.frontier
@@ -269,42 +296,14 @@ class UnitRangeShard:
         self._mark("decode", ev)
         return self.pack
 
-    def _refill(self, owned):
-        """LRU plan for the owned part of a retrieval (context_manager.py:246-265, 495-515) and the copies of
-        the units that are not cached, from the pinned store into free slots."""
-        self.load_count += 1
-        if not owned:
-            return
-        n = len(owned)
-        want = (ctypes.c_int32 * n)(*owned)
-        ev = (ctypes.c_int32 * max(self.max_cached, 1))()
-        n_ev = ctypes.c_int()
-        _lib.check(_lib.lib.infllm_lru_plan(self.lru, want, n, ev, ctypes.byref(n_ev)))
-        changed = {}
-        for i in range(n_ev.value):
-            self.free_slots.append(self.slot_of.pop(ev[i]))
-            changed[ev[i] - self.lo] = -1
-        _lib.check(_lib.lib.infllm_lru_stamp(self.lru, want, n, float(self.load_count)))
-        for b in owned:
-            if b in self.slot_of:
-                self.hits += 1
-                continue
-            self.misses += 1
-            slot = self.free_slots.pop()
-            self.slot_of[b] = slot
-            changed[b - self.lo] = slot
-            _lib.check(_lib.lib.infllm_unit_fetch(self._p["cache"] + slot * self.unit_bytes,
-                                                  self._p["host_units"] + (b - self.lo) * self.unit_bytes,
-                                                  self.unit_bytes, self._stream))
-        if changed:  # the device copies of the slot table (attend_device) and of the unit addresses (run_token)
-            m = len(changed)
-            ids = (ctypes.c_int32 * m)(*changed.keys())
-            slots = (ctypes.c_int32 * m)(*changed.values())
-            _lib.check(_lib.lib.infllm_slot_table_update(self._p["slot_table"], ids, slots, m, self._stream))
-            addrs = (ctypes.c_uint64 * m)(*[
-                self._p["cache"] + sl * self.unit_bytes if sl >= 0 else self._p["host_units"] + i * self.unit_bytes
-                for i, sl in changed.items()])
-            _lib.check(_lib.lib.infllm_ptr_table_update(self._p["ptr_table"], ids, addrs, m, self._stream))
+    def _refill(self, ids, n=None):
+        """LRU plan for the owned part of a retrieval (context_manager.py:246-265, 495-515) and the copies of the
+        units that are not cached, from the pinned store into free slots: one call into the library.  `ids`: a list,
+        or the address of n int32 (entries that are negative or another rank's are skipped)."""
+        if n is None:
+            n = len(ids)
+            ids = (ctypes.c_int32 * max(n, 1))(*ids)
+        _lib.check(_lib.lib.infllm_shard_refill(ctypes.byref(self._cs), ids, n, self._stream))
 
     def run_token(self, q, k, v, out, mb):
         """One token through infllm_shard_token_run: every launch of it in one call (see the header).  Leaves the
@@ -422,6 +421,7 @@ class UnitRangeShard:
             unit[0].copy_(self.k_raw[:, s0:s0 + self.bs], non_blocking=True)
             unit[1].copy_(self.v[:, s0:s0 + self.bs], non_blocking=True)
             self.n_owned += 1
+            self._cs.n_owned = self.n_owned
         self.frontier += self.bs
         self.n_total += 1
 
@@ -443,6 +443,7 @@ class UnitRangeShard:
             ptrs[b - self.lo] = self._p["cache"] + slot * self.unit_bytes
         self.ptr_table = ptrs
         self._store_pointers()
+        self._sync_cache_state()
         self._token_args = None
 
 
@@ -514,6 +515,8 @@ class ShardedDecodeMemory:
     def last_ids(self):
         """The global retrieval of the last token (applies it to the cache tables first if that is still due)."""
         self._settle()
+        if self._last_ids is None:
+            self._last_ids = [int(b) for b in self._last_status if b >= 0]
         return self._last_ids
 
     @last_ids.setter
@@ -529,14 +532,14 @@ class ShardedDecodeMemory:
         s = self.shards[0]
         self._pending.synchronize()
         self._pending = None
-        status = s.h_status.tolist()
-        if status[s.topk]:
+        st = s._status_np
+        if st[s.topk]:
             s.d_status[s.topk:].zero_()
-            raise _lib.InfLLMError(_lib.E_TIMEOUT, f"rank {status[s.topk] - 1} did not arrive at an exchange of the "
+            raise _lib.InfLLMError(_lib.E_TIMEOUT, f"rank {int(st[s.topk]) - 1} did not arrive at an exchange of the "
                                                    "sharded decode within the limit")
-        ids = [b for b in status[:s.topk] if b >= 0]
-        self._last_ids = ids
-        s._refill([b for b in ids if s.lo <= b < s.lo + s.n_owned])
+        self._last_ids = None
+        self._last_status = st[:s.topk].copy()
+        s._refill(s._status_ptr, s.topk)
 
     def _all_gather(self, local):
         """local: (n_local_shards, ...) -> (world, ...) in rank order."""

@@ -2086,6 +2086,56 @@ extern "C" int infllm_unit_fetch(void* d_slot, const void* h_unit, int64_t bytes
   return INFLLM_OK;
 }
 
+constexpr int kShardMaxIds = 256;
+// The cache of a caller that keeps its own (the unit-range shard of the sharded decode): LRU plan for the owned
+// part of a retrieval, eviction, refills from the pinned store on `stream`, and the two device tables, in one call.
+extern "C" int infllm_shard_refill(infllm_shard_cache* c, const int32_t* ids, int n, void* stream) {
+  if (!c || !c->lru || !c->slot_of || !c->free_slots || (n > 0 && !ids)) return fail(INFLLM_E_BADARG, "shard_refill: null pointer");
+  if (n > kShardMaxIds) return fail(INFLLM_E_BADARG, "shard_refill: %d ids, at most %d", n, kShardMaxIds);
+  c->load_count += 1;
+  int32_t owned[kShardMaxIds];
+  int m = 0;
+  for (int i = 0; i < n; ++i)
+    if (ids[i] >= c->id_lo && ids[i] < c->id_lo + c->n_owned) owned[m++] = ids[i];
+  if (m == 0) return INFLLM_OK;
+  int32_t ch_ids[2 * kShardMaxIds], ch_slots[2 * kShardMaxIds];
+  uint64_t ch_addrs[2 * kShardMaxIds];
+  int n_ch = 0;
+  std::vector<int32_t> ev;
+  c->lru->t.plan(owned, m, &ev);
+  for (int32_t b : ev) {
+    const int i = b - c->id_lo;
+    if (i < 0 || i >= c->n_owned || c->slot_of[i] < 0 || n_ch >= 2 * kShardMaxIds)
+      return fail(INFLLM_E_CAPACITY, "shard_refill: evicted unit %d is not in the cache", b);
+    c->free_slots[c->n_free++] = c->slot_of[i];
+    c->slot_of[i] = -1;
+    ch_ids[n_ch] = i, ch_slots[n_ch] = -1;
+    ch_addrs[n_ch++] = (uint64_t)(uintptr_t)c->h_units + (uint64_t)i * (uint64_t)c->unit_bytes;
+  }
+  c->lru->t.stamp(owned, m, (double)c->load_count);
+  for (int j = 0; j < m; ++j) {
+    const int i = owned[j] - c->id_lo;
+    if (c->slot_of[i] >= 0) {
+      c->hits += 1;
+      continue;
+    }
+    c->misses += 1;
+    if (c->n_free <= 0 || n_ch >= 2 * kShardMaxIds) return fail(INFLLM_E_CAPACITY, "shard_refill: no free cache slot");
+    const int slot = c->free_slots[--c->n_free];
+    c->slot_of[i] = slot;
+    char* dst = (char*)c->d_cache + (size_t)slot * (size_t)c->unit_bytes;
+    INFLLM_CUDA_OK(cudaMemcpyAsync(dst, (const char*)c->h_units + (size_t)i * (size_t)c->unit_bytes, (size_t)c->unit_bytes,
+                                   cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    ch_ids[n_ch] = i, ch_slots[n_ch] = slot;
+    ch_addrs[n_ch++] = (uint64_t)(uintptr_t)dst;
+  }
+  if (n_ch > 0) {
+    if (c->d_slot_table) INFLLM_TRY(infllm_slot_table_update(c->d_slot_table, ch_ids, ch_slots, n_ch, stream));
+    if (c->d_ptr_table) INFLLM_TRY(infllm_ptr_table_update(c->d_ptr_table, ch_ids, ch_addrs, n_ch, stream));
+  }
+  return INFLLM_OK;
+}
+
 extern "C" int infllm_ctx_set_comm(infllm_ctx* c, infllm_comm* comm) {
   if (!c) return fail(INFLLM_E_BADARG, "ctx_set_comm: null context");
   if (c->length != 0) return fail(INFLLM_E_BADARG, "ctx_set_comm: the context already holds tokens");
