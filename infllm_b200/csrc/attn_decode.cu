@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
   constexpr int HD = 128;
   __shared__ __align__(16) float sm_o[kDecWarps][kMaxGroup][HD];
   __shared__ float sm_m[kDecWarps][kMaxGroup], sm_l[kDecWarps][kMaxGroup];
+  chain_enter();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int run = blockIdx.x, hkv = blockIdx.y;
   const int group = P.n_heads / P.n_kv_heads;
@@ -302,6 +303,7 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
   extern __shared__ float s_w[];  // n_part weights
   __shared__ float s_num[kMergeGroups][128];
   __shared__ float s_mx, s_den;
+  chain_enter();
   const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (wait.flags) {  // the partials come from peers: every CTA waits for every sender's flag, with a bound
     bool ok = true;
@@ -437,7 +439,7 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
   P.logits = logits;
   P.scale_log2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid(runs, n_kv_heads);
-  INFLLM_DISPATCH_DTYPE(dtype, T, { attn_decode_kernel<T><<<grid, kDecThreads, 0, s>>>(P); });
+  INFLLM_DISPATCH_DTYPE(dtype, T, { launch_chained(attn_decode_kernel<T>, grid, dim3(kDecThreads), 0, s, P); });
   INFLLM_LAUNCH_OK("attn_decode_kernel");
   return INFLLM_OK;
 }
@@ -454,12 +456,12 @@ int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int
   if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
     return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
   if (dtype == INFLLM_F32) {
-    lse_merge_kernel<float><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
+    launch_chained(lse_merge_kernel<float>, dim3(n_heads), dim3(kMergeGroups * head_dim), n_part * sizeof(float), s,
         part_o, part_lse, n_part, n_heads, head_dim, (float*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
         o_ps, lse_ps, w);
   } else {
     INFLLM_DISPATCH_DTYPE(dtype, T, {
-      lse_merge_kernel<T><<<n_heads, kMergeGroups * head_dim, n_part * sizeof(float), s>>>(
+      launch_chained(lse_merge_kernel<T>, dim3(n_heads), dim3(kMergeGroups * head_dim), n_part * sizeof(float), s,
           part_o, part_lse, n_part, n_heads, head_dim, (T*)out, o_hs, lse, logits, logit_len, score, score_hs, skip,
           o_ps, lse_ps, w);
     });

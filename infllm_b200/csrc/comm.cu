@@ -129,6 +129,7 @@ struct PeerList {
 // one CTA per destination: copy n16 16-byte words, make them visible system-wide, then raise the flag
 __global__ void __launch_bounds__(256)
 peer_put_kernel(const uint4* __restrict__ src, int n16, const __grid_constant__ PeerList peers, uint32_t seq) {
+  chain_enter();
   uint4* dst = reinterpret_cast<uint4*>(peers.dst[blockIdx.x]);
   for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
   __threadfence_system();
@@ -179,6 +180,7 @@ exchange_rank_kernel(const uint4* __restrict__ src, int n16, const __grid_consta
                      const int32_t* __restrict__ cand, int64_t sender_stride, int k, int32_t* __restrict__ out_ids) {
   __shared__ float s_score[1024];
   __shared__ int32_t s_id[1024];
+  chain_enter();
   const int tid = threadIdx.x;
   for (int i = tid; i < world * n16; i += blockDim.x) reinterpret_cast<uint4*>(peers.dst[i / n16])[i % n16] = src[i % n16];
   __threadfence_system();
@@ -325,7 +327,7 @@ extern "C" int infllm_mailbox_put(infllm_mailbox* m, const void* d_src, int64_t 
     pl.dst[r] = (char*)m->peer[r] + slot_off + (int64_t)m->rank * slot_bytes;
     pl.flag[r] = reinterpret_cast<uint32_t*>((char*)m->peer[r] + flag_off) + m->rank;
   }
-  peer_put_kernel<<<m->world, 256, 0, (cudaStream_t)stream>>>((const uint4*)d_src, (int)(bytes / 16), pl, seq);
+  launch_chained(peer_put_kernel, dim3(m->world), dim3(256), 0, (cudaStream_t)stream, (const uint4*)d_src, (int)(bytes / 16), pl, seq);
   INFLLM_LAUNCH_OK("peer_put_kernel");
   return INFLLM_OK;
 }
@@ -405,7 +407,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
       pl.dst[r] = (char*)mb->peer[r] + a->cand_off + (int64_t)mb->rank * a->cand_slot;
       pl.flag[r] = reinterpret_cast<uint32_t*>((char*)mb->peer[r] + a->flag1_off) + mb->rank;
     }
-    exchange_rank_kernel<<<1, 256, 0, s>>>(
+    launch_chained(exchange_rank_kernel, dim3(1), dim3(256), 0, s,
         reinterpret_cast<const uint4*>(a->d_cand), (int)(a->cand_bytes / 16), pl, mb->world, a->seq,
         reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag1_off), limit, err, miss_word,
         reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4, a->topk, a->d_status);

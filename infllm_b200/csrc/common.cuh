@@ -33,6 +33,32 @@ void count_launch();  // every kernel launch of the library is counted (infllm_l
     ::infllm::count_launch();                                                                 \
   } while (0)
 
+// ---- programmatic dependent launch for the chain of small kernels behind a decode token.  A kernel of the chain
+// lets the next launch of its stream be scheduled at once (its CTAs come onto the SMs as this grid's drain) and
+// waits, before it touches anything a predecessor wrote, until the grids before it have completed and their
+// writes are visible.  Both statements do nothing in a kernel that was launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// launch `kern` so that it may start while the kernel before it on the stream winds down (it must call chain_enter())
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 #define INFLLM_TRY(expr)        \
   do {                          \
     int _rc = (expr);           \

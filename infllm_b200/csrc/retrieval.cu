@@ -312,6 +312,7 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
   __shared__ int s_cnt;
   __shared__ unsigned long long s_tau;
   __shared__ bool s_last;
+  chain_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Rows of up to 2048 elements (the usual 4096 needs two rounds of it) live in a rolling buffer of eight 16-byte
   // loads per lane: a piece is consumed and at once replaced by the matching piece of the warp's next row, so that
@@ -475,6 +476,7 @@ struct PtrUpdates {
   unsigned long long val[kMaxTableUpdates];
 };
 __global__ void ptr_table_update_kernel(unsigned long long* __restrict__ table, const __grid_constant__ PtrUpdates u, int n) {
+  chain_enter();
   const int i = threadIdx.x;
   if (i < n) table[u.id[i]] = u.val[i];
 }
@@ -488,7 +490,7 @@ int ptr_table_update_launch(unsigned long long* table, const int32_t* ids, const
       u.id[i] = ids[done + i];
       u.val[i] = vals[done + i];
     }
-    ptr_table_update_kernel<<<1, kMaxTableUpdates, 0, s>>>(table, u, m);
+    launch_chained(ptr_table_update_kernel, dim3(1), dim3(kMaxTableUpdates), 0, s, table, u, m);
     INFLLM_LAUNCH_OK("ptr_table_update_kernel");
   }
   return INFLLM_OK;
@@ -510,8 +512,8 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
       // without asking
       // (asked for at every launch: the opt-in holds for the current device only)
       INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      kern<<<grid, kTopkThreads, smem, s>>>((const T*)bk, (int)n, width, qbar, scores, k, id_base, out_ids, out_scores,
-                                           ticket);
+      launch_chained(kern, dim3(grid), dim3(kTopkThreads), smem, s, (const T*)bk, (int)n, width, qbar, scores, k, id_base,
+                     out_ids, out_scores, ticket);
     });
     INFLLM_LAUNCH_OK("block_score_topk_kernel");
     if (!ticket) {

@@ -167,6 +167,7 @@ __global__ void ingest_token_kernel(const T* __restrict__ q, int64_t q_hs, const
                                     int64_t kv_hs, float* __restrict__ score, int64_t score_hs, int n_heads,
                                     int head_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                     int64_t pos_loc, int64_t pos_glb, int32_t* __restrict__ clear) {
+  chain_enter();
   const int half = head_dim / 2, i = threadIdx.x, b = blockIdx.x;
   if (clear && b == 0 && i == 0) *clear = 0;  // the "retrieved unit not cached" flag of this token's attention
   if (i >= half) return;
@@ -206,7 +207,7 @@ int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs
     return fail(INFLLM_E_BADARG, "ingest: positions %lld / %lld outside the table of %lld rows", (long long)pos_loc,
                 (long long)pos_glb, (long long)table_len);
   INFLLM_DISPATCH_DTYPE(dtype, T, {
-    ingest_token_kernel<T><<<n_heads + n_kv_heads, head_dim / 2, 0, s>>>(
+    launch_chained(ingest_token_kernel<T>, dim3(n_heads + n_kv_heads), dim3(head_dim / 2), 0, s,
         (const T*)q, q_hs, (const T*)k, k_hs, (const T*)v, v_hs, (T*)q_loc, (T*)q_glb, qs_hs, qbar, (T*)k_raw, (T*)k_rot,
         (T*)v_out, kv_hs, score, score_hs, n_heads, head_dim, cos_t, sin_t, pos_loc, pos_glb, clear);
   });
