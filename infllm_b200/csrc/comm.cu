@@ -375,7 +375,8 @@ int ingest_token_launch(const void* q, int64_t q_hs, const void* k, int64_t k_hs
                         const float* cos_t, const float* sin_t, int64_t table_len, int64_t pos_loc, int64_t pos_glb,
                         int dtype, cudaStream_t s, int32_t* clear);
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
-                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket);
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket,
+                      int32_t* out_ids_copy = nullptr);
 }  // namespace infllm
 
 extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbox* mb, void* stream) {

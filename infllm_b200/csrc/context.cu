@@ -39,7 +39,8 @@ int stage_units_launch(const void* const* h_src, void* const* d_dst, int n, int6
 int qbar_launch(const void* q, int64_t q_hs, int64_t q_ts, int n_heads, int64_t len, int exc, int head_dim,
                 float* qbar, int64_t qbar_stride, int dtype, cudaStream_t s);
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
-                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket);
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket,
+                      int32_t* out_ids_copy = nullptr);
 int block_score_rows_launch(const void* bk, const int32_t* rows, int n, int width, const float* qbar, float* scores,
                             int dtype, cudaStream_t s);
 int repr_select_launch(const void* k, int64_t k_hs, int64_t k_ts, const float* score, int64_t score_hs,
@@ -278,6 +279,7 @@ struct infllm_ctx {
   int pack_idx = 0, pack_units = 0;
   cudaStream_t d2h_stream = nullptr;
   cudaEvent_t ev_d2h = nullptr, ev_ingest = nullptr;
+  bool ingest_event_due = false;  // a one-token append left ev_ingest unrecorded
   bool d2h_recorded = false;
   int64_t d2h_synced_upto_urgent = 0;  // the same bookkeeping for the urgent stream
   int64_t d2h_synced_upto = 0;  // units below this id are known to be in the host store as far as copy_stream is concerned
@@ -647,12 +649,12 @@ int ensure_scores(infllm_ctx* c, int64_t n, cudaStream_t s) {
 // this context holds a slice of the heads) the scores are summed over the ranks between the two halves, so that
 // every rank ranks the same numbers.  `which` picks the communicator of the stream (0 main, 1 look-ahead).
 int score_topk(infllm_ctx* c, int64_t n, const float* qbar, float* scores, int32_t* d_ids, cudaStream_t s, int which,
-               int k = 0) {
+               int k = 0, int32_t* ids_copy = nullptr) {
   const infllm_config& g = c->cfg;
   if (k <= 0) k = g.topk;
   if (!c->comm)
     return block_topk_launch(c->block_k, n, (int)c->width, qbar, scores, k, 0, d_ids, nullptr, g.dtype, s,
-                             c->tickets + which);
+                             c->tickets + which, ids_copy);
   INFLLM_TRY(block_score_launch(c->block_k, n, (int)c->width, qbar, scores, g.dtype, s));
   INFLLM_TRY(comm_allreduce_sum(c->comm, which, scores, (size_t)n, s));
   return topk_launch(scores, n, k, 0, d_ids, nullptr, s);
@@ -1225,6 +1227,10 @@ int seal_offload(infllm_ctx* c, int64_t first, int n_new, int64_t tok0, cudaStre
   // offload to the host store (MemoryUnit.__init__, context_manager.py:39-45), entirely on the device-to-host
   // stream: pack the new units into the store's layout, then one copy per run of units.  The tokens were
   // final when they were ingested; ev_ingest orders the packing behind that.
+  if (c->ingest_event_due) {
+    INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
+    c->ingest_event_due = false;
+  }
   INFLLM_CUDA_OK(cudaStreamWaitEvent(c->d2h_stream, c->ev_ingest, 0));
   for (int done = 0; done < n_new;) {
     const int n = std::min(n_new - done, c->pack_units);
@@ -1347,11 +1353,12 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
                                    (char*)tb.v + at * D * esz, kv_hs, tb.score + at, tb.cap, (int)H, (int)HKV, (int)D,
                                    c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, g.n_local - 1, g.dtype, s,
                                    c->d_miss));
-    INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
+    c->ingest_event_due = true;  // recorded when a sealing asks for it (seal_offload): one call less per token
   } else {
     INFLLM_TRY(copy_rows_launch(k, k_hs, k_ts, (char*)tb.k_raw + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
     INFLLM_TRY(copy_rows_launch(v, v_hs, v_ts, (char*)tb.v + at * D * esz, kv_hs, D, (int)HKV, L, (int)D, s));
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_ingest, s));
+    c->ingest_event_due = false;
     INFLLM_CUDA_OK(cudaMemset2DAsync(tb.score + at, tb.cap * sizeof(float), 0, L * sizeof(float), H, s));
     INFLLM_TRY(rope_apply_launch((char*)tb.k_raw + at * D * esz, kv_hs, D, (char*)tb.k_rot + at * D * esz, kv_hs, D,
                                  (int)HKV, L, (int)D, c->cos_t, c->sin_t, c->tab_len, T - c->rope_origin, 1, g.dtype,
@@ -1389,7 +1396,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
   }
   std::vector<int32_t> ids;
   for (auto& l : c->la) l.target = -1, l.launched = l.staged = false;
-  INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));
+  if (L > 1) INFLLM_CUDA_OK(cudaEventRecord(c->ev_seal, s));  // the look-ahead's starting point; one token has none
   std::vector<KvSeg> gsegs;
   int eb = 0, n_cand = 0;
   bool have_ids = false;  // the ids of this exec block were already ranked at the end of the previous one
@@ -1408,6 +1415,8 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       if ((c->call_off + st) % chunk == 0) c->chunk_n0 = c->num_blocks;
     }
     const bool spec = run_ahead;
+    const bool ids_direct = !c->comm && g.topk <= 64 && c->num_blocks <= 16384;  // the scorer's one-launch form
+    cudaEvent_t token_ev = nullptr;
     int32_t* d_ids_tok = nullptr;  // the device-side ids of a run-ahead token
     if (!spec) {
       if (!have_ids) {
@@ -1429,12 +1438,18 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
       d_ids_tok = c->d_topk_ring + (int64_t)slot * std::max(1, g.topk);
       {
         ProfScope ps(c, s, INFLLM_PROF_TOPK, (double)c->num_blocks * c->width * c->esz);
-        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, d_ids_tok, s, 0, g.topk));
+        INFLLM_TRY(score_topk(c, c->num_blocks, c->qbar, c->scores, d_ids_tok, s, 0, g.topk, ids_direct ? pt.h_ids : nullptr));
       }
-      INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
-      INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
-      INFLLM_CUDA_OK(cudaMemcpyAsync(pt.h_ids, d_ids_tok, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->mail_stream));
-      INFLLM_CUDA_OK(cudaEventRecord(pt.ev, c->mail_stream));
+      if (ids_direct) {
+        // the ranking threads wrote the ids into the pinned words themselves; the event that tells the host so is
+        // recorded behind the token's last kernel, so that nothing stands between the kernels of the chain
+        token_ev = pt.ev;
+      } else {
+        INFLLM_CUDA_OK(cudaEventRecord(c->ev_main, s));
+        INFLLM_CUDA_OK(cudaStreamWaitEvent(c->mail_stream, c->ev_main, 0));
+        INFLLM_CUDA_OK(cudaMemcpyAsync(pt.h_ids, d_ids_tok, g.topk * sizeof(int32_t), cudaMemcpyDeviceToHost, c->mail_stream));
+        INFLLM_CUDA_OK(cudaEventRecord(pt.ev, c->mail_stream));
+      }
       pt.serial = c->call_serial;
       c->pend_count += 1;
       INFLLM_TRY(flush_table(c, s));
@@ -1608,6 +1623,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
     c->attn_prev_recorded = c->attn_recorded;
     INFLLM_CUDA_OK(cudaEventRecord(c->ev_attn, s));
     c->attn_recorded = true;
+    if (token_ev) INFLLM_CUDA_OK(cudaEventRecord(token_ev, s));
     delete ht_attn;
     trace_mark(c, s, TR_ATTN_END, eb);
     // the look-ahead of the next exec blocks goes out behind the attention launch: it runs on its own stream and

@@ -235,7 +235,7 @@ __device__ __forceinline__ unsigned long long max64(unsigned long long a, unsign
 // `gm` holds kFastGroups keys, `cand` kFastCand keys, `s_cnt` one int, `s_tau` one key.  All 1024 threads call.
 __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, int32_t* __restrict__ out_ids,
                               float* __restrict__ out_scores, unsigned long long* gm, unsigned long long* cand,
-                              int* s_cnt, unsigned long long* s_tau) {
+                              int* s_cnt, unsigned long long* s_tau, int32_t* __restrict__ out_ids_copy = nullptr) {
   const int tid = threadIdx.x;
   unsigned long long key[kFastItems];
 #pragma unroll
@@ -281,6 +281,7 @@ __device__ void cta_topk_fast(const float* scores, int n, int k, int id_base, in
     if (rank < k) {
       const int id = (int)(~(uint32_t)(mine & 0xffffffffu));
       out_ids[rank] = id + id_base;
+      if (out_ids_copy) out_ids_copy[rank] = id + id_base;  // e.g. pinned host memory: no copy behind the kernel
       if (out_scores) out_scores[rank] = __ldcg(scores + id);
     }
   }
@@ -304,7 +305,8 @@ template <typename T>
 __global__ void __launch_bounds__(kTopkThreads)
 block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float* __restrict__ qbar,
                         float* __restrict__ scores, int k, int id_base, int32_t* __restrict__ out_ids,
-                        float* __restrict__ out_scores, unsigned int* __restrict__ ticket) {
+                        float* __restrict__ out_scores, unsigned int* __restrict__ ticket,
+                        int32_t* __restrict__ out_ids_copy) {
   extern __shared__ __align__(16) unsigned char dyn_raw[];
   float* sq = reinterpret_cast<float*>(dyn_raw);
   __shared__ unsigned long long sm[kFastGroups];
@@ -381,7 +383,7 @@ block_score_topk_kernel(const T* __restrict__ bk, int n, int width, const float*
   __threadfence();
   if (threadIdx.x == 0) *ticket = 0;
   if (threadIdx.x == 0) s_tau = 0ull;
-  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt, &s_tau);
+  cta_topk_fast(scores, n, k, id_base, out_ids, out_scores, sm, cand, &s_cnt, &s_tau, out_ids_copy);
 }
 
 template <typename T>
@@ -496,8 +498,13 @@ int ptr_table_update_launch(unsigned long long* table, const int32_t* ids, const
   return INFLLM_OK;
 }
 
+// out_ids_copy (may be null; honoured only by the one-launch form, i.e. with a ticket, k <= 64, n <= 16384): a second
+// place for the ids, written by the same threads - pinned host memory saves the copy behind the kernel
 int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, float* scores, int k, int id_base,
-                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket) {
+                      int32_t* out_ids, float* out_scores, int dtype, cudaStream_t s, unsigned int* ticket,
+                      int32_t* out_ids_copy) {
+  if (out_ids_copy && !(ticket && k <= kFastMaxK && n <= kFastMaxN))
+    return fail(INFLLM_E_UNSUPPORTED, "block_topk: a second id destination needs the one-launch form");
   if (n <= 0 || k <= 0 || k > n) return fail(INFLLM_E_BADARG, "block_topk: need 0 < k <= n_blocks (k=%d n=%lld)", k, (long long)n);
   if (k > 1024) return fail(INFLLM_E_UNSUPPORTED, "block_topk: k=%d > 1024", k);
   if (width % 8 != 0 || width > 12 * 1024 || ((uintptr_t)bk % 16) != 0)
@@ -513,7 +520,7 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
       // (asked for at every launch: the opt-in holds for the current device only)
       INFLLM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       launch_chained(kern, dim3(grid), dim3(kTopkThreads), smem, s, (const T*)bk, (int)n, width, qbar, scores, k, id_base,
-                     out_ids, out_scores, ticket);
+                     out_ids, out_scores, ticket, out_ids_copy);
     });
     INFLLM_LAUNCH_OK("block_score_topk_kernel");
     if (!ticket) {
@@ -601,7 +608,7 @@ extern "C" int infllm_block_topk(const void* d_block_k, int64_t n_blocks, int wi
   using namespace infllm;
   if (!d_block_k || !d_qbar || !d_scores || !d_out_ids) return fail(INFLLM_E_BADARG, "block_topk: null pointer");
   return block_topk_launch(d_block_k, n_blocks, width, d_qbar, d_scores, k, id_base, d_out_ids, d_out_scores, dtype,
-                           (cudaStream_t)stream, nullptr);
+                           (cudaStream_t)stream, nullptr, nullptr);
 }
 
 extern "C" int infllm_repr_select(const void* d_k, int64_t k_hs, int64_t k_ts, const float* d_score,
