@@ -1042,7 +1042,7 @@ def run_decode_sharded(args, rank, world, local_rank):
         del units, block_k
         mems.append(ShardedDecodeMemory([sh], distributed=world > 1, mailbox=mailbox))
         dirs.append(direction)
-    total = (args.warmup + 2 * args.steps + 2) * n_layers
+    total = (args.warmup + 2 * args.steps + 2 + 32) * n_layers
     g = torch.Generator(device=dev).manual_seed(100)  # the same token stream on every rank
     lean_q = torch.stack([dirs[i % n_layers] for i in range(total)])
     qs = (torch.randn((total, H, 1, D), generator=g, device=dev) + 3.0 * lean_q).to(torch.bfloat16)
@@ -1121,6 +1121,25 @@ def run_decode_sharded(args, rank, world, local_rank):
             prof = [dict(topk=(sum(a.elapsed_time(b) for a, b in evs[len(shards):]), len(evs) - len(shards)), decode=(0.0, 0))]
         clocks = sample_clocks_stop(clk_p, clk_f)
         hits, misses = sum(sh.hits for sh in shards), sum(sh.misses for sh in shards)
+        # where a token's time goes on this rank's GPU: a short pass with a one-thread timestamp kernel between the
+        # token's launches (each adds about a microsecond to the phase before it; untimed)
+        phases = None
+        if all(sh._token_args is not None for sh in shards):
+            n_st = 32
+            for sh in shards:
+                sh.stamps, sh.stamp_row = torch.zeros((n_st, 8), dtype=torch.int64, device=dev), 0
+            for _ in range(n_st):
+                step_device()
+            torch.cuda.synchronize()
+            st = torch.stack([sh.stamps for sh in shards]).double()[:, 4:]          # (layers, tokens, 8 stamps)
+            for sh in shards:
+                sh.stamps = None
+            d = (st[..., 1:] - st[..., :-1]).mean(dim=(0, 1)) / 1e3                 # us
+            names = ("ingest", "scoring_topk", "exchange1_rank", "attention", "local_merge", "put_partials",
+                     "wait_final_merge")
+            phases = {n: round(float(x), 2) for n, x in zip(names, d)}
+            phases["token_on_device"] = round(float((st[..., 7] - st[..., 0]).mean() / 1e3), 2)
+            phases["note"] = "mean over the layers' last tokens of a 32-token pass; rank %d" % rank
         step_host()
         ms_e2e = timed(step_host, args.steps)
     _, hbm_peak, which = measured_peaks()
@@ -1160,6 +1179,7 @@ def run_decode_sharded(args, rank, world, local_rank):
                               us_per_launch=1e3 * dec_ms / max(dec_n, 1)),
         store=dict(hits=int(counts[0].item()), misses=int(counts[1].item()),
                    miss_rate=counts[1].item() / max(counts.sum().item(), 1)),
+        phases_us=phases,
         clocks=clocks)
     return line
 

@@ -432,6 +432,8 @@ typedef struct infllm_shard_token {
   int32_t wait_us;
   const uint64_t* d_unit_ptrs;             /* (n_owned) id - id_lo -> address of the unit's K block; NULL: the slot table */
   uint32_t* d_ticket;                      /* one zeroed word: scoring and top-k as ONE launch; NULL: two launches */
+  uint64_t* d_stamps;                      /* NULL, or 8 words: the device's nanosecond timer before the token and behind
+                                              each of its 7 launches (a one-thread kernel per stamp: for a profiling pass) */
 } infllm_shard_token;
 int infllm_shard_token_run(const infllm_shard_token* args, infllm_mailbox* mailbox, void* stream);
 

@@ -101,6 +101,7 @@ class UnitRangeShard:
         self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
         self.scores_buf = None
         self.profile = False  # when set, CUDA events bracket the scoring and the attention of every token
+        self.stamps, self.stamp_row = None, 0  # (rows, 8) int64 on the device: see infllm_shard_token.d_stamps
         self._events = {"topk": [], "decode": []}
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
         self.block_k = self.host_units = self.init_k = self.init_v = None
@@ -340,6 +341,11 @@ class UnitRangeShard:
         last = r == G - 1 and wlo > self.frontier
         a.ovf_at, a.ovf_len = (self.frontier - self.t0, wlo - self.frontier) if last else (0, 0)
         a.d_out, a.seq = out.data_ptr(), mb.seq
+        if self.stamps is not None:  # a profiling pass: one row of 8 device timestamps per token
+            a.d_stamps = self.stamps.data_ptr() + 64 * (self.stamp_row % self.stamps.shape[0])
+            self.stamp_row += 1
+        else:
+            a.d_stamps = None
         self._stream = _lib.stream_ptr()
         _lib.check(_lib.lib.infllm_shard_token_run(ctypes.byref(a), mb.handle, self._stream))
 

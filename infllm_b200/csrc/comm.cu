@@ -379,6 +379,18 @@ int block_topk_launch(const void* bk, int64_t n, int width, const float* qbar, f
                       int32_t* out_ids_copy = nullptr);
 }  // namespace infllm
 
+__global__ void stamp_kernel(unsigned long long* p) {
+  chain_enter();
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *p = t;
+}
+#define INFLLM_STAMP(i)                                                                                   \
+  if (a->d_stamps) {                                                                                      \
+    launch_chained(stamp_kernel, dim3(1), dim3(1), 0, s, reinterpret_cast<unsigned long long*>(a->d_stamps) + (i)); \
+    INFLLM_LAUNCH_OK("stamp_kernel");                                                                     \
+  }
+
 extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbox* mb, void* stream) {
   if (!a || !mb) return fail(INFLLM_E_BADARG, "shard_token_run: null pointer");
   if (a->topk <= 0 || a->topk > kMaxSeg - 3 || a->n_owned < a->topk)
@@ -387,13 +399,16 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   const int H = a->n_heads, HKV = a->n_kv_heads, D = a->head_dim, esz = 2;
   const int64_t row = a->at * D * esz;
   char *k_raw = (char*)a->d_k_raw, *k_rot = (char*)a->d_k_rot, *vbuf = (char*)a->d_v;
+  INFLLM_STAMP(0);
   // 1. the token: copies, rotations, query mean, score column
   INFLLM_TRY(ingest_token_launch(a->d_q, a->q_hs, a->d_k, a->k_hs, a->d_vin, a->v_hs, a->d_q_loc, a->d_q_glb, D, a->d_qbar,
                                  k_raw + row, k_rot + row, vbuf + row, a->cap * D, a->d_score + a->at, a->cap, H, HKV, D,
                                  a->d_cos, a->d_sin, a->cap, a->at, a->n_local - 1, a->dtype, s, nullptr));
+  INFLLM_STAMP(1);
   // 2. this rank's candidates: [score bits (topk) | ids (topk)]
   INFLLM_TRY(block_topk_launch(a->d_block_k, a->n_owned, H * D, a->d_qbar, a->d_scores, a->topk, a->id_lo,
                                a->d_cand + a->topk, reinterpret_cast<float*>(a->d_cand), a->dtype, s, a->d_ticket));
+  INFLLM_STAMP(2);
   // 3. exchange 1, global top-k
   int* err = a->d_status + a->topk;
   int32_t* any_miss = a->d_status + a->topk + 1;
@@ -414,6 +429,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
         reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4, a->topk, a->d_status);
     INFLLM_LAUNCH_OK("exchange_rank_kernel");
   }
+  INFLLM_STAMP(3);
   // 4. attention: [retrieved units, resolved on the device | window share | sink | overflow]
   KvSeg segs[kMaxSeg];
   int32_t qsel[kMaxSeg];
@@ -443,10 +459,15 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   int parts = 0;
   INFLLM_TRY(attn_decode_launch(a->d_q_loc, a->d_q_glb, D, H, HKV, D, n, segs, qsel, a->d_part_o, a->d_part_lse,
                                 a->max_parts, &parts, logit_seg, a->d_logits, a->dtype, s, &ind));
+  INFLLM_STAMP(4);
   INFLLM_TRY(lse_merge_launch(a->d_part_o, a->d_part_lse, parts, H, D, a->d_pack, D, a->d_pack + (int64_t)H * D,
                               INFLLM_F32, s, nullptr, 0, nullptr, 0, nullptr));
-  // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores
+  INFLLM_STAMP(5);
+  // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores.  (Putting the merged rows
+  //    into the peers' slots from the merge kernel's 32 CTAs, flags raised by the last of them, took 18.7 us against
+  //    4.7 + 8.1 for the two kernels: 32 system-wide fences behind small remote stores.)
   INFLLM_TRY(infllm_mailbox_put(mb, a->d_pack, a->part_bytes, a->part_off, a->part_slot, a->flag2_off, a->seq, stream));
+  INFLLM_STAMP(6);
   // the final merge waits for the peers' partials itself (every CTA polls the flag words, with the bound)
   (void)any_miss;
   MergeWait mw;
@@ -456,6 +477,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   INFLLM_TRY(lse_merge_launch(parts_g, parts_g + (int64_t)H * D, mb->world, H, D, a->d_out, D, a->d_lse, a->dtype, s,
                               a->share_len > 0 ? a->d_logits : nullptr, a->share_len, a->d_score + a->share_at, a->cap,
                               nullptr, a->part_slot / 4, a->part_slot / 4, &mw));
+  INFLLM_STAMP(7);
   // 6. retrieval and status words for the host
   INFLLM_CUDA_OK(cudaMemcpyAsync(a->h_status, a->d_status, (a->topk + 4) * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   return INFLLM_OK;
