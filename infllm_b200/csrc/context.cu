@@ -767,7 +767,9 @@ int lookahead_stage(infllm_ctx* c, int64_t target) {
     // Units that have a device copy are gathered by the copy kernel (one launch for the batch); units that only the
     // pinned host store holds travel by one cudaMemcpyAsync each on the copy engine: a kernel that reads host memory
     // gets more out of the link (49 against 38 GB/s) but its CTAs sit on SMs for the whole transfer and slowed the
-    // exec-block attention by a tenth when measured, so that the prompt took longer.  Flag bit 2: no copy kernel.
+    // exec-block attention by a tenth when measured, so that the prompt took longer - also when only 4 of a batch's
+    // 13 units went through the kernel on a stream of its own beside the copy engine (attention 88 -> 92 us, prompt
+    // unchanged; 6 and more units: slower).  Flag bit 2: no copy kernel.
     std::vector<const void*> ksrc;
     std::vector<void*> kdst;
     for (size_t i = 0; i < src.size(); ++i) {
