@@ -432,6 +432,10 @@ typedef struct infllm_shard_token {
   int32_t wait_us;
   const uint64_t* d_unit_ptrs;             /* (n_owned) id - id_lo -> address of the unit's K block; NULL: the slot table */
   uint32_t* d_ticket;                      /* one zeroed word: scoring and top-k as ONE launch; NULL: two launches */
+  int64_t ll_part_off, ll_part_slot;       /* the same for the partials: slots of part_bytes / 4 8-byte words */
+  int64_t ll_cand_off, ll_cand_slot;       /* 0, or a second candidate region of the mailbox, slots of 2 * topk 8-byte
+                                              words: the candidates travel as {value, seq} pairs that carry their own
+                                              arrival flag (no system-wide fence, no flag word) */
   uint64_t* d_stamps;                      /* NULL, or 8 words: the device's nanosecond timer before the token and behind
                                               each of its 7 launches (a one-thread kernel per stamp: for a profiling pass) */
 } infllm_shard_token;

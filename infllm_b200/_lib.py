@@ -85,7 +85,8 @@ class ShardToken(ctypes.Structure):
         ("cand_off", c_int64), ("cand_slot", c_int64), ("cand_bytes", c_int64), ("part_off", c_int64),
         ("part_slot", c_int64), ("part_bytes", c_int64), ("flag1_off", c_int64), ("flag2_off", c_int64),
         ("seq", ctypes.c_uint32), ("wait_us", c_int32),
-        ("d_unit_ptrs", c_void_p), ("d_ticket", c_void_p), ("d_stamps", c_void_p),
+        ("d_unit_ptrs", c_void_p), ("d_ticket", c_void_p), ("ll_part_off", c_int64), ("ll_part_slot", c_int64), ("ll_cand_off", c_int64), ("ll_cand_slot", c_int64),
+        ("d_stamps", c_void_p),
     ]
 
 

@@ -101,6 +101,7 @@ class UnitRangeShard:
         self.cand = torch.empty((2, topk), dtype=torch.int32, device=dev)         # [score bits | ids]
         self.scores_buf = None
         self.profile = False  # when set, CUDA events bracket the scoring and the attention of every token
+        self.flag_in_data = True  # the candidate exchange of run_token: words that carry their own arrival flag
         self.stamps, self.stamp_row = None, 0  # (rows, 8) int64 on the device: see infllm_shard_token.d_stamps
         self._events = {"topk": [], "decode": []}
         self.t0 = self.length = self.frontier = self.n_total = self.lo = self.n_owned = 0
@@ -324,6 +325,8 @@ class UnitRangeShard:
             a.cand_off, a.cand_slot, a.cand_bytes = mb.cand_off, mb.cand_slot, mb.cand_bytes
             a.part_off, a.part_slot, a.part_bytes = mb.part_off, mb.part_slot, mb.part_bytes
             a.flag1_off, a.flag2_off, a.wait_us = mb.flag1, mb.flag2, mb.wait_us
+            a.ll_cand_off, a.ll_cand_slot = (mb.ll_cand_off, mb.ll_cand_slot) if self.flag_in_data else (0, 0)
+            a.ll_part_off, a.ll_part_slot = (mb.ll_part_off, mb.ll_part_slot) if self.flag_in_data else (0, 0)
             # (the store's addresses change only when it grows, which drops this block)
             a.d_block_k, a.d_scores, a.d_slot_table = p["block_k"], p["scores_buf"], p["slot_table"]
             a.d_unit_ptrs, a.d_ticket = p["ptr_table"], p["ticket"]
@@ -472,7 +475,12 @@ class PeerMailbox:
         self.part_bytes = (n_heads * (head_dim + 1) + 4) * 4  # [o | lse | miss word | pad]
         self.part_slot = (self.part_bytes + 15) // 16 * 16
         self.miss_off = n_heads * (head_dim + 1) * 4
-        total = self.part_off + self.world * self.part_slot
+        # a second candidate region for the exchange whose words carry their own arrival flag (8 bytes per word)
+        self.ll_cand_off = (self.part_off + self.world * self.part_slot + 255) // 256 * 256
+        self.ll_cand_slot = 2 * topk * 8
+        self.ll_part_off = (self.ll_cand_off + self.world * self.ll_cand_slot + 255) // 256 * 256
+        self.ll_part_slot = self.part_bytes // 4 * 8
+        total = self.ll_part_off + self.world * self.ll_part_slot
         n = int(_lib.lib.infllm_mailbox_handle_bytes())
         mine = (ctypes.c_ubyte * n)()
         self.handle = ctypes.c_void_p()

@@ -94,6 +94,10 @@ int attn_decode_launch(const void* q0, const void* q1, int64_t q_hs, int n_heads
 // merged were put into this GPU's mailbox by peers.  A flag that does not arrive within `limit` polls leaves
 // 1 + its rank in *err and the kernel writes nothing.
 struct MergeWait {
+  // flag-in-data partials: when set, partial p's o row and lse are 8-byte words {value, seq} at
+  // ll[p * o_ps + h * head_dim + d] and ll[p * lse_ps + n_heads * head_dim + h] (strides in words); every thread polls
+  // the words it needs until they carry `seq` (bounded by `limit`), part_o / part_lse / flags are not used
+  const volatile unsigned long long* ll = nullptr;
   const volatile uint32_t* flags = nullptr;
   uint32_t seq = 0, limit = 0;
   int32_t world = 0;

@@ -324,11 +324,25 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
   if (skip && *skip) return;  // the partials were declared invalid by whoever produced them
   const int grp = tid / head_dim, d = tid % head_dim, ngrp = blockDim.x / head_dim;
   const float* po = part_o + (int64_t)h * head_dim + d;
+  bool ll_ok = true;
+  auto ll_get = [&](int64_t idx, int sender) -> float {  // a word that carries its own arrival flag
+    const volatile unsigned long long* p = wait.ll + idx;
+    unsigned long long v = *p;
+    for (uint32_t it = 0; (uint32_t)(v >> 32) != wait.seq; v = *p) {
+      if (++it > wait.limit) {
+        ll_ok = false;
+        atomicExch(wait.err, 1 + sender);
+        break;
+      }
+      __nanosleep(100);
+    }
+    return __uint_as_float((uint32_t)v);
+  };
   float pv[kMergeUnroll];
 #pragma unroll
   for (int u = 0; u < kMergeUnroll; ++u) {
     const int p = grp + u * ngrp;
-    pv[u] = p < n_part ? __ldcs(po + (int64_t)p * o_ps) : 0.f;
+    pv[u] = p >= n_part ? 0.f : wait.ll ? ll_get((int64_t)p * o_ps + (int64_t)h * head_dim + d, p) : __ldcs(po + (int64_t)p * o_ps);
   }
   float lg[kMergeCols], sc[kMergeCols];
 #pragma unroll
@@ -341,7 +355,7 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
   if (warp == 0) {
     float mx = -INFINITY;
     for (int p = lane; p < n_part; p += 32) {
-      const float v = part_lse[(int64_t)p * lse_ps + h];
+      const float v = wait.ll ? ll_get((int64_t)p * lse_ps + (int64_t)n_heads * head_dim + h, p) : part_lse[(int64_t)p * lse_ps + h];
       s_w[p] = v;
       mx = fmaxf(mx, v);
     }
@@ -358,7 +372,7 @@ lse_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
       s_den = den;
     }
   }
-  __syncthreads();
+  if (__syncthreads_or(!ll_ok)) return;  // a sender's words did not arrive: nothing is written
   const float den = s_den;
   const float l = den > 0.f ? s_mx + log2f(den) : -INFINITY;
   float num = 0.f;
@@ -453,6 +467,8 @@ int lse_merge_launch(const float* part_o, const float* part_lse, int n_part, int
   if (lse_ps <= 0) lse_ps = n_heads;
   if (n_part <= 0) return fail(INFLLM_E_BADARG, "lse_merge: no partials");
   if (n_part > 8192) return fail(INFLLM_E_CAPACITY, "lse_merge: %d partials (at most 8192)", n_part);
+  if (w.ll && (n_part > kMergeUnroll * kMergeGroups || !w.err))
+    return fail(INFLLM_E_BADARG, "lse_merge: %d flag-in-data partials (at most %d)", n_part, kMergeUnroll * kMergeGroups);
   if (head_dim <= 0 || head_dim > 128 || head_dim % 32)
     return fail(INFLLM_E_UNSUPPORTED, "lse_merge: head_dim %d (a multiple of 32, at most 128)", head_dim);
   if (dtype == INFLLM_F32) {

@@ -210,6 +210,70 @@ exchange_rank_kernel(const uint4* __restrict__ src, int n16, const __grid_consta
   rank_candidates(cand, sender_stride, world, k, out_ids, s_score, s_id);
 }
 
+// The same exchange with the arrival flag inside the data: every 32-bit word of the message travels as an 8-byte
+// store {word, seq} into the peer's slot and the receiver polls each word until it carries this token's sequence
+// number.  An aligned 8-byte store arrives whole, so there is no system-wide fence and no separate flag store behind
+// the data: one link latency instead of three.  Slots of 2k 8-byte words per sender; sequence numbers start at 1
+// and the region starts zeroed.
+struct PeerWords {
+  unsigned long long* dst[kMaxPeers];
+};
+__global__ void __launch_bounds__(256)
+exchange_rank_ll_kernel(const int32_t* __restrict__ src, const __grid_constant__ PeerWords peers, int world, uint32_t seq,
+                        const volatile unsigned long long* local, int64_t sender_stride, uint32_t limit, int* err,
+                        int32_t* clear_word, int k, int32_t* __restrict__ out_ids) {
+  __shared__ float s_score[1024];
+  __shared__ int32_t s_id[1024];
+  chain_enter();
+  const int tid = threadIdx.x, m = 2 * k, n = world * k;
+  for (int i = tid; i < world * m; i += blockDim.x) {
+    const unsigned long long w = ((unsigned long long)seq << 32) | (uint32_t)src[i % m];
+    *reinterpret_cast<volatile unsigned long long*>(peers.dst[i / m] + i % m) = w;
+  }
+  if (clear_word && tid == 0) *clear_word = 0;
+  bool ok = true;
+  for (int i = tid; i < world * m && ok; i += blockDim.x) {
+    const int r = i / m, w = i % m;
+    const volatile unsigned long long* p = local + (int64_t)r * sender_stride + w;
+    unsigned long long v = *p;
+    for (uint32_t it = 0; (uint32_t)(v >> 32) != seq; v = *p) {
+      if (++it > limit) {
+        ok = false;
+        atomicExch(err, 1 + r);
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (w < k) s_score[r * k + w] = __int_as_float((int32_t)(uint32_t)v);
+    else s_id[r * k + w - k] = (int32_t)(uint32_t)v;
+  }
+  if (__syncthreads_or(!ok)) {  // the exchange failed: no retrieval
+    for (int i = tid; i < k; i += blockDim.x) out_ids[i] = -1;
+    return;
+  }
+  for (int i = tid; i < k; i += blockDim.x) out_ids[i] = -1;  // fewer than k real candidates: padding
+  __syncthreads();
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = s_score[i];
+    const int32_t id = s_id[i];
+    if (id < 0) continue;
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const int32_t oj = s_id[j];
+      rank += oj >= 0 && (s_score[j] > v || (s_score[j] == v && oj < id));
+    }
+    if (rank < k) out_ids[rank] = id;
+  }
+}
+
+// one CTA per destination: the message's n 32-bit words as {word, seq} pairs into this rank's slot there
+__global__ void __launch_bounds__(256)
+peer_put_ll_kernel(const uint32_t* __restrict__ src, int n, const __grid_constant__ PeerWords peers, uint32_t seq) {
+  chain_enter();
+  volatile unsigned long long* dst = peers.dst[blockIdx.x];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = ((unsigned long long)seq << 32) | src[i];
+}
+
 __device__ void rank_candidates(const int32_t* __restrict__ cand, int64_t sender_stride, int world, int k,
                                 int32_t* __restrict__ out_ids, float* s_score, int32_t* s_id) {
   const int n = world * k;
@@ -423,11 +487,26 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
       pl.dst[r] = (char*)mb->peer[r] + a->cand_off + (int64_t)mb->rank * a->cand_slot;
       pl.flag[r] = reinterpret_cast<uint32_t*>((char*)mb->peer[r] + a->flag1_off) + mb->rank;
     }
+    if (a->ll_cand_slot > 0) {
+      if (a->ll_cand_off % 8 || a->ll_cand_slot % 8 || a->ll_cand_slot < 16ll * a->topk ||
+          a->ll_cand_off + (int64_t)mb->world * a->ll_cand_slot > (int64_t)mb->bytes)
+        return fail(INFLLM_E_BADARG, "shard_token_run: flag-in-data candidate region at %lld, slots of %lld bytes",
+                    (long long)a->ll_cand_off, (long long)a->ll_cand_slot);
+      PeerWords pw{};
+      for (int r = 0; r < mb->world; ++r)
+        pw.dst[r] = reinterpret_cast<unsigned long long*>((char*)mb->peer[r] + a->ll_cand_off + (int64_t)mb->rank * a->ll_cand_slot);
+      launch_chained(exchange_rank_ll_kernel, dim3(1), dim3(256), 0, s, reinterpret_cast<const int32_t*>(a->d_cand), pw,
+                     mb->world, a->seq,
+                     reinterpret_cast<const volatile unsigned long long*>((char*)mb->local + a->ll_cand_off),
+                     a->ll_cand_slot / 8, limit, err, miss_word, a->topk, a->d_status);
+      INFLLM_LAUNCH_OK("exchange_rank_ll_kernel");
+    } else {
     launch_chained(exchange_rank_kernel, dim3(1), dim3(256), 0, s,
         reinterpret_cast<const uint4*>(a->d_cand), (int)(a->cand_bytes / 16), pl, mb->world, a->seq,
         reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag1_off), limit, err, miss_word,
         reinterpret_cast<const int32_t*>((char*)mb->local + a->cand_off), a->cand_slot / 4, a->topk, a->d_status);
     INFLLM_LAUNCH_OK("exchange_rank_kernel");
+    }
   }
   INFLLM_STAMP(3);
   // 4. attention: [retrieved units, resolved on the device | window share | sink | overflow]
@@ -466,17 +545,35 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   // 5. exchange 2, merge of the ranks' partials + this rank's share of the local scores.  (Putting the merged rows
   //    into the peers' slots from the merge kernel's 32 CTAs, flags raised by the last of them, took 18.7 us against
   //    4.7 + 8.1 for the two kernels: 32 system-wide fences behind small remote stores.)
-  INFLLM_TRY(infllm_mailbox_put(mb, a->d_pack, a->part_bytes, a->part_off, a->part_slot, a->flag2_off, a->seq, stream));
+  const bool ll_part = a->ll_part_slot > 0;
+  if (ll_part) {
+    const int words = (int)(a->part_bytes / 4);
+    if (a->ll_part_off % 8 || a->ll_part_slot < 8ll * words || a->ll_part_slot % 8 ||
+        a->ll_part_off + (int64_t)mb->world * a->ll_part_slot > (int64_t)mb->bytes)
+      return fail(INFLLM_E_BADARG, "shard_token_run: flag-in-data partial region at %lld, slots of %lld bytes",
+                  (long long)a->ll_part_off, (long long)a->ll_part_slot);
+    PeerWords pw{};
+    for (int r = 0; r < mb->world; ++r)
+      pw.dst[r] = reinterpret_cast<unsigned long long*>((char*)mb->peer[r] + a->ll_part_off + (int64_t)mb->rank * a->ll_part_slot);
+    launch_chained(peer_put_ll_kernel, dim3(mb->world), dim3(256), 0, s, reinterpret_cast<const uint32_t*>(a->d_pack), words, pw,
+                   a->seq);
+    INFLLM_LAUNCH_OK("peer_put_ll_kernel");
+  } else {
+    INFLLM_TRY(infllm_mailbox_put(mb, a->d_pack, a->part_bytes, a->part_off, a->part_slot, a->flag2_off, a->seq, stream));
+  }
   INFLLM_STAMP(6);
-  // the final merge waits for the peers' partials itself (every CTA polls the flag words, with the bound)
+  // the final merge waits for the peers' partials itself (every CTA polls, with the bound: the flag words, or the
+  // data words that carry their flag)
   (void)any_miss;
   MergeWait mw;
-  mw.flags = reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag2_off);
+  mw.flags = ll_part ? nullptr : reinterpret_cast<const volatile uint32_t*>((char*)mb->local + a->flag2_off);
+  mw.ll = ll_part ? reinterpret_cast<const volatile unsigned long long*>((char*)mb->local + a->ll_part_off) : nullptr;
   mw.seq = a->seq; mw.limit = limit; mw.world = mb->world; mw.err = err;
   const float* parts_g = reinterpret_cast<const float*>((char*)mb->local + a->part_off);
+  const int64_t ps = ll_part ? a->ll_part_slot / 8 : a->part_slot / 4;
   INFLLM_TRY(lse_merge_launch(parts_g, parts_g + (int64_t)H * D, mb->world, H, D, a->d_out, D, a->d_lse, a->dtype, s,
                               a->share_len > 0 ? a->d_logits : nullptr, a->share_len, a->d_score + a->share_at, a->cap,
-                              nullptr, a->part_slot / 4, a->part_slot / 4, &mw));
+                              nullptr, ps, ps, &mw));
   INFLLM_STAMP(7);
   // 6. retrieval and status words for the host
   INFLLM_CUDA_OK(cudaMemcpyAsync(a->h_status, a->d_status, (a->topk + 4) * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
