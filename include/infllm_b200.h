@@ -385,6 +385,9 @@ typedef struct infllm_mailbox infllm_mailbox;
 int infllm_mailbox_handle_bytes(void);
 int infllm_mailbox_create(int64_t bytes, int rank, int world, void* h_handle, infllm_mailbox** out);
 int infllm_mailbox_open(infllm_mailbox* m, const void* h_handles);
+/* Instead of opening rank `rank`'s handle: that rank's buffer is `d_buffer`, device memory of this process (several
+ * ranks emulated in one process, or a stand-in for a rank that will never post, in a test of the bounded waits). */
+int infllm_mailbox_alias(infllm_mailbox* m, int rank, void* d_buffer);
 void* infllm_mailbox_local(infllm_mailbox* m);
 int infllm_mailbox_destroy(infllm_mailbox* m);
 int infllm_mailbox_put(infllm_mailbox* m, const void* d_src, int64_t bytes, int64_t slot_off, int64_t slot_bytes,

@@ -130,6 +130,7 @@ SIGNATURES = {
     "infllm_mailbox_handle_bytes": (c_int, []),
     "infllm_mailbox_create": (c_int, [c_int64, c_int, c_int, c_void_p, POINTER(c_void_p)]),
     "infllm_mailbox_open": (c_int, [c_void_p, c_void_p]),
+    "infllm_mailbox_alias": (c_int, [c_void_p, c_int, c_void_p]),
     "infllm_mailbox_local": (c_void_p, [c_void_p]),
     "infllm_mailbox_destroy": (c_int, [c_void_p]),
     "infllm_mailbox_put": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, ctypes.c_uint32, c_void_p]),

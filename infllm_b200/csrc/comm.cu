@@ -114,6 +114,7 @@ extern "C" int infllm_comm_destroy(infllm_comm* c) {
 struct infllm_mailbox {
   void* local = nullptr;        // this rank's buffer
   void* peer[16] = {nullptr};   // the same buffer of every rank as mapped here (peer[rank] == local)
+  bool aliased[16] = {false};   // peer[r] is a pointer of this process (infllm_mailbox_alias): not ours to unmap
   size_t bytes = 0;
   int rank = 0, world = 1;
 };
@@ -369,10 +370,17 @@ extern "C" int infllm_mailbox_open(infllm_mailbox* m, const void* h_handles) {
 
 extern "C" void* infllm_mailbox_local(infllm_mailbox* m) { return m ? m->local : nullptr; }
 
+extern "C" int infllm_mailbox_alias(infllm_mailbox* m, int rank, void* d_buffer) {
+  if (!m || !d_buffer || rank < 0 || rank >= m->world || rank == m->rank || m->peer[rank])
+    return fail(INFLLM_E_BADARG, "mailbox_alias: bad argument");
+  m->peer[rank] = d_buffer;
+  m->aliased[rank] = true;
+  return INFLLM_OK;
+}
 extern "C" int infllm_mailbox_destroy(infllm_mailbox* m) {
   if (!m) return INFLLM_OK;
   for (int r = 0; r < m->world; ++r)
-    if (r != m->rank && m->peer[r]) cudaIpcCloseMemHandle(m->peer[r]);
+    if (r != m->rank && m->peer[r] && !m->aliased[r]) cudaIpcCloseMemHandle(m->peer[r]);
   if (m->local) cudaFree(m->local);
   delete m;
   return INFLLM_OK;
