@@ -371,7 +371,13 @@ def run_reference(args, rank):
 
 # ------------------------------------------------------------------------------------- GPU arm
 def sample_clocks_start(gpu_index):
+    """One sampler for the whole job: local rank 0 polls the GPUs of all local ranks (eight pollers, one per rank, took
+    host time and driver locks from the ranks they were watching)."""
     f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+    if gpu_index != 0:
+        return None, f
+    n_local = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+    gpu_index = ",".join(str(i) for i in range(max(n_local, 1)))
     q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     try:
@@ -698,10 +704,11 @@ def run_decode(args, rank, world, local_rank, device_store_mb=0):
         return out
 
     with torch.inference_mode():
+        # (the sampler starts with the warm-up: the timed region of a decode run is shorter than a polling period)
+        clk_p, clk_f = sample_clocks_start(local_rank)
         for _ in range(args.warmup):
             step_device()
         info0 = [cm.info() for cm in cms]
-        clk_p, clk_f = sample_clocks_start(local_rank)
         l0 = _lib.lib.infllm_launch_count()
         ms = timed(step_device, args.steps)
         launches = _lib.lib.infllm_launch_count() - l0
@@ -1089,13 +1096,13 @@ def run_decode_sharded(args, rank, world, local_rank):
 
     with torch.inference_mode():
         parity = sharded_decode_selfcheck(rank, world, dev, mailbox_on=not args.nccl_exchange) if world > 1 else None
+        clk_p, clk_f = sample_clocks_start(local_rank)  # with the warm-up: the timed region is shorter than a polling period
         for _ in range(args.warmup):
             step_device()
         shards = [m.shards[0] for m in mems]
         for sh in shards:
             sh.profile = True
             sh.hits = sh.misses = 0
-        clk_p, clk_f = sample_clocks_start(local_rank)
         l0 = _lib.lib.infllm_launch_count()
         ms = timed(step_device, args.steps)
         launches = _lib.lib.infllm_launch_count() - l0
