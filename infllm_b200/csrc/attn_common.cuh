@@ -83,6 +83,9 @@ struct DecodeIndirect {
   // unit-range sharding: this GPU owns the ids [id_lo, id_lo + n_owned) and the tables start at id_lo; a retrieved
   // unit of another rank, or a padding id < 0, gets weight zero here and is not a miss
   int32_t id_lo = 0, n_owned = 0x7fffffff;
+  // the launch directly before this one on the stream is a chain kernel (common.cuh) that writes nothing the other
+  // segments need: their keys are attended to before the kernel waits for it, the units' after
+  int32_t early_rest = 0;
 };
 
 int attn_general_launch(const AttnParams& p, int head_dim, int dtype, cudaStream_t s);

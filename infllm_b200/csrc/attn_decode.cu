@@ -73,11 +73,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
   constexpr int HD = 128;
   __shared__ __align__(16) float sm_o[kDecWarps][kMaxGroup][HD];
   __shared__ float sm_m[kDecWarps][kMaxGroup], sm_l[kDecWarps][kMaxGroup];
-  chain_enter();
+  const bool early = P.ind.early_rest != 0 && P.ind.n_units > 0;
+  if (early) chain_trigger(); else chain_enter();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int run = blockIdx.x, hkv = blockIdx.y;
   const int group = P.n_heads / P.n_kv_heads;
-  const int lo = (int)((int64_t)run * P.n_items / P.n_runs), hi = (int)((int64_t)(run + 1) * P.n_items / P.n_runs);
   const bool qrow = g < group;          // this thread's S row is a real query head
   const int hq = hkv * group + (qrow ? g : 0);
 
@@ -88,11 +88,24 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
   for (int i = 0; i < 8; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
   float m = -INFINITY, l = 0.f;  // running maximum of head g; this thread's share of its row sum
 
-  int sg = 0, sg_resolved = -1;
+  // A run is a contiguous share of the groups outside the device-resolved units plus a contiguous share of the
+  // units' groups, so that every CTA has work of both kinds; the first kind comes first (it needs no retrieval: with
+  // early_rest the kernel has not waited for its predecessor yet), the units' groups second.
   const char *kbase = nullptr, *vbase = nullptr;
   char* deposit = nullptr;  // != nullptr: the segment is a unit read in place; its K block's copy in the landing slot
   bool seg_ok = true;
-  for (int it = lo + warp; it < hi; it += kDecWarps) {
+  const int u_beg = P.ind.n_units > 0 ? P.item_begin[P.ind.first_seg] : 0;
+  const int u_end = P.ind.n_units > 0 ? P.item_begin[P.ind.first_seg + P.ind.n_units] : 0;
+  const int n_unit = u_end - u_beg, n_rest = P.n_items - n_unit;
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+  if (pass == 1 && early) chain_wait();
+  const int n_pass = pass ? n_unit : n_rest;
+  const int lo = (int)((int64_t)run * n_pass / P.n_runs), hi = (int)((int64_t)(run + 1) * n_pass / P.n_runs);
+  int sg = 0, sg_resolved = -1;
+#pragma unroll 1
+  for (int j = lo + warp; j < hi; j += kDecWarps) {
+    const int it = pass ? u_beg + j : (j < u_beg ? j : j + n_unit);
     while (it >= P.item_begin[sg + 1]) ++sg;
     const DecodeSeg& S = P.seg[sg];
     if (sg != sg_resolved) {  // pointers of the segment; a memory unit named on the device is looked up here
@@ -244,6 +257,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
       a[3] = __byte_perm(v21[r], v31[r], sel);
       mma16816<T>(ot[i], a, b0, b1);
     }
+  }
   }
   // ---- the warps' results meet in shared memory
   l += __shfl_xor_sync(0xffffffffu, l, 1);

@@ -543,6 +543,7 @@ extern "C" int infllm_shard_token_run(const infllm_shard_token* a, infllm_mailbo
   ind.ids = a->d_status; ind.table = a->d_slot_table; ind.cache = (const char*)a->d_cache; ind.unit_bytes = a->unit_bytes;
   ind.ptrs = reinterpret_cast<const unsigned long long*>(a->d_unit_ptrs);  // set: found wherever the unit lives
   ind.n_units = a->topk; ind.first_seg = 0; ind.miss = miss_word; ind.id_lo = a->id_lo; ind.n_owned = a->n_owned;
+  ind.early_rest = a->d_stamps ? 0 : 1;  // behind the candidate exchange: the window share and the sink do not wait for it
   int parts = 0;
   INFLLM_TRY(attn_decode_launch(a->d_q_loc, a->d_q_glb, D, H, HKV, D, n, segs, qsel, a->d_part_o, a->d_part_lse,
                                 a->max_parts, &parts, logit_seg, a->d_logits, a->dtype, s, &ind));

@@ -34,13 +34,18 @@ void count_launch();  // every kernel launch of the library is counted (infllm_l
   } while (0)
 
 // ---- programmatic dependent launch for the chain of small kernels behind a decode token.  A kernel of the chain
-// lets the next launch of its stream be scheduled at once (its CTAs come onto the SMs as this grid's drain) and
-// waits, before it touches anything a predecessor wrote, until the grids before it have completed and their
-// writes are visible.  Both statements do nothing in a kernel that was launched the ordinary way.
+// waits, before it touches anything, until the grids before it have completed and their writes are visible, and
+// then lets the next launch of its stream be scheduled (its CTAs come onto the SMs as this grid's drain).  In this
+// order a kernel that is being scheduled knows that everything before its predecessor is complete, so it may do,
+// ahead of its own wait, work that depends on nothing its predecessor writes (chain_trigger(), then chain_wait()
+// where the predecessor's results are first needed).  The statements do nothing in a kernel that was launched the
+// ordinary way.
 #ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void chain_enter() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  chain_wait();
+  chain_trigger();
 }
 // launch `kern` so that it may start while the kernel before it on the stream winds down (it must call chain_enter())
 template <typename... KArgs, typename... Args>

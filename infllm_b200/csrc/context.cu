@@ -1507,6 +1507,7 @@ int append_sub(infllm_ctx* c, const char* q, int64_t q_hs, int64_t q_ts, const c
         ind.n_units = g.topk;
         ind.first_seg = 1;
         ind.landing = c->d_unit_ptrs + c->tab_cap;
+        ind.early_rest = 1;  // behind the scorer or the table update: neither writes what the window and the sink need
       }
       {
         // the merge also adds this token's local attention row into the accumulated scores

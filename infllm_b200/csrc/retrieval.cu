@@ -478,7 +478,10 @@ struct PtrUpdates {
   unsigned long long val[kMaxTableUpdates];
 };
 __global__ void ptr_table_update_kernel(unsigned long long* __restrict__ table, const __grid_constant__ PtrUpdates u, int n) {
-  chain_enter();
+  // scheduled once the kernel before it has passed its own wait: everything older is complete, and what follows this
+  // kernel may be scheduled at once (the attention starts on the keys that need no table)
+  chain_trigger();
+  chain_wait();
   const int i = threadIdx.x;
   if (i < n) table[u.id[i]] = u.val[i];
 }
