@@ -198,3 +198,31 @@ def test_oracle_is_invariant_to_how_a_prompt_is_split_into_appends():
     assert [t.topk_raw for t in a.trace] == [t.topk_raw for t in b.trace]
     assert [t.cached_after for t in a.trace] == [t.cached_after for t in b.trace]
     torch.testing.assert_close(oa, ob, atol=1e-6, rtol=0)
+
+
+def test_shard_refill_argument_checks_and_foreign_ids_need_no_device():
+    """infllm_shard_refill: bad arguments are refused, and a retrieval that names only other ranks' units (or holes)
+    counts the load and touches nothing else — no device call is made for it."""
+    import numpy as np
+
+    from infllm_b200 import _lib as L
+
+    lru = ctypes.c_void_p()
+    L.check(L.lib.infllm_lru_create(4, ctypes.byref(lru)))
+    try:
+        slots, free = np.full((8,), -1, dtype=np.int32), np.arange(3, -1, -1, dtype=np.int32)
+        cs = L.ShardCache()
+        cs.lru, cs.slot_of, cs.free_slots, cs.n_free = lru, slots.ctypes.data, free.ctypes.data, 4
+        cs.id_lo, cs.n_owned, cs.unit_bytes = 100, 8, 1024
+        ids = (ctypes.c_int32 * 4)(-1, 3, 99, 108)  # a hole, and ids below and above [100, 108)
+        assert L.lib.infllm_shard_refill(ctypes.byref(cs), ids, 4, None) == L.OK
+        assert (cs.load_count, cs.hits, cs.misses, cs.n_free) == (1, 0, 0, 4)
+        assert (slots == -1).all()
+        assert L.lib.infllm_shard_refill(None, ids, 4, None) == L.E_BADARG
+        assert L.lib.infllm_shard_refill(ctypes.byref(cs), None, 4, None) == L.E_BADARG
+        big = (ctypes.c_int32 * 300)()
+        assert L.lib.infllm_shard_refill(ctypes.byref(cs), big, 300, None) == L.E_BADARG
+        cs.lru = None
+        assert L.lib.infllm_shard_refill(ctypes.byref(cs), ids, 4, None) == L.E_BADARG
+    finally:
+        L.lib.infllm_lru_destroy(lru)
