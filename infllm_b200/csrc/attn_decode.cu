@@ -89,23 +89,25 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
   float m = -INFINITY, l = 0.f;  // running maximum of head g; this thread's share of its row sum
 
   // A run is a contiguous share of the groups outside the device-resolved units plus a contiguous share of the
-  // units' groups, so that every CTA has work of both kinds; the first kind comes first (it needs no retrieval: with
-  // early_rest the kernel has not waited for its predecessor yet), the units' groups second.
+  // units' groups; the CTA's warps divide into two teams in proportion, one per kind, so that both kinds proceed side
+  // by side.  The first kind needs no retrieval: with early_rest its team has not waited for the kernel's
+  // predecessor, only the units' team does.
   const char *kbase = nullptr, *vbase = nullptr;
   char* deposit = nullptr;  // != nullptr: the segment is a unit read in place; its K block's copy in the landing slot
   bool seg_ok = true;
   const int u_beg = P.ind.n_units > 0 ? P.item_begin[P.ind.first_seg] : 0;
   const int u_end = P.ind.n_units > 0 ? P.item_begin[P.ind.first_seg + P.ind.n_units] : 0;
   const int n_unit = u_end - u_beg, n_rest = P.n_items - n_unit;
-#pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {
-  if (pass == 1 && early) chain_wait();
-  const int n_pass = pass ? n_unit : n_rest;
-  const int lo = (int)((int64_t)run * n_pass / P.n_runs), hi = (int)((int64_t)(run + 1) * n_pass / P.n_runs);
+  int w_rest = n_unit == 0 ? kDecWarps : (kDecWarps * n_rest + P.n_items / 2) / P.n_items;
+  if (n_unit > 0 && n_rest > 0) w_rest = w_rest < 1 ? 1 : (w_rest > kDecWarps - 1 ? kDecWarps - 1 : w_rest);
+  const bool unit_team = warp >= w_rest;
+  if (unit_team && early) chain_wait();
+  const int n_kind = unit_team ? n_unit : n_rest, team = unit_team ? kDecWarps - w_rest : w_rest;
+  const int lo = (int)((int64_t)run * n_kind / P.n_runs), hi = (int)((int64_t)(run + 1) * n_kind / P.n_runs);
   int sg = 0, sg_resolved = -1;
 #pragma unroll 1
-  for (int j = lo + warp; j < hi; j += kDecWarps) {
-    const int it = pass ? u_beg + j : (j < u_beg ? j : j + n_unit);
+  for (int j = lo + (unit_team ? warp - w_rest : warp); j < hi; j += team) {
+    const int it = unit_team ? u_beg + j : (j < u_beg ? j : j + n_unit);
     while (it >= P.item_begin[sg + 1]) ++sg;
     const DecodeSeg& S = P.seg[sg];
     if (sg != sg_resolved) {  // pointers of the segment; a memory unit named on the device is looked up here
@@ -257,7 +259,6 @@ __global__ void __launch_bounds__(kDecThreads, 2) attn_decode_kernel(const __gri
       a[3] = __byte_perm(v21[r], v31[r], sel);
       mma16816<T>(ot[i], a, b0, b1);
     }
-  }
   }
   // ---- the warps' results meet in shared memory
   l += __shfl_xor_sync(0xffffffffu, l, 1);
